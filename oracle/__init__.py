@@ -1,0 +1,274 @@
+"""numpy front end of the CPU oracle (liboracle.so, built by oracle/Makefile).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
+CPU-baseline leg of the benchmark. The shipped package never imports it.
+Each function forwards to the C restatement in oracle.c, which cites the
+reference file and lines it follows.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+ACT_NONE, ACT_RELU, ACT_RELU_N1_TO_1, ACT_RELU6, ACT_TANH, ACT_SIGN_BIT, ACT_SIGMOID = range(7)
+REQUANT_MBQM, REQUANT_FLOAT_REF = 0, 1
+
+
+def build(force=False):
+    """Compile liboracle.so / liboracle_fast.so (and oracle/_ref when the reference tree exists)."""
+    targets = ["liboracle.so", "liboracle_fast.so"]
+    if force or not all(os.path.exists(os.path.join(_HERE, t)) for t in targets):
+        subprocess.check_call(["make", "-C", _HERE, "-s", "liboracle.so", "liboracle_fast.so"])
+    if os.path.isdir("/root/reference/tflite") and (
+        force or not os.path.exists(os.path.join(_HERE, "_ref", "libref_quant.so"))
+    ):
+        subprocess.check_call(["make", "-C", _HERE, "-s", "ref"])
+
+
+_lib = None
+_fast = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        _lib = ctypes.CDLL(path)
+        _lib.orc_multiply_by_quantized_multiplier.restype = ctypes.c_int32
+        _lib.orc_multiply_by_quantized_multiplier_i64.restype = ctypes.c_int32
+        _lib.orc_saturating_rounding_doubling_high_mul.restype = ctypes.c_int32
+        _lib.orc_rounding_divide_by_pot.restype = ctypes.c_int32
+        _lib.orc_half_to_float.restype = ctypes.c_float
+        _lib.orc_float_to_half.restype = ctypes.c_uint16
+    return _lib
+
+
+def fast():
+    """The vectorised / multi-threaded twin used only for CPU-baseline timing."""
+    global _fast
+    if _fast is None:
+        path = os.path.join(_HERE, "liboracle_fast.so")
+        if not os.path.exists(path):
+            build()
+        _fast = ctypes.CDLL(path)
+        _fast.orcf_num_threads.restype = ctypes.c_int
+    return _fast
+
+
+def ref_lib():
+    """Reference sources compiled as they are (oracle/_ref); None when not built."""
+    path = os.path.join(_HERE, "_ref", "libref_quant.so")
+    return ctypes.CDLL(path) if os.path.exists(path) else None
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _c(a, dtype):
+    return None if a is None else np.ascontiguousarray(a, dtype=dtype)
+
+
+_f = ctypes.c_float
+_d = ctypes.c_double
+_i = ctypes.c_int
+_i32 = ctypes.c_int32
+
+
+# ---- requantization -------------------------------------------------------
+def quantize_multiplier(m):
+    q, s = _i32(), _i()
+    lib().orc_quantize_multiplier(_d(m), ctypes.byref(q), ctypes.byref(s))
+    return q.value, s.value
+
+
+def multiply_by_quantized_multiplier(x, mult, shift):
+    return lib().orc_multiply_by_quantized_multiplier(_i32(x), _i32(mult), _i(shift))
+
+
+def multiply_by_quantized_multiplier_i64(x, mult, shift):
+    return lib().orc_multiply_by_quantized_multiplier_i64(ctypes.c_int64(x), _i32(mult), _i(shift))
+
+
+def activation_range_int8(activation, out_scale, out_zp):
+    lo, hi = _i32(), _i32()
+    rc = lib().orc_activation_range_int8(_i(activation), _f(out_scale), _i32(out_zp), ctypes.byref(lo), ctypes.byref(hi))
+    if rc:
+        raise ValueError("activation range overflow")
+    return lo.value, hi.value
+
+
+def fc_per_channel_multipliers(input_scale, output_scale, filter_scales):
+    fs = _c(filter_scales, np.float32)
+    n = fs.size
+    mult = np.empty(n, np.int32)
+    shift = np.empty(n, np.int32)
+    lib().orc_fc_per_channel_multipliers(_f(input_scale), _f(output_scale), _p(fs), _i(n), _p(mult), _p(shift))
+    return mult, shift
+
+
+def fc_per_tensor_multiplier(input_scale, filter_scale, bias_scale, output_scale):
+    q, s = _i32(), _i()
+    rc = lib().orc_fc_per_tensor_multiplier(
+        _f(input_scale), _f(filter_scale), _i(0 if bias_scale is None else 1),
+        _f(0.0 if bias_scale is None else bias_scale), _f(output_scale), ctypes.byref(q), ctypes.byref(s))
+    if rc:
+        raise ValueError("bias scale check failed")
+    return q.value, s.value
+
+
+# ---- full-integer FC ------------------------------------------------------
+def fc_int8_per_channel(x, w, bias, input_zp, input_scale, filter_scales, output_scale, output_zp,
+                        activation=ACT_NONE, requant=REQUANT_MBQM):
+    x = _c(x, np.int8)
+    w = _c(w, np.int8)
+    n, k = w.shape
+    m = x.size // k
+    bias = _c(bias, np.int32)
+    fs = _c(filter_scales, np.float32)
+    mult, shift = fc_per_channel_multipliers(input_scale, output_scale, fs)
+    lo, hi = activation_range_int8(activation, output_scale, output_zp)
+    y = np.empty((m, n), np.int8)
+    lib().orc_fc_int8_per_channel(_i(requant), _i(m), _i(n), _i(k), _p(x), _p(w), _p(bias), _i32(-input_zp),
+                                  _i32(output_zp), _p(mult), _p(shift), _f(input_scale), _f(output_scale),
+                                  _p(fs), _i32(lo), _i32(hi), _p(y))
+    return y
+
+
+def fc_int8_per_tensor(x, w, bias, input_zp, input_scale, filter_zp, filter_scale, output_scale, output_zp,
+                       activation=ACT_NONE, bias_scale=None):
+    x = _c(x, np.int8)
+    w = _c(w, np.int8)
+    n, k = w.shape
+    m = x.size // k
+    bias = _c(bias, np.int32)
+    if bias is not None and bias_scale is None:
+        bias_scale = np.float32(input_scale) * np.float32(filter_scale)
+    mult, shift = fc_per_tensor_multiplier(input_scale, filter_scale, bias_scale if bias is not None else None,
+                                           output_scale)
+    lo, hi = activation_range_int8(activation, output_scale, output_zp)
+    y = np.empty((m, n), np.int8)
+    lib().orc_fc_int8_per_tensor(_i(m), _i(n), _i(k), _p(x), _p(w), _p(bias), _i32(-input_zp), _i32(-filter_zp),
+                                 _i32(output_zp), _i32(mult), _i(shift), _i32(lo), _i32(hi), _p(y))
+    return y
+
+
+# ---- hybrid ---------------------------------------------------------------
+def batch_quantize_floats(x, asymmetric=True):
+    x = _c(x, np.float32)
+    m, k = x.shape
+    q = np.empty((m, k), np.int8)
+    scales = np.empty(m, np.float32)
+    zps = np.zeros(m, np.int32)
+    lib().orc_batch_quantize_floats(_p(x), _i(m), _i(k), _p(q), _p(scales), _p(zps), _i(1 if asymmetric else 0))
+    return q, scales, zps
+
+
+def fc_hybrid(x, w, filter_scales, bias=None, asymmetric_inputs=True, activation=ACT_NONE):
+    w = _c(w, np.int8)
+    n, k = w.shape
+    x = _c(x, np.float32).reshape(-1, k)
+    m = x.shape[0]
+    fs = np.atleast_1d(_c(filter_scales, np.float32))
+    per_channel = 1 if fs.size > 1 else 0
+    bias = _c(bias, np.float32)
+    y = np.empty((m, n), np.float32)
+    lib().orc_fc_hybrid(_i(m), _i(n), _i(k), _p(x), _p(w), _p(fs), _i(per_channel), _p(bias),
+                        _i(1 if asymmetric_inputs else 0), _i(activation), _p(y))
+    return y
+
+
+def fc_blockwise4(x, w4, scales_f16, blocksize, bias=None):
+    """w4: uint8 [n, ceil(k/2)] packed low nibble first; scales_f16: float16 [n, k/blocksize]."""
+    w4 = _c(w4, np.uint8)
+    sc = np.ascontiguousarray(scales_f16, dtype=np.float16)
+    n = w4.shape[0]
+    k = sc.shape[1] * blocksize
+    x = _c(x, np.float32).reshape(-1, k)
+    m = x.shape[0]
+    bias = _c(bias, np.float32)
+    y = np.empty((m, n), np.float32)
+    lib().orc_fc_blockwise4(_i(m), _i(n), _i(k), _i(blocksize), _p(x), _p(w4), _p(sc.view(np.uint16)), _p(bias),
+                            _p(y))
+    return y
+
+
+def unpack_int4(w4, num_elements):
+    w4 = _c(w4, np.uint8)
+    out = np.empty(num_elements, np.int8)
+    lib().orc_unpack_int4(_p(w4), _i(num_elements), _p(out))
+    return out
+
+
+def pack_int4(values):
+    """int8 values in [-8,7], last dim even -> uint8 packed, element 2i in the low nibble."""
+    v = np.asarray(values, np.int8)
+    assert v.shape[-1] % 2 == 0
+    u = (v.astype(np.uint8) & 0xF)
+    return (u[..., 0::2] | (u[..., 1::2] << 4)).astype(np.uint8)
+
+
+# ---- BATCH_MATMUL ---------------------------------------------------------
+def _dims(a):
+    return (ctypes.c_int * a.ndim)(*a.shape)
+
+
+def _bmm_out_shape(x, y, adj_x, adj_y):
+    xs, ys = list(x.shape), list(y.shape)
+    a = xs[-1] if adj_x else xs[-2]
+    c = ys[-2] if adj_y else ys[-1]
+    rank = max(len(xs), len(ys))
+    xb = [1] * (rank - len(xs)) + xs[:-2]
+    yb = [1] * (rank - len(ys)) + ys[:-2]
+    batch = [max(p, q) for p, q in zip(xb, yb)]
+    return tuple(batch + [a, c])
+
+
+def batch_matmul_float(x, y, adj_x=False, adj_y=False):
+    x = _c(x, np.float32)
+    y = _c(y, np.float32)
+    out = np.empty(_bmm_out_shape(x, y, adj_x, adj_y), np.float32)
+    lib().orc_batch_matmul_float(_i(x.ndim), _dims(x), _p(x), _i(y.ndim), _dims(y), _p(y), _i(adj_x), _i(adj_y),
+                                 _p(out))
+    return out
+
+
+def batch_matmul_hybrid(x, y, y_scale, adj_x=False, adj_y=False, asymmetric_inputs=True):
+    x = _c(x, np.float32)
+    y = _c(y, np.int8)
+    out = np.empty(_bmm_out_shape(x, y, adj_x, adj_y), np.float32)
+    lib().orc_batch_matmul_hybrid(_i(x.ndim), _dims(x), _p(x), _i(y.ndim), _dims(y), _p(y), _f(y_scale),
+                                  _i(adj_x), _i(adj_y), _i(1 if asymmetric_inputs else 0), _p(out))
+    return out
+
+
+def batch_matmul_int8(x, x_zp, x_scale, y, y_zp, y_scale, out_scale, out_zp, adj_x=False, adj_y=False):
+    x = _c(x, np.int8)
+    y = _c(y, np.int8)
+    # tflite/kernels/batch_matmul.cc:315-321: multiplier from the float product of the two scales.
+    mult, shift = fc_per_tensor_multiplier(x_scale, y_scale, None, out_scale)
+    out = np.empty(_bmm_out_shape(x, y, adj_x, adj_y), np.int8)
+    lib().orc_batch_matmul_int8(_i(x.ndim), _dims(x), _p(x), _i32(x_zp), _i(y.ndim), _dims(y), _p(y), _i32(y_zp),
+                                _i(adj_x), _i(adj_y), _i32(mult), _i(shift), _i32(out_zp), _p(out))
+    return out
+
+
+# ---- SDPA -----------------------------------------------------------------
+def sdpa_f32(q, k, v, mask=None, scale=None, logit_cap=0.0):
+    q = _c(q, np.float32)
+    k = _c(k, np.float32)
+    v = _c(v, np.float32)
+    b, t, n, h = q.shape
+    s, nkv = k.shape[1], k.shape[2]
+    if scale is None or scale <= 0:
+        scale = 1.0 / np.sqrt(np.float32(h))  # tflite/experimental/genai/sdpa.cc:99-105
+    mask = _c(mask, np.float32)
+    out = np.empty_like(q)
+    lib().orc_sdpa_f32(_i(b), _i(t), _i(n), _i(nkv), _i(h), _i(s), _p(q), _p(k), _p(v), _p(mask),
+                       _f(scale), _f(logit_cap), _p(out))
+    return out
