@@ -1,0 +1,144 @@
+/*
+ * litert_b200 -- C ABI of the B200 (sm_100a) kernels behind the LiteRT /
+ * TFLite quantized-inference hot path: FULLY_CONNECTED and BATCH_MATMUL with
+ * full-integer int8, dynamic-range (hybrid) int8 and blockwise int4 weights,
+ * and the odml.scaled_dot_product_attention decode step.
+ *
+ * This is the boundary a host runtime binds: plain pointers and sizes, no C++
+ * or torch types. Every pointer named d_* is a device pointer on the current
+ * CUDA device; `stream` is a cudaStream_t passed as void* (NULL = default
+ * stream). Calls enqueue work and return without synchronising. Return value:
+ * B200_OK or an error code; b200_last_error() gives the message of the last
+ * failure on the calling thread. Reference interfaces cited below are paths
+ * inside the LiteRT source tree.
+ *
+ * Weights are repacked once (b200_pack_w8 / b200_pack_w4) into the tiled
+ * device layout the kernels stream; activations stay in the reference's
+ * row-major layouts at this boundary.
+ */
+#ifndef LITERT_B200_H_
+#define LITERT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_API __attribute__((visibility("default")))
+
+enum {
+  B200_OK = 0,
+  B200_ERR_INVALID_ARGUMENT = 1,
+  B200_ERR_CUDA = 2,
+  B200_ERR_KERNEL_TIMEOUT = 3, /* a bounded device-side wait ran out */
+  B200_ERR_UNSUPPORTED = 4
+};
+
+/* Fused activations, numbered like TfLiteFusedActivation
+ * (tflite/converter/core/c/builtin_op_data.h). */
+enum {
+  B200_ACT_NONE = 0,
+  B200_ACT_RELU = 1,
+  B200_ACT_RELU_N1_TO_1 = 2,
+  B200_ACT_RELU6 = 3,
+  B200_ACT_TANH = 4,
+  B200_ACT_SIGN_BIT = 5,
+  B200_ACT_SIGMOID = 6
+};
+
+enum { B200_DTYPE_F16 = 0, B200_DTYPE_I8 = 1, B200_DTYPE_F32 = 2 };
+
+B200_API int b200_abi_version(void);
+B200_API const char* b200_last_error(void);
+
+/* ---- workspaces ---------------------------------------------------------
+ * Two device buffers, owned by the caller, may be shared by all ops that run
+ * on one stream (ops on different streams need their own):
+ *  - the "zero workspace": fixed size, cleared once with
+ *    b200_zero_workspace_init; kernels leave it cleared after every call. Its
+ *    first int is a status word (see b200_read_status).
+ *  - the "scratch": sized per op shape, no initial contents required; takes
+ *    the role of the temporary tensors the reference op allocates
+ *    (tflite/kernels/fully_connected.cc:602-719: input_quantized,
+ *    scaling_factors, input_offsets). */
+B200_API size_t b200_zero_workspace_bytes(void);
+B200_API int b200_zero_workspace_init(void* d_zero_ws, void* stream);
+B200_API size_t b200_fc_scratch_bytes(int m, int k);
+/* Copies the status word to the host (synchronises the stream). 0 = ok. */
+B200_API int b200_read_status(void* d_zero_ws, void* stream, int* status_out);
+
+/* ---- weight preparation (once per constant tensor) ----------------------
+ * int8 weights [n,k] row-major, as a FULLY_CONNECTED filter tensor lies in
+ * the model (tflite/kernels/fully_connected.cc:498-503). d_row_sums [n]
+ * (optional) receives sum_k w[n,k], the reference's cached row_sums temporary
+ * (tflite/kernels/fully_connected.cc:697-708). */
+B200_API size_t b200_packed_w8_bytes(int n, int k);
+B200_API int b200_pack_w8(const int8_t* d_w, int n, int k, void* d_packed, int32_t* d_row_sums, void* stream);
+
+/* int4 weights: n rows of ((k+1)&~1)/2 bytes, element 2i in the low nibble
+ * (tflite/kernels/fully_connected.cc:1053-1067), fp16 scales
+ * [n, k/blocksize] (TfLiteBlockwiseQuantization, tflite/core/c/common.h:390-398).
+ * d_kfsum [n] receives the activation-independent zero-point term. */
+B200_API size_t b200_packed_w4_bytes(int n, int k);
+B200_API int b200_pack_w4(const uint8_t* d_w4, const uint16_t* d_scales_f16, int n, int k, int blocksize,
+                          void* d_packed, float* d_kfsum, void* stream);
+
+/* ---- activation quantization --------------------------------------------
+ * Replaces tensor_utils::BatchQuantizeFloats
+ * (tflite/kernels/internal/portable_tensor_utils.h:158-176): per row of
+ * x [m,k], int8 values (row-major d_q), scale and zero point. */
+B200_API int b200_quantize_rows(const float* d_x, int m, int k, int asymmetric, int8_t* d_q, float* d_scales,
+                                int32_t* d_zero_points, void* stream);
+
+/* ---- FULLY_CONNECTED ------------------------------------------------------
+ * Full-integer int8. Replaces FullyConnectedPerChannelInt8 / FullyConnectedInt8
+ * (tflite/kernels/fully_connected.cc:1383-1421, 1255-1285) i.e.
+ * reference_integer_ops::FullyConnected[PerChannel]
+ * (tflite/kernels/internal/reference/integer_ops/fully_connected.h:33-77,
+ * 134-180). y = clamp(MBQM(sum (w+filter_offset)(x+input_offset) + bias,
+ * mult, shift) + output_offset). per_channel != 0: d_multipliers/d_shifts have
+ * n entries and filter_offset must be 0; else one entry. */
+B200_API int b200_fc_int8(const int8_t* d_x, int m, int k, const void* d_w_packed, int n,
+                          const int32_t* d_row_sums, const int32_t* d_bias, int32_t input_offset,
+                          int32_t filter_offset, int32_t output_offset, const int32_t* d_multipliers,
+                          const int32_t* d_shifts, int per_channel, int32_t act_min, int32_t act_max,
+                          int8_t* d_y, void* d_zero_ws, void* d_scratch, size_t scratch_bytes, void* stream);
+
+/* Dynamic-range hybrid. Replaces EvalHybridDense
+ * (tflite/kernels/fully_connected.cc:763-858): per-row input quantization,
+ * int8 dot products, y = act(bias + (dot - row_sum*zp) * in_scale * w_scale).
+ * d_w_scales has n entries (per_channel) or 1. */
+B200_API int b200_fc_hybrid(const float* d_x, int m, int k, const void* d_w_packed, int n,
+                            const int32_t* d_row_sums, const float* d_w_scales, int per_channel,
+                            const float* d_bias, int asymmetric_inputs, int activation, float* d_y,
+                            void* d_zero_ws, void* d_scratch, size_t scratch_bytes, void* stream);
+
+/* Blockwise int4. Replaces EvalBlockwise4Bit
+ * (tflite/kernels/fully_connected.cc:1014-1086): always asymmetric inputs, no
+ * fused activation. blocksize must be a multiple of 32. */
+B200_API int b200_fc_w4(const float* d_x, int m, int k, const void* d_w4_packed, int n, int blocksize,
+                        const float* d_kfsum, const float* d_bias, float* d_y, void* d_zero_ws,
+                        void* d_scratch, size_t scratch_bytes, void* stream);
+
+/* ---- odml.scaled_dot_product_attention, one query token -------------------
+ * Replaces ops::custom::llm::SDPAEval (tflite/experimental/genai/sdpa.cc:361-662)
+ * for T = 1. q/out [b,1,n,h] (f16 or f32), k/v [b,s_max,nkv,h] (f16, int8 with
+ * one f32 scale per cached token and kv head in d_k_scale/d_v_scale
+ * [b,s_max,nkv], or f32). d_lengths [b] (optional) bounds the attended prefix
+ * per sequence; d_mask [b,1,1,s_max] (optional) is the reference's additive
+ * mask. scale <= 0 means 1/sqrt(h) (sdpa.cc:99-105). logit_cap > 0 applies
+ * cap*tanh(x/cap) before the mask
+ * (tflite/delegates/xnnpack/xnnpack_delegate.cc:6639-6678). */
+B200_API size_t b200_sdpa_workspace_bytes(int b, int n, int h, int s_max);
+B200_API int b200_sdpa_decode(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale,
+                              const float* d_v_scale, const int32_t* d_lengths, const float* d_mask,
+                              void* d_out, int b, int n, int nkv, int h, int s_max, int q_dtype, int kv_dtype,
+                              float scale, float logit_cap, void* d_workspace, size_t workspace_bytes,
+                              void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LITERT_B200_H_ */

@@ -1,0 +1,61 @@
+"""ctypes binding of the C ABI (include/litert_b200.h). Fails loudly when the library is missing."""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "liblitert_b200.so")
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_i32 = ctypes.c_int32
+_sz = ctypes.c_size_t
+_f = ctypes.c_float
+
+# name -> (restype, argtypes); mirrors include/litert_b200.h one to one
+SIGNATURES = {
+    "b200_abi_version": (_i, []),
+    "b200_last_error": (ctypes.c_char_p, []),
+    "b200_zero_workspace_bytes": (_sz, []),
+    "b200_zero_workspace_init": (_i, [_vp, _vp]),
+    "b200_fc_scratch_bytes": (_sz, [_i, _i]),
+    "b200_read_status": (_i, [_vp, _vp, ctypes.POINTER(_i)]),
+    "b200_packed_w8_bytes": (_sz, [_i, _i]),
+    "b200_pack_w8": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
+    "b200_packed_w4_bytes": (_sz, [_i, _i]),
+    "b200_pack_w4": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "b200_quantize_rows": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "b200_fc_int8": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _i, _i32, _i32, _vp, _vp, _vp,
+                          _sz, _vp]),
+    "b200_fc_hybrid": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
+    "b200_fc_w4": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "b200_sdpa_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "b200_sdpa_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _sz,
+                              _vp]),
+}
+
+_lib = None
+
+
+class B200Error(RuntimeError):
+    pass
+
+
+def load():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise B200Error(
+                f"{LIB_PATH} is missing: build it with `python -m litert_b200.build` "
+                "(there is no CPU fallback in this package)")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the export is missing
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        raise B200Error(f"litert_b200 error {rc}: {load().b200_last_error().decode()}")

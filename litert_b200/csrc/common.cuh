@@ -1,0 +1,163 @@
+// Shared device helpers for the sm_100a kernels: mbarrier and bulk-copy PTX
+// wrappers with bounded waits, the legacy tensor-core int8/f16 MMA wrappers,
+// and the tile geometry of the packed weight layouts.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+// ---- packed layouts -------------------------------------------------------
+// Weights are repacked once into tiles that one bulk copy moves and that both
+// MMA paths read without bank conflicts. A tile covers kTileN output channels
+// by kTileK8 reduction bytes. Inside a tile the unit is a "core matrix": 8
+// rows x 16 bytes, stored as 128 contiguous bytes (row r at byte 16 r). Core
+// matrices are ordered [row group (kTileN/8)][16-byte K chunk]. This is also
+// the canonical K-major, non-swizzled operand layout of tcgen05.mma, so the
+// same packed buffer feeds the TMEM kernels.
+constexpr int kTileN = 128;        // output channels per tile
+constexpr int kTileK8 = 128;       // int8 reduction elements per tile
+constexpr int kTileBytes = kTileN * kTileK8;  // 16 KiB
+constexpr int kRowGroups = kTileN / 8;        // 16
+constexpr int kChunks8 = kTileK8 / 16;        // 8 core matrices along K
+
+// 4-bit tiles: kTileN rows x 256 reduction elements (8 sub-blocks of 32), the
+// same 16 KiB of nibbles, followed by kTileN x 8 fp16 scales (2 KiB).
+constexpr int kTileK4 = 256;
+constexpr int kSubBlocks4 = kTileK4 / 32;                     // 8
+constexpr int kTile4ScaleBytes = kTileN * kSubBlocks4 * 2;    // 2 KiB
+constexpr int kTile4Bytes = kTileBytes + kTile4ScaleBytes;    // 18 KiB
+
+// Status word values written by kernels (0 = ok).
+enum : int {
+  kStatusOk = 0,
+  kStatusWaitTimeoutFull = 101,   // consumer gave up waiting for a stage
+  kStatusWaitTimeoutEmpty = 102,  // producer gave up waiting for a free stage
+  kStatusWaitTimeoutTmem = 103,
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- mbarrier -------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Every wait in these kernels is bounded. When a wait runs out, the thread
+// records why in *status, raises the CTA-wide abort flag and carries on as if
+// the wait had succeeded: control flow stays uniform (every barrier is still
+// reached, every accumulator still freed), later waits return at once, the
+// kernel ends, and the host sees a non-zero status instead of a hung GPU.
+constexpr uint32_t kWaitSpins = 1u << 22;
+
+__device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  int* status, int code) {
+  if (*abort_flag) return;
+  for (uint32_t i = 0; i < kWaitSpins; ++i) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((i & 1023u) == 1023u && *abort_flag) return;
+  }
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+}
+
+// ---- bulk async copy (TMA engine, linear form) ------------------------------
+// Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// ---- legacy tensor-core MMA -------------------------------------------------
+// D(16x8,s32) += A(16x32,s8,row) * B(32x8,s8,col)
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Sub-CTA barrier over `count` threads (count a multiple of 32), id 1..15.
+__device__ __forceinline__ void named_barrier(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// ---- fixed-point requantization (int32 accumulator -> int32) --------------
+// Same arithmetic as tflite/kernels/internal/common.cc:81-90
+// (MultiplyByQuantizedMultiplier, double rounding): x * 2^left, then the
+// nearest integer to (that * multiplier) / 2^31 with ties toward +infinity and
+// saturation for INT32_MIN^2, then a rounding right shift with ties away from
+// zero.
+__device__ __forceinline__ int32_t requantize_mbqm(int32_t x, int32_t multiplier, int shift) {
+  const int left = shift > 0 ? shift : 0;
+  const int right = shift > 0 ? 0 : -shift;
+  const int32_t xs = static_cast<int32_t>(static_cast<uint32_t>(x) << left);
+  int32_t hi;
+  if (xs == INT32_MIN && multiplier == INT32_MIN) {
+    hi = INT32_MAX;
+  } else {
+    const long long ab = static_cast<long long>(xs) * static_cast<long long>(multiplier);
+    hi = static_cast<int32_t>((ab + (1ll << 30)) >> 31);
+  }
+  if (right == 0) return hi;
+  const int32_t mask = static_cast<int32_t>((1u << right) - 1u);
+  const int32_t rem = hi & mask;
+  const int32_t threshold = (mask >> 1) + (hi < 0 ? 1 : 0);
+  return (hi >> right) + (rem > threshold ? 1 : 0);
+}
+
+// Float fused activations of the hybrid path, numbered like
+// TfLiteFusedActivation (tflite/kernels/internal/tensor_utils.h:58-80).
+__device__ __forceinline__ float apply_activation(float v, int act) {
+  switch (act) {
+    case 1: return fmaxf(0.0f, v);
+    case 2: return fmaxf(-1.0f, fminf(v, 1.0f));
+    case 3: return fmaxf(0.0f, fminf(v, 6.0f));
+    case 4: return tanhf(v);
+    case 5: return signbit(v) ? 1.0f : 0.0f;
+    case 6: return 1.0f / (1.0f + expf(-v));
+    default: return v;
+  }
+}
+
+}  // namespace b200

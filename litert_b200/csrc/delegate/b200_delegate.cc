@@ -1,0 +1,846 @@
+// TfLiteDelegate for the B200 kernels: claims FULLY_CONNECTED, BATCH_MATMUL
+// (constant right-hand side) and the odml.scaled_dot_product_attention
+// composite / custom op, and runs them through the C ABI in
+// include/litert_b200.h. Built as an external-delegate plugin
+// (tflite/delegates/external/external_delegate_interface.h:64-73).
+//
+// Contract followed (tflite/core/c/common.h:1442-1493 and
+// tflite/core/subgraph.cc:2497-2622): Prepare walks the execution plan, asks
+// the runtime to replace the supported node subsets with one delegate kernel
+// each; the kernel's init uploads and repacks constant weights once, prepare
+// plans the device arena for the partition's tensors, invoke copies the
+// partition inputs to the device, enqueues the ops on the delegate's stream
+// and brings the outputs back (or publishes buffer handles). There is no CPU
+// fallback inside the delegate: an unsupported node is simply not claimed.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include <cuda_runtime_api.h>
+
+#include "../../../include/litert_b200.h"
+#include "../../../include/litert_b200_delegate.h"
+#include "device_arena.h"
+#include "flex_scale.h"
+#include "tflite/builtin_ops.h"
+#include "tflite/core/c/builtin_op_data.h"
+#include "tflite/core/c/common.h"
+
+namespace {
+
+constexpr char kSdpaName[] = "odml.scaled_dot_product_attention";
+constexpr char kDelegateName[] = "B200Delegate";
+
+struct Options {
+  int device = 0;
+  std::string fail_on;          // "", "init", "prepare", "invoke", "alloc": host-side fault injection
+  bool buffer_handles = false;  // publish outputs as buffer handles instead of copying back in invoke
+  bool claim_fc = true, claim_bmm = true, claim_sdpa = true;
+  int min_nodes_per_partition = 1;
+};
+
+#define CUDA_OK(ctx, expr)                                                             \
+  do {                                                                                 \
+    cudaError_t _e = (expr);                                                           \
+    if (_e != cudaSuccess) {                                                           \
+      TF_LITE_KERNEL_LOG((ctx), "B200 delegate: %s failed: %s", #expr, cudaGetErrorString(_e)); \
+      return kTfLiteDelegateError;                                                     \
+    }                                                                                  \
+  } while (0)
+
+#define B200_OK_OR_RETURN(ctx, expr)                                                   \
+  do {                                                                                 \
+    int _rc = (expr);                                                                  \
+    if (_rc != B200_OK) {                                                              \
+      TF_LITE_KERNEL_LOG((ctx), "B200 delegate: %s", b200_last_error());               \
+      return kTfLiteDelegateError;                                                     \
+    }                                                                                  \
+  } while (0)
+
+// ---------------------------------------------------------------- device helpers
+struct DeviceMem {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  ~DeviceMem() { reset(); }
+  void reset() {
+    if (ptr) cudaFree(ptr);
+    ptr = nullptr;
+    bytes = 0;
+  }
+  bool ensure(size_t n) {
+    if (n <= bytes) return true;
+    reset();
+    if (cudaMalloc(&ptr, n) != cudaSuccess) return false;
+    bytes = n;
+    return true;
+  }
+};
+
+struct DelegateState {
+  Options options;
+  TfLiteDelegate delegate;
+  cudaStream_t stream = nullptr;
+  DeviceMem zero_ws, scratch, sdpa_ws;
+  bool ready = false;
+  // buffer handles: handle id -> (device pointer, bytes)
+  std::unordered_map<int, std::pair<const void*, size_t>> handles;
+  int next_handle = 1;
+  int delegated_nodes = 0, partitions = 0;
+
+  TfLiteStatus EnsureDevice(TfLiteContext* ctx) {
+    CUDA_OK(ctx, cudaSetDevice(options.device));
+    if (ready) return kTfLiteOk;
+    CUDA_OK(ctx, cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    if (!zero_ws.ensure(b200_zero_workspace_bytes())) {
+      TF_LITE_KERNEL_LOG(ctx, "B200 delegate: cannot allocate the zero workspace");
+      return kTfLiteDelegateError;
+    }
+    B200_OK_OR_RETURN(ctx, b200_zero_workspace_init(zero_ws.ptr, stream));
+    ready = true;
+    return kTfLiteOk;
+  }
+};
+
+static void* ArenaAlloc(void* user, size_t bytes) {
+  auto* st = static_cast<DelegateState*>(user);
+  if (st->options.fail_on == "alloc") return nullptr;
+  void* p = nullptr;
+  return cudaMalloc(&p, bytes) == cudaSuccess ? p : nullptr;
+}
+static void ArenaFree(void*, void* p) { cudaFree(p); }
+
+// ---------------------------------------------------------------- node classification
+enum class OpKind { kNone, kFcInt8, kFcHybrid, kFcW4, kBmmHybrid, kBmmInt8, kSdpa };
+
+inline bool IsConst(const TfLiteTensor& t) { return t.allocation_type == kTfLiteMmapRo && t.data.raw != nullptr; }
+
+inline int64_t NumElements(const TfLiteTensor& t) {
+  int64_t n = 1;
+  for (int i = 0; i < t.dims->size; ++i) n *= t.dims->data[i];
+  return n;
+}
+
+inline const TfLiteAffineQuantization* Affine(const TfLiteTensor& t) {
+  return t.quantization.type == kTfLiteAffineQuantization
+             ? static_cast<const TfLiteAffineQuantization*>(t.quantization.params)
+             : nullptr;
+}
+
+bool IsSdpaNode(const TfLiteNode* node, const TfLiteRegistration* reg) {
+  if (reg->builtin_code == kTfLiteBuiltinStablehloComposite) {
+    // tflite/delegates/xnnpack/xnnpack_delegate.cc:3400-3408 recognises the composite by name
+    const auto* p = static_cast<const TfLiteStablehloCompositeParams*>(node->builtin_data);
+    return p && p->name && strcmp(p->name, kSdpaName) == 0;
+  }
+  if (reg->builtin_code == kTfLiteBuiltinCustom) {
+    return reg->custom_name && strcmp(reg->custom_name, kSdpaName) == 0;  // xnnpack_delegate.cc:3443-3444
+  }
+  return false;
+}
+
+// Why a node is not claimed is reported through `why` (one line).
+OpKind Classify(TfLiteContext* ctx, const TfLiteNode* node, const TfLiteRegistration* reg, const Options& opt,
+                std::string* why) {
+  const TfLiteTensor* T = ctx->tensors;
+  auto in = [&](int i) -> const TfLiteTensor* {
+    if (i >= node->inputs->size) return nullptr;
+    const int idx = node->inputs->data[i];
+    return idx == kTfLiteOptionalTensor ? nullptr : &T[idx];
+  };
+  if (reg->builtin_code == kTfLiteBuiltinFullyConnected && opt.claim_fc) {
+    const auto* p = static_cast<const TfLiteFullyConnectedParams*>(node->builtin_data);
+    const TfLiteTensor *x = in(0), *w = in(1), *b = in(2);
+    const TfLiteTensor* y = &T[node->outputs->data[0]];
+    if (!p || !x || !w) return *why = "missing operands", OpKind::kNone;
+    if (p->weights_format != kTfLiteFullyConnectedWeightsFormatDefault) return *why = "shuffled weights", OpKind::kNone;
+    if (w->sparsity) return *why = "sparse weights", OpKind::kNone;
+    if (!IsConst(*w) || w->dims->size != 2) return *why = "weights not a constant matrix", OpKind::kNone;
+    if (b && !IsConst(*b)) return *why = "bias not constant", OpKind::kNone;
+    if (x->dims->size < 1 || NumElements(*x) % w->dims->data[1] != 0) return *why = "input shape", OpKind::kNone;
+    if (x->type == kTfLiteInt8 && w->type == kTfLiteInt8 && y->type == kTfLiteInt8) {
+      const auto* q = Affine(*w);
+      if (!q || !q->scale || q->scale->size < 1) return *why = "weights lack affine quantization", OpKind::kNone;
+      if (b && b->type != kTfLiteInt32) return *why = "bias type", OpKind::kNone;
+      if (q->scale->size > 1 && (q->quantized_dimension != 0 || q->scale->size != w->dims->data[0]))
+        return *why = "per-channel axis must be 0", OpKind::kNone;  // fully_connected.cc:539
+      if (p->activation != kTfLiteActNone && p->activation != kTfLiteActRelu &&
+          p->activation != kTfLiteActReluN1To1 && p->activation != kTfLiteActRelu6)
+        return *why = "activation", OpKind::kNone;  // fully_connected.cc:748-753
+      return OpKind::kFcInt8;
+    }
+    if (x->type == kTfLiteFloat32 && w->type == kTfLiteInt8 && y->type == kTfLiteFloat32) {
+      if (b && b->type != kTfLiteFloat32) return *why = "bias type", OpKind::kNone;
+      const auto* q = Affine(*w);
+      if (q && q->scale && q->scale->size > 1 && (q->quantized_dimension != 0 || q->scale->size != w->dims->data[0]))
+        return *why = "per-channel axis must be 0", OpKind::kNone;
+      return OpKind::kFcHybrid;
+    }
+    if (x->type == kTfLiteFloat32 && w->type == kTfLiteInt4 && y->type == kTfLiteFloat32 &&
+        w->quantization.type == kTfLiteBlockwiseQuantization) {
+      const auto* q = static_cast<const TfLiteBlockwiseQuantization*>(w->quantization.params);
+      if (!q || q->blocksize != 32) return *why = "blocksize", OpKind::kNone;
+      const TfLiteTensor& s = T[q->scale];
+      if (!IsConst(s) || s.type != kTfLiteFloat16) return *why = "block scales", OpKind::kNone;
+      if (w->dims->data[1] % q->blocksize) return *why = "k not a multiple of the blocksize", OpKind::kNone;
+      if (b && b->type != kTfLiteFloat32) return *why = "bias type", OpKind::kNone;
+      return OpKind::kFcW4;
+    }
+    return *why = "tensor types", OpKind::kNone;
+  }
+  if (reg->builtin_code == kTfLiteBuiltinBatchMatmul && opt.claim_bmm) {
+    const auto* p = static_cast<const TfLiteBatchMatMulParams*>(node->builtin_data);
+    const TfLiteTensor *x = in(0), *w = in(1);
+    const TfLiteTensor* y = &T[node->outputs->data[0]];
+    if (!p || !x || !w) return *why = "missing operands", OpKind::kNone;
+    if (p->adj_x) return *why = "adj_x", OpKind::kNone;
+    if (!IsConst(*w) || w->dims->size != 2) return *why = "rhs not a constant matrix", OpKind::kNone;
+    if (x->dims->size < 2) return *why = "lhs rank", OpKind::kNone;
+    if (x->type == kTfLiteFloat32 && w->type == kTfLiteInt8 && y->type == kTfLiteFloat32) {
+      const auto* q = Affine(*w);
+      if (q && q->scale && q->scale->size > 1) return *why = "per-channel rhs", OpKind::kNone;
+      return OpKind::kBmmHybrid;
+    }
+    if (x->type == kTfLiteInt8 && w->type == kTfLiteInt8 && y->type == kTfLiteInt8) return OpKind::kBmmInt8;
+    return *why = "tensor types", OpKind::kNone;
+  }
+  if (opt.claim_sdpa && IsSdpaNode(node, reg)) {
+    if (node->inputs->size < 3) return *why = "sdpa operands", OpKind::kNone;
+    const TfLiteTensor *q = in(0), *k = in(1), *v = in(2), *m = in(3);
+    const TfLiteTensor* y = &T[node->outputs->data[0]];
+    if (!q || !k || !v) return *why = "sdpa operands", OpKind::kNone;
+    for (const TfLiteTensor* t : {q, k, v, y})
+      if (t->type != kTfLiteFloat32 || t->dims->size != 4) return *why = "sdpa wants 4-D float32", OpKind::kNone;
+    if (m && (m->type != kTfLiteFloat32 || m->dims->size != 4)) return *why = "sdpa mask", OpKind::kNone;
+    const int B = q->dims->data[0], Tq = q->dims->data[1], N = q->dims->data[2], H = q->dims->data[3];
+    const int S = k->dims->data[1], Nkv = k->dims->data[2];
+    if (Tq != 1) return *why = "sdpa with more than one query token", OpKind::kNone;
+    if (k->dims->data[0] != B || v->dims->data[0] != B || k->dims->data[3] != H || v->dims->data[3] != H ||
+        v->dims->data[1] != S || v->dims->data[2] != Nkv || Nkv <= 0 || N % Nkv != 0)
+      return *why = "sdpa shapes", OpKind::kNone;  // xnnpack_delegate.cc:6433-6459
+    if (m && (m->dims->data[0] != B || m->dims->data[1] != 1 || m->dims->data[2] != Tq || m->dims->data[3] != S))
+      return *why = "sdpa mask shape", OpKind::kNone;
+    return OpKind::kSdpa;
+  }
+  return *why = "op not on the hot path", OpKind::kNone;
+}
+
+// ---------------------------------------------------------------- delegate kernel
+struct OpRecord {
+  OpKind kind = OpKind::kNone;
+  int node_index = -1;
+  int x = -1, y = -1;              // tensor indices (graph numbering)
+  int q = -1, k = -1, v = -1, mask = -1;
+  int m = 0, n = 0, kdim = 0;
+  // constants on the device
+  DeviceMem packed, row_sums, w_scales, bias, mult, shift, kfsum;
+  bool per_channel = false, asymmetric = false;
+  int activation = 0;
+  int32_t input_offset = 0, filter_offset = 0, output_offset = 0, act_min = -128, act_max = 127;
+  // sdpa
+  int B = 0, N = 0, Nkv = 0, H = 0, S = 0;
+  float scale = 0.0f, logit_cap = 0.0f;
+};
+
+// int32 requantization constants, computed as the reference's Prepare does
+// (tflite/kernels/fully_connected.cc:552-582, tflite/kernels/internal/quantization_util.cc:53-104,
+// tflite/kernels/kernel_util.cc:354-410).
+void QuantizeMultiplier(double m, int32_t* q, int* shift) {
+  if (m == 0.) {
+    *q = 0;
+    *shift = 0;
+    return;
+  }
+  const double f = std::frexp(m, shift);
+  int64_t q_fixed = static_cast<int64_t>(std::round(f * (1LL << 31)));
+  if (q_fixed == (1LL << 31)) {
+    q_fixed /= 2;
+    ++*shift;
+  }
+  if (*shift < -31) {
+    *shift = 0;
+    q_fixed = 0;
+  }
+  *q = static_cast<int32_t>(q_fixed);
+}
+
+bool ActivationRangeInt8(TfLiteFusedActivation act, float scale, int32_t zp, int32_t* lo, int32_t* hi) {
+  auto quant = [&](float f, int32_t* q) {
+    const float t = std::round(f / scale);
+    if (!(t >= -2147483648.0f && t <= 2147483648.0f)) return false;
+    *q = zp + static_cast<int32_t>(t);
+    return true;
+  };
+  *lo = -128;
+  *hi = 127;
+  int32_t t;
+  if (act == kTfLiteActRelu) {
+    if (!quant(0.f, &t)) return false;
+    *lo = std::max(*lo, t);
+  } else if (act == kTfLiteActRelu6) {
+    if (!quant(0.f, &t)) return false;
+    *lo = std::max(*lo, t);
+    if (!quant(6.f, &t)) return false;
+    *hi = std::min(*hi, t);
+  } else if (act == kTfLiteActReluN1To1) {
+    if (!quant(-1.f, &t)) return false;
+    *lo = std::max(*lo, t);
+    if (!quant(1.f, &t)) return false;
+    *hi = std::min(*hi, t);
+  }
+  return true;
+}
+
+class DelegateKernel {
+ public:
+  explicit DelegateKernel(DelegateState* st) : st_(st), arena_(ArenaAlloc, ArenaFree, st) {}
+
+  TfLiteStatus Init(TfLiteContext* ctx, const TfLiteDelegateParams* params) {
+    if (st_->options.fail_on == "init") {
+      TF_LITE_KERNEL_LOG(ctx, "B200 delegate: injected failure in init");
+      return kTfLiteDelegateError;
+    }
+    TF_LITE_ENSURE_STATUS(st_->EnsureDevice(ctx));
+    inputs_.assign(params->input_tensors->data, params->input_tensors->data + params->input_tensors->size);
+    outputs_.assign(params->output_tensors->data, params->output_tensors->data + params->output_tensors->size);
+    ops_.clear();
+    for (int i = 0; i < params->nodes_to_replace->size; ++i) {
+      const int node_index = params->nodes_to_replace->data[i];
+      TfLiteNode* node = nullptr;
+      TfLiteRegistration* reg = nullptr;
+      TF_LITE_ENSURE_STATUS(ctx->GetNodeAndRegistration(ctx, node_index, &node, &reg));
+      std::string why;
+      const OpKind kind = Classify(ctx, node, reg, st_->options, &why);
+      if (kind == OpKind::kNone) {
+        TF_LITE_KERNEL_LOG(ctx, "B200 delegate: node %d handed to the kernel but unsupported (%s)", node_index,
+                           why.c_str());
+        return kTfLiteDelegateError;
+      }
+      ops_.emplace_back(new OpRecord());
+      OpRecord& op = *ops_.back();
+      op.kind = kind;
+      op.node_index = node_index;
+      TF_LITE_ENSURE_STATUS(BuildOp(ctx, node, reg, &op));
+    }
+    CUDA_OK(ctx, cudaStreamSynchronize(st_->stream));  // staging buffers below go out of scope
+    return kTfLiteOk;
+  }
+
+  TfLiteStatus Prepare(TfLiteContext* ctx, TfLiteNode*) {
+    if (st_->options.fail_on == "prepare") {
+      TF_LITE_KERNEL_LOG(ctx, "B200 delegate: injected failure in prepare");
+      return kTfLiteDelegateError;
+    }
+    CUDA_OK(ctx, cudaSetDevice(st_->options.device));
+    // tensors living on the device for this partition: every op operand that is not a constant
+    slot_of_.clear();
+    std::vector<b200::ArenaRequest> req;
+    const int num_ops = static_cast<int>(ops_.size());
+    auto touch = [&](int tensor, int op_index) {
+      if (tensor < 0) return;
+      const TfLiteTensor& t = ctx->tensors[tensor];
+      if (IsConst(t)) return;
+      auto it = slot_of_.find(tensor);
+      if (it == slot_of_.end()) {
+        slot_of_[tensor] = static_cast<int>(req.size());
+        b200::ArenaRequest r;
+        r.bytes = t.bytes;
+        r.first_use = r.last_use = op_index;
+        req.push_back(r);
+      } else {
+        req[it->second].last_use = op_index;
+      }
+    };
+    size_t scratch = 0, sdpa = 0;
+    for (int i = 0; i < num_ops; ++i) {
+      OpRecord& op = *ops_[i];
+      if (op.kind == OpKind::kSdpa) {
+        for (int t : {op.q, op.k, op.v, op.mask, op.y}) touch(t, i);
+        sdpa = std::max(sdpa, b200_sdpa_workspace_bytes(op.B, op.N, op.H, op.S));
+      } else {
+        const TfLiteTensor& x = ctx->tensors[op.x];
+        op.m = static_cast<int>(NumElements(x) / op.kdim);  // fully_connected.cc:502
+        touch(op.x, i);
+        touch(op.y, i);
+        scratch = std::max(scratch, b200_fc_scratch_bytes(op.m, op.kdim));
+      }
+    }
+    // partition inputs arrive before the first op and outputs are read after the last one
+    for (int t : inputs_) {
+      auto it = slot_of_.find(t);
+      if (it != slot_of_.end()) req[it->second].first_use = 0;
+    }
+    for (int t : outputs_) {
+      auto it = slot_of_.find(t);
+      if (it != slot_of_.end()) req[it->second].last_use = num_ops - 1;
+    }
+    if (!arena_.Commit(req, num_ops)) {
+      TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device arena allocation of %zu bytes failed", arena_.planned_bytes());
+      return kTfLiteDelegateError;
+    }
+    if (!st_->scratch.ensure(scratch) || !st_->sdpa_ws.ensure(sdpa)) {
+      TF_LITE_KERNEL_LOG(ctx, "B200 delegate: workspace allocation failed");
+      return kTfLiteDelegateError;
+    }
+    return kTfLiteOk;
+  }
+
+  TfLiteStatus Invoke(TfLiteContext* ctx, TfLiteNode*) {
+    if (st_->options.fail_on == "invoke") {
+      TF_LITE_KERNEL_LOG(ctx, "B200 delegate: injected failure in invoke");
+      return kTfLiteDelegateError;
+    }
+    CUDA_OK(ctx, cudaSetDevice(st_->options.device));
+    cudaStream_t s = st_->stream;
+    // host -> device for the partition's non-constant inputs (tensor data pointers may change
+    // between invocations, tflite/delegates/utils/simple_delegate.h:62-63, so read them now)
+    for (int t : inputs_) {
+      auto it = slot_of_.find(t);
+      if (it == slot_of_.end()) continue;
+      const TfLiteTensor& tensor = ctx->tensors[t];
+      if (!tensor.data.raw) continue;
+      CUDA_OK(ctx, cudaMemcpyAsync(arena_.Resolve(it->second), tensor.data.raw, tensor.bytes, cudaMemcpyHostToDevice, s));
+    }
+    for (auto& opp : ops_) TF_LITE_ENSURE_STATUS(Launch(ctx, *opp));
+    for (int t : outputs_) {
+      auto it = slot_of_.find(t);
+      if (it == slot_of_.end()) continue;
+      TfLiteTensor& tensor = ctx->tensors[t];
+      if (st_->options.buffer_handles) {
+        if (tensor.buffer_handle == kTfLiteNullBufferHandle) tensor.buffer_handle = st_->next_handle++;
+        st_->handles[tensor.buffer_handle] = {arena_.Resolve(it->second), tensor.bytes};
+        tensor.delegate = &st_->delegate;
+        tensor.data_is_stale = true;
+      } else if (tensor.data.raw) {
+        CUDA_OK(ctx, cudaMemcpyAsync(tensor.data.raw, arena_.Resolve(it->second), tensor.bytes, cudaMemcpyDeviceToHost, s));
+      }
+    }
+    int status = 0;
+    B200_OK_OR_RETURN(ctx, b200_read_status(st_->zero_ws.ptr, s, &status));  // synchronises the stream
+    return kTfLiteOk;
+  }
+
+ private:
+  void* Dev(int tensor) {
+    auto it = slot_of_.find(tensor);
+    return it == slot_of_.end() ? nullptr : arena_.Resolve(it->second);
+  }
+
+  template <typename T>
+  TfLiteStatus Upload(TfLiteContext* ctx, const std::vector<T>& host, DeviceMem* dst) {
+    if (host.empty()) return kTfLiteOk;
+    if (!dst->ensure(host.size() * sizeof(T))) {
+      TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed");
+      return kTfLiteDelegateError;
+    }
+    CUDA_OK(ctx, cudaMemcpyAsync(dst->ptr, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice, st_->stream));
+    // the vector may die before the copy runs from pageable memory: cudaMemcpyAsync from pageable
+    // host memory stages the data before returning, so this is safe
+    return kTfLiteOk;
+  }
+
+  TfLiteStatus UploadRaw(TfLiteContext* ctx, const void* host, size_t bytes, DeviceMem* dst) {
+    if (!dst->ensure(bytes)) {
+      TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed");
+      return kTfLiteDelegateError;
+    }
+    CUDA_OK(ctx, cudaMemcpyAsync(dst->ptr, host, bytes, cudaMemcpyHostToDevice, st_->stream));
+    return kTfLiteOk;
+  }
+
+  // Uploads an int8 weight matrix [n,k] (optionally the transpose of a [k,n] one) and packs it.
+  TfLiteStatus PackInt8(TfLiteContext* ctx, const int8_t* host, int n, int k, bool transpose, OpRecord* op) {
+    DeviceMem staging;
+    if (transpose) {
+      std::vector<int8_t> t(static_cast<size_t>(n) * k);
+      for (int r = 0; r < k; ++r)
+        for (int c = 0; c < n; ++c) t[static_cast<size_t>(c) * k + r] = host[static_cast<size_t>(r) * n + c];
+      TF_LITE_ENSURE_STATUS(Upload(ctx, t, &staging));
+    } else {
+      TF_LITE_ENSURE_STATUS(UploadRaw(ctx, host, static_cast<size_t>(n) * k, &staging));
+    }
+    if (!op->packed.ensure(b200_packed_w8_bytes(n, k)) || !op->row_sums.ensure(sizeof(int32_t) * n)) {
+      TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed");
+      return kTfLiteDelegateError;
+    }
+    B200_OK_OR_RETURN(ctx, b200_pack_w8(static_cast<const int8_t*>(staging.ptr), n, k, op->packed.ptr,
+                                       static_cast<int32_t*>(op->row_sums.ptr), st_->stream));
+    CUDA_OK(ctx, cudaStreamSynchronize(st_->stream));  // staging is freed on return
+    return kTfLiteOk;
+  }
+
+  TfLiteStatus BuildOp(TfLiteContext* ctx, TfLiteNode* node, TfLiteRegistration* reg, OpRecord* op) {
+    const TfLiteTensor* T = ctx->tensors;
+    auto idx = [&](int i) { return i < node->inputs->size ? node->inputs->data[i] : -1; };
+    op->y = node->outputs->data[0];
+    switch (op->kind) {
+      case OpKind::kFcInt8: {
+        const auto* p = static_cast<const TfLiteFullyConnectedParams*>(node->builtin_data);
+        op->x = idx(0);
+        const TfLiteTensor &x = T[op->x], &w = T[idx(1)], &y = T[op->y];
+        const TfLiteTensor* b = idx(2) >= 0 ? &T[idx(2)] : nullptr;
+        op->n = w.dims->data[0];
+        op->kdim = w.dims->data[1];
+        TF_LITE_ENSURE_STATUS(PackInt8(ctx, w.data.int8, op->n, op->kdim, false, op));
+        const auto* q = Affine(w);
+        op->per_channel = q->scale->size > 1;
+        std::vector<int32_t> mult, shift;
+        if (op->per_channel) {
+          mult.resize(op->n);
+          shift.resize(op->n);
+          for (int i = 0; i < op->n; ++i) {
+            const double eff = static_cast<double>(x.params.scale) * static_cast<double>(q->scale->data[i]) /
+                               static_cast<double>(y.params.scale);
+            int sh;
+            QuantizeMultiplier(eff, &mult[i], &sh);
+            shift[i] = sh;
+          }
+          op->filter_offset = 0;
+        } else {
+          // tflite/kernels/kernel_util.cc:291-339
+          if (b) {
+            const double ips = static_cast<double>(x.params.scale) * static_cast<double>(w.params.scale);
+            const double diff = std::abs(ips - static_cast<double>(b->params.scale));
+            if (!(diff / static_cast<double>(y.params.scale) <= 0.02)) {
+              TF_LITE_KERNEL_LOG(ctx, "B200 delegate: bias scale does not match input*filter scale");
+              return kTfLiteError;
+            }
+          }
+          const double ips = static_cast<double>(x.params.scale * w.params.scale);
+          mult.resize(1);
+          shift.resize(1);
+          int sh;
+          QuantizeMultiplier(ips / static_cast<double>(y.params.scale), &mult[0], &sh);
+          shift[0] = sh;
+          op->filter_offset = -w.params.zero_point;
+        }
+        TF_LITE_ENSURE_STATUS(Upload(ctx, mult, &op->mult));
+        TF_LITE_ENSURE_STATUS(Upload(ctx, shift, &op->shift));
+        if (b) TF_LITE_ENSURE_STATUS(UploadRaw(ctx, b->data.raw, sizeof(int32_t) * op->n, &op->bias));
+        op->input_offset = -x.params.zero_point;
+        op->output_offset = y.params.zero_point;
+        if (!ActivationRangeInt8(p->activation, y.params.scale, y.params.zero_point, &op->act_min, &op->act_max)) {
+          TF_LITE_KERNEL_LOG(ctx, "B200 delegate: activation range overflow");
+          return kTfLiteError;
+        }
+        return kTfLiteOk;
+      }
+      case OpKind::kFcHybrid:
+      case OpKind::kBmmHybrid: {
+        op->x = idx(0);
+        const TfLiteTensor& w = T[idx(1)];
+        const TfLiteTensor* b = nullptr;
+        const bool bmm = op->kind == OpKind::kBmmHybrid;
+        bool transpose = false;
+        if (bmm) {
+          const auto* p = static_cast<const TfLiteBatchMatMulParams*>(node->builtin_data);
+          // rhs [k,n] unless adj_y ([n,k]); the reference transposes a constant rhs once
+          // (tflite/kernels/batch_matmul.cc:791-798)
+          transpose = !p->adj_y;
+          op->n = p->adj_y ? w.dims->data[0] : w.dims->data[1];
+          op->kdim = p->adj_y ? w.dims->data[1] : w.dims->data[0];
+          op->asymmetric = p->asymmetric_quantize_inputs;
+          op->activation = kTfLiteActNone;
+        } else {
+          const auto* p = static_cast<const TfLiteFullyConnectedParams*>(node->builtin_data);
+          op->n = w.dims->data[0];
+          op->kdim = w.dims->data[1];
+          op->asymmetric = p->asymmetric_quantize_inputs;
+          op->activation = p->activation;
+          if (idx(2) >= 0) b = &T[idx(2)];
+        }
+        TF_LITE_ENSURE_STATUS(PackInt8(ctx, w.data.int8, op->n, op->kdim, transpose, op));
+        const auto* q = Affine(w);
+        std::vector<float> scales;
+        if (q && q->scale && q->scale->size > 1) {
+          scales.assign(q->scale->data, q->scale->data + q->scale->size);
+          op->per_channel = true;
+        } else {
+          scales.assign(1, w.params.scale);  // fully_connected.cc:838-843
+          op->per_channel = false;
+        }
+        TF_LITE_ENSURE_STATUS(Upload(ctx, scales, &op->w_scales));
+        if (b) TF_LITE_ENSURE_STATUS(UploadRaw(ctx, b->data.raw, sizeof(float) * op->n, &op->bias));
+        return kTfLiteOk;
+      }
+      case OpKind::kBmmInt8: {
+        const auto* p = static_cast<const TfLiteBatchMatMulParams*>(node->builtin_data);
+        op->x = idx(0);
+        const TfLiteTensor &x = T[op->x], &w = T[idx(1)], &y = T[op->y];
+        op->n = p->adj_y ? w.dims->data[0] : w.dims->data[1];
+        op->kdim = p->adj_y ? w.dims->data[1] : w.dims->data[0];
+        TF_LITE_ENSURE_STATUS(PackInt8(ctx, w.data.int8, op->n, op->kdim, !p->adj_y, op));
+        // tflite/kernels/batch_matmul.cc:315-331 and 528-556
+        const double ips = static_cast<double>(x.params.scale * w.params.scale);
+        std::vector<int32_t> mult(1), shift(1);
+        int sh;
+        QuantizeMultiplier(ips / static_cast<double>(y.params.scale), &mult[0], &sh);
+        shift[0] = sh;
+        TF_LITE_ENSURE_STATUS(Upload(ctx, mult, &op->mult));
+        TF_LITE_ENSURE_STATUS(Upload(ctx, shift, &op->shift));
+        op->per_channel = false;
+        op->input_offset = -x.params.zero_point;
+        op->filter_offset = -w.params.zero_point;
+        op->output_offset = y.params.zero_point;
+        op->act_min = -128;
+        op->act_max = 127;
+        return kTfLiteOk;
+      }
+      case OpKind::kFcW4: {
+        op->x = idx(0);
+        const TfLiteTensor& w = T[idx(1)];
+        const auto* q = static_cast<const TfLiteBlockwiseQuantization*>(w.quantization.params);
+        const TfLiteTensor& s = T[q->scale];
+        op->n = w.dims->data[0];
+        op->kdim = w.dims->data[1];
+        DeviceMem w_stage, s_stage;
+        const size_t row_bytes = (static_cast<size_t>(op->kdim) + 1) / 2;
+        TF_LITE_ENSURE_STATUS(UploadRaw(ctx, w.data.raw, row_bytes * op->n, &w_stage));
+        TF_LITE_ENSURE_STATUS(UploadRaw(ctx, s.data.raw, s.bytes, &s_stage));
+        if (!op->packed.ensure(b200_packed_w4_bytes(op->n, op->kdim)) || !op->kfsum.ensure(sizeof(float) * op->n)) {
+          TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed");
+          return kTfLiteDelegateError;
+        }
+        B200_OK_OR_RETURN(ctx, b200_pack_w4(static_cast<const uint8_t*>(w_stage.ptr),
+                                           static_cast<const uint16_t*>(s_stage.ptr), op->n, op->kdim, q->blocksize,
+                                           op->packed.ptr, static_cast<float*>(op->kfsum.ptr), st_->stream));
+        if (idx(2) >= 0) TF_LITE_ENSURE_STATUS(UploadRaw(ctx, T[idx(2)].data.raw, sizeof(float) * op->n, &op->bias));
+        CUDA_OK(ctx, cudaStreamSynchronize(st_->stream));
+        return kTfLiteOk;
+      }
+      case OpKind::kSdpa: {
+        op->q = idx(0);
+        op->k = idx(1);
+        op->v = idx(2);
+        op->mask = node->inputs->size > 3 ? idx(3) : -1;
+        const TfLiteTensor &q = T[op->q], &k = T[op->k];
+        op->B = q.dims->data[0];
+        op->N = q.dims->data[2];
+        op->H = q.dims->data[3];
+        op->S = k.dims->data[1];
+        op->Nkv = k.dims->data[2];
+        const uint8_t* attr = nullptr;
+        size_t attr_size = 0;
+        if (reg->builtin_code == kTfLiteBuiltinStablehloComposite) {
+          const auto* p = static_cast<const TfLiteStablehloCompositeParams*>(node->builtin_data);
+          attr = p->attributes;
+          attr_size = p->attributes_size;
+        } else {
+          attr = static_cast<const uint8_t*>(node->custom_initial_data);
+          attr_size = static_cast<size_t>(node->custom_initial_data_size);
+        }
+        float scale = 0.0f, cap = 0.0f;
+        b200::FlexMapFloat(attr, attr_size, "scale", &scale);
+        b200::FlexMapFloat(attr, attr_size, "logit_cap", &cap);
+        op->scale = scale;  // <= 0 or absent: 1/sqrt(H), tflite/experimental/genai/sdpa.cc:99-105
+        op->logit_cap = cap;
+        return kTfLiteOk;
+      }
+      default:
+        return kTfLiteDelegateError;
+    }
+  }
+
+  TfLiteStatus Launch(TfLiteContext* ctx, OpRecord& op) {
+    cudaStream_t s = st_->stream;
+    switch (op.kind) {
+      case OpKind::kFcInt8:
+      case OpKind::kBmmInt8:
+        B200_OK_OR_RETURN(ctx, b200_fc_int8(static_cast<const int8_t*>(Dev(op.x)), op.m, op.kdim, op.packed.ptr, op.n,
+                                           static_cast<const int32_t*>(op.row_sums.ptr),
+                                           static_cast<const int32_t*>(op.bias.ptr), op.input_offset, op.filter_offset,
+                                           op.output_offset, static_cast<const int32_t*>(op.mult.ptr),
+                                           static_cast<const int32_t*>(op.shift.ptr), op.per_channel ? 1 : 0,
+                                           op.act_min, op.act_max, static_cast<int8_t*>(Dev(op.y)), st_->zero_ws.ptr,
+                                           st_->scratch.ptr, st_->scratch.bytes, s));
+        return kTfLiteOk;
+      case OpKind::kFcHybrid:
+      case OpKind::kBmmHybrid:
+        B200_OK_OR_RETURN(ctx, b200_fc_hybrid(static_cast<const float*>(Dev(op.x)), op.m, op.kdim, op.packed.ptr, op.n,
+                                             static_cast<const int32_t*>(op.row_sums.ptr),
+                                             static_cast<const float*>(op.w_scales.ptr), op.per_channel ? 1 : 0,
+                                             static_cast<const float*>(op.bias.ptr), op.asymmetric ? 1 : 0,
+                                             op.activation, static_cast<float*>(Dev(op.y)), st_->zero_ws.ptr,
+                                             st_->scratch.ptr, st_->scratch.bytes, s));
+        return kTfLiteOk;
+      case OpKind::kFcW4:
+        B200_OK_OR_RETURN(ctx, b200_fc_w4(static_cast<const float*>(Dev(op.x)), op.m, op.kdim, op.packed.ptr, op.n, 32,
+                                         static_cast<const float*>(op.kfsum.ptr),
+                                         static_cast<const float*>(op.bias.ptr), static_cast<float*>(Dev(op.y)),
+                                         st_->zero_ws.ptr, st_->scratch.ptr, st_->scratch.bytes, s));
+        return kTfLiteOk;
+      case OpKind::kSdpa:
+        B200_OK_OR_RETURN(ctx, b200_sdpa_decode(Dev(op.q), Dev(op.k), Dev(op.v), nullptr, nullptr, nullptr,
+                                               op.mask >= 0 ? static_cast<const float*>(Dev(op.mask)) : nullptr,
+                                               Dev(op.y), op.B, op.N, op.Nkv, op.H, op.S, B200_DTYPE_F32,
+                                               B200_DTYPE_F32, op.scale, op.logit_cap, st_->sdpa_ws.ptr,
+                                               st_->sdpa_ws.bytes, s));
+        return kTfLiteOk;
+      default:
+        return kTfLiteDelegateError;
+    }
+  }
+
+  DelegateState* st_;
+  b200::DeviceArena arena_;
+  std::vector<int> inputs_, outputs_;
+  std::vector<std::unique_ptr<OpRecord>> ops_;
+  std::unordered_map<int, int> slot_of_;
+};
+
+// ---------------------------------------------------------------- registration glue
+void* KernelInit(TfLiteContext* ctx, const char* buffer, size_t) {
+  const auto* params = reinterpret_cast<const TfLiteDelegateParams*>(buffer);
+  if (!params || !params->delegate) return nullptr;
+  auto* st = static_cast<DelegateState*>(params->delegate->data_);
+  auto* kernel = new DelegateKernel(st);
+  if (kernel->Init(ctx, params) != kTfLiteOk) {
+    delete kernel;
+    return TfLiteKernelInitFailed();
+  }
+  return kernel;
+}
+
+void KernelFree(TfLiteContext*, void* buffer) {
+  if (buffer && buffer != TfLiteKernelInitFailed()) delete static_cast<DelegateKernel*>(buffer);
+}
+
+TfLiteStatus KernelPrepare(TfLiteContext* ctx, TfLiteNode* node) {
+  if (!node->user_data || node->user_data == TfLiteKernelInitFailed()) return kTfLiteDelegateError;
+  return static_cast<DelegateKernel*>(node->user_data)->Prepare(ctx, node);
+}
+
+TfLiteStatus KernelInvoke(TfLiteContext* ctx, TfLiteNode* node) {
+  if (!node->user_data || node->user_data == TfLiteKernelInitFailed()) return kTfLiteDelegateError;
+  return static_cast<DelegateKernel*>(node->user_data)->Invoke(ctx, node);
+}
+
+TfLiteStatus DelegatePrepare(TfLiteContext* ctx, TfLiteDelegate* delegate) {
+  auto* st = static_cast<DelegateState*>(delegate->data_);
+  TfLiteIntArray* plan = nullptr;
+  TF_LITE_ENSURE_STATUS(ctx->GetExecutionPlan(ctx, &plan));
+  // the plan array belongs to the runtime and is invalidated by the next call: copy it
+  std::vector<int> nodes(plan->data, plan->data + plan->size);
+  std::vector<int> supported;
+  for (int node_index : nodes) {
+    TfLiteNode* node = nullptr;
+    TfLiteRegistration* reg = nullptr;
+    TF_LITE_ENSURE_STATUS(ctx->GetNodeAndRegistration(ctx, node_index, &node, &reg));
+    std::string why;
+    if (Classify(ctx, node, reg, st->options, &why) != OpKind::kNone) supported.push_back(node_index);
+  }
+  st->delegated_nodes = static_cast<int>(supported.size());
+  if (supported.empty()) return kTfLiteOk;  // nothing to claim is not an error
+  TfLiteRegistration reg;
+  memset(&reg, 0, sizeof(reg));
+  reg.init = KernelInit;
+  reg.free = KernelFree;
+  reg.prepare = KernelPrepare;
+  reg.invoke = KernelInvoke;
+  reg.builtin_code = kTfLiteBuiltinDelegate;
+  reg.custom_name = kDelegateName;
+  reg.version = 1;
+  TfLiteIntArray* arr = TfLiteIntArrayCreate(static_cast<int>(supported.size()));
+  for (size_t i = 0; i < supported.size(); ++i) arr->data[i] = supported[i];
+  const TfLiteStatus status = ctx->ReplaceNodeSubsetsWithDelegateKernels(ctx, reg, arr, delegate);
+  TfLiteIntArrayFree(arr);
+  return status;
+}
+
+TfLiteStatus CopyFromBufferHandle(TfLiteContext* ctx, TfLiteDelegate* delegate, TfLiteBufferHandle handle,
+                                  TfLiteTensor* tensor) {
+  auto* st = static_cast<DelegateState*>(delegate->data_);
+  auto it = st->handles.find(handle);
+  if (it == st->handles.end() || !tensor->data.raw) {
+    TF_LITE_KERNEL_LOG(ctx, "B200 delegate: unknown buffer handle %d", handle);
+    return kTfLiteDelegateError;
+  }
+  CUDA_OK(ctx, cudaSetDevice(st->options.device));
+  const size_t bytes = std::min(it->second.second, tensor->bytes);
+  CUDA_OK(ctx, cudaMemcpyAsync(tensor->data.raw, it->second.first, bytes, cudaMemcpyDeviceToHost, st->stream));
+  CUDA_OK(ctx, cudaStreamSynchronize(st->stream));
+  return kTfLiteOk;
+}
+
+void FreeBufferHandle(TfLiteContext*, TfLiteDelegate* delegate, TfLiteBufferHandle* handle) {
+  auto* st = static_cast<DelegateState*>(delegate->data_);
+  if (handle && *handle != kTfLiteNullBufferHandle) {
+    st->handles.erase(*handle);
+    *handle = kTfLiteNullBufferHandle;
+  }
+}
+
+bool ParseBool(const char* v) { return v && (!strcmp(v, "1") || !strcmp(v, "true") || !strcmp(v, "TRUE")); }
+
+}  // namespace
+
+extern "C" {
+
+TfLiteDelegate* tflite_plugin_create_delegate(const char* const* keys, const char* const* values, size_t num_options,
+                                              void (*report_error)(const char*)) {
+  auto st = std::make_unique<DelegateState>();
+  char msg[256];
+  for (size_t i = 0; i < num_options; ++i) {
+    const char* k = keys ? keys[i] : nullptr;
+    const char* v = values ? values[i] : nullptr;
+    if (!k || !v) continue;
+    if (!strcmp(k, "device")) {
+      st->options.device = atoi(v);
+    } else if (!strcmp(k, "fail_on")) {
+      st->options.fail_on = v;
+      if (st->options.fail_on == "create") {
+        if (report_error) report_error("B200 delegate: injected failure in create");
+        return nullptr;
+      }
+    } else if (!strcmp(k, "buffer_handles")) {
+      st->options.buffer_handles = ParseBool(v);
+    } else if (!strcmp(k, "claim_fc")) {
+      st->options.claim_fc = ParseBool(v);
+    } else if (!strcmp(k, "claim_bmm")) {
+      st->options.claim_bmm = ParseBool(v);
+    } else if (!strcmp(k, "claim_sdpa")) {
+      st->options.claim_sdpa = ParseBool(v);
+    } else {
+      snprintf(msg, sizeof(msg), "B200 delegate: unknown option '%s'", k);
+      if (report_error) report_error(msg);
+      return nullptr;
+    }
+  }
+  if (st->options.device < 0) {
+    if (report_error) report_error("B200 delegate: negative device index");
+    return nullptr;
+  }
+  memset(&st->delegate, 0, sizeof(st->delegate));
+  st->delegate.data_ = st.get();
+  st->delegate.Prepare = DelegatePrepare;
+  st->delegate.CopyFromBufferHandle = CopyFromBufferHandle;
+  st->delegate.CopyToBufferHandle = nullptr;
+  st->delegate.FreeBufferHandle = FreeBufferHandle;
+  st->delegate.flags = kTfLiteDelegateFlagsNone;  // static shapes only
+  st->delegate.opaque_delegate_builder = nullptr;
+  return &st.release()->delegate;
+}
+
+void tflite_plugin_destroy_delegate(TfLiteDelegate* delegate) {
+  if (!delegate) return;
+  auto* st = static_cast<DelegateState*>(delegate->data_);
+  if (st->ready) {
+    cudaSetDevice(st->options.device);
+    if (st->stream) {
+      cudaStreamSynchronize(st->stream);
+      cudaStreamDestroy(st->stream);
+    }
+  }
+  delete st;
+}
+
+int b200_delegate_num_claimed_nodes(const TfLiteDelegate* delegate) {
+  return delegate ? static_cast<const DelegateState*>(delegate->data_)->delegated_nodes : -1;
+}
+
+}  // extern "C"

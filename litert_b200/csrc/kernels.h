@@ -1,0 +1,101 @@
+// Internal launch interface between the C-ABI shim and the kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+inline int tiles_n(int n) { return (n + 127) / 128; }
+inline int tiles_k8(int k) { return (k + 127) / 128; }
+inline int tiles_k4(int k) { return (k + 255) / 256; }
+
+// Number of 8-row activation groups one launch carries (1, 2, 4 or 8).
+inline int m_tiles_for(int m) {
+  const int g = (m + 7) / 8;
+  return g <= 1 ? 1 : (g <= 2 ? 2 : (g <= 4 ? 4 : 8));
+}
+// Rows allocated in the tiled activation buffer for m real rows.
+inline int m_alloc_for(int m) {
+  if (m <= 64) return 8 * m_tiles_for(m);
+  return ((m + 63) / 64) * 64;
+}
+
+cudaError_t launch_pack_w8(const int8_t* w, int n, int k, uint8_t* packed, int32_t* row_sums, cudaStream_t s);
+cudaError_t launch_pack_w4(const uint8_t* w4, const void* scales_f16, int n, int k, int blocksize, uint8_t* packed,
+                           float* kfsum, cudaStream_t s);
+cudaError_t launch_quantize_rows(const float* x, int m, int k, int k_pad, int m_alloc, int asymmetric,
+                                 int8_t* q_tiled, int8_t* q_rowmajor, float* scales, int32_t* zps, cudaStream_t s);
+cudaError_t launch_retile_x8(const int8_t* x, int m, int k, int k_pad, int m_alloc, int8_t* q_tiled,
+                             int32_t* x_sums, cudaStream_t s);
+
+// Epilogue selection for the streamed int8 GEMM.
+enum FcEpilogue : int {
+  kEpiHybridF32 = 0,  // float out: bias + (acc - row_sum*zp) * (in_scale*w_scale), activation
+  kEpiRequantI8 = 1,  // int8 out: fixed-point requantization
+  kEpiRawI32 = 2,     // int32 accumulators out (row-major [m,n])
+};
+
+struct FcParams {
+  // operands
+  const uint8_t* w_packed;   // tiles [n_tiles][k_tiles]
+  const int8_t* q_tiled;     // activations, tiled, m_alloc rows
+  int m, n, k;               // logical sizes
+  int n_tiles, k_tiles, m_alloc;
+  // hybrid epilogue
+  const float* in_scales;    // [m]
+  const int32_t* in_zps;     // [m] or null
+  const float* w_scales;     // [n] or [1]
+  int per_channel;
+  const float* bias_f32;     // [n] or null
+  const int32_t* row_sums;   // [n]
+  int activation;
+  // int8 epilogue
+  const int32_t* bias_i32;
+  const int32_t* multipliers;  // [n] or [1]
+  const int32_t* shifts;
+  const int32_t* x_sums;     // [m] or null (only with filter_offset != 0)
+  int32_t input_offset, filter_offset, output_offset, act_min, act_max;
+  // 4-bit
+  const float* kfsum;        // [n]
+  // outputs
+  void* y;                   // [m,n] row-major float / int8 / int32
+  // split-K workspace: kZeroWsSlots slots of 128*64 int32/float accumulators and as many counters;
+  // all zero between calls
+  int32_t* ws_acc;
+  int32_t* ws_count;
+  int* status;
+  int max_ctas;              // 0 = one per SM
+};
+
+// Streamed-weights GEMM on the packed int8 tiles (any m; m > 64 runs in
+// chunks of 64 rows).
+cudaError_t launch_fc_i8(const FcParams& p, FcEpilogue epi, cudaStream_t s);
+// Blockwise 4-bit weights, float out.
+cudaError_t launch_fc_w4(const FcParams& p, cudaStream_t s);
+
+constexpr int kZeroWsSlots = 256;            // >= CTAs per launch
+constexpr int kZeroWsSlotInts = 128 * 64;    // accumulators per slot
+int device_sm_count();
+
+struct SdpaParams {
+  const void* q;        // [b, t(=1), n, h] f16 or f32
+  const void* k;        // [b, s_max, nkv, h] f16 / int8 / f32
+  const void* v;
+  const float* k_scale; // [b, s_max, nkv] for int8 kv
+  const float* v_scale;
+  const int32_t* lengths;  // [b] or null (= s_max)
+  const float* mask;       // [b,1,1,s_max] additive or null
+  void* out;               // same type/shape as q
+  int b, n, nkv, h, s_max;
+  int q_dtype;   // 0 = f16, 1 = f32
+  int kv_dtype;  // 0 = f16, 1 = int8, 2 = f32
+  float scale, logit_cap;
+  float* ws;     // partials workspace
+  size_t ws_bytes;
+  int* status;
+};
+cudaError_t launch_sdpa_decode(const SdpaParams& p, cudaStream_t s);
+size_t sdpa_workspace_bytes(int b, int n, int h, int s_max);
+
+}  // namespace b200

@@ -1,0 +1,320 @@
+// One-time weight repacking (run at delegate-kernel init) and the per-call
+// activation preparation kernels: row quantization and int8 re-tiling.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b200 {
+
+// ---- int8 weights: row-major [n,k] -> tiles --------------------------------
+// One thread per 16-byte chunk of the packed buffer.
+__global__ void pack_w8_kernel(const int8_t* __restrict__ w, int n, int k, int n_tiles, int k_tiles,
+                               uint8_t* __restrict__ packed) {
+  const long long total = (long long)n_tiles * k_tiles * (kTileBytes / 16);
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(idx & 7);
+    const int c = (int)((idx >> 3) & 7);
+    const int rg = (int)((idx >> 6) & 15);
+    const long long tile = idx >> 10;
+    const int kt = (int)(tile % k_tiles);
+    const int nt = (int)(tile / k_tiles);
+    const int row = nt * kTileN + rg * 8 + r;
+    const int k0 = kt * kTileK8 + c * 16;
+    uint32_t v[4] = {0, 0, 0, 0};
+    if (row < n) {
+      const int8_t* src = w + (size_t)row * k + k0;
+#pragma unroll
+      for (int b = 0; b < 16; ++b) {
+        if (k0 + b < k) v[b >> 2] |= (uint32_t)(uint8_t)src[b] << (8 * (b & 3));
+      }
+    }
+    *reinterpret_cast<uint4*>(packed + idx * 16) = make_uint4(v[0], v[1], v[2], v[3]);
+  }
+}
+
+// row_sums[r] = sum_k w[r,k]; one warp per row.
+__global__ void row_sums_kernel(const int8_t* __restrict__ w, int n, int k, int32_t* __restrict__ row_sums) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= n) return;
+  const int8_t* row = w + (size_t)warp * k;
+  int32_t s = 0;
+  for (int i = lane; i < k; i += 32) s += row[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) row_sums[warp] = s;
+}
+
+// ---- int4 blockwise weights -------------------------------------------------
+// Source: n rows of k2/2 bytes (k2 = k rounded up to even), element 2i in the
+// low nibble of byte i (tflite/kernels/fully_connected.cc:1053-1067); fp16
+// scales [n, k/blocksize]. Destination tile: [row group][sub-block of 32][row]
+// [4 words]; word t of a row holds, in byte j, element 4t+j of the sub-block in
+// the low nibble and element 16+4t+j in the high nibble, so that one shift and
+// two masks turn a word into the two int8 MMA registers (values x16). The
+// tile's fp16 scales follow as [sub-block][row].
+__device__ __forceinline__ uint32_t nibble_at(const uint8_t* __restrict__ w4, size_t row_bytes, int row, int kk,
+                                              int n, int k) {
+  if (row >= n || kk >= k) return 0u;
+  const uint8_t byte = w4[(size_t)row * row_bytes + (kk >> 1)];
+  return (kk & 1) ? (byte >> 4) : (byte & 0xF);
+}
+
+__global__ void pack_w4_kernel(const uint8_t* __restrict__ w4, const __half* __restrict__ scales, int n, int k,
+                               int blocksize, int n_tiles, int k_tiles, uint8_t* __restrict__ packed) {
+  const size_t row_bytes = ((size_t)k + 1) / 2;
+  const int num_blocks = k / blocksize;
+  // words of nibbles
+  const long long words_per_tile = kTileBytes / 4;
+  const long long total_words = (long long)n_tiles * k_tiles * words_per_tile;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_words; idx += stride) {
+    const int t = (int)(idx & 3);
+    const int r = (int)((idx >> 2) & 7);
+    const int blk = (int)((idx >> 5) & 7);
+    const int rg = (int)((idx >> 8) & 15);
+    const long long tile = idx >> 12;
+    const int kt = (int)(tile % k_tiles);
+    const int nt = (int)(tile / k_tiles);
+    const int row = nt * kTileN + rg * 8 + r;
+    const int k0 = kt * kTileK4 + blk * 32;
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t lo = nibble_at(w4, row_bytes, row, k0 + 4 * t + j, n, k);
+      const uint32_t hi = nibble_at(w4, row_bytes, row, k0 + 16 + 4 * t + j, n, k);
+      word |= (lo | (hi << 4)) << (8 * j);
+    }
+    *reinterpret_cast<uint32_t*>(packed + (size_t)tile * kTile4Bytes + (size_t)(idx & 4095) * 4) = word;
+  }
+  // scales
+  const long long scales_per_tile = kTileN * kSubBlocks4;
+  const long long total_scales = (long long)n_tiles * k_tiles * scales_per_tile;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_scales; idx += stride) {
+    const int row_in = (int)(idx % kTileN);
+    const int blk = (int)((idx / kTileN) % kSubBlocks4);
+    const long long tile = idx / scales_per_tile;
+    const int kt = (int)(tile % k_tiles);
+    const int nt = (int)(tile / k_tiles);
+    const int row = nt * kTileN + row_in;
+    const int k0 = kt * kTileK4 + blk * 32;
+    __half s = __float2half(0.0f);
+    if (row < n && k0 < k && k0 / blocksize < num_blocks) s = scales[(size_t)row * num_blocks + k0 / blocksize];
+    reinterpret_cast<__half*>(packed + (size_t)tile * kTile4Bytes + kTileBytes)[blk * kTileN + row_in] = s;
+  }
+}
+
+// kfsum[row] = sum over blocks, in increasing block order, of
+// scale[row,b] * (sum of the block's weights)  -- the zero-point correction
+// term of tflite/kernels/fully_connected.cc:1057-1078, which does not depend
+// on the activations. One thread per row; float operations are kept
+// unfused and in the reference's order.
+__global__ void w4_kfsum_kernel(const uint8_t* __restrict__ w4, const __half* __restrict__ scales, int n, int k,
+                                int blocksize, float* __restrict__ kfsum) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n) return;
+  const size_t row_bytes = ((size_t)k + 1) / 2;
+  const int num_blocks = k / blocksize;
+  float acc = 0.0f;
+  for (int b = 0; b < num_blocks; ++b) {
+    int32_t ksum = 0;
+    for (int i = 0; i < blocksize; ++i) {
+      const int v = (int)nibble_at(w4, row_bytes, row, b * blocksize + i, n, k);
+      ksum += (v ^ 8) - 8;
+    }
+    const float s = __half2float(scales[(size_t)row * num_blocks + b]);
+    acc = __fadd_rn(acc, __fmul_rn(s, (float)ksum));
+  }
+  kfsum[row] = acc;
+}
+
+// ---- activations ------------------------------------------------------------
+// Tiled activation layout shared by all MMA kernels: [k tile][row group of 8]
+// [16-byte chunk (8)][row (8)][16 bytes]; m_alloc rows are allocated.
+__device__ __forceinline__ size_t q_tiled_offset(int m, int kk, int m_alloc) {
+  const int kt = kk / kTileK8, c = (kk % kTileK8) / 16, b = kk % 16;
+  return (((size_t)kt * (m_alloc / 8) + (m / 8)) * kChunks8 + c) * 128 + (m % 8) * 16 + b;
+}
+
+template <typename T, typename Op>
+__device__ __forceinline__ T block_reduce(T v, Op op, T identity, T* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  v = lane < nw ? scratch[lane] : identity;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  return v;
+}
+
+// Per-row quantization of float activations to int8, one CTA per row.
+// Asymmetric: tflite/kernels/internal/reference/portable_tensor_utils.cc:74-119;
+// symmetric: :41-71. The scale and zero point are derived in double exactly as
+// there; the element loop is float multiply, float add, round half away from
+// zero, clamp -- with no fused multiply-add, as on the reference's x86 build.
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restrict__ x, int m, int k, int k_pad,
+                                                            int m_alloc, int asymmetric,
+                                                            int8_t* __restrict__ q_tiled,
+                                                            int8_t* __restrict__ q_rowmajor,
+                                                            float* __restrict__ scales,
+                                                            int32_t* __restrict__ zero_points) {
+  __shared__ float red[32];
+  __shared__ float s_inv;
+  __shared__ int s_zp;
+  __shared__ int s_zero;
+  const int row = blockIdx.x;
+  const float* xr = x + (size_t)row * k;
+  float mn = xr[0], mx = xr[0];
+  for (int i = threadIdx.x; i < k; i += blockDim.x) {
+    const float v = xr[i];
+    mn = fminf(mn, v);
+    mx = fmaxf(mx, v);
+  }
+  mn = block_reduce(mn, [](float a, float b) { return fminf(a, b); }, mn, red);
+  mx = block_reduce(mx, [](float a, float b) { return fmaxf(a, b); }, mx, red);
+  if (threadIdx.x == 0) {
+    if (asymmetric) {
+      const double rmin = (double)fminf(0.0f, mn);
+      const double rmax = (double)fmaxf(0.0f, mx);
+      if (rmin == rmax) {
+        s_zero = 1;
+        scales[row] = 1.0f;
+        zero_points[row] = 0;
+      } else {
+        const double qmin = -128.0, qmax = 127.0;
+        const double scale = (rmax - rmin) / (qmax - qmin);
+        const double zp_from_min = qmin - rmin / scale;
+        const double zp_from_max = qmax - rmax / scale;
+        const double err_min = fabs(qmin) + fabs(rmin / scale);
+        const double err_max = fabs(qmax) + fabs(rmax / scale);
+        const double zp_d = err_min < err_max ? zp_from_min : zp_from_max;
+        int zp;
+        if (zp_d <= qmin) {
+          zp = -128;
+        } else if (zp_d >= qmax) {
+          zp = 127;
+        } else {
+          zp = (int)(int8_t)round(zp_d);
+        }
+        const float sf = (float)scale;
+        s_zero = 0;
+        s_inv = __fdiv_rn(1.0f, sf);
+        s_zp = zp;
+        scales[row] = sf;
+        zero_points[row] = zp;
+      }
+    } else {
+      const float range = fmaxf(fabsf(mn), fabsf(mx));
+      if (range == 0.0f) {
+        s_zero = 1;
+        scales[row] = 1.0f;
+      } else {
+        s_zero = 0;
+        s_inv = __fdiv_rn(127.0f, range);
+        scales[row] = __fdiv_rn(range, 127.0f);
+      }
+      s_zp = 0;
+      if (zero_points) zero_points[row] = 0;
+    }
+  }
+  __syncthreads();
+  const bool zero = s_zero != 0;
+  const float inv = s_inv;
+  const float zpf = (float)s_zp;
+  const int lo = asymmetric ? -128 : -127;
+  for (int c = threadIdx.x; c < k_pad / 16; c += blockDim.x) {
+    uint32_t v[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int b = 0; b < 16; ++b) {
+      const int kk = c * 16 + b;
+      int qv = 0;
+      if (kk < k && !zero) {
+        const float t = asymmetric ? __fadd_rn(zpf, __fmul_rn(xr[kk], inv)) : __fmul_rn(xr[kk], inv);
+        qv = (int)roundf(t);
+        qv = max(lo, min(127, qv));
+      }
+      v[b >> 2] |= (uint32_t)(uint8_t)(int8_t)qv << (8 * (b & 3));
+    }
+    if (q_tiled)
+      *reinterpret_cast<uint4*>(q_tiled + q_tiled_offset(row, c * 16, m_alloc)) = make_uint4(v[0], v[1], v[2], v[3]);
+    if (q_rowmajor) {
+#pragma unroll
+      for (int b = 0; b < 16; ++b)
+        if (c * 16 + b < k) q_rowmajor[(size_t)row * k + c * 16 + b] = (int8_t)(v[b >> 2] >> (8 * (b & 3)));
+    }
+  }
+}
+
+// int8 activations [m,k] row-major -> tiled layout, plus optional row sums
+// (needed only when the weights have a non-zero zero point).
+__global__ void __launch_bounds__(256) retile_x8_kernel(const int8_t* __restrict__ x, int m, int k, int k_pad,
+                                                        int m_alloc, int8_t* __restrict__ q_tiled,
+                                                        int32_t* __restrict__ x_sums) {
+  __shared__ int red[32];
+  const int row = blockIdx.x;
+  const int8_t* xr = x + (size_t)row * k;
+  int sum = 0;
+  for (int c = threadIdx.x; c < k_pad / 16; c += blockDim.x) {
+    uint32_t v[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int b = 0; b < 16; ++b) {
+      const int kk = c * 16 + b;
+      if (kk < k) {
+        const int8_t e = xr[kk];
+        sum += e;
+        v[b >> 2] |= (uint32_t)(uint8_t)e << (8 * (b & 3));
+      }
+    }
+    *reinterpret_cast<uint4*>(q_tiled + q_tiled_offset(row, c * 16, m_alloc)) = make_uint4(v[0], v[1], v[2], v[3]);
+  }
+  if (x_sums) {
+    sum = block_reduce(sum, [](int a, int b) { return a + b; }, 0, red);
+    if (threadIdx.x == 0) x_sums[row] = sum;
+  }
+}
+
+// ---- launchers ---------------------------------------------------------------
+static inline int grid_for(long long work, int block, int cap = 148 * 16) {
+  long long g = (work + block - 1) / block;
+  if (g < 1) g = 1;
+  return (int)(g > cap ? cap : g);
+}
+
+cudaError_t launch_pack_w8(const int8_t* w, int n, int k, uint8_t* packed, int32_t* row_sums, cudaStream_t s) {
+  const int n_tiles = tiles_n(n), k_tiles = tiles_k8(k);
+  const long long chunks = (long long)n_tiles * k_tiles * (kTileBytes / 16);
+  pack_w8_kernel<<<grid_for(chunks, 256), 256, 0, s>>>(w, n, k, n_tiles, k_tiles, packed);
+  if (row_sums) row_sums_kernel<<<(n * 32 + 255) / 256, 256, 0, s>>>(w, n, k, row_sums);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_w4(const uint8_t* w4, const void* scales_f16, int n, int k, int blocksize, uint8_t* packed,
+                           float* kfsum, cudaStream_t s) {
+  const int n_tiles = tiles_n(n), k_tiles = tiles_k4(k);
+  const long long words = (long long)n_tiles * k_tiles * (kTileBytes / 4);
+  pack_w4_kernel<<<grid_for(words, 256), 256, 0, s>>>(w4, (const __half*)scales_f16, n, k, blocksize, n_tiles,
+                                                      k_tiles, packed);
+  w4_kfsum_kernel<<<(n + 127) / 128, 128, 0, s>>>(w4, (const __half*)scales_f16, n, k, blocksize, kfsum);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quantize_rows(const float* x, int m, int k, int k_pad, int m_alloc, int asymmetric,
+                                 int8_t* q_tiled, int8_t* q_rowmajor, float* scales, int32_t* zps,
+                                 cudaStream_t s) {
+  if (m <= 0) return cudaSuccess;
+  quantize_rows_kernel<<<m, 256, 0, s>>>(x, m, k, k_pad, m_alloc, asymmetric, q_tiled, q_rowmajor, scales, zps);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_retile_x8(const int8_t* x, int m, int k, int k_pad, int m_alloc, int8_t* q_tiled,
+                             int32_t* x_sums, cudaStream_t s) {
+  if (m <= 0) return cudaSuccess;
+  retile_x8_kernel<<<m, 256, 0, s>>>(x, m, k, k_pad, m_alloc, q_tiled, x_sums);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

@@ -1,0 +1,192 @@
+"""Host-side mirror of the reference operators on the hot path, over the C ABI.
+
+Each function takes torch CUDA tensors in the reference's own layouts, and mirrors the argument
+meaning of the reference kernel it replaces (cited per function; paths are inside the LiteRT
+source tree). torch only provides device memory and the current stream. There is no CPU
+fallback: every call goes to liblitert_b200.so.
+"""
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from ._lib import B200Error, check
+
+ACT_NONE, ACT_RELU, ACT_RELU_N1_TO_1, ACT_RELU6, ACT_TANH, ACT_SIGN_BIT, ACT_SIGMOID = range(7)
+DTYPE_F16, DTYPE_I8, DTYPE_F32 = 0, 1, 2
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t, dtype, name):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise B200Error(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise B200Error(f"{name} must be {dtype}, got {t.dtype}")
+    return t.contiguous()
+
+
+class Workspace:
+    """The two device buffers every op on one stream shares (see include/litert_b200.h)."""
+
+    def __init__(self, device="cuda", scratch_bytes=1 << 20):
+        lib = _lib.load()
+        self.device = torch.device(device)
+        self.zero = torch.empty(lib.b200_zero_workspace_bytes(), dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            check(lib.b200_zero_workspace_init(_ptr(self.zero), _stream()))
+        self.scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=self.device)
+        self.sdpa = None
+
+    def scratch_for(self, m, k):
+        need = _lib.load().b200_fc_scratch_bytes(m, k)
+        if self.scratch.numel() < need:
+            self.scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
+        return self.scratch
+
+    def sdpa_for(self, b, n, h, s_max):
+        need = _lib.load().b200_sdpa_workspace_bytes(b, n, h, s_max)
+        if self.sdpa is None or self.sdpa.numel() < need:
+            self.sdpa = torch.empty(need, dtype=torch.uint8, device=self.device)
+        return self.sdpa
+
+    def check_status(self):
+        """Synchronises and raises if a device-side bounded wait ran out."""
+        st = ctypes.c_int(0)
+        check(_lib.load().b200_read_status(_ptr(self.zero), _stream(), ctypes.byref(st)))
+
+
+class PackedInt8Weights:
+    """int8 filter [n,k] repacked once into the streamed tile layout, with its row sums
+    (the reference's persistent row_sums temporary, tflite/kernels/fully_connected.cc:697-708)."""
+
+    def __init__(self, w):
+        lib = _lib.load()
+        w = _need(w, torch.int8, "weights")
+        self.n, self.k = w.shape
+        self.packed = torch.empty(lib.b200_packed_w8_bytes(self.n, self.k), dtype=torch.uint8, device=w.device)
+        self.row_sums = torch.empty(self.n, dtype=torch.int32, device=w.device)
+        check(lib.b200_pack_w8(_ptr(w), self.n, self.k, _ptr(self.packed), _ptr(self.row_sums), _stream()))
+
+
+class PackedInt4Weights:
+    """Blockwise int4 filter (packed nibbles [n, ceil(k/2)], fp16 scales [n, k/blocksize])."""
+
+    def __init__(self, w4, scales_f16, blocksize):
+        lib = _lib.load()
+        w4 = _need(w4, torch.uint8, "w4")
+        sc = _need(scales_f16, torch.float16, "scales")
+        self.n = w4.shape[0]
+        self.k = sc.shape[1] * blocksize
+        self.blocksize = blocksize
+        if w4.shape[1] != (self.k + 1) // 2:
+            raise B200Error("w4 row length does not match the scales")
+        self.packed = torch.empty(lib.b200_packed_w4_bytes(self.n, self.k), dtype=torch.uint8, device=w4.device)
+        self.kfsum = torch.empty(self.n, dtype=torch.float32, device=w4.device)
+        check(lib.b200_pack_w4(_ptr(w4), _ptr(sc), self.n, self.k, blocksize, _ptr(self.packed), _ptr(self.kfsum),
+                               _stream()))
+
+
+def quantize_rows(x, asymmetric=True):
+    """tensor_utils::BatchQuantizeFloats (tflite/kernels/internal/portable_tensor_utils.h:158-176)."""
+    x = _need(x, torch.float32, "x")
+    m, k = x.shape
+    q = torch.empty((m, k), dtype=torch.int8, device=x.device)
+    scales = torch.empty(m, dtype=torch.float32, device=x.device)
+    zps = torch.zeros(m, dtype=torch.int32, device=x.device)
+    check(_lib.load().b200_quantize_rows(_ptr(x), m, k, 1 if asymmetric else 0, _ptr(q), _ptr(scales), _ptr(zps),
+                                         _stream()))
+    return q, scales, zps
+
+
+def fully_connected_int8(x, weights, bias, input_zero_point, output_zero_point, multipliers, shifts, act_min=-128,
+                         act_max=127, filter_zero_point=0, ws=None, out=None):
+    """Full-integer FULLY_CONNECTED (tflite/kernels/fully_connected.cc:1383-1421 per channel, 1255-1285 per
+    tensor). x int8 [..., k]; multipliers/shifts int32 tensors with n entries (per channel) or one."""
+    lib = _lib.load()
+    x = _need(x, torch.int8, "x")
+    k = weights.k
+    m = x.numel() // k
+    bias = _need(bias, torch.int32, "bias")
+    mult = _need(multipliers, torch.int32, "multipliers")
+    shift = _need(shifts, torch.int32, "shifts")
+    per_channel = 1 if mult.numel() > 1 else 0
+    ws = ws or Workspace(x.device)
+    y = out if out is not None else torch.empty((m, weights.n), dtype=torch.int8, device=x.device)
+    scratch = ws.scratch_for(m, k)
+    check(lib.b200_fc_int8(_ptr(x), m, k, _ptr(weights.packed), weights.n, _ptr(weights.row_sums), _ptr(bias),
+                           -int(input_zero_point), -int(filter_zero_point), int(output_zero_point), _ptr(mult),
+                           _ptr(shift), per_channel, int(act_min), int(act_max), _ptr(y), _ptr(ws.zero),
+                           _ptr(scratch), scratch.numel(), _stream()))
+    return y
+
+
+def fully_connected_hybrid(x, weights, filter_scales, bias=None, asymmetric_quantize_inputs=True,
+                           activation=ACT_NONE, ws=None, out=None):
+    """Dynamic-range FULLY_CONNECTED, EvalHybridDense (tflite/kernels/fully_connected.cc:763-858)."""
+    lib = _lib.load()
+    x = _need(x, torch.float32, "x")
+    k = weights.k
+    m = x.numel() // k
+    fs = _need(filter_scales, torch.float32, "filter_scales").reshape(-1)
+    if fs.numel() not in (1, weights.n):
+        raise B200Error("filter_scales must have 1 or n entries")
+    bias = _need(bias, torch.float32, "bias")
+    ws = ws or Workspace(x.device)
+    y = out if out is not None else torch.empty((m, weights.n), dtype=torch.float32, device=x.device)
+    scratch = ws.scratch_for(m, k)
+    check(lib.b200_fc_hybrid(_ptr(x), m, k, _ptr(weights.packed), weights.n, _ptr(weights.row_sums), _ptr(fs),
+                             1 if fs.numel() > 1 else 0, _ptr(bias), 1 if asymmetric_quantize_inputs else 0,
+                             int(activation), _ptr(y), _ptr(ws.zero), _ptr(scratch), scratch.numel(), _stream()))
+    return y
+
+
+def fully_connected_blockwise4(x, weights, bias=None, ws=None, out=None):
+    """Blockwise int4 FULLY_CONNECTED, EvalBlockwise4Bit (tflite/kernels/fully_connected.cc:1014-1086)."""
+    lib = _lib.load()
+    x = _need(x, torch.float32, "x")
+    k = weights.k
+    m = x.numel() // k
+    bias = _need(bias, torch.float32, "bias")
+    ws = ws or Workspace(x.device)
+    y = out if out is not None else torch.empty((m, weights.n), dtype=torch.float32, device=x.device)
+    scratch = ws.scratch_for(m, k)
+    check(lib.b200_fc_w4(_ptr(x), m, k, _ptr(weights.packed), weights.n, weights.blocksize, _ptr(weights.kfsum),
+                         _ptr(bias), _ptr(y), _ptr(ws.zero), _ptr(scratch), scratch.numel(), _stream()))
+    return y
+
+
+_DT = {torch.float16: DTYPE_F16, torch.int8: DTYPE_I8, torch.float32: DTYPE_F32}
+
+
+def sdpa_decode(q, k, v, lengths=None, mask=None, scale=None, logit_cap=0.0, k_scale=None, v_scale=None, ws=None):
+    """odml.scaled_dot_product_attention for one query token per sequence
+    (tflite/experimental/genai/sdpa.cc:361-662). q [b,1,n,h]; k, v [b,s_max,nkv,h]."""
+    lib = _lib.load()
+    if q.dtype not in (torch.float16, torch.float32) or k.dtype not in _DT or v.dtype != k.dtype:
+        raise B200Error("unsupported dtypes for sdpa_decode")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    b, t, n, h = q.shape
+    if t != 1:
+        raise B200Error("sdpa_decode handles one query token per sequence")
+    s_max, nkv = k.shape[1], k.shape[2]
+    lengths = _need(lengths, torch.int32, "lengths")
+    mask = _need(mask, torch.float32, "mask")
+    k_scale = _need(k_scale, torch.float32, "k_scale")
+    v_scale = _need(v_scale, torch.float32, "v_scale")
+    ws = ws or Workspace(q.device)
+    out = torch.empty_like(q)
+    wsb = ws.sdpa_for(b, n, h, s_max)
+    check(lib.b200_sdpa_decode(_ptr(q), _ptr(k), _ptr(v), _ptr(k_scale), _ptr(v_scale), _ptr(lengths), _ptr(mask),
+                               _ptr(out), b, n, nkv, h, s_max, _DT[q.dtype], _DT[k.dtype],
+                               float(scale) if scale else 0.0, float(logit_cap), _ptr(wsb), wsb.numel(), _stream()))
+    return out
