@@ -1,0 +1,44 @@
+"""Builds libtflite_b200_delegate.so (the TfLiteDelegate plugin) in-tree.
+
+The delegate is compiled against the LiteRT C headers where they lie in a LiteRT checkout
+(LITERT_ROOT, default /root/reference); two of its small C sources (TfLiteIntArray helpers) are
+compiled from there too. Without the checkout an already built library is kept as is.
+"""
+import os
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc", "delegate")
+LIB = os.path.join(HERE, "lib")
+LITERT_ROOT = os.environ.get("LITERT_ROOT", "/root/reference")
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+OUT = os.path.join(LIB, "libtflite_b200_delegate.so")
+
+
+def _newer(target, deps):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
+
+
+def build(force=False):
+    have_headers = os.path.exists(os.path.join(LITERT_ROOT, "tflite", "core", "c", "common.h"))
+    if not have_headers:
+        return OUT if os.path.exists(OUT) else None
+    from . import build as kernels_build
+
+    kernels = kernels_build.build_kernels(force)
+    srcs = [os.path.join(CSRC, f) for f in ("b200_delegate.cc", "device_arena.cc")]
+    deps = srcs + [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [kernels]
+    deps += [os.path.join(os.path.dirname(HERE), "include", f) for f in ("litert_b200.h", "litert_b200_delegate.h")]
+    if not force and not _newer(OUT, deps):
+        return OUT
+    ref_srcs = [os.path.join(LITERT_ROOT, "tflite", "core", "c", "common.cc"),
+                os.path.join(LITERT_ROOT, "tflite", "array.cc")]
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-shared", "-o", OUT] + srcs + ref_srcs + [
+        "-I" + LITERT_ROOT, "-I" + os.path.join(CUDA_HOME, "include"),
+        "-L" + LIB, "-llitert_b200", "-Wl,-rpath,$ORIGIN",
+        "-L" + os.path.join(CUDA_HOME, "lib64"), "-lcudart_static", "-ldl", "-lrt", "-lpthread"]
+    subprocess.check_call(cmd)
+    return OUT

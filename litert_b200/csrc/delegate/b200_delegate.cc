@@ -595,13 +595,13 @@ class DelegateKernel {
         op->x = idx(0);
         const TfLiteTensor& w = T[idx(1)];
         const auto* q = static_cast<const TfLiteBlockwiseQuantization*>(w.quantization.params);
-        const TfLiteTensor& s = T[q->scale];
+        const TfLiteTensor& scale_t = T[q->scale];
         op->n = w.dims->data[0];
         op->kdim = w.dims->data[1];
         DeviceMem w_stage, s_stage;
         const size_t row_bytes = (static_cast<size_t>(op->kdim) + 1) / 2;
         TF_LITE_ENSURE_STATUS(UploadRaw(ctx, w.data.raw, row_bytes * op->n, &w_stage));
-        TF_LITE_ENSURE_STATUS(UploadRaw(ctx, s.data.raw, s.bytes, &s_stage));
+        TF_LITE_ENSURE_STATUS(UploadRaw(ctx, scale_t.data.raw, scale_t.bytes, &s_stage));
         if (!op->packed.ensure(b200_packed_w4_bytes(op->n, op->kdim)) || !op->kfsum.ensure(sizeof(float) * op->n)) {
           TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed");
           return kTfLiteDelegateError;
@@ -837,6 +837,20 @@ void tflite_plugin_destroy_delegate(TfLiteDelegate* delegate) {
     }
   }
   delete st;
+}
+
+size_t b200_arena_plan(int n, const size_t* bytes, const int* first_use, const int* last_use, int num_ops,
+                       size_t* offsets) {
+  std::vector<b200::ArenaRequest> req(n > 0 ? n : 0);
+  for (int i = 0; i < n; ++i) {
+    req[i].bytes = bytes[i];
+    req[i].first_use = first_use[i];
+    req[i].last_use = last_use[i];
+  }
+  std::vector<size_t> off;
+  const size_t total = b200::PlanArena(req, num_ops, &off);
+  for (int i = 0; i < n; ++i) offsets[i] = off[i];
+  return total;
 }
 
 int b200_delegate_num_claimed_nodes(const TfLiteDelegate* delegate) {

@@ -32,13 +32,21 @@ size_t PlanArena(const std::vector<ArenaRequest>& requests, int num_ops, std::ve
     const ArenaRequest& r = requests[idx];
     if (r.bytes == 0) continue;
     const size_t size = AlignUp(r.bytes);
-    // lowest gap among the live-overlapping allocations
-    size_t candidate = 0;
+    // best fit: the smallest gap, among the allocations alive at the same time, that still
+    // holds the tensor; the open end of the slab only when no gap does
+    size_t cursor = 0, candidate = 0, best_gap = static_cast<size_t>(-1);
+    bool found = false;
     for (const Placed& p : placed) {
       if (p.last < r.first_use || p.first > r.last_use) continue;  // never alive together
-      if (candidate + size <= p.offset) break;                      // fits before this one
-      candidate = std::max(candidate, p.offset + p.size);
+      if (cursor + size <= p.offset && p.offset - cursor < best_gap) {
+        best_gap = p.offset - cursor;
+        candidate = cursor;
+        found = true;
+      }
+      cursor = std::max(cursor, p.offset + p.size);
+      if (best_gap == 0) break;
     }
+    if (!found) candidate = cursor;
     (*offsets)[idx] = candidate;
     Placed np{candidate, size, r.first_use, r.last_use};
     placed.insert(std::upper_bound(placed.begin(), placed.end(), np,

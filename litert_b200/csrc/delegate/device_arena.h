@@ -31,8 +31,9 @@ constexpr size_t kArenaAlignment = 256;
 // Assigns offsets; returns the slab size needed. Ordering: tensors alive for
 // the whole plan first, then by size descending, ties by first use (same
 // policy as ArenaPlanner::CreateTensorAllocationVector,
-// tflite/arena_planner.cc:442-472); each tensor takes the lowest gap that fits
-// among the already placed tensors whose lifetimes intersect its own.
+// tflite/arena_planner.cc:442-472); each tensor takes the smallest gap that
+// fits (best fit) among the already placed tensors whose lifetimes intersect its own,
+// as SimpleMemoryArena::Allocate does.
 size_t PlanArena(const std::vector<ArenaRequest>& requests, int num_ops, std::vector<size_t>* offsets);
 
 typedef void* (*ArenaAllocFn)(void* user, size_t bytes);

@@ -50,3 +50,25 @@ int ref_conv_multiplier(float in_scale, float w_scale, int has_bias, float bias_
   return tflite::GetQuantizedConvolutionMultipler(&ctx, &in, &w, &out, multiplier);
 }
 }
+
+// The reference's greedy gap search, tflite/simple_memory_arena.cc:370-434,
+// driven with a caller-chosen allocation order: offsets[i] for request
+// order[i]. Returns the high-water mark. Used to validate the delegate's
+// device-arena planner.
+#include "tflite/simple_memory_arena.h"
+extern "C" size_t ref_arena_offsets(int n, const size_t* sizes, const int* first, const int* last, const int* order,
+                                    size_t alignment, size_t* offsets) {
+  TfLiteContext ctx;
+  std::memset(&ctx, 0, sizeof(ctx));
+  ctx.ReportError = noop_report;
+  tflite::SimpleMemoryArena arena(alignment);
+  size_t high = 0;
+  for (int i = 0; i < n; ++i) {
+    const int r = order[i];
+    tflite::ArenaAllocWithUsageInterval alloc;
+    if (arena.Allocate(&ctx, alignment, sizes[r], r, first[r], last[r], &alloc) != kTfLiteOk) return (size_t)-1;
+    offsets[r] = alloc.offset;
+    if (alloc.offset + alloc.size > high) high = alloc.offset + alloc.size;
+  }
+  return high;
+}

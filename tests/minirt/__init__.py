@@ -1,0 +1,228 @@
+"""Python handle on the mini runtime (tests/minirt/minirt.cc) and on the delegate plugin.
+
+TEST INFRASTRUCTURE ONLY. The mini runtime is compiled against the LiteRT C headers where they
+lie (LITERT_ROOT, default /root/reference); a prebuilt libminirt.so is used when they are absent.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+LITERT_ROOT = os.environ.get("LITERT_ROOT", "/root/reference")
+LIB = os.path.join(HERE, "libminirt.so")
+
+# TfLiteType values (tflite/core/c/c_api_types.h)
+F32, I32, U8, I64, I16, I8, F16, I4 = 1, 2, 3, 4, 7, 9, 10, 18
+_NP = {F32: np.float32, I32: np.int32, U8: np.uint8, I8: np.int8, F16: np.float16, I4: np.uint8}
+# builtin operator codes (tflite/builtin_ops.h)
+OP_ADD, OP_FULLY_CONNECTED, OP_SOFTMAX = 0, 9, 25
+
+
+def build():
+    src = os.path.join(HERE, "minirt.cc")
+    have = os.path.exists(os.path.join(LITERT_ROOT, "tflite", "core", "c", "common.h"))
+    if not have:
+        if os.path.exists(LIB):
+            return LIB
+        raise RuntimeError("libminirt.so is missing and the LiteRT headers are not available to build it")
+    if os.path.exists(LIB) and os.path.getmtime(LIB) >= os.path.getmtime(src):
+        return LIB
+    subprocess.check_call(["g++", "-O1", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-shared", "-o", LIB, src,
+                           os.path.join(LITERT_ROOT, "tflite", "core", "c", "common.cc"),
+                           os.path.join(LITERT_ROOT, "tflite", "array.cc"), "-I" + LITERT_ROOT])
+    return LIB
+
+
+_CB = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_int)
+_ERR = ctypes.CFUNCTYPE(None, ctypes.c_char_p)
+
+
+class Delegate:
+    """Loads the plugin the way tflite/delegates/external/external_delegate.cc:39-64 does."""
+
+    def __init__(self, options=None, path=None):
+        from litert_b200 import build_delegate
+
+        path = path or build_delegate.build()
+        self.lib = ctypes.CDLL(path)
+        self.lib.tflite_plugin_create_delegate.restype = ctypes.c_void_p
+        self.lib.tflite_plugin_create_delegate.argtypes = [ctypes.POINTER(ctypes.c_char_p),
+                                                           ctypes.POINTER(ctypes.c_char_p), ctypes.c_size_t, _ERR]
+        self.lib.tflite_plugin_destroy_delegate.argtypes = [ctypes.c_void_p]
+        self.lib.b200_delegate_num_claimed_nodes.argtypes = [ctypes.c_void_p]
+        self.errors = []
+        self._err = _ERR(lambda m: self.errors.append(m.decode()))
+        options = options or {}
+        n = len(options)
+        keys = (ctypes.c_char_p * max(n, 1))(*[k.encode() for k in options])
+        vals = (ctypes.c_char_p * max(n, 1))(*[str(v).encode() for v in options.values()])
+        self.ptr = self.lib.tflite_plugin_create_delegate(keys, vals, n, self._err)
+
+    @property
+    def claimed(self):
+        return self.lib.b200_delegate_num_claimed_nodes(self.ptr)
+
+    def close(self):
+        if self.ptr:
+            self.lib.tflite_plugin_destroy_delegate(self.ptr)
+            self.ptr = None
+
+
+class MiniRuntime:
+    def __init__(self):
+        self.lib = ctypes.CDLL(build())
+        L = self.lib
+        L.mrt_create.restype = ctypes.c_void_p
+        L.mrt_last_error.restype = ctypes.c_char_p
+        L.mrt_tensor_data.restype = ctypes.c_void_p
+        L.mrt_tensor_bytes.restype = ctypes.c_size_t
+        for name in ("mrt_destroy", "mrt_last_error", "mrt_clear_error", "mrt_num_partitions", "mrt_plan_size",
+                     "mrt_num_cpu_nodes_in_plan", "mrt_invoke"):
+            getattr(L, name).argtypes = [ctypes.c_void_p]
+        L.mrt_apply_delegate.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        L.mrt_tensor_data.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        L.mrt_tensor_bytes.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        L.mrt_tensor_is_stale.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        L.mrt_set_cpu_callback.argtypes = [ctypes.c_void_p, _CB]
+        L.mrt_add_tensor.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                     ctypes.c_int, ctypes.c_void_p, ctypes.c_float, ctypes.c_int, ctypes.c_int,
+                                     ctypes.c_void_p, ctypes.c_int]
+        L.mrt_set_blockwise.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+        L.mrt_add_fully_connected.argtypes = [ctypes.c_void_p] + [ctypes.c_int] * 8
+        L.mrt_add_batch_matmul.argtypes = [ctypes.c_void_p] + [ctypes.c_int] * 6
+        L.mrt_add_composite.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int, ctypes.c_int,
+                                        ctypes.POINTER(ctypes.c_int), ctypes.c_int]
+        L.mrt_add_custom.argtypes = L.mrt_add_composite.argtypes
+        L.mrt_add_other.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                    ctypes.c_int]
+        L.mrt_set_io.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int,
+                                 ctypes.POINTER(ctypes.c_int)]
+        self.h = L.mrt_create()
+        self.meta = []  # (type, shape)
+        self._cb = None
+
+    # ---- graph construction
+    def tensor(self, ttype, shape, data=None, scale=0.0, zero_point=0, channel_scales=None, quantized_dimension=0):
+        dims = (ctypes.c_int * max(len(shape), 1))(*shape)
+        buf = None
+        if data is not None:
+            buf = np.ascontiguousarray(data)
+            ptr = buf.ctypes.data_as(ctypes.c_void_p)
+        else:
+            ptr = None
+        cs = None if channel_scales is None else np.ascontiguousarray(channel_scales, np.float32)
+        idx = self.lib.mrt_add_tensor(self.h, ttype, len(shape), dims, 1 if data is not None else 0, ptr,
+                                      float(scale), int(zero_point), 0 if cs is None else cs.size,
+                                      None if cs is None else cs.ctypes.data_as(ctypes.c_void_p), quantized_dimension)
+        self.meta.append((ttype, tuple(shape)))
+        return idx
+
+    def set_blockwise(self, tensor, scale_tensor, blocksize):
+        self.lib.mrt_set_blockwise(self.h, tensor, scale_tensor, blocksize)
+
+    def fully_connected(self, x, w, bias, y, activation=0, keep_num_dims=False, asymmetric=True, weights_format=0):
+        return self.lib.mrt_add_fully_connected(self.h, x, w, -1 if bias is None else bias, y, activation,
+                                                int(keep_num_dims), int(asymmetric), weights_format)
+
+    def batch_matmul(self, x, y, out, adj_x=False, adj_y=False, asymmetric=True):
+        return self.lib.mrt_add_batch_matmul(self.h, x, y, out, int(adj_x), int(adj_y), int(asymmetric))
+
+    def _ints(self, v):
+        return (ctypes.c_int * max(len(v), 1))(*v)
+
+    def composite(self, name, attributes, ins, out):
+        return self.lib.mrt_add_composite(self.h, name.encode(), attributes, len(attributes), len(ins),
+                                          self._ints(ins), out)
+
+    def custom(self, name, init_data, ins, out):
+        return self.lib.mrt_add_custom(self.h, name.encode(), init_data, len(init_data), len(ins), self._ints(ins), out)
+
+    def other(self, builtin_code, ins, out):
+        return self.lib.mrt_add_other(self.h, builtin_code, len(ins), self._ints(ins), out)
+
+    def set_io(self, ins, outs):
+        self.lib.mrt_set_io(self.h, len(ins), self._ints(ins), len(outs), self._ints(outs))
+
+    # ---- execution
+    def apply(self, delegate):
+        return self.lib.mrt_apply_delegate(self.h, delegate.ptr)
+
+    def set_cpu(self, fn):
+        self._cb = _CB(fn)
+        self.lib.mrt_set_cpu_callback(self.h, self._cb)
+
+    def invoke(self):
+        return self.lib.mrt_invoke(self.h)
+
+    def view(self, tensor):
+        ttype, shape = self.meta[tensor]
+        nbytes = self.lib.mrt_tensor_bytes(self.h, tensor)
+        raw = (ctypes.c_uint8 * nbytes).from_address(self.lib.mrt_tensor_data(self.h, tensor))
+        arr = np.frombuffer(raw, dtype=_NP[ttype])
+        return arr if ttype == I4 else arr.reshape(shape)
+
+    def write(self, tensor, data):
+        self.view(tensor)[...] = np.asarray(data).reshape(self.meta[tensor][1])
+
+    @property
+    def error(self):
+        return self.lib.mrt_last_error(self.h).decode()
+
+    @property
+    def partitions(self):
+        return self.lib.mrt_num_partitions(self.h)
+
+    @property
+    def cpu_nodes(self):
+        return self.lib.mrt_num_cpu_nodes_in_plan(self.h)
+
+    @property
+    def plan_size(self):
+        return self.lib.mrt_plan_size(self.h)
+
+    def close(self):
+        if self.h:
+            self.lib.mrt_destroy(self.h)
+            self.h = None
+
+
+def flex_map(values):
+    """Encodes {key: float} as a FlexBuffers map with 4-byte inline floats -- the form the SDPA
+    composite's attribute blob takes. Layout, back to front: root (offset to the map, type, width);
+    map = [keys vector offset][keys width][size][values...][value types]; keys vector of offsets to
+    NUL-terminated strings, sorted by key."""
+    import struct
+
+    keys = sorted(values)
+    buf = bytearray()
+    key_pos = []
+    for k in keys:
+        key_pos.append(len(buf))
+        buf += k.encode() + b"\0"
+    while len(buf) % 4:
+        buf += b"\0"
+    # keys vector (width 4): size, then offsets
+    buf += struct.pack("<I", len(keys))
+    keys_vec = len(buf)
+    for i, kp in enumerate(key_pos):
+        here = keys_vec + 4 * i
+        buf += struct.pack("<I", here - kp)
+    # map prefix: offset to keys vector, keys byte width, size
+    here = len(buf)
+    buf += struct.pack("<I", here - keys_vec)
+    buf += struct.pack("<I", 4)
+    buf += struct.pack("<I", len(keys))
+    map_pos = len(buf)
+    for k in keys:
+        buf += struct.pack("<f", values[k])
+    for _ in keys:
+        buf += bytes([(3 << 2) | 2])  # FLOAT, 4 bytes
+    while len(buf) % 4:
+        buf += b"\0"
+    root = len(buf)
+    buf += struct.pack("<I", root - map_pos)
+    buf += bytes([(9 << 2) | 2, 4])  # MAP with 4-byte elements; root width 4
+    return bytes(buf)

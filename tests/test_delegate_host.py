@@ -1,0 +1,211 @@
+"""Host-side logic of the delegate, exercised without a GPU through the mini runtime: plugin
+exports and options, the support predicate (what is claimed, what is left to the CPU kernels),
+loud failure plus roll-back when no CUDA device can be initialised, the device-arena planner
+against the reference's own arena code, and the FlexBuffers attribute reader."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from tests import minirt
+from tests.minirt import F16, F32, I4, I8, I32
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def plugin_path():
+    from litert_b200 import build_delegate
+
+    p = build_delegate.build()
+    if p is None:
+        pytest.skip("delegate library not built and LiteRT headers absent")
+    return p
+
+
+def test_plugin_exports_the_external_delegate_symbols(plugin_path):
+    lib = ctypes.CDLL(plugin_path)
+    text = open(os.path.join(ROOT, "include", "litert_b200_delegate.h")).read()
+    names = set(re.findall(r"\b(tflite_plugin_[a-z_]+|b200_[a-z0-9_]+)\s*\(", text))
+    assert {"tflite_plugin_create_delegate", "tflite_plugin_destroy_delegate"} <= names
+    for n in names:
+        assert hasattr(lib, n), n
+    lib.tflite_plugin_destroy_delegate(None)  # NULL is allowed
+
+
+def test_options(plugin_path):
+    d = minirt.Delegate({"device": 0, "buffer_handles": 1, "claim_bmm": 0})
+    assert d.ptr and not d.errors
+    d.close()
+    bad = minirt.Delegate({"no_such_option": "x"})
+    assert bad.ptr is None and "unknown option" in bad.errors[0]
+    inj = minirt.Delegate({"fail_on": "create"})
+    assert inj.ptr is None and "injected" in inj.errors[0]
+
+
+def _fc_graph(m, x_type, w_type, y_type, *, w_const=True, bias_type=None, per_channel=False, activation=0,
+              weights_format=0, w_shape=(3, 10), blockwise=False, sparse=False):
+    n, k = w_shape
+    x = m.tensor(x_type, (2, k), scale=0.5 if x_type == I8 else 0.0, zero_point=-1)
+    wdata = np.ones(w_shape, np.int8) if w_type == I8 else np.zeros((n, (k + 1) // 2), np.uint8)
+    kw = {}
+    if per_channel:
+        kw = dict(channel_scales=np.full(n, 0.25, np.float32))
+    elif w_type == I8:
+        kw = dict(scale=0.25)
+    w = m.tensor(w_type, w_shape, wdata if w_const else None, **kw)
+    if blockwise:
+        s = m.tensor(F16, (n, k // 32), np.ones((n, k // 32), np.float16))
+        m.set_blockwise(w, s, 32)
+    b = None
+    if bias_type is not None:
+        b = m.tensor(bias_type, (n,), np.zeros(n, np.int32 if bias_type == I32 else np.float32), scale=0.125)
+    y = m.tensor(y_type, (2, n), scale=1.0 if y_type == I8 else 0.0, zero_point=-1)
+    m.fully_connected(x, w, b, y, activation=activation, weights_format=weights_format)
+    m.set_io([x], [y])
+
+
+CLAIM_CASES = [
+    ("int8 per tensor", dict(x_type=I8, w_type=I8, y_type=I8, bias_type=I32), 1),
+    ("int8 per channel", dict(x_type=I8, w_type=I8, y_type=I8, per_channel=True), 1),
+    ("hybrid", dict(x_type=F32, w_type=I8, y_type=F32, bias_type=F32, activation=4), 1),
+    ("blockwise int4", dict(x_type=F32, w_type=I4, y_type=F32, w_shape=(4, 64), blockwise=True), 1),
+    ("int4 without block scales", dict(x_type=F32, w_type=I4, y_type=F32, w_shape=(4, 64)), 0),
+    ("non-constant weights", dict(x_type=F32, w_type=I8, y_type=F32, w_const=False), 0),
+    ("shuffled weights format", dict(x_type=I8, w_type=I8, y_type=I8, weights_format=1), 0),
+    ("int8 with tanh", dict(x_type=I8, w_type=I8, y_type=I8, activation=4), 0),
+    ("float weights", dict(x_type=F32, w_type=F32, y_type=F32), 0),
+    ("int8 in, float out", dict(x_type=I8, w_type=I8, y_type=F32), 0),
+]
+
+
+@pytest.mark.parametrize("name,kwargs,claimed", CLAIM_CASES, ids=[c[0] for c in CLAIM_CASES])
+def test_support_predicate_fully_connected(plugin_path, name, kwargs, claimed):
+    m, d = minirt.MiniRuntime(), minirt.Delegate()
+    if kwargs.get("w_type") == F32:
+        x = m.tensor(F32, (2, 10))
+        w = m.tensor(F32, (3, 10), np.ones((3, 10), np.float32))
+        y = m.tensor(F32, (2, 3))
+        m.fully_connected(x, w, None, y)
+        m.set_io([x], [y])
+    else:
+        _fc_graph(m, **kwargs)
+    rc = m.apply(d)
+    assert d.claimed == claimed
+    if claimed == 0:
+        assert rc == 0 and m.partitions == 0 and m.cpu_nodes == 1  # nothing claimed is not an error
+    m.close()
+    d.close()
+
+
+def test_support_predicate_bmm_and_sdpa(plugin_path):
+    m, d = minirt.MiniRuntime(), minirt.Delegate()
+    x = m.tensor(F32, (2, 10))
+    w = m.tensor(I8, (10, 3), np.ones((10, 3), np.int8), scale=0.1)
+    y0 = m.tensor(F32, (2, 3))
+    m.batch_matmul(x, w, y0)                       # claimed: hybrid, constant rhs
+    w2 = m.tensor(I8, (3, 10))                     # not constant
+    y1 = m.tensor(F32, (2, 10))
+    m.batch_matmul(y0, w2, y1)                     # not claimed
+    q = m.tensor(F32, (1, 1, 8, 64))
+    k = m.tensor(F32, (1, 32, 2, 64))
+    v = m.tensor(F32, (1, 32, 2, 64))
+    mask = m.tensor(F32, (1, 1, 1, 32))
+    o = m.tensor(F32, (1, 1, 8, 64))
+    m.composite("odml.scaled_dot_product_attention", minirt.flex_map({"scale": 0.125}), [q, k, v, mask], o)  # claimed
+    o2 = m.tensor(F32, (1, 1, 8, 64))
+    m.composite("odml.rms_norm", b"", [q], o2)     # some other composite: not claimed
+    o3 = m.tensor(F32, (1, 1, 8, 64))
+    m.custom("odml.scaled_dot_product_attention", b"", [q, k, v, mask], o3)  # custom-op form: claimed
+    q4 = m.tensor(F32, (1, 4, 8, 64))
+    mask4 = m.tensor(F32, (1, 1, 4, 32))
+    o4 = m.tensor(F32, (1, 4, 8, 64))
+    m.custom("odml.scaled_dot_product_attention", b"", [q4, k, v, mask4], o4)  # 4 query tokens: not claimed
+    m.set_io([x, q, k, v, mask, q4, mask4], [y1, o, o2, o3, o4])
+    m.apply(d)
+    assert d.claimed == 3
+    m.close()
+    d.close()
+
+
+def test_no_cuda_device_fails_loudly_and_rolls_back(plugin_path):
+    """On a host without a usable CUDA device the kernel's init must fail (no CPU fallback inside
+    the delegate), and the runtime must be left with its original plan."""
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    m, d = minirt.MiniRuntime(), minirt.Delegate()
+    _fc_graph(m, x_type=F32, w_type=I8, y_type=F32)
+    assert m.apply(d) == 2  # kTfLiteDelegateError
+    assert "cudaSetDevice" in m.error
+    assert m.partitions == 0 and m.cpu_nodes == 1 and m.plan_size == 1
+    m.close()
+    d.close()
+
+
+# ----------------------------------------------------------------------------- arena planner
+def _plan(lib, sizes, first, last, num_ops):
+    n = len(sizes)
+    offs = (ctypes.c_size_t * n)()
+    lib.b200_arena_plan.restype = ctypes.c_size_t
+    total = lib.b200_arena_plan(n, (ctypes.c_size_t * n)(*sizes), (ctypes.c_int * n)(*first), (ctypes.c_int * n)(*last),
+                                num_ops, offs)
+    return total, list(offs)
+
+
+def test_arena_planner_no_live_overlap_and_reuse(plugin_path):
+    lib = ctypes.CDLL(plugin_path)
+    rng = np.random.default_rng(4)
+    for trial in range(50):
+        n, ops = int(rng.integers(1, 40)), int(rng.integers(1, 12))
+        sizes = [int(s) for s in rng.integers(0, 5000, n)]
+        first = [int(f) for f in rng.integers(0, ops, n)]
+        last = [int(min(ops - 1, f + rng.integers(0, 4))) for f in first]
+        total, offs = _plan(lib, sizes, first, last, ops)
+        for i in range(n):
+            assert offs[i] % 256 == 0 and offs[i] + sizes[i] <= total
+            for j in range(i):
+                if sizes[i] == 0 or sizes[j] == 0:
+                    continue
+                alive_together = not (last[i] < first[j] or last[j] < first[i])
+                overlap = offs[i] < offs[j] + sizes[j] and offs[j] < offs[i] + sizes[i]
+                assert not (alive_together and overlap)
+    # a chain of equal-sized temporaries ping-pongs between two slots
+    total, offs = _plan(lib, [1000] * 6, [0, 1, 2, 3, 4, 5], [1, 2, 3, 4, 5, 5], 6)
+    assert total == 2 * 1024 and len(set(offs)) == 2
+
+
+def test_arena_planner_matches_reference_arena(plugin_path, oracle):
+    """Same ordering policy fed to the reference's SimpleMemoryArena (compiled from its own source)
+    must give the same offsets."""
+    ref = oracle.ref_lib()
+    if ref is None or not hasattr(ref, "ref_arena_offsets"):
+        pytest.skip("oracle/_ref not built")
+    ref.ref_arena_offsets.restype = ctypes.c_size_t
+    lib = ctypes.CDLL(plugin_path)
+    rng = np.random.default_rng(5)
+    for trial in range(30):
+        n, ops = int(rng.integers(2, 30)), int(rng.integers(2, 10))
+        sizes = [int(s) * 256 for s in rng.integers(1, 40, n)]
+        first = [int(f) for f in rng.integers(0, ops, n)]
+        last = [int(min(ops - 1, f + rng.integers(0, 3))) for f in first]
+        total, offs = _plan(lib, sizes, first, last, ops)
+        whole = [first[i] <= 0 and last[i] >= ops - 1 for i in range(n)]
+        order = sorted(range(n), key=lambda i: (not whole[i], -sizes[i], first[i], i))
+        roffs = (ctypes.c_size_t * n)()
+        rtotal = ref.ref_arena_offsets(n, (ctypes.c_size_t * n)(*sizes), (ctypes.c_int * n)(*first),
+                                       (ctypes.c_int * n)(*last), (ctypes.c_int * n)(*order), 256, roffs)
+        assert (total, offs) == (rtotal, list(roffs))
+
+
+# ----------------------------------------------------------------------------- attribute blob
+def test_flex_map_reader_through_the_predicate(plugin_path):
+    """The encoder used by the tests writes the documented FlexBuffers map layout; check a few
+    structural facts so the GPU tests' `scale` really reaches the kernel."""
+    blob = minirt.flex_map({"scale": 0.125, "logit_cap": 30.0})
+    assert blob[-1] == 4 and blob[-2] >> 2 == 9
+    assert b"logit_cap\0" in blob and b"scale\0" in blob
+    assert blob.index(b"logit_cap") < blob.index(b"scale")  # keys sorted

@@ -1,0 +1,281 @@
+"""The delegate end to end on a GPU, driven through the mini runtime the way the reference
+interpreter drives an external delegate: reference goldens through FULLY_CONNECTED /
+BATCH_MATMUL nodes, the SDPA composite and custom op against the oracle, mixed graphs with
+CPU nodes in between, buffer handles, and host-side fault injection with roll-back."""
+import numpy as np
+import pytest
+
+from tests import minirt
+from tests.golden import reference_vectors as gv
+from tests.minirt import F16, F32, I4, I8, I32, OP_SOFTMAX
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def rt():
+    m = minirt.MiniRuntime()
+    yield m
+    m.close()
+
+
+@pytest.fixture()
+def delegate():
+    d = minirt.Delegate()
+    yield d
+    d.close()
+
+
+def _int8_fc_graph(m, case, keep_num_dims=False):
+    in_scale, in_zp = gv.quantization_params_int8(*case["input_range"])
+    out_scale, out_zp = gv.quantization_params_int8(*case["output_range"])
+    xin = np.asarray(case["input"], np.float32)
+    xq = gv.quantize(xin, in_scale, in_zp).astype(np.int8)
+    n = len(case["weights"])
+    if case["kind"] == "per_tensor":
+        w_scale, w_zp = gv.quantization_params_int8(*case["weight_range"])
+        wq = gv.quantize(case["weights"], w_scale, w_zp).astype(np.int8)
+        w = m.tensor(I8, wq.shape, wq, scale=w_scale, zero_point=w_zp)
+        bs = np.float32(in_scale * w_scale)
+        bq = gv.quantize(case["bias"], bs, 0, -2**31, 2**31 - 1).astype(np.int32)
+        b = m.tensor(I32, (n,), bq, scale=bs)
+    else:
+        scales = np.asarray(case["scales"], np.float32)
+        wq = gv.per_channel_symmetric_quantize(case["weights"], scales)
+        w = m.tensor(I8, wq.shape, wq, channel_scales=scales)
+        bq = np.asarray([round(bv / float(np.float32(s * in_scale))) for bv, s in zip(case["bias"], scales)], np.int32)
+        b = m.tensor(I32, (n,), bq, channel_scales=scales * in_scale)
+    x = m.tensor(I8, xq.shape, scale=in_scale, zero_point=in_zp)
+    y = m.tensor(I8, (xq.shape[0], n), scale=out_scale, zero_point=out_zp)
+    m.fully_connected(x, w, b, y, activation=1, keep_num_dims=keep_num_dims)
+    m.set_io([x], [y])
+    m.write(x, xq)
+    return x, y
+
+
+@pytest.mark.parametrize("name", sorted(gv.FC_INT8))
+def test_int8_fc_goldens_through_the_delegate(rt, delegate, name):
+    x, y = _int8_fc_graph(rt, gv.FC_INT8[name])
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.partitions == 1 and rt.cpu_nodes == 0
+    assert rt.invoke() == 0, rt.error
+    assert rt.view(y).reshape(-1).tolist() == gv.FC_INT8[name]["expected"]
+    assert rt.invoke() == 0  # a second invocation reuses the packed weights
+    assert rt.view(y).reshape(-1).tolist() == gv.FC_INT8[name]["expected"]
+
+
+@pytest.mark.parametrize("name", sorted(gv.HYBRID_FC))
+def test_hybrid_fc_goldens_through_the_delegate(rt, delegate, oracle, name):
+    case = gv.HYBRID_FC[name]
+    if case["per_channel_scales"] is None:
+        wq, scale = gv.symmetric_quantize(case["weights"])
+        w = rt.tensor(I8, wq.shape, wq, scale=scale)
+        scales = np.asarray([scale], np.float32)
+    else:
+        scales = np.asarray(case["per_channel_scales"], np.float32)
+        wq = gv.per_channel_symmetric_quantize(case["weights"], scales)
+        w = rt.tensor(I8, wq.shape, wq, channel_scales=scales)
+    xin = np.asarray(case["input"], np.float32)
+    b = rt.tensor(F32, (3,), np.asarray([1, 2, 3], np.float32))
+    x = rt.tensor(F32, xin.shape)
+    y = rt.tensor(F32, (2, 3))
+    rt.fully_connected(x, w, b, y, activation=1, asymmetric=case["asymmetric"])
+    rt.set_io([x], [y])
+    rt.write(x, xin)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.invoke() == 0, rt.error
+    np.testing.assert_allclose(rt.view(y).reshape(-1), case["expected"], atol=case["max_abs_err"], rtol=0)
+    want = oracle.fc_hybrid(xin, wq, scales, np.asarray([1, 2, 3], np.float32), case["asymmetric"], oracle.ACT_RELU)
+    assert np.array_equal(rt.view(y), want)
+
+
+def test_blockwise_int4_fc_through_the_delegate(rt, delegate, oracle):
+    from litert_b200 import workloads
+
+    c = workloads.config3(3, 200, 320, seed=11)
+    w = rt.tensor(I4, (200, 320), c["w4"])
+    s = rt.tensor(F16, (200, 10), c["scales"])
+    rt.set_blockwise(w, s, 32)
+    bias = np.linspace(-1, 1, 200).astype(np.float32)
+    b = rt.tensor(F32, (200,), bias)
+    x = rt.tensor(F32, (3, 320))
+    y = rt.tensor(F32, (3, 200))
+    rt.fully_connected(x, w, b, y)
+    rt.set_io([x], [y])
+    rt.write(x, c["x"])
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.invoke() == 0, rt.error
+    want = oracle.fc_blockwise4(c["x"], c["w4"], c["scales"], 32, bias)
+    np.testing.assert_allclose(rt.view(y), want, rtol=1e-3, atol=1e-3 * np.abs(want).max())
+
+
+@pytest.mark.parametrize("name", ["SimpleTestQuantizedInt8", "MultipleNumBatchQuantizedInt8",
+                                  "BatchesAndUnitsGreaterThanAccumDimSize",
+                                  "BatchesAndUnitsGreaterThanAccumDimSizeAdjY"])
+def test_hybrid_bmm_goldens_through_the_delegate(rt, delegate, name):
+    c = gv.BMM_HYBRID[name]
+    yq, y_scale = gv.symmetric_quantize(c["y"])
+    w = rt.tensor(I8, c["y_shape"], yq.reshape(c["y_shape"]), scale=y_scale)
+    x = rt.tensor(F32, c["x_shape"])
+    out = rt.tensor(F32, c["out_shape"])
+    rt.batch_matmul(x, w, out, adj_y=c["adj_y"])
+    rt.set_io([x], [out])
+    rt.write(x, np.asarray(c["x"], np.float32))
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.invoke() == 0, rt.error
+    np.testing.assert_allclose(rt.view(out).reshape(-1), c["expected"], atol=c["max_abs_err"], rtol=0)
+
+
+@pytest.mark.parametrize("name", sorted(gv.BMM_INT8))
+def test_int8_bmm_goldens_through_the_delegate(rt, delegate, name):
+    c = gv.BMM_INT8[name]
+    (xs, xzp), (ys, yzp), (os_, ozp) = [gv.quantization_params_int8(*r) for r in c["ranges"]]
+    xq = gv.quantize(c["x"], xs, xzp).astype(np.int8).reshape(c["x_shape"])
+    yq = gv.quantize(c["y"], ys, yzp).astype(np.int8).reshape(c["y_shape"])
+    w = rt.tensor(I8, c["y_shape"], yq, scale=ys, zero_point=yzp)
+    x = rt.tensor(I8, c["x_shape"], scale=xs, zero_point=xzp)
+    out = rt.tensor(I8, (2, 3), scale=os_, zero_point=ozp)
+    rt.batch_matmul(x, w, out, adj_y=c["adj_y"])
+    rt.set_io([x], [out])
+    rt.write(x, xq)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.invoke() == 0, rt.error
+    assert rt.view(out).reshape(-1).tolist() == c["expected"]
+
+
+@pytest.mark.parametrize("form", ["composite", "custom"])
+@pytest.mark.parametrize("name", sorted(gv.SDPA_SHAPES))
+def test_sdpa_reference_shapes_through_the_delegate(rt, delegate, oracle, name, form):
+    p = gv.SDPA_SHAPES[name]
+    rng = np.random.default_rng(21)
+    shapes = [(p["b"], p["t"], p["n"], p["h"]), (p["b"], p["s"], p["nkv"], p["h"]), (p["b"], p["s"], p["nkv"], p["h"]),
+              (p["b"], 1, p["t"], p["s"])]
+    data = [rng.uniform(0, 1, s).astype(np.float32) for s in shapes]
+    ins = [rt.tensor(F32, s) for s in shapes]
+    out = rt.tensor(F32, shapes[0])
+    scale = 0.37
+    blob = minirt.flex_map({"scale": scale})
+    if form == "composite":
+        rt.composite("odml.scaled_dot_product_attention", blob, ins, out)
+    else:
+        rt.custom("odml.scaled_dot_product_attention", blob, ins, out)
+    rt.set_io(ins, [out])
+    for t, d in zip(ins, data):
+        rt.write(t, d)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.partitions == 1
+    assert rt.invoke() == 0, rt.error
+    want = oracle.sdpa_f32(*data, scale=scale)
+    np.testing.assert_allclose(rt.view(out), want, rtol=1e-4, atol=1e-5)
+    assert np.array_equal(rt.view(ins[0]), data[0])  # the query tensor is not scaled in place
+
+
+def test_sdpa_decode_shape_default_scale(rt, delegate, oracle):
+    rng = np.random.default_rng(22)
+    b, n, nkv, h, s = 2, 8, 1, 256, 384
+    shapes = [(b, 1, n, h), (b, s, nkv, h), (b, s, nkv, h), (b, 1, 1, s)]
+    q, k, v = [rng.standard_normal(sh).astype(np.float32) for sh in shapes[:3]]
+    mask = np.where(np.arange(s)[None, None, None, :] < np.asarray([300, 77])[:, None, None, None], 0, -1e30)
+    mask = mask.astype(np.float32)
+    ins = [rt.tensor(F32, sh) for sh in shapes]
+    out = rt.tensor(F32, shapes[0])
+    rt.composite("odml.scaled_dot_product_attention", b"", ins, out)  # no attributes: 1/sqrt(h)
+    rt.set_io(ins, [out])
+    for t, d in zip(ins, (q, k, v, mask)):
+        rt.write(t, d)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.invoke() == 0, rt.error
+    want = oracle.sdpa_f32(q, k, v, mask)
+    assert np.max(np.abs(rt.view(out) - want)) / np.max(np.abs(want)) <= 2e-2
+
+
+def _two_fc_with_cpu_node_between(m, rng):
+    w1 = np.clip(np.rint(rng.standard_normal((24, 40)) * 40), -127, 127).astype(np.int8)
+    w2 = np.clip(np.rint(rng.standard_normal((8, 24)) * 40), -127, 127).astype(np.int8)
+    x = m.tensor(F32, (5, 40))
+    t1 = m.tensor(F32, (5, 24))
+    t2 = m.tensor(F32, (5, 24))
+    y = m.tensor(F32, (5, 8))
+    a = m.tensor(I8, w1.shape, w1, scale=0.01)
+    b = m.tensor(I8, w2.shape, w2, scale=0.02)
+    m.fully_connected(x, a, None, t1)
+    m.other(OP_SOFTMAX, [t1], t2)  # stays on the CPU
+    m.fully_connected(t2, b, None, y)
+    m.set_io([x], [y])
+    return x, t1, t2, y, w1, w2
+
+
+@pytest.mark.parametrize("buffer_handles", [0, 1])
+def test_mixed_graph_two_partitions_with_a_cpu_node_between(rt, oracle, buffer_handles):
+    rng = np.random.default_rng(30)
+    d = minirt.Delegate({"buffer_handles": buffer_handles})
+    x, t1, t2, y, w1, w2 = _two_fc_with_cpu_node_between(rt, rng)
+    xin = rng.standard_normal((5, 40)).astype(np.float32)
+    rt.write(x, xin)
+    stale_seen = []
+
+    def cpu(node):
+        stale_seen.append(rt.lib.mrt_tensor_is_stale(rt.h, t1))
+        e = np.exp(rt.view(t1) - rt.view(t1).max(-1, keepdims=True))
+        rt.write(t2, e / e.sum(-1, keepdims=True))
+        return 0
+
+    rt.set_cpu(cpu)
+    assert rt.apply(d) == 0, rt.error
+    assert d.claimed == 2 and rt.partitions == 2 and rt.cpu_nodes == 1
+    assert rt.invoke() == 0, rt.error
+    h1 = oracle.fc_hybrid(xin, w1, np.asarray([0.01], np.float32))
+    e = np.exp(h1 - h1.max(-1, keepdims=True))
+    want = oracle.fc_hybrid((e / e.sum(-1, keepdims=True)).astype(np.float32), w2, np.asarray([0.02], np.float32))
+    assert np.array_equal(rt.view(t1), h1)
+    assert np.array_equal(rt.view(y), want)
+    assert stale_seen == [0]  # the runtime made the tensor readable before the CPU node ran
+    rt.close()
+    rt.h = None
+    d.close()
+
+
+def test_chain_in_one_partition_keeps_the_intermediate_on_the_device(rt, delegate, oracle):
+    rng = np.random.default_rng(31)
+    w1 = np.clip(np.rint(rng.standard_normal((300, 70)) * 40), -127, 127).astype(np.int8)
+    w2 = np.clip(np.rint(rng.standard_normal((33, 300)) * 40), -127, 127).astype(np.int8)
+    s1 = rng.uniform(1e-3, 1e-2, 300).astype(np.float32)
+    s2 = rng.uniform(1e-3, 1e-2, 33).astype(np.float32)
+    x = rt.tensor(F32, (9, 70))
+    t = rt.tensor(F32, (9, 300))
+    y = rt.tensor(F32, (9, 33))
+    rt.fully_connected(x, rt.tensor(I8, w1.shape, w1, channel_scales=s1), None, t, activation=1)
+    rt.fully_connected(t, rt.tensor(I8, w2.shape, w2, channel_scales=s2), None, y)
+    rt.set_io([x], [y])
+    xin = rng.standard_normal((9, 70)).astype(np.float32)
+    rt.write(x, xin)
+    rt.write(t, np.full((9, 300), 7.0, np.float32))
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.partitions == 1
+    assert rt.invoke() == 0, rt.error
+    h = oracle.fc_hybrid(xin, w1, s1, activation=oracle.ACT_RELU)
+    assert np.array_equal(rt.view(y), oracle.fc_hybrid(h, w2, s2))
+    assert np.all(rt.view(t) == 7.0)  # the intermediate never came back to the host
+
+
+@pytest.mark.parametrize("where", ["init", "prepare", "alloc"])
+def test_injected_failures_roll_back_to_the_cpu_plan(rt, where):
+    rng = np.random.default_rng(32)
+    d = minirt.Delegate({"fail_on": where})
+    x, t1, t2, y, w1, w2 = _two_fc_with_cpu_node_between(rt, rng)
+    assert rt.apply(d) == 2  # kTfLiteDelegateError
+    assert rt.partitions == 0 and rt.cpu_nodes == 3 and rt.plan_size == 3
+    ran = []
+    rt.set_cpu(lambda node: ran.append(node) or 0)
+    assert rt.invoke() == 0  # the untouched plan still runs, on the CPU kernels
+    assert ran == [0, 1, 2]
+    d.close()
+
+
+def test_injected_invoke_failure_is_reported(rt):
+    d = minirt.Delegate({"fail_on": "invoke"})
+    _int8_fc_graph(rt, gv.FC_INT8["SimpleTestPerChannelQuantizedInt8"])
+    assert rt.apply(d) == 0
+    assert rt.invoke() == 2
+    assert "injected failure in invoke" in rt.error
+    d.close()
