@@ -15,10 +15,12 @@ inline int m_tiles_for(int m) {
   const int g = (m + 7) / 8;
   return g <= 1 ? 1 : (g <= 2 ? 2 : (g <= 4 ? 4 : 8));
 }
-// Rows allocated in the tiled activation buffer for m real rows.
+// Rows allocated in the tiled activation buffer for m real rows: a multiple of the rows either
+// GEMM path takes per pass (8..64 for the mma.sync path, 16..256 for the tcgen05 path).
 inline int m_alloc_for(int m) {
-  if (m <= 64) return 8 * m_tiles_for(m);
-  return ((m + 63) / 64) * 64;
+  int nb = 16;
+  while (nb < m && nb < 256) nb *= 2;
+  return ((m + nb - 1) / nb) * nb;
 }
 
 cudaError_t launch_pack_w8(const int8_t* w, int n, int k, uint8_t* packed, int32_t* row_sums, cudaStream_t s);
@@ -71,11 +73,15 @@ struct FcParams {
 // Streamed-weights GEMM on the packed int8 tiles (any m; m > 64 runs in
 // chunks of 64 rows).
 cudaError_t launch_fc_i8(const FcParams& p, FcEpilogue epi, cudaStream_t s);
+// Same contract on the tcgen05 / TMEM path; activation rows are processed umma_rows_per_pass(m) at a
+// time and the tiled activation buffer must hold a multiple of that many rows.
+cudaError_t launch_fc_i8_umma(const FcParams& p, FcEpilogue epi, cudaStream_t s);
+int umma_rows_per_pass(int m);
 // Blockwise 4-bit weights, float out.
 cudaError_t launch_fc_w4(const FcParams& p, cudaStream_t s);
 
 constexpr int kZeroWsSlots = 256;            // >= CTAs per launch
-constexpr int kZeroWsSlotInts = 128 * 64;    // accumulators per slot
+constexpr int kZeroWsSlotInts = 128 * 256;   // accumulators per slot (128 rows x up to 256 activation rows)
 int device_sm_count();
 
 struct SdpaParams {

@@ -169,10 +169,23 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restr
   const int row = blockIdx.x;
   const float* xr = x + (size_t)row * k;
   float mn = xr[0], mx = xr[0];
-  for (int i = threadIdx.x; i < k; i += blockDim.x) {
-    const float v = xr[i];
-    mn = fminf(mn, v);
-    mx = fmaxf(mx, v);
+  if ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) {
+    const int k4 = k & ~3;
+    for (int i = threadIdx.x * 4; i < k4; i += blockDim.x * 4) {
+      const float4 f = *reinterpret_cast<const float4*>(xr + i);
+      mn = fminf(fminf(mn, f.x), fminf(f.y, fminf(f.z, f.w)));
+      mx = fmaxf(fmaxf(mx, f.x), fmaxf(f.y, fmaxf(f.z, f.w)));
+    }
+    for (int i = k4 + threadIdx.x; i < k; i += blockDim.x) {
+      mn = fminf(mn, xr[i]);
+      mx = fmaxf(mx, xr[i]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < k; i += blockDim.x) {
+      const float v = xr[i];
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
+    }
   }
   mn = block_reduce(mn, [](float a, float b) { return fminf(a, b); }, mn, red);
   mx = block_reduce(mx, [](float a, float b) { return fmaxf(a, b); }, mx, red);
@@ -226,25 +239,37 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restr
   const float inv = s_inv;
   const float zpf = (float)s_zp;
   const int lo = asymmetric ? -128 : -127;
-  for (int c = threadIdx.x; c < k_pad / 16; c += blockDim.x) {
-    uint32_t v[4] = {0, 0, 0, 0};
+  // round half away from zero (std::round): the fraction t - trunc(t) is exact
+  auto quant = [&](float v) -> uint32_t {
+    if (zero) return 0u;
+    const float t = asymmetric ? __fadd_rn(zpf, __fmul_rn(v, inv)) : __fmul_rn(v, inv);
+    float r = truncf(t);
+    if (fabsf(t - r) >= 0.5f) r += copysignf(1.0f, t);
+    int qv = (int)fmaxf(-129.0f, fminf(128.0f, r));
+    qv = max(lo, min(127, qv));
+    return (uint32_t)(uint8_t)(int8_t)qv;
+  };
+  const bool vec = ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
+  // four consecutive elements per thread and step: one float4 in, one 32-bit word out
+  for (int k4 = threadIdx.x * 4; k4 < k_pad; k4 += blockDim.x * 4) {
+    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (vec && k4 + 3 < k) {
+      const float4 f = *reinterpret_cast<const float4*>(xr + k4);
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
 #pragma unroll
-    for (int b = 0; b < 16; ++b) {
-      const int kk = c * 16 + b;
-      int qv = 0;
-      if (kk < k && !zero) {
-        const float t = asymmetric ? __fadd_rn(zpf, __fmul_rn(xr[kk], inv)) : __fmul_rn(xr[kk], inv);
-        qv = (int)roundf(t);
-        qv = max(lo, min(127, qv));
-      }
-      v[b >> 2] |= (uint32_t)(uint8_t)(int8_t)qv << (8 * (b & 3));
+      for (int b = 0; b < 4; ++b)
+        if (k4 + b < k) v[b] = xr[k4 + b];
     }
-    if (q_tiled)
-      *reinterpret_cast<uint4*>(q_tiled + q_tiled_offset(row, c * 16, m_alloc)) = make_uint4(v[0], v[1], v[2], v[3]);
+    uint32_t word = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+      if (k4 + b < k) word |= quant(v[b]) << (8 * b);
+    if (q_tiled) *reinterpret_cast<uint32_t*>(q_tiled + q_tiled_offset(row, k4, m_alloc)) = word;
     if (q_rowmajor) {
 #pragma unroll
-      for (int b = 0; b < 16; ++b)
-        if (c * 16 + b < k) q_rowmajor[(size_t)row * k + c * 16 + b] = (int8_t)(v[b >> 2] >> (8 * (b & 3)));
+      for (int b = 0; b < 4; ++b)
+        if (k4 + b < k) q_rowmajor[(size_t)row * k + k4 + b] = (int8_t)(word >> (8 * b));
     }
   }
 }

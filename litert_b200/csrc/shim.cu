@@ -3,6 +3,7 @@
 // header says so.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/litert_b200.h"
@@ -59,6 +60,21 @@ Scratch carve_scratch(void* base, int m, int k_tiles8) {
   off += (size_t)k_tiles8 * m_alloc * 128;
   s.bytes = off;
   return s;
+}
+
+// int8 GEMMs run on the tcgen05 path unless B200_FC_PATH=mma selects the mma.sync kernel
+// (kept for A/B measurement; both give identical results).
+bool use_umma() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* e = getenv("B200_FC_PATH");
+    cached = (e && !strcmp(e, "mma")) ? 0 : 1;
+  }
+  return cached == 1;
+}
+
+cudaError_t run_fc_i8(const b200::FcParams& p, b200::FcEpilogue epi, cudaStream_t s) {
+  return use_umma() ? b200::launch_fc_i8_umma(p, epi, s) : b200::launch_fc_i8(p, epi, s);
 }
 
 void fill_ws(b200::FcParams& p, void* d_zero_ws) {
@@ -183,7 +199,7 @@ int b200_fc_int8(const int8_t* d_x, int m, int k, const void* d_w_packed, int n,
   p.act_min = act_min; p.act_max = act_max;
   p.y = d_y;
   fill_ws(p, d_zero_ws);
-  e = b200::launch_fc_i8(p, b200::kEpiRequantI8, s);
+  e = run_fc_i8(p, b200::kEpiRequantI8, s);
   return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_fc_int8");
 }
 
@@ -217,7 +233,7 @@ int b200_fc_hybrid(const float* d_x, int m, int k, const void* d_w_packed, int n
   p.activation = activation;
   p.y = d_y;
   fill_ws(p, d_zero_ws);
-  e = b200::launch_fc_i8(p, b200::kEpiHybridF32, s);
+  e = run_fc_i8(p, b200::kEpiHybridF32, s);
   return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_fc_hybrid");
 }
 
