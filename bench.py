@@ -1,0 +1,301 @@
+#!/usr/bin/env python
+"""Decode benchmark: tokens/s of a Gemma-2B-shaped int8 (dynamic-range) decoder, with the HBM
+roofline of its dominant kernel (the streamed int8 GEMV) and a CPU baseline beside it.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--context C] [--impl ours|reference]
+
+One "step" is one decode step (one new token per sequence) over a KV cache that already holds
+`context` tokens. All inputs are synthetic: seeded random-init weights of the named architecture and
+random token ids. With --gpus N > 1 (launched under torchrun, one rank per GPU) every rank decodes
+its own batch on its own replica (independent invocations partitioned across GPUs, no data-path
+collective): weak scaling, aggregate tokens/s.
+
+--impl reference times the CPU implementation of the same graph (the oracle's vectorised,
+multi-threaded restatement of the reference kernels; the reference's own ruy/XNNPACK kernels cannot
+be built offline) on the host cores of the box, on a bounded sample of the workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode tokens/s (Gemma-2B-shaped int8) + GEMV HBM GB/s vs peak"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--context", type=int, default=1024, help="tokens already in the KV cache when timing starts")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="gemma2b", choices=["gemma2b", "tiny"])
+    ap.add_argument("--kv", default="f16", choices=["f16", "i8"])
+    ap.add_argument("--cpu-steps", type=int, default=6, help="decode steps of the CPU baseline sample")
+    return ap.parse_args()
+
+
+def model_config(name):
+    from litert_b200 import decoder as dec
+
+    return dict(dec.GEMMA_2B if name == "gemma2b" else dec.TINY)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get("hbm_gbs"), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+
+    def __init__(self, gpu_index):
+        self.samples = []
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            parts = [p.strip() for p in s.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_run(cfg, batch, steps, warmup, seed=1005):
+    """The CPU arm: all host threads, weights generated on the host with the same distributions."""
+    import oracle
+    import torch
+
+    oracle.build()
+    g = torch.Generator()
+    g.manual_seed(seed)
+
+    def w(n, k):
+        out = torch.empty((n, k), dtype=torch.int8)
+        step = max(1, (1 << 24) // k)
+        for r in range(0, n, step):
+            rows = min(step, n - r)
+            out[r:r + rows] = torch.randn((rows, k), generator=g).mul_(40).round_().clamp_(-127, 127)
+        return out.numpy()
+
+    def s(n):
+        return (torch.rand(n, generator=g) * (1e-2 - 1e-3) + 1e-3).numpy()
+
+    def gain(n):
+        return (torch.randn(n, generator=g) * 0.02 + 1.0).numpy()
+
+    d, qd, kd, f = cfg["d_model"], cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"], cfg["d_ff"]
+    layers = [dict(wq=w(qd, d), wk=w(kd, d), wv=w(kd, d), wo=w(d, qd), wgate=w(f, d), wup=w(f, d), wdown=w(d, f),
+                   sq=s(qd), sk=s(kd), sv=s(kd), so=s(d), sgate=s(f), sup=s(f), sdown=s(d), norm1=gain(d),
+                   norm2=gain(d)) for _ in range(cfg["n_layers"])]
+    weights = dict(layers=layers, embed=w(cfg["vocab"], d), embed_scales=s(cfg["vocab"]), final_norm=gain(d))
+    ref = oracle.DecoderRef(cfg, weights, batch, warmup + steps + 2, fast=True)
+    cores = oracle.fast().orcf_num_threads()
+    rng = np.random.default_rng(seed)
+    tok = rng.integers(0, cfg["vocab"], batch).astype(np.int32)
+    for _ in range(warmup):
+        tok, _ = ref.step(tok, want_logits=False)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok, _ = ref.step(tok, want_logits=False)
+    dt = time.perf_counter() - t0
+    ref.close()
+    return batch * steps / dt, dt / steps * 1e3, cores
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = model_config(args.model)
+    steps = max(1, min(args.steps, args.cpu_steps))
+    warm = 1
+    tps, ms, cores = cpu_reference_run(cfg, args.batch, steps, warm)
+    sample = (f"{steps} decode steps after {warm} warm-up, batch {args.batch}, context {warm}..{warm + steps} tokens "
+              f"(attention over a short cache; the {weight_bytes(cfg) / 1e9:.2f} GB of weights per step dominate)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 weights x int8 dynamically quantized activations, int32 accumulate, fp32 outputs",
+        "data": "synthetic",
+        "config": workload_config(args, cfg),
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def weight_bytes(cfg):
+    qd, kd = cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"]
+    per_layer = cfg["d_model"] * (qd + 2 * kd) + qd * cfg["d_model"] + 3 * cfg["d_model"] * cfg["d_ff"]
+    return cfg["n_layers"] * per_layer + cfg["vocab"] * cfg["d_model"]
+
+
+def workload_config(args, cfg):
+    return {"workload": f"config 5: Gemma-2B-shaped decoder, decode step, batch {args.batch} per GPU, "
+                        f"{args.context}-token KV context" if args.model == "gemma2b" else f"tiny decoder, batch {args.batch}",
+            "layers": cfg["n_layers"], "d_model": cfg["d_model"], "heads": cfg["n_heads"], "kv_heads": cfg["n_kv_heads"],
+            "head_dim": cfg["head_dim"], "d_ff": cfg["d_ff"], "vocab": cfg["vocab"], "batch_per_gpu": args.batch,
+            "context": args.context, "kv_cache": args.kv, "parallelism": f"replica x{args.gpus} (independent batches)",
+            "l2": "inputs larger than L2: every step streams the full weight set (2.5 GB >> 126 MB)"}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from litert_b200 import decoder as dec
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback in this package)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cfg = model_config(args.model)
+    max_seq = args.context + args.warmup + 2 * args.steps + 16
+    d = dec.Decoder(cfg, max_seq=max_seq, max_batch=args.batch, kv_dtype=args.kv, seed=1005 + rank,
+                    device=f"cuda:{local}")
+    rng = np.random.default_rng(1005 + rank)
+    first = rng.integers(0, cfg["vocab"], args.batch).astype(np.int32)
+    # prefill stand-in: fill the cache by decoding `context` tokens (untimed)
+    d.run(first, args.context, fetch=True)
+    stream = d.stream
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-resident timing: K steps of the captured graph, tokens fed back on the device
+    d.run(None, args.warmup, fetch=True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        d.run(None, args.steps, fetch=False)
+        e1.record(stream)
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    # ---- end to end through the public call: host tokens in, host tokens out, every step
+    tok = d.run(None, 1, fetch=True)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tok, _ = d.step(tok)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    # ---- per-kernel-class device time of one step (CUDA events around every launch)
+    prof = d.profile_step(tok)
+    launches = d.launches_per_step
+
+    times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = times.tolist()
+    if rank == 0:
+        tokens = args.batch * args.steps * world
+        peak, peak_kind = measured_peaks()
+        wbytes = weight_bytes(cfg)
+        gemv_ms, gemv_launches = prof["gemv"]
+        # algorithmic bytes of the GEMV launches of one step: every int8 weight once, plus per launch the
+        # per-channel scales and row sums (8 B per output channel), the quantized activation rows and the
+        # float outputs
+        n_out = cfg["n_layers"] * ((cfg["n_heads"] + 2 * cfg["n_kv_heads"]) * cfg["head_dim"] + 2 * cfg["d_model"]
+                                   + 2 * cfg["d_ff"]) + cfg["vocab"]
+        k_in = cfg["n_layers"] * (2 * cfg["d_model"] + cfg["n_heads"] * cfg["head_dim"] + cfg["d_ff"]) + cfg["d_model"]
+        gemv_bytes = wbytes + 8 * n_out + args.batch * (k_in + 4 * n_out)
+        achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9 if gemv_ms > 0 else None
+        line = {
+            "metric": METRIC, "value": tokens / (dev_ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 weights x int8 dynamically quantized activations, int32 accumulate, fp32 outputs",
+            "data": "synthetic", "config": workload_config(args, cfg),
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
+                    "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches * args.steps,
+            "launches_per_step": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "fc_umma_kernel (streamed int8 GEMV, all projections of one step)",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if achieved else None,
+                         "peak_kind": peak_kind, "traffic": None, "launches": gemv_launches,
+                         "algorithmic_bytes_per_step": gemv_bytes, "gemv_ms_per_step": gemv_ms,
+                         "whole_step_frac": (wbytes / (dev_ms / args.steps * 1e-3) / 1e9) / peak},
+            "step_breakdown_ms": {k: v[0] for k, v in prof.items()},
+        }
+        try:
+            steps = max(1, min(args.cpu_steps, args.steps))
+            tps, ms, cores = cpu_reference_run(cfg, args.batch, steps, 1)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                    "sample": f"{steps} decode steps, batch {args.batch}, short context, all host threads"}
+        except Exception as exc:  # the baseline is a report, not part of the product path
+            line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port",
+                                    "sample": f"failed: {exc}"}
+        print(json.dumps(line), flush=True)
+    d.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

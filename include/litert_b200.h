@@ -138,6 +138,76 @@ B200_API int b200_sdpa_decode(const void* d_q, const void* d_k, const void* d_v,
                               float scale, float logit_cap, void* d_workspace, size_t workspace_bytes,
                               void* stream);
 
+/* ---- Gemma-shaped decoder, one decode step per call ---------------------------
+ * A resident decoder for the decode benchmark: every projection is a dynamic-range
+ * hybrid FULLY_CONNECTED (b200_fc_hybrid semantics: per-row asymmetric input
+ * quantization, int8 per-channel weights), attention is b200_sdpa_decode over an
+ * fp16 or int8 KV cache kept on the device, and the ops in between (RMS norm,
+ * rotary embedding, GELU(tanh)*up, residual adds, hybrid embedding lookup, greedy
+ * argmax) follow the graph tensor/examples/gemma3/gemma3_graph.cc authors, with
+ * the Gemma-1 layout (no q/k norms, no post-norms). The whole step is one CUDA
+ * graph. No counterpart exists in the reference as a single entry point: there
+ * the same work is the Interpreter invoking the graph node by node
+ * (tflite/core/subgraph.cc:1666-1811).
+ *
+ * Tensor parallelism: with tp_size > 1 each rank holds the column shard of
+ * q/k/v, gate and up (heads and FFN channels split; the single KV head is
+ * replicated) and the row shard of o and down; the two partial sums per layer
+ * are combined by the all-reduce callback the host installs (NCCL). */
+typedef struct b200_decoder b200_decoder;
+
+typedef struct {
+  int n_layers, d_model, n_heads, n_kv_heads, head_dim, d_ff, vocab;
+  int max_seq, max_batch;
+  float rms_eps, rope_base, embed_scale;
+  int kv_dtype;          /* B200_DTYPE_F16 or B200_DTYPE_I8 */
+  int tp_size, tp_rank;  /* 1, 0 for a single GPU */
+} b200_decoder_config;
+
+/* All weight pointers are DEVICE pointers to row-major int8 [n,k] with one f32
+ * scale per output channel; they are repacked inside and may be freed after the
+ * call. With tp_size > 1 pass this rank's shard. */
+typedef struct {
+  const int8_t *wq, *wk, *wv, *wo, *wgate, *wup, *wdown;
+  const float *sq, *sk, *sv, *so, *sgate, *sup, *sdown;
+  const float *norm1, *norm2; /* [d_model] */
+} b200_decoder_layer_weights;
+
+/* Sum over ranks, in place, of `count` floats on `stream` (device buffer). */
+typedef int (*b200_allreduce_fn)(void* user, float* d_buf, size_t count, void* stream);
+
+B200_API int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_decoder** out);
+B200_API void b200_decoder_destroy(b200_decoder* dec);
+B200_API int b200_decoder_set_layer(b200_decoder* dec, int layer, const b200_decoder_layer_weights* w);
+/* Embedding table [vocab, d_model] (also the LM head; with tp_size > 1 the LM
+ * head uses rows [rank*vocab/tp, (rank+1)*vocab/tp) and the logits are left
+ * sharded), per-row scales [vocab], final norm gain [d_model]. */
+B200_API int b200_decoder_set_embedding(b200_decoder* dec, const int8_t* d_table, const float* d_row_scales,
+                                        const float* d_final_norm);
+B200_API int b200_decoder_set_allreduce(b200_decoder* dec, b200_allreduce_fn fn, void* user);
+B200_API int b200_decoder_reset(b200_decoder* dec);
+/* One token per sequence. h_tokens / h_next_tokens are HOST arrays of `batch`
+ * ints (pinned memory avoids a staging copy); d_logits (optional, device,
+ * [batch, vocab]) receives the logits. Synchronises the stream before returning
+ * when h_next_tokens is given. */
+B200_API int b200_decoder_step(b200_decoder* dec, const int32_t* h_tokens, int batch, int32_t* h_next_tokens,
+                               float* d_logits);
+/* Device-resident variant: feeds the previous step's greedy tokens back without
+ * touching the host (first call after a reset uses h_first_tokens). Runs `steps`
+ * steps; the last tokens are copied to h_next_tokens when given. */
+B200_API int b200_decoder_run(b200_decoder* dec, const int32_t* h_first_tokens, int batch, int steps,
+                              int32_t* h_next_tokens);
+/* Runs ONE step eagerly (no graph) with CUDA events around every launch and
+ * returns the device time per kernel class: [0] the streamed GEMVs, [1]
+ * attention, [2] the glue kernels (ms), and how many launches each class had.
+ * Advances the sequence like a normal step. */
+B200_API int b200_decoder_profile_step(b200_decoder* dec, const int32_t* h_tokens, int batch, float* ms_by_class,
+                                       int* launches_by_class);
+/* Message of the last b200_decoder_* failure on the calling thread. */
+B200_API const char* b200_decoder_last_error(void);
+/* Number of kernels one step launches (for reporting). */
+B200_API int b200_decoder_launches_per_step(const b200_decoder* dec);
+
 #ifdef __cplusplus
 }
 #endif

@@ -31,7 +31,32 @@ SIGNATURES = {
     "b200_sdpa_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "b200_sdpa_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _sz,
                               _vp]),
+    "b200_decoder_create": (_i, [_vp, _vp, ctypes.POINTER(_vp)]),
+    "b200_decoder_destroy": (None, [_vp]),
+    "b200_decoder_set_layer": (_i, [_vp, _i, _vp]),
+    "b200_decoder_set_embedding": (_i, [_vp, _vp, _vp, _vp]),
+    "b200_decoder_set_allreduce": (_i, [_vp, _vp, _vp]),
+    "b200_decoder_reset": (_i, [_vp]),
+    "b200_decoder_step": (_i, [_vp, _vp, _i, _vp, _vp]),
+    "b200_decoder_run": (_i, [_vp, _vp, _i, _i, _vp]),
+    "b200_decoder_launches_per_step": (_i, [_vp]),
+    "b200_decoder_profile_step": (_i, [_vp, _vp, _i, _vp, _vp]),
+    "b200_decoder_last_error": (ctypes.c_char_p, []),
 }
+
+
+class DecoderConfig(ctypes.Structure):
+    """b200_decoder_config of include/litert_b200.h."""
+    _fields_ = [(n, _i) for n in ("n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim", "d_ff", "vocab",
+                                  "max_seq", "max_batch")] + \
+               [(n, _f) for n in ("rms_eps", "rope_base", "embed_scale")] + \
+               [(n, _i) for n in ("kv_dtype", "tp_size", "tp_rank")]
+
+
+class DecoderLayerWeights(ctypes.Structure):
+    """b200_decoder_layer_weights of include/litert_b200.h (device pointers)."""
+    _fields_ = [(n, _vp) for n in ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown", "sq", "sk", "sv", "so", "sgate",
+                                   "sup", "sdown", "norm1", "norm2")]
 
 _lib = None
 

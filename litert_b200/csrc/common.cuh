@@ -73,14 +73,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // the wait had succeeded: control flow stays uniform (every barrier is still
 // reached, every accumulator still freed), later waits return at once, the
 // kernel ends, and the host sees a non-zero status instead of a hung GPU.
-constexpr uint32_t kWaitSpins = 1u << 22;
+constexpr unsigned long long kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // one second per wait
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   int* status, int code) {
   if (*abort_flag) return;
-  for (uint32_t i = 0; i < kWaitSpins; ++i) {
+  if (mbar_try_wait(bar, parity)) return;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return;
-    if ((i & 1023u) == 1023u && *abort_flag) return;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return;
+      if (global_timer_ns() - t0 > kWaitBudgetNs) break;
+    }
   }
   *abort_flag = 1;
   atomicCAS(status, 0, code);

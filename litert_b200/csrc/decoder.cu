@@ -1,0 +1,479 @@
+// Resident Gemma-shaped decoder: weights packed once on the device, KV cache on
+// the device, one decode step = one CUDA graph over the GEMV, attention and glue
+// kernels. C ABI in include/litert_b200.h (b200_decoder_*).
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <vector>
+
+#include "../../include/litert_b200.h"
+#include "common.cuh"
+#include "decoder_kernels.h"
+#include "kernels.h"
+
+namespace {
+
+using namespace b200;
+
+struct DevBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+  ~DevBuf() { release(); }
+  void release() {
+    if (p) cudaFree(p);
+    p = nullptr;
+    bytes = 0;
+  }
+  cudaError_t alloc(size_t n) {
+    release();
+    if (n == 0) return cudaSuccess;
+    cudaError_t e = cudaMalloc(&p, n);
+    if (e == cudaSuccess) bytes = n;
+    return e;
+  }
+  template <typename T>
+  T* as() const { return static_cast<T*>(p); }
+};
+
+// One packed projection: y[n] = hybrid_fc(x[k]).
+struct Projection {
+  int n = 0, k = 0;
+  DevBuf packed, row_sums, scales;
+};
+
+struct Layer {
+  Projection qkv, o, gate_up, down;
+  DevBuf norm1, norm2;
+  DevBuf k_cache, v_cache, k_scale, v_scale;
+};
+
+}  // namespace
+
+struct b200_decoder {
+  b200_decoder_config cfg;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  std::vector<std::unique_ptr<Layer>> layers;
+  Projection lm_head;
+  DevBuf embed_table, embed_scales, final_norm;
+  // activations and scratch
+  DevBuf tokens, next_tokens, positions, attn_len;
+  DevBuf h, qkv, q, attn, proj, gate_up, down_out, logits;
+  DevBuf q_d, q_a, q_f;         // tiled int8 activations for K = d_model, heads*head_dim, d_ff
+  DevBuf sc_d, sc_a, sc_f, zp_d, zp_a, zp_f;
+  DevBuf zero_ws, sdpa_ws, arg_val, arg_idx;
+  int32_t *h_tokens_pinned = nullptr, *h_next_pinned = nullptr;
+  b200_allreduce_fn allreduce = nullptr;
+  void* allreduce_user = nullptr;
+  cudaGraphExec_t graph[257] = {nullptr};  // indexed by batch
+  int launches = 0;
+  // per-kernel-class timing of one eager step (b200_decoder_profile_step)
+  bool profiling = false;
+  std::vector<cudaEvent_t> prof_events;  // start/stop pairs
+  std::vector<int> prof_class;           // 0 = GEMV, 1 = attention, 2 = glue
+};
+
+namespace {
+
+thread_local char g_dec_error[512] = "";
+int dec_fail(int code, const char* what, cudaError_t e = cudaSuccess) {
+  if (e != cudaSuccess) {
+    snprintf(g_dec_error, sizeof(g_dec_error), "%s: %s", what, cudaGetErrorString(e));
+  } else {
+    snprintf(g_dec_error, sizeof(g_dec_error), "%s", what);
+  }
+  return code;
+}
+#define DEC_CUDA(expr)                                              \
+  do {                                                              \
+    cudaError_t _e = (expr);                                        \
+    if (_e != cudaSuccess) return dec_fail(B200_ERR_CUDA, #expr, _e); \
+  } while (0)
+
+struct ProfScope {
+  b200_decoder* d;
+  ProfScope(b200_decoder* dec, int cls) : d(dec) {
+    if (!d->profiling) return;
+    cudaEvent_t a, b;
+    cudaEventCreate(&a);
+    cudaEventCreate(&b);
+    d->prof_events.push_back(a);
+    d->prof_events.push_back(b);
+    d->prof_class.push_back(cls);
+    cudaEventRecord(a, d->stream);
+  }
+  ~ProfScope() {
+    if (d->profiling) cudaEventRecord(d->prof_events.back(), d->stream);
+  }
+};
+
+#define GLUE_CUDA(expr)      \
+  do {                       \
+    ProfScope _scope(d, 2);  \
+    DEC_CUDA(expr);          \
+  } while (0)
+
+size_t q_tiled_bytes(int m_alloc, int k) { return (size_t)tiles_k8(k) * m_alloc * 128; }
+
+// Concatenates row-major [n_i, k] int8 matrices (and their scales) and packs them as one projection.
+int build_projection(b200_decoder* d, Projection* pr, int k, std::initializer_list<const int8_t*> ws,
+                     std::initializer_list<const float*> ss, std::initializer_list<int> ns) {
+  int n = 0;
+  for (int v : ns) n += v;
+  pr->n = n;
+  pr->k = k;
+  DevBuf staging;
+  DEC_CUDA(staging.alloc((size_t)n * k));
+  DEC_CUDA(pr->scales.alloc(sizeof(float) * n));
+  DEC_CUDA(pr->row_sums.alloc(sizeof(int32_t) * n));
+  DEC_CUDA(pr->packed.alloc((size_t)tiles_n(n) * tiles_k8(k) * kTileBytes));
+  size_t row = 0;
+  auto wi = ws.begin();
+  auto si = ss.begin();
+  for (int v : ns) {
+    DEC_CUDA(cudaMemcpyAsync(staging.as<int8_t>() + row * k, *wi, (size_t)v * k, cudaMemcpyDeviceToDevice, d->stream));
+    DEC_CUDA(cudaMemcpyAsync(pr->scales.as<float>() + row, *si, sizeof(float) * v, cudaMemcpyDeviceToDevice, d->stream));
+    row += v;
+    ++wi;
+    ++si;
+  }
+  DEC_CUDA(launch_pack_w8(staging.as<int8_t>(), n, k, pr->packed.as<uint8_t>(), pr->row_sums.as<int32_t>(), d->stream));
+  DEC_CUDA(cudaStreamSynchronize(d->stream));  // staging dies here
+  return B200_OK;
+}
+
+cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_t* q_tiled, const float* scales,
+                   const int32_t* zps, float* y) {
+  FcParams p;
+  memset(&p, 0, sizeof(p));
+  p.w_packed = pr.packed.as<uint8_t>();
+  p.q_tiled = q_tiled;
+  p.m = batch;
+  p.n = pr.n;
+  p.k = pr.k;
+  p.n_tiles = tiles_n(pr.n);
+  p.k_tiles = tiles_k8(pr.k);
+  p.m_alloc = m_alloc_for(batch);
+  p.in_scales = scales;
+  p.in_zps = zps;
+  p.w_scales = pr.scales.as<float>();
+  p.per_channel = 1;
+  p.row_sums = pr.row_sums.as<int32_t>();
+  p.activation = 0;
+  p.y = y;
+  uint8_t* z = d->zero_ws.as<uint8_t>();
+  p.status = reinterpret_cast<int*>(z);
+  p.ws_count = reinterpret_cast<int32_t*>(z + zero_ws_counter_off());
+  p.ws_acc = reinterpret_cast<int32_t*>(z + zero_ws_acc_off());
+  ++d->launches;
+  ProfScope scope(d, 0);
+  return launch_fc_i8_umma(p, kEpiHybridF32, d->stream);
+}
+
+// Enqueues one full decode step for `batch` sequences on the decoder's stream.
+int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
+  const b200_decoder_config& c = d->cfg;
+  cudaStream_t s = d->stream;
+  const int m_alloc = m_alloc_for(batch);
+  const int qdim = c.n_heads * c.head_dim;
+  d->launches = 0;
+  auto count = [&](int n = 1) { d->launches += n; };
+  GLUE_CUDA(launch_embed(d->tokens.as<int32_t>(), d->embed_table.as<int8_t>(), d->embed_scales.as<float>(), batch,
+                        c.d_model, c.embed_scale, d->h.as<float>(), d->positions.as<int32_t>(),
+                        d->attn_len.as<int32_t>(), s));
+  count();
+  for (int l = 0; l < c.n_layers; ++l) {
+    Layer& L = *d->layers[l];
+    GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), l == 0 ? nullptr : d->down_out.as<float>(), L.norm1.as<float>(),
+                                   batch, c.d_model, c.rms_eps, m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(),
+                                   d->zp_d.as<int32_t>(), s));
+    count();
+    DEC_CUDA(run_fc(d, L.qkv, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), d->qkv.as<float>()));
+    GLUE_CUDA(launch_rope_cache(d->qkv.as<float>(), batch, c.n_heads, c.n_kv_heads, c.head_dim, c.rope_base,
+                               d->positions.as<int32_t>(), c.max_seq, d->q.as<float>(), L.k_cache.p, L.v_cache.p,
+                               L.k_scale.as<float>(), L.v_scale.as<float>(), c.kv_dtype == B200_DTYPE_I8, s));
+    count();
+    SdpaParams sp;
+    memset(&sp, 0, sizeof(sp));
+    sp.q = d->q.p;
+    sp.k = L.k_cache.p;
+    sp.v = L.v_cache.p;
+    sp.k_scale = L.k_scale.as<float>();
+    sp.v_scale = L.v_scale.as<float>();
+    sp.lengths = d->attn_len.as<int32_t>();
+    sp.out = d->attn.p;
+    sp.b = batch;
+    sp.n = c.n_heads;
+    sp.nkv = c.n_kv_heads;
+    sp.h = c.head_dim;
+    sp.s_max = c.max_seq;
+    sp.q_dtype = 1;
+    sp.kv_dtype = c.kv_dtype == B200_DTYPE_I8 ? 1 : 0;
+    sp.scale = 1.0f / sqrtf((float)c.head_dim);
+    sp.ws = d->sdpa_ws.as<float>();
+    sp.ws_bytes = d->sdpa_ws.bytes;
+    sp.status = d->zero_ws.as<int>();
+    {
+      ProfScope scope(d, 1);
+      DEC_CUDA(launch_sdpa_decode(sp, s));
+    }
+    count(2);
+    GLUE_CUDA(launch_quantize_rows(d->attn.as<float>(), batch, qdim, tiles_k8(qdim) * 128, m_alloc, 1,
+                                  d->q_a.as<int8_t>(), nullptr, d->sc_a.as<float>(), d->zp_a.as<int32_t>(), s));
+    count();
+    DEC_CUDA(run_fc(d, L.o, batch, d->q_a.as<int8_t>(), d->sc_a.as<float>(), d->zp_a.as<int32_t>(), d->proj.as<float>()));
+    GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->proj.as<float>(), L.norm2.as<float>(), batch, c.d_model,
+                                   c.rms_eps, m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), s));
+    count();
+    DEC_CUDA(run_fc(d, L.gate_up, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(),
+                    d->gate_up.as<float>()));
+    GLUE_CUDA(launch_geglu_quant(d->gate_up.as<float>(), batch, c.d_ff, m_alloc, d->q_f.as<int8_t>(), d->sc_f.as<float>(),
+                                d->zp_f.as<int32_t>(), s));
+    count();
+    DEC_CUDA(run_fc(d, L.down, batch, d->q_f.as<int8_t>(), d->sc_f.as<float>(), d->zp_f.as<int32_t>(),
+                    d->down_out.as<float>()));
+  }
+  GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->down_out.as<float>(), d->final_norm.as<float>(), batch, c.d_model,
+                                 c.rms_eps, m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), s));
+  count();
+  float* logits = d_logits_out ? d_logits_out : d->logits.as<float>();
+  DEC_CUDA(run_fc(d, d->lm_head, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), logits));
+  GLUE_CUDA(launch_argmax(logits, batch, c.vocab, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
+                         d->next_tokens.as<int32_t>(), d->positions.as<int32_t>(), c.max_seq, s));
+  count(2);
+  return B200_OK;
+}
+
+// Graph of one step (default logits buffer), captured on first use per batch size.
+int ensure_graph(b200_decoder* d, int batch) {
+  if (d->graph[batch]) return B200_OK;
+  // Run once uncaptured so that every kernel's one-time attribute setup happens outside capture.
+  // The warm-up advances the positions (restored below) and writes one cache row and the scratch
+  // buffers, all of which the next real step overwrites.
+  std::vector<int32_t> saved(d->cfg.max_batch);
+  DEC_CUDA(cudaMemcpyAsync(saved.data(), d->positions.p, sizeof(int32_t) * saved.size(), cudaMemcpyDeviceToHost, d->stream));
+  DEC_CUDA(cudaStreamSynchronize(d->stream));
+  int rc = enqueue_step(d, batch, nullptr);
+  if (rc) return rc;
+  DEC_CUDA(cudaMemcpyAsync(d->positions.p, saved.data(), sizeof(int32_t) * saved.size(), cudaMemcpyHostToDevice, d->stream));
+  DEC_CUDA(cudaStreamSynchronize(d->stream));
+  cudaGraph_t g = nullptr;
+  DEC_CUDA(cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal));
+  rc = enqueue_step(d, batch, nullptr);
+  cudaError_t e = cudaStreamEndCapture(d->stream, &g);
+  if (rc) {
+    if (g) cudaGraphDestroy(g);
+    return rc;
+  }
+  if (e != cudaSuccess) return dec_fail(B200_ERR_CUDA, "cudaStreamEndCapture", e);
+  e = cudaGraphInstantiate(&d->graph[batch], g, 0);
+  cudaGraphDestroy(g);
+  if (e != cudaSuccess) return dec_fail(B200_ERR_CUDA, "cudaGraphInstantiate", e);
+  return B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_decoder** out) {
+  if (!config || !out) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_create: null argument");
+  const b200_decoder_config& c = *config;
+  if (c.n_layers <= 0 || c.d_model <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.head_dim <= 0 || c.d_ff <= 0 ||
+      c.vocab <= 0 || c.max_seq <= 0 || c.max_batch <= 0 || c.max_batch > 256 || c.n_heads % c.n_kv_heads != 0 ||
+      c.head_dim % 2 != 0)
+    return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_create: bad configuration");
+  if (c.kv_dtype != B200_DTYPE_F16 && c.kv_dtype != B200_DTYPE_I8)
+    return dec_fail(B200_ERR_UNSUPPORTED, "b200_decoder_create: kv_dtype must be f16 or int8");
+  if (c.tp_size > 1) return dec_fail(B200_ERR_UNSUPPORTED, "b200_decoder_create: tensor parallelism is not built yet");
+  auto d = std::make_unique<b200_decoder>();
+  d->cfg = c;
+  if (d->cfg.tp_size < 1) d->cfg.tp_size = 1;
+  if (stream) {
+    d->stream = static_cast<cudaStream_t>(stream);
+  } else {
+    DEC_CUDA(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+    d->own_stream = true;
+  }
+  const int B = c.max_batch, m_alloc = m_alloc_for(B), qdim = c.n_heads * c.head_dim;
+  const int kvdim = c.n_kv_heads * c.head_dim;
+  DEC_CUDA(d->tokens.alloc(sizeof(int32_t) * B));
+  DEC_CUDA(d->next_tokens.alloc(sizeof(int32_t) * B));
+  DEC_CUDA(d->positions.alloc(sizeof(int32_t) * B));
+  DEC_CUDA(d->attn_len.alloc(sizeof(int32_t) * B));
+  DEC_CUDA(d->h.alloc(sizeof(float) * B * c.d_model));
+  DEC_CUDA(d->qkv.alloc(sizeof(float) * B * (qdim + 2 * kvdim)));
+  DEC_CUDA(d->q.alloc(sizeof(float) * B * qdim));
+  DEC_CUDA(d->attn.alloc(sizeof(float) * B * qdim));
+  DEC_CUDA(d->proj.alloc(sizeof(float) * B * c.d_model));
+  DEC_CUDA(d->gate_up.alloc(sizeof(float) * (size_t)B * 2 * c.d_ff));
+  DEC_CUDA(d->down_out.alloc(sizeof(float) * B * c.d_model));
+  DEC_CUDA(d->logits.alloc(sizeof(float) * (size_t)B * c.vocab));
+  DEC_CUDA(d->q_d.alloc(q_tiled_bytes(m_alloc, c.d_model)));
+  DEC_CUDA(d->q_a.alloc(q_tiled_bytes(m_alloc, qdim)));
+  DEC_CUDA(d->q_f.alloc(q_tiled_bytes(m_alloc, c.d_ff)));
+  for (DevBuf* b : {&d->sc_d, &d->sc_a, &d->sc_f, &d->zp_d, &d->zp_a, &d->zp_f}) DEC_CUDA(b->alloc(sizeof(float) * m_alloc));
+  DEC_CUDA(d->zero_ws.alloc(zero_ws_total_bytes()));
+  DEC_CUDA(cudaMemsetAsync(d->zero_ws.p, 0, d->zero_ws.bytes, d->stream));
+  DEC_CUDA(d->sdpa_ws.alloc(sdpa_workspace_bytes(B, c.n_heads, c.head_dim, c.max_seq)));
+  DEC_CUDA(d->arg_val.alloc(sizeof(float) * B * kArgmaxParts));
+  DEC_CUDA(d->arg_idx.alloc(sizeof(int32_t) * B * kArgmaxParts));
+  DEC_CUDA(cudaMemsetAsync(d->positions.p, 0, sizeof(int32_t) * B, d->stream));
+  DEC_CUDA(cudaMallocHost(&d->h_tokens_pinned, sizeof(int32_t) * B));
+  DEC_CUDA(cudaMallocHost(&d->h_next_pinned, sizeof(int32_t) * B));
+  const size_t kv_elems = (size_t)B * c.max_seq * kvdim;
+  const size_t kv_bytes = kv_elems * (c.kv_dtype == B200_DTYPE_I8 ? 1 : 2);
+  for (int l = 0; l < c.n_layers; ++l) {
+    d->layers.emplace_back(new Layer());
+    Layer& L = *d->layers.back();
+    DEC_CUDA(L.k_cache.alloc(kv_bytes));
+    DEC_CUDA(L.v_cache.alloc(kv_bytes));
+    if (c.kv_dtype == B200_DTYPE_I8) {
+      DEC_CUDA(L.k_scale.alloc(sizeof(float) * (size_t)B * c.max_seq * c.n_kv_heads));
+      DEC_CUDA(L.v_scale.alloc(sizeof(float) * (size_t)B * c.max_seq * c.n_kv_heads));
+    }
+    DEC_CUDA(L.norm1.alloc(sizeof(float) * c.d_model));
+    DEC_CUDA(L.norm2.alloc(sizeof(float) * c.d_model));
+  }
+  DEC_CUDA(d->final_norm.alloc(sizeof(float) * c.d_model));
+  DEC_CUDA(cudaStreamSynchronize(d->stream));
+  *out = d.release();
+  return B200_OK;
+}
+
+void b200_decoder_destroy(b200_decoder* d) {
+  if (!d) return;
+  cudaStreamSynchronize(d->stream);
+  for (auto& g : d->graph)
+    if (g) cudaGraphExecDestroy(g);
+  if (d->h_tokens_pinned) cudaFreeHost(d->h_tokens_pinned);
+  if (d->h_next_pinned) cudaFreeHost(d->h_next_pinned);
+  if (d->own_stream) cudaStreamDestroy(d->stream);
+  delete d;
+}
+
+int b200_decoder_set_layer(b200_decoder* d, int layer, const b200_decoder_layer_weights* w) {
+  if (!d || !w || layer < 0 || layer >= d->cfg.n_layers) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_set_layer: bad argument");
+  const b200_decoder_config& c = d->cfg;
+  const int qdim = c.n_heads * c.head_dim, kvdim = c.n_kv_heads * c.head_dim;
+  Layer& L = *d->layers[layer];
+  int rc = build_projection(d, &L.qkv, c.d_model, {w->wq, w->wk, w->wv}, {w->sq, w->sk, w->sv}, {qdim, kvdim, kvdim});
+  if (rc) return rc;
+  rc = build_projection(d, &L.o, qdim, {w->wo}, {w->so}, {c.d_model});
+  if (rc) return rc;
+  rc = build_projection(d, &L.gate_up, c.d_model, {w->wgate, w->wup}, {w->sgate, w->sup}, {c.d_ff, c.d_ff});
+  if (rc) return rc;
+  rc = build_projection(d, &L.down, c.d_ff, {w->wdown}, {w->sdown}, {c.d_model});
+  if (rc) return rc;
+  DEC_CUDA(cudaMemcpyAsync(L.norm1.p, w->norm1, sizeof(float) * c.d_model, cudaMemcpyDeviceToDevice, d->stream));
+  DEC_CUDA(cudaMemcpyAsync(L.norm2.p, w->norm2, sizeof(float) * c.d_model, cudaMemcpyDeviceToDevice, d->stream));
+  DEC_CUDA(cudaStreamSynchronize(d->stream));
+  return B200_OK;
+}
+
+int b200_decoder_set_embedding(b200_decoder* d, const int8_t* table, const float* row_scales, const float* final_norm) {
+  if (!d || !table || !row_scales || !final_norm) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_set_embedding: null");
+  const b200_decoder_config& c = d->cfg;
+  DEC_CUDA(d->embed_table.alloc((size_t)c.vocab * c.d_model));
+  DEC_CUDA(d->embed_scales.alloc(sizeof(float) * c.vocab));
+  DEC_CUDA(cudaMemcpyAsync(d->embed_table.p, table, (size_t)c.vocab * c.d_model, cudaMemcpyDeviceToDevice, d->stream));
+  DEC_CUDA(cudaMemcpyAsync(d->embed_scales.p, row_scales, sizeof(float) * c.vocab, cudaMemcpyDeviceToDevice, d->stream));
+  DEC_CUDA(cudaMemcpyAsync(d->final_norm.p, final_norm, sizeof(float) * c.d_model, cudaMemcpyDeviceToDevice, d->stream));
+  return build_projection(d, &d->lm_head, c.d_model, {table}, {row_scales}, {c.vocab});
+}
+
+int b200_decoder_set_allreduce(b200_decoder* d, b200_allreduce_fn fn, void* user) {
+  if (!d) return dec_fail(B200_ERR_INVALID_ARGUMENT, "null decoder");
+  d->allreduce = fn;
+  d->allreduce_user = user;
+  return B200_OK;
+}
+
+int b200_decoder_reset(b200_decoder* d) {
+  if (!d) return dec_fail(B200_ERR_INVALID_ARGUMENT, "null decoder");
+  DEC_CUDA(cudaMemsetAsync(d->positions.p, 0, sizeof(int32_t) * d->cfg.max_batch, d->stream));
+  return B200_OK;
+}
+
+int b200_decoder_step(b200_decoder* d, const int32_t* h_tokens, int batch, int32_t* h_next_tokens, float* d_logits) {
+  if (!d || !h_tokens || batch <= 0 || batch > d->cfg.max_batch) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_step: bad argument");
+  if (d->lm_head.n == 0) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_step: weights not set");
+  memcpy(d->h_tokens_pinned, h_tokens, sizeof(int32_t) * batch);
+  DEC_CUDA(cudaMemcpyAsync(d->tokens.p, d->h_tokens_pinned, sizeof(int32_t) * batch, cudaMemcpyHostToDevice, d->stream));
+  if (d_logits) {
+    int rc = enqueue_step(d, batch, d_logits);  // caller-owned logits buffer: not the captured graph
+    if (rc) return rc;
+  } else {
+    int rc = ensure_graph(d, batch);
+    if (rc) return rc;
+    DEC_CUDA(cudaGraphLaunch(d->graph[batch], d->stream));
+  }
+  if (h_next_tokens) {
+    DEC_CUDA(cudaMemcpyAsync(d->h_next_pinned, d->next_tokens.p, sizeof(int32_t) * batch, cudaMemcpyDeviceToHost, d->stream));
+    DEC_CUDA(cudaStreamSynchronize(d->stream));
+    memcpy(h_next_tokens, d->h_next_pinned, sizeof(int32_t) * batch);
+    int status = 0;
+    DEC_CUDA(cudaMemcpy(&status, d->zero_ws.p, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status != 0) return dec_fail(B200_ERR_KERNEL_TIMEOUT, "b200_decoder_step: a device-side wait ran out");
+  }
+  return B200_OK;
+}
+
+int b200_decoder_run(b200_decoder* d, const int32_t* h_first_tokens, int batch, int steps, int32_t* h_next_tokens) {
+  if (!d || batch <= 0 || batch > d->cfg.max_batch || steps <= 0) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_run: bad argument");
+  int rc = ensure_graph(d, batch);
+  if (rc) return rc;
+  if (h_first_tokens) {
+    memcpy(d->h_tokens_pinned, h_first_tokens, sizeof(int32_t) * batch);
+    DEC_CUDA(cudaMemcpyAsync(d->tokens.p, d->h_tokens_pinned, sizeof(int32_t) * batch, cudaMemcpyHostToDevice, d->stream));
+  }
+  for (int i = 0; i < steps; ++i) {
+    if (i > 0 || !h_first_tokens)
+      DEC_CUDA(cudaMemcpyAsync(d->tokens.p, d->next_tokens.p, sizeof(int32_t) * batch, cudaMemcpyDeviceToDevice, d->stream));
+    DEC_CUDA(cudaGraphLaunch(d->graph[batch], d->stream));
+  }
+  if (h_next_tokens) {
+    DEC_CUDA(cudaMemcpyAsync(d->h_next_pinned, d->next_tokens.p, sizeof(int32_t) * batch, cudaMemcpyDeviceToHost, d->stream));
+    DEC_CUDA(cudaStreamSynchronize(d->stream));
+    memcpy(h_next_tokens, d->h_next_pinned, sizeof(int32_t) * batch);
+  }
+  return B200_OK;
+}
+
+int b200_decoder_launches_per_step(const b200_decoder* d) { return d ? d->launches : 0; }
+
+int b200_decoder_profile_step(b200_decoder* d, const int32_t* h_tokens, int batch, float* ms_by_class,
+                              int* launches_by_class) {
+  if (!d || !h_tokens || !ms_by_class || batch <= 0 || batch > d->cfg.max_batch)
+    return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_profile_step: bad argument");
+  memcpy(d->h_tokens_pinned, h_tokens, sizeof(int32_t) * batch);
+  DEC_CUDA(cudaMemcpyAsync(d->tokens.p, d->h_tokens_pinned, sizeof(int32_t) * batch, cudaMemcpyHostToDevice, d->stream));
+  d->profiling = true;
+  d->prof_events.clear();
+  d->prof_class.clear();
+  int rc = enqueue_step(d, batch, nullptr);
+  d->profiling = false;
+  cudaError_t e = cudaStreamSynchronize(d->stream);
+  for (int c = 0; c < 3; ++c) {
+    ms_by_class[c] = 0.0f;
+    if (launches_by_class) launches_by_class[c] = 0;
+  }
+  for (size_t i = 0; i < d->prof_class.size(); ++i) {
+    float ms = 0.0f;
+    if (e == cudaSuccess) cudaEventElapsedTime(&ms, d->prof_events[2 * i], d->prof_events[2 * i + 1]);
+    ms_by_class[d->prof_class[i]] += ms;
+    if (launches_by_class) launches_by_class[d->prof_class[i]] += 1;
+    cudaEventDestroy(d->prof_events[2 * i]);
+    cudaEventDestroy(d->prof_events[2 * i + 1]);
+  }
+  d->prof_events.clear();
+  d->prof_class.clear();
+  if (rc) return rc;
+  if (e != cudaSuccess) return dec_fail(B200_ERR_CUDA, "b200_decoder_profile_step", e);
+  return B200_OK;
+}
+
+const char* b200_decoder_last_error(void) { return g_dec_error; }
+
+}  // extern "C"

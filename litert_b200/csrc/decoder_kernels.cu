@@ -1,0 +1,284 @@
+// Glue kernels of the decode step of a Gemma-shaped decoder: everything between
+// the quantized projections and the attention kernel. Each one fuses an
+// elementwise stage with the per-row int8 quantization the next hybrid
+// FULLY_CONNECTED needs, and writes the quantized row directly in the tiled
+// layout the GEMM streams, so the only float activations that touch HBM are
+// the residual stream and the projection outputs.
+// The ops are the ones tensor/examples/gemma3/gemma3_graph.cc authors out of
+// TFLite builtins: RMS norm, rotary embedding (x*cos + rotate_half(x)*sin,
+// :150-176), GELU(tanh) * up (:118-146), residual add, hybrid embedding lookup
+// (tflite/kernels/embedding_lookup.cc), first-index argmax.
+#include "common.cuh"
+#include "decoder_kernels.h"
+#include "quant.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int kRowThreads = 256;
+
+// Quantizes the row held in shared memory `xs[0..k)` (asymmetric, per row) and
+// writes it tiled; thread 0 publishes scale and zero point.
+__device__ void quantize_smem_row(const float* xs, int k, int k_pad, int row, int m_alloc, float mn, float mx,
+                                  int8_t* q_tiled, float* scales, int32_t* zps, float* red) {
+  __shared__ float s_inv;
+  __shared__ int s_zp, s_zero;
+  mn = block_reduce(mn, [](float a, float b) { return fminf(a, b); }, mn, red);
+  mx = block_reduce(mx, [](float a, float b) { return fmaxf(a, b); }, mx, red);
+  if (threadIdx.x == 0) {
+    float sf, inv;
+    int zp, zero_row;
+    row_quant_params(mn, mx, true, &sf, &inv, &zp, &zero_row);
+    s_zero = zero_row;
+    s_inv = inv;
+    s_zp = zp;
+    scales[row] = sf;
+    zps[row] = zp;
+  }
+  __syncthreads();
+  const bool zero = s_zero != 0;
+  const float inv = s_inv, zpf = (float)s_zp;
+  for (int k4 = threadIdx.x * 4; k4 < k_pad; k4 += blockDim.x * 4) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+      if (k4 + b < k && !zero) word |= quantize_value(xs[k4 + b], inv, zpf, true) << (8 * b);
+    *reinterpret_cast<uint32_t*>(q_tiled + q_tiled_offset(row, k4, m_alloc)) = word;
+  }
+}
+
+// h[b,:] = int8 embedding row * its scale * embed_scale; also attn_len = positions + 1.
+__global__ void __launch_bounds__(kRowThreads) embed_kernel(const int32_t* __restrict__ tokens,
+                                                            const int8_t* __restrict__ table,
+                                                            const float* __restrict__ row_scales, int d,
+                                                            float embed_scale, float* __restrict__ h,
+                                                            const int32_t* __restrict__ positions,
+                                                            int32_t* __restrict__ attn_len) {
+  const int b = blockIdx.x;
+  const int tok = tokens[b];
+  const float s = row_scales[tok];
+  const int8_t* row = table + (size_t)tok * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x)
+    h[(size_t)b * d + i] = __fmul_rn(__fmul_rn((float)row[i], s), embed_scale);
+  if (threadIdx.x == 0) attn_len[b] = positions[b] + 1;
+}
+
+// h += delta (optional); x = h * rsqrt(mean(h^2) + eps) * gain; quantize x.
+__global__ void __launch_bounds__(kRowThreads) add_norm_quant_kernel(float* __restrict__ h,
+                                                                     const float* __restrict__ delta,
+                                                                     const float* __restrict__ gain, int d, int d_pad,
+                                                                     float eps, int m_alloc,
+                                                                     int8_t* __restrict__ q_tiled,
+                                                                     float* __restrict__ scales,
+                                                                     int32_t* __restrict__ zps) {
+  extern __shared__ float xs[];
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  float* hr = h + (size_t)b * d;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = hr[i];
+    if (delta) {
+      v = __fadd_rn(v, delta[(size_t)b * d + i]);
+      hr[i] = v;
+    }
+    xs[i] = v;
+    ss += v * v;
+  }
+  ss = block_reduce(ss, [](float a, float c) { return a + c; }, 0.0f, red);
+  const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = __fmul_rn(__fmul_rn(xs[i], inv), gain[i]);
+    xs[i] = v;
+    mn = fminf(mn, v);
+    mx = fmaxf(mx, v);
+  }
+  quantize_smem_row(xs, d, d_pad, b, m_alloc, mn, mx, q_tiled, scales, zps, red);
+}
+
+__device__ __forceinline__ float gelu_tanh(float v) {
+  const float k0 = 0.7978845608028654f;
+  return 0.5f * v * (1.0f + tanhf(k0 * (v + 0.044715f * v * v * v)));
+}
+
+// f = gelu_tanh(gate) * up from the fused projection output [b, 2 f]; quantize f.
+__global__ void __launch_bounds__(1024) geglu_quant_kernel(const float* __restrict__ gate_up, int f, int f_pad,
+                                                           int m_alloc, int8_t* __restrict__ q_tiled,
+                                                           float* __restrict__ scales, int32_t* __restrict__ zps) {
+  extern __shared__ float xs[];
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  const float* g = gate_up + (size_t)b * 2 * f;
+  const float* u = g + f;
+  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+  for (int i = threadIdx.x; i < f; i += blockDim.x) {
+    const float v = __fmul_rn(gelu_tanh(g[i]), u[i]);
+    xs[i] = v;
+    mn = fminf(mn, v);
+    mx = fmaxf(mx, v);
+  }
+  quantize_smem_row(xs, f, f_pad, b, m_alloc, mn, mx, q_tiled, scales, zps, red);
+}
+
+// Rotary embedding of q and k from the fused qkv projection output, and the
+// cache append. grid (b, heads + kv_heads + kv_heads), head_dim / 2 threads.
+template <bool KV_I8>
+__global__ void rope_cache_kernel(const float* __restrict__ qkv, int heads, int kv_heads, int head_dim,
+                                  float rope_base, const int32_t* __restrict__ positions, int max_seq,
+                                  float* __restrict__ q_out, void* __restrict__ k_cache, void* __restrict__ v_cache,
+                                  float* __restrict__ k_scale, float* __restrict__ v_scale) {
+  __shared__ float red[32];
+  const int b = blockIdx.x, slot = blockIdx.y, i = threadIdx.x, half = head_dim / 2;
+  const int pos = positions[b];
+  const float* src = qkv + ((size_t)b * (heads + 2 * kv_heads) + slot) * head_dim;
+  float x1 = src[i], x2 = src[i + half];
+  const bool is_v = slot >= heads + kv_heads;
+  if (!is_v) {
+    const float freq = powf(rope_base, -2.0f * (float)i / (float)head_dim);
+    float sn, cs;
+    sincosf((float)pos * freq, &sn, &cs);
+    const float r1 = x1 * cs - x2 * sn, r2 = x2 * cs + x1 * sn;
+    x1 = r1;
+    x2 = r2;
+  }
+  if (slot < heads) {
+    float* dst = q_out + ((size_t)b * heads + slot) * head_dim;
+    dst[i] = x1;
+    dst[i + half] = x2;
+    return;
+  }
+  const int kvh = is_v ? slot - heads - kv_heads : slot - heads;
+  if (pos >= max_seq) return;  // cache full: the step is ignored for this sequence
+  const size_t tok = ((size_t)b * max_seq + pos) * kv_heads + kvh;
+  if constexpr (KV_I8) {
+    // symmetric per token and kv head: scale = max|row| / 127
+    float amax = fmaxf(fabsf(x1), fabsf(x2));
+    amax = block_reduce(amax, [](float a, float c) { return fmaxf(a, c); }, 0.0f, red);
+    const float sc = amax > 0.0f ? amax / 127.0f : 1.0f;
+    int8_t* dst = static_cast<int8_t*>(is_v ? v_cache : k_cache) + tok * head_dim;
+    dst[i] = (int8_t)max(-127, min(127, __float2int_rn(x1 / sc)));
+    dst[i + half] = (int8_t)max(-127, min(127, __float2int_rn(x2 / sc)));
+    if (i == 0) (is_v ? v_scale : k_scale)[tok] = sc;
+  } else {
+    __half* dst = static_cast<__half*>(is_v ? v_cache : k_cache) + tok * head_dim;
+    dst[i] = __float2half_rn(x1);
+    dst[i + half] = __float2half_rn(x2);
+  }
+}
+
+struct BestPair {
+  float v;
+  int i;
+};
+__device__ __forceinline__ BestPair better(BestPair a, BestPair b) {
+  // larger value wins; ties go to the lower index (first-index argmax)
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+
+// grid (parts, b): each CTA scans a slice of the row.
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ logits, int n, int parts,
+                                                             float* __restrict__ part_val,
+                                                             int32_t* __restrict__ part_idx) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int b = blockIdx.y, part = blockIdx.x;
+  const int per = (n + parts - 1) / parts;
+  const int lo = part * per, hi = min(n, lo + per);
+  const float* row = logits + (size_t)b * n;
+  BestPair best{lo < n ? row[lo] : -3.402823466e+38f, lo < n ? lo : 0x7fffffff};
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) best = better(best, BestPair{row[i], i});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    BestPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sv[threadIdx.x >> 5] = best.v;
+    si[threadIdx.x >> 5] = best.i;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) best = better(best, BestPair{sv[w], si[w]});
+    part_val[(size_t)b * parts + part] = best.v;
+    part_idx[(size_t)b * parts + part] = best.i;
+  }
+}
+
+// grid b, 32 threads: final reduction; also advances the sequence position.
+__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int32_t* __restrict__ part_idx,
+                                    int parts, int32_t* __restrict__ next_tokens, int32_t* __restrict__ positions,
+                                    int max_seq) {
+  const int b = blockIdx.x;
+  BestPair best{part_val[(size_t)b * parts], part_idx[(size_t)b * parts]};
+  for (int i = threadIdx.x; i < parts; i += 32)
+    best = better(best, BestPair{part_val[(size_t)b * parts + i], part_idx[(size_t)b * parts + i]});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    BestPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (threadIdx.x == 0) {
+    next_tokens[b] = best.i;
+    if (positions[b] < max_seq) positions[b] += 1;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_embed(const int32_t* tokens, const int8_t* table, const float* row_scales, int batch, int d,
+                         float embed_scale, float* h, const int32_t* positions, int32_t* attn_len, cudaStream_t s) {
+  embed_kernel<<<batch, kRowThreads, 0, s>>>(tokens, table, row_scales, d, embed_scale, h, positions, attn_len);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_add_norm_quant(float* h, const float* delta, const float* gain, int batch, int d, float eps,
+                                  int m_alloc, int8_t* q_tiled, float* scales, int32_t* zps, cudaStream_t s) {
+  const int d_pad = (d + 127) / 128 * 128;
+  add_norm_quant_kernel<<<batch, kRowThreads, sizeof(float) * d, s>>>(h, delta, gain, d, d_pad, eps, m_alloc, q_tiled,
+                                                                       scales, zps);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_alloc, int8_t* q_tiled, float* scales,
+                               int32_t* zps, cudaStream_t s) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  const size_t smem = sizeof(float) * f;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(geglu_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  const int f_pad = (f + 127) / 128 * 128;
+  geglu_quant_kernel<<<batch, 1024, smem, s>>>(gate_up, f, f_pad, m_alloc, q_tiled, scales, zps);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, float rope_base,
+                              const int32_t* positions, int max_seq, float* q_out, void* k_cache, void* v_cache,
+                              float* k_scale, float* v_scale, int kv_int8, cudaStream_t s) {
+  dim3 grid(batch, heads + 2 * kv_heads);
+  if (kv_int8) {
+    rope_cache_kernel<true><<<grid, head_dim / 2, 0, s>>>(qkv, heads, kv_heads, head_dim, rope_base, positions, max_seq,
+                                                          q_out, k_cache, v_cache, k_scale, v_scale);
+  } else {
+    rope_cache_kernel<false><<<grid, head_dim / 2, 0, s>>>(qkv, heads, kv_heads, head_dim, rope_base, positions,
+                                                           max_seq, q_out, k_cache, v_cache, k_scale, v_scale);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_argmax(const float* logits, int batch, int n, float* part_val, int32_t* part_idx,
+                          int32_t* next_tokens, int32_t* positions, int max_seq, cudaStream_t s) {
+  argmax_partial_kernel<<<dim3(kArgmaxParts, batch), 256, 0, s>>>(logits, n, kArgmaxParts, part_val, part_idx);
+  argmax_final_kernel<<<batch, 32, 0, s>>>(part_val, part_idx, kArgmaxParts, next_tokens, positions, max_seq);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

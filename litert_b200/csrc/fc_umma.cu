@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
             // two 16-byte K chunks per MMA: 128 B apart; 8-row groups 1 KiB apart
             const uint64_t a_desc = umma_smem_desc(a_addr + ks * 256, 128, 1024);
             const uint64_t b_desc = umma_smem_desc(b_addr + ks * 256, 128, 1024);
-            umma_s8(d_tmem, a_desc, b_desc, idesc, (first && ks == 0) ? 0u : 1u);
+            if (!(p.debug_flags & 1)) umma_s8(d_tmem, a_desc, b_desc, idesc, (first && ks == 0) ? 0u : 1u);
           }
           first = false;
           umma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
@@ -219,7 +219,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
       }
 
       const bool partial = seg_tiles != p.k_tiles;
-      if (!partial) {
+      if (p.debug_flags & 2) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[ab]);
+      } else if (!partial) {
 #pragma unroll 1
         for (int c = 0; c < NB / 16; ++c) {
           int r[16];
@@ -310,7 +314,9 @@ cudaError_t launch_umma_one(const FcParams& p, int m_base, cudaStream_t s) {
 }
 
 template <int EPI>
-cudaError_t launch_umma_nb(const FcParams& p, int m_base, int nb, cudaStream_t s) {
+cudaError_t launch_umma_nb(const FcParams& p_in, int m_base, int nb, cudaStream_t s) {
+  FcParams p = p_in;
+  if (const char* e = getenv("B200_FC_DEBUG")) p.debug_flags = atoi(e);
   switch (nb) {
     case 16: return launch_umma_one<16, EPI>(p, m_base, s);
     case 32: return launch_umma_one<32, EPI>(p, m_base, s);

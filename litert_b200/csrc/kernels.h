@@ -68,6 +68,7 @@ struct FcParams {
   int32_t* ws_count;
   int* status;
   int max_ctas;              // 0 = one per SM
+  int debug_flags;           // measurement only: 1 = skip the MMAs, 2 = skip the epilogue
 };
 
 // Streamed-weights GEMM on the packed int8 tiles (any m; m > 64 runs in
@@ -83,6 +84,11 @@ cudaError_t launch_fc_w4(const FcParams& p, cudaStream_t s);
 constexpr int kZeroWsSlots = 256;            // >= CTAs per launch
 constexpr int kZeroWsSlotInts = 128 * 256;   // accumulators per slot (128 rows x up to 256 activation rows)
 int device_sm_count();
+
+// Layout of the zero workspace: [status word + padding: 256 B][slot counters][slot accumulators].
+inline size_t zero_ws_counter_off() { return 256; }
+inline size_t zero_ws_acc_off() { return 256 + ((sizeof(int32_t) * kZeroWsSlots + 255) / 256) * 256; }
+inline size_t zero_ws_total_bytes() { return zero_ws_acc_off() + sizeof(int32_t) * (size_t)kZeroWsSlots * kZeroWsSlotInts; }
 
 struct SdpaParams {
   const void* q;        // [b, t(=1), n, h] f16 or f32

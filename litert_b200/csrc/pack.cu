@@ -2,6 +2,7 @@
 // activation preparation kernels: row quantization and int8 re-tiling.
 #include "common.cuh"
 #include "kernels.h"
+#include "quant.cuh"
 
 namespace b200 {
 
@@ -129,28 +130,6 @@ __global__ void w4_kfsum_kernel(const uint8_t* __restrict__ w4, const __half* __
 }
 
 // ---- activations ------------------------------------------------------------
-// Tiled activation layout shared by all MMA kernels: [k tile][row group of 8]
-// [16-byte chunk (8)][row (8)][16 bytes]; m_alloc rows are allocated.
-__device__ __forceinline__ size_t q_tiled_offset(int m, int kk, int m_alloc) {
-  const int kt = kk / kTileK8, c = (kk % kTileK8) / 16, b = kk % 16;
-  return (((size_t)kt * (m_alloc / 8) + (m / 8)) * kChunks8 + c) * 128 + (m % 8) * 16 + b;
-}
-
-template <typename T, typename Op>
-__device__ __forceinline__ T block_reduce(T v, Op op, T identity, T* scratch) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
-  if (lane == 0) scratch[warp] = v;
-  __syncthreads();
-  const int nw = (blockDim.x + 31) >> 5;
-  v = lane < nw ? scratch[lane] : identity;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
-  __syncthreads();
-  return v;
-}
-
 // Per-row quantization of float activations to int8, one CTA per row.
 // Asymmetric: tflite/kernels/internal/reference/portable_tensor_utils.cc:74-119;
 // symmetric: :41-71. The scale and zero point are derived in double exactly as
@@ -190,65 +169,20 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restr
   mn = block_reduce(mn, [](float a, float b) { return fminf(a, b); }, mn, red);
   mx = block_reduce(mx, [](float a, float b) { return fmaxf(a, b); }, mx, red);
   if (threadIdx.x == 0) {
-    if (asymmetric) {
-      const double rmin = (double)fminf(0.0f, mn);
-      const double rmax = (double)fmaxf(0.0f, mx);
-      if (rmin == rmax) {
-        s_zero = 1;
-        scales[row] = 1.0f;
-        zero_points[row] = 0;
-      } else {
-        const double qmin = -128.0, qmax = 127.0;
-        const double scale = (rmax - rmin) / (qmax - qmin);
-        const double zp_from_min = qmin - rmin / scale;
-        const double zp_from_max = qmax - rmax / scale;
-        const double err_min = fabs(qmin) + fabs(rmin / scale);
-        const double err_max = fabs(qmax) + fabs(rmax / scale);
-        const double zp_d = err_min < err_max ? zp_from_min : zp_from_max;
-        int zp;
-        if (zp_d <= qmin) {
-          zp = -128;
-        } else if (zp_d >= qmax) {
-          zp = 127;
-        } else {
-          zp = (int)(int8_t)round(zp_d);
-        }
-        const float sf = (float)scale;
-        s_zero = 0;
-        s_inv = __fdiv_rn(1.0f, sf);
-        s_zp = zp;
-        scales[row] = sf;
-        zero_points[row] = zp;
-      }
-    } else {
-      const float range = fmaxf(fabsf(mn), fabsf(mx));
-      if (range == 0.0f) {
-        s_zero = 1;
-        scales[row] = 1.0f;
-      } else {
-        s_zero = 0;
-        s_inv = __fdiv_rn(127.0f, range);
-        scales[row] = __fdiv_rn(range, 127.0f);
-      }
-      s_zp = 0;
-      if (zero_points) zero_points[row] = 0;
-    }
+    float sf, inv;
+    int zp, zero_row;
+    row_quant_params(mn, mx, asymmetric != 0, &sf, &inv, &zp, &zero_row);
+    s_zero = zero_row;
+    s_inv = inv;
+    s_zp = zp;
+    scales[row] = sf;
+    if (zero_points) zero_points[row] = zp;
   }
   __syncthreads();
   const bool zero = s_zero != 0;
   const float inv = s_inv;
   const float zpf = (float)s_zp;
-  const int lo = asymmetric ? -128 : -127;
-  // round half away from zero (std::round): the fraction t - trunc(t) is exact
-  auto quant = [&](float v) -> uint32_t {
-    if (zero) return 0u;
-    const float t = asymmetric ? __fadd_rn(zpf, __fmul_rn(v, inv)) : __fmul_rn(v, inv);
-    float r = truncf(t);
-    if (fabsf(t - r) >= 0.5f) r += copysignf(1.0f, t);
-    int qv = (int)fmaxf(-129.0f, fminf(128.0f, r));
-    qv = max(lo, min(127, qv));
-    return (uint32_t)(uint8_t)(int8_t)qv;
-  };
+  auto quant = [&](float v) -> uint32_t { return zero ? 0u : quantize_value(v, inv, zpf, asymmetric != 0); };
   const bool vec = ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
   // four consecutive elements per thread and step: one float4 in, one 32-bit word out
   for (int k4 = threadIdx.x * 4; k4 < k_pad; k4 += blockDim.x * 4) {

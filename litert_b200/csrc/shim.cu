@@ -28,13 +28,9 @@ int cuda_fail(cudaError_t e, const char* what) {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Zero workspace: [status + padding: 256 B][counters: slots ints][accumulators]
-constexpr size_t kStatusBytes = 256;
-inline size_t zero_ws_counter_off() { return kStatusBytes; }
-inline size_t zero_ws_acc_off() { return kStatusBytes + align_up(sizeof(int32_t) * b200::kZeroWsSlots, 256); }
-inline size_t zero_ws_bytes() {
-  return zero_ws_acc_off() + sizeof(int32_t) * (size_t)b200::kZeroWsSlots * b200::kZeroWsSlotInts;
-}
+inline size_t zero_ws_counter_off() { return b200::zero_ws_counter_off(); }
+inline size_t zero_ws_acc_off() { return b200::zero_ws_acc_off(); }
+inline size_t zero_ws_bytes() { return b200::zero_ws_total_bytes(); }
 
 struct Scratch {
   float* scales;

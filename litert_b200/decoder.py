@@ -1,0 +1,127 @@
+"""Python handle on the resident decoder (b200_decoder_* in include/litert_b200.h) and the seeded
+synthetic Gemma-shaped weights the decode benchmark uses (random init, as the configuration says;
+no checkpoint is involved)."""
+import ctypes
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import B200Error
+
+GEMMA_2B = dict(n_layers=18, d_model=2048, n_heads=8, n_kv_heads=1, head_dim=256, d_ff=16384, vocab=256000)
+TINY = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=1, head_dim=64, d_ff=512, vocab=1000)
+
+
+def _check(rc):
+    if rc != 0:
+        raise B200Error(f"decoder error {rc}: {_lib.load().b200_decoder_last_error().decode()}")
+
+
+def make_weights(cfg, seed=1005, device="cuda"):
+    """int8 per-channel weights ~ clip(round(N(0,40)), +-127) with scales ~ U[1e-3,1e-2]; RMS-norm
+    gains ~ N(1, 0.02). Generated on `device` with a seeded torch generator, layer by layer."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+
+    def w(n, k):
+        out = torch.empty((n, k), dtype=torch.int8, device=device)
+        step = max(1, (1 << 26) // k)
+        for r in range(0, n, step):
+            rows = min(step, n - r)
+            out[r:r + rows] = torch.randn((rows, k), generator=g, device=device).mul_(40).round_().clamp_(-127, 127)
+        return out
+
+    def s(n):
+        return torch.rand(n, generator=g, device=device) * (1e-2 - 1e-3) + 1e-3
+
+    def gain(n):
+        return torch.randn(n, generator=g, device=device) * 0.02 + 1.0
+
+    d, qd, kd, f = cfg["d_model"], cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"], cfg["d_ff"]
+    layers = []
+    for _ in range(cfg["n_layers"]):
+        layers.append(dict(wq=w(qd, d), wk=w(kd, d), wv=w(kd, d), wo=w(d, qd), wgate=w(f, d), wup=w(f, d),
+                           wdown=w(d, f), sq=s(qd), sk=s(kd), sv=s(kd), so=s(d), sgate=s(f), sup=s(f), sdown=s(d),
+                           norm1=gain(d), norm2=gain(d)))
+    return dict(layers=layers, embed=w(cfg["vocab"], d), embed_scales=s(cfg["vocab"]), final_norm=gain(d))
+
+
+class Decoder:
+    def __init__(self, cfg, max_seq, max_batch, weights=None, kv_dtype="f16", rms_eps=1e-6, rope_base=10000.0,
+                 seed=1005, device="cuda", keep_weights=False):
+        self.lib = _lib.load()
+        self.cfg = dict(cfg)
+        self.device = torch.device(device)
+        c = _lib.DecoderConfig(
+            n_layers=cfg["n_layers"], d_model=cfg["d_model"], n_heads=cfg["n_heads"], n_kv_heads=cfg["n_kv_heads"],
+            head_dim=cfg["head_dim"], d_ff=cfg["d_ff"], vocab=cfg["vocab"], max_seq=max_seq, max_batch=max_batch,
+            rms_eps=rms_eps, rope_base=rope_base, embed_scale=math.sqrt(cfg["d_model"]),
+            kv_dtype=1 if kv_dtype == "i8" else 0, tp_size=1, tp_rank=0)
+        self.config_struct = c
+        self.rms_eps, self.rope_base, self.max_seq, self.max_batch = rms_eps, rope_base, max_seq, max_batch
+        self.handle = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            self.stream = torch.cuda.Stream()
+            _check(self.lib.b200_decoder_create(ctypes.byref(c), ctypes.c_void_p(self.stream.cuda_stream),
+                                                ctypes.byref(self.handle)))
+            weights = weights or make_weights(cfg, seed, device)
+            for i, lw in enumerate(weights["layers"]):
+                st = _lib.DecoderLayerWeights(**{k: lw[k].data_ptr() for k in lw})
+                _check(self.lib.b200_decoder_set_layer(self.handle, i, ctypes.byref(st)))
+            _check(self.lib.b200_decoder_set_embedding(self.handle, weights["embed"].data_ptr(),
+                                                       weights["embed_scales"].data_ptr(),
+                                                       weights["final_norm"].data_ptr()))
+            torch.cuda.synchronize()
+        self.weights = weights if keep_weights else None
+
+    def reset(self):
+        _check(self.lib.b200_decoder_reset(self.handle))
+
+    def step(self, tokens, want_logits=False):
+        """tokens: host int32 array [batch] -> (next tokens [batch], logits or None)."""
+        tok = np.ascontiguousarray(tokens, np.int32)
+        nxt = np.empty_like(tok)
+        logits = None
+        with torch.cuda.device(self.device):
+            if want_logits:
+                logits = torch.empty((tok.size, self.cfg["vocab"]), dtype=torch.float32, device=self.device)
+            _check(self.lib.b200_decoder_step(self.handle, tok.ctypes.data_as(ctypes.c_void_p), tok.size,
+                                              nxt.ctypes.data_as(ctypes.c_void_p),
+                                              None if logits is None else ctypes.c_void_p(logits.data_ptr())))
+        return nxt, logits
+
+    def run(self, first_tokens, steps, fetch=True):
+        tok = None if first_tokens is None else np.ascontiguousarray(first_tokens, np.int32)
+        batch = self._batch if tok is None else tok.size
+        self._batch = batch
+        nxt = np.empty(batch, np.int32) if fetch else None
+        with torch.cuda.device(self.device):
+            _check(self.lib.b200_decoder_run(self.handle, None if tok is None else tok.ctypes.data_as(ctypes.c_void_p),
+                                             batch, steps, None if nxt is None else nxt.ctypes.data_as(ctypes.c_void_p)))
+        return nxt
+
+    def profile_step(self, tokens):
+        """One eager step with per-launch CUDA events: {'gemv','attention','glue'} -> (ms, launches)."""
+        tok = np.ascontiguousarray(tokens, np.int32)
+        ms = (ctypes.c_float * 3)()
+        n = (ctypes.c_int * 3)()
+        with torch.cuda.device(self.device):
+            _check(self.lib.b200_decoder_profile_step(self.handle, tok.ctypes.data_as(ctypes.c_void_p), tok.size, ms, n))
+        return {k: (ms[i], n[i]) for i, k in enumerate(("gemv", "attention", "glue"))}
+
+    @property
+    def launches_per_step(self):
+        return self.lib.b200_decoder_launches_per_step(self.handle)
+
+    def weight_bytes_per_step(self):
+        c = self.cfg
+        qd, kd = c["n_heads"] * c["head_dim"], c["n_kv_heads"] * c["head_dim"]
+        per_layer = c["d_model"] * (qd + 2 * kd) + qd * c["d_model"] + 3 * c["d_model"] * c["d_ff"]
+        return c["n_layers"] * per_layer + c["vocab"] * c["d_model"]
+
+    def close(self):
+        if self.handle:
+            self.lib.b200_decoder_destroy(self.handle)
+            self.handle = None

@@ -272,3 +272,58 @@ def sdpa_f32(q, k, v, mask=None, scale=None, logit_cap=0.0):
     lib().orc_sdpa_f32(_i(b), _i(t), _i(n), _i(nkv), _i(h), _i(s), _p(q), _p(k), _p(v), _p(mask),
                        _f(scale), _f(logit_cap), _p(out))
     return out
+
+
+# ---- Gemma-shaped decoder (oracle/decoder_ref.c) ------------------------------------------
+class _DecCfg(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in ("n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim", "d_ff",
+                                            "vocab", "max_seq")] + \
+               [(n, ctypes.c_float) for n in ("rms_eps", "rope_base", "embed_scale")]
+
+
+class _DecLayer(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown", "sq", "sk", "sv", "so",
+                                               "sgate", "sup", "sdown", "norm1", "norm2")]
+
+
+class DecoderRef:
+    """CPU decode steps over numpy weights (dict of layers / embed / embed_scales / final_norm with
+    the key names of _DecLayer). fast=True uses the vectorised multi-threaded kernels."""
+
+    def __init__(self, cfg, weights, batch, max_seq, rms_eps=1e-6, rope_base=10000.0, fast=False):
+        use_fast = bool(fast)
+        self.lib = fast_lib = globals()["fast"]()
+        self.cfg = cfg
+        self.batch = batch
+        c = _DecCfg(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"],
+                    cfg["vocab"], max_seq, rms_eps, rope_base, float(np.sqrt(np.float32(cfg["d_model"]))))
+        fast_lib.orc_decoder_create.restype = ctypes.c_void_p
+        self.h = ctypes.c_void_p(fast_lib.orc_decoder_create(ctypes.byref(c), batch, 1 if use_fast else 0))
+        self._keep = []
+        for i, lw in enumerate(weights["layers"]):
+            st = _DecLayer()
+            for k in lw:
+                arr = np.ascontiguousarray(lw[k], np.int8 if k.startswith("w") else np.float32)
+                self._keep.append(arr)
+                setattr(st, k, arr.ctypes.data)
+            fast_lib.orc_decoder_set_layer(self.h, i, ctypes.byref(st))
+        e = np.ascontiguousarray(weights["embed"], np.int8)
+        es = np.ascontiguousarray(weights["embed_scales"], np.float32)
+        fn = np.ascontiguousarray(weights["final_norm"], np.float32)
+        self._keep += [e, es, fn]
+        fast_lib.orc_decoder_set_embedding(self.h, _p(e), _p(es), _p(fn))
+
+    def reset(self):
+        self.lib.orc_decoder_reset(self.h)
+
+    def step(self, tokens, want_logits=True):
+        tok = np.ascontiguousarray(tokens, np.int32)
+        logits = np.empty((self.batch, self.cfg["vocab"]), np.float32) if want_logits else None
+        nxt = np.empty(self.batch, np.int32)
+        self.lib.orc_decoder_step(self.h, _p(tok), _p(logits), _p(nxt))
+        return nxt, logits
+
+    def close(self):
+        if self.h:
+            self.lib.orc_decoder_destroy(self.h)
+            self.h = None

@@ -1,0 +1,179 @@
+/*
+ * CPU restatement of one decode step of a Gemma-shaped decoder-only graph whose
+ * projections are dynamic-range (hybrid) int8 FULLY_CONNECTED ops. TEST
+ * INFRASTRUCTURE ONLY (parity arbiter and timed CPU baseline of the decode
+ * benchmark).
+ *
+ * The graph is the one tensor/examples/gemma3/gemma3_graph.cc authors out of
+ * TFLite ops (RMS norm, q/k/v projections, rotary embedding as
+ * x*cos + rotate_half(x)*sin :150-176, attention, output projection, residual
+ * adds, GeGLU feed-forward :118-146, final norm, tied LM head), with the
+ * Gemma-1 layout the benchmark names: one KV head (MQA), no q/k norms, no
+ * post-norms. Every projection goes through the hybrid kernel restated in
+ * oracle.c (orc_fc_hybrid, asymmetric inputs, per-channel scales); the
+ * embedding is the hybrid EMBEDDING_LOOKUP (tflite/kernels/embedding_lookup.cc:
+ * int8 row times its per-row scale); attention is orc_sdpa_f32 over the cached
+ * prefix. `fast` != 0 swaps in the vectorised multi-threaded twins of
+ * oracle_fast.c (same formulas) for timing.
+ */
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "oracle.h"
+#include "oracle_fast.h"
+
+typedef struct {
+  int n_layers, d_model, n_heads, n_kv_heads, head_dim, d_ff, vocab, max_seq;
+  float rms_eps, rope_base, embed_scale;
+} orc_decoder_config;
+
+typedef struct {
+  const int8_t *wq, *wk, *wv, *wo, *wgate, *wup, *wdown;
+  const float *sq, *sk, *sv, *so, *sgate, *sup, *sdown; /* per-output-channel scales */
+  const float *norm1, *norm2;                            /* RMS norm gains [d_model] */
+} orc_decoder_layer;
+
+typedef struct {
+  orc_decoder_config cfg;
+  orc_decoder_layer* layers;
+  const int8_t* embed; /* [vocab, d_model] */
+  const float* embed_scales; /* [vocab] */
+  const float* final_norm;
+  float* k_cache; /* [layers][batch][max_seq][kvh*hd] */
+  float* v_cache;
+  int* lengths; /* [batch] */
+  int batch;
+  int fast;
+} orc_decoder;
+
+static void fc(const orc_decoder* d, int m, int n, int k, const float* x, const int8_t* w, const float* s, float* y) {
+  if (d->fast) {
+    orcf_fc_hybrid(m, n, k, x, w, s, 1, NULL, 1, ORC_ACT_NONE, NULL, y);
+  } else {
+    orc_fc_hybrid(m, n, k, x, w, s, 1, NULL, 1, ORC_ACT_NONE, y);
+  }
+}
+
+static void rms_norm(const float* x, const float* gain, int n, float eps, float* y) {
+  float ss = 0.0f;
+  for (int i = 0; i < n; ++i) ss += x[i] * x[i];
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  for (int i = 0; i < n; ++i) y[i] = x[i] * inv * gain[i];
+}
+
+/* x*cos + rotate_half(x)*sin with rotate_half(x) = cat(-x2, x1); angle of pair i = pos * base^(-2i/hd) */
+static void rope(float* x, int head_dim, int pos, float base) {
+  const int half = head_dim / 2;
+  for (int i = 0; i < half; ++i) {
+    const float freq = powf(base, -2.0f * (float)i / (float)head_dim);
+    const float ang = (float)pos * freq;
+    const float c = cosf(ang), s = sinf(ang);
+    const float x1 = x[i], x2 = x[i + half];
+    x[i] = x1 * c - x2 * s;
+    x[i + half] = x2 * c + x1 * s;
+  }
+}
+
+static float gelu_tanh(float v) {
+  const float k0 = 0.7978845608028654f; /* sqrt(2/pi) */
+  return 0.5f * v * (1.0f + tanhf(k0 * (v + 0.044715f * v * v * v)));
+}
+
+orc_decoder* orc_decoder_create(const orc_decoder_config* cfg, int batch, int fast) {
+  orc_decoder* d = (orc_decoder*)calloc(1, sizeof(orc_decoder));
+  d->cfg = *cfg;
+  d->batch = batch;
+  d->fast = fast;
+  d->layers = (orc_decoder_layer*)calloc((size_t)cfg->n_layers, sizeof(orc_decoder_layer));
+  const size_t kv = (size_t)cfg->n_layers * batch * cfg->max_seq * cfg->n_kv_heads * cfg->head_dim;
+  d->k_cache = (float*)calloc(kv, sizeof(float));
+  d->v_cache = (float*)calloc(kv, sizeof(float));
+  d->lengths = (int*)calloc((size_t)batch, sizeof(int));
+  return d;
+}
+
+void orc_decoder_destroy(orc_decoder* d) {
+  free(d->layers);
+  free(d->k_cache);
+  free(d->v_cache);
+  free(d->lengths);
+  free(d);
+}
+
+void orc_decoder_set_layer(orc_decoder* d, int layer, const orc_decoder_layer* w) { d->layers[layer] = *w; }
+void orc_decoder_set_embedding(orc_decoder* d, const int8_t* w, const float* scales, const float* final_norm) {
+  d->embed = w;
+  d->embed_scales = scales;
+  d->final_norm = final_norm;
+}
+void orc_decoder_reset(orc_decoder* d) { memset(d->lengths, 0, sizeof(int) * (size_t)d->batch); }
+
+/* One token per sequence: tokens [batch] -> logits [batch, vocab] (may be NULL) and the greedy next
+ * token (first index of the maximum). Appends to the caches. */
+void orc_decoder_step(orc_decoder* d, const int32_t* tokens, float* logits_out, int32_t* next_tokens) {
+  const orc_decoder_config* c = &d->cfg;
+  const int B = d->batch, D = c->d_model, H = c->n_heads, KVH = c->n_kv_heads, HD = c->head_dim, F = c->d_ff;
+  float* h = (float*)malloc(sizeof(float) * (size_t)B * D);
+  float* x = (float*)malloc(sizeof(float) * (size_t)B * D);
+  float* q = (float*)malloc(sizeof(float) * (size_t)B * H * HD);
+  float* kk = (float*)malloc(sizeof(float) * (size_t)B * KVH * HD);
+  float* vv = (float*)malloc(sizeof(float) * (size_t)B * KVH * HD);
+  float* att = (float*)malloc(sizeof(float) * (size_t)B * H * HD);
+  float* o = (float*)malloc(sizeof(float) * (size_t)B * D);
+  float* gate = (float*)malloc(sizeof(float) * (size_t)B * F);
+  float* up = (float*)malloc(sizeof(float) * (size_t)B * F);
+  float* logits = logits_out ? logits_out : (float*)malloc(sizeof(float) * (size_t)B * c->vocab);
+
+  for (int b = 0; b < B; ++b) {
+    const int8_t* row = d->embed + (size_t)tokens[b] * D;
+    const float s = d->embed_scales[tokens[b]];
+    for (int i = 0; i < D; ++i) h[(size_t)b * D + i] = (float)row[i] * s * c->embed_scale;
+  }
+  const size_t per_seq = (size_t)c->max_seq * KVH * HD;
+  for (int l = 0; l < c->n_layers; ++l) {
+    const orc_decoder_layer* w = &d->layers[l];
+    for (int b = 0; b < B; ++b) rms_norm(h + (size_t)b * D, w->norm1, D, c->rms_eps, x + (size_t)b * D);
+    fc(d, B, H * HD, D, x, w->wq, w->sq, q);
+    fc(d, B, KVH * HD, D, x, w->wk, w->sk, kk);
+    fc(d, B, KVH * HD, D, x, w->wv, w->sv, vv);
+    float* kc = d->k_cache + (size_t)l * B * per_seq;
+    float* vc = d->v_cache + (size_t)l * B * per_seq;
+    for (int b = 0; b < B; ++b) {
+      const int pos = d->lengths[b];
+      for (int hh = 0; hh < H; ++hh) rope(q + ((size_t)b * H + hh) * HD, HD, pos, c->rope_base);
+      for (int hh = 0; hh < KVH; ++hh) rope(kk + ((size_t)b * KVH + hh) * HD, HD, pos, c->rope_base);
+      memcpy(kc + (size_t)b * per_seq + (size_t)pos * KVH * HD, kk + (size_t)b * KVH * HD, sizeof(float) * KVH * HD);
+      memcpy(vc + (size_t)b * per_seq + (size_t)pos * KVH * HD, vv + (size_t)b * KVH * HD, sizeof(float) * KVH * HD);
+      const int len = pos + 1;
+      const float scale = 1.0f / sqrtf((float)HD);
+      if (d->fast) {
+        orcf_sdpa_f32(1, 1, H, KVH, HD, len, q + (size_t)b * H * HD, kc + (size_t)b * per_seq, vc + (size_t)b * per_seq,
+                      NULL, NULL, scale, att + (size_t)b * H * HD);
+      } else {
+        orc_sdpa_f32(1, 1, H, KVH, HD, len, q + (size_t)b * H * HD, kc + (size_t)b * per_seq, vc + (size_t)b * per_seq,
+                     NULL, scale, 0.0f, att + (size_t)b * H * HD);
+      }
+    }
+    fc(d, B, D, H * HD, att, w->wo, w->so, o);
+    for (size_t i = 0; i < (size_t)B * D; ++i) h[i] += o[i];
+    for (int b = 0; b < B; ++b) rms_norm(h + (size_t)b * D, w->norm2, D, c->rms_eps, x + (size_t)b * D);
+    fc(d, B, F, D, x, w->wgate, w->sgate, gate);
+    fc(d, B, F, D, x, w->wup, w->sup, up);
+    for (size_t i = 0; i < (size_t)B * F; ++i) gate[i] = gelu_tanh(gate[i]) * up[i];
+    fc(d, B, D, F, gate, w->wdown, w->sdown, o);
+    for (size_t i = 0; i < (size_t)B * D; ++i) h[i] += o[i];
+  }
+  for (int b = 0; b < B; ++b) rms_norm(h + (size_t)b * D, d->final_norm, D, c->rms_eps, x + (size_t)b * D);
+  fc(d, B, c->vocab, D, x, d->embed, d->embed_scales, logits);
+  for (int b = 0; b < B; ++b) {
+    const float* lg = logits + (size_t)b * c->vocab;
+    int best = 0;
+    for (int i = 1; i < c->vocab; ++i)
+      if (lg[i] > lg[best]) best = i;
+    if (next_tokens) next_tokens[b] = best;
+    d->lengths[b] += 1;
+  }
+  free(h); free(x); free(q); free(kk); free(vv); free(att); free(o); free(gate); free(up);
+  if (!logits_out) free(logits);
+}
