@@ -186,6 +186,9 @@ B200_API int b200_decoder_set_embedding(b200_decoder* dec, const int8_t* d_table
                                         const float* d_final_norm);
 B200_API int b200_decoder_set_allreduce(b200_decoder* dec, b200_allreduce_fn fn, void* user);
 B200_API int b200_decoder_reset(b200_decoder* dec);
+/* Declares h_positions[i] tokens already cached for sequence i (cache rows never written hold
+ * zeros): lets a caller resume from a cache filled elsewhere, or time a step at a given depth. */
+B200_API int b200_decoder_set_positions(b200_decoder* dec, const int32_t* h_positions, int batch);
 /* One token per sequence. h_tokens / h_next_tokens are HOST arrays of `batch`
  * ints (pinned memory avoids a staging copy); d_logits (optional, device,
  * [batch, vocab]) receives the logits. Synchronises the stream before returning

@@ -37,6 +37,7 @@ SIGNATURES = {
     "b200_decoder_set_embedding": (_i, [_vp, _vp, _vp, _vp]),
     "b200_decoder_set_allreduce": (_i, [_vp, _vp, _vp]),
     "b200_decoder_reset": (_i, [_vp]),
+    "b200_decoder_set_positions": (_i, [_vp, _vp, _i]),
     "b200_decoder_step": (_i, [_vp, _vp, _i, _vp, _vp]),
     "b200_decoder_run": (_i, [_vp, _vp, _i, _i, _vp]),
     "b200_decoder_launches_per_step": (_i, [_vp]),

@@ -234,3 +234,36 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&r)[16]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 }  // namespace b200
+
+// ---- programmatic dependent launch ---------------------------------------------
+// Kernels of a dependent chain are launched with programmatic stream
+// serialization: a kernel may start while its predecessor is still running, does
+// whatever does not depend on it (barrier set-up, TMEM allocation, prefetching
+// constant weights), and calls pdl_wait() before touching anything the
+// predecessor produces (the wait returns once the predecessor grid has completed
+// and its writes are visible). pdl_launch_dependents() lets the successor start;
+// it is only ever called after pdl_wait(), so at most two consecutive kernels of
+// a chain overlap. Both are no-ops for a kernel launched the ordinary way.
+namespace b200 {
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// B200_PDL=0 turns the attribute off (plain stream order) for A/B measurement.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                  Args... args) {
+  cudaLaunchConfig_t cfg;
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+}  // namespace b200

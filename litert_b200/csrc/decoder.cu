@@ -166,6 +166,7 @@ cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_
   p.status = reinterpret_cast<int*>(z);
   p.ws_count = reinterpret_cast<int32_t*>(z + zero_ws_counter_off());
   p.ws_acc = reinterpret_cast<int32_t*>(z + zero_ws_acc_off());
+  p.ws_part = reinterpret_cast<int32_t*>(z + b200::zero_ws_part_off());
   ++d->launches;
   ProfScope scope(d, 0);
   return launch_fc_i8_umma(p, kEpiHybridF32, d->stream);
@@ -202,7 +203,11 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
     sp.k_scale = L.k_scale.as<float>();
     sp.v_scale = L.v_scale.as<float>();
     sp.lengths = d->attn_len.as<int32_t>();
-    sp.out = d->attn.p;
+    sp.out = nullptr;  // only the quantized rows are needed downstream
+    sp.q_tiled_out = d->q_a.as<int8_t>();
+    sp.out_scales = d->sc_a.as<float>();
+    sp.out_zps = d->zp_a.as<int32_t>();
+    sp.m_alloc = m_alloc;
     sp.b = batch;
     sp.n = c.n_heads;
     sp.nkv = c.n_kv_heads;
@@ -219,9 +224,6 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
       DEC_CUDA(launch_sdpa_decode(sp, s));
     }
     count(2);
-    GLUE_CUDA(launch_quantize_rows(d->attn.as<float>(), batch, qdim, tiles_k8(qdim) * 128, m_alloc, 1,
-                                  d->q_a.as<int8_t>(), nullptr, d->sc_a.as<float>(), d->zp_a.as<int32_t>(), s));
-    count();
     DEC_CUDA(run_fc(d, L.o, batch, d->q_a.as<int8_t>(), d->sc_a.as<float>(), d->zp_a.as<int32_t>(), d->proj.as<float>()));
     GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->proj.as<float>(), L.norm2.as<float>(), batch, c.d_model,
                                    c.rms_eps, m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), s));
@@ -329,6 +331,8 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
     Layer& L = *d->layers.back();
     DEC_CUDA(L.k_cache.alloc(kv_bytes));
     DEC_CUDA(L.v_cache.alloc(kv_bytes));
+    DEC_CUDA(cudaMemsetAsync(L.k_cache.p, 0, kv_bytes, d->stream));
+    DEC_CUDA(cudaMemsetAsync(L.v_cache.p, 0, kv_bytes, d->stream));
     if (c.kv_dtype == B200_DTYPE_I8) {
       DEC_CUDA(L.k_scale.alloc(sizeof(float) * (size_t)B * c.max_seq * c.n_kv_heads));
       DEC_CUDA(L.v_scale.alloc(sizeof(float) * (size_t)B * c.max_seq * c.n_kv_heads));
@@ -393,6 +397,15 @@ int b200_decoder_set_allreduce(b200_decoder* d, b200_allreduce_fn fn, void* user
 int b200_decoder_reset(b200_decoder* d) {
   if (!d) return dec_fail(B200_ERR_INVALID_ARGUMENT, "null decoder");
   DEC_CUDA(cudaMemsetAsync(d->positions.p, 0, sizeof(int32_t) * d->cfg.max_batch, d->stream));
+  return B200_OK;
+}
+
+int b200_decoder_set_positions(b200_decoder* d, const int32_t* h_positions, int batch) {
+  if (!d || !h_positions || batch <= 0 || batch > d->cfg.max_batch) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_set_positions: bad argument");
+  for (int i = 0; i < batch; ++i)
+    if (h_positions[i] < 0 || h_positions[i] >= d->cfg.max_seq) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_set_positions: position out of range");
+  DEC_CUDA(cudaMemcpyAsync(d->positions.p, h_positions, sizeof(int32_t) * batch, cudaMemcpyHostToDevice, d->stream));
+  DEC_CUDA(cudaStreamSynchronize(d->stream));
   return B200_OK;
 }
 

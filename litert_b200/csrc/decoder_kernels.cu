@@ -18,36 +18,6 @@ namespace {
 
 constexpr int kRowThreads = 256;
 
-// Quantizes the row held in shared memory `xs[0..k)` (asymmetric, per row) and
-// writes it tiled; thread 0 publishes scale and zero point.
-__device__ void quantize_smem_row(const float* xs, int k, int k_pad, int row, int m_alloc, float mn, float mx,
-                                  int8_t* q_tiled, float* scales, int32_t* zps, float* red) {
-  __shared__ float s_inv;
-  __shared__ int s_zp, s_zero;
-  mn = block_reduce(mn, [](float a, float b) { return fminf(a, b); }, mn, red);
-  mx = block_reduce(mx, [](float a, float b) { return fmaxf(a, b); }, mx, red);
-  if (threadIdx.x == 0) {
-    float sf, inv;
-    int zp, zero_row;
-    row_quant_params(mn, mx, true, &sf, &inv, &zp, &zero_row);
-    s_zero = zero_row;
-    s_inv = inv;
-    s_zp = zp;
-    scales[row] = sf;
-    zps[row] = zp;
-  }
-  __syncthreads();
-  const bool zero = s_zero != 0;
-  const float inv = s_inv, zpf = (float)s_zp;
-  for (int k4 = threadIdx.x * 4; k4 < k_pad; k4 += blockDim.x * 4) {
-    uint32_t word = 0;
-#pragma unroll
-    for (int b = 0; b < 4; ++b)
-      if (k4 + b < k && !zero) word |= quantize_value(xs[k4 + b], inv, zpf, true) << (8 * b);
-    *reinterpret_cast<uint32_t*>(q_tiled + q_tiled_offset(row, k4, m_alloc)) = word;
-  }
-}
-
 // h[b,:] = int8 embedding row * its scale * embed_scale; also attn_len = positions + 1.
 __global__ void __launch_bounds__(kRowThreads) embed_kernel(const int32_t* __restrict__ tokens,
                                                             const int8_t* __restrict__ table,
@@ -55,6 +25,8 @@ __global__ void __launch_bounds__(kRowThreads) embed_kernel(const int32_t* __res
                                                             float embed_scale, float* __restrict__ h,
                                                             const int32_t* __restrict__ positions,
                                                             int32_t* __restrict__ attn_len) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.x;
   const int tok = tokens[b];
   const float s = row_scales[tok];
@@ -74,6 +46,8 @@ __global__ void __launch_bounds__(kRowThreads) add_norm_quant_kernel(float* __re
                                                                      int32_t* __restrict__ zps) {
   extern __shared__ float xs[];
   __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.x;
   float* hr = h + (size_t)b * d;
   float ss = 0.0f;
@@ -109,6 +83,8 @@ __global__ void __launch_bounds__(1024) geglu_quant_kernel(const float* __restri
                                                            float* __restrict__ scales, int32_t* __restrict__ zps) {
   extern __shared__ float xs[];
   __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.x;
   const float* g = gate_up + (size_t)b * 2 * f;
   const float* u = g + f;
@@ -130,6 +106,8 @@ __global__ void rope_cache_kernel(const float* __restrict__ qkv, int heads, int 
                                   float* __restrict__ q_out, void* __restrict__ k_cache, void* __restrict__ v_cache,
                                   float* __restrict__ k_scale, float* __restrict__ v_scale) {
   __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.x, slot = blockIdx.y, i = threadIdx.x, half = head_dim / 2;
   const int pos = positions[b];
   const float* src = qkv + ((size_t)b * (heads + 2 * kv_heads) + slot) * head_dim;
@@ -184,6 +162,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
                                                              int32_t* __restrict__ part_idx) {
   __shared__ float sv[8];
   __shared__ int si[8];
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.y, part = blockIdx.x;
   const int per = (n + parts - 1) / parts;
   const int lo = part * per, hi = min(n, lo + per);
@@ -211,6 +191,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
 __global__ void argmax_final_kernel(const float* __restrict__ part_val, const int32_t* __restrict__ part_idx,
                                     int parts, int32_t* __restrict__ next_tokens, int32_t* __restrict__ positions,
                                     int max_seq) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.x;
   BestPair best{part_val[(size_t)b * parts], part_idx[(size_t)b * parts]};
   for (int i = threadIdx.x; i < parts; i += 32)
@@ -230,16 +212,15 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val, const in
 
 cudaError_t launch_embed(const int32_t* tokens, const int8_t* table, const float* row_scales, int batch, int d,
                          float embed_scale, float* h, const int32_t* positions, int32_t* attn_len, cudaStream_t s) {
-  embed_kernel<<<batch, kRowThreads, 0, s>>>(tokens, table, row_scales, d, embed_scale, h, positions, attn_len);
-  return cudaGetLastError();
+  return launch_chained(embed_kernel, dim3(batch), dim3(kRowThreads), 0, s, tokens, table, row_scales, d, embed_scale, h, positions,
+                        attn_len);
 }
 
 cudaError_t launch_add_norm_quant(float* h, const float* delta, const float* gain, int batch, int d, float eps,
                                   int m_alloc, int8_t* q_tiled, float* scales, int32_t* zps, cudaStream_t s) {
   const int d_pad = (d + 127) / 128 * 128;
-  add_norm_quant_kernel<<<batch, kRowThreads, sizeof(float) * d, s>>>(h, delta, gain, d, d_pad, eps, m_alloc, q_tiled,
-                                                                       scales, zps);
-  return cudaGetLastError();
+  return launch_chained(add_norm_quant_kernel, dim3(batch), dim3(kRowThreads), sizeof(float) * d, s, h, delta, gain, d, d_pad,
+                        eps, m_alloc, q_tiled, scales, zps);
 }
 
 cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_alloc, int8_t* q_tiled, float* scales,
@@ -256,8 +237,7 @@ cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_all
   }
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   const int f_pad = (f + 127) / 128 * 128;
-  geglu_quant_kernel<<<batch, 1024, smem, s>>>(gate_up, f, f_pad, m_alloc, q_tiled, scales, zps);
-  return cudaGetLastError();
+  return launch_chained(geglu_quant_kernel, dim3(batch), dim3(1024), smem, s, gate_up, f, f_pad, m_alloc, q_tiled, scales, zps);
 }
 
 cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, float rope_base,
@@ -265,20 +245,20 @@ cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_hea
                               float* k_scale, float* v_scale, int kv_int8, cudaStream_t s) {
   dim3 grid(batch, heads + 2 * kv_heads);
   if (kv_int8) {
-    rope_cache_kernel<true><<<grid, head_dim / 2, 0, s>>>(qkv, heads, kv_heads, head_dim, rope_base, positions, max_seq,
-                                                          q_out, k_cache, v_cache, k_scale, v_scale);
-  } else {
-    rope_cache_kernel<false><<<grid, head_dim / 2, 0, s>>>(qkv, heads, kv_heads, head_dim, rope_base, positions,
-                                                           max_seq, q_out, k_cache, v_cache, k_scale, v_scale);
+    return launch_chained(rope_cache_kernel<true>, grid, dim3(head_dim / 2), 0, s, qkv, heads, kv_heads, head_dim, rope_base,
+                          positions, max_seq, q_out, k_cache, v_cache, k_scale, v_scale);
   }
-  return cudaGetLastError();
+  return launch_chained(rope_cache_kernel<false>, grid, dim3(head_dim / 2), 0, s, qkv, heads, kv_heads, head_dim, rope_base,
+                        positions, max_seq, q_out, k_cache, v_cache, k_scale, v_scale);
 }
 
 cudaError_t launch_argmax(const float* logits, int batch, int n, float* part_val, int32_t* part_idx,
                           int32_t* next_tokens, int32_t* positions, int max_seq, cudaStream_t s) {
-  argmax_partial_kernel<<<dim3(kArgmaxParts, batch), 256, 0, s>>>(logits, n, kArgmaxParts, part_val, part_idx);
-  argmax_final_kernel<<<batch, 32, 0, s>>>(part_val, part_idx, kArgmaxParts, next_tokens, positions, max_seq);
-  return cudaGetLastError();
+  cudaError_t e = launch_chained(argmax_partial_kernel, dim3(kArgmaxParts, batch), dim3(256), 0, s, logits, n, (int)kArgmaxParts,
+                                 part_val, part_idx);
+  if (e != cudaSuccess) return e;
+  return launch_chained(argmax_final_kernel, dim3(batch), dim3(32), 0, s, (const float*)part_val, (const int32_t*)part_idx,
+                        (int)kArgmaxParts, next_tokens, positions, max_seq);
 }
 
 }  // namespace b200

@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(kThreads, 1) fc_stream_kernel(const FcParams p
         // Scratch slot = index of the CTA holding this tile's first k tile: tiles
         // that are split have distinct first CTAs, so gridDim.x slots suffice.
         const int slot = (int)((((long long)nt * p.k_tiles + 1) * gridDim.x - 1) / total);
-        AccT* ws = reinterpret_cast<AccT*>(p.ws_acc) + (size_t)slot * (kTileN * 64);
+        AccT* ws = reinterpret_cast<AccT*>(p.ws_acc) + (size_t)slot * kAccSlotInts;
 #pragma unroll
         for (int j = 0; j < MT; ++j)
 #pragma unroll
@@ -335,7 +335,7 @@ cudaError_t launch_one(const FcParams& p, int m_base, cudaStream_t s) {
     const int v = atoi(e);
     if (v > 0) ctas = v;
   }
-  if (ctas > kZeroWsSlots) ctas = kZeroWsSlots;
+  if (ctas > kAccSlots) ctas = kAccSlots;
   if (ctas > total) ctas = (int)total;
   if (ctas < 1) ctas = 1;
   kernel<<<ctas, kThreads, L::kSmemBytes, s>>>(p, m_base);

@@ -18,10 +18,10 @@
 //                      coalesced along n.
 // The (n tile, k tile) sequence is cut into equal contiguous ranges, one per
 // CTA (stream-K): every SM streams the same number of weight bytes. A CTA that
-// holds only part of an n tile's reduction adds its int32 partials to a global
-// scratch slot; the CTA whose arrival completes the tile's k count reloads the
-// sums, runs the epilogue and clears the slot. Integer addition makes the
-// result independent of arrival order and bit-equal to a serial sum.
+// holds only part of an n tile's reduction parks its int32 partials in a scratch
+// slot of its own (plain stores); the CTA whose arrival completes the tile's k
+// count sums the contributors' slots and runs the epilogue. Integer addition
+// makes the result bit-equal to a serial sum.
 // Every wait is bounded (see mbar_wait_bounded); TMEM is always freed.
 #include <cstdlib>
 
@@ -121,8 +121,23 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
   if (warp == 0) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      uint32_t it = 0;
-      for (long long t = t_begin; t < t_end; ++t, ++it) {
+      // The weights are constants: start streaming them before the kernel that produces the
+      // activations has finished (programmatic dependent launch), one ring's worth at most.
+      uint32_t pre = 0;
+      for (long long t = t_begin; t < t_end && pre < (uint32_t)L::kStages; ++t, ++pre) {
+        uint8_t* dst = smem + (size_t)pre * L::kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[pre], L::kStageBytes);
+        bulk_g2s(dst, p.w_packed + (size_t)t * kTileBytes, kTileBytes, &full_bar[pre]);
+      }
+      pdl_wait();               // activations (and the split-K scratch) are now safe to touch
+      pdl_launch_dependents();
+      for (uint32_t i = 0; i < pre; ++i) {
+        const int kt = (int)((t_begin + i) % p.k_tiles);
+        const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
+        bulk_g2s(smem + (size_t)i * L::kStageBytes + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[i]);
+      }
+      uint32_t it = pre;
+      for (long long t = t_begin + pre; t < t_end; ++t, ++it) {
         const int s = it % L::kStages;
         const uint32_t ph = (it / L::kStages) & 1u;
         mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, p.status, kStatusWaitTimeoutEmpty);
@@ -187,6 +202,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
     const int row_in_tile = quarter * 32 + lane;
     const int etid = tid - 64;
     const int m_valid = p.m - m_base < NB ? p.m - m_base : NB;
+    pdl_wait();  // the epilogue reads activation scales written by the previous kernel
     uint32_t seg = 0;
     long long t = t_begin;
     while (t < t_end) {
@@ -226,6 +242,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
       } else if (!partial) {
 #pragma unroll 1
         for (int c = 0; c < NB / 16; ++c) {
+          if (c * 16 >= m_valid) break;
           int r[16];
           tmem_ld16(taddr + c * 16, r);
           tmem_ld_wait();
@@ -241,27 +258,37 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[ab]);
       } else {
-        // scratch slot = index of the CTA holding this tile's first k tile (distinct for split tiles)
-        const int slot = (int)((((long long)nt * p.k_tiles + 1) * gridDim.x - 1) / total);
-        int32_t* ws = p.ws_acc + (size_t)slot * kZeroWsSlotInts;
+        // Split tile: every contributing CTA parks its int32 partials in a scratch slot of its own
+        // (two per CTA: one for a tile continued from an earlier CTA, one for a tile that goes on in
+        // the next) with plain coalesced stores, then adds its k-tile count to the tile's counter.
+        // Whoever completes the count sums the contributors' slots in CTA order and runs the
+        // epilogue. No accumulator ever needs clearing; only the counter is reset.
+        const long long tile_first = nt * p.k_tiles, tile_last = tile_first + p.k_tiles - 1;
+        const int g = gridDim.x;
+        const int c_first = (int)(((tile_first + 1) * g - 1) / total);
+        const int c_last = (int)(((tile_last + 1) * g - 1) / total);
+        const int which = (t_begin <= tile_first) ? 1 : 0;
+        int32_t* mine = p.ws_part + (size_t)(blockIdx.x * 2 + which) * kZeroWsSlotInts;
 #pragma unroll 1
         for (int c = 0; c < NB / 16; ++c) {
+          if (c * 16 >= m_valid) break;
           int r[16];
           tmem_ld16(taddr + c * 16, r);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = c * 16 + j;
-            if (m < m_valid) atomicAdd(&ws[m * kTileN + row_in_tile], r[j]);
+            if (m < m_valid) __stcg(&mine[m * kTileN + row_in_tile], r[j]);
           }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[ab]);
+        __threadfence();
         named_barrier(1, kEpiThreads);
         if (etid == 0) {
           __threadfence();
-          const int old = atomicAdd(&p.ws_count[slot], seg_tiles);
+          const int old = atomicAdd(&p.ws_count[c_first], seg_tiles);
           sh->last = (old + seg_tiles == p.k_tiles) ? 1 : 0;
         }
         named_barrier(1, kEpiThreads);
@@ -269,12 +296,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         if (last) {
           __threadfence();
           for (int m = 0; m < m_valid; ++m) {
-            int32_t* slotp = &ws[m * kTileN + row_in_tile];
-            const int32_t v = __ldcg(slotp);
-            __stcg(slotp, 0);
+            int32_t v = 0;
+            for (int c = c_first; c <= c_last; ++c) {
+              const int w = (c == c_first) ? 1 : 0;
+              v += __ldcg(p.ws_part + (size_t)(c * 2 + w) * kZeroWsSlotInts + m * kTileN + row_in_tile);
+            }
             if (row_ok) store_output<EPI>(p, m_base + m, n, v, rs, wsc, bias_f, base_i, mult, shift);
           }
-          if (etid == 0) p.ws_count[slot] = 0;
+          if (etid == 0) p.ws_count[c_first] = 0;
         }
         named_barrier(1, kEpiThreads);  // sh->last is rewritten by the next split tile
       }
@@ -306,11 +335,10 @@ cudaError_t launch_umma_one(const FcParams& p, int m_base, cudaStream_t s) {
     const int v = atoi(e);
     if (v > 0) ctas = v;
   }
-  if (ctas > kZeroWsSlots) ctas = kZeroWsSlots;
+  if (ctas > kZeroWsSlots / 2) ctas = kZeroWsSlots / 2;  // two scratch slots per CTA
   if (ctas > total) ctas = (int)total;
   if (ctas < 1) ctas = 1;
-  kernel<<<ctas, kUmmaThreads, L::kSmemBytes, s>>>(p, m_base);
-  return cudaGetLastError();
+  return launch_chained(kernel, dim3(ctas), dim3(kUmmaThreads), (size_t)L::kSmemBytes, s, p, m_base);
 }
 
 template <int EPI>

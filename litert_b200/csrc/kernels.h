@@ -64,7 +64,8 @@ struct FcParams {
   void* y;                   // [m,n] row-major float / int8 / int32
   // split-K workspace: kZeroWsSlots slots of 128*64 int32/float accumulators and as many counters;
   // all zero between calls
-  int32_t* ws_acc;
+  int32_t* ws_acc;    // mma.sync path: zero between calls
+  int32_t* ws_part;   // tcgen05 path: per-CTA partial slots, no initial contents needed
   int32_t* ws_count;
   int* status;
   int max_ctas;              // 0 = one per SM
@@ -81,14 +82,18 @@ int umma_rows_per_pass(int m);
 // Blockwise 4-bit weights, float out.
 cudaError_t launch_fc_w4(const FcParams& p, cudaStream_t s);
 
-constexpr int kZeroWsSlots = 256;            // >= CTAs per launch
-constexpr int kZeroWsSlotInts = 128 * 256;   // accumulators per slot (128 rows x up to 256 activation rows)
+constexpr int kZeroWsSlots = 320;            // counters; >= 2 x CTAs per launch
+constexpr int kAccSlots = 160;               // mma.sync path: one accumulator slot per CTA
+constexpr int kAccSlotInts = 128 * 64;       // 128 rows x up to 64 activation rows
+constexpr int kZeroWsSlotInts = 128 * 256;   // tcgen05 path: 128 rows x up to 256 activation rows per partial slot
 int device_sm_count();
 
-// Layout of the zero workspace: [status word + padding: 256 B][slot counters][slot accumulators].
+// Layout of the zero workspace: [status word + padding: 256 B][slot counters][mma.sync accumulators]
+// [tcgen05 partial slots]. Only the first three parts must be zero between calls.
 inline size_t zero_ws_counter_off() { return 256; }
 inline size_t zero_ws_acc_off() { return 256 + ((sizeof(int32_t) * kZeroWsSlots + 255) / 256) * 256; }
-inline size_t zero_ws_total_bytes() { return zero_ws_acc_off() + sizeof(int32_t) * (size_t)kZeroWsSlots * kZeroWsSlotInts; }
+inline size_t zero_ws_part_off() { return zero_ws_acc_off() + sizeof(int32_t) * (size_t)kAccSlots * kAccSlotInts; }
+inline size_t zero_ws_total_bytes() { return zero_ws_part_off() + sizeof(int32_t) * (size_t)kZeroWsSlots * kZeroWsSlotInts; }
 
 struct SdpaParams {
   const void* q;        // [b, t(=1), n, h] f16 or f32
@@ -104,6 +109,12 @@ struct SdpaParams {
   int kv_dtype;  // 0 = f16, 1 = int8, 2 = f32
   float scale, logit_cap;
   float* ws;     // partials workspace
+  // optional fused output quantization (decoder): the merged [b, n*h] rows are quantized per row
+  // (asymmetric) and written tiled for the next GEMM instead of / in addition to `out`
+  int8_t* q_tiled_out;
+  float* out_scales;
+  int32_t* out_zps;
+  int m_alloc;
   size_t ws_bytes;
   int* status;
 };

@@ -1,10 +1,21 @@
 // One-time weight repacking (run at delegate-kernel init) and the per-call
 // activation preparation kernels: row quantization and int8 re-tiling.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "quant.cuh"
 
 namespace b200 {
+
+bool pdl_enabled() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* e = getenv("B200_PDL");
+    cached = (e && e[0] == '0') ? 0 : 1;
+  }
+  return cached == 1;
+}
 
 // ---- int8 weights: row-major [n,k] -> tiles --------------------------------
 // One thread per 16-byte chunk of the packed buffer.
@@ -145,6 +156,8 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restr
   __shared__ float s_inv;
   __shared__ int s_zp;
   __shared__ int s_zero;
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x;
   const float* xr = x + (size_t)row * k;
   float mn = xr[0], mx = xr[0];
@@ -265,8 +278,8 @@ cudaError_t launch_quantize_rows(const float* x, int m, int k, int k_pad, int m_
                                  int8_t* q_tiled, int8_t* q_rowmajor, float* scales, int32_t* zps,
                                  cudaStream_t s) {
   if (m <= 0) return cudaSuccess;
-  quantize_rows_kernel<<<m, 256, 0, s>>>(x, m, k, k_pad, m_alloc, asymmetric, q_tiled, q_rowmajor, scales, zps);
-  return cudaGetLastError();
+  return launch_chained(quantize_rows_kernel, dim3(m), dim3(256), 0, s, x, m, k, k_pad, m_alloc, asymmetric, q_tiled, q_rowmajor,
+                        scales, zps);
 }
 
 cudaError_t launch_retile_x8(const int8_t* x, int m, int k, int k_pad, int m_alloc, int8_t* q_tiled,

@@ -88,4 +88,35 @@ __device__ __forceinline__ uint32_t quantize_value(float v, float inv, float zpf
   return (uint32_t)(uint8_t)(int8_t)qv;
 }
 
+// Quantizes the row held in shared memory `xs[0..k)` (asymmetric, per row) and
+// writes it tiled; thread 0 publishes scale and zero point.
+__device__ __forceinline__ void quantize_smem_row(const float* xs, int k, int k_pad, int row, int m_alloc, float mn, float mx,
+                                  int8_t* q_tiled, float* scales, int32_t* zps, float* red) {
+  __shared__ float s_inv;
+  __shared__ int s_zp, s_zero;
+  mn = block_reduce(mn, [](float a, float b) { return fminf(a, b); }, mn, red);
+  mx = block_reduce(mx, [](float a, float b) { return fmaxf(a, b); }, mx, red);
+  if (threadIdx.x == 0) {
+    float sf, inv;
+    int zp, zero_row;
+    row_quant_params(mn, mx, true, &sf, &inv, &zp, &zero_row);
+    s_zero = zero_row;
+    s_inv = inv;
+    s_zp = zp;
+    scales[row] = sf;
+    zps[row] = zp;
+  }
+  __syncthreads();
+  const bool zero = s_zero != 0;
+  const float inv = s_inv, zpf = (float)s_zp;
+  for (int k4 = threadIdx.x * 4; k4 < k_pad; k4 += blockDim.x * 4) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+      if (k4 + b < k && !zero) word |= quantize_value(xs[k4 + b], inv, zpf, true) << (8 * b);
+    *reinterpret_cast<uint32_t*>(q_tiled + q_tiled_offset(row, k4, m_alloc)) = word;
+  }
+}
+
+
 }  // namespace b200

@@ -24,6 +24,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "quant.cuh"
 
 namespace b200 {
 
@@ -103,6 +104,8 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
   constexpr int DPT = DB / 8;            // head-dim elements per thread per block (8 or 16)
   constexpr int KSTEPS = H / 32;         // 16-byte K pieces per thread per row
 
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.z, kvh = blockIdx.y, chunk = blockIdx.x;
   const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
   const int c0 = chunk * chunk_tokens;
@@ -327,6 +330,8 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
 // H threads.
 template <int H, bool QF32>
 __global__ void sdpa_merge_kernel(const SdpaParams p, const int chunk_tokens, const int chunks_max) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.y, head = blockIdx.x, d = threadIdx.x;
   const int group = p.n / p.nkv;
   const int kvh = head / group, hg = head % group;
@@ -350,6 +355,46 @@ __global__ void sdpa_merge_kernel(const SdpaParams p, const int chunk_tokens, co
   } else {
     static_cast<__half*>(p.out)[oi] = __float2half_rn(out);
   }
+}
+
+// Merge of the per-chunk partials fused with the per-row asymmetric int8 quantization the next
+// hybrid FULLY_CONNECTED applies to the attention output: grid (b), one CTA per sequence over all
+// n*h outputs. Writes the tiled int8 row (+ scale, zero point) and, when p.out is set, the floats.
+template <int H>
+__global__ void __launch_bounds__(256) sdpa_merge_quant_kernel(const SdpaParams p, const int chunk_tokens,
+                                                              const int chunks_max) {
+  extern __shared__ float xs[];
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x;
+  const int group = p.n / p.nkv;
+  const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
+  const int chunks = (len + chunk_tokens - 1) / chunk_tokens;
+  const size_t cstride = 8 * partial_stride(H);
+  const int width = p.n * H;
+  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+  for (int idx = threadIdx.x; idx < width; idx += blockDim.x) {
+    const int head = idx / H, d = idx % H;
+    const int kvh = head / group, hg = head % group;
+    const float* base = p.ws + ((((size_t)b * p.nkv + kvh) * chunks_max) * 8 + hg) * partial_stride(H);
+    float mm = -CUDART_INF_F;
+    for (int c = 0; c < chunks; ++c) mm = fmaxf(mm, base[c * cstride + H]);
+    const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
+    float acc = 0.0f, l = 0.0f;
+    for (int c = 0; c < chunks; ++c) {
+      const float f = exp2f(base[c * cstride + H] - muse);
+      acc += f * base[c * cstride + d];
+      l += f * base[c * cstride + H + 1];
+    }
+    const float v = acc / l;
+    xs[idx] = v;
+    if (p.out) static_cast<float*>(p.out)[(size_t)b * width + idx] = v;
+    mn = fminf(mn, v);
+    mx = fmaxf(mx, v);
+  }
+  const int k_pad = (width + 127) / 128 * 128;
+  quantize_smem_row(xs, width, k_pad, b, p.m_alloc, mn, mx, p.q_tiled_out, p.out_scales, p.out_zps, red);
 }
 
 // Generic fallback (any head size / group size): one warp per (batch, head),
@@ -418,9 +463,13 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
   const int chunk_tokens = pick_chunk_tokens(p.s_max);
   const int chunks_max = (p.s_max + chunk_tokens - 1) / chunk_tokens;
   dim3 grid(chunks_max, p.nkv, p.b);
-  sdpa_decode_kernel<KV, H, QF32><<<grid, kWarps * 32, 0, s>>>(p, chunk_tokens, chunks_max);
-  sdpa_merge_kernel<H, QF32><<<dim3(p.n, p.b), H, 0, s>>>(p, chunk_tokens, chunks_max);
-  return cudaGetLastError();
+  cudaError_t e = launch_chained(sdpa_decode_kernel<KV, H, QF32>, grid, dim3(kWarps * 32), 0, s, p, chunk_tokens, chunks_max);
+  if (e != cudaSuccess) return e;
+  if (p.q_tiled_out) {
+    return launch_chained(sdpa_merge_quant_kernel<H>, dim3(p.b), dim3(256), sizeof(float) * p.n * H, s, p, chunk_tokens,
+                          chunks_max);
+  }
+  return launch_chained(sdpa_merge_kernel<H, QF32>, dim3(p.n, p.b), dim3(H), 0, s, p, chunk_tokens, chunks_max);
 }
 
 template <int KV, bool QF32>
@@ -428,6 +477,8 @@ cudaError_t launch_kv(const SdpaParams& p, cudaStream_t s) {
   const int group = p.nkv > 0 ? p.n / p.nkv : 0;
   const bool fast = group >= 1 && group <= 8 && p.n % p.nkv == 0 && p.ws != nullptr &&
                     p.ws_bytes >= sdpa_workspace_bytes(p.b, p.n, p.h, p.s_max);
+  if (p.q_tiled_out && (!fast || !QF32 || (p.h != 256 && p.h != 128 && p.h != 64)))
+    return cudaErrorInvalidValue;  // fused output quantization exists on the fast f32-query path only
   if (fast && p.h == 256) return launch_fast<KV, 256, QF32>(p, s);
   if (fast && p.h == 128) return launch_fast<KV, 128, QF32>(p, s);
   if (fast && p.h == 64) return launch_fast<KV, 64, QF32>(p, s);

@@ -78,6 +78,7 @@ void fill_ws(b200::FcParams& p, void* d_zero_ws) {
   p.status = reinterpret_cast<int*>(z);
   p.ws_count = reinterpret_cast<int32_t*>(z + zero_ws_counter_off());
   p.ws_acc = reinterpret_cast<int32_t*>(z + zero_ws_acc_off());
+  p.ws_part = reinterpret_cast<int32_t*>(z + b200::zero_ws_part_off());
 }
 
 }  // namespace

@@ -79,6 +79,10 @@ class Decoder:
     def reset(self):
         _check(self.lib.b200_decoder_reset(self.handle))
 
+    def set_positions(self, positions):
+        pos = np.ascontiguousarray(positions, np.int32)
+        _check(self.lib.b200_decoder_set_positions(self.handle, pos.ctypes.data_as(ctypes.c_void_p), pos.size))
+
     def step(self, tokens, want_logits=False):
         """tokens: host int32 array [batch] -> (next tokens [batch], logits or None)."""
         tok = np.ascontiguousarray(tokens, np.int32)
