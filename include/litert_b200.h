@@ -138,6 +138,26 @@ B200_API int b200_sdpa_decode(const void* d_q, const void* d_k, const void* d_v,
                               float scale, float logit_cap, void* d_workspace, size_t workspace_bytes,
                               void* stream);
 
+/* ---- attention decode step without any allocation --------------------------
+ * No counterpart in the reference: this entry point exists for callers of THIS
+ * library that are not allowed to allocate device memory (a serving loop that
+ * has frozen its allocator after start-up, a plugin living inside someone
+ * else's fixed memory budget, code being recorded for replay) and therefore
+ * cannot supply the workspace b200_sdpa_decode asks for. Same arguments and
+ * results as b200_sdpa_decode, minus the workspace: the split-K partials go to
+ * a built-in device array of b200_sdpa_static_workspace_limit() bytes (8 MiB,
+ * held by every GPU that loads the library until exit). Shapes that need more
+ * are rejected with B200_ERR_UNSUPPORTED. The first call on a device looks up
+ * the array's device address (set-up; make it before any stream capture).
+ * Calls share the array: calls that overlap on the GPU race, serialise them.
+ * Calls no cudaMalloc/cudaFree or allocating routine. */
+B200_API size_t b200_sdpa_static_workspace_limit(void);
+B200_API int b200_sdpa_decode_static(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale,
+                                     const float* d_v_scale, const int32_t* d_lengths, const float* d_mask,
+                                     void* d_out, int b, int n, int nkv, int h, int s_max, int q_dtype, int kv_dtype,
+                                     float scale, float logit_cap, void* stream);
+B200_API const char* b200_sdpa_static_last_error(void);
+
 /* ---- Gemma-shaped decoder, one decode step per call ---------------------------
  * A resident decoder for the decode benchmark: every projection is a dynamic-range
  * hybrid FULLY_CONNECTED (b200_fc_hybrid semantics: per-row asymmetric input

@@ -31,6 +31,9 @@ SIGNATURES = {
     "b200_sdpa_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "b200_sdpa_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _sz,
                               _vp]),
+    "b200_sdpa_static_workspace_limit": (_sz, []),
+    "b200_sdpa_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
+    "b200_sdpa_static_last_error": (ctypes.c_char_p, []),
     "b200_decoder_create": (_i, [_vp, _vp, ctypes.POINTER(_vp)]),
     "b200_decoder_destroy": (None, [_vp]),
     "b200_decoder_set_layer": (_i, [_vp, _i, _vp]),

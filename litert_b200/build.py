@@ -15,7 +15,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden"]
 
-KERNEL_SOURCES = ["pack.cu", "fc_stream.cu", "fc_umma.cu", "sdpa_decode.cu", "decoder_kernels.cu", "decoder.cu", "shim.cu"]
+KERNEL_SOURCES = ["pack.cu", "fc_stream.cu", "fc_umma.cu", "sdpa_decode.cu", "decoder_kernels.cu", "decoder.cu", "shim.cu", "sdpa_static.cu"]
 
 
 def _newer(target, deps):
