@@ -71,9 +71,14 @@ class ClockSampler:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "25"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
+            # nvidia-smi needs a moment to come up: wait for its first line so that short timed regions are covered
+            t_end = time.time() + 5.0
+            while not self.samples and time.time() < t_end:
+                time.sleep(0.01)
+            self.samples.clear()
         except OSError:
             self.proc = None
 

@@ -131,7 +131,7 @@ B200_API int b200_fc_w4(const float* d_x, int m, int k, const void* d_w4_packed,
  * mask. scale <= 0 means 1/sqrt(h) (sdpa.cc:99-105). logit_cap > 0 applies
  * cap*tanh(x/cap) before the mask
  * (tflite/delegates/xnnpack/xnnpack_delegate.cc:6639-6678). */
-B200_API size_t b200_sdpa_workspace_bytes(int b, int n, int h, int s_max);
+B200_API size_t b200_sdpa_workspace_bytes(int b, int n, int nkv, int h, int s_max);
 B200_API int b200_sdpa_decode(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale,
                               const float* d_v_scale, const int32_t* d_lengths, const float* d_mask,
                               void* d_out, int b, int n, int nkv, int h, int s_max, int q_dtype, int kv_dtype,

@@ -241,12 +241,20 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // whatever does not depend on it (barrier set-up, TMEM allocation, prefetching
 // constant weights), and calls pdl_wait() before touching anything the
 // predecessor produces (the wait returns once the predecessor grid has completed
-// and its writes are visible). pdl_launch_dependents() lets the successor start;
-// it is only ever called after pdl_wait(), so at most two consecutive kernels of
-// a chain overlap. Both are no-ops for a kernel launched the ordinary way.
+// and its writes are visible). pdl_launch_dependents() lets the successor start.
+// Every kernel of a chain calls pdl_wait(), so completion is transitive: when a
+// kernel's wait returns, every earlier kernel of the chain has completed. That makes
+// it safe to call pdl_launch_dependents() first thing (pdl_enter): several later
+// kernels may then be resident early, but before their own wait they only read
+// constants. Both are no-ops for a kernel launched the ordinary way.
 namespace b200 {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Entry of a kernel with no work to do ahead of its predecessor: release the successor, then wait.
+__device__ __forceinline__ void pdl_enter() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
 
 // B200_PDL=0 turns the attribute off (plain stream order) for A/B measurement.
 bool pdl_enabled();
@@ -264,6 +272,28 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Same, with the grid grouped into thread-block clusters of `cluster_x` CTAs (distributed shared
+// memory between the CTAs of a cluster).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_x,
+                                          cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg;
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = cluster_x;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 }  // namespace b200

@@ -1,6 +1,7 @@
 // Resident Gemma-shaped decoder: weights packed once on the device, KV cache on
 // the device, one decode step = one CUDA graph over the GEMV, attention and glue
 // kernels. C ABI in include/litert_b200.h (b200_decoder_*).
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -177,7 +178,6 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
   const b200_decoder_config& c = d->cfg;
   cudaStream_t s = d->stream;
   const int m_alloc = m_alloc_for(batch);
-  const int qdim = c.n_heads * c.head_dim;
   d->launches = 0;
   auto count = [&](int n = 1) { d->launches += n; };
   GLUE_CUDA(launch_embed(d->tokens.as<int32_t>(), d->embed_table.as<int8_t>(), d->embed_scales.as<float>(), batch,
@@ -318,7 +318,9 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
   for (DevBuf* b : {&d->sc_d, &d->sc_a, &d->sc_f, &d->zp_d, &d->zp_a, &d->zp_f}) DEC_CUDA(b->alloc(sizeof(float) * m_alloc));
   DEC_CUDA(d->zero_ws.alloc(zero_ws_total_bytes()));
   DEC_CUDA(cudaMemsetAsync(d->zero_ws.p, 0, d->zero_ws.bytes, d->stream));
-  DEC_CUDA(d->sdpa_ws.alloc(sdpa_workspace_bytes(B, c.n_heads, c.head_dim, c.max_seq)));
+  size_t sdpa_bytes = 0;  // the chunking depends on the batch: size for the worst batch <= max_batch
+  for (int b = 1; b <= B; ++b) sdpa_bytes = std::max(sdpa_bytes, sdpa_workspace_bytes(b, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq));
+  DEC_CUDA(d->sdpa_ws.alloc(sdpa_bytes));
   DEC_CUDA(d->arg_val.alloc(sizeof(float) * B * kArgmaxParts));
   DEC_CUDA(d->arg_idx.alloc(sizeof(int32_t) * B * kArgmaxParts));
   DEC_CUDA(cudaMemsetAsync(d->positions.p, 0, sizeof(int32_t) * B, d->stream));

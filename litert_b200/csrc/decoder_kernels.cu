@@ -8,6 +8,8 @@
 // TFLite builtins: RMS norm, rotary embedding (x*cos + rotate_half(x)*sin,
 // :150-176), GELU(tanh) * up (:118-146), residual add, hybrid embedding lookup
 // (tflite/kernels/embedding_lookup.cc), first-index argmax.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "decoder_kernels.h"
 #include "quant.cuh"
@@ -17,6 +19,7 @@ namespace b200 {
 namespace {
 
 constexpr int kRowThreads = 256;
+constexpr int kNormThreads = 1024;
 
 // h[b,:] = int8 embedding row * its scale * embed_scale; also attn_len = positions + 1.
 __global__ void __launch_bounds__(kRowThreads) embed_kernel(const int32_t* __restrict__ tokens,
@@ -25,8 +28,7 @@ __global__ void __launch_bounds__(kRowThreads) embed_kernel(const int32_t* __res
                                                             float embed_scale, float* __restrict__ h,
                                                             const int32_t* __restrict__ positions,
                                                             int32_t* __restrict__ attn_len) {
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_enter();
   const int b = blockIdx.x;
   const int tok = tokens[b];
   const float s = row_scales[tok];
@@ -37,7 +39,7 @@ __global__ void __launch_bounds__(kRowThreads) embed_kernel(const int32_t* __res
 }
 
 // h += delta (optional); x = h * rsqrt(mean(h^2) + eps) * gain; quantize x.
-__global__ void __launch_bounds__(kRowThreads) add_norm_quant_kernel(float* __restrict__ h,
+__global__ void __launch_bounds__(kNormThreads) add_norm_quant_kernel(float* __restrict__ h,
                                                                      const float* __restrict__ delta,
                                                                      const float* __restrict__ gain, int d, int d_pad,
                                                                      float eps, int m_alloc,
@@ -46,8 +48,7 @@ __global__ void __launch_bounds__(kRowThreads) add_norm_quant_kernel(float* __re
                                                                      int32_t* __restrict__ zps) {
   extern __shared__ float xs[];
   __shared__ float red[32];
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_enter();
   const int b = blockIdx.x;
   float* hr = h + (size_t)b * d;
   float ss = 0.0f;
@@ -77,25 +78,74 @@ __device__ __forceinline__ float gelu_tanh(float v) {
   return 0.5f * v * (1.0f + tanhf(k0 * (v + 0.044715f * v * v * v)));
 }
 
-// f = gelu_tanh(gate) * up from the fused projection output [b, 2 f]; quantize f.
-__global__ void __launch_bounds__(1024) geglu_quant_kernel(const float* __restrict__ gate_up, int f, int f_pad,
-                                                           int m_alloc, int8_t* __restrict__ q_tiled,
-                                                           float* __restrict__ scales, int32_t* __restrict__ zps) {
+// f = gelu_tanh(gate) * up from the fused projection output [b, 2 f]; quantize f per row.
+// A row (16384 elements at the benchmark's size) is spread over a cluster of kGegluCluster CTAs:
+// each computes its slice into shared memory with its local min / max, the CTAs exchange those
+// through distributed shared memory, and each then quantizes its slice with the row's parameters.
+constexpr int kGegluCluster = 8;
+constexpr int kGegluThreads = 512;
+
+__global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float* __restrict__ gate_up, int f,
+                                                                    int per_cta, int m_alloc,
+                                                                    int8_t* __restrict__ q_tiled,
+                                                                    float* __restrict__ scales,
+                                                                    int32_t* __restrict__ zps) {
+  namespace cg = cooperative_groups;
   extern __shared__ float xs[];
   __shared__ float red[32];
-  pdl_wait();
-  pdl_launch_dependents();
-  const int b = blockIdx.x;
+  __shared__ float s_minmax[2];
+  __shared__ float s_inv;
+  __shared__ int s_zp, s_zero;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int b = blockIdx.x / kGegluCluster;
+  pdl_enter();
   const float* g = gate_up + (size_t)b * 2 * f;
   const float* u = g + f;
+  const int lo = rank * per_cta, hi = min(f, lo + per_cta);
   float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
-  for (int i = threadIdx.x; i < f; i += blockDim.x) {
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     const float v = __fmul_rn(gelu_tanh(g[i]), u[i]);
-    xs[i] = v;
+    xs[i - lo] = v;
     mn = fminf(mn, v);
     mx = fmaxf(mx, v);
   }
-  quantize_smem_row(xs, f, f_pad, b, m_alloc, mn, mx, q_tiled, scales, zps, red);
+  mn = block_reduce(mn, [](float a, float c) { return fminf(a, c); }, mn, red);
+  mx = block_reduce(mx, [](float a, float c) { return fmaxf(a, c); }, mx, red);
+  if (threadIdx.x == 0) {
+    s_minmax[0] = mn;
+    s_minmax[1] = mx;
+  }
+  cluster.sync();
+  if (threadIdx.x == 0) {
+    float rmn = 3.402823466e+38f, rmx = -3.402823466e+38f;
+    for (int r = 0; r < kGegluCluster; ++r) {
+      const float* remote = cluster.map_shared_rank(s_minmax, r);
+      rmn = fminf(rmn, remote[0]);
+      rmx = fmaxf(rmx, remote[1]);
+    }
+    float sf, inv;
+    int zp, zero_row;
+    row_quant_params(rmn, rmx, true, &sf, &inv, &zp, &zero_row);
+    s_zero = zero_row;
+    s_inv = inv;
+    s_zp = zp;
+    if (rank == 0) {
+      scales[b] = sf;
+      zps[b] = zp;
+    }
+  }
+  __syncthreads();
+  const bool zero = s_zero != 0;
+  const float inv = s_inv, zpf = (float)s_zp;
+  for (int k4 = lo + threadIdx.x * 4; k4 < lo + per_cta; k4 += blockDim.x * 4) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (k4 + e < f && !zero) word |= quantize_value(xs[k4 + e - lo], inv, zpf, true) << (8 * e);
+    *reinterpret_cast<uint32_t*>(q_tiled + q_tiled_offset(b, k4, m_alloc)) = word;
+  }
+  cluster.sync();  // no CTA may exit while a neighbour can still read its shared memory
 }
 
 // Rotary embedding of q and k from the fused qkv projection output, and the
@@ -106,8 +156,7 @@ __global__ void rope_cache_kernel(const float* __restrict__ qkv, int heads, int 
                                   float* __restrict__ q_out, void* __restrict__ k_cache, void* __restrict__ v_cache,
                                   float* __restrict__ k_scale, float* __restrict__ v_scale) {
   __shared__ float red[32];
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_enter();
   const int b = blockIdx.x, slot = blockIdx.y, i = threadIdx.x, half = head_dim / 2;
   const int pos = positions[b];
   const float* src = qkv + ((size_t)b * (heads + 2 * kv_heads) + slot) * head_dim;
@@ -162,8 +211,7 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
                                                              int32_t* __restrict__ part_idx) {
   __shared__ float sv[8];
   __shared__ int si[8];
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_enter();
   const int b = blockIdx.y, part = blockIdx.x;
   const int per = (n + parts - 1) / parts;
   const int lo = part * per, hi = min(n, lo + per);
@@ -191,8 +239,7 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
 __global__ void argmax_final_kernel(const float* __restrict__ part_val, const int32_t* __restrict__ part_idx,
                                     int parts, int32_t* __restrict__ next_tokens, int32_t* __restrict__ positions,
                                     int max_seq) {
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_enter();
   const int b = blockIdx.x;
   BestPair best{part_val[(size_t)b * parts], part_idx[(size_t)b * parts]};
   for (int i = threadIdx.x; i < parts; i += 32)
@@ -219,25 +266,28 @@ cudaError_t launch_embed(const int32_t* tokens, const int8_t* table, const float
 cudaError_t launch_add_norm_quant(float* h, const float* delta, const float* gain, int batch, int d, float eps,
                                   int m_alloc, int8_t* q_tiled, float* scales, int32_t* zps, cudaStream_t s) {
   const int d_pad = (d + 127) / 128 * 128;
-  return launch_chained(add_norm_quant_kernel, dim3(batch), dim3(kRowThreads), sizeof(float) * d, s, h, delta, gain, d, d_pad,
+  return launch_chained(add_norm_quant_kernel, dim3(batch), dim3(kNormThreads), sizeof(float) * d, s, h, delta, gain, d, d_pad,
                         eps, m_alloc, q_tiled, scales, zps);
 }
 
 cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_alloc, int8_t* q_tiled, float* scales,
                                int32_t* zps, cudaStream_t s) {
+  const int f_pad = (f + 127) / 128 * 128;
+  // slice per CTA: a multiple of 128 elements so that slices tile the padded row exactly
+  const int per_cta = ((f_pad / 128 + kGegluCluster - 1) / kGegluCluster) * 128;
+  const size_t smem = sizeof(float) * per_cta;
+  if (smem > 160 * 1024) return cudaErrorInvalidValue;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
-  const size_t smem = sizeof(float) * f;
-  if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(geglu_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (!configured[dev] && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(geglu_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  if (smem > 200 * 1024) return cudaErrorInvalidValue;
-  const int f_pad = (f + 127) / 128 * 128;
-  return launch_chained(geglu_quant_kernel, dim3(batch), dim3(1024), smem, s, gate_up, f, f_pad, m_alloc, q_tiled, scales, zps);
+  return launch_chained_cluster(geglu_quant_kernel, dim3(batch * kGegluCluster), dim3(kGegluThreads), smem, kGegluCluster,
+                                s, gate_up, f, per_cta, m_alloc, q_tiled, scales, zps);
 }
 
 cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, float rope_base,

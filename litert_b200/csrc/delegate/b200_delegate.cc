@@ -361,7 +361,7 @@ class DelegateKernel {
       OpRecord& op = *ops_[i];
       if (op.kind == OpKind::kSdpa) {
         for (int t : {op.q, op.k, op.v, op.mask, op.y}) touch(t, i);
-        sdpa = std::max(sdpa, b200_sdpa_workspace_bytes(op.B, op.N, op.H, op.S));
+        sdpa = std::max(sdpa, b200_sdpa_workspace_bytes(op.B, op.N, op.Nkv, op.H, op.S));
       } else {
         const TfLiteTensor& x = ctx->tensors[op.x];
         op.m = static_cast<int>(NumElements(x) / op.kdim);  // fully_connected.cc:502

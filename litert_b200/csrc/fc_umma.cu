@@ -112,9 +112,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
 
+  // Work split over the CTAs: either whole n tiles (no cross-CTA reduction) or equal contiguous
+  // ranges of the flat (n tile, k tile) sequence (stream-K), chosen on the host per shape.
   const long long total = (long long)p.n_tiles * p.k_tiles;
-  const long long t_begin = total * blockIdx.x / gridDim.x;
-  const long long t_end = total * (blockIdx.x + 1) / gridDim.x;
+  const long long t_begin = p.whole_tiles ? ((long long)p.n_tiles * blockIdx.x / gridDim.x) * p.k_tiles
+                                          : total * blockIdx.x / gridDim.x;
+  const long long t_end = p.whole_tiles ? ((long long)p.n_tiles * (blockIdx.x + 1) / gridDim.x) * p.k_tiles
+                                        : total * (blockIdx.x + 1) / gridDim.x;
   const int m_groups_alloc = p.m_alloc / 8;
   const int mg_base = m_base / 8;
 
@@ -123,6 +127,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
     if (lane == 0) {
       // The weights are constants: start streaming them before the kernel that produces the
       // activations has finished (programmatic dependent launch), one ring's worth at most.
+      pdl_launch_dependents();
       uint32_t pre = 0;
       for (long long t = t_begin; t < t_end && pre < (uint32_t)L::kStages; ++t, ++pre) {
         uint8_t* dst = smem + (size_t)pre * L::kStageBytes;
@@ -130,7 +135,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         bulk_g2s(dst, p.w_packed + (size_t)t * kTileBytes, kTileBytes, &full_bar[pre]);
       }
       pdl_wait();               // activations (and the split-K scratch) are now safe to touch
-      pdl_launch_dependents();
       for (uint32_t i = 0; i < pre; ++i) {
         const int kt = (int)((t_begin + i) % p.k_tiles);
         const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
@@ -211,8 +215,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
       const int seg_tiles = (int)(seg_end - t);
       t = seg_end;
       const uint32_t ab = seg & 1u;
-      mbar_wait_bounded(&acc_full[ab], (seg >> 1) & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
-      tc_fence_after();
       const uint32_t taddr = tmem_base + ab * NB + ((uint32_t)(quarter * 32) << 16);
 
       const int n = (int)nt * kTileN + row_in_tile;
@@ -233,6 +235,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
           }
         }
       }
+
+      // the per-channel constants above are in flight while the MMAs of this segment finish
+      mbar_wait_bounded(&acc_full[ab], (seg >> 1) & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
+      tc_fence_after();
 
       const bool partial = seg_tiles != p.k_tiles;
       if (p.debug_flags & 2) {
@@ -284,7 +290,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[ab]);
-        __threadfence();
         named_barrier(1, kEpiThreads);
         if (etid == 0) {
           __threadfence();
@@ -316,6 +321,36 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
   if (warp == 1) tmem_dealloc(tmem_base, L::kTmemCols);
 }
 
+// Chooses the number of CTAs and the split for one launch (measured on B200, batch 1, graph
+// replays): with at least half as many n tiles as SMs, whole n tiles per CTA win (no cross-CTA
+// reduction; CTAs with one tile fewer finish early and the kernel stays HBM-bound); with fewer,
+// one SM per n tile cannot pull more than ~80 GB/s, so the flat (n tile, k tile) sequence is cut
+// into equal ranges over all SMs (stream-K) and the partials are merged by the last arriver.
+int plan_ctas(FcParams* p) {
+  const int sms = device_sm_count();
+  const long long total = (long long)p->n_tiles * p->k_tiles;
+  int mode = -1;  // -1 auto, 0 stream-K, 1 whole tiles
+  if (const char* e = getenv("B200_FC_SPLIT")) mode = atoi(e) ? 0 : 1;  // measurement knob
+  int ctas;
+  if (mode == 1 || (mode < 0 && p->n_tiles * 2 >= sms)) {
+    p->whole_tiles = 1;
+    ctas = p->n_tiles < sms ? p->n_tiles : sms;
+  } else {
+    p->whole_tiles = 0;
+    ctas = sms;
+  }
+  if (p->max_ctas > 0) ctas = p->max_ctas;
+  if (const char* e = getenv("B200_FC_MAX_CTAS")) {  // measurement knob
+    const int v = atoi(e);
+    if (v > 0) ctas = v;
+  }
+  if (ctas > kZeroWsSlots / 2) ctas = kZeroWsSlots / 2;  // two scratch slots per CTA
+  if (p->whole_tiles && ctas > p->n_tiles) ctas = p->n_tiles;
+  if (ctas > total) ctas = (int)total;
+  if (ctas < 1) ctas = 1;
+  return ctas;
+}
+
 template <int NB, int EPI>
 cudaError_t launch_umma_one(const FcParams& p, int m_base, cudaStream_t s) {
   using L = UmmaLayout<NB>;
@@ -329,16 +364,9 @@ cudaError_t launch_umma_one(const FcParams& p, int m_base, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const long long total = (long long)p.n_tiles * p.k_tiles;
-  int ctas = p.max_ctas > 0 ? p.max_ctas : device_sm_count();
-  if (const char* e = getenv("B200_FC_MAX_CTAS")) {  // tuning knob
-    const int v = atoi(e);
-    if (v > 0) ctas = v;
-  }
-  if (ctas > kZeroWsSlots / 2) ctas = kZeroWsSlots / 2;  // two scratch slots per CTA
-  if (ctas > total) ctas = (int)total;
-  if (ctas < 1) ctas = 1;
-  return launch_chained(kernel, dim3(ctas), dim3(kUmmaThreads), (size_t)L::kSmemBytes, s, p, m_base);
+  FcParams q = p;
+  const int ctas = plan_ctas(&q);
+  return launch_chained(kernel, dim3(ctas), dim3(kUmmaThreads), (size_t)L::kSmemBytes, s, q, m_base);
 }
 
 template <int EPI>

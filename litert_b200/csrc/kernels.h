@@ -68,7 +68,8 @@ struct FcParams {
   int32_t* ws_part;   // tcgen05 path: per-CTA partial slots, no initial contents needed
   int32_t* ws_count;
   int* status;
-  int max_ctas;              // 0 = one per SM
+  int max_ctas;              // 0 = chosen per shape
+  int whole_tiles;           // set by the launcher: CTAs own whole n tiles (no split-K)
   int debug_flags;           // measurement only: 1 = skip the MMAs, 2 = skip the epilogue
 };
 
@@ -119,6 +120,6 @@ struct SdpaParams {
   int* status;
 };
 cudaError_t launch_sdpa_decode(const SdpaParams& p, cudaStream_t s);
-size_t sdpa_workspace_bytes(int b, int n, int h, int s_max);
+size_t sdpa_workspace_bytes(int b, int n, int nkv, int h, int s_max);
 
 }  // namespace b200

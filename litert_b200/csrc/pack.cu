@@ -156,8 +156,7 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restr
   __shared__ float s_inv;
   __shared__ int s_zp;
   __shared__ int s_zero;
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_enter();
   const int row = blockIdx.x;
   const float* xr = x + (size_t)row * k;
   float mn = xr[0], mx = xr[0];

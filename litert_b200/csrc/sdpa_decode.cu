@@ -31,7 +31,6 @@ namespace b200 {
 namespace {
 
 constexpr int kWarps = 4;
-constexpr int kTokensPerWarpIter = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 
 enum : int { kKvF16 = 0, kKvI8 = 1, kKvF32 = 2 };
@@ -95,7 +94,9 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 // un-normalised output followed by the running max (log2 domain) and sum.
 __host__ __device__ inline size_t partial_stride(int h) { return (size_t)h + 2; }
 
-template <int KV, int H, bool QF32>
+// GPI = groups of 16 tokens a warp takes per pass (1, 2 or 4): small for short caches, where the
+// kernel is latency-bound and wants as many warps as possible, 4 for long ones.
+template <int KV, int H, bool QF32, int GPI>
 __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaParams p, const int chunk_tokens,
                                                                   const int chunks_max) {
   constexpr int DB = H < 128 ? H : 128;  // head-dim block of the PV step
@@ -103,9 +104,9 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
   constexpr int TPB = DB / 16;           // m16 tiles per block
   constexpr int DPT = DB / 8;            // head-dim elements per thread per block (8 or 16)
   constexpr int KSTEPS = H / 32;         // 16-byte K pieces per thread per row
+  constexpr int kTokensPerWarpIter = 16 * GPI;
 
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_enter();
   const int b = blockIdx.z, kvh = blockIdx.y, chunk = blockIdx.x;
   const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
   const int c0 = chunk * chunk_tokens;
@@ -153,10 +154,10 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
   const float scale_log2 = p.scale * kLog2e;
 
   for (int base = c0 + warp * kTokensPerWarpIter; base < c1; base += kWarps * kTokensPerWarpIter) {
-    // ---- S^T = K Q^T for 4 groups of 16 tokens ----
-    float s[4][4];
+    // ---- S^T = K Q^T for GPI groups of 16 tokens ----
+    float s[GPI][4];
 #pragma unroll
-    for (int gi = 0; gi < 4; ++gi) {
+    for (int gi = 0; gi < GPI; ++gi) {
       s[gi][0] = s[gi][1] = s[gi][2] = s[gi][3] = 0.0f;
       const int ta = base + gi * 16 + g, tb = ta + 8;
       const bool va = ta < c1, vb = tb < c1;
@@ -196,12 +197,13 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
       if (!va) s[gi][0] = s[gi][1] = -CUDART_INF_F;
       if (!vb) s[gi][2] = s[gi][3] = -CUDART_INF_F;
     }
-    // ---- online softmax over these 64 tokens ----
+    // ---- online softmax over these tokens ----
     float mx[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      float v = fmaxf(fmaxf(s[0][e], s[0][e + 2]), fmaxf(s[1][e], s[1][e + 2]));
-      v = fmaxf(v, fmaxf(fmaxf(s[2][e], s[2][e + 2]), fmaxf(s[3][e], s[3][e + 2])));
+      float v = fmaxf(s[0][e], s[0][e + 2]);
+#pragma unroll
+      for (int gi = 1; gi < GPI; ++gi) v = fmaxf(v, fmaxf(s[gi][e], s[gi][e + 2]));
       v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
       v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
       v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
@@ -225,7 +227,7 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
     }
     // ---- O^T += V^T P^T ----
 #pragma unroll
-    for (int gi = 0; gi < 4; ++gi) {
+    for (int gi = 0; gi < GPI; ++gi) {
       float pa0 = exp2f(s[gi][0] - m_use[0]), pa1 = exp2f(s[gi][1] - m_use[1]);
       float pb0 = exp2f(s[gi][2] - m_use[0]), pb1 = exp2f(s[gi][3] - m_use[1]);
       l_run[0] += pa0 + pb0;
@@ -330,8 +332,7 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
 // H threads.
 template <int H, bool QF32>
 __global__ void sdpa_merge_kernel(const SdpaParams p, const int chunk_tokens, const int chunks_max) {
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_enter();
   const int b = blockIdx.y, head = blockIdx.x, d = threadIdx.x;
   const int group = p.n / p.nkv;
   const int kvh = head / group, hg = head % group;
@@ -361,12 +362,11 @@ __global__ void sdpa_merge_kernel(const SdpaParams p, const int chunk_tokens, co
 // hybrid FULLY_CONNECTED applies to the attention output: grid (b), one CTA per sequence over all
 // n*h outputs. Writes the tiled int8 row (+ scale, zero point) and, when p.out is set, the floats.
 template <int H>
-__global__ void __launch_bounds__(256) sdpa_merge_quant_kernel(const SdpaParams p, const int chunk_tokens,
+__global__ void __launch_bounds__(1024) sdpa_merge_quant_kernel(const SdpaParams p, const int chunk_tokens,
                                                               const int chunks_max) {
   extern __shared__ float xs[];
   __shared__ float red[32];
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_enter();
   const int b = blockIdx.x;
   const int group = p.n / p.nkv;
   const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
@@ -451,22 +451,34 @@ __global__ void sdpa_decode_generic_kernel(const SdpaParams p) {
   }
 }
 
-int pick_chunk_tokens(int s_max) {
-  // 256 tokens per warp pass x 4 warps... one pass per warp keeps partial
-  // traffic ~3% of the K/V bytes at 512 tokens per CTA.
-  (void)s_max;
+// Tokens per CTA. The kernel is latency-bound on short caches (one decode step of a small batch
+// reads ~1 MB) and bandwidth-bound on long ragged batches: small chunks give many warps one short
+// pass each, large chunks amortise the partial records. Depends only on (batch, s_max) so that the
+// workspace size can be computed without the lengths.
+int pick_chunk_tokens(int b, int s_max) {
+  const long long tokens = (long long)b * s_max;
+  if (tokens <= 16384) return 64;
+  if (tokens <= 65536) return 128;
+  if (tokens <= 262144) return 256;
   return 512;
 }
 
 template <int KV, int H, bool QF32>
 cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
-  const int chunk_tokens = pick_chunk_tokens(p.s_max);
+  const int chunk_tokens = pick_chunk_tokens(p.b, p.s_max);
   const int chunks_max = (p.s_max + chunk_tokens - 1) / chunk_tokens;
   dim3 grid(chunks_max, p.nkv, p.b);
-  cudaError_t e = launch_chained(sdpa_decode_kernel<KV, H, QF32>, grid, dim3(kWarps * 32), 0, s, p, chunk_tokens, chunks_max);
+  cudaError_t e;
+  if (chunk_tokens == 64) {
+    e = launch_chained(sdpa_decode_kernel<KV, H, QF32, 1>, grid, dim3(kWarps * 32), 0, s, p, chunk_tokens, chunks_max);
+  } else if (chunk_tokens == 128) {
+    e = launch_chained(sdpa_decode_kernel<KV, H, QF32, 2>, grid, dim3(kWarps * 32), 0, s, p, chunk_tokens, chunks_max);
+  } else {
+    e = launch_chained(sdpa_decode_kernel<KV, H, QF32, 4>, grid, dim3(kWarps * 32), 0, s, p, chunk_tokens, chunks_max);
+  }
   if (e != cudaSuccess) return e;
   if (p.q_tiled_out) {
-    return launch_chained(sdpa_merge_quant_kernel<H>, dim3(p.b), dim3(256), sizeof(float) * p.n * H, s, p, chunk_tokens,
+    return launch_chained(sdpa_merge_quant_kernel<H>, dim3(p.b), dim3(1024), sizeof(float) * p.n * H, s, p, chunk_tokens,
                           chunks_max);
   }
   return launch_chained(sdpa_merge_kernel<H, QF32>, dim3(p.n, p.b), dim3(H), 0, s, p, chunk_tokens, chunks_max);
@@ -476,7 +488,7 @@ template <int KV, bool QF32>
 cudaError_t launch_kv(const SdpaParams& p, cudaStream_t s) {
   const int group = p.nkv > 0 ? p.n / p.nkv : 0;
   const bool fast = group >= 1 && group <= 8 && p.n % p.nkv == 0 && p.ws != nullptr &&
-                    p.ws_bytes >= sdpa_workspace_bytes(p.b, p.n, p.h, p.s_max);
+                    p.ws_bytes >= sdpa_workspace_bytes(p.b, p.n, p.nkv, p.h, p.s_max);
   if (p.q_tiled_out && (!fast || !QF32 || (p.h != 256 && p.h != 128 && p.h != 64)))
     return cudaErrorInvalidValue;  // fused output quantization exists on the fast f32-query path only
   if (fast && p.h == 256) return launch_fast<KV, 256, QF32>(p, s);
@@ -494,12 +506,12 @@ cudaError_t launch_kv(const SdpaParams& p, cudaStream_t s) {
 
 }  // namespace
 
-size_t sdpa_workspace_bytes(int b, int n, int h, int s_max) {
+size_t sdpa_workspace_bytes(int b, int n, int nkv, int h, int s_max) {
   (void)n;
-  const int chunk_tokens = pick_chunk_tokens(s_max);
+  const int chunk_tokens = pick_chunk_tokens(b, s_max);
   const int chunks_max = (s_max + chunk_tokens - 1) / chunk_tokens;
-  // [b][nkv <= n][chunks][8][h+2] floats, sized for the worst case nkv = n
-  return (size_t)b * n * chunks_max * 8 * partial_stride(h) * sizeof(float);
+  // [b][nkv][chunks][8 (query heads of the group, padded)][h + 2] floats
+  return (size_t)b * nkv * chunks_max * 8 * partial_stride(h) * sizeof(float);
 }
 
 cudaError_t launch_sdpa_decode(const SdpaParams& p, cudaStream_t s) {

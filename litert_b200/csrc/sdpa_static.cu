@@ -88,7 +88,7 @@ int b200_sdpa_decode_static(const void* d_q, const void* d_k, const void* d_v, c
     return static_fail(B200_ERR_UNSUPPORTED, "b200_sdpa_decode_static: kv dtype %d", kv_dtype);
   if (kv_dtype == B200_DTYPE_I8 && (!d_k_scale || !d_v_scale))
     return static_fail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa_decode_static: int8 cache needs scales");
-  const size_t need = b200::sdpa_workspace_bytes(b, n, h, s_max);
+  const size_t need = b200::sdpa_workspace_bytes(b, n, nkv, h, s_max);
   if (need > kStaticWorkspaceBytes)
     return static_fail(B200_ERR_UNSUPPORTED,
                        "b200_sdpa_decode_static: this shape needs %zu bytes of workspace, the built-in one holds %zu "

@@ -262,9 +262,9 @@ int b200_fc_w4(const float* d_x, int m, int k, const void* d_w4_packed, int n, i
   return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_fc_w4");
 }
 
-size_t b200_sdpa_workspace_bytes(int b, int n, int h, int s_max) {
-  if (b <= 0 || n <= 0 || h <= 0 || s_max <= 0) return 0;
-  return b200::sdpa_workspace_bytes(b, n, h, s_max);
+size_t b200_sdpa_workspace_bytes(int b, int n, int nkv, int h, int s_max) {
+  if (b <= 0 || n <= 0 || nkv <= 0 || h <= 0 || s_max <= 0) return 0;
+  return b200::sdpa_workspace_bytes(b, n, nkv, h, s_max);
 }
 
 int b200_sdpa_decode(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale, const float* d_v_scale,

@@ -53,8 +53,8 @@ class Workspace:
             self.scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
         return self.scratch
 
-    def sdpa_for(self, b, n, h, s_max):
-        need = _lib.load().b200_sdpa_workspace_bytes(b, n, h, s_max)
+    def sdpa_for(self, b, n, nkv, h, s_max):
+        need = _lib.load().b200_sdpa_workspace_bytes(b, n, nkv, h, s_max)
         if self.sdpa is None or self.sdpa.numel() < need:
             self.sdpa = torch.empty(need, dtype=torch.uint8, device=self.device)
         return self.sdpa
@@ -185,7 +185,7 @@ def sdpa_decode(q, k, v, lengths=None, mask=None, scale=None, logit_cap=0.0, k_s
     v_scale = _need(v_scale, torch.float32, "v_scale")
     ws = ws or Workspace(q.device)
     out = torch.empty_like(q)
-    wsb = ws.sdpa_for(b, n, h, s_max)
+    wsb = ws.sdpa_for(b, n, nkv, h, s_max)
     check(lib.b200_sdpa_decode(_ptr(q), _ptr(k), _ptr(v), _ptr(k_scale), _ptr(v_scale), _ptr(lengths), _ptr(mask),
                                _ptr(out), b, n, nkv, h, s_max, _DT[q.dtype], _DT[k.dtype],
                                float(scale) if scale else 0.0, float(logit_cap), _ptr(wsb), wsb.numel(), _stream()))

@@ -47,7 +47,7 @@ def test_size_queries_need_no_gpu():
     assert lib.b200_zero_workspace_bytes() > 256 * 128 * 64 * 4
     assert lib.b200_fc_scratch_bytes(1, 4096) >= 8 * 4096
     assert lib.b200_fc_scratch_bytes(0, 4096) == 0
-    assert lib.b200_sdpa_workspace_bytes(16, 8, 256, 8192) > 0
+    assert lib.b200_sdpa_workspace_bytes(16, 8, 1, 256, 8192) > 0
 
 
 def test_argument_errors_are_reported_not_fatal():

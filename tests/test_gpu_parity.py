@@ -311,7 +311,8 @@ def test_sdpa_config4_full_size_properties(ops, ws):
     assert torch.isfinite(out.float()).all()
     for i in (0, 7, 15):
         alone = ops.sdpa_decode(q[i:i + 1], k[i:i + 1], v[i:i + 1], L[i:i + 1], scale=c["scale"], ws=ws)
-        assert torch.equal(alone, out[i:i + 1])
+        # the split of a sequence into chunks depends on the batch, so the sums associate differently
+        torch.testing.assert_close(alone.float(), out[i:i + 1].float(), rtol=4e-3, atol=2e-4)
     i = int(np.argmin(c["lengths"]))
     n0 = int(c["lengths"][i])
     if 2 * n0 <= 8192:

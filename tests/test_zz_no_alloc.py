@@ -55,9 +55,9 @@ def test_static_workspace_variant_rejects_shapes_beyond_its_limit():
     limit = lib.b200_sdpa_static_workspace_limit()
     assert limit == 8 << 20
     b, n, h, s_max = 64, 8, 256, 8192
-    assert lib.b200_sdpa_workspace_bytes(b, n, h, s_max) > limit
+    assert lib.b200_sdpa_workspace_bytes(b, n, 8, h, s_max) > limit
     x = torch.zeros(16, device="cuda")  # never dereferenced: the size check comes first
     rc = lib.b200_sdpa_decode_static(x.data_ptr(), x.data_ptr(), x.data_ptr(), None, None, None, None, x.data_ptr(), b,
-                                     n, 1, h, s_max, 0, 0, 0.0, 0.0, None)
+                                     n, 8, h, s_max, 0, 0, 0.0, 0.0, None)
     assert rc == 4  # B200_ERR_UNSUPPORTED
     assert b"built-in one holds" in lib.b200_sdpa_static_last_error()
