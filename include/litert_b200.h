@@ -170,10 +170,23 @@ B200_API const char* b200_sdpa_static_last_error(void);
  * the same work is the Interpreter invoking the graph node by node
  * (tflite/core/subgraph.cc:1666-1811).
  *
- * Tensor parallelism: with tp_size > 1 each rank holds the column shard of
- * q/k/v, gate and up (heads and FFN channels split; the single KV head is
- * replicated) and the row shard of o and down; the two partial sums per layer
- * are combined by the all-reduce callback the host installs (NCCL). */
+ * Tensor parallelism (one process per GPU, tp_size <= 8): the config holds the
+ * whole model's sizes; rank r keeps heads [r*n_heads/tp, ...), feed-forward units
+ * [r*d_ff/tp, ...) and LM-head rows [r*vocab/tp, ...): q/gate/up are cut by output
+ * rows, o/down by input columns, a KV head that several ranks share is replicated.
+ * Each rank quantizes its own slice of an activation row, as a graph with one
+ * FULLY_CONNECTED per shard would. The two partial sums per layer and the greedy
+ * winner over the vocabulary shards cross the ranks in one of two ways:
+ *  - b200_decoder_connect_peers: every rank exports its exchange buffer
+ *    (b200_decoder_exchange_handle, a CUDA IPC handle), the host passes all handles
+ *    to every rank, and the kernel that consumes a sum (residual add + RMS norm +
+ *    quantization, or the final token pick) reads the peers' partials itself over
+ *    NVLink after a flag handshake: no collective launch on the path;
+ *  - b200_decoder_init_nccl / b200_decoder_set_allreduce: an all-reduce (NCCL
+ *    loaded at run time, or the caller's own) enqueued between the kernels.
+ * All ranks must make the same calls in the same order. A peer that never arrives
+ * makes the waiting kernel give up after one second; the step then returns
+ * B200_ERR_KERNEL_TIMEOUT. */
 typedef struct b200_decoder b200_decoder;
 
 typedef struct {
@@ -205,6 +218,14 @@ B200_API int b200_decoder_set_layer(b200_decoder* dec, int layer, const b200_dec
 B200_API int b200_decoder_set_embedding(b200_decoder* dec, const int8_t* d_table, const float* d_row_scales,
                                         const float* d_final_norm);
 B200_API int b200_decoder_set_allreduce(b200_decoder* dec, b200_allreduce_fn fn, void* user);
+/* 128-byte NCCL unique id, made on one rank and handed to all (ncclGetUniqueId). */
+B200_API int b200_nccl_unique_id(void* out, size_t bytes);
+/* Joins the communicator of tp_size ranks (ncclCommInitRank) and installs its all-reduce. */
+B200_API int b200_decoder_init_nccl(b200_decoder* dec, const void* unique_id);
+/* CUDA IPC handle (64 bytes) of this rank's exchange buffer. */
+B200_API int b200_decoder_exchange_handle(b200_decoder* dec, void* handle_out, size_t bytes);
+/* handles: tp_size handles, bytes_per_handle apart, in rank order (the own entry is ignored). */
+B200_API int b200_decoder_connect_peers(b200_decoder* dec, const void* handles, size_t bytes_per_handle);
 B200_API int b200_decoder_reset(b200_decoder* dec);
 /* Declares h_positions[i] tokens already cached for sequence i (cache rows never written hold
  * zeros): lets a caller resume from a cache filled elsewhere, or time a step at a given depth. */

@@ -39,6 +39,10 @@ SIGNATURES = {
     "b200_decoder_set_layer": (_i, [_vp, _i, _vp]),
     "b200_decoder_set_embedding": (_i, [_vp, _vp, _vp, _vp]),
     "b200_decoder_set_allreduce": (_i, [_vp, _vp, _vp]),
+    "b200_nccl_unique_id": (_i, [_vp, _sz]),
+    "b200_decoder_init_nccl": (_i, [_vp, _vp]),
+    "b200_decoder_exchange_handle": (_i, [_vp, _vp, _sz]),
+    "b200_decoder_connect_peers": (_i, [_vp, _vp, _sz]),
     "b200_decoder_reset": (_i, [_vp]),
     "b200_decoder_set_positions": (_i, [_vp, _vp, _i]),
     "b200_decoder_step": (_i, [_vp, _vp, _i, _vp, _vp]),

@@ -36,6 +36,7 @@ enum : int {
   kStatusWaitTimeoutFull = 101,   // consumer gave up waiting for a stage
   kStatusWaitTimeoutEmpty = 102,  // producer gave up waiting for a free stage
   kStatusWaitTimeoutTmem = 103,
+  kStatusTimeoutPeer = 104,       // a tensor-parallel peer never signalled its partial result
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

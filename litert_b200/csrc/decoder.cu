@@ -1,6 +1,8 @@
 // Resident Gemma-shaped decoder: weights packed once on the device, KV cache on
 // the device, one decode step = one CUDA graph over the GEMV, attention and glue
 // kernels. C ABI in include/litert_b200.h (b200_decoder_*).
+#include <dlfcn.h>
+
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
@@ -60,13 +62,23 @@ struct b200_decoder {
   DevBuf embed_table, embed_scales, final_norm;
   // activations and scratch
   DevBuf tokens, next_tokens, positions, attn_len;
-  DevBuf h, qkv, q, attn, proj, gate_up, down_out, logits;
+  DevBuf h, qkv, q, attn, gate_up, logits;
+  float *proj = nullptr, *down_out = nullptr;  // inside comm
   DevBuf q_d, q_a, q_f;         // tiled int8 activations for K = d_model, heads*head_dim, d_ff
   DevBuf sc_d, sc_a, sc_f, zp_d, zp_a, zp_f;
   DevBuf zero_ws, sdpa_ws, arg_val, arg_idx;
   int32_t *h_tokens_pinned = nullptr, *h_next_pinned = nullptr;
+  // tensor parallelism: this rank's share of the heads, KV heads, feed-forward units and vocabulary rows
+  int hl = 0, kvl = 0, fl = 0, vl = 0;
+  // Exchange buffer (one cudaMalloc, exported to the peers): flags | step counter | o-projection
+  // partial | down-projection partial | argmax candidate pairs. proj / down_out point into it.
+  DevBuf comm, gather;
+  size_t off_epoch = 0, off_part_a = 0, off_part_b = 0, off_pairs = 0;
+  uint8_t* peer_comm[b200::kMaxTpRanks] = {nullptr};  // peers' exchange buffers mapped here (own entry: comm.p)
+  bool peers_connected = false;
   b200_allreduce_fn allreduce = nullptr;
   void* allreduce_user = nullptr;
+  void* nccl_comm = nullptr;
   cudaGraphExec_t graph[257] = {nullptr};  // indexed by batch
   int launches = 0;
   // per-kernel-class timing of one eager step (b200_decoder_profile_step)
@@ -91,6 +103,50 @@ int dec_fail(int code, const char* what, cudaError_t e = cudaSuccess) {
     cudaError_t _e = (expr);                                        \
     if (_e != cudaSuccess) return dec_fail(B200_ERR_CUDA, #expr, _e); \
   } while (0)
+
+// ---- NCCL, loaded at run time (no link-time dependency) ---------------------------------------
+// Only the four calls the decoder needs, through the library's stable C ABI: the unique id is a
+// 128-byte struct passed by value, data type 7 is float32, reduction 0 is sum.
+struct NcclId {
+  char bytes[128];
+};
+struct NcclApi {
+  void* lib = nullptr;
+  int (*get_unique_id)(NcclId*) = nullptr;
+  int (*comm_init_rank)(void**, int, NcclId, int) = nullptr;
+  int (*all_reduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*comm_destroy)(void*) = nullptr;
+  const char* (*get_error_string)(int) = nullptr;
+};
+NcclApi* nccl_api() {
+  static NcclApi api;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    // a process that already holds an NCCL (PyTorch's, say) gets that one back
+    void* lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (lib) {
+      api.get_unique_id = reinterpret_cast<decltype(api.get_unique_id)>(dlsym(lib, "ncclGetUniqueId"));
+      api.comm_init_rank = reinterpret_cast<decltype(api.comm_init_rank)>(dlsym(lib, "ncclCommInitRank"));
+      api.all_reduce = reinterpret_cast<decltype(api.all_reduce)>(dlsym(lib, "ncclAllReduce"));
+      api.comm_destroy = reinterpret_cast<decltype(api.comm_destroy)>(dlsym(lib, "ncclCommDestroy"));
+      api.get_error_string = reinterpret_cast<decltype(api.get_error_string)>(dlsym(lib, "ncclGetErrorString"));
+      if (api.get_unique_id && api.comm_init_rank && api.all_reduce && api.comm_destroy) api.lib = lib;
+    }
+  }
+  return api.lib ? &api : nullptr;
+}
+int nccl_allreduce_cb(void* user, float* buf, size_t count, void* stream) {
+  NcclApi* api = nccl_api();
+  if (!api || !user) return 1;
+  return api->all_reduce(buf, buf, count, /*ncclFloat32=*/7, /*ncclSum=*/0, user, static_cast<cudaStream_t>(stream));
+}
+void nccl_release(b200_decoder* d) {
+  NcclApi* api = nccl_api();
+  if (api && d->nccl_comm) api->comm_destroy(d->nccl_comm);
+  d->nccl_comm = nullptr;
+}
 
 struct ProfScope {
   b200_decoder* d;
@@ -173,25 +229,59 @@ cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_
   return launch_fc_i8_umma(p, kEpiHybridF32, d->stream);
 }
 
+// The exchange whose sum the next consuming kernel needs: partials at byte offset `off` of every
+// rank's exchange buffer, `seq` = its number within the step.
+TpExchange make_exchange(const b200_decoder* d, int seq, size_t off) {
+  TpExchange x;
+  const b200_decoder_config& c = d->cfg;
+  x.tp_size = c.tp_size;
+  x.tp_rank = c.tp_rank;
+  x.seq = seq;
+  x.per_step = 2 * c.n_layers + 1;
+  for (int j = 0; j < c.tp_size; ++j) {
+    x.partial[j] = reinterpret_cast<const float*>(d->peer_comm[j] + off);
+    x.flag_out[j] = reinterpret_cast<unsigned long long*>(d->peer_comm[j]) + c.tp_rank;
+  }
+  x.flags_in = reinterpret_cast<const unsigned long long*>(d->comm.p);
+  x.step_epoch = reinterpret_cast<const unsigned long long*>(d->comm.as<uint8_t>() + d->off_epoch);
+  x.status = d->zero_ws.as<int>();
+  return x;
+}
+
 // Enqueues one full decode step for `batch` sequences on the decoder's stream.
 int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
   const b200_decoder_config& c = d->cfg;
   cudaStream_t s = d->stream;
   const int m_alloc = m_alloc_for(batch);
+  const bool tp = c.tp_size > 1;
+  const bool fused = tp && d->peers_connected;  // sums fetched from peer memory inside the consuming kernels
+  if (tp && !fused && !d->allreduce)
+    return dec_fail(B200_ERR_INVALID_ARGUMENT, "tensor-parallel decoder: connect the peers or set an all-reduce first");
   d->launches = 0;
   auto count = [&](int n = 1) { d->launches += n; };
+  // sum over ranks of a partial projection output through the caller's collective (not a kernel of ours)
+  auto reduce = [&](float* buf, size_t n) -> int {
+    if (!tp || fused) return B200_OK;
+    ProfScope scope(d, 2);
+    if (d->allreduce(d->allreduce_user, buf, n, s) != 0) return dec_fail(B200_ERR_CUDA, "all-reduce callback failed");
+    return B200_OK;
+  };
+  unsigned long long* epoch = fused ? reinterpret_cast<unsigned long long*>(d->comm.as<uint8_t>() + d->off_epoch) : nullptr;
   GLUE_CUDA(launch_embed(d->tokens.as<int32_t>(), d->embed_table.as<int8_t>(), d->embed_scales.as<float>(), batch,
                         c.d_model, c.embed_scale, d->h.as<float>(), d->positions.as<int32_t>(),
-                        d->attn_len.as<int32_t>(), s));
+                        d->attn_len.as<int32_t>(), epoch, s));
   count();
   for (int l = 0; l < c.n_layers; ++l) {
     Layer& L = *d->layers[l];
-    GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), l == 0 ? nullptr : d->down_out.as<float>(), L.norm1.as<float>(),
-                                   batch, c.d_model, c.rms_eps, m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(),
-                                   d->zp_d.as<int32_t>(), s));
+    {
+      const TpExchange x = fused && l > 0 ? make_exchange(d, 2 * l - 1, d->off_part_b) : TpExchange();
+      GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), l == 0 ? nullptr : d->down_out, L.norm1.as<float>(), batch,
+                                     c.d_model, c.rms_eps, m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(),
+                                     d->zp_d.as<int32_t>(), fused && l > 0 ? &x : nullptr, s));
+    }
     count();
     DEC_CUDA(run_fc(d, L.qkv, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), d->qkv.as<float>()));
-    GLUE_CUDA(launch_rope_cache(d->qkv.as<float>(), batch, c.n_heads, c.n_kv_heads, c.head_dim, c.rope_base,
+    GLUE_CUDA(launch_rope_cache(d->qkv.as<float>(), batch, d->hl, d->kvl, c.head_dim, c.rope_base,
                                d->positions.as<int32_t>(), c.max_seq, d->q.as<float>(), L.k_cache.p, L.v_cache.p,
                                L.k_scale.as<float>(), L.v_scale.as<float>(), c.kv_dtype == B200_DTYPE_I8, s));
     count();
@@ -209,8 +299,8 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
     sp.out_zps = d->zp_a.as<int32_t>();
     sp.m_alloc = m_alloc;
     sp.b = batch;
-    sp.n = c.n_heads;
-    sp.nkv = c.n_kv_heads;
+    sp.n = d->hl;
+    sp.nkv = d->kvl;
     sp.h = c.head_dim;
     sp.s_max = c.max_seq;
     sp.q_dtype = 1;
@@ -224,26 +314,60 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
       DEC_CUDA(launch_sdpa_decode(sp, s));
     }
     count(2);
-    DEC_CUDA(run_fc(d, L.o, batch, d->q_a.as<int8_t>(), d->sc_a.as<float>(), d->zp_a.as<int32_t>(), d->proj.as<float>()));
-    GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->proj.as<float>(), L.norm2.as<float>(), batch, c.d_model,
-                                   c.rms_eps, m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), s));
+    DEC_CUDA(run_fc(d, L.o, batch, d->q_a.as<int8_t>(), d->sc_a.as<float>(), d->zp_a.as<int32_t>(), d->proj));
+    if (int rc = reduce(d->proj, (size_t)batch * c.d_model)) return rc;
+    {
+      const TpExchange x = fused ? make_exchange(d, 2 * l, d->off_part_a) : TpExchange();
+      GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->proj, L.norm2.as<float>(), batch, c.d_model, c.rms_eps,
+                                     m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(),
+                                     fused ? &x : nullptr, s));
+    }
     count();
     DEC_CUDA(run_fc(d, L.gate_up, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(),
                     d->gate_up.as<float>()));
-    GLUE_CUDA(launch_geglu_quant(d->gate_up.as<float>(), batch, c.d_ff, m_alloc, d->q_f.as<int8_t>(), d->sc_f.as<float>(),
+    GLUE_CUDA(launch_geglu_quant(d->gate_up.as<float>(), batch, d->fl, m_alloc, d->q_f.as<int8_t>(), d->sc_f.as<float>(),
                                 d->zp_f.as<int32_t>(), s));
     count();
-    DEC_CUDA(run_fc(d, L.down, batch, d->q_f.as<int8_t>(), d->sc_f.as<float>(), d->zp_f.as<int32_t>(),
-                    d->down_out.as<float>()));
+    DEC_CUDA(run_fc(d, L.down, batch, d->q_f.as<int8_t>(), d->sc_f.as<float>(), d->zp_f.as<int32_t>(), d->down_out));
+    if (int rc = reduce(d->down_out, (size_t)batch * c.d_model)) return rc;
   }
-  GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->down_out.as<float>(), d->final_norm.as<float>(), batch, c.d_model,
-                                 c.rms_eps, m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), s));
+  {
+    const TpExchange x = fused ? make_exchange(d, 2 * c.n_layers - 1, d->off_part_b) : TpExchange();
+    GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->down_out, d->final_norm.as<float>(), batch, c.d_model, c.rms_eps,
+                                   m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(),
+                                   fused ? &x : nullptr, s));
+  }
   count();
   float* logits = d_logits_out ? d_logits_out : d->logits.as<float>();
   DEC_CUDA(run_fc(d, d->lm_head, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), logits));
-  GLUE_CUDA(launch_argmax(logits, batch, c.vocab, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
-                         d->next_tokens.as<int32_t>(), d->positions.as<int32_t>(), c.max_seq, s));
-  count(2);
+  if (!tp) {
+    GLUE_CUDA(launch_argmax(logits, batch, c.vocab, 0, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
+                           d->next_tokens.as<int32_t>(), d->positions.as<int32_t>(), c.max_seq, nullptr, s));
+    count(2);
+    return B200_OK;
+  }
+  // every rank proposes the best of its vocabulary rows; the winner over ranks is the next token
+  const float2* pairs[kMaxTpRanks] = {nullptr};
+  if (fused) {
+    float2* own = reinterpret_cast<float2*>(d->comm.as<uint8_t>() + d->off_pairs);
+    GLUE_CUDA(launch_argmax(logits, batch, d->vl, c.tp_rank * d->vl, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
+                           nullptr, nullptr, c.max_seq, own, s));
+    for (int j = 0; j < c.tp_size; ++j) pairs[j] = reinterpret_cast<const float2*>(d->peer_comm[j] + d->off_pairs);
+    const TpExchange x = make_exchange(d, 2 * c.n_layers, d->off_pairs);
+    GLUE_CUDA(launch_argmax_pick(pairs, c.tp_size, batch, d->next_tokens.as<int32_t>(), d->positions.as<int32_t>(),
+                                c.max_seq, &x, s));
+  } else {
+    // gather through the sum collective: every rank fills its own slot of a zeroed table
+    float2* table = d->gather.as<float2>();
+    DEC_CUDA(cudaMemsetAsync(table, 0, sizeof(float2) * c.tp_size * c.max_batch, s));
+    GLUE_CUDA(launch_argmax(logits, batch, d->vl, c.tp_rank * d->vl, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
+                           nullptr, nullptr, c.max_seq, table + (size_t)c.tp_rank * c.max_batch, s));
+    if (int rc = reduce(reinterpret_cast<float*>(table), (size_t)2 * c.tp_size * c.max_batch)) return rc;
+    for (int j = 0; j < c.tp_size; ++j) pairs[j] = table + (size_t)j * c.max_batch;
+    GLUE_CUDA(launch_argmax_pick(pairs, c.tp_size, batch, d->next_tokens.as<int32_t>(), d->positions.as<int32_t>(),
+                                c.max_seq, nullptr, s));
+  }
+  count(3);
   return B200_OK;
 }
 
@@ -288,18 +412,29 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
     return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_create: bad configuration");
   if (c.kv_dtype != B200_DTYPE_F16 && c.kv_dtype != B200_DTYPE_I8)
     return dec_fail(B200_ERR_UNSUPPORTED, "b200_decoder_create: kv_dtype must be f16 or int8");
-  if (c.tp_size > 1) return dec_fail(B200_ERR_UNSUPPORTED, "b200_decoder_create: tensor parallelism is not built yet");
+  const int T = c.tp_size < 1 ? 1 : c.tp_size;
+  if (T > kMaxTpRanks || c.tp_rank < 0 || c.tp_rank >= T)
+    return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_create: tp_size must be 1..8 and tp_rank below it");
+  if (c.n_heads % T != 0 || c.d_ff % T != 0 || c.vocab % T != 0 || (c.n_kv_heads % T != 0 && T % c.n_kv_heads != 0) ||
+      (T > 1 && c.vocab >= (1 << 24)))
+    return dec_fail(B200_ERR_UNSUPPORTED,
+                    "b200_decoder_create: heads, d_ff and vocab must divide by tp_size (KV heads divide or are replicated)");
   auto d = std::make_unique<b200_decoder>();
   d->cfg = c;
-  if (d->cfg.tp_size < 1) d->cfg.tp_size = 1;
+  d->cfg.tp_size = T;
+  if (T == 1) d->cfg.tp_rank = 0;
+  d->hl = c.n_heads / T;
+  d->kvl = c.n_kv_heads % T == 0 ? c.n_kv_heads / T : 1;
+  d->fl = c.d_ff / T;
+  d->vl = c.vocab / T;
   if (stream) {
     d->stream = static_cast<cudaStream_t>(stream);
   } else {
     DEC_CUDA(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
     d->own_stream = true;
   }
-  const int B = c.max_batch, m_alloc = m_alloc_for(B), qdim = c.n_heads * c.head_dim;
-  const int kvdim = c.n_kv_heads * c.head_dim;
+  const int B = c.max_batch, m_alloc = m_alloc_for(B), qdim = d->hl * c.head_dim;
+  const int kvdim = d->kvl * c.head_dim;
   DEC_CUDA(d->tokens.alloc(sizeof(int32_t) * B));
   DEC_CUDA(d->next_tokens.alloc(sizeof(int32_t) * B));
   DEC_CUDA(d->positions.alloc(sizeof(int32_t) * B));
@@ -308,18 +443,32 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
   DEC_CUDA(d->qkv.alloc(sizeof(float) * B * (qdim + 2 * kvdim)));
   DEC_CUDA(d->q.alloc(sizeof(float) * B * qdim));
   DEC_CUDA(d->attn.alloc(sizeof(float) * B * qdim));
-  DEC_CUDA(d->proj.alloc(sizeof(float) * B * c.d_model));
-  DEC_CUDA(d->gate_up.alloc(sizeof(float) * (size_t)B * 2 * c.d_ff));
-  DEC_CUDA(d->down_out.alloc(sizeof(float) * B * c.d_model));
-  DEC_CUDA(d->logits.alloc(sizeof(float) * (size_t)B * c.vocab));
+  DEC_CUDA(d->gate_up.alloc(sizeof(float) * (size_t)B * 2 * d->fl));
+  DEC_CUDA(d->logits.alloc(sizeof(float) * (size_t)B * d->vl));
+  {
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    const size_t part = up(sizeof(float) * (size_t)B * c.d_model);
+    d->off_epoch = 256;
+    d->off_part_a = 512;
+    d->off_part_b = d->off_part_a + part;
+    d->off_pairs = d->off_part_b + part;
+    const size_t total = d->off_pairs + up(sizeof(float2) * B);
+    // whole 2 MiB pages, so that the exported allocation holds nothing else
+    DEC_CUDA(d->comm.alloc((total + (2u << 20) - 1) / (2u << 20) * (2u << 20)));
+    DEC_CUDA(cudaMemsetAsync(d->comm.p, 0, d->comm.bytes, d->stream));
+    d->proj = reinterpret_cast<float*>(d->comm.as<uint8_t>() + d->off_part_a);
+    d->down_out = reinterpret_cast<float*>(d->comm.as<uint8_t>() + d->off_part_b);
+    d->peer_comm[d->cfg.tp_rank] = d->comm.as<uint8_t>();
+    if (T > 1) DEC_CUDA(d->gather.alloc(sizeof(float2) * T * B));
+  }
   DEC_CUDA(d->q_d.alloc(q_tiled_bytes(m_alloc, c.d_model)));
   DEC_CUDA(d->q_a.alloc(q_tiled_bytes(m_alloc, qdim)));
-  DEC_CUDA(d->q_f.alloc(q_tiled_bytes(m_alloc, c.d_ff)));
+  DEC_CUDA(d->q_f.alloc(q_tiled_bytes(m_alloc, d->fl)));
   for (DevBuf* b : {&d->sc_d, &d->sc_a, &d->sc_f, &d->zp_d, &d->zp_a, &d->zp_f}) DEC_CUDA(b->alloc(sizeof(float) * m_alloc));
   DEC_CUDA(d->zero_ws.alloc(zero_ws_total_bytes()));
   DEC_CUDA(cudaMemsetAsync(d->zero_ws.p, 0, d->zero_ws.bytes, d->stream));
   size_t sdpa_bytes = 0;  // the chunking depends on the batch: size for the worst batch <= max_batch
-  for (int b = 1; b <= B; ++b) sdpa_bytes = std::max(sdpa_bytes, sdpa_workspace_bytes(b, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq));
+  for (int b = 1; b <= B; ++b) sdpa_bytes = std::max(sdpa_bytes, sdpa_workspace_bytes(b, d->hl, d->kvl, c.head_dim, c.max_seq));
   DEC_CUDA(d->sdpa_ws.alloc(sdpa_bytes));
   DEC_CUDA(d->arg_val.alloc(sizeof(float) * B * kArgmaxParts));
   DEC_CUDA(d->arg_idx.alloc(sizeof(int32_t) * B * kArgmaxParts));
@@ -336,8 +485,8 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
     DEC_CUDA(cudaMemsetAsync(L.k_cache.p, 0, kv_bytes, d->stream));
     DEC_CUDA(cudaMemsetAsync(L.v_cache.p, 0, kv_bytes, d->stream));
     if (c.kv_dtype == B200_DTYPE_I8) {
-      DEC_CUDA(L.k_scale.alloc(sizeof(float) * (size_t)B * c.max_seq * c.n_kv_heads));
-      DEC_CUDA(L.v_scale.alloc(sizeof(float) * (size_t)B * c.max_seq * c.n_kv_heads));
+      DEC_CUDA(L.k_scale.alloc(sizeof(float) * (size_t)B * c.max_seq * d->kvl));
+      DEC_CUDA(L.v_scale.alloc(sizeof(float) * (size_t)B * c.max_seq * d->kvl));
     }
     DEC_CUDA(L.norm1.alloc(sizeof(float) * c.d_model));
     DEC_CUDA(L.norm2.alloc(sizeof(float) * c.d_model));
@@ -353,6 +502,10 @@ void b200_decoder_destroy(b200_decoder* d) {
   cudaStreamSynchronize(d->stream);
   for (auto& g : d->graph)
     if (g) cudaGraphExecDestroy(g);
+  if (d->peers_connected)
+    for (int j = 0; j < d->cfg.tp_size; ++j)
+      if (j != d->cfg.tp_rank && d->peer_comm[j]) cudaIpcCloseMemHandle(d->peer_comm[j]);
+  nccl_release(d);
   if (d->h_tokens_pinned) cudaFreeHost(d->h_tokens_pinned);
   if (d->h_next_pinned) cudaFreeHost(d->h_next_pinned);
   if (d->own_stream) cudaStreamDestroy(d->stream);
@@ -362,15 +515,15 @@ void b200_decoder_destroy(b200_decoder* d) {
 int b200_decoder_set_layer(b200_decoder* d, int layer, const b200_decoder_layer_weights* w) {
   if (!d || !w || layer < 0 || layer >= d->cfg.n_layers) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_set_layer: bad argument");
   const b200_decoder_config& c = d->cfg;
-  const int qdim = c.n_heads * c.head_dim, kvdim = c.n_kv_heads * c.head_dim;
+  const int qdim = d->hl * c.head_dim, kvdim = d->kvl * c.head_dim;  // this rank's shard
   Layer& L = *d->layers[layer];
   int rc = build_projection(d, &L.qkv, c.d_model, {w->wq, w->wk, w->wv}, {w->sq, w->sk, w->sv}, {qdim, kvdim, kvdim});
   if (rc) return rc;
   rc = build_projection(d, &L.o, qdim, {w->wo}, {w->so}, {c.d_model});
   if (rc) return rc;
-  rc = build_projection(d, &L.gate_up, c.d_model, {w->wgate, w->wup}, {w->sgate, w->sup}, {c.d_ff, c.d_ff});
+  rc = build_projection(d, &L.gate_up, c.d_model, {w->wgate, w->wup}, {w->sgate, w->sup}, {d->fl, d->fl});
   if (rc) return rc;
-  rc = build_projection(d, &L.down, c.d_ff, {w->wdown}, {w->sdown}, {c.d_model});
+  rc = build_projection(d, &L.down, d->fl, {w->wdown}, {w->sdown}, {c.d_model});
   if (rc) return rc;
   DEC_CUDA(cudaMemcpyAsync(L.norm1.p, w->norm1, sizeof(float) * c.d_model, cudaMemcpyDeviceToDevice, d->stream));
   DEC_CUDA(cudaMemcpyAsync(L.norm2.p, w->norm2, sizeof(float) * c.d_model, cudaMemcpyDeviceToDevice, d->stream));
@@ -386,13 +539,73 @@ int b200_decoder_set_embedding(b200_decoder* d, const int8_t* table, const float
   DEC_CUDA(cudaMemcpyAsync(d->embed_table.p, table, (size_t)c.vocab * c.d_model, cudaMemcpyDeviceToDevice, d->stream));
   DEC_CUDA(cudaMemcpyAsync(d->embed_scales.p, row_scales, sizeof(float) * c.vocab, cudaMemcpyDeviceToDevice, d->stream));
   DEC_CUDA(cudaMemcpyAsync(d->final_norm.p, final_norm, sizeof(float) * c.d_model, cudaMemcpyDeviceToDevice, d->stream));
-  return build_projection(d, &d->lm_head, c.d_model, {table}, {row_scales}, {c.vocab});
+  const size_t first = (size_t)c.tp_rank * d->vl;  // this rank's rows of the tied LM head
+  return build_projection(d, &d->lm_head, c.d_model, {table + first * c.d_model}, {row_scales + first}, {d->vl});
 }
 
 int b200_decoder_set_allreduce(b200_decoder* d, b200_allreduce_fn fn, void* user) {
   if (!d) return dec_fail(B200_ERR_INVALID_ARGUMENT, "null decoder");
   d->allreduce = fn;
   d->allreduce_user = user;
+  return B200_OK;
+}
+
+int b200_nccl_unique_id(void* out, size_t bytes) {
+  NcclApi* api = nccl_api();
+  if (!api) return dec_fail(B200_ERR_UNSUPPORTED, "b200_nccl_unique_id: libnccl.so.2 could not be loaded");
+  if (!out || bytes < sizeof(NcclId)) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_nccl_unique_id: need 128 bytes");
+  if (api->get_unique_id(static_cast<NcclId*>(out)) != 0) return dec_fail(B200_ERR_CUDA, "ncclGetUniqueId failed");
+  return B200_OK;
+}
+
+int b200_decoder_init_nccl(b200_decoder* d, const void* unique_id) {
+  if (!d || !unique_id) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_init_nccl: null argument");
+  NcclApi* api = nccl_api();
+  if (!api) return dec_fail(B200_ERR_UNSUPPORTED, "b200_decoder_init_nccl: libnccl.so.2 could not be loaded");
+  NcclId id;
+  memcpy(&id, unique_id, sizeof(id));
+  nccl_release(d);
+  const int rc = api->comm_init_rank(&d->nccl_comm, d->cfg.tp_size, id, d->cfg.tp_rank);
+  if (rc != 0) {
+    snprintf(g_dec_error, sizeof(g_dec_error), "ncclCommInitRank: %s", api->get_error_string ? api->get_error_string(rc) : "failed");
+    return B200_ERR_CUDA;
+  }
+  d->allreduce = nccl_allreduce_cb;
+  d->allreduce_user = d->nccl_comm;
+  return B200_OK;
+}
+
+int b200_decoder_exchange_handle(b200_decoder* d, void* handle_out, size_t bytes) {
+  if (!d || !handle_out || bytes < sizeof(cudaIpcMemHandle_t))
+    return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_exchange_handle: need 64 bytes");
+  cudaIpcMemHandle_t h;
+  DEC_CUDA(cudaIpcGetMemHandle(&h, d->comm.p));
+  memcpy(handle_out, &h, sizeof(h));
+  return B200_OK;
+}
+
+int b200_decoder_connect_peers(b200_decoder* d, const void* handles, size_t bytes_per_handle) {
+  if (!d || !handles || bytes_per_handle < sizeof(cudaIpcMemHandle_t))
+    return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_connect_peers: bad argument");
+  if (d->peers_connected) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_connect_peers: already connected");
+  const int T = d->cfg.tp_size;
+  for (int j = 0; j < T; ++j) {
+    if (j == d->cfg.tp_rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const uint8_t*>(handles) + (size_t)j * bytes_per_handle, sizeof(h));
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      for (int i = 0; i < j; ++i)
+        if (i != d->cfg.tp_rank && d->peer_comm[i]) {
+          cudaIpcCloseMemHandle(d->peer_comm[i]);
+          d->peer_comm[i] = nullptr;
+        }
+      return dec_fail(B200_ERR_CUDA, "cudaIpcOpenMemHandle (peer exchange buffer)", e);
+    }
+    d->peer_comm[j] = static_cast<uint8_t*>(p);
+  }
+  d->peers_connected = T > 1;
   return B200_OK;
 }
 

@@ -21,14 +21,55 @@ namespace {
 constexpr int kRowThreads = 256;
 constexpr int kNormThreads = 1024;
 
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ float ld_peer(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Handshake of one exchange (see TpExchange). Called by every thread of the CTA after the
+// predecessor kernel has completed; CTA 0 signals, every CTA waits. A wait that runs out
+// (one second) records kStatusTimeoutPeer and lets the kernel finish with whatever is there.
+__device__ __forceinline__ void tp_handshake(const TpExchange& x, bool signaller) {
+  const unsigned long long epoch = *x.step_epoch * (unsigned long long)x.per_step + (unsigned long long)x.seq + 1ull;
+  const int j = threadIdx.x;
+  if (j < x.tp_size && j != x.tp_rank) {
+    if (signaller) {
+      __threadfence_system();
+      st_release_sys(x.flag_out[j], epoch);
+    }
+    // after one wait has run out the status stays set and later waits give up at once
+    const unsigned long long t0 = global_timer_ns();
+    while (ld_acquire_sys(x.flags_in + j) < epoch) {
+      if (*reinterpret_cast<volatile int*>(x.status) != 0) break;
+      if (global_timer_ns() - t0 > kWaitBudgetNs) {
+        atomicCAS(x.status, 0, kStatusTimeoutPeer);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+}
+
 // h[b,:] = int8 embedding row * its scale * embed_scale; also attn_len = positions + 1.
 __global__ void __launch_bounds__(kRowThreads) embed_kernel(const int32_t* __restrict__ tokens,
                                                             const int8_t* __restrict__ table,
                                                             const float* __restrict__ row_scales, int d,
                                                             float embed_scale, float* __restrict__ h,
                                                             const int32_t* __restrict__ positions,
-                                                            int32_t* __restrict__ attn_len) {
+                                                            int32_t* __restrict__ attn_len,
+                                                            unsigned long long* __restrict__ step_epoch) {
   pdl_enter();
+  if (step_epoch && blockIdx.x == 0 && threadIdx.x == 0) *step_epoch += 1ull;
   const int b = blockIdx.x;
   const int tok = tokens[b];
   const float s = row_scales[tok];
@@ -45,16 +86,28 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_kernel(float* __r
                                                                      float eps, int m_alloc,
                                                                      int8_t* __restrict__ q_tiled,
                                                                      float* __restrict__ scales,
-                                                                     int32_t* __restrict__ zps) {
+                                                                     int32_t* __restrict__ zps, TpExchange xch) {
   extern __shared__ float xs[];
   __shared__ float red[32];
   pdl_enter();
   const int b = blockIdx.x;
+  const bool exchange = xch.tp_size > 1;
+  if (exchange) tp_handshake(xch, blockIdx.x == 0);
   float* hr = h + (size_t)b * d;
   float ss = 0.0f;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = hr[i];
-    if (delta) {
+    if (exchange) {
+      // sum of the ranks' partial outputs, in rank order on every rank
+      float sum = 0.0f;
+      for (int j = 0; j < xch.tp_size; ++j) {
+        const float* pj = xch.partial[j] + (size_t)b * d + i;
+        const float t = j == xch.tp_rank ? *pj : ld_peer(pj);
+        sum = j == 0 ? t : __fadd_rn(sum, t);
+      }
+      v = __fadd_rn(v, sum);
+      hr[i] = v;
+    } else if (delta) {
       v = __fadd_rn(v, delta[(size_t)b * d + i]);
       hr[i] = v;
     }
@@ -85,7 +138,7 @@ __device__ __forceinline__ float gelu_tanh(float v) {
 constexpr int kGegluCluster = 8;
 constexpr int kGegluThreads = 512;
 
-__global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float* __restrict__ gate_up, int f,
+__global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float* __restrict__ gate_up, int f, int f_pad,
                                                                     int per_cta, int m_alloc,
                                                                     int8_t* __restrict__ q_tiled,
                                                                     float* __restrict__ scales,
@@ -138,7 +191,8 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
   __syncthreads();
   const bool zero = s_zero != 0;
   const float inv = s_inv, zpf = (float)s_zp;
-  for (int k4 = lo + threadIdx.x * 4; k4 < lo + per_cta; k4 += blockDim.x * 4) {
+  const int k_end = min(lo + per_cta, f_pad);  // the tiled row ends at the padded length
+  for (int k4 = lo + threadIdx.x * 4; k4 < k_end; k4 += blockDim.x * 4) {
     uint32_t word = 0;
 #pragma unroll
     for (int e = 0; e < 4; ++e)
@@ -237,8 +291,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
 
 // grid b, 32 threads: final reduction; also advances the sequence position.
 __global__ void argmax_final_kernel(const float* __restrict__ part_val, const int32_t* __restrict__ part_idx,
-                                    int parts, int32_t* __restrict__ next_tokens, int32_t* __restrict__ positions,
-                                    int max_seq) {
+                                    int parts, int idx_offset, int32_t* __restrict__ next_tokens,
+                                    int32_t* __restrict__ positions, int max_seq, float2* __restrict__ pair_out) {
   pdl_enter();
   const int b = blockIdx.x;
   BestPair best{part_val[(size_t)b * parts], part_idx[(size_t)b * parts]};
@@ -250,6 +304,33 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val, const in
     best = better(best, other);
   }
   if (threadIdx.x == 0) {
+    if (pair_out) {
+      pair_out[b] = make_float2(best.v, (float)(best.i + idx_offset));  // exact below 2^24
+    } else {
+      next_tokens[b] = best.i + idx_offset;
+      if (positions[b] < max_seq) positions[b] += 1;
+    }
+  }
+}
+
+struct PairTable {
+  const float2* p[kMaxTpRanks];
+};
+
+// grid b, 32 threads: winner over the ranks' candidates (larger value, then lower index).
+__global__ void argmax_pick_kernel(PairTable pairs, int tp_size, int32_t* __restrict__ next_tokens,
+                                   int32_t* __restrict__ positions, int max_seq, TpExchange xch) {
+  pdl_enter();
+  if (xch.tp_size > 1) tp_handshake(xch, blockIdx.x == 0);
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) {
+    BestPair best{-3.402823466e+38f, 0x7fffffff};
+    for (int j = 0; j < tp_size; ++j) {
+      const float* pj = reinterpret_cast<const float*>(pairs.p[j] + b);
+      const float v = ld_peer(pj), fi = ld_peer(pj + 1);
+      const BestPair cand{v, (int)fi};
+      best = j == 0 ? cand : better(best, cand);
+    }
     next_tokens[b] = best.i;
     if (positions[b] < max_seq) positions[b] += 1;
   }
@@ -258,16 +339,19 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val, const in
 }  // namespace
 
 cudaError_t launch_embed(const int32_t* tokens, const int8_t* table, const float* row_scales, int batch, int d,
-                         float embed_scale, float* h, const int32_t* positions, int32_t* attn_len, cudaStream_t s) {
+                         float embed_scale, float* h, const int32_t* positions, int32_t* attn_len,
+                         unsigned long long* step_epoch, cudaStream_t s) {
   return launch_chained(embed_kernel, dim3(batch), dim3(kRowThreads), 0, s, tokens, table, row_scales, d, embed_scale, h, positions,
-                        attn_len);
+                        attn_len, step_epoch);
 }
 
 cudaError_t launch_add_norm_quant(float* h, const float* delta, const float* gain, int batch, int d, float eps,
-                                  int m_alloc, int8_t* q_tiled, float* scales, int32_t* zps, cudaStream_t s) {
+                                  int m_alloc, int8_t* q_tiled, float* scales, int32_t* zps, const TpExchange* xch,
+                                  cudaStream_t s) {
   const int d_pad = (d + 127) / 128 * 128;
+  const TpExchange x = xch ? *xch : TpExchange();
   return launch_chained(add_norm_quant_kernel, dim3(batch), dim3(kNormThreads), sizeof(float) * d, s, h, delta, gain, d, d_pad,
-                        eps, m_alloc, q_tiled, scales, zps);
+                        eps, m_alloc, q_tiled, scales, zps, x);
 }
 
 cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_alloc, int8_t* q_tiled, float* scales,
@@ -287,7 +371,7 @@ cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_all
     configured[dev] = true;
   }
   return launch_chained_cluster(geglu_quant_kernel, dim3(batch * kGegluCluster), dim3(kGegluThreads), smem, kGegluCluster,
-                                s, gate_up, f, per_cta, m_alloc, q_tiled, scales, zps);
+                                s, gate_up, f, f_pad, per_cta, m_alloc, q_tiled, scales, zps);
 }
 
 cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, float rope_base,
@@ -302,13 +386,22 @@ cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_hea
                         positions, max_seq, q_out, k_cache, v_cache, k_scale, v_scale);
 }
 
-cudaError_t launch_argmax(const float* logits, int batch, int n, float* part_val, int32_t* part_idx,
-                          int32_t* next_tokens, int32_t* positions, int max_seq, cudaStream_t s) {
+cudaError_t launch_argmax(const float* logits, int batch, int n, int idx_offset, float* part_val, int32_t* part_idx,
+                          int32_t* next_tokens, int32_t* positions, int max_seq, float2* pair_out, cudaStream_t s) {
   cudaError_t e = launch_chained(argmax_partial_kernel, dim3(kArgmaxParts, batch), dim3(256), 0, s, logits, n, (int)kArgmaxParts,
                                  part_val, part_idx);
   if (e != cudaSuccess) return e;
   return launch_chained(argmax_final_kernel, dim3(batch), dim3(32), 0, s, (const float*)part_val, (const int32_t*)part_idx,
-                        (int)kArgmaxParts, next_tokens, positions, max_seq);
+                        (int)kArgmaxParts, idx_offset, next_tokens, positions, max_seq, pair_out);
+}
+
+cudaError_t launch_argmax_pick(const float2* const* pairs, int tp_size, int batch, int32_t* next_tokens,
+                               int32_t* positions, int max_seq, const TpExchange* xch, cudaStream_t s) {
+  if (tp_size < 1 || tp_size > kMaxTpRanks) return cudaErrorInvalidValue;
+  PairTable t;
+  for (int j = 0; j < kMaxTpRanks; ++j) t.p[j] = j < tp_size ? pairs[j] : nullptr;
+  const TpExchange x = xch ? *xch : TpExchange();
+  return launch_chained(argmax_pick_kernel, dim3(batch), dim3(32), 0, s, t, tp_size, next_tokens, positions, max_seq, x);
 }
 
 }  // namespace b200

@@ -7,17 +7,47 @@
 namespace b200 {
 
 constexpr int kArgmaxParts = 128;
+constexpr int kMaxTpRanks = 8;
 
+// One cross-rank exchange of a tensor-parallel step, done inside the kernel that consumes the sum.
+// Every rank keeps its partial result in its own exchange buffer; the consuming kernel tells each
+// peer "my partial number `epoch` is complete" with a release store into the peer's flag array,
+// waits (bounded) until every peer's flag in its own array has reached `epoch`, then reads the
+// peers' partials straight from their memory over NVLink and adds them in rank order.
+// epoch = *step_epoch * per_step + seq + 1: the step counter lives on the device and is advanced
+// by the first kernel of each step, so that a captured graph can be replayed.
+struct TpExchange {
+  int tp_size = 1, tp_rank = 0;
+  int seq = 0, per_step = 1;
+  const float* partial[kMaxTpRanks] = {nullptr};        // rank j's partial of this exchange (own entry: local)
+  unsigned long long* flag_out[kMaxTpRanks] = {nullptr};  // slot [tp_rank] of rank j's flag array
+  const unsigned long long* flags_in = nullptr;          // this rank's flag array [kMaxTpRanks]
+  const unsigned long long* step_epoch = nullptr;
+  int* status = nullptr;
+};
+
+// step_epoch (optional): device counter advanced by one, the clock of the cross-rank exchanges.
 cudaError_t launch_embed(const int32_t* tokens, const int8_t* table, const float* row_scales, int batch, int d,
-                         float embed_scale, float* h, const int32_t* positions, int32_t* attn_len, cudaStream_t s);
+                         float embed_scale, float* h, const int32_t* positions, int32_t* attn_len,
+                         unsigned long long* step_epoch, cudaStream_t s);
+// h += delta; x = rms_norm(h) * gain; quantize x. With xch (tp_size > 1) delta is the sum over ranks of
+// xch->partial[j], fetched inside the kernel.
 cudaError_t launch_add_norm_quant(float* h, const float* delta, const float* gain, int batch, int d, float eps,
-                                  int m_alloc, int8_t* q_tiled, float* scales, int32_t* zps, cudaStream_t s);
+                                  int m_alloc, int8_t* q_tiled, float* scales, int32_t* zps, const TpExchange* xch,
+                                  cudaStream_t s);
 cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_alloc, int8_t* q_tiled, float* scales,
                                int32_t* zps, cudaStream_t s);
 cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, float rope_base,
                               const int32_t* positions, int max_seq, float* q_out, void* k_cache, void* v_cache,
                               float* k_scale, float* v_scale, int kv_int8, cudaStream_t s);
-cudaError_t launch_argmax(const float* logits, int batch, int n, float* part_val, int32_t* part_idx,
-                          int32_t* next_tokens, int32_t* positions, int max_seq, cudaStream_t s);
+// First-index argmax of each row; advances positions. idx_offset is added to the winning column.
+// With pair_out the winner goes to pair_out[b] = {value, index as float} instead, and neither
+// next_tokens nor positions change (launch_argmax_pick finishes the job across ranks).
+cudaError_t launch_argmax(const float* logits, int batch, int n, int idx_offset, float* part_val, int32_t* part_idx,
+                          int32_t* next_tokens, int32_t* positions, int max_seq, float2* pair_out, cudaStream_t s);
+// Picks the best of tp_size candidate pairs per row. pairs[j] = rank j's float2[batch]; when xch is given
+// they are peers' memory and the exchange handshake runs first, otherwise they are local.
+cudaError_t launch_argmax_pick(const float2* const* pairs, int tp_size, int batch, int32_t* next_tokens,
+                               int32_t* positions, int max_seq, const TpExchange* xch, cudaStream_t s);
 
 }  // namespace b200

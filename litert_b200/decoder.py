@@ -48,17 +48,49 @@ def make_weights(cfg, seed=1005, device="cuda"):
     return dict(layers=layers, embed=w(cfg["vocab"], d), embed_scales=s(cfg["vocab"]), final_norm=gain(d))
 
 
+def shard_weights(cfg, weights, tp_size, rank):
+    """This rank's slices of the whole model's weights (tensors of make_weights' layout): q, gate and up by
+    output rows, o and down by input columns, k/v by KV head (replicated when ranks share a head). The
+    embedding table stays whole: the decoder takes its LM-head rows itself."""
+    H, KVH, HD, F = cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"]
+    if H % tp_size or F % tp_size or cfg["vocab"] % tp_size or (KVH % tp_size and tp_size % KVH):
+        raise ValueError("heads, d_ff and vocab must divide by tp_size")
+    hl, fl = H // tp_size, F // tp_size
+    if KVH % tp_size == 0:
+        kvl, kv0 = KVH // tp_size, rank * (KVH // tp_size)
+    else:
+        kvl, kv0 = 1, rank // (tp_size // KVH)
+    q0, q1, k0, k1, f0, f1 = rank * hl * HD, (rank + 1) * hl * HD, kv0 * HD, (kv0 + kvl) * HD, rank * fl, (rank + 1) * fl
+    layers = []
+    for lw in weights["layers"]:
+        layers.append({
+            "wq": lw["wq"][q0:q1].contiguous(), "sq": lw["sq"][q0:q1].contiguous(),
+            "wk": lw["wk"][k0:k1].contiguous(), "sk": lw["sk"][k0:k1].contiguous(),
+            "wv": lw["wv"][k0:k1].contiguous(), "sv": lw["sv"][k0:k1].contiguous(),
+            "wo": lw["wo"][:, q0:q1].contiguous(), "so": lw["so"],
+            "wgate": lw["wgate"][f0:f1].contiguous(), "sgate": lw["sgate"][f0:f1].contiguous(),
+            "wup": lw["wup"][f0:f1].contiguous(), "sup": lw["sup"][f0:f1].contiguous(),
+            "wdown": lw["wdown"][:, f0:f1].contiguous(), "sdown": lw["sdown"],
+            "norm1": lw["norm1"], "norm2": lw["norm2"]})
+    return {"layers": layers, "embed": weights["embed"], "embed_scales": weights["embed_scales"],
+            "final_norm": weights["final_norm"]}
+
+
 class Decoder:
     def __init__(self, cfg, max_seq, max_batch, weights=None, kv_dtype="f16", rms_eps=1e-6, rope_base=10000.0,
-                 seed=1005, device="cuda", keep_weights=False):
+                 seed=1005, device="cuda", keep_weights=False, tp_size=1, tp_rank=0):
+        """cfg holds the whole model's sizes. With tp_size > 1 this is rank tp_rank's shard: `weights` (whole
+        model, default: seeded random) is cut with shard_weights, and connect() must run before the first
+        step."""
         self.lib = _lib.load()
+        self.tp_size, self.tp_rank = tp_size, tp_rank
         self.cfg = dict(cfg)
         self.device = torch.device(device)
         c = _lib.DecoderConfig(
             n_layers=cfg["n_layers"], d_model=cfg["d_model"], n_heads=cfg["n_heads"], n_kv_heads=cfg["n_kv_heads"],
             head_dim=cfg["head_dim"], d_ff=cfg["d_ff"], vocab=cfg["vocab"], max_seq=max_seq, max_batch=max_batch,
             rms_eps=rms_eps, rope_base=rope_base, embed_scale=math.sqrt(cfg["d_model"]),
-            kv_dtype=1 if kv_dtype == "i8" else 0, tp_size=1, tp_rank=0)
+            kv_dtype=1 if kv_dtype == "i8" else 0, tp_size=tp_size, tp_rank=tp_rank)
         self.config_struct = c
         self.rms_eps, self.rope_base, self.max_seq, self.max_batch = rms_eps, rope_base, max_seq, max_batch
         self.handle = ctypes.c_void_p()
@@ -67,6 +99,9 @@ class Decoder:
             _check(self.lib.b200_decoder_create(ctypes.byref(c), ctypes.c_void_p(self.stream.cuda_stream),
                                                 ctypes.byref(self.handle)))
             weights = weights or make_weights(cfg, seed, device)
+            whole = weights
+            if tp_size > 1:
+                weights = shard_weights(cfg, whole, tp_size, tp_rank)
             for i, lw in enumerate(weights["layers"]):
                 st = _lib.DecoderLayerWeights(**{k: lw[k].data_ptr() for k in lw})
                 _check(self.lib.b200_decoder_set_layer(self.handle, i, ctypes.byref(st)))
@@ -74,7 +109,35 @@ class Decoder:
                                                        weights["embed_scales"].data_ptr(),
                                                        weights["final_norm"].data_ptr()))
             torch.cuda.synchronize()
-        self.weights = weights if keep_weights else None
+        self.weights = whole if keep_weights else None
+
+    def connect(self, mode="peer", group=None):
+        """Joins the tensor-parallel ranks of `group` (torch.distributed, any backend; group rank = tp_rank).
+        'peer': the ranks swap the CUDA IPC handles of their exchange buffers and the consuming kernels
+        read the peers' partial sums themselves; 'nccl': an NCCL communicator of the ranks' own."""
+        import torch.distributed as dist
+        if self.tp_size == 1:
+            return
+        with torch.cuda.device(self.device):
+            if mode == "peer":
+                buf = ctypes.create_string_buffer(64)
+                _check(self.lib.b200_decoder_exchange_handle(self.handle, buf, 64))
+                handles = [None] * self.tp_size
+                dist.all_gather_object(handles, bytes(buf.raw), group=group)
+                blob = b"".join(handles)
+                _check(self.lib.b200_decoder_connect_peers(self.handle, blob, 64))
+            elif mode == "nccl":
+                ids = [None]
+                if self.tp_rank == 0:
+                    buf = ctypes.create_string_buffer(128)
+                    _check(self.lib.b200_nccl_unique_id(buf, 128))
+                    ids[0] = bytes(buf.raw)
+                src = dist.get_global_rank(group, 0) if group is not None else 0
+                dist.broadcast_object_list(ids, src=src, group=group)
+                _check(self.lib.b200_decoder_init_nccl(self.handle, ids[0]))
+            else:
+                raise ValueError("mode must be 'peer' or 'nccl'")
+            dist.barrier(group=group)
 
     def reset(self):
         _check(self.lib.b200_decoder_reset(self.handle))
@@ -90,7 +153,9 @@ class Decoder:
         logits = None
         with torch.cuda.device(self.device):
             if want_logits:
-                logits = torch.empty((tok.size, self.cfg["vocab"]), dtype=torch.float32, device=self.device)
+                # with tensor parallelism: this rank's columns [tp_rank * vocab / tp_size, ...)
+                logits = torch.empty((tok.size, self.cfg["vocab"] // self.tp_size), dtype=torch.float32,
+                                     device=self.device)
             _check(self.lib.b200_decoder_step(self.handle, tok.ctypes.data_as(ctypes.c_void_p), tok.size,
                                               nxt.ctypes.data_as(ctypes.c_void_p),
                                               None if logits is None else ctypes.c_void_p(logits.data_ptr())))

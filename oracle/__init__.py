@@ -20,7 +20,11 @@ REQUANT_MBQM, REQUANT_FLOAT_REF = 0, 1
 def build(force=False):
     """Compile liboracle.so / liboracle_fast.so (and oracle/_ref when the reference tree exists)."""
     targets = ["liboracle.so", "liboracle_fast.so"]
-    if force or not all(os.path.exists(os.path.join(_HERE, t)) for t in targets):
+    sources = [f for f in os.listdir(_HERE) if f.endswith((".c", ".h"))]
+    newest = max(os.path.getmtime(os.path.join(_HERE, f)) for f in sources)
+    stale = not all(os.path.exists(os.path.join(_HERE, t)) and os.path.getmtime(os.path.join(_HERE, t)) >= newest
+                    for t in targets)
+    if force or stale:
         subprocess.check_call(["make", "-C", _HERE, "-s", "liboracle.so", "liboracle_fast.so"])
     if os.path.isdir("/root/reference/tflite") and (
         force or not os.path.exists(os.path.join(_HERE, "_ref", "libref_quant.so"))
@@ -286,11 +290,47 @@ class _DecLayer(ctypes.Structure):
                                                "sgate", "sup", "sdown", "norm1", "norm2")]
 
 
+_REDUCE_FN = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.POINTER(ctypes.c_float), ctypes.c_size_t)
+
+
+def shard_decoder(cfg, weights, tp_size, rank):
+    """Tensor-parallel shard `rank` of `tp_size`: (shard cfg, shard weights, (first LM row, LM rows)).
+    Query heads, feed-forward units and LM-head rows are split evenly; q/gate/up are cut by output
+    rows, o/down by input columns; a KV head shared by several ranks is replicated on each."""
+    H, KVH, HD, F, V = cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"], cfg["vocab"]
+    assert H % tp_size == 0 and F % tp_size == 0 and V % tp_size == 0
+    hl, fl = H // tp_size, F // tp_size
+    if KVH % tp_size == 0:
+        kvl = KVH // tp_size
+        kv0 = rank * kvl
+    else:
+        assert tp_size % KVH == 0
+        kvl = 1
+        kv0 = rank // (tp_size // KVH)
+    q0, q1 = rank * hl * HD, (rank + 1) * hl * HD
+    k0, k1 = kv0 * HD, (kv0 + kvl) * HD
+    f0, f1 = rank * fl, (rank + 1) * fl
+    layers = []
+    for lw in weights["layers"]:
+        layers.append(dict(
+            wq=lw["wq"][q0:q1], sq=lw["sq"][q0:q1], wk=lw["wk"][k0:k1], sk=lw["sk"][k0:k1],
+            wv=lw["wv"][k0:k1], sv=lw["sv"][k0:k1], wo=lw["wo"][:, q0:q1], so=lw["so"],
+            wgate=lw["wgate"][f0:f1], sgate=lw["sgate"][f0:f1], wup=lw["wup"][f0:f1], sup=lw["sup"][f0:f1],
+            wdown=lw["wdown"][:, f0:f1], sdown=lw["sdown"], norm1=lw["norm1"], norm2=lw["norm2"]))
+    scfg = dict(cfg, n_heads=hl, n_kv_heads=kvl, d_ff=fl)
+    sw = dict(layers=layers, embed=weights["embed"], embed_scales=weights["embed_scales"],
+              final_norm=weights["final_norm"])
+    return scfg, sw, (rank * (V // tp_size), V // tp_size)
+
+
 class DecoderRef:
     """CPU decode steps over numpy weights (dict of layers / embed / embed_scales / final_norm with
     the key names of _DecLayer). fast=True uses the vectorised multi-threaded kernels."""
 
-    def __init__(self, cfg, weights, batch, max_seq, rms_eps=1e-6, rope_base=10000.0, fast=False):
+    def __init__(self, cfg, weights, batch, max_seq, rms_eps=1e-6, rope_base=10000.0, fast=False, reduce=None,
+                 lm_rows=None):
+        """reduce(arr): sums a float32 array over tensor-parallel ranks in place (shard decoders only);
+        lm_rows=(first, rows) limits the LM head to those rows of the table."""
         use_fast = bool(fast)
         self.lib = fast_lib = globals()["fast"]()
         self.cfg = cfg
@@ -312,13 +352,24 @@ class DecoderRef:
         fn = np.ascontiguousarray(weights["final_norm"], np.float32)
         self._keep += [e, es, fn]
         fast_lib.orc_decoder_set_embedding(self.h, _p(e), _p(es), _p(fn))
+        self.lm_rows = cfg["vocab"]
+        if lm_rows is not None:
+            self.lm_rows = int(lm_rows[1])
+            fast_lib.orc_decoder_set_lm_rows(self.h, int(lm_rows[0]), int(lm_rows[1]))
+        self._reduce_cb = None
+        if reduce is not None:
+            def _cb(_user, buf, count):
+                arr = np.ctypeslib.as_array(buf, shape=(count,))
+                reduce(arr)
+            self._reduce_cb = _REDUCE_FN(_cb)
+            fast_lib.orc_decoder_set_reduce(self.h, self._reduce_cb, None)
 
     def reset(self):
         self.lib.orc_decoder_reset(self.h)
 
     def step(self, tokens, want_logits=True):
         tok = np.ascontiguousarray(tokens, np.int32)
-        logits = np.empty((self.batch, self.cfg["vocab"]), np.float32) if want_logits else None
+        logits = np.empty((self.batch, self.lm_rows), np.float32) if want_logits else None
         nxt = np.empty(self.batch, np.int32)
         self.lib.orc_decoder_step(self.h, _p(tok), _p(logits), _p(nxt))
         return nxt, logits
@@ -327,3 +378,50 @@ class DecoderRef:
         if self.h:
             self.lib.orc_decoder_destroy(self.h)
             self.h = None
+
+
+class DecoderRefTP:
+    """tp_size shard decoders stepped side by side on CPU threads (scalar kernels); the partial
+    outputs of the input-sharded projections are summed in rank order. step() returns the next
+    tokens and the logits over the whole vocabulary."""
+
+    def __init__(self, cfg, weights, tp_size, batch, max_seq, **kw):
+        import threading
+        self.tp = tp_size
+        self.batch = batch
+        self._barrier = threading.Barrier(tp_size)
+        self._bufs = [None] * tp_size
+        self.shards = []
+        for r in range(tp_size):
+            scfg, sw, lm = shard_decoder(cfg, weights, tp_size, r)
+            self.shards.append(DecoderRef(scfg, sw, batch, max_seq, reduce=self._make_reduce(r), lm_rows=lm, **kw))
+
+    def _make_reduce(self, r):
+        def red(arr):
+            self._bufs[r] = arr
+            self._barrier.wait()
+            total = self._bufs[0].copy()
+            for j in range(1, self.tp):
+                total += self._bufs[j]
+            self._barrier.wait()  # every rank holds its sum before any buffer changes
+            arr[:] = total
+        return red
+
+    def step(self, tokens):
+        import threading
+        out = [None] * self.tp
+
+        def run(r):
+            out[r] = self.shards[r].step(tokens, want_logits=True)
+        threads = [threading.Thread(target=run, args=(r,)) for r in range(self.tp)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        logits = np.concatenate([o[1] for o in out], axis=1)
+        return np.argmax(logits, axis=1).astype(np.int32), logits
+
+    def close(self):
+        for s in self.shards:
+            s.close()
+

@@ -15,6 +15,15 @@
  * int8 row times its per-row scale); attention is orc_sdpa_f32 over the cached
  * prefix. `fast` != 0 swaps in the vectorised multi-threaded twins of
  * oracle_fast.c (same formulas) for timing.
+ *
+ * Tensor-parallel shards: a shard decoder is created with this rank's head and
+ * feed-forward counts and given this rank's slices of the weights (q/gate/up by
+ * output rows, o/down by input columns). The partial outputs of the two
+ * input-sharded projections are summed over ranks by the hook set with
+ * orc_decoder_set_reduce before the residual add; the LM head may be limited to
+ * a row range of the table (orc_decoder_set_lm_rows), the winner over ranks is
+ * then picked by the caller. Each shard quantizes its own slice of the
+ * activation row, as a graph with one FULLY_CONNECTED per shard would.
  */
 #include <math.h>
 #include <stdlib.h>
@@ -45,6 +54,9 @@ typedef struct {
   int* lengths; /* [batch] */
   int batch;
   int fast;
+  void (*reduce)(void* user, float* buf, size_t count); /* in-place sum over ranks, or NULL */
+  void* reduce_user;
+  int lm_first, lm_rows; /* LM head rows [lm_first, lm_first + lm_rows) of the table */
 } orc_decoder;
 
 static void fc(const orc_decoder* d, int m, int n, int k, const float* x, const int8_t* w, const float* s, float* y) {
@@ -90,6 +102,8 @@ orc_decoder* orc_decoder_create(const orc_decoder_config* cfg, int batch, int fa
   d->k_cache = (float*)calloc(kv, sizeof(float));
   d->v_cache = (float*)calloc(kv, sizeof(float));
   d->lengths = (int*)calloc((size_t)batch, sizeof(int));
+  d->lm_first = 0;
+  d->lm_rows = cfg->vocab;
   return d;
 }
 
@@ -107,10 +121,18 @@ void orc_decoder_set_embedding(orc_decoder* d, const int8_t* w, const float* sca
   d->embed_scales = scales;
   d->final_norm = final_norm;
 }
+void orc_decoder_set_reduce(orc_decoder* d, void (*fn)(void*, float*, size_t), void* user) {
+  d->reduce = fn;
+  d->reduce_user = user;
+}
+void orc_decoder_set_lm_rows(orc_decoder* d, int first, int rows) {
+  d->lm_first = first;
+  d->lm_rows = rows;
+}
 void orc_decoder_reset(orc_decoder* d) { memset(d->lengths, 0, sizeof(int) * (size_t)d->batch); }
 
-/* One token per sequence: tokens [batch] -> logits [batch, vocab] (may be NULL) and the greedy next
- * token (first index of the maximum). Appends to the caches. */
+/* One token per sequence: tokens [batch] -> logits [batch, lm_rows] (may be NULL) and the greedy next
+ * token (first index of the maximum, as a row number of the whole table). Appends to the caches. */
 void orc_decoder_step(orc_decoder* d, const int32_t* tokens, float* logits_out, int32_t* next_tokens) {
   const orc_decoder_config* c = &d->cfg;
   const int B = d->batch, D = c->d_model, H = c->n_heads, KVH = c->n_kv_heads, HD = c->head_dim, F = c->d_ff;
@@ -123,7 +145,7 @@ void orc_decoder_step(orc_decoder* d, const int32_t* tokens, float* logits_out, 
   float* o = (float*)malloc(sizeof(float) * (size_t)B * D);
   float* gate = (float*)malloc(sizeof(float) * (size_t)B * F);
   float* up = (float*)malloc(sizeof(float) * (size_t)B * F);
-  float* logits = logits_out ? logits_out : (float*)malloc(sizeof(float) * (size_t)B * c->vocab);
+  float* logits = logits_out ? logits_out : (float*)malloc(sizeof(float) * (size_t)B * d->lm_rows);
 
   for (int b = 0; b < B; ++b) {
     const int8_t* row = d->embed + (size_t)tokens[b] * D;
@@ -156,22 +178,24 @@ void orc_decoder_step(orc_decoder* d, const int32_t* tokens, float* logits_out, 
       }
     }
     fc(d, B, D, H * HD, att, w->wo, w->so, o);
+    if (d->reduce) d->reduce(d->reduce_user, o, (size_t)B * D);
     for (size_t i = 0; i < (size_t)B * D; ++i) h[i] += o[i];
     for (int b = 0; b < B; ++b) rms_norm(h + (size_t)b * D, w->norm2, D, c->rms_eps, x + (size_t)b * D);
     fc(d, B, F, D, x, w->wgate, w->sgate, gate);
     fc(d, B, F, D, x, w->wup, w->sup, up);
     for (size_t i = 0; i < (size_t)B * F; ++i) gate[i] = gelu_tanh(gate[i]) * up[i];
     fc(d, B, D, F, gate, w->wdown, w->sdown, o);
+    if (d->reduce) d->reduce(d->reduce_user, o, (size_t)B * D);
     for (size_t i = 0; i < (size_t)B * D; ++i) h[i] += o[i];
   }
   for (int b = 0; b < B; ++b) rms_norm(h + (size_t)b * D, d->final_norm, D, c->rms_eps, x + (size_t)b * D);
-  fc(d, B, c->vocab, D, x, d->embed, d->embed_scales, logits);
+  fc(d, B, d->lm_rows, D, x, d->embed + (size_t)d->lm_first * D, d->embed_scales + d->lm_first, logits);
   for (int b = 0; b < B; ++b) {
-    const float* lg = logits + (size_t)b * c->vocab;
+    const float* lg = logits + (size_t)b * d->lm_rows;
     int best = 0;
-    for (int i = 1; i < c->vocab; ++i)
+    for (int i = 1; i < d->lm_rows; ++i)
       if (lg[i] > lg[best]) best = i;
-    if (next_tokens) next_tokens[b] = best;
+    if (next_tokens) next_tokens[b] = d->lm_first + best;
     d->lengths[b] += 1;
   }
   free(h); free(x); free(q); free(kk); free(vv); free(att); free(o); free(gate); free(up);
