@@ -41,6 +41,10 @@ def parse_args():
     ap.add_argument("--model", default="gemma2b", choices=["gemma2b", "tiny"])
     ap.add_argument("--kv", default="f16", choices=["f16", "i8"])
     ap.add_argument("--cpu-steps", type=int, default=6, help="decode steps of the CPU baseline sample")
+    ap.add_argument("--side-batch", type=int, default=32,
+                    help="also time this batch size (reported beside the headline; 0 = skip)")
+    ap.add_argument("--tp", default="both", choices=["both", "peer", "nccl", "off"],
+                    help="with --gpus > 1 also time ONE batch run tensor-parallel over all ranks")
     return ap.parse_args()
 
 
@@ -188,6 +192,45 @@ def workload_config(args, cfg):
             "l2": "inputs larger than L2: every step streams the full weight set (2.5 GB >> 126 MB)"}
 
 
+def tensor_parallel_run(args, cfg, mode, world, rank, local, barrier):
+    """One batch decoded by all ranks together: every rank holds 1/world of each projection."""
+    import torch
+    import torch.distributed as dist
+
+    from litert_b200 import decoder as dec
+
+    max_seq = args.context + args.warmup + args.steps + 16
+    d = dec.Decoder(cfg, max_seq=max_seq, max_batch=args.batch, kv_dtype=args.kv, seed=1005, device=f"cuda:{local}",
+                    tp_size=world, tp_rank=rank)
+    d.connect(mode)
+    first = np.random.default_rng(1005).integers(0, cfg["vocab"], args.batch).astype(np.int32)
+    d.run(first, args.context, fetch=True)
+    d.run(None, args.warmup, fetch=True)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(d.stream):
+        e0.record(d.stream)
+        d.run(None, args.steps, fetch=False)
+        e1.record(d.stream)
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    tok = d.run(None, 1, fetch=True)   # also checks the device status word
+    agree = torch.tensor(tok.astype(np.int64), device="cuda")
+    lo, hi = agree.clone(), agree.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    launches = d.launches_per_step
+    d.close()
+    del d
+    torch.cuda.empty_cache()
+    ms = t.item() / args.steps
+    return {"tokens_per_s": args.batch / (ms * 1e-3), "ms_per_step": ms, "ranks": world, "scaling": "strong",
+            "launches_per_step_per_rank": launches, "ranks_agree_on_tokens": bool(torch.equal(lo, hi)),
+            "exchange": ("partial sums read from peer memory inside the consuming kernels (flag handshake, no "
+                         "collective launch)") if mode == "peer" else "NCCL all-reduce between the kernels"}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -204,7 +247,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = model_config(args.model)
     max_seq = args.context + args.warmup + 2 * args.steps + 16
-    d = dec.Decoder(cfg, max_seq=max_seq, max_batch=args.batch, kv_dtype=args.kv, seed=1005 + rank,
+    side_batch = 0 if args.side_batch == args.batch else args.side_batch
+    d = dec.Decoder(cfg, max_seq=max_seq, max_batch=max(args.batch, side_batch), kv_dtype=args.kv, seed=1005 + rank,
                     device=f"cuda:{local}")
     rng = np.random.default_rng(1005 + rank)
     first = rng.integers(0, cfg["vocab"], args.batch).astype(np.int32)
@@ -244,6 +288,26 @@ def run_ours(args):
     # ---- per-kernel-class device time of one step (CUDA events around every launch)
     prof = d.profile_step(tok)
     launches = d.launches_per_step
+    # ---- the dominant kernel alone: the step's GEMV launches replayed back to back as one graph
+    gemv_ms, gemv_launches = d.time_gemv(args.batch, reps=max(8, min(64, args.steps)))
+
+    # ---- the other batch size of the workload, same decoder (cache depth declared, rows hold zeros)
+    side = None
+    if side_batch > 0:
+        d.set_positions(np.full(side_batch, args.context, np.int32))
+        d.run(rng.integers(0, cfg["vocab"], side_batch).astype(np.int32), max(3, args.warmup), fetch=True)
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            s0.record(stream)
+            d.run(None, args.steps, fetch=False)
+            s1.record(stream)
+        barrier()
+        side_ms = s0.elapsed_time(s1) / args.steps
+        side_gemv_ms, _ = d.time_gemv(side_batch, reps=8)
+        side = {"batch_per_gpu": side_batch, "tokens_per_s_per_gpu": side_batch / (side_ms * 1e-3),
+                "ms_per_step": side_ms, "gemv_ms_per_step": side_gemv_ms,
+                "gemv_gbs": weight_bytes(cfg) / (side_gemv_ms * 1e-3) / 1e9}
 
     times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -253,7 +317,6 @@ def run_ours(args):
         tokens = args.batch * args.steps * world
         peak, peak_kind = measured_peaks()
         wbytes = weight_bytes(cfg)
-        gemv_ms, gemv_launches = prof["gemv"]
         # algorithmic bytes of the GEMV launches of one step: every int8 weight once, plus per launch the
         # per-channel scales and row sums (8 B per output channel), the quantized activation rows and the
         # float outputs
@@ -277,19 +340,38 @@ def run_ours(args):
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if achieved else None,
                          "peak_kind": peak_kind, "traffic": None, "launches": gemv_launches,
                          "algorithmic_bytes_per_step": gemv_bytes, "gemv_ms_per_step": gemv_ms,
+                         "avg_launch_us": gemv_ms * 1e3 / gemv_launches,
+                         "timing": "CUDA events around a graph of the step's GEMV launches alone, on the launching stream",
                          "whole_step_frac": (wbytes / (dev_ms / args.steps * 1e-3) / 1e9) / peak},
             "step_breakdown_ms": {k: v[0] for k, v in prof.items()},
         }
+        if side:
+            line["side_batch"] = side
         try:
+            if world > 1:
+                raise RuntimeError("timed at --gpus 1 only")
             steps = max(1, min(args.cpu_steps, args.steps))
             tps, ms, cores = cpu_reference_run(cfg, args.batch, steps, 1)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
                                     "sample": f"{steps} decode steps, batch {args.batch}, short context, all host threads"}
         except Exception as exc:  # the baseline is a report, not part of the product path
             line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port",
-                                    "sample": f"failed: {exc}"}
-        print(json.dumps(line), flush=True)
+                                    "sample": f"not run: {exc}"}
     d.close()
+    del d
+    torch.cuda.empty_cache()
+    # ---- the same batch run tensor-parallel over all ranks (strong scaling of one sequence batch)
+    tp = {}
+    if world > 1 and args.tp != "off":
+        for mode in (["peer", "nccl"] if args.tp == "both" else [args.tp]):
+            try:
+                tp[mode] = tensor_parallel_run(args, cfg, mode, world, rank, local, barrier)
+            except Exception as exc:  # reported, the replica line above stands on its own
+                tp[mode] = {"error": str(exc)[:300]}
+    if rank == 0:
+        if tp:
+            line["tensor_parallel"] = tp
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

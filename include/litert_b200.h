@@ -251,6 +251,10 @@ B200_API int b200_decoder_profile_step(b200_decoder* dec, const int32_t* h_token
 B200_API const char* b200_decoder_last_error(void);
 /* Number of kernels one step launches (for reporting). */
 B200_API int b200_decoder_launches_per_step(const b200_decoder* dec);
+/* Times the projections of one step alone: the step's GEMV launches, in step order over the
+ * current activation buffers, replayed `reps` times as one CUDA graph between two events on the
+ * decoder's stream. ms_per_step = device time of one pass over all of them. */
+B200_API int b200_decoder_time_gemv(b200_decoder* dec, int batch, int reps, float* ms_per_step, int* launches_per_step);
 
 #ifdef __cplusplus
 }

@@ -671,6 +671,60 @@ int b200_decoder_run(b200_decoder* d, const int32_t* h_first_tokens, int batch, 
 
 int b200_decoder_launches_per_step(const b200_decoder* d) { return d ? d->launches : 0; }
 
+int b200_decoder_time_gemv(b200_decoder* d, int batch, int reps, float* ms_per_step, int* launches_per_step) {
+  if (!d || !ms_per_step || batch <= 0 || batch > d->cfg.max_batch || reps <= 0)
+    return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_time_gemv: bad argument");
+  if (d->lm_head.n == 0) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_time_gemv: weights not set");
+  const int saved_launches = d->launches;
+  // the projections of one step, in step order, over whatever the activation buffers hold
+  auto enqueue = [&]() -> int {
+    for (auto& lp : d->layers) {
+      Layer& L = *lp;
+      DEC_CUDA(run_fc(d, L.qkv, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), d->qkv.as<float>()));
+      DEC_CUDA(run_fc(d, L.o, batch, d->q_a.as<int8_t>(), d->sc_a.as<float>(), d->zp_a.as<int32_t>(), d->proj));
+      DEC_CUDA(run_fc(d, L.gate_up, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), d->gate_up.as<float>()));
+      DEC_CUDA(run_fc(d, L.down, batch, d->q_f.as<int8_t>(), d->sc_f.as<float>(), d->zp_f.as<int32_t>(), d->down_out));
+    }
+    DEC_CUDA(run_fc(d, d->lm_head, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), d->logits.as<float>()));
+    return B200_OK;
+  };
+  d->launches = 0;
+  int rc = enqueue();  // uncaptured once: one-time kernel attribute set-up
+  const int n_launch = d->launches;
+  d->launches = saved_launches;
+  if (rc) return rc;
+  cudaGraph_t g = nullptr;
+  cudaGraphExec_t ge = nullptr;
+  DEC_CUDA(cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal));
+  rc = enqueue();
+  d->launches = saved_launches;
+  cudaError_t e = cudaStreamEndCapture(d->stream, &g);
+  if (rc || e != cudaSuccess) {
+    if (g) cudaGraphDestroy(g);
+    return rc ? rc : dec_fail(B200_ERR_CUDA, "cudaStreamEndCapture", e);
+  }
+  e = cudaGraphInstantiate(&ge, g, 0);
+  cudaGraphDestroy(g);
+  if (e != cudaSuccess) return dec_fail(B200_ERR_CUDA, "cudaGraphInstantiate", e);
+  cudaEvent_t a, b;
+  cudaEventCreate(&a);
+  cudaEventCreate(&b);
+  for (int i = 0; i < 2; ++i) cudaGraphLaunch(ge, d->stream);
+  cudaEventRecord(a, d->stream);
+  for (int i = 0; i < reps; ++i) cudaGraphLaunch(ge, d->stream);
+  cudaEventRecord(b, d->stream);
+  e = cudaStreamSynchronize(d->stream);
+  float ms = 0.0f;
+  cudaEventElapsedTime(&ms, a, b);
+  cudaEventDestroy(a);
+  cudaEventDestroy(b);
+  cudaGraphExecDestroy(ge);
+  if (e != cudaSuccess) return dec_fail(B200_ERR_CUDA, "b200_decoder_time_gemv", e);
+  *ms_per_step = ms / (float)reps;
+  if (launches_per_step) *launches_per_step = n_launch;
+  return B200_OK;
+}
+
 int b200_decoder_profile_step(b200_decoder* d, const int32_t* h_tokens, int batch, float* ms_by_class,
                               int* launches_by_class) {
   if (!d || !h_tokens || !ms_by_class || batch <= 0 || batch > d->cfg.max_batch)

@@ -24,6 +24,7 @@
 // makes the result bit-equal to a serial sum.
 // Every wait is bounded (see mbar_wait_bounded); TMEM is always freed.
 #include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -35,6 +36,16 @@ namespace {
 constexpr int kUmmaThreads = 192;
 constexpr int kEpiThreads = 128;
 
+struct UmmaShared {
+  uint32_t tmem_base;
+  int abort_flag;
+  int last;
+  int pad;
+  // per activation row of this launch's pass: input scale, zero point (hybrid) or row sum (int8)
+  float in_scale[256];
+  int32_t in_aux[256];
+};
+
 template <int NB>
 struct UmmaLayout {
   static constexpr int kQBytes = NB * kTileK8;  // NB/8 row groups x 1 KiB
@@ -42,32 +53,24 @@ struct UmmaLayout {
   static constexpr int kStagesRaw = 200 * 1024 / kStageBytes;
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
   static constexpr int kBarriers = 2 * kStages + 4;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarriers * 8 + 64;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarriers * 8 + (int)sizeof(UmmaShared) + 16;
   static constexpr int kTmemCols = 2 * NB < 32 ? 32 : 2 * NB;
-};
-
-struct UmmaShared {
-  uint32_t tmem_base;
-  int abort_flag;
-  int last;
-  int pad;
 };
 
 // Epilogue for one output element; `total` is the exact int32 dot product.
 template <int EPI>
 __device__ __forceinline__ void store_output(const FcParams& p, int m, int n, int32_t total, int32_t rs, float ws,
-                                             float bias_f, int32_t base_i, int32_t mult, int32_t shift) {
+                                             float bias_f, int32_t base_i, int32_t mult, int32_t shift,
+                                             float in_scale, int32_t in_aux) {
   if constexpr (EPI == kEpiHybridF32) {
-    int32_t dot = total;
-    if (p.in_zps) dot -= rs * p.in_zps[m];
+    const int32_t dot = total - rs * in_aux;  // in_aux: the row's zero point
     // reference order: scale = in_scale * w_scale; out = bias + dot * scale (no fused multiply-add)
-    const float scale = __fmul_rn(p.in_scales[m], ws);
+    const float scale = __fmul_rn(in_scale, ws);
     float out = __fadd_rn(bias_f, __fmul_rn((float)dot, scale));
     out = apply_activation(out, p.activation);
     static_cast<float*>(p.y)[(size_t)m * p.n + n] = out;
   } else {
-    int32_t t = total + base_i;
-    if (p.x_sums) t += p.filter_offset * p.x_sums[m];
+    const int32_t t = total + base_i + p.filter_offset * in_aux;  // in_aux: the row's sum
     if constexpr (EPI == kEpiRawI32) {
       static_cast<int32_t*>(p.y)[(size_t)m * p.n + n] = t;
     } else {
@@ -206,7 +209,39 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
     const int row_in_tile = quarter * 32 + lane;
     const int etid = tid - 64;
     const int m_valid = p.m - m_base < NB ? p.m - m_base : NB;
-    pdl_wait();  // the epilogue reads activation scales written by the previous kernel
+    // Per-output-channel constants of a segment (weights-side data, never written by other kernels).
+    int32_t rs = 0, base_i = 0, mult = 0, shift = 0;
+    float wsc = 0.0f, bias_f = 0.0f;
+    auto load_channel_constants = [&](int n) {
+      rs = 0, base_i = 0, mult = 0, shift = 0, wsc = 0.0f, bias_f = 0.0f;
+      if (n >= p.n) return;
+      rs = p.row_sums ? p.row_sums[n] : 0;
+      if constexpr (EPI == kEpiHybridF32) {
+        wsc = p.per_channel ? p.w_scales[n] : p.w_scales[0];
+        bias_f = p.bias_f32 ? p.bias_f32[n] : 0.0f;
+      } else {
+        // sum (w+fo)(x+io) = sum w x + io sum w + fo sum x + k fo io
+        base_i = p.input_offset * rs + p.k * p.filter_offset * p.input_offset + (p.bias_i32 ? p.bias_i32[n] : 0);
+        if (p.multipliers) {
+          mult = p.multipliers[p.per_channel ? n : 0];
+          shift = p.shifts[p.per_channel ? n : 0];
+        }
+      }
+    };
+    // those of the first segment are fetched while the predecessor kernel is still running
+    if (t_begin < t_end) load_channel_constants((int)(t_begin / p.k_tiles) * kTileN + row_in_tile);
+    pdl_wait();  // the activation rows' scales are written by the previous kernel
+    for (int i = etid; i < NB; i += kEpiThreads) {
+      const int m = m_base + i;
+      const bool ok = m < p.m;
+      sh->in_scale[i] = (ok && p.in_scales) ? p.in_scales[m] : 0.0f;
+      if constexpr (EPI == kEpiHybridF32) {
+        sh->in_aux[i] = (ok && p.in_zps) ? p.in_zps[m] : 0;
+      } else {
+        sh->in_aux[i] = (ok && p.x_sums) ? p.x_sums[m] : 0;
+      }
+    }
+    named_barrier(1, kEpiThreads);
     uint32_t seg = 0;
     long long t = t_begin;
     while (t < t_end) {
@@ -219,22 +254,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
 
       const int n = (int)nt * kTileN + row_in_tile;
       const bool row_ok = n < p.n;
-      int32_t rs = 0, base_i = 0, mult = 0, shift = 0;
-      float wsc = 0.0f, bias_f = 0.0f;
-      if (row_ok) {
-        rs = p.row_sums ? p.row_sums[n] : 0;
-        if constexpr (EPI == kEpiHybridF32) {
-          wsc = p.per_channel ? p.w_scales[n] : p.w_scales[0];
-          bias_f = p.bias_f32 ? p.bias_f32[n] : 0.0f;
-        } else {
-          // sum (w+fo)(x+io) = sum w x + io sum w + fo sum x + k fo io
-          base_i = p.input_offset * rs + p.k * p.filter_offset * p.input_offset + (p.bias_i32 ? p.bias_i32[n] : 0);
-          if (p.multipliers) {
-            mult = p.multipliers[p.per_channel ? n : 0];
-            shift = p.shifts[p.per_channel ? n : 0];
-          }
-        }
-      }
+      if (seg > 0) load_channel_constants(n);
 
       // the per-channel constants above are in flight while the MMAs of this segment finish
       mbar_wait_bounded(&acc_full[ab], (seg >> 1) & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
@@ -256,7 +276,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int m = c * 16 + j;
-              if (m < m_valid) store_output<EPI>(p, m_base + m, n, r[j], rs, wsc, bias_f, base_i, mult, shift);
+              if (m < m_valid)
+                store_output<EPI>(p, m_base + m, n, r[j], rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[m], sh->in_aux[m]);
             }
           }
         }
@@ -300,13 +321,24 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         const bool last = sh->last != 0;
         if (last) {
           __threadfence();
-          for (int m = 0; m < m_valid; ++m) {
-            int32_t v = 0;
+          // eight activation rows at a time: all their loads are issued before the first store,
+          // so the L2 round trips overlap instead of queueing behind one another
+          for (int m0 = 0; m0 < m_valid; m0 += 8) {
+            int32_t v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             for (int c = c_first; c <= c_last; ++c) {
               const int w = (c == c_first) ? 1 : 0;
-              v += __ldcg(p.ws_part + (size_t)(c * 2 + w) * kZeroWsSlotInts + m * kTileN + row_in_tile);
+              const int32_t* slot = p.ws_part + (size_t)(c * 2 + w) * kZeroWsSlotInts + row_in_tile;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (m0 + j < m_valid) v[j] += __ldcg(slot + (m0 + j) * kTileN);
             }
-            if (row_ok) store_output<EPI>(p, m_base + m, n, v, rs, wsc, bias_f, base_i, mult, shift);
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (m0 + j < m_valid)
+                  store_output<EPI>(p, m_base + m0 + j, n, v[j], rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[m0 + j],
+                                    sh->in_aux[m0 + j]);
+            }
           }
           if (etid == 0) p.ws_count[c_first] = 0;
         }
@@ -316,6 +348,221 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
     }
   }
 
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, L::kTmemCols);
+}
+
+// ---- cluster split-K variant ---------------------------------------------------------------------
+// For layers with few n tiles (attention and down projections at decode time) the reduction over K
+// must be split across SMs to pull the weights fast enough, and merging the pieces through global
+// memory costs more than streaming them. Here the `split` CTAs that share an n tile form one
+// thread-block cluster: each accumulates its k range in TMEM, then sends every 128/split-row slice
+// of its int32 accumulator to the CTA that owns those rows through distributed shared memory
+// (reduce-scatter); after one cluster barrier each CTA adds the `split` pieces of its own rows and
+// runs the epilogue on them. No global scratch, no counters, no fences; integer addition keeps the
+// result bit-equal to a serial sum.
+template <int NB>
+struct ClusterLayout {
+  static constexpr int kQBytes = NB * kTileK8;
+  static constexpr int kStageBytes = kTileBytes + kQBytes;
+  static constexpr int kRedBytes = kTileN * NB * 4;  // split x (128 / split) rows x NB columns of int32
+  static constexpr int kStagesRaw = (200 * 1024 - kRedBytes) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+  static constexpr int kBarriers = 2 * kStages + 1;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kRedBytes + kBarriers * 8 + (int)sizeof(UmmaShared) + 16;
+  static constexpr int kTmemCols = NB < 32 ? 32 : NB;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// Address, in the cluster-wide shared window, of `local` inside CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t addr, int32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+template <int NB, int EPI>
+__global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcParams p, const int m_base, const int split) {
+  using L = ClusterLayout<NB>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  int32_t* red = reinterpret_cast<int32_t*>(smem + L::kStages * L::kStageBytes);  // [source][column][row in slice]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes + L::kRedBytes);
+  uint64_t* empty_bar = full_bar + L::kStages;
+  uint64_t* acc_full = empty_bar + L::kStages;
+  UmmaShared* sh = reinterpret_cast<UmmaShared*>(acc_full + 1);
+  volatile int* abort_flag = &sh->abort_flag;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int rank = (int)cluster_ctarank();
+  const int nt = blockIdx.x / split;
+  const int kt_begin = (int)((long long)p.k_tiles * rank / split);
+  const int kt_end = (int)((long long)p.k_tiles * (rank + 1) / split);
+  const int rows_per_owner = kTileN / split;
+
+  if (tid == 0) {
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    sh->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&sh->tmem_base, L::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+  cluster_arrive();  // phase 0: "this CTA is running" (waited for before the first remote store)
+
+  const int m_groups_alloc = p.m_alloc / 8;
+  const int mg_base = m_base / 8;
+  const uint8_t* w_tiles = p.w_packed + (size_t)nt * p.k_tiles * kTileBytes;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      pdl_launch_dependents();
+      uint32_t pre = 0;
+      for (int kt = kt_begin; kt < kt_end && pre < (uint32_t)L::kStages; ++kt, ++pre) {
+        mbar_arrive_expect_tx(&full_bar[pre], L::kStageBytes);
+        bulk_g2s(smem + (size_t)pre * L::kStageBytes, w_tiles + (size_t)kt * kTileBytes, kTileBytes, &full_bar[pre]);
+      }
+      pdl_wait();
+      for (uint32_t i = 0; i < pre; ++i) {
+        const size_t off = (((size_t)(kt_begin + i) * m_groups_alloc) + mg_base) * 1024;
+        bulk_g2s(smem + (size_t)i * L::kStageBytes + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[i]);
+      }
+      uint32_t it = pre;
+      for (int kt = kt_begin + (int)pre; kt < kt_end; ++kt, ++it) {
+        const int s = it % L::kStages;
+        const uint32_t ph = (it / L::kStages) & 1u;
+        mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, p.status, kStatusWaitTimeoutEmpty);
+        uint8_t* dst = smem + (size_t)s * L::kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[s], L::kStageBytes);
+        bulk_g2s(dst, w_tiles + (size_t)kt * kTileBytes, kTileBytes, &full_bar[s]);
+        const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
+        bulk_g2s(dst + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[s]);
+      }
+      const uint32_t issued = it;  // never leave with copies in flight (only possible after an abort)
+      for (uint32_t back = 0; back < (uint32_t)L::kStages && back < issued; ++back) {
+        const uint32_t j = issued - 1 - back;
+        mbar_wait_bounded(&full_bar[j % L::kStages], (j / L::kStages) & 1u, abort_flag, p.status,
+                          kStatusWaitTimeoutFull);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && kt_begin < kt_end) {
+      constexpr uint32_t idesc = umma_idesc_s8(NB);
+      uint32_t it = 0;
+      for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
+        const int s = it % L::kStages;
+        const uint32_t ph = (it / L::kStages) & 1u;
+        mbar_wait_bounded(&full_bar[s], ph, abort_flag, p.status, kStatusWaitTimeoutFull);
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + (size_t)s * L::kStageBytes);
+        const uint32_t b_addr = a_addr + kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < kTileK8 / 32; ++ks) {
+          const uint64_t a_desc = umma_smem_desc(a_addr + ks * 256, 128, 1024);
+          const uint64_t b_desc = umma_smem_desc(b_addr + ks * 256, 128, 1024);
+          umma_s8(tmem_base, a_desc, b_desc, idesc, (kt == kt_begin && ks == 0) ? 0u : 1u);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(acc_full);
+      mbar_wait_bounded(acc_full, 0, abort_flag, p.status, kStatusWaitTimeoutTmem);  // before TMEM goes away
+    }
+    __syncwarp();
+  }
+
+  // Rows this thread finishes after the exchange: row r_own of this CTA's slice, columns col0, col0 + split, ...
+  const int etid = tid - 64;
+  const int r_own = etid >= 0 ? etid % rows_per_owner : 0;
+  const int col0 = etid >= 0 ? etid / rows_per_owner : 0;
+  const int n_own = nt * kTileN + rank * rows_per_owner + r_own;
+  int32_t rs = 0, base_i = 0, mult = 0, shift = 0;
+  float wsc = 0.0f, bias_f = 0.0f;
+  const int m_valid = p.m - m_base < NB ? p.m - m_base : NB;
+
+  if (warp >= 2) {
+    // weights-side constants of the owned row: fetched while the predecessor kernel still runs
+    if (n_own < p.n) {
+      rs = p.row_sums ? p.row_sums[n_own] : 0;
+      if constexpr (EPI == kEpiHybridF32) {
+        wsc = p.per_channel ? p.w_scales[n_own] : p.w_scales[0];
+        bias_f = p.bias_f32 ? p.bias_f32[n_own] : 0.0f;
+      } else {
+        base_i = p.input_offset * rs + p.k * p.filter_offset * p.input_offset + (p.bias_i32 ? p.bias_i32[n_own] : 0);
+        if (p.multipliers) {
+          mult = p.multipliers[p.per_channel ? n_own : 0];
+          shift = p.shifts[p.per_channel ? n_own : 0];
+        }
+      }
+    }
+    pdl_wait();
+    for (int i = etid; i < NB; i += kEpiThreads) {
+      const int m = m_base + i;
+      const bool ok = m < p.m;
+      sh->in_scale[i] = (ok && p.in_scales) ? p.in_scales[m] : 0.0f;
+      if constexpr (EPI == kEpiHybridF32) {
+        sh->in_aux[i] = (ok && p.in_zps) ? p.in_zps[m] : 0;
+      } else {
+        sh->in_aux[i] = (ok && p.x_sums) ? p.x_sums[m] : 0;
+      }
+    }
+    // this CTA's accumulator row (zero when its k range is empty)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const bool have = kt_begin < kt_end;
+    if (have) {
+      mbar_wait_bounded(acc_full, 0, abort_flag, p.status, kStatusWaitTimeoutTmem);
+      tc_fence_after();
+    }
+    cluster_wait();  // phase 0: every CTA of the cluster is running, remote stores are legal
+    const uint32_t owner = (uint32_t)(row / rows_per_owner);
+    const uint32_t slot = map_to_rank(smem_u32(red), owner) +
+                          4u * (uint32_t)((rank * NB) * rows_per_owner + row % rows_per_owner);
+#pragma unroll 1
+    for (int c = 0; c < NB / 16; ++c) {
+      if (c * 16 >= m_valid) break;
+      int r[16];
+      if (have) {
+        tmem_ld16(taddr + c * 16, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r[j] = 0;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (c * 16 + j < m_valid) st_cluster_u32(slot + 4u * (uint32_t)((c * 16 + j) * rows_per_owner), r[j]);
+    }
+    tc_fence_before();
+  } else {
+    cluster_wait();  // phase 0
+  }
+  cluster_arrive();  // phase 1: this CTA's pieces are delivered ...
+  cluster_wait();    // ... and everyone else's have arrived here
+  if (warp >= 2 && n_own < p.n) {
+    for (int col = col0; col < m_valid; col += split) {
+      int32_t v = 0;
+      for (int src = 0; src < split; ++src) v += red[(src * NB + col) * rows_per_owner + r_own];
+      store_output<EPI>(p, m_base + col, n_own, v, rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[col], sh->in_aux[col]);
+    }
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, L::kTmemCols);
@@ -382,6 +629,91 @@ cudaError_t launch_umma_nb(const FcParams& p_in, int m_base, int nb, cudaStream_
   }
 }
 
+// Largest split of {8, 4, 2} whose clusters all fit on the device at once, 0 when the shape is
+// better served by the kernels above (many n tiles, or a single k tile).
+template <int NB, int EPI>
+int plan_cluster_split(const FcParams& p) {
+  if (const char* e = getenv("B200_FC_CLUSTER"))  // measurement knob
+    if (e[0] == '0') return 0;
+  const int sms = device_sm_count();
+  if (p.n_tiles * 2 >= sms || p.k_tiles < 2) return 0;
+  using L = ClusterLayout<NB>;
+  auto kernel = fc_cluster_kernel<NB, EPI>;
+  static int capacity[64][3] = {{0}};  // [device][split index]: co-resident clusters, -1 = query failed
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes) != cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
+    configured[dev] = true;
+  }
+  const int splits[3] = {8, 4, 2};
+  for (int i = 0; i < 3; ++i) {
+    const int split = splits[i];
+    if (split > p.k_tiles) continue;
+    if (capacity[dev][i] == 0) {
+      cudaLaunchConfig_t cfg;
+      memset(&cfg, 0, sizeof(cfg));
+      cfg.gridDim = dim3(split * 16);
+      cfg.blockDim = dim3(kUmmaThreads);
+      cfg.dynamicSmemBytes = L::kSmemBytes;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = split;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = -1;
+      }
+      capacity[dev][i] = n;
+    }
+    if (capacity[dev][i] >= p.n_tiles) return split;
+  }
+  return 0;
+}
+
+template <int NB, int EPI>
+cudaError_t launch_cluster_one(const FcParams& p, int m_base, int split, cudaStream_t s) {
+  using L = ClusterLayout<NB>;
+  return launch_chained_cluster(fc_cluster_kernel<NB, EPI>, dim3(p.n_tiles * split), dim3(kUmmaThreads),
+                                (size_t)L::kSmemBytes, split, s, p, m_base, split);
+}
+
+// One pass of nb <= 64 activation rows: the cluster kernel when the shape suits it. Returns
+// cudaErrorNotSupported when the caller should use the stream-K kernel instead.
+template <int EPI>
+cudaError_t try_cluster_pass(const FcParams& p, int m_base, int nb, cudaStream_t s) {
+  int split = 0;
+  switch (nb) {
+    case 16:
+      split = plan_cluster_split<16, EPI>(p);
+      return split ? launch_cluster_one<16, EPI>(p, m_base, split, s) : cudaErrorNotSupported;
+    case 32:
+      split = plan_cluster_split<32, EPI>(p);
+      return split ? launch_cluster_one<32, EPI>(p, m_base, split, s) : cudaErrorNotSupported;
+    case 64:
+      split = plan_cluster_split<64, EPI>(p);
+      return split ? launch_cluster_one<64, EPI>(p, m_base, split, s) : cudaErrorNotSupported;
+    default:
+      return cudaErrorNotSupported;
+  }
+}
+
+template <int EPI>
+cudaError_t launch_pass(const FcParams& p, int m_base, int nb, cudaStream_t s) {
+  const cudaError_t e = try_cluster_pass<EPI>(p, m_base, nb, s);
+  if (e != cudaErrorNotSupported) return e;
+  return launch_umma_nb<EPI>(p, m_base, nb, s);
+}
+
 }  // namespace
 
 int umma_rows_per_pass(int m) {
@@ -395,11 +727,11 @@ cudaError_t launch_fc_i8_umma(const FcParams& p, FcEpilogue epi, cudaStream_t s)
   for (int m_base = 0; m_base < p.m; m_base += nb) {
     cudaError_t e;
     if (epi == kEpiHybridF32) {
-      e = launch_umma_nb<kEpiHybridF32>(p, m_base, nb, s);
+      e = launch_pass<kEpiHybridF32>(p, m_base, nb, s);
     } else if (epi == kEpiRequantI8) {
-      e = launch_umma_nb<kEpiRequantI8>(p, m_base, nb, s);
+      e = launch_pass<kEpiRequantI8>(p, m_base, nb, s);
     } else {
-      e = launch_umma_nb<kEpiRawI32>(p, m_base, nb, s);
+      e = launch_pass<kEpiRawI32>(p, m_base, nb, s);
     }
     if (e != cudaSuccess) return e;
   }

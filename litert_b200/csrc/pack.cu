@@ -146,13 +146,13 @@ __global__ void w4_kfsum_kernel(const uint8_t* __restrict__ w4, const __half* __
 // symmetric: :41-71. The scale and zero point are derived in double exactly as
 // there; the element loop is float multiply, float add, round half away from
 // zero, clamp -- with no fused multiply-add, as on the reference's x86 build.
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restrict__ x, int m, int k, int k_pad,
+__global__ void __launch_bounds__(1024) quantize_rows_kernel(const float* __restrict__ x, int m, int k, int k_pad,
                                                             int m_alloc, int asymmetric,
                                                             int8_t* __restrict__ q_tiled,
                                                             int8_t* __restrict__ q_rowmajor,
                                                             float* __restrict__ scales,
                                                             int32_t* __restrict__ zero_points) {
-  __shared__ float red[32];
+  __shared__ float2 s_mm[32];
   __shared__ float s_inv;
   __shared__ int s_zp;
   __shared__ int s_zero;
@@ -178,8 +178,7 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restr
       mx = fmaxf(mx, v);
     }
   }
-  mn = block_reduce(mn, [](float a, float b) { return fminf(a, b); }, mn, red);
-  mx = block_reduce(mx, [](float a, float b) { return fmaxf(a, b); }, mx, red);
+  block_minmax(mn, mx, s_mm);
   if (threadIdx.x == 0) {
     float sf, inv;
     int zp, zero_row;
@@ -277,8 +276,10 @@ cudaError_t launch_quantize_rows(const float* x, int m, int k, int k_pad, int m_
                                  int8_t* q_tiled, int8_t* q_rowmajor, float* scales, int32_t* zps,
                                  cudaStream_t s) {
   if (m <= 0) return cudaSuccess;
-  return launch_chained(quantize_rows_kernel, dim3(m), dim3(256), 0, s, x, m, k, k_pad, m_alloc, asymmetric, q_tiled, q_rowmajor,
-                        scales, zps);
+  // few long rows (decode): one large CTA per row hides more latency; many rows: more CTAs per SM
+  const int threads = (m <= 32 && k >= 2048) ? 1024 : 256;
+  return launch_chained(quantize_rows_kernel, dim3(m), dim3(threads), 0, s, x, m, k, k_pad, m_alloc, asymmetric, q_tiled,
+                        q_rowmajor, scales, zps);
 }
 
 cudaError_t launch_retile_x8(const int8_t* x, int m, int k, int k_pad, int m_alloc, int8_t* q_tiled,

@@ -29,6 +29,28 @@ __device__ __forceinline__ T block_reduce(T v, Op op, T identity, T* scratch) {
 }
 
 
+// Block-wide minimum and maximum in one pass (one barrier); every thread gets both.
+// `scratch` holds one float2 per warp and must not be reused before the next barrier.
+__device__ __forceinline__ void block_minmax(float& mn, float& mx, float2* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if (lane == 0) scratch[warp] = make_float2(mn, mx);
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  const float2 v = scratch[lane < nw ? lane : 0];
+  mn = v.x;
+  mx = v.y;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+}
+
 // Scale, reciprocal scale and zero point of one activation row from its min
 // and max. Asymmetric: tflite/kernels/internal/reference/portable_tensor_utils.cc:74-108
 // (range widened to include 0, scale and the two zero-point candidates in
@@ -94,8 +116,9 @@ __device__ __forceinline__ void quantize_smem_row(const float* xs, int k, int k_
                                   int8_t* q_tiled, float* scales, int32_t* zps, float* red) {
   __shared__ float s_inv;
   __shared__ int s_zp, s_zero;
-  mn = block_reduce(mn, [](float a, float b) { return fminf(a, b); }, mn, red);
-  mx = block_reduce(mx, [](float a, float b) { return fmaxf(a, b); }, mx, red);
+  __shared__ float2 s_mm[32];
+  (void)red;
+  block_minmax(mn, mx, s_mm);
   if (threadIdx.x == 0) {
     float sf, inv;
     int zp, zero_row;

@@ -364,8 +364,9 @@ __global__ void sdpa_merge_kernel(const SdpaParams p, const int chunk_tokens, co
 template <int H>
 __global__ void __launch_bounds__(1024) sdpa_merge_quant_kernel(const SdpaParams p, const int chunk_tokens,
                                                               const int chunks_max) {
-  extern __shared__ float xs[];
+  extern __shared__ float xs[];        // n * H merged outputs, then n * chunks_max weights
   __shared__ float red[32];
+  __shared__ float s_linv[64];         // 1 / softmax denominator per head
   pdl_enter();
   const int b = blockIdx.x;
   const int group = p.n / p.nkv;
@@ -373,21 +374,48 @@ __global__ void __launch_bounds__(1024) sdpa_merge_quant_kernel(const SdpaParams
   const int chunks = (len + chunk_tokens - 1) / chunk_tokens;
   const size_t cstride = 8 * partial_stride(H);
   const int width = p.n * H;
+  float* wts = xs + width;              // [head][chunk]: exp2(m_chunk - m_head)
+  auto head_base = [&](int head) {
+    const int kvh = head / group, hg = head % group;
+    return p.ws + ((((size_t)b * p.nkv + kvh) * chunks_max) * 8 + hg) * partial_stride(H);
+  };
+  // one warp per head: maximum over the chunks, the chunks' weights and the denominator
+  for (int head = threadIdx.x >> 5; head < p.n; head += blockDim.x >> 5) {
+    const int lane = threadIdx.x & 31;
+    const float* base = head_base(head);
+    float mm = -CUDART_INF_F;
+    for (int c = lane; c < chunks; c += 32) mm = fmaxf(mm, base[c * cstride + H]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
+    float l = 0.0f;
+    for (int c = lane; c < chunks; c += 32) {
+      const float f = exp2f(base[c * cstride + H] - muse);
+      wts[head * chunks_max + c] = f;
+      l += f * base[c * cstride + H + 1];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) s_linv[head & 63] = l;
+  }
+  __syncthreads();
   float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
   for (int idx = threadIdx.x; idx < width; idx += blockDim.x) {
     const int head = idx / H, d = idx % H;
-    const int kvh = head / group, hg = head % group;
-    const float* base = p.ws + ((((size_t)b * p.nkv + kvh) * chunks_max) * 8 + hg) * partial_stride(H);
-    float mm = -CUDART_INF_F;
-    for (int c = 0; c < chunks; ++c) mm = fmaxf(mm, base[c * cstride + H]);
-    const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
-    float acc = 0.0f, l = 0.0f;
-    for (int c = 0; c < chunks; ++c) {
-      const float f = exp2f(base[c * cstride + H] - muse);
-      acc += f * base[c * cstride + d];
-      l += f * base[c * cstride + H + 1];
+    const float* base = head_base(head) + d;
+    const float* w = wts + head * chunks_max;
+    float acc = 0.0f;
+    int c = 0;
+    for (; c + 4 <= chunks; c += 4) {   // four independent loads in flight per thread
+      const float a0 = base[(c + 0) * cstride], a1 = base[(c + 1) * cstride];
+      const float a2 = base[(c + 2) * cstride], a3 = base[(c + 3) * cstride];
+      acc += w[c] * a0;
+      acc += w[c + 1] * a1;
+      acc += w[c + 2] * a2;
+      acc += w[c + 3] * a3;
     }
-    const float v = acc / l;
+    for (; c < chunks; ++c) acc += w[c] * base[c * cstride];
+    const float v = acc / s_linv[head & 63];
     xs[idx] = v;
     if (p.out) static_cast<float*>(p.out)[(size_t)b * width + idx] = v;
     mn = fminf(mn, v);
@@ -478,8 +506,13 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
   }
   if (e != cudaSuccess) return e;
   if (p.q_tiled_out) {
-    return launch_chained(sdpa_merge_quant_kernel<H>, dim3(p.b), dim3(1024), sizeof(float) * p.n * H, s, p, chunk_tokens,
-                          chunks_max);
+    if (p.n > 64) return cudaErrorInvalidValue;
+    const size_t smem = sizeof(float) * ((size_t)p.n * H + (size_t)p.n * chunks_max);
+    if (smem > 48 * 1024) {
+      cudaError_t ea = cudaFuncSetAttribute(sdpa_merge_quant_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (ea != cudaSuccess) return ea;
+    }
+    return launch_chained(sdpa_merge_quant_kernel<H>, dim3(p.b), dim3(1024), smem, s, p, chunk_tokens, chunks_max);
   }
   return launch_chained(sdpa_merge_kernel<H, QF32>, dim3(p.n, p.b), dim3(H), 0, s, p, chunk_tokens, chunks_max);
 }

@@ -180,6 +180,13 @@ class Decoder:
             _check(self.lib.b200_decoder_profile_step(self.handle, tok.ctypes.data_as(ctypes.c_void_p), tok.size, ms, n))
         return {k: (ms[i], n[i]) for i, k in enumerate(("gemv", "attention", "glue"))}
 
+    def time_gemv(self, batch, reps=20):
+        """(ms, launches) of one step's projections alone, replayed as a CUDA graph (see the header)."""
+        ms, n = ctypes.c_float(), ctypes.c_int()
+        with torch.cuda.device(self.device):
+            _check(self.lib.b200_decoder_time_gemv(self.handle, batch, reps, ctypes.byref(ms), ctypes.byref(n)))
+        return ms.value, n.value
+
     @property
     def launches_per_step(self):
         return self.lib.b200_decoder_launches_per_step(self.handle)
