@@ -177,6 +177,15 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# DRAM bytes moved per algorithmic byte by the GEMV kernels, from ncu captures of single launches
+# (dram__bytes_read.sum + dram__bytes_write.sum over the launch's algorithmic bytes): 1.002 for
+# fc_umma_kernel on [14336, 4096] and 1.008 for fc_cluster_kernel on [2048, 16384]; the summaries
+# are profiles/fc_umma_kernel_hybrid_14336x4096_m1.md and profiles/fc_cluster_kernel_hybrid_2048x16384_m1.md.
+# A whole step's 2.5 GB cannot be captured under the profiler's size rule, so the per-launch traffic
+# reported here is this ratio times the launch's algorithmic bytes (traffic grows with the weights).
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.004
+
+
 def weight_bytes(cfg):
     qd, kd = cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"]
     per_layer = cfg["d_model"] * (qd + 2 * kd) + qd * cfg["d_model"] + 3 * cfg["d_model"] * cfg["d_ff"]
@@ -336,9 +345,13 @@ def run_ours(args):
             "gpu_launches": launches * args.steps,
             "launches_per_step": launches,
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "fc_umma_kernel (streamed int8 GEMV, all projections of one step)",
+            "roofline": {"bound": "hbm", "kernel": "fc_umma_kernel + fc_cluster_kernel (streamed int8 GEMV, all projections of one step)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if achieved else None,
-                         "peak_kind": peak_kind, "traffic": None, "launches": gemv_launches,
+                         "peak_kind": peak_kind,
+                         "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * gemv_bytes / gemv_launches,
+                         "traffic_unit": "bytes per launch (average over the step's GEMV launches), ncu ratio x "
+                                         "algorithmic bytes",
+                         "algorithmic_bytes_per_launch": gemv_bytes / gemv_launches, "launches": gemv_launches,
                          "algorithmic_bytes_per_step": gemv_bytes, "gemv_ms_per_step": gemv_ms,
                          "avg_launch_us": gemv_ms * 1e3 / gemv_launches,
                          "timing": "CUDA events around a graph of the step's GEMV launches alone, on the launching stream",

@@ -23,6 +23,7 @@
 // count sums the contributors' slots and runs the epilogue. Integer addition
 // makes the result bit-equal to a serial sum.
 // Every wait is bounded (see mbar_wait_bounded); TMEM is always freed.
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -357,8 +358,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
 // For layers with few n tiles (attention and down projections at decode time) the reduction over K
 // must be split across SMs to pull the weights fast enough, and merging the pieces through global
 // memory costs more than streaming them. Here the `split` CTAs that share an n tile form one
-// thread-block cluster: each accumulates its k range in TMEM, then sends every 128/split-row slice
-// of its int32 accumulator to the CTA that owns those rows through distributed shared memory
+// thread-block cluster: each accumulates its k range in TMEM, then sends every ceil(128/split)-row
+// slice of its int32 accumulator to the CTA that owns those rows through distributed shared memory
 // (reduce-scatter); after one cluster barrier each CTA adds the `split` pieces of its own rows and
 // runs the epilogue on them. No global scratch, no counters, no fences; integer addition keeps the
 // result bit-equal to a serial sum.
@@ -366,7 +367,7 @@ template <int NB>
 struct ClusterLayout {
   static constexpr int kQBytes = NB * kTileK8;
   static constexpr int kStageBytes = kTileBytes + kQBytes;
-  static constexpr int kRedBytes = kTileN * NB * 4;  // split x (128 / split) rows x NB columns of int32
+  static constexpr int kRedBytes = (kTileN + 8) * NB * 4;  // split x ceil(128 / split) rows x NB columns of int32
   static constexpr int kStagesRaw = (200 * 1024 - kRedBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
   static constexpr int kBarriers = 2 * kStages + 1;
@@ -408,7 +409,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
   const int nt = blockIdx.x / split;
   const int kt_begin = (int)((long long)p.k_tiles * rank / split);
   const int kt_end = (int)((long long)p.k_tiles * (rank + 1) / split);
-  const int rows_per_owner = kTileN / split;
+  const int rows_per_owner = (kTileN + split - 1) / split;  // the last owner may hold fewer
 
   if (tid == 0) {
     for (int s = 0; s < L::kStages; ++s) {
@@ -487,11 +488,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
     __syncwarp();
   }
 
-  // Rows this thread finishes after the exchange: row r_own of this CTA's slice, columns col0, col0 + split, ...
+  // Rows this thread finishes after the exchange: row r_own of this CTA's slice, columns col0,
+  // col0 + col_step, ... (threads beyond the last whole group of rows_per_owner stay idle).
   const int etid = tid - 64;
+  const int col_step = kEpiThreads / rows_per_owner;
   const int r_own = etid >= 0 ? etid % rows_per_owner : 0;
   const int col0 = etid >= 0 ? etid / rows_per_owner : 0;
-  const int n_own = nt * kTileN + rank * rows_per_owner + r_own;
+  const int row_own = rank * rows_per_owner + r_own;  // row of the n tile
+  const bool owns = etid >= 0 && col0 < col_step && row_own < kTileN;
+  const int n_own = owns ? nt * kTileN + row_own : p.n;
   int32_t rs = 0, base_i = 0, mult = 0, shift = 0;
   float wsc = 0.0f, bias_f = 0.0f;
   const int m_valid = p.m - m_base < NB ? p.m - m_base : NB;
@@ -557,7 +562,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
   cluster_arrive();  // phase 1: this CTA's pieces are delivered ...
   cluster_wait();    // ... and everyone else's have arrived here
   if (warp >= 2 && n_own < p.n) {
-    for (int col = col0; col < m_valid; col += split) {
+    for (int col = col0; col < m_valid; col += col_step) {
       int32_t v = 0;
       for (int src = 0; src < split; ++src) v += red[(src * NB + col) * rows_per_owner + r_own];
       store_output<EPI>(p, m_base + col, n_own, v, rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[col], sh->in_aux[col]);
@@ -633,13 +638,13 @@ cudaError_t launch_umma_nb(const FcParams& p_in, int m_base, int nb, cudaStream_
 // better served by the kernels above (many n tiles, or a single k tile).
 template <int NB, int EPI>
 int plan_cluster_split(const FcParams& p) {
-  if (const char* e = getenv("B200_FC_CLUSTER"))  // measurement knob
+  if (const char* e = getenv("B200_FC_CLUSTER"))  // measurement knob: 0 turns the cluster kernel off
     if (e[0] == '0') return 0;
   const int sms = device_sm_count();
   if (p.n_tiles * 2 >= sms || p.k_tiles < 2) return 0;
   using L = ClusterLayout<NB>;
   auto kernel = fc_cluster_kernel<NB, EPI>;
-  static int capacity[64][3] = {{0}};  // [device][split index]: co-resident clusters, -1 = query failed
+  static int capacity[64][9] = {{0}};  // [device][split]: co-resident clusters, -1 = query failed
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -651,11 +656,15 @@ int plan_cluster_split(const FcParams& p) {
     }
     configured[dev] = true;
   }
-  const int splits[3] = {8, 4, 2};
-  for (int i = 0; i < 3; ++i) {
-    const int split = splits[i];
-    if (split > p.k_tiles) continue;
-    if (capacity[dev][i] == 0) {
+  if (const char* e = getenv("B200_FC_CLUSTER")) {  // measurement knob: force a split
+    const int v = atoi(e);
+    if (v >= 2 && v <= 8 && v <= p.k_tiles) return v;
+  }
+  // the split that puts the most SMs to work with every cluster resident at once
+  int best = 0;
+  for (int split = 8; split >= 2; --split) {
+    if (split > p.k_tiles || p.n_tiles * split > sms) continue;
+    if (capacity[dev][split] == 0) {
       cudaLaunchConfig_t cfg;
       memset(&cfg, 0, sizeof(cfg));
       cfg.gridDim = dim3(split * 16);
@@ -673,11 +682,15 @@ int plan_cluster_split(const FcParams& p) {
         cudaGetLastError();
         n = -1;
       }
-      capacity[dev][i] = n;
+      capacity[dev][split] = n;
+      if (getenv("B200_FC_VERBOSE")) fprintf(stderr, "[b200] cluster size %d: %d clusters resident (NB=%d)\n", split, n, NB);
     }
-    if (capacity[dev][i] >= p.n_tiles) return split;
+    if (capacity[dev][split] >= p.n_tiles) {
+      best = split;
+      break;
+    }
   }
-  return 0;
+  return best;
 }
 
 template <int NB, int EPI>
