@@ -62,7 +62,7 @@ struct b200_decoder {
   DevBuf embed_table, embed_scales, final_norm;
   // activations and scratch
   DevBuf tokens, next_tokens, positions, attn_len;
-  DevBuf h, qkv, q, attn, gate_up, logits;
+  DevBuf h, h2, qkv, q, attn, gate_up, logits;  // h / h2: residual stream, ping-pong when the norm is fused into a GEMV
   float *proj = nullptr, *down_out = nullptr;  // inside comm
   DevBuf q_d, q_a, q_f;         // tiled int8 activations for K = d_model, heads*head_dim, d_ff
   DevBuf sc_d, sc_a, sc_f, zp_d, zp_a, zp_f;
@@ -200,10 +200,26 @@ int build_projection(b200_decoder* d, Projection* pr, int k, std::initializer_li
   return B200_OK;
 }
 
+// Residual add + RMS norm + quantization done inside the GEMV (FcParams::prologue).
+struct FusedInput {
+  const float* h_in;
+  const float* delta;
+  const float* gain;
+  float* h_out;
+};
+
 cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_t* q_tiled, const float* scales,
-                   const int32_t* zps, float* y) {
+                   const int32_t* zps, float* y, const FusedInput* fused = nullptr) {
   FcParams p;
   memset(&p, 0, sizeof(p));
+  if (fused) {
+    p.prologue = 1;
+    p.pro_h_in = fused->h_in;
+    p.pro_delta = fused->delta;
+    p.pro_gain = fused->gain;
+    p.pro_h_out = fused->h_out;
+    p.pro_eps = d->cfg.rms_eps;
+  }
   p.w_packed = pr.packed.as<uint8_t>();
   p.q_tiled = q_tiled;
   p.m = batch;
@@ -271,17 +287,42 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
                         c.d_model, c.embed_scale, d->h.as<float>(), d->positions.as<int32_t>(),
                         d->attn_len.as<int32_t>(), epoch, s));
   count();
+  // Opt-in (B200_FUSED_PROLOGUE=1): with one GPU and a decode-sized batch the residual add, RMS norm
+  // and quantization in front of the qkv, gate/up and LM-head projections run inside those GEMVs
+  // (no kernel of their own); the residual stream then alternates between two buffers, because every
+  // CTA reads the old one. Measured on B200 at batch 1 this is 7 % SLOWER than the separate kernel
+  // (1.40 vs 1.30 ms per step): a GEMV's CTAs cannot become resident while the previous GEMV holds
+  // the shared memory, so the prologue's latency is exposed, whereas the small separate kernel runs
+  // beside the previous GEMV and the next one fills its ring meanwhile. Kept for wider rows per SM.
+  static const bool fuse_env = [] {
+    const char* e = getenv("B200_FUSED_PROLOGUE");
+    return e && e[0] == '1';
+  }();
+  const bool fuse_norm = fuse_env && !tp && fc_prologue_supported(batch, c.d_model);
+  // Measurement knob: leave kernels out of the step to read their marginal cost off the step time
+  // (the results are then meaningless). Bits: 1 norm, 2 rope, 4 attention, 8 GeGLU, 16 qkv, 32 o,
+  // 64 gate/up, 128 down, 256 LM head.
+  static const int skip = [] {
+    const char* e = getenv("B200_DEC_SKIP");
+    return e ? atoi(e) : 0;
+  }();
+  float* hbuf[2] = {d->h.as<float>(), d->h2.as<float>()};
+  int cur = 0;
   for (int l = 0; l < c.n_layers; ++l) {
     Layer& L = *d->layers[l];
-    {
+    if (fuse_norm) {
+      const FusedInput fi{hbuf[cur], l == 0 ? nullptr : d->down_out, L.norm1.as<float>(), hbuf[cur ^ 1]};
+      if (!(skip & 16)) DEC_CUDA(run_fc(d, L.qkv, batch, nullptr, nullptr, nullptr, d->qkv.as<float>(), &fi));
+      cur ^= 1;
+    } else {
       const TpExchange x = fused && l > 0 ? make_exchange(d, 2 * l - 1, d->off_part_b) : TpExchange();
-      GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), l == 0 ? nullptr : d->down_out, L.norm1.as<float>(), batch,
+      if (!(skip & 1)) GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), l == 0 ? nullptr : d->down_out, L.norm1.as<float>(), batch,
                                      c.d_model, c.rms_eps, m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(),
                                      d->zp_d.as<int32_t>(), fused && l > 0 ? &x : nullptr, s));
+      count();
+      if (!(skip & 16)) DEC_CUDA(run_fc(d, L.qkv, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), d->qkv.as<float>()));
     }
-    count();
-    DEC_CUDA(run_fc(d, L.qkv, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), d->qkv.as<float>()));
-    GLUE_CUDA(launch_rope_cache(d->qkv.as<float>(), batch, d->hl, d->kvl, c.head_dim, c.rope_base,
+    if (!(skip & 2)) GLUE_CUDA(launch_rope_cache(d->qkv.as<float>(), batch, d->hl, d->kvl, c.head_dim, c.rope_base,
                                d->positions.as<int32_t>(), c.max_seq, d->q.as<float>(), L.k_cache.p, L.v_cache.p,
                                L.k_scale.as<float>(), L.v_scale.as<float>(), c.kv_dtype == B200_DTYPE_I8, s));
     count();
@@ -311,35 +352,42 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
     sp.status = d->zero_ws.as<int>();
     {
       ProfScope scope(d, 1);
-      DEC_CUDA(launch_sdpa_decode(sp, s));
+      if (!(skip & 4)) DEC_CUDA(launch_sdpa_decode(sp, s));
     }
     count(2);
-    DEC_CUDA(run_fc(d, L.o, batch, d->q_a.as<int8_t>(), d->sc_a.as<float>(), d->zp_a.as<int32_t>(), d->proj));
+    if (!(skip & 32)) DEC_CUDA(run_fc(d, L.o, batch, d->q_a.as<int8_t>(), d->sc_a.as<float>(), d->zp_a.as<int32_t>(), d->proj));
     if (int rc = reduce(d->proj, (size_t)batch * c.d_model)) return rc;
-    {
+    if (fuse_norm) {
+      const FusedInput fi{hbuf[cur], d->proj, L.norm2.as<float>(), hbuf[cur ^ 1]};
+      if (!(skip & 64)) DEC_CUDA(run_fc(d, L.gate_up, batch, nullptr, nullptr, nullptr, d->gate_up.as<float>(), &fi));
+      cur ^= 1;
+    } else {
       const TpExchange x = fused ? make_exchange(d, 2 * l, d->off_part_a) : TpExchange();
-      GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->proj, L.norm2.as<float>(), batch, c.d_model, c.rms_eps,
+      if (!(skip & 1)) GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->proj, L.norm2.as<float>(), batch, c.d_model, c.rms_eps,
                                      m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(),
                                      fused ? &x : nullptr, s));
+      count();
+      if (!(skip & 64)) DEC_CUDA(run_fc(d, L.gate_up, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(),
+                      d->gate_up.as<float>()));
     }
-    count();
-    DEC_CUDA(run_fc(d, L.gate_up, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(),
-                    d->gate_up.as<float>()));
-    GLUE_CUDA(launch_geglu_quant(d->gate_up.as<float>(), batch, d->fl, m_alloc, d->q_f.as<int8_t>(), d->sc_f.as<float>(),
+    if (!(skip & 8)) GLUE_CUDA(launch_geglu_quant(d->gate_up.as<float>(), batch, d->fl, m_alloc, d->q_f.as<int8_t>(), d->sc_f.as<float>(),
                                 d->zp_f.as<int32_t>(), s));
     count();
-    DEC_CUDA(run_fc(d, L.down, batch, d->q_f.as<int8_t>(), d->sc_f.as<float>(), d->zp_f.as<int32_t>(), d->down_out));
+    if (!(skip & 128)) DEC_CUDA(run_fc(d, L.down, batch, d->q_f.as<int8_t>(), d->sc_f.as<float>(), d->zp_f.as<int32_t>(), d->down_out));
     if (int rc = reduce(d->down_out, (size_t)batch * c.d_model)) return rc;
   }
-  {
+  float* logits = d_logits_out ? d_logits_out : d->logits.as<float>();
+  if (fuse_norm) {
+    const FusedInput fi{hbuf[cur], d->down_out, d->final_norm.as<float>(), hbuf[cur ^ 1]};
+    if (!(skip & 256)) DEC_CUDA(run_fc(d, d->lm_head, batch, nullptr, nullptr, nullptr, logits, &fi));
+  } else {
     const TpExchange x = fused ? make_exchange(d, 2 * c.n_layers - 1, d->off_part_b) : TpExchange();
-    GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->down_out, d->final_norm.as<float>(), batch, c.d_model, c.rms_eps,
+    if (!(skip & 1)) GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->down_out, d->final_norm.as<float>(), batch, c.d_model, c.rms_eps,
                                    m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(),
                                    fused ? &x : nullptr, s));
+    count();
+    if (!(skip & 256)) DEC_CUDA(run_fc(d, d->lm_head, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), logits));
   }
-  count();
-  float* logits = d_logits_out ? d_logits_out : d->logits.as<float>();
-  DEC_CUDA(run_fc(d, d->lm_head, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), logits));
   if (!tp) {
     GLUE_CUDA(launch_argmax(logits, batch, c.vocab, 0, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
                            d->next_tokens.as<int32_t>(), d->positions.as<int32_t>(), c.max_seq, nullptr, s));
@@ -440,6 +488,7 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
   DEC_CUDA(d->positions.alloc(sizeof(int32_t) * B));
   DEC_CUDA(d->attn_len.alloc(sizeof(int32_t) * B));
   DEC_CUDA(d->h.alloc(sizeof(float) * B * c.d_model));
+  DEC_CUDA(d->h2.alloc(sizeof(float) * B * c.d_model));
   DEC_CUDA(d->qkv.alloc(sizeof(float) * B * (qdim + 2 * kvdim)));
   DEC_CUDA(d->q.alloc(sizeof(float) * B * qdim));
   DEC_CUDA(d->attn.alloc(sizeof(float) * B * qdim));

@@ -29,12 +29,14 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "prologue.cuh"
 
 namespace b200 {
 
 namespace {
 
 constexpr int kUmmaThreads = 192;
+constexpr int kMaxDynamicSmem = 227 * 1024;  // opt-in limit per CTA
 constexpr int kEpiThreads = 128;
 
 struct UmmaShared {
@@ -53,8 +55,10 @@ struct UmmaLayout {
   static constexpr int kStageBytes = kTileBytes + kQBytes;
   static constexpr int kStagesRaw = 200 * 1024 / kStageBytes;
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
-  static constexpr int kBarriers = 2 * kStages + 4;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarriers * 8 + (int)sizeof(UmmaShared) + 16;
+  static constexpr int kBarriers = 2 * kStages + 5;
+  // without the fused prologue's operand buffer, which the launcher adds (k tiles x kQBytes)
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + kBarriers * 8 + (int)sizeof(UmmaShared) + 2 * (int)sizeof(PrologueShared) + 128 + 16;
   static constexpr int kTmemCols = 2 * NB < 32 ? 32 : 2 * NB;
 };
 
@@ -91,7 +95,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
   uint64_t* empty_bar = full_bar + L::kStages;
   uint64_t* acc_full = empty_bar + L::kStages;  // [2]
   uint64_t* acc_empty = acc_full + 2;           // [2]
-  UmmaShared* sh = reinterpret_cast<UmmaShared*>(acc_empty + 2);
+  uint64_t* b_ready = acc_empty + 2;            // fused prologue: the operand rows are in place
+  UmmaShared* sh = reinterpret_cast<UmmaShared*>(b_ready + 1);
+  PrologueShared* ps = reinterpret_cast<PrologueShared*>(sh + 1);
+  uint8_t* bbuf = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ps + 2) + 127) & ~uintptr_t(127));
   volatile int* abort_flag = &sh->abort_flag;
 
   const int tid = threadIdx.x;
@@ -106,6 +113,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
     }
+    mbar_init(b_ready, 1);
     sh->abort_flag = 0;
     sh->last = 0;
     mbar_fence_init();
@@ -132,17 +140,20 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
       // The weights are constants: start streaming them before the kernel that produces the
       // activations has finished (programmatic dependent launch), one ring's worth at most.
       pdl_launch_dependents();
+      const uint32_t stage_tx = p.prologue ? (uint32_t)kTileBytes : (uint32_t)L::kStageBytes;
       uint32_t pre = 0;
       for (long long t = t_begin; t < t_end && pre < (uint32_t)L::kStages; ++t, ++pre) {
         uint8_t* dst = smem + (size_t)pre * L::kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[pre], L::kStageBytes);
+        mbar_arrive_expect_tx(&full_bar[pre], stage_tx);
         bulk_g2s(dst, p.w_packed + (size_t)t * kTileBytes, kTileBytes, &full_bar[pre]);
       }
       pdl_wait();               // activations (and the split-K scratch) are now safe to touch
-      for (uint32_t i = 0; i < pre; ++i) {
-        const int kt = (int)((t_begin + i) % p.k_tiles);
-        const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
-        bulk_g2s(smem + (size_t)i * L::kStageBytes + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[i]);
+      if (!p.prologue) {
+        for (uint32_t i = 0; i < pre; ++i) {
+          const int kt = (int)((t_begin + i) % p.k_tiles);
+          const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
+          bulk_g2s(smem + (size_t)i * L::kStageBytes + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[i]);
+        }
       }
       uint32_t it = pre;
       for (long long t = t_begin + pre; t < t_end; ++t, ++it) {
@@ -150,11 +161,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         const uint32_t ph = (it / L::kStages) & 1u;
         mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, p.status, kStatusWaitTimeoutEmpty);
         uint8_t* dst = smem + (size_t)s * L::kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[s], L::kStageBytes);
+        mbar_arrive_expect_tx(&full_bar[s], stage_tx);
         bulk_g2s(dst, p.w_packed + (size_t)t * kTileBytes, kTileBytes, &full_bar[s]);
-        const int kt = (int)(t % p.k_tiles);
-        const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
-        bulk_g2s(dst + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[s]);
+        if (!p.prologue) {
+          const int kt = (int)(t % p.k_tiles);
+          const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
+          bulk_g2s(dst + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[s]);
+        }
       }
       // never leave with copies in flight (only possible after an abort)
       const uint32_t issued = it;
@@ -170,6 +183,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
       constexpr uint32_t idesc = umma_idesc_s8(NB);
       uint32_t it = 0, seg = 0;
       long long t = t_begin;
+      if (p.prologue) {
+        mbar_wait_bounded(b_ready, 0, abort_flag, p.status, kStatusWaitTimeoutFull);
+        tc_fence_after();
+      }
       while (t < t_end) {
         const long long nt = t / p.k_tiles;
         const long long seg_end = (nt + 1) * p.k_tiles < t_end ? (nt + 1) * p.k_tiles : t_end;
@@ -184,7 +201,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
           mbar_wait_bounded(&full_bar[s], ph, abort_flag, p.status, kStatusWaitTimeoutFull);
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + (size_t)s * L::kStageBytes);
-          const uint32_t b_addr = a_addr + kTileBytes;
+          const uint32_t b_addr =
+              p.prologue ? smem_u32(bbuf) + (uint32_t)(t % p.k_tiles) * (uint32_t)L::kQBytes : a_addr + kTileBytes;
 #pragma unroll
           for (int ks = 0; ks < kTileK8 / 32; ++ks) {
             // two 16-byte K chunks per MMA: 128 B apart; 8-row groups 1 KiB apart
@@ -232,17 +250,22 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
     // those of the first segment are fetched while the predecessor kernel is still running
     if (t_begin < t_end) load_channel_constants((int)(t_begin / p.k_tiles) * kTileN + row_in_tile);
     pdl_wait();  // the activation rows' scales are written by the previous kernel
-    for (int i = etid; i < NB; i += kEpiThreads) {
-      const int m = m_base + i;
-      const bool ok = m < p.m;
-      sh->in_scale[i] = (ok && p.in_scales) ? p.in_scales[m] : 0.0f;
-      if constexpr (EPI == kEpiHybridF32) {
-        sh->in_aux[i] = (ok && p.in_zps) ? p.in_zps[m] : 0;
-      } else {
-        sh->in_aux[i] = (ok && p.x_sums) ? p.x_sums[m] : 0;
+    if (p.prologue) {
+      prologue_norm_quant(p, bbuf, NB, 0, p.k_tiles, sh->in_scale, sh->in_aux, ps, etid, blockIdx.x == 0, 1);
+      if (etid == 0) mbar_arrive(b_ready);
+    } else {
+      for (int i = etid; i < NB; i += kEpiThreads) {
+        const int m = m_base + i;
+        const bool ok = m < p.m;
+        sh->in_scale[i] = (ok && p.in_scales) ? p.in_scales[m] : 0.0f;
+        if constexpr (EPI == kEpiHybridF32) {
+          sh->in_aux[i] = (ok && p.in_zps) ? p.in_zps[m] : 0;
+        } else {
+          sh->in_aux[i] = (ok && p.x_sums) ? p.x_sums[m] : 0;
+        }
       }
+      named_barrier(1, kEpiThreads);
     }
-    named_barrier(1, kEpiThreads);
     uint32_t seg = 0;
     long long t = t_begin;
     while (t < t_end) {
@@ -370,27 +393,12 @@ struct ClusterLayout {
   static constexpr int kRedBytes = (kTileN + 8) * NB * 4;  // split x ceil(128 / split) rows x NB columns of int32
   static constexpr int kStagesRaw = (200 * 1024 - kRedBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
-  static constexpr int kBarriers = 2 * kStages + 1;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kRedBytes + kBarriers * 8 + (int)sizeof(UmmaShared) + 16;
+  static constexpr int kBarriers = 2 * kStages + 2;
+  // without the fused prologue's operand buffer, which the launcher adds
+  static constexpr int kSmemBytes = kStages * kStageBytes + kRedBytes + kBarriers * 8 + (int)sizeof(UmmaShared) +
+                                    2 * (int)sizeof(PrologueShared) + 128 + 16;
   static constexpr int kTmemCols = NB < 32 ? 32 : NB;
 };
-
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-// Address, in the cluster-wide shared window, of `local` inside CTA `rank` of this cluster.
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void st_cluster_u32(uint32_t addr, int32_t v) {
-  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
 
 template <int NB, int EPI>
 __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcParams p, const int m_base, const int split) {
@@ -400,7 +408,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes + L::kRedBytes);
   uint64_t* empty_bar = full_bar + L::kStages;
   uint64_t* acc_full = empty_bar + L::kStages;
-  UmmaShared* sh = reinterpret_cast<UmmaShared*>(acc_full + 1);
+  uint64_t* b_ready = acc_full + 1;  // fused prologue: the operand rows are in place
+  UmmaShared* sh = reinterpret_cast<UmmaShared*>(b_ready + 1);
+  PrologueShared* ps = reinterpret_cast<PrologueShared*>(sh + 1);
+  uint8_t* bbuf = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ps + 2) + 127) & ~uintptr_t(127));
   volatile int* abort_flag = &sh->abort_flag;
 
   const int tid = threadIdx.x;
@@ -417,6 +428,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(acc_full, 1);
+    mbar_init(b_ready, 1);
     sh->abort_flag = 0;
     mbar_fence_init();
   }
@@ -434,15 +446,18 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
   if (warp == 0) {
     if (lane == 0) {
       pdl_launch_dependents();
+      const uint32_t stage_tx = p.prologue ? (uint32_t)kTileBytes : (uint32_t)L::kStageBytes;
       uint32_t pre = 0;
       for (int kt = kt_begin; kt < kt_end && pre < (uint32_t)L::kStages; ++kt, ++pre) {
-        mbar_arrive_expect_tx(&full_bar[pre], L::kStageBytes);
+        mbar_arrive_expect_tx(&full_bar[pre], stage_tx);
         bulk_g2s(smem + (size_t)pre * L::kStageBytes, w_tiles + (size_t)kt * kTileBytes, kTileBytes, &full_bar[pre]);
       }
       pdl_wait();
-      for (uint32_t i = 0; i < pre; ++i) {
-        const size_t off = (((size_t)(kt_begin + i) * m_groups_alloc) + mg_base) * 1024;
-        bulk_g2s(smem + (size_t)i * L::kStageBytes + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[i]);
+      if (!p.prologue) {
+        for (uint32_t i = 0; i < pre; ++i) {
+          const size_t off = (((size_t)(kt_begin + i) * m_groups_alloc) + mg_base) * 1024;
+          bulk_g2s(smem + (size_t)i * L::kStageBytes + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[i]);
+        }
       }
       uint32_t it = pre;
       for (int kt = kt_begin + (int)pre; kt < kt_end; ++kt, ++it) {
@@ -450,10 +465,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
         const uint32_t ph = (it / L::kStages) & 1u;
         mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, p.status, kStatusWaitTimeoutEmpty);
         uint8_t* dst = smem + (size_t)s * L::kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[s], L::kStageBytes);
+        mbar_arrive_expect_tx(&full_bar[s], stage_tx);
         bulk_g2s(dst, w_tiles + (size_t)kt * kTileBytes, kTileBytes, &full_bar[s]);
-        const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
-        bulk_g2s(dst + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[s]);
+        if (!p.prologue) {
+          const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
+          bulk_g2s(dst + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[s]);
+        }
       }
       const uint32_t issued = it;  // never leave with copies in flight (only possible after an abort)
       for (uint32_t back = 0; back < (uint32_t)L::kStages && back < issued; ++back) {
@@ -467,13 +484,18 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
     if (lane == 0 && kt_begin < kt_end) {
       constexpr uint32_t idesc = umma_idesc_s8(NB);
       uint32_t it = 0;
+      if (p.prologue) {
+        mbar_wait_bounded(b_ready, 0, abort_flag, p.status, kStatusWaitTimeoutFull);
+        tc_fence_after();
+      }
       for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
         const int s = it % L::kStages;
         const uint32_t ph = (it / L::kStages) & 1u;
         mbar_wait_bounded(&full_bar[s], ph, abort_flag, p.status, kStatusWaitTimeoutFull);
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + (size_t)s * L::kStageBytes);
-        const uint32_t b_addr = a_addr + kTileBytes;
+        const uint32_t b_addr =
+            p.prologue ? smem_u32(bbuf) + (uint32_t)(kt - kt_begin) * (uint32_t)L::kQBytes : a_addr + kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < kTileK8 / 32; ++ks) {
           const uint64_t a_desc = umma_smem_desc(a_addr + ks * 256, 128, 1024);
@@ -517,14 +539,19 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
       }
     }
     pdl_wait();
-    for (int i = etid; i < NB; i += kEpiThreads) {
-      const int m = m_base + i;
-      const bool ok = m < p.m;
-      sh->in_scale[i] = (ok && p.in_scales) ? p.in_scales[m] : 0.0f;
-      if constexpr (EPI == kEpiHybridF32) {
-        sh->in_aux[i] = (ok && p.in_zps) ? p.in_zps[m] : 0;
-      } else {
-        sh->in_aux[i] = (ok && p.x_sums) ? p.x_sums[m] : 0;
+    if (p.prologue) {
+      prologue_norm_quant(p, bbuf, NB, kt_begin, kt_end, sh->in_scale, sh->in_aux, ps, etid, blockIdx.x == 0, 1);
+      if (etid == 0) mbar_arrive(b_ready);
+    } else {
+      for (int i = etid; i < NB; i += kEpiThreads) {
+        const int m = m_base + i;
+        const bool ok = m < p.m;
+        sh->in_scale[i] = (ok && p.in_scales) ? p.in_scales[m] : 0.0f;
+        if constexpr (EPI == kEpiHybridF32) {
+          sh->in_aux[i] = (ok && p.in_zps) ? p.in_zps[m] : 0;
+        } else {
+          sh->in_aux[i] = (ok && p.x_sums) ? p.x_sums[m] : 0;
+        }
       }
     }
     // this CTA's accumulator row (zero when its k range is empty)
@@ -612,13 +639,18 @@ cudaError_t launch_umma_one(const FcParams& p, int m_base, cudaStream_t s) {
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
   if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   FcParams q = p;
   const int ctas = plan_ctas(&q);
-  return launch_chained(kernel, dim3(ctas), dim3(kUmmaThreads), (size_t)L::kSmemBytes, s, q, m_base);
+  size_t smem = (size_t)L::kSmemBytes;
+  if (p.prologue) {
+    if (!fc_prologue_supported(p.m, p.k) || NB != 16 || m_base != 0) return cudaErrorInvalidValue;
+    smem += (size_t)p.k_tiles * L::kQBytes;
+  }
+  return launch_chained(kernel, dim3(ctas), dim3(kUmmaThreads), smem, s, q, m_base);
 }
 
 template <int EPI>
@@ -650,7 +682,7 @@ int plan_cluster_split(const FcParams& p) {
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
   if (!configured[dev]) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes) != cudaSuccess) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem) != cudaSuccess) {
       cudaGetLastError();
       return 0;
     }
@@ -669,7 +701,7 @@ int plan_cluster_split(const FcParams& p) {
       memset(&cfg, 0, sizeof(cfg));
       cfg.gridDim = dim3(split * 16);
       cfg.blockDim = dim3(kUmmaThreads);
-      cfg.dynamicSmemBytes = L::kSmemBytes;
+      cfg.dynamicSmemBytes = L::kSmemBytes + 4 * L::kQBytes;  // as with the fused prologue's operand buffer
       cudaLaunchAttribute attr[1];
       attr[0].id = cudaLaunchAttributeClusterDimension;
       attr[0].val.clusterDim.x = split;
@@ -696,8 +728,13 @@ int plan_cluster_split(const FcParams& p) {
 template <int NB, int EPI>
 cudaError_t launch_cluster_one(const FcParams& p, int m_base, int split, cudaStream_t s) {
   using L = ClusterLayout<NB>;
-  return launch_chained_cluster(fc_cluster_kernel<NB, EPI>, dim3(p.n_tiles * split), dim3(kUmmaThreads),
-                                (size_t)L::kSmemBytes, split, s, p, m_base, split);
+  size_t smem = (size_t)L::kSmemBytes;
+  if (p.prologue) {
+    if (!fc_prologue_supported(p.m, p.k) || NB != 16 || m_base != 0) return cudaErrorInvalidValue;
+    smem += (size_t)((p.k_tiles + split - 1) / split + 1) * L::kQBytes;
+  }
+  return launch_chained_cluster(fc_cluster_kernel<NB, EPI>, dim3(p.n_tiles * split), dim3(kUmmaThreads), smem, split, s,
+                                p, m_base, split);
 }
 
 // One pass of nb <= 64 activation rows: the cluster kernel when the shape suits it. Returns
@@ -728,6 +765,8 @@ cudaError_t launch_pass(const FcParams& p, int m_base, int nb, cudaStream_t s) {
 }
 
 }  // namespace
+
+bool fc_prologue_supported(int m, int k) { return m >= 1 && m <= kPrologueMaxM && k >= 1 && k <= kPrologueMaxK; }
 
 int umma_rows_per_pass(int m) {
   int nb = 16;

@@ -68,6 +68,19 @@ struct FcParams {
   int32_t* ws_part;   // tcgen05 path: per-CTA partial slots, no initial contents needed
   int32_t* ws_count;
   int* status;
+  // Fused input prologue (decode-sized m, see prologue.cuh): when `prologue` is 1 the activation rows
+  // are built inside the kernel from the residual stream instead of being read from q_tiled:
+  // v = pro_h_in + pro_delta (delta may be null), pro_h_out = v, x = rms_norm(v, pro_eps) * pro_gain,
+  // x quantized per row. q_tiled, in_scales and in_zps are ignored; pro_scales_out / pro_zps_out
+  // (optional) receive the rows' parameters.
+  int prologue;
+  const float* pro_h_in;
+  const float* pro_delta;
+  const float* pro_gain;
+  float* pro_h_out;
+  float pro_eps;
+  float* pro_scales_out;
+  int32_t* pro_zps_out;
   int max_ctas;              // 0 = chosen per shape
   int whole_tiles;           // set by the launcher: CTAs own whole n tiles (no split-K)
   int debug_flags;           // measurement only: 1 = skip the MMAs, 2 = skip the epilogue
@@ -80,6 +93,8 @@ cudaError_t launch_fc_i8(const FcParams& p, FcEpilogue epi, cudaStream_t s);
 // time and the tiled activation buffer must hold a multiple of that many rows.
 cudaError_t launch_fc_i8_umma(const FcParams& p, FcEpilogue epi, cudaStream_t s);
 int umma_rows_per_pass(int m);
+// Whether FcParams::prologue can be used for these sizes (the tcgen05 kernels only).
+bool fc_prologue_supported(int m, int k);
 // Blockwise 4-bit weights, float out.
 cudaError_t launch_fc_w4(const FcParams& p, cudaStream_t s);
 

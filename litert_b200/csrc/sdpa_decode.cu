@@ -379,6 +379,17 @@ __global__ void __launch_bounds__(1024) sdpa_merge_quant_kernel(const SdpaParams
     const int kvh = head / group, hg = head % group;
     return p.ws + ((((size_t)b * p.nkv + kvh) * chunks_max) * 8 + hg) * partial_stride(H);
   };
+  // The partial outputs of this thread's first two elements (first kPre chunks) are requested
+  // before anything else, so that their L2 round trips overlap the per-head statistics below.
+  constexpr int kPre = 16;
+  float pre[2][kPre];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int idx = threadIdx.x + e * blockDim.x;
+    const float* base = idx < width ? head_base(idx / H) + idx % H : nullptr;
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) pre[e][j] = (base && j < chunks) ? base[j * cstride] : 0.0f;
+  }
   // one warp per head: maximum over the chunks, the chunks' weights and the denominator
   for (int head = threadIdx.x >> 5; head < p.n; head += blockDim.x >> 5) {
     const int lane = threadIdx.x & 31;
@@ -400,19 +411,26 @@ __global__ void __launch_bounds__(1024) sdpa_merge_quant_kernel(const SdpaParams
   }
   __syncthreads();
   float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
-  for (int idx = threadIdx.x; idx < width; idx += blockDim.x) {
+  int e = 0;
+  for (int idx = threadIdx.x; idx < width; idx += blockDim.x, ++e) {
     const int head = idx / H, d = idx % H;
     const float* base = head_base(head) + d;
     const float* w = wts + head * chunks_max;
     float acc = 0.0f;
     int c = 0;
-    for (; c + 4 <= chunks; c += 4) {   // four independent loads in flight per thread
-      const float a0 = base[(c + 0) * cstride], a1 = base[(c + 1) * cstride];
-      const float a2 = base[(c + 2) * cstride], a3 = base[(c + 3) * cstride];
-      acc += w[c] * a0;
-      acc += w[c + 1] * a1;
-      acc += w[c + 2] * a2;
-      acc += w[c + 3] * a3;
+    if (e < 2) {
+      const int npre = chunks < kPre ? chunks : kPre;
+#pragma unroll
+      for (int j = 0; j < kPre; ++j)
+        if (j < npre) acc += w[j] * (e == 0 ? pre[0][j] : pre[1][j]);
+      c = npre;
+    }
+    for (; c + 8 <= chunks; c += 8) {   // eight independent loads in flight per thread
+      float a[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = base[(c + j) * cstride];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += w[c + j] * a[j];
     }
     for (; c < chunks; ++c) acc += w[c] * base[c * cstride];
     const float v = acc / s_linv[head & 63];
