@@ -67,6 +67,8 @@ struct b200_decoder {
   DevBuf q_d, q_a, q_f;         // tiled int8 activations for K = d_model, heads*head_dim, d_ff
   DevBuf sc_d, sc_a, sc_f, zp_d, zp_a, zp_f;
   DevBuf zero_ws, sdpa_ws, arg_val, arg_idx;
+  DevBuf trace;        // B200_DEC_TRACE=<file>: 4 timer stamps per GEMV launch of a step
+  int trace_next = 0;  // slot of the next GEMV launch while a step is being enqueued
   int32_t *h_tokens_pinned = nullptr, *h_next_pinned = nullptr;
   // tensor parallelism: this rank's share of the heads, KV heads, feed-forward units and vocabulary rows
   int hl = 0, kvl = 0, fl = 0, vl = 0;
@@ -200,6 +202,8 @@ int build_projection(b200_decoder* d, Projection* pr, int k, std::initializer_li
   return B200_OK;
 }
 
+constexpr int kTraceSlots = 256;
+
 // Residual add + RMS norm + quantization done inside the GEMV (FcParams::prologue).
 struct FusedInput {
   const float* h_in;
@@ -241,6 +245,7 @@ cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_
   p.ws_acc = reinterpret_cast<int32_t*>(z + zero_ws_acc_off());
   p.ws_part = reinterpret_cast<int32_t*>(z + b200::zero_ws_part_off());
   ++d->launches;
+  if (d->trace.p && d->trace_next < kTraceSlots) p.trace = d->trace.as<unsigned long long>() + 4 * d->trace_next++;
   ProfScope scope(d, 0);
   return launch_fc_i8_umma(p, kEpiHybridF32, d->stream);
 }
@@ -274,6 +279,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
   if (tp && !fused && !d->allreduce)
     return dec_fail(B200_ERR_INVALID_ARGUMENT, "tensor-parallel decoder: connect the peers or set an all-reduce first");
   d->launches = 0;
+  d->trace_next = 0;
   auto count = [&](int n = 1) { d->launches += n; };
   // sum over ranks of a partial projection output through the caller's collective (not a kernel of ours)
   auto reduce = [&](float* buf, size_t n) -> int {
@@ -306,6 +312,17 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
     const char* e = getenv("B200_DEC_SKIP");
     return e ? atoi(e) : 0;
   }();
+  // Rotary embedding, cache append, attention and output quantization as one cluster kernel where
+  // the shape allows (one KV head on this rank, at most eight query heads); B200_ATTN_STEP=0 keeps
+  // the three separate kernels.
+  static const bool attn_env = [] {
+    const char* e = getenv("B200_ATTN_STEP");
+    return !(e && e[0] == '0');
+  }();
+  // (one cluster of 8 CTAs per sequence, each with most of an SM's shared memory: beyond about a
+  // sixth of the SMs in sequences the chunked kernels do better: 1.69 vs 1.86 ms per step at batch 32)
+  const bool attn_one_launch = attn_env && batch * 8 <= device_sm_count() / 2 &&
+                               attn_step_supported(d->hl, d->kvl, c.head_dim, c.kv_dtype == B200_DTYPE_I8 ? 1 : 0);
   float* hbuf[2] = {d->h.as<float>(), d->h2.as<float>()};
   int cur = 0;
   for (int l = 0; l < c.n_layers; ++l) {
@@ -322,39 +339,68 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
       count();
       if (!(skip & 16)) DEC_CUDA(run_fc(d, L.qkv, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), d->qkv.as<float>()));
     }
-    if (!(skip & 2)) GLUE_CUDA(launch_rope_cache(d->qkv.as<float>(), batch, d->hl, d->kvl, c.head_dim, c.rope_base,
-                               d->positions.as<int32_t>(), c.max_seq, d->q.as<float>(), L.k_cache.p, L.v_cache.p,
-                               L.k_scale.as<float>(), L.v_scale.as<float>(), c.kv_dtype == B200_DTYPE_I8, s));
-    count();
-    SdpaParams sp;
-    memset(&sp, 0, sizeof(sp));
-    sp.q = d->q.p;
-    sp.k = L.k_cache.p;
-    sp.v = L.v_cache.p;
-    sp.k_scale = L.k_scale.as<float>();
-    sp.v_scale = L.v_scale.as<float>();
-    sp.lengths = d->attn_len.as<int32_t>();
-    sp.out = nullptr;  // only the quantized rows are needed downstream
-    sp.q_tiled_out = d->q_a.as<int8_t>();
-    sp.out_scales = d->sc_a.as<float>();
-    sp.out_zps = d->zp_a.as<int32_t>();
-    sp.m_alloc = m_alloc;
-    sp.b = batch;
-    sp.n = d->hl;
-    sp.nkv = d->kvl;
-    sp.h = c.head_dim;
-    sp.s_max = c.max_seq;
-    sp.q_dtype = 1;
-    sp.kv_dtype = c.kv_dtype == B200_DTYPE_I8 ? 1 : 0;
-    sp.scale = 1.0f / sqrtf((float)c.head_dim);
-    sp.ws = d->sdpa_ws.as<float>();
-    sp.ws_bytes = d->sdpa_ws.bytes;
-    sp.status = d->zero_ws.as<int>();
-    {
-      ProfScope scope(d, 1);
-      if (!(skip & 4)) DEC_CUDA(launch_sdpa_decode(sp, s));
+    if (attn_one_launch) {
+      AttnStepParams ap;
+      memset(&ap, 0, sizeof(ap));
+      ap.qkv = d->qkv.as<float>();
+      ap.positions = d->positions.as<int32_t>();
+      ap.k_cache = L.k_cache.p;
+      ap.v_cache = L.v_cache.p;
+      ap.k_scale = L.k_scale.as<float>();
+      ap.v_scale = L.v_scale.as<float>();
+      ap.b = batch;
+      ap.n = d->hl;
+      ap.h = c.head_dim;
+      ap.s_max = c.max_seq;
+      ap.kv_dtype = c.kv_dtype == B200_DTYPE_I8 ? 1 : 0;
+      ap.rope_base = c.rope_base;
+      ap.scale = 1.0f / sqrtf((float)c.head_dim);
+      ap.q_tiled_out = d->q_a.as<int8_t>();
+      ap.out_scales = d->sc_a.as<float>();
+      ap.out_zps = d->zp_a.as<int32_t>();
+      ap.m_alloc = m_alloc;
+      ap.status = d->zero_ws.as<int>();
+      if (d->trace.p) ap.trace = d->trace.as<unsigned long long>() + 4 * kTraceSlots + 16 * l;
+      {
+        ProfScope scope(d, 1);
+        if (!(skip & 4)) DEC_CUDA(launch_attn_step(ap, s));
+      }
+      count();
+    } else {
+      if (!(skip & 2)) GLUE_CUDA(launch_rope_cache(d->qkv.as<float>(), batch, d->hl, d->kvl, c.head_dim, c.rope_base,
+                                 d->positions.as<int32_t>(), c.max_seq, d->q.as<float>(), L.k_cache.p, L.v_cache.p,
+                                 L.k_scale.as<float>(), L.v_scale.as<float>(), c.kv_dtype == B200_DTYPE_I8, s));
+      count();
+      SdpaParams sp;
+      memset(&sp, 0, sizeof(sp));
+      sp.q = d->q.p;
+      sp.k = L.k_cache.p;
+      sp.v = L.v_cache.p;
+      sp.k_scale = L.k_scale.as<float>();
+      sp.v_scale = L.v_scale.as<float>();
+      sp.lengths = d->attn_len.as<int32_t>();
+      sp.out = nullptr;  // only the quantized rows are needed downstream
+      sp.q_tiled_out = d->q_a.as<int8_t>();
+      sp.out_scales = d->sc_a.as<float>();
+      sp.out_zps = d->zp_a.as<int32_t>();
+      sp.m_alloc = m_alloc;
+      sp.b = batch;
+      sp.n = d->hl;
+      sp.nkv = d->kvl;
+      sp.h = c.head_dim;
+      sp.s_max = c.max_seq;
+      sp.q_dtype = 1;
+      sp.kv_dtype = c.kv_dtype == B200_DTYPE_I8 ? 1 : 0;
+      sp.scale = 1.0f / sqrtf((float)c.head_dim);
+      sp.ws = d->sdpa_ws.as<float>();
+      sp.ws_bytes = d->sdpa_ws.bytes;
+      sp.status = d->zero_ws.as<int>();
+      {
+        ProfScope scope(d, 1);
+        if (!(skip & 4)) DEC_CUDA(launch_sdpa_decode(sp, s));
+      }
+      count(2);
     }
-    count(2);
     if (!(skip & 32)) DEC_CUDA(run_fc(d, L.o, batch, d->q_a.as<int8_t>(), d->sc_a.as<float>(), d->zp_a.as<int32_t>(), d->proj));
     if (int rc = reduce(d->proj, (size_t)batch * c.d_model)) return rc;
     if (fuse_norm) {
@@ -515,6 +561,10 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
   DEC_CUDA(d->q_f.alloc(q_tiled_bytes(m_alloc, d->fl)));
   for (DevBuf* b : {&d->sc_d, &d->sc_a, &d->sc_f, &d->zp_d, &d->zp_a, &d->zp_f}) DEC_CUDA(b->alloc(sizeof(float) * m_alloc));
   DEC_CUDA(d->zero_ws.alloc(zero_ws_total_bytes()));
+  if (getenv("B200_DEC_TRACE")) {
+    DEC_CUDA(d->trace.alloc(sizeof(unsigned long long) * (4 * kTraceSlots + 16 * 64)));
+    DEC_CUDA(cudaMemsetAsync(d->trace.p, 0, d->trace.bytes, d->stream));
+  }
   DEC_CUDA(cudaMemsetAsync(d->zero_ws.p, 0, d->zero_ws.bytes, d->stream));
   size_t sdpa_bytes = 0;  // the chunking depends on the batch: size for the worst batch <= max_batch
   for (int b = 1; b <= B; ++b) sdpa_bytes = std::max(sdpa_bytes, sdpa_workspace_bytes(b, d->hl, d->kvl, c.head_dim, c.max_seq));
@@ -549,6 +599,23 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
 void b200_decoder_destroy(b200_decoder* d) {
   if (!d) return;
   cudaStreamSynchronize(d->stream);
+  if (d->trace.p) {  // measurement: the last step's stamps, one line per GEMV launch
+    std::vector<unsigned long long> t(4 * kTraceSlots + 16 * 64);
+    if (cudaMemcpy(t.data(), d->trace.p, d->trace.bytes, cudaMemcpyDeviceToHost) == cudaSuccess) {
+      if (FILE* f = fopen(getenv("B200_DEC_TRACE"), "w")) {
+        for (int i = 0; i < kTraceSlots && t[4 * i]; ++i)
+          fprintf(f, "%d %llu %llu %llu %llu\n", i, t[4 * i], t[4 * i + 1], t[4 * i + 2], t[4 * i + 3]);
+        for (int l = 0; l < 64 && l < d->cfg.n_layers; ++l) {  // attention step kernel, nine stamps per layer
+          const unsigned long long* a = t.data() + 4 * kTraceSlots + 16 * l;
+          if (!a[0]) break;
+          fprintf(f, "attn %d", l);
+          for (int j = 0; j < 12; ++j) fprintf(f, " %llu", a[j]);
+          fprintf(f, "\n");
+        }
+        fclose(f);
+      }
+    }
+  }
   for (auto& g : d->graph)
     if (g) cudaGraphExecDestroy(g);
   if (d->peers_connected)

@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+  if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[0] = global_timer_ns();
 
   if (tid == 0) {
     for (int s = 0; s < L::kStages; ++s) {
@@ -148,6 +149,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         bulk_g2s(dst, p.w_packed + (size_t)t * kTileBytes, kTileBytes, &full_bar[pre]);
       }
       pdl_wait();               // activations (and the split-K scratch) are now safe to touch
+      if (p.trace && blockIdx.x == 0) p.trace[1] = global_timer_ns();
       if (!p.prologue) {
         for (uint32_t i = 0; i < pre; ++i) {
           const int kt = (int)((t_begin + i) % p.k_tiles);
@@ -375,6 +377,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, L::kTmemCols);
+  if (p.trace && tid == 0) {
+    const unsigned long long now = global_timer_ns();
+    if (blockIdx.x == 0) p.trace[2] = now;
+    atomicMax(p.trace + 3, now);
+  }
 }
 
 // ---- cluster split-K variant ---------------------------------------------------------------------
@@ -418,6 +425,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
   const int warp = tid >> 5, lane = tid & 31;
   const int rank = (int)cluster_ctarank();
   const int nt = blockIdx.x / split;
+  if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[0] = global_timer_ns();
   const int kt_begin = (int)((long long)p.k_tiles * rank / split);
   const int kt_end = (int)((long long)p.k_tiles * (rank + 1) / split);
   const int rows_per_owner = (kTileN + split - 1) / split;  // the last owner may hold fewer
@@ -453,6 +461,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
         bulk_g2s(smem + (size_t)pre * L::kStageBytes, w_tiles + (size_t)kt * kTileBytes, kTileBytes, &full_bar[pre]);
       }
       pdl_wait();
+      if (p.trace && blockIdx.x == 0) p.trace[1] = global_timer_ns();
       if (!p.prologue) {
         for (uint32_t i = 0; i < pre; ++i) {
           const size_t off = (((size_t)(kt_begin + i) * m_groups_alloc) + mg_base) * 1024;
@@ -598,6 +607,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, L::kTmemCols);
+  if (p.trace && tid == 0) {
+    const unsigned long long now = global_timer_ns();
+    if (blockIdx.x == 0) p.trace[2] = now;
+    atomicMax(p.trace + 3, now);
+  }
 }
 
 // Chooses the number of CTAs and the split for one launch (measured on B200, batch 1, graph

@@ -81,6 +81,9 @@ struct FcParams {
   float pro_eps;
   float* pro_scales_out;
   int32_t* pro_zps_out;
+  // measurement only: four %globaltimer stamps per launch (first CTA: entry, dependency wait passed,
+  // exit; any CTA: latest exit), or null
+  unsigned long long* trace;
   int max_ctas;              // 0 = chosen per shape
   int whole_tiles;           // set by the launcher: CTAs own whole n tiles (no split-K)
   int debug_flags;           // measurement only: 1 = skip the MMAs, 2 = skip the epilogue
@@ -134,6 +137,28 @@ struct SdpaParams {
   size_t ws_bytes;
   int* status;
 };
+// One decode step of a decoder layer's attention in one launch (multi-query attention, at most
+// eight query heads): rotary embedding of q and of the new key, cache append, attention over the
+// cached tokens, per-row asymmetric int8 quantization of the result in the tiled activation layout.
+struct AttnStepParams {
+  const float* qkv;           // [b][(n + 2) * h]: n query heads, the new key, the new value
+  const int32_t* positions;   // [b]: tokens already cached = position of the new token
+  void* k_cache;              // [b][s_max][h] fp16 or int8
+  void* v_cache;
+  float* k_scale;             // [b][s_max] (int8 caches)
+  float* v_scale;
+  int b, n, h, s_max;
+  int kv_dtype;               // 0 fp16, 1 int8
+  float rope_base, scale;
+  int8_t* q_tiled_out;        // tiled rows of width n * h
+  float* out_scales;
+  int32_t* out_zps;
+  int m_alloc;
+  int* status;                // device status word (bounded waits)
+  unsigned long long* trace;  // measurement only: nine %globaltimer stamps of the first CTA, or null
+};
+bool attn_step_supported(int n, int nkv, int h, int kv_dtype);
+cudaError_t launch_attn_step(const AttnStepParams& p, cudaStream_t s);
 cudaError_t launch_sdpa_decode(const SdpaParams& p, cudaStream_t s);
 size_t sdpa_workspace_bytes(int b, int n, int nkv, int h, int s_max);
 

@@ -36,20 +36,38 @@ constexpr float kLog2e = 1.4426950408889634f;
 enum : int { kKvF16 = 0, kKvI8 = 1, kKvF32 = 2 };
 
 // Loads 8 consecutive head-dim elements of one cached row as four f16x2 words.
-template <int KV>
+// SRC: where the row lives. kSrcGlobal: read-only path; kSrcGlobalCoherent: ordinary loads (the
+// kernel itself wrote one of the rows earlier); kSrcShared: a shared-memory copy (ld.shared, free to
+// be scheduled early: the copy does not change while it is read).
+enum : int { kSrcGlobal = 0, kSrcGlobalCoherent = 1, kSrcShared = 2 };
+
+__device__ __forceinline__ uint4 lds128(const void* p) {
+  uint4 v;
+  asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_u32(p)));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(const void* p) {
+  uint2 v;
+  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(smem_u32(p)));
+  return v;
+}
+
+template <int KV, int SRC = kSrcGlobal>
 __device__ __forceinline__ void load8(const void* row, int d0, bool valid, uint32_t (&out)[4]) {
   if (!valid) {
     out[0] = out[1] = out[2] = out[3] = 0u;
     return;
   }
   if constexpr (KV == kKvF16) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(row) + d0));
+    const uint4* ptr = reinterpret_cast<const uint4*>(static_cast<const __half*>(row) + d0);
+    const uint4 v = SRC == kSrcShared ? lds128(ptr) : (SRC == kSrcGlobalCoherent ? *ptr : __ldg(ptr));
     out[0] = v.x;
     out[1] = v.y;
     out[2] = v.z;
     out[3] = v.w;
   } else if constexpr (KV == kKvI8) {
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(static_cast<const int8_t*>(row) + d0));
+    const uint2* ptr = reinterpret_cast<const uint2*>(static_cast<const int8_t*>(row) + d0);
+    const uint2 v = SRC == kSrcShared ? lds64(ptr) : (SRC == kSrcGlobalCoherent ? *ptr : __ldg(ptr));
     // int8 -> f16, exact: bias to unsigned, splice into 1024 + u, subtract 1152
     const uint32_t w[2] = {v.x ^ 0x80808080u, v.y ^ 0x80808080u};
     const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
@@ -79,6 +97,12 @@ __device__ __forceinline__ size_t kv_elem_bytes() {
   return KV == kKvF16 ? 2 : (KV == kKvI8 ? 1 : 4);
 }
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t transpose8x8(uint32_t x) {
   uint32_t y;
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
@@ -94,89 +118,96 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 // un-normalised output followed by the running max (log2 domain) and sum.
 __host__ __device__ inline size_t partial_stride(int h) { return (size_t)h + 2; }
 
+// Attention of the warp's share of the tokens [c0, c1) of one (batch entry, kv head): online
+// softmax state for heads 2t and 2t+1 (log2 domain) and the un-normalised outputs, in registers.
 // GPI = groups of 16 tokens a warp takes per pass (1, 2 or 4): small for short caches, where the
 // kernel is latency-bound and wants as many warps as possible, 4 for long ones.
-template <int KV, int H, bool QF32, int GPI>
-__global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaParams p, const int chunk_tokens,
-                                                                  const int chunks_max) {
-  constexpr int DB = H < 128 ? H : 128;  // head-dim block of the PV step
-  constexpr int NBLK = H / DB;
-  constexpr int TPB = DB / 16;           // m16 tiles per block
-  constexpr int DPT = DB / 8;            // head-dim elements per thread per block (8 or 16)
-  constexpr int KSTEPS = H / 32;         // 16-byte K pieces per thread per row
-  constexpr int kTokensPerWarpIter = 16 * GPI;
+template <int KV, int H, int GPI>
+struct WarpAttention {
+  static constexpr int DB = H < 128 ? H : 128;  // head-dim block of the PV step
+  static constexpr int NBLK = H / DB;
+  static constexpr int TPB = DB / 16;           // m16 tiles per block
+  static constexpr int DPT = DB / 8;            // head-dim elements per thread per block (8 or 16)
+  static constexpr int KSTEPS = H / 32;         // 16-byte K pieces per thread per row
+  static constexpr int kTokensPerWarpIter = 16 * GPI;
 
-  pdl_enter();
-  const int b = blockIdx.z, kvh = blockIdx.y, chunk = blockIdx.x;
-  const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
-  const int c0 = chunk * chunk_tokens;
-  if (c0 >= len) return;
-  const int c1 = min(len, c0 + chunk_tokens);
+  float m_run[2], l_run[2];
+  float o[NBLK * TPB][4];
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = lane >> 2, t = lane & 3;
-  const int group = p.n / p.nkv;  // query heads per kv head (<= 8)
-
-  // ---- Q fragments: thread (g,t) keeps head g, 16-byte pieces t + 4 i ----
-  uint32_t qf[KSTEPS][4];
-  {
-    const bool head_ok = g < group;
-    const int head = kvh * group + (head_ok ? g : 0);
+  __device__ __forceinline__ void clear() {
+    m_run[0] = m_run[1] = -CUDART_INF_F;
+    l_run[0] = l_run[1] = 0.0f;
 #pragma unroll
-    for (int i = 0; i < KSTEPS; ++i) {
-      const int d0 = 8 * (t + 4 * i);
-      if (!head_ok) {
-        qf[i][0] = qf[i][1] = qf[i][2] = qf[i][3] = 0u;
-      } else if constexpr (QF32) {
-        const float* q = static_cast<const float*>(p.q) + ((size_t)b * p.n + head) * H + d0;
-        load8<kKvF32>(q, 0, true, qf[i]);
-      } else {
-        const __half* q = static_cast<const __half*>(p.q) + ((size_t)b * p.n + head) * H + d0;
-        load8<kKvF16>(q, 0, true, qf[i]);
-      }
-    }
+    for (int i = 0; i < NBLK * TPB; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
   }
 
-  const size_t row_stride = (size_t)p.nkv * H * kv_elem_bytes<KV>();
-  const uint8_t* kbase = static_cast<const uint8_t*>(p.k) + ((size_t)b * p.s_max * p.nkv + kvh) * H * kv_elem_bytes<KV>();
-  const uint8_t* vbase = static_cast<const uint8_t*>(p.v) + ((size_t)b * p.s_max * p.nkv + kvh) * H * kv_elem_bytes<KV>();
-  const float* ksc = p.k_scale ? p.k_scale + (size_t)b * p.s_max * p.nkv + kvh : nullptr;
-  const float* vsc = p.v_scale ? p.v_scale + (size_t)b * p.s_max * p.nkv + kvh : nullptr;
-  const float* maskp = p.mask ? p.mask + (size_t)b * p.s_max : nullptr;
+  // Where the rows come from: `k` / `v` point at token 0's row (global cache or a shared-memory
+  // copy biased by the copy's first token), rows `stride` bytes apart; per-token scales (int8).
+  struct Rows {
+    const uint8_t* k;
+    const uint8_t* v;
+    size_t stride;
+    const float* k_scale;
+    const float* v_scale;
+    int scale_stride;
+  };
+  static __device__ __forceinline__ Rows cache_rows(const SdpaParams& p, int b, int kvh) {
+    Rows r;
+    r.stride = (size_t)p.nkv * H * kv_elem_bytes<KV>();
+    r.k = static_cast<const uint8_t*>(p.k) + ((size_t)b * p.s_max * p.nkv + kvh) * H * kv_elem_bytes<KV>();
+    r.v = static_cast<const uint8_t*>(p.v) + ((size_t)b * p.s_max * p.nkv + kvh) * H * kv_elem_bytes<KV>();
+    r.k_scale = p.k_scale ? p.k_scale + (size_t)b * p.s_max * p.nkv + kvh : nullptr;
+    r.v_scale = p.v_scale ? p.v_scale + (size_t)b * p.s_max * p.nkv + kvh : nullptr;
+    r.scale_stride = p.nkv;
+    return r;
+  }
 
-  // online softmax state for heads 2t and 2t+1 (log2 domain)
-  float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};
-  float l_run[2] = {0.0f, 0.0f};
-  float o[NBLK * TPB][4];
-#pragma unroll
-  for (int i = 0; i < NBLK * TPB; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  // Tokens first, first + step, ... (blocks of kTokensPerWarpIter) below `c1`.
+  template <int SRC>
+  __device__ __forceinline__ void run(const SdpaParams& p, const uint32_t (&qf)[KSTEPS][4], const Rows& rows_src, int b,
+                                      int first, int step, int c1, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    clear();
+  const size_t row_stride = rows_src.stride;
+  const uint8_t* kbase = rows_src.k;
+  const uint8_t* vbase = rows_src.v;
+  const float* ksc = rows_src.k_scale;
+  const float* vsc = rows_src.v_scale;
+  const int sc_stride = rows_src.scale_stride;
+  const float* maskp = p.mask ? p.mask + (size_t)b * p.s_max : nullptr;
 
   const float scale_log2 = p.scale * kLog2e;
 
-  for (int base = c0 + warp * kTokensPerWarpIter; base < c1; base += kWarps * kTokensPerWarpIter) {
+  for (int base = first; base < c1; base += step) {
     // ---- S^T = K Q^T for GPI groups of 16 tokens ----
     float s[GPI][4];
 #pragma unroll
     for (int gi = 0; gi < GPI; ++gi) {
-      s[gi][0] = s[gi][1] = s[gi][2] = s[gi][3] = 0.0f;
       const int ta = base + gi * 16 + g, tb = ta + 8;
       const bool va = ta < c1, vb = tb < c1;
       const void* ra = kbase + (size_t)ta * row_stride;
       const void* rb = kbase + (size_t)tb * row_stride;
+      // four independent accumulation chains: a chain of 2 * KSTEPS dependent MMAs would leave the
+      // tensor pipe idle for its whole latency between steps
+      float part[4][4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) part[c][0] = part[c][1] = part[c][2] = part[c][3] = 0.0f;
 #pragma unroll
       for (int i = 0; i < KSTEPS; ++i) {
         uint32_t ka[4], kb[4];
         const int d0 = 8 * (t + 4 * i);
-        load8<KV>(ra, d0, va, ka);
-        load8<KV>(rb, d0, vb, kb);
-        mma_f16(s[gi], ka[0], kb[0], ka[1], kb[1], qf[i][0], qf[i][1]);
-        mma_f16(s[gi], ka[2], kb[2], ka[3], kb[3], qf[i][2], qf[i][3]);
+        load8<KV, SRC>(ra, d0, va, ka);
+        load8<KV, SRC>(rb, d0, vb, kb);
+        mma_f16(part[(2 * i) & 3], ka[0], kb[0], ka[1], kb[1], qf[i][0], qf[i][1]);
+        mma_f16(part[(2 * i + 1) & 3], ka[2], kb[2], ka[3], kb[3], qf[i][2], qf[i][3]);
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[gi][e] = (part[0][e] + part[1][e]) + (part[2][e] + part[3][e]);
       // scale (and dequantise), cap, mask; work in the log2 domain
       float fa = scale_log2, fb = scale_log2;
       if constexpr (KV == kKvI8) {
-        fa *= va ? ksc[(size_t)ta * p.nkv] : 0.0f;
-        fb *= vb ? ksc[(size_t)tb * p.nkv] : 0.0f;
+        fa *= va ? ksc[(size_t)ta * sc_stride] : 0.0f;
+        fb *= vb ? ksc[(size_t)tb * sc_stride] : 0.0f;
       }
       s[gi][0] *= fa;
       s[gi][1] *= fa;
@@ -234,8 +265,8 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
       l_run[1] += pa1 + pb1;
       if constexpr (KV == kKvI8) {
         const int ta = base + gi * 16 + g, tb = ta + 8;
-        const float sa = ta < c1 ? vsc[(size_t)ta * p.nkv] : 0.0f;
-        const float sb = tb < c1 ? vsc[(size_t)tb * p.nkv] : 0.0f;
+        const float sa = ta < c1 ? vsc[(size_t)ta * sc_stride] : 0.0f;
+        const float sb = tb < c1 ? vsc[(size_t)tb * sc_stride] : 0.0f;
         pa0 *= sa;
         pa1 *= sa;
         pb0 *= sb;
@@ -256,7 +287,7 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
 #pragma unroll
           for (int hlf = 0; hlf < DPT / 8; ++hlf) {
             uint32_t tmp[4];
-            load8<KV>(row, blk * DB + DPT * g + 8 * hlf, ok, tmp);
+            load8<KV, SRC>(row, blk * DB + DPT * g + 8 * hlf, ok, tmp);
             vr[r][4 * hlf + 0] = tmp[0];
             vr[r][4 * hlf + 1] = tmp[1];
             vr[r][4 * hlf + 2] = tmp[2];
@@ -276,34 +307,81 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
     }
   }
 
-  // ---- merge the warps of this CTA ----
-  // l is still per-thread; reduce over the token lanes
+    // l is still per-thread; reduce over the token lanes
 #pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    float v = l_run[e];
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
-    v += __shfl_xor_sync(0xffffffffu, v, 8);
-    v += __shfl_xor_sync(0xffffffffu, v, 16);
-    l_run[e] = v;
+    for (int e = 0; e < 2; ++e) {
+      float v = l_run[e];
+      v += __shfl_xor_sync(0xffffffffu, v, 4);
+      v += __shfl_xor_sync(0xffffffffu, v, 8);
+      v += __shfl_xor_sync(0xffffffffu, v, 16);
+      l_run[e] = v;
+    }
   }
+
+  // Parks the warp's state in shared memory (sm_o rows are H + 4 floats).
+  __device__ __forceinline__ void park(float (*sm_m)[8], float (*sm_l)[8], float (*sm_o)[8][H + 4], int warp, int lane) const {
+    const int g = lane >> 2, t = lane & 3;
+    if (g == 0) {
+      sm_m[warp][2 * t] = m_run[0];
+      sm_m[warp][2 * t + 1] = m_run[1];
+      sm_l[warp][2 * t] = l_run[0];
+      sm_l[warp][2 * t + 1] = l_run[1];
+    }
+#pragma unroll
+    for (int blk = 0; blk < NBLK; ++blk)
+#pragma unroll
+      for (int i = 0; i < TPB; ++i) {
+        const int d = blk * DB + DPT * g + 2 * i;
+        sm_o[warp][2 * t][d] = o[blk * TPB + i][0];
+        sm_o[warp][2 * t + 1][d] = o[blk * TPB + i][1];
+        sm_o[warp][2 * t][d + 1] = o[blk * TPB + i][2];
+        sm_o[warp][2 * t + 1][d + 1] = o[blk * TPB + i][3];
+      }
+  }
+};
+
+template <int KV, int H, bool QF32, int GPI>
+__global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaParams p, const int chunk_tokens,
+                                                                  const int chunks_max) {
+  using WA = WarpAttention<KV, H, GPI>;
+  constexpr int KSTEPS = WA::KSTEPS;
+  pdl_enter();
+  const int b = blockIdx.z, kvh = blockIdx.y, chunk = blockIdx.x;
+  const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
+  const int c0 = chunk * chunk_tokens;
+  if (c0 >= len) return;
+  const int c1 = min(len, c0 + chunk_tokens);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int group = p.n / p.nkv;  // query heads per kv head (<= 8)
+
+  // ---- Q fragments: thread (g,t) keeps head g, 16-byte pieces t + 4 i ----
+  uint32_t qf[KSTEPS][4];
+  {
+    const bool head_ok = g < group;
+    const int head = kvh * group + (head_ok ? g : 0);
+#pragma unroll
+    for (int i = 0; i < KSTEPS; ++i) {
+      const int d0 = 8 * (t + 4 * i);
+      if (!head_ok) {
+        qf[i][0] = qf[i][1] = qf[i][2] = qf[i][3] = 0u;
+      } else if constexpr (QF32) {
+        const float* q = static_cast<const float*>(p.q) + ((size_t)b * p.n + head) * H + d0;
+        load8<kKvF32>(q, 0, true, qf[i]);
+      } else {
+        const __half* q = static_cast<const __half*>(p.q) + ((size_t)b * p.n + head) * H + d0;
+        load8<kKvF16>(q, 0, true, qf[i]);
+      }
+    }
+  }
+  WA wa;
+  wa.template run<kSrcGlobal>(p, qf, WA::cache_rows(p, b, kvh), b, c0 + warp * WA::kTokensPerWarpIter, kWarps * WA::kTokensPerWarpIter, c1, lane);
+
+  // ---- merge the warps of this CTA ----
   __shared__ float sm_m[kWarps][8], sm_l[kWarps][8];
   __shared__ float sm_o[kWarps][8][H + 4];
-  if (g == 0) {
-    sm_m[warp][2 * t] = m_run[0];
-    sm_m[warp][2 * t + 1] = m_run[1];
-    sm_l[warp][2 * t] = l_run[0];
-    sm_l[warp][2 * t + 1] = l_run[1];
-  }
-#pragma unroll
-  for (int blk = 0; blk < NBLK; ++blk)
-#pragma unroll
-    for (int i = 0; i < TPB; ++i) {
-      const int d = blk * DB + DPT * g + 2 * i;
-      sm_o[warp][2 * t][d] = o[blk * TPB + i][0];
-      sm_o[warp][2 * t + 1][d] = o[blk * TPB + i][1];
-      sm_o[warp][2 * t][d + 1] = o[blk * TPB + i][2];
-      sm_o[warp][2 * t + 1][d + 1] = o[blk * TPB + i][3];
-    }
+  wa.park(sm_m, sm_l, sm_o, warp, lane);
   __syncthreads();
   float* part = p.ws + ((((size_t)b * p.nkv + kvh) * chunks_max + chunk) * 8) * partial_stride(H);
   for (int idx = tid; idx < group * H; idx += kWarps * 32) {
@@ -326,6 +404,335 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
       rec[H + 1] = l;
     }
   }
+}
+
+// ---- one decode step of a decoder layer's attention in ONE launch -------------------------------
+// For a fused q/k/v projection output with a single KV head (multi-query attention) and at most
+// eight query heads: rotary embedding of q and of the new key, append of the new key / value row to
+// the cache, attention over the cached tokens, and the per-row asymmetric int8 quantization that
+// the output projection (a hybrid FULLY_CONNECTED) applies to its input. One cluster of
+// kAttnCluster CTAs per sequence: the CTAs split the tokens, merge their softmax states through
+// distributed shared memory (CTA r finishes head r), exchange the finished heads' min / max the
+// same way, and each writes its head's quantized bytes in the tiled activation layout.
+constexpr int kAttnCluster = 8;
+// Warps per CTA. Measured on B200 (batch 1, 1040 cached tokens): 4 warps x 3 passes of 16 tokens
+// take 4.6 us in the token loop, 8 warps x 2 passes 5.4 us: the loop's cost is mostly fixed (cold
+// instruction and data fetches after the weight stream has swept L2), not per token.
+constexpr int kAttnWarps = 4;
+
+template <int H>
+struct AttnStepSmem {
+  static constexpr int kRec = H + 2;
+  float2 cs[H / 2];               // cos, sin per rotation pair
+  float q[8][H];                  // rotated query heads
+  float sm_m[kAttnWarps][8], sm_l[kAttnWarps][8], wf[kAttnWarps][8];
+  float rec[8][kRec];             // this CTA's merged state per head
+  float inbox[kAttnCluster][kRec];  // the states of the head this CTA finishes, from every CTA
+  float own[H];                   // finished head
+  float2 mmbox[kAttnCluster];     // min / max of every CTA's finished head
+  float2 red[kAttnWarps];
+  // followed by the staging area: `stage_rows` key rows then as many value rows, each padded by
+  // 16 bytes against bank conflicts; the warps' parked outputs reuse it after the token loop
+};
+template <int KV, int H>
+__host__ __device__ constexpr int attn_row_pitch() {
+  return H * (KV == kKvI8 ? 1 : 2) + 16;
+}
+template <int H>
+constexpr size_t attn_park_bytes() {
+  return sizeof(float) * kAttnWarps * 8 * (H + 4);
+}
+
+template <int KV, int H, int GPI>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(const AttnStepParams p, const int stage_rows) {
+  using WA = WarpAttention<KV, H, GPI>;
+  constexpr int KSTEPS = WA::KSTEPS;
+  constexpr int C = kAttnCluster, HALF = H / 2, REC = H + 2;
+  constexpr int PITCH = attn_row_pitch<KV, H>();
+  constexpr int ROW_BYTES = H * (KV == kKvI8 ? 1 : 2);
+  extern __shared__ __align__(128) uint8_t attn_smem_raw[];
+  AttnStepSmem<H>& sm = *reinterpret_cast<AttnStepSmem<H>*>(attn_smem_raw);
+  uint8_t* stage_k = attn_smem_raw + ((sizeof(AttnStepSmem<H>) + 127) / 128) * 128;
+  uint8_t* stage_v = stage_k + (size_t)stage_rows * PITCH;
+  float (*sm_o)[8][H + 4] = reinterpret_cast<float (*)[8][H + 4]>(stage_k);
+
+  const bool tracer = p.trace && blockIdx.x == 0 && threadIdx.x == 0;
+  if (tracer) p.trace[0] = global_timer_ns();
+  pdl_launch_dependents();
+  cluster_arrive();  // phase 0: this CTA runs (waited for before the first remote store)
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int rank = (int)cluster_ctarank();
+  const int b = blockIdx.x / C;
+  // The positions and every cached row below the new token date from earlier steps: they can be
+  // read before the kernel that produces this step's q / k / v has finished.
+  const int pos = p.positions[b];
+  if (tracer) p.trace[9] = global_timer_ns() + (pos == -12345);
+  const bool append = pos < p.s_max;  // a full cache ignores the step's key / value
+  const int len = append ? pos + 1 : p.s_max;
+  // tokens of this CTA: equal shares, a multiple of 16
+  const int per = (((len + C - 1) / C) + 15) / 16 * 16;
+  const int c0 = rank * per;
+  const int c1 = min(len, c0 + per);
+  const bool staged = c1 - c0 <= stage_rows;   // else the rows are read straight from the cache
+  const int old_end = append ? min(c1, pos) : c1;  // rows [c0, old_end) are already in the cache
+  const uint8_t* kglob = static_cast<const uint8_t*>(p.k_cache) + (size_t)b * p.s_max * ROW_BYTES;
+  const uint8_t* vglob = static_cast<const uint8_t*>(p.v_cache) + (size_t)b * p.s_max * ROW_BYTES;
+  if (staged) {
+    // 16-byte asynchronous copies, all in flight at once (no registers held): the rows land padded
+    constexpr int PIECES = ROW_BYTES / 16;
+    const int n_pieces = (old_end - c0) * PIECES;
+    for (int i = tid; i < n_pieces; i += kAttnWarps * 32) {
+      const int r = i / PIECES, c = i % PIECES;
+      cp_async16(stage_k + (size_t)r * PITCH + c * 16, kglob + (size_t)(c0 + r) * ROW_BYTES + c * 16);
+      cp_async16(stage_v + (size_t)r * PITCH + c * 16, vglob + (size_t)(c0 + r) * ROW_BYTES + c * 16);
+    }
+    cp_async_commit();
+  }
+  if (tracer) p.trace[10] = global_timer_ns();
+  for (int i = tid; i < HALF; i += kAttnWarps * 32) {
+    const float freq = powf(p.rope_base, -2.0f * (float)i / (float)H);
+    float sn, cs;
+    sincosf((float)pos * freq, &sn, &cs);
+    sm.cs[i] = make_float2(cs, sn);
+  }
+  if (tracer) p.trace[11] = global_timer_ns();
+  pdl_wait();  // this step's q / k / v
+  if (tracer) p.trace[1] = global_timer_ns();
+  __syncthreads();
+  const float* src = p.qkv + (size_t)b * (p.n + 2) * H;
+  for (int idx = tid; idx < p.n * HALF; idx += kAttnWarps * 32) {
+    const int head = idx / HALF, i = idx % HALF;
+    const float x1 = src[head * H + i], x2 = src[head * H + i + HALF];
+    const float2 r = sm.cs[i];
+    sm.q[head][i] = x1 * r.x - x2 * r.y;
+    sm.q[head][i + HALF] = x2 * r.x + x1 * r.y;
+  }
+  if (append && pos >= c0 && pos < c1) {
+    // The CTA whose share holds the new token writes its row: to the cache, and to the staged
+    // copy it is about to read (the same rounded values later steps will find in the cache).
+    const float* ksrc = src + (size_t)p.n * H;
+    const float* vsrc = ksrc + H;
+    const size_t tok = (size_t)b * p.s_max + pos;
+    if constexpr (KV == kKvI8) {
+      // symmetric per token: scale = max|row| / 127 (key after the rotation)
+      float ka = 0.0f, va = 0.0f;
+      for (int i = tid; i < HALF; i += kAttnWarps * 32) {
+        const float2 r = sm.cs[i];
+        const float x1 = ksrc[i], x2 = ksrc[i + HALF];
+        ka = fmaxf(ka, fmaxf(fabsf(x1 * r.x - x2 * r.y), fabsf(x2 * r.x + x1 * r.y)));
+        va = fmaxf(va, fmaxf(fabsf(vsrc[i]), fabsf(vsrc[i + HALF])));
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        ka = fmaxf(ka, __shfl_xor_sync(0xffffffffu, ka, o));
+        va = fmaxf(va, __shfl_xor_sync(0xffffffffu, va, o));
+      }
+      if (lane == 0) sm.red[warp] = make_float2(ka, va);
+      __syncthreads();
+      ka = sm.red[0].x, va = sm.red[0].y;
+#pragma unroll
+      for (int w = 1; w < kAttnWarps; ++w) {
+        ka = fmaxf(ka, sm.red[w].x);
+        va = fmaxf(va, sm.red[w].y);
+      }
+      const float ks = ka > 0.0f ? ka / 127.0f : 1.0f, vs = va > 0.0f ? va / 127.0f : 1.0f;
+      int8_t* kd = static_cast<int8_t*>(p.k_cache) + tok * H;
+      int8_t* vd = static_cast<int8_t*>(p.v_cache) + tok * H;
+      int8_t* ks_row = reinterpret_cast<int8_t*>(stage_k + (size_t)(pos - c0) * PITCH);
+      int8_t* vs_row = reinterpret_cast<int8_t*>(stage_v + (size_t)(pos - c0) * PITCH);
+      for (int i = tid; i < HALF; i += kAttnWarps * 32) {
+        const float2 r = sm.cs[i];
+        const float x1 = ksrc[i], x2 = ksrc[i + HALF];
+        const int8_t k1 = (int8_t)max(-127, min(127, __float2int_rn((x1 * r.x - x2 * r.y) / ks)));
+        const int8_t k2 = (int8_t)max(-127, min(127, __float2int_rn((x2 * r.x + x1 * r.y) / ks)));
+        const int8_t v1 = (int8_t)max(-127, min(127, __float2int_rn(vsrc[i] / vs)));
+        const int8_t v2 = (int8_t)max(-127, min(127, __float2int_rn(vsrc[i + HALF] / vs)));
+        kd[i] = k1, kd[i + HALF] = k2, vd[i] = v1, vd[i + HALF] = v2;
+        if (staged) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
+      }
+      if (tid == 0) {
+        p.k_scale[tok] = ks;
+        p.v_scale[tok] = vs;
+      }
+    } else {
+      __half* kd = static_cast<__half*>(p.k_cache) + tok * H;
+      __half* vd = static_cast<__half*>(p.v_cache) + tok * H;
+      __half* ks_row = reinterpret_cast<__half*>(stage_k + (size_t)(pos - c0) * PITCH);
+      __half* vs_row = reinterpret_cast<__half*>(stage_v + (size_t)(pos - c0) * PITCH);
+      for (int i = tid; i < HALF; i += kAttnWarps * 32) {
+        const float2 r = sm.cs[i];
+        const float x1 = ksrc[i], x2 = ksrc[i + HALF];
+        const __half k1 = __float2half_rn(x1 * r.x - x2 * r.y), k2 = __float2half_rn(x2 * r.x + x1 * r.y);
+        const __half v1 = __float2half_rn(vsrc[i]), v2 = __float2half_rn(vsrc[i + HALF]);
+        kd[i] = k1, kd[i + HALF] = k2, vd[i] = v1, vd[i + HALF] = v2;
+        if (staged) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
+      }
+    }
+  }
+  cp_async_wait_all();
+  __syncthreads();  // rotated queries, staged rows and the new row (staged copy, or the cache through this CTA's own stores) in place
+
+  if (tracer) p.trace[2] = global_timer_ns();
+  uint32_t qf[KSTEPS][4];
+#pragma unroll
+  for (int i = 0; i < KSTEPS; ++i) {
+    const int d0 = 8 * (t + 4 * i);
+    if (g < p.n) {
+      const float* q = &sm.q[g][d0];
+      qf[i][0] = pack_half2(q[0], q[1]);
+      qf[i][1] = pack_half2(q[2], q[3]);
+      qf[i][2] = pack_half2(q[4], q[5]);
+      qf[i][3] = pack_half2(q[6], q[7]);
+    } else {
+      qf[i][0] = qf[i][1] = qf[i][2] = qf[i][3] = 0u;
+    }
+  }
+  SdpaParams sp;
+  sp.mask = nullptr;
+  sp.nkv = 1;
+  sp.s_max = p.s_max;
+  sp.scale = p.scale;
+  sp.logit_cap = 0.0f;
+  typename WA::Rows rows;
+  rows.k_scale = p.k_scale ? p.k_scale + (size_t)b * p.s_max : nullptr;
+  rows.v_scale = p.v_scale ? p.v_scale + (size_t)b * p.s_max : nullptr;
+  rows.scale_stride = 1;
+  if (staged) {
+    rows.k = stage_k - (ptrdiff_t)c0 * PITCH;  // indexed by absolute token
+    rows.v = stage_v - (ptrdiff_t)c0 * PITCH;
+    rows.stride = PITCH;
+  } else {
+    rows.k = kglob;
+    rows.v = vglob;
+    rows.stride = ROW_BYTES;
+  }
+  if (tracer) p.trace[3] = global_timer_ns();
+  // the warps take equal contiguous shares of the CTA's tokens (multiples of 16)
+  const int wper = ((((c1 - c0) + kAttnWarps - 1) / kAttnWarps) + 15) / 16 * 16;
+  const int first = c0 + warp * wper;
+  const int last = min(c1, first + wper);
+  WA wa;
+  if (first >= last) {
+    wa.clear();
+  } else if (staged) {
+    wa.template run<kSrcShared>(sp, qf, rows, b, first, WA::kTokensPerWarpIter, last, lane);
+  } else {
+    wa.template run<kSrcGlobalCoherent>(sp, qf, rows, b, first, WA::kTokensPerWarpIter, last, lane);
+  }
+  if (tracer) p.trace[4] = global_timer_ns();
+  __syncthreads();  // every warp is done with the staged rows: their space now takes the parked outputs
+  wa.park(sm.sm_m, sm.sm_l, sm_o, warp, lane);
+  __syncthreads();
+  // this CTA's state per head: the warps merged (weights per warp and head computed once)
+  if (tid < 8) {
+    const int head = tid;
+    float mm = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, sm.sm_m[w][head]);
+    const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
+    float l = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float f = exp2f(sm.sm_m[w][head] - muse);
+      sm.wf[w][head] = f;
+      l += f * sm.sm_l[w][head];
+    }
+    sm.rec[head][H] = mm;
+    sm.rec[head][H + 1] = l;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < p.n * H; idx += kAttnWarps * 32) {
+    const int head = idx / H, d = idx % H;
+    float acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) acc += sm.wf[w][head] * sm_o[w][head][d];
+    sm.rec[head][d] = acc;
+  }
+  __syncthreads();
+  if (tracer) p.trace[5] = global_timer_ns();
+  cluster_wait();  // phase 0
+  // head h goes to CTA h (n <= 8 = cluster size)
+  for (int head = 0; head < p.n; ++head) {
+    const uint32_t dst = map_to_rank(smem_u32(&sm.inbox[rank][0]), (uint32_t)head);
+    for (int i = tid; i < REC; i += kAttnWarps * 32) st_cluster_f32(dst + 4u * (uint32_t)i, sm.rec[head][i]);
+  }
+  cluster_arrive();  // phase 1: delivered ...
+  cluster_wait();    // ... and received
+  if (tracer) p.trace[6] = global_timer_ns();
+  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+  const bool owner = rank < p.n;
+  if (owner) {
+    float mm = -CUDART_INF_F;
+#pragma unroll
+    for (int c = 0; c < C; ++c) mm = fmaxf(mm, sm.inbox[c][H]);
+    const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
+    float f[C], l = 0.0f;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      f[c] = exp2f(sm.inbox[c][H] - muse);
+      l += f[c] * sm.inbox[c][H + 1];
+    }
+    for (int d = tid; d < H; d += kAttnWarps * 32) {
+      float acc = 0.0f;
+#pragma unroll
+      for (int c = 0; c < C; ++c) acc += f[c] * sm.inbox[c][d];
+      const float v = acc / l;
+      sm.own[d] = v;
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if (lane == 0) sm.red[warp] = make_float2(mn, mx);
+  __syncthreads();
+  if (tid < C) {
+    float lo = sm.red[0].x, hi = sm.red[0].y;
+#pragma unroll
+    for (int w = 1; w < kAttnWarps; ++w) {
+      lo = fminf(lo, sm.red[w].x);
+      hi = fmaxf(hi, sm.red[w].y);
+    }
+    const uint32_t dst = map_to_rank(smem_u32(&sm.mmbox[rank]), (uint32_t)tid);
+    st_cluster_f32(dst, lo);
+    st_cluster_f32(dst + 4u, hi);
+  }
+  cluster_arrive();  // phase 2
+  cluster_wait();
+  if (tracer) p.trace[7] = global_timer_ns();
+  float lo = sm.mmbox[0].x, hi = sm.mmbox[0].y;
+#pragma unroll
+  for (int c = 1; c < C; ++c) {
+    lo = fminf(lo, sm.mmbox[c].x);
+    hi = fmaxf(hi, sm.mmbox[c].y);
+  }
+  float sf, inv;
+  int zp, zero_row;
+  row_quant_params(lo, hi, true, &sf, &inv, &zp, &zero_row);
+  const float zpf = (float)zp;
+  if (owner) {
+    for (int d4 = tid * 4; d4 < H; d4 += kAttnWarps * 32 * 4) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (!zero_row) word |= quantize_value(sm.own[d4 + e], inv, zpf, true) << (8 * e);
+      *reinterpret_cast<uint32_t*>(p.q_tiled_out + q_tiled_offset(b, rank * H + d4, p.m_alloc)) = word;
+    }
+  }
+  if (rank == 0) {
+    const int width = p.n * H, k_pad = (width + 127) / 128 * 128;
+    for (int k4 = width + tid * 4; k4 < k_pad; k4 += kAttnWarps * 32 * 4)
+      *reinterpret_cast<uint32_t*>(p.q_tiled_out + q_tiled_offset(b, k4, p.m_alloc)) = 0u;
+    if (tid == 0) {
+      p.out_scales[b] = sf;
+      p.out_zps[b] = zp;
+    }
+  }
+  if (tracer) p.trace[8] = global_timer_ns();
 }
 
 // Reduces the per-chunk partials of one (batch, query head): grid (n, b),
@@ -555,6 +962,34 @@ cudaError_t launch_kv(const SdpaParams& p, cudaStream_t s) {
   return cudaGetLastError();
 }
 
+template <int KV, int H>
+cudaError_t launch_attn_step_h(const AttnStepParams& p, cudaStream_t s) {
+  constexpr size_t kBudget = 200 * 1024;
+  const size_t fixed = ((sizeof(AttnStepSmem<H>) + 127) / 128) * 128;
+  const int pitch = attn_row_pitch<KV, H>();
+  // as many staged rows as a CTA's share of the longest cache needs, within the budget; the
+  // staging area is never smaller than the warps' parked outputs that reuse it
+  const int per_max = ((p.s_max + kAttnCluster - 1) / kAttnCluster + 15) / 16 * 16;
+  int rows = (int)((kBudget - fixed) / (2 * (size_t)pitch));
+  if (rows > per_max) rows = per_max;
+  size_t stage = 2 * (size_t)rows * pitch;
+  if (stage < attn_park_bytes<H>()) stage = attn_park_bytes<H>();
+  const size_t smem = fixed + stage;
+  auto go = [&](auto kernel) -> cudaError_t {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+    }
+    return launch_chained_cluster(kernel, dim3(p.b * kAttnCluster), dim3(kAttnWarps * 32), smem, kAttnCluster, s, p, rows);
+  };
+  // Staged rows are read from shared memory: passes are cheap, and the smallest loop body (16
+  // tokens per warp and pass) costs the fewest instruction-cache misses, which dominate a kernel
+  // that runs once per layer between large GEMVs. Rows read from the cache want long passes.
+  if (rows >= per_max || per_max <= 64) return go(attn_step_cluster_kernel<KV, H, 1>);
+  if (per_max <= 128) return go(attn_step_cluster_kernel<KV, H, 2>);
+  return go(attn_step_cluster_kernel<KV, H, 4>);
+}
+
 }  // namespace
 
 size_t sdpa_workspace_bytes(int b, int n, int nkv, int h, int s_max) {
@@ -573,6 +1008,22 @@ cudaError_t launch_sdpa_decode(const SdpaParams& p, cudaStream_t s) {
     case kKvF32: return qf32 ? launch_kv<kKvF32, true>(p, s) : launch_kv<kKvF32, false>(p, s);
     default: return cudaErrorInvalidValue;
   }
+}
+
+bool attn_step_supported(int n, int nkv, int h, int kv_dtype) {
+  return nkv == 1 && n >= 1 && n <= 8 && (h == 64 || h == 128 || h == 256) && (kv_dtype == kKvF16 || kv_dtype == kKvI8);
+}
+
+cudaError_t launch_attn_step(const AttnStepParams& p, cudaStream_t s) {
+  if (!attn_step_supported(p.n, 1, p.h, p.kv_dtype) || p.b < 1) return cudaErrorInvalidValue;
+  if (p.kv_dtype == kKvI8) {
+    if (p.h == 256) return launch_attn_step_h<kKvI8, 256>(p, s);
+    if (p.h == 128) return launch_attn_step_h<kKvI8, 128>(p, s);
+    return launch_attn_step_h<kKvI8, 64>(p, s);
+  }
+  if (p.h == 256) return launch_attn_step_h<kKvF16, 256>(p, s);
+  if (p.h == 128) return launch_attn_step_h<kKvF16, 128>(p, s);
+  return launch_attn_step_h<kKvF16, 64>(p, s);
 }
 
 }  // namespace b200

@@ -47,6 +47,27 @@ def test_decoder_matches_cpu_graph(oracle, kv_dtype, tol):
     ref.close()
 
 
+def test_decoder_wide_batch_uses_chunked_attention(oracle):
+    """Twelve sequences: past the size where one cluster per sequence pays, the step goes through the
+    rotary / flash-decode / merge kernels instead. Same bound as above."""
+    from litert_b200 import decoder as dec
+
+    cfg = dict(dec.TINY)
+    batch, steps, max_seq = 12, 4, 12
+    weights = dec.make_weights(cfg, seed=9)
+    gpu = dec.Decoder(cfg, max_seq=max_seq, max_batch=batch, weights=weights)
+    ref = oracle.DecoderRef(cfg, _host(weights), batch, max_seq, fast=False)
+    tokens = np.random.default_rng(4).integers(0, cfg["vocab"], batch).astype(np.int32)
+    for s in range(steps):
+        _, logits_g = gpu.step(tokens, want_logits=True)
+        nxt_r, logits_r = ref.step(tokens)
+        err = np.linalg.norm(logits_g.cpu().numpy() - logits_r) / np.linalg.norm(logits_r)
+        assert err <= 6e-2, (s, err)
+        tokens = nxt_r
+    gpu.close()
+    ref.close()
+
+
 def test_decoder_graph_path_equals_eager_path_and_is_repeatable():
     from litert_b200 import decoder as dec
 
