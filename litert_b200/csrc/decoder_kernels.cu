@@ -89,41 +89,55 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_kernel(float* __r
                                                                      int32_t* __restrict__ zps, TpExchange xch) {
   extern __shared__ float xs[];
   __shared__ float red[32];
-  pdl_enter();
+  pdl_launch_dependents();
   const int b = blockIdx.x;
   const bool exchange = xch.tp_size > 1;
-  if (exchange) tp_handshake(xch, blockIdx.x == 0);
   float* hr = h + (size_t)b * d;
-  float ss = 0.0f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float v = hr[i];
-    if (exchange) {
-      // sum of the ranks' partial outputs, in rank order on every rank
-      float sum = 0.0f;
-      for (int j = 0; j < xch.tp_size; ++j) {
-        const float* pj = xch.partial[j] + (size_t)b * d + i;
-        const float t = j == xch.tp_rank ? *pj : ld_peer(pj);
-        sum = j == 0 ? t : __fadd_rn(sum, t);
-      }
-      v = __fadd_rn(v, sum);
-      hr[i] = v;
-    } else if (delta) {
-      v = __fadd_rn(v, delta[(size_t)b * d + i]);
-      hr[i] = v;
+  // Two passes over the same code. The first runs while the producing kernel is still busy, on
+  // whatever the inputs hold, and stores nothing: it only pulls the instructions (and the gain
+  // vector) into the caches, which is most of what this short kernel otherwise waits for. The
+  // second, after the dependency wait, is the real one.
+#pragma unroll 1
+  for (int pass = 0; pass < 2; ++pass) {
+    const bool live = pass == 1;
+    if (live) {
+      pdl_wait();
+      if (exchange) tp_handshake(xch, blockIdx.x == 0);
     }
-    xs[i] = v;
-    ss += v * v;
+    // inputs written by earlier kernels are read past L1 (__ldcg): the dry run must leave no stale
+    // line behind for the real pass
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      float v = __ldcg(hr + i);
+      if (exchange) {
+        // sum of the ranks' partial outputs, in rank order on every rank
+        float sum = 0.0f;
+        for (int j = 0; j < xch.tp_size; ++j) {
+          const float* pj = xch.partial[j] + (size_t)b * d + i;
+          const float t = j == xch.tp_rank ? __ldcg(pj) : ld_peer(pj);
+          sum = j == 0 ? t : __fadd_rn(sum, t);
+        }
+        v = __fadd_rn(v, sum);
+        if (live) hr[i] = v;
+      } else if (delta) {
+        v = __fadd_rn(v, __ldcg(delta + (size_t)b * d + i));
+        if (live) hr[i] = v;
+      }
+      xs[i] = v;
+      ss += v * v;
+    }
+    ss = block_reduce(ss, [](float a, float c) { return a + c; }, 0.0f, red);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      const float v = __fmul_rn(__fmul_rn(xs[i], inv), gain[i]);
+      xs[i] = v;
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
+    }
+    quantize_smem_row(xs, d, d_pad, b, m_alloc, mn, mx, q_tiled, scales, zps, red, live);
+    __syncthreads();
   }
-  ss = block_reduce(ss, [](float a, float c) { return a + c; }, 0.0f, red);
-  const float inv = 1.0f / sqrtf(ss / (float)d + eps);
-  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    const float v = __fmul_rn(__fmul_rn(xs[i], inv), gain[i]);
-    xs[i] = v;
-    mn = fminf(mn, v);
-    mx = fmaxf(mx, v);
-  }
-  quantize_smem_row(xs, d, d_pad, b, m_alloc, mn, mx, q_tiled, scales, zps, red);
 }
 
 __device__ __forceinline__ float gelu_tanh(float v) {
@@ -152,54 +166,61 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank();
   const int b = blockIdx.x / kGegluCluster;
-  pdl_enter();
+  pdl_launch_dependents();
   const float* g = gate_up + (size_t)b * 2 * f;
   const float* u = g + f;
   const int lo = rank * per_cta, hi = min(f, lo + per_cta);
-  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-    const float v = __fmul_rn(gelu_tanh(g[i]), u[i]);
-    xs[i - lo] = v;
-    mn = fminf(mn, v);
-    mx = fmaxf(mx, v);
-  }
-  mn = block_reduce(mn, [](float a, float c) { return fminf(a, c); }, mn, red);
-  mx = block_reduce(mx, [](float a, float c) { return fmaxf(a, c); }, mx, red);
-  if (threadIdx.x == 0) {
-    s_minmax[0] = mn;
-    s_minmax[1] = mx;
-  }
-  cluster.sync();
-  if (threadIdx.x == 0) {
-    float rmn = 3.402823466e+38f, rmx = -3.402823466e+38f;
-    for (int r = 0; r < kGegluCluster; ++r) {
-      const float* remote = cluster.map_shared_rank(s_minmax, r);
-      rmn = fminf(rmn, remote[0]);
-      rmx = fmaxf(rmx, remote[1]);
+  // two passes over the same code: a dry run that warms the instruction caches while the producing
+  // kernel is still busy (nothing stored), then the real one after the dependency wait
+#pragma unroll 1
+  for (int pass = 0; pass < 2; ++pass) {
+    const bool live = pass == 1;
+    if (live) pdl_wait();
+    float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const float v = __fmul_rn(gelu_tanh(__ldcg(g + i)), __ldcg(u + i));  // past L1: see add_norm_quant_kernel
+      xs[i - lo] = v;
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
     }
-    float sf, inv;
-    int zp, zero_row;
-    row_quant_params(rmn, rmx, true, &sf, &inv, &zp, &zero_row);
-    s_zero = zero_row;
-    s_inv = inv;
-    s_zp = zp;
-    if (rank == 0) {
-      scales[b] = sf;
-      zps[b] = zp;
+    mn = block_reduce(mn, [](float a, float c) { return fminf(a, c); }, mn, red);
+    mx = block_reduce(mx, [](float a, float c) { return fmaxf(a, c); }, mx, red);
+    if (threadIdx.x == 0) {
+      s_minmax[0] = mn;
+      s_minmax[1] = mx;
     }
-  }
-  __syncthreads();
-  const bool zero = s_zero != 0;
-  const float inv = s_inv, zpf = (float)s_zp;
-  const int k_end = min(lo + per_cta, f_pad);  // the tiled row ends at the padded length
-  for (int k4 = lo + threadIdx.x * 4; k4 < k_end; k4 += blockDim.x * 4) {
-    uint32_t word = 0;
+    cluster.sync();
+    if (threadIdx.x == 0) {
+      float rmn = 3.402823466e+38f, rmx = -3.402823466e+38f;
+      for (int r = 0; r < kGegluCluster; ++r) {
+        const float* remote = cluster.map_shared_rank(s_minmax, r);
+        rmn = fminf(rmn, remote[0]);
+        rmx = fmaxf(rmx, remote[1]);
+      }
+      float sf, inv;
+      int zp, zero_row;
+      row_quant_params(rmn, rmx, true, &sf, &inv, &zp, &zero_row);
+      s_zero = zero_row;
+      s_inv = inv;
+      s_zp = zp;
+      if (rank == 0 && live) {
+        scales[b] = sf;
+        zps[b] = zp;
+      }
+    }
+    __syncthreads();
+    const bool zero = s_zero != 0;
+    const float inv = s_inv, zpf = (float)s_zp;
+    const int k_end = min(lo + per_cta, f_pad);  // the tiled row ends at the padded length
+    for (int k4 = lo + threadIdx.x * 4; k4 < k_end; k4 += blockDim.x * 4) {
+      uint32_t word = 0;
 #pragma unroll
-    for (int e = 0; e < 4; ++e)
-      if (k4 + e < f && !zero) word |= quantize_value(xs[k4 + e - lo], inv, zpf, true) << (8 * e);
-    *reinterpret_cast<uint32_t*>(q_tiled + q_tiled_offset(b, k4, m_alloc)) = word;
+      for (int e = 0; e < 4; ++e)
+        if (k4 + e < f && !zero) word |= quantize_value(xs[k4 + e - lo], inv, zpf, true) << (8 * e);
+      if (live) *reinterpret_cast<uint32_t*>(q_tiled + q_tiled_offset(b, k4, m_alloc)) = word;
+    }
+    cluster.sync();  // neighbours are done with this CTA's min / max (and no CTA exits before that)
   }
-  cluster.sync();  // no CTA may exit while a neighbour can still read its shared memory
 }
 
 // Rotary embedding of q and k from the fused qkv projection output, and the

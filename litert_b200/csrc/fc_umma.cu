@@ -142,11 +142,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
       // activations has finished (programmatic dependent launch), one ring's worth at most.
       pdl_launch_dependents();
       const uint32_t stage_tx = p.prologue ? (uint32_t)kTileBytes : (uint32_t)L::kStageBytes;
+      const uint64_t stream_policy = l2_policy_evict_first();  // weights are read once per launch
       uint32_t pre = 0;
       for (long long t = t_begin; t < t_end && pre < (uint32_t)L::kStages; ++t, ++pre) {
         uint8_t* dst = smem + (size_t)pre * L::kStageBytes;
         mbar_arrive_expect_tx(&full_bar[pre], stage_tx);
-        bulk_g2s(dst, p.w_packed + (size_t)t * kTileBytes, kTileBytes, &full_bar[pre]);
+        bulk_g2s_hint(dst, p.w_packed + (size_t)t * kTileBytes, kTileBytes, &full_bar[pre], stream_policy);
       }
       pdl_wait();               // activations (and the split-K scratch) are now safe to touch
       if (p.trace && blockIdx.x == 0) p.trace[1] = global_timer_ns();
@@ -164,7 +165,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, p.status, kStatusWaitTimeoutEmpty);
         uint8_t* dst = smem + (size_t)s * L::kStageBytes;
         mbar_arrive_expect_tx(&full_bar[s], stage_tx);
-        bulk_g2s(dst, p.w_packed + (size_t)t * kTileBytes, kTileBytes, &full_bar[s]);
+        bulk_g2s_hint(dst, p.w_packed + (size_t)t * kTileBytes, kTileBytes, &full_bar[s], stream_policy);
         if (!p.prologue) {
           const int kt = (int)(t % p.k_tiles);
           const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
@@ -455,10 +456,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
     if (lane == 0) {
       pdl_launch_dependents();
       const uint32_t stage_tx = p.prologue ? (uint32_t)kTileBytes : (uint32_t)L::kStageBytes;
+      const uint64_t stream_policy = l2_policy_evict_first();  // weights are read once per launch
       uint32_t pre = 0;
       for (int kt = kt_begin; kt < kt_end && pre < (uint32_t)L::kStages; ++kt, ++pre) {
         mbar_arrive_expect_tx(&full_bar[pre], stage_tx);
-        bulk_g2s(smem + (size_t)pre * L::kStageBytes, w_tiles + (size_t)kt * kTileBytes, kTileBytes, &full_bar[pre]);
+        bulk_g2s_hint(smem + (size_t)pre * L::kStageBytes, w_tiles + (size_t)kt * kTileBytes, kTileBytes, &full_bar[pre],
+                      stream_policy);
       }
       pdl_wait();
       if (p.trace && blockIdx.x == 0) p.trace[1] = global_timer_ns();
@@ -475,7 +478,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
         mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, p.status, kStatusWaitTimeoutEmpty);
         uint8_t* dst = smem + (size_t)s * L::kStageBytes;
         mbar_arrive_expect_tx(&full_bar[s], stage_tx);
-        bulk_g2s(dst, w_tiles + (size_t)kt * kTileBytes, kTileBytes, &full_bar[s]);
+        bulk_g2s_hint(dst, w_tiles + (size_t)kt * kTileBytes, kTileBytes, &full_bar[s], stream_policy);
         if (!p.prologue) {
           const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
           bulk_g2s(dst + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[s]);

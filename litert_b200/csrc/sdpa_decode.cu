@@ -122,6 +122,11 @@ __host__ __device__ inline size_t partial_stride(int h) { return (size_t)h + 2; 
 // softmax state for heads 2t and 2t+1 (log2 domain) and the un-normalised outputs, in registers.
 // GPI = groups of 16 tokens a warp takes per pass (1, 2 or 4): small for short caches, where the
 // kernel is latency-bound and wants as many warps as possible, 4 for long ones.
+#ifdef B200_ATTN_DBG
+__device__ long long g_attn_dbg[64];
+__device__ int g_attn_dbg_on;
+#endif
+
 template <int KV, int H, int GPI>
 struct WarpAttention {
   static constexpr int DB = H < 128 ? H : 128;  // head-dim block of the PV step
@@ -178,7 +183,14 @@ struct WarpAttention {
 
   const float scale_log2 = p.scale * kLog2e;
 
+#ifdef B200_ATTN_DBG
+  int dbg_i = 0;
+#define DBG_STAMP(k) if (g_attn_dbg_on && threadIdx.x == 0 && blockIdx.x == 0 && dbg_i < 4) g_attn_dbg[dbg_i * 8 + (k)] = clock64()
+#else
+#define DBG_STAMP(k)
+#endif
   for (int base = first; base < c1; base += step) {
+    DBG_STAMP(0);
     // ---- S^T = K Q^T for GPI groups of 16 tokens ----
     float s[GPI][4];
 #pragma unroll
@@ -203,6 +215,7 @@ struct WarpAttention {
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[gi][e] = (part[0][e] + part[1][e]) + (part[2][e] + part[3][e]);
+      if (gi == 0) { DBG_STAMP(1); }
       // scale (and dequantise), cap, mask; work in the log2 domain
       float fa = scale_log2, fb = scale_log2;
       if constexpr (KV == kKvI8) {
@@ -228,6 +241,7 @@ struct WarpAttention {
       if (!va) s[gi][0] = s[gi][1] = -CUDART_INF_F;
       if (!vb) s[gi][2] = s[gi][3] = -CUDART_INF_F;
     }
+    DBG_STAMP(2);
     // ---- online softmax over these tokens ----
     float mx[2];
 #pragma unroll
@@ -256,6 +270,7 @@ struct WarpAttention {
       o[i][2] *= alpha[0];
       o[i][3] *= alpha[1];
     }
+    DBG_STAMP(3);
     // ---- O^T += V^T P^T ----
 #pragma unroll
     for (int gi = 0; gi < GPI; ++gi) {
@@ -419,6 +434,7 @@ constexpr int kAttnCluster = 8;
 // take 4.6 us in the token loop, 8 warps x 2 passes 5.4 us: the loop's cost is mostly fixed (cold
 // instruction and data fetches after the weight stream has swept L2), not per token.
 constexpr int kAttnWarps = 4;
+constexpr bool kAttnDryRun = false;
 
 template <int H>
 struct AttnStepSmem {
@@ -431,8 +447,8 @@ struct AttnStepSmem {
   float own[H];                   // finished head
   float2 mmbox[kAttnCluster];     // min / max of every CTA's finished head
   float2 red[kAttnWarps];
-  // followed by the staging area: `stage_rows` key rows then as many value rows, each padded by
-  // 16 bytes against bank conflicts; the warps' parked outputs reuse it after the token loop
+  // followed by the staging area (`stage_rows` key rows then as many value rows, each padded by
+  // 16 bytes against bank conflicts) and the warps' parked outputs
 };
 template <int KV, int H>
 __host__ __device__ constexpr int attn_row_pitch() {
@@ -454,7 +470,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
   AttnStepSmem<H>& sm = *reinterpret_cast<AttnStepSmem<H>*>(attn_smem_raw);
   uint8_t* stage_k = attn_smem_raw + ((sizeof(AttnStepSmem<H>) + 127) / 128) * 128;
   uint8_t* stage_v = stage_k + (size_t)stage_rows * PITCH;
-  float (*sm_o)[8][H + 4] = reinterpret_cast<float (*)[8][H + 4]>(stage_k);
+  // the warps' parked outputs follow the staged rows (the dry-run pass parks too: no sharing)
+  float (*sm_o)[8][H + 4] = reinterpret_cast<float (*)[8][H + 4]>(stage_v + (size_t)stage_rows * PITCH);
 
   const bool tracer = p.trace && blockIdx.x == 0 && threadIdx.x == 0;
   if (tracer) p.trace[0] = global_timer_ns();
@@ -497,242 +514,254 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
     sm.cs[i] = make_float2(cs, sn);
   }
   if (tracer) p.trace[11] = global_timer_ns();
-  pdl_wait();  // this step's q / k / v
-  if (tracer) p.trace[1] = global_timer_ns();
-  __syncthreads();
-  const float* src = p.qkv + (size_t)b * (p.n + 2) * H;
-  for (int idx = tid; idx < p.n * HALF; idx += kAttnWarps * 32) {
-    const int head = idx / HALF, i = idx % HALF;
-    const float x1 = src[head * H + i], x2 = src[head * H + i + HALF];
-    const float2 r = sm.cs[i];
-    sm.q[head][i] = x1 * r.x - x2 * r.y;
-    sm.q[head][i + HALF] = x2 * r.x + x1 * r.y;
-  }
-  if (append && pos >= c0 && pos < c1) {
-    // The CTA whose share holds the new token writes its row: to the cache, and to the staged
-    // copy it is about to read (the same rounded values later steps will find in the cache).
-    const float* ksrc = src + (size_t)p.n * H;
-    const float* vsrc = ksrc + H;
-    const size_t tok = (size_t)b * p.s_max + pos;
-    if constexpr (KV == kKvI8) {
-      // symmetric per token: scale = max|row| / 127 (key after the rotation)
-      float ka = 0.0f, va = 0.0f;
-      for (int i = tid; i < HALF; i += kAttnWarps * 32) {
-        const float2 r = sm.cs[i];
-        const float x1 = ksrc[i], x2 = ksrc[i + HALF];
-        ka = fmaxf(ka, fmaxf(fabsf(x1 * r.x - x2 * r.y), fabsf(x2 * r.x + x1 * r.y)));
-        va = fmaxf(va, fmaxf(fabsf(vsrc[i]), fabsf(vsrc[i + HALF])));
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        ka = fmaxf(ka, __shfl_xor_sync(0xffffffffu, ka, o));
-        va = fmaxf(va, __shfl_xor_sync(0xffffffffu, va, o));
-      }
-      if (lane == 0) sm.red[warp] = make_float2(ka, va);
-      __syncthreads();
-      ka = sm.red[0].x, va = sm.red[0].y;
-#pragma unroll
-      for (int w = 1; w < kAttnWarps; ++w) {
-        ka = fmaxf(ka, sm.red[w].x);
-        va = fmaxf(va, sm.red[w].y);
-      }
-      const float ks = ka > 0.0f ? ka / 127.0f : 1.0f, vs = va > 0.0f ? va / 127.0f : 1.0f;
-      int8_t* kd = static_cast<int8_t*>(p.k_cache) + tok * H;
-      int8_t* vd = static_cast<int8_t*>(p.v_cache) + tok * H;
-      int8_t* ks_row = reinterpret_cast<int8_t*>(stage_k + (size_t)(pos - c0) * PITCH);
-      int8_t* vs_row = reinterpret_cast<int8_t*>(stage_v + (size_t)(pos - c0) * PITCH);
-      for (int i = tid; i < HALF; i += kAttnWarps * 32) {
-        const float2 r = sm.cs[i];
-        const float x1 = ksrc[i], x2 = ksrc[i + HALF];
-        const int8_t k1 = (int8_t)max(-127, min(127, __float2int_rn((x1 * r.x - x2 * r.y) / ks)));
-        const int8_t k2 = (int8_t)max(-127, min(127, __float2int_rn((x2 * r.x + x1 * r.y) / ks)));
-        const int8_t v1 = (int8_t)max(-127, min(127, __float2int_rn(vsrc[i] / vs)));
-        const int8_t v2 = (int8_t)max(-127, min(127, __float2int_rn(vsrc[i + HALF] / vs)));
-        kd[i] = k1, kd[i + HALF] = k2, vd[i] = v1, vd[i + HALF] = v2;
-        if (staged) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
-      }
-      if (tid == 0) {
-        p.k_scale[tok] = ks;
-        p.v_scale[tok] = vs;
-      }
-    } else {
-      __half* kd = static_cast<__half*>(p.k_cache) + tok * H;
-      __half* vd = static_cast<__half*>(p.v_cache) + tok * H;
-      __half* ks_row = reinterpret_cast<__half*>(stage_k + (size_t)(pos - c0) * PITCH);
-      __half* vs_row = reinterpret_cast<__half*>(stage_v + (size_t)(pos - c0) * PITCH);
-      for (int i = tid; i < HALF; i += kAttnWarps * 32) {
-        const float2 r = sm.cs[i];
-        const float x1 = ksrc[i], x2 = ksrc[i + HALF];
-        const __half k1 = __float2half_rn(x1 * r.x - x2 * r.y), k2 = __float2half_rn(x2 * r.x + x1 * r.y);
-        const __half v1 = __float2half_rn(vsrc[i]), v2 = __float2half_rn(vsrc[i + HALF]);
-        kd[i] = k1, kd[i + HALF] = k2, vd[i] = v1, vd[i + HALF] = v2;
-        if (staged) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
+  // With kAttnDryRun the code below runs twice: first at once, on stale q / k / v, storing nothing
+  // outside the CTAs' shared memory, to pull instructions into the caches while the projection
+  // kernel is still running; then for real after the dependency wait. Measured on B200 it does not
+  // pay here (the dry run outlasts the projection kernel by 8 us, and the real pass is no faster:
+  // its time is not instruction fetches), so it is off; the row kernels of the decoder keep theirs.
+#pragma unroll 1
+  for (int pass = kAttnDryRun ? 0 : 1; pass < 2; ++pass) {
+    const bool live = pass == 1;
+    if (live) {
+      pdl_wait();  // this step's q / k / v
+      if (tracer) p.trace[1] = global_timer_ns();
+    }
+    __syncthreads();
+    const float* src = p.qkv + (size_t)b * (p.n + 2) * H;
+    for (int idx = tid; idx < p.n * HALF; idx += kAttnWarps * 32) {
+      const int head = idx / HALF, i = idx % HALF;
+      const float x1 = __ldcg(src + head * H + i), x2 = __ldcg(src + head * H + i + HALF);  // past L1: the dry run read them too
+      const float2 r = sm.cs[i];
+      sm.q[head][i] = x1 * r.x - x2 * r.y;
+      sm.q[head][i + HALF] = x2 * r.x + x1 * r.y;
+    }
+    if (append && pos >= c0 && pos < c1) {
+      // The CTA whose share holds the new token writes its row: to the cache, and to the staged
+      // copy it is about to read (the same rounded values later steps will find in the cache).
+      const float* ksrc = src + (size_t)p.n * H;
+      const float* vsrc = ksrc + H;
+      const size_t tok = (size_t)b * p.s_max + pos;
+      if constexpr (KV == kKvI8) {
+        // symmetric per token: scale = max|row| / 127 (key after the rotation)
+        float ka = 0.0f, va = 0.0f;
+        for (int i = tid; i < HALF; i += kAttnWarps * 32) {
+          const float2 r = sm.cs[i];
+          const float x1 = __ldcg(ksrc + i), x2 = __ldcg(ksrc + i + HALF);
+          ka = fmaxf(ka, fmaxf(fabsf(x1 * r.x - x2 * r.y), fabsf(x2 * r.x + x1 * r.y)));
+          va = fmaxf(va, fmaxf(fabsf(__ldcg(vsrc + i)), fabsf(__ldcg(vsrc + i + HALF))));
+        }
+  #pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          ka = fmaxf(ka, __shfl_xor_sync(0xffffffffu, ka, o));
+          va = fmaxf(va, __shfl_xor_sync(0xffffffffu, va, o));
+        }
+        if (lane == 0) sm.red[warp] = make_float2(ka, va);
+        __syncthreads();
+        ka = sm.red[0].x, va = sm.red[0].y;
+  #pragma unroll
+        for (int w = 1; w < kAttnWarps; ++w) {
+          ka = fmaxf(ka, sm.red[w].x);
+          va = fmaxf(va, sm.red[w].y);
+        }
+        const float ks = ka > 0.0f ? ka / 127.0f : 1.0f, vs = va > 0.0f ? va / 127.0f : 1.0f;
+        int8_t* kd = static_cast<int8_t*>(p.k_cache) + tok * H;
+        int8_t* vd = static_cast<int8_t*>(p.v_cache) + tok * H;
+        int8_t* ks_row = reinterpret_cast<int8_t*>(stage_k + (size_t)(pos - c0) * PITCH);
+        int8_t* vs_row = reinterpret_cast<int8_t*>(stage_v + (size_t)(pos - c0) * PITCH);
+        for (int i = tid; i < HALF; i += kAttnWarps * 32) {
+          const float2 r = sm.cs[i];
+          const float x1 = __ldcg(ksrc + i), x2 = __ldcg(ksrc + i + HALF);
+          const int8_t k1 = (int8_t)max(-127, min(127, __float2int_rn((x1 * r.x - x2 * r.y) / ks)));
+          const int8_t k2 = (int8_t)max(-127, min(127, __float2int_rn((x2 * r.x + x1 * r.y) / ks)));
+          const int8_t v1 = (int8_t)max(-127, min(127, __float2int_rn(__ldcg(vsrc + i) / vs)));
+          const int8_t v2 = (int8_t)max(-127, min(127, __float2int_rn(__ldcg(vsrc + i + HALF) / vs)));
+          if (live) kd[i] = k1, kd[i + HALF] = k2, vd[i] = v1, vd[i + HALF] = v2;
+          if (staged) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
+        }
+        if (tid == 0 && live) {
+          p.k_scale[tok] = ks;
+          p.v_scale[tok] = vs;
+        }
+      } else {
+        __half* kd = static_cast<__half*>(p.k_cache) + tok * H;
+        __half* vd = static_cast<__half*>(p.v_cache) + tok * H;
+        __half* ks_row = reinterpret_cast<__half*>(stage_k + (size_t)(pos - c0) * PITCH);
+        __half* vs_row = reinterpret_cast<__half*>(stage_v + (size_t)(pos - c0) * PITCH);
+        for (int i = tid; i < HALF; i += kAttnWarps * 32) {
+          const float2 r = sm.cs[i];
+          const float x1 = __ldcg(ksrc + i), x2 = __ldcg(ksrc + i + HALF);
+          const __half k1 = __float2half_rn(x1 * r.x - x2 * r.y), k2 = __float2half_rn(x2 * r.x + x1 * r.y);
+          const __half v1 = __float2half_rn(__ldcg(vsrc + i)), v2 = __float2half_rn(__ldcg(vsrc + i + HALF));
+          if (live) kd[i] = k1, kd[i + HALF] = k2, vd[i] = v1, vd[i + HALF] = v2;
+          if (staged) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
+        }
       }
     }
-  }
-  cp_async_wait_all();
-  __syncthreads();  // rotated queries, staged rows and the new row (staged copy, or the cache through this CTA's own stores) in place
+    cp_async_wait_all();
+    __syncthreads();  // rotated queries, staged rows and the new row (staged copy, or the cache through this CTA's own stores) in place
 
-  if (tracer) p.trace[2] = global_timer_ns();
-  uint32_t qf[KSTEPS][4];
-#pragma unroll
-  for (int i = 0; i < KSTEPS; ++i) {
-    const int d0 = 8 * (t + 4 * i);
-    if (g < p.n) {
-      const float* q = &sm.q[g][d0];
-      qf[i][0] = pack_half2(q[0], q[1]);
-      qf[i][1] = pack_half2(q[2], q[3]);
-      qf[i][2] = pack_half2(q[4], q[5]);
-      qf[i][3] = pack_half2(q[6], q[7]);
+    if (tracer && live) p.trace[2] = global_timer_ns();
+    uint32_t qf[KSTEPS][4];
+  #pragma unroll
+    for (int i = 0; i < KSTEPS; ++i) {
+      const int d0 = 8 * (t + 4 * i);
+      if (g < p.n) {
+        const float* q = &sm.q[g][d0];
+        qf[i][0] = pack_half2(q[0], q[1]);
+        qf[i][1] = pack_half2(q[2], q[3]);
+        qf[i][2] = pack_half2(q[4], q[5]);
+        qf[i][3] = pack_half2(q[6], q[7]);
+      } else {
+        qf[i][0] = qf[i][1] = qf[i][2] = qf[i][3] = 0u;
+      }
+    }
+    SdpaParams sp;
+    sp.mask = nullptr;
+    sp.nkv = 1;
+    sp.s_max = p.s_max;
+    sp.scale = p.scale;
+    sp.logit_cap = 0.0f;
+    typename WA::Rows rows;
+    rows.k_scale = p.k_scale ? p.k_scale + (size_t)b * p.s_max : nullptr;
+    rows.v_scale = p.v_scale ? p.v_scale + (size_t)b * p.s_max : nullptr;
+    rows.scale_stride = 1;
+    if (staged) {
+      rows.k = stage_k - (ptrdiff_t)c0 * PITCH;  // indexed by absolute token
+      rows.v = stage_v - (ptrdiff_t)c0 * PITCH;
+      rows.stride = PITCH;
     } else {
-      qf[i][0] = qf[i][1] = qf[i][2] = qf[i][3] = 0u;
+      rows.k = kglob;
+      rows.v = vglob;
+      rows.stride = ROW_BYTES;
     }
-  }
-  SdpaParams sp;
-  sp.mask = nullptr;
-  sp.nkv = 1;
-  sp.s_max = p.s_max;
-  sp.scale = p.scale;
-  sp.logit_cap = 0.0f;
-  typename WA::Rows rows;
-  rows.k_scale = p.k_scale ? p.k_scale + (size_t)b * p.s_max : nullptr;
-  rows.v_scale = p.v_scale ? p.v_scale + (size_t)b * p.s_max : nullptr;
-  rows.scale_stride = 1;
-  if (staged) {
-    rows.k = stage_k - (ptrdiff_t)c0 * PITCH;  // indexed by absolute token
-    rows.v = stage_v - (ptrdiff_t)c0 * PITCH;
-    rows.stride = PITCH;
-  } else {
-    rows.k = kglob;
-    rows.v = vglob;
-    rows.stride = ROW_BYTES;
-  }
-  if (tracer) p.trace[3] = global_timer_ns();
-  // the warps take equal contiguous shares of the CTA's tokens (multiples of 16)
-  const int wper = ((((c1 - c0) + kAttnWarps - 1) / kAttnWarps) + 15) / 16 * 16;
-  const int first = c0 + warp * wper;
-  const int last = min(c1, first + wper);
-  WA wa;
-  if (first >= last) {
-    wa.clear();
-  } else if (staged) {
-    wa.template run<kSrcShared>(sp, qf, rows, b, first, WA::kTokensPerWarpIter, last, lane);
-  } else {
-    wa.template run<kSrcGlobalCoherent>(sp, qf, rows, b, first, WA::kTokensPerWarpIter, last, lane);
-  }
-  if (tracer) p.trace[4] = global_timer_ns();
-  __syncthreads();  // every warp is done with the staged rows: their space now takes the parked outputs
-  wa.park(sm.sm_m, sm.sm_l, sm_o, warp, lane);
-  __syncthreads();
-  // this CTA's state per head: the warps merged (weights per warp and head computed once)
-  if (tid < 8) {
-    const int head = tid;
-    float mm = -CUDART_INF_F;
-#pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, sm.sm_m[w][head]);
-    const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
-    float l = 0.0f;
-#pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) {
-      const float f = exp2f(sm.sm_m[w][head] - muse);
-      sm.wf[w][head] = f;
-      l += f * sm.sm_l[w][head];
+    if (tracer && live) p.trace[3] = global_timer_ns();
+    // the warps take equal contiguous shares of the CTA's tokens (multiples of 16)
+    const int wper = ((((c1 - c0) + kAttnWarps - 1) / kAttnWarps) + 15) / 16 * 16;
+    const int first = c0 + warp * wper;
+    const int last = min(c1, first + wper);
+    WA wa;
+    if (first >= last) {
+      wa.clear();
+    } else if (staged) {
+      wa.template run<kSrcShared>(sp, qf, rows, b, first, WA::kTokensPerWarpIter, last, lane);
+    } else {
+      wa.template run<kSrcGlobalCoherent>(sp, qf, rows, b, first, WA::kTokensPerWarpIter, last, lane);
     }
-    sm.rec[head][H] = mm;
-    sm.rec[head][H + 1] = l;
-  }
-  __syncthreads();
-  for (int idx = tid; idx < p.n * H; idx += kAttnWarps * 32) {
-    const int head = idx / H, d = idx % H;
-    float acc = 0.0f;
-#pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) acc += sm.wf[w][head] * sm_o[w][head][d];
-    sm.rec[head][d] = acc;
-  }
-  __syncthreads();
-  if (tracer) p.trace[5] = global_timer_ns();
-  cluster_wait();  // phase 0
-  // head h goes to CTA h (n <= 8 = cluster size)
-  for (int head = 0; head < p.n; ++head) {
-    const uint32_t dst = map_to_rank(smem_u32(&sm.inbox[rank][0]), (uint32_t)head);
-    for (int i = tid; i < REC; i += kAttnWarps * 32) st_cluster_f32(dst + 4u * (uint32_t)i, sm.rec[head][i]);
-  }
-  cluster_arrive();  // phase 1: delivered ...
-  cluster_wait();    // ... and received
-  if (tracer) p.trace[6] = global_timer_ns();
-  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
-  const bool owner = rank < p.n;
-  if (owner) {
-    float mm = -CUDART_INF_F;
-#pragma unroll
-    for (int c = 0; c < C; ++c) mm = fmaxf(mm, sm.inbox[c][H]);
-    const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
-    float f[C], l = 0.0f;
-#pragma unroll
-    for (int c = 0; c < C; ++c) {
-      f[c] = exp2f(sm.inbox[c][H] - muse);
-      l += f[c] * sm.inbox[c][H + 1];
+    if (tracer && live) p.trace[4] = global_timer_ns();
+      wa.park(sm.sm_m, sm.sm_l, sm_o, warp, lane);
+    __syncthreads();
+    // this CTA's state per head: the warps merged (weights per warp and head computed once)
+    if (tid < 8) {
+      const int head = tid;
+      float mm = -CUDART_INF_F;
+  #pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, sm.sm_m[w][head]);
+      const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
+      float l = 0.0f;
+  #pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) {
+        const float f = exp2f(sm.sm_m[w][head] - muse);
+        sm.wf[w][head] = f;
+        l += f * sm.sm_l[w][head];
+      }
+      sm.rec[head][H] = mm;
+      sm.rec[head][H + 1] = l;
     }
-    for (int d = tid; d < H; d += kAttnWarps * 32) {
+    __syncthreads();
+    for (int idx = tid; idx < p.n * H; idx += kAttnWarps * 32) {
+      const int head = idx / H, d = idx % H;
       float acc = 0.0f;
-#pragma unroll
-      for (int c = 0; c < C; ++c) acc += f[c] * sm.inbox[c][d];
-      const float v = acc / l;
-      sm.own[d] = v;
-      mn = fminf(mn, v);
-      mx = fmaxf(mx, v);
+  #pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) acc += sm.wf[w][head] * sm_o[w][head][d];
+      sm.rec[head][d] = acc;
     }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  }
-  if (lane == 0) sm.red[warp] = make_float2(mn, mx);
-  __syncthreads();
-  if (tid < C) {
-    float lo = sm.red[0].x, hi = sm.red[0].y;
-#pragma unroll
-    for (int w = 1; w < kAttnWarps; ++w) {
-      lo = fminf(lo, sm.red[w].x);
-      hi = fmaxf(hi, sm.red[w].y);
+    __syncthreads();
+    if (tracer && live) p.trace[5] = global_timer_ns();
+    if (pass == (kAttnDryRun ? 0 : 1)) cluster_wait();  // phase 0, once
+    // head h goes to CTA h (n <= 8 = cluster size)
+    for (int head = 0; head < p.n; ++head) {
+      const uint32_t dst = map_to_rank(smem_u32(&sm.inbox[rank][0]), (uint32_t)head);
+      for (int i = tid; i < REC; i += kAttnWarps * 32) st_cluster_f32(dst + 4u * (uint32_t)i, sm.rec[head][i]);
     }
-    const uint32_t dst = map_to_rank(smem_u32(&sm.mmbox[rank]), (uint32_t)tid);
-    st_cluster_f32(dst, lo);
-    st_cluster_f32(dst + 4u, hi);
-  }
-  cluster_arrive();  // phase 2
-  cluster_wait();
-  if (tracer) p.trace[7] = global_timer_ns();
-  float lo = sm.mmbox[0].x, hi = sm.mmbox[0].y;
-#pragma unroll
-  for (int c = 1; c < C; ++c) {
-    lo = fminf(lo, sm.mmbox[c].x);
-    hi = fmaxf(hi, sm.mmbox[c].y);
-  }
-  float sf, inv;
-  int zp, zero_row;
-  row_quant_params(lo, hi, true, &sf, &inv, &zp, &zero_row);
-  const float zpf = (float)zp;
-  if (owner) {
-    for (int d4 = tid * 4; d4 < H; d4 += kAttnWarps * 32 * 4) {
-      uint32_t word = 0;
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (!zero_row) word |= quantize_value(sm.own[d4 + e], inv, zpf, true) << (8 * e);
-      *reinterpret_cast<uint32_t*>(p.q_tiled_out + q_tiled_offset(b, rank * H + d4, p.m_alloc)) = word;
+    cluster_arrive();  // phase 1: delivered ...
+    cluster_wait();    // ... and received
+    if (tracer && live) p.trace[6] = global_timer_ns();
+    float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+    const bool owner = rank < p.n;
+    if (owner) {
+      float mm = -CUDART_INF_F;
+  #pragma unroll
+      for (int c = 0; c < C; ++c) mm = fmaxf(mm, sm.inbox[c][H]);
+      const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
+      float f[C], l = 0.0f;
+  #pragma unroll
+      for (int c = 0; c < C; ++c) {
+        f[c] = exp2f(sm.inbox[c][H] - muse);
+        l += f[c] * sm.inbox[c][H + 1];
+      }
+      for (int d = tid; d < H; d += kAttnWarps * 32) {
+        float acc = 0.0f;
+  #pragma unroll
+        for (int c = 0; c < C; ++c) acc += f[c] * sm.inbox[c][d];
+        const float v = acc / l;
+        sm.own[d] = v;
+        mn = fminf(mn, v);
+        mx = fmaxf(mx, v);
+      }
     }
-  }
-  if (rank == 0) {
-    const int width = p.n * H, k_pad = (width + 127) / 128 * 128;
-    for (int k4 = width + tid * 4; k4 < k_pad; k4 += kAttnWarps * 32 * 4)
-      *reinterpret_cast<uint32_t*>(p.q_tiled_out + q_tiled_offset(b, k4, p.m_alloc)) = 0u;
-    if (tid == 0) {
-      p.out_scales[b] = sf;
-      p.out_zps[b] = zp;
+  #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     }
+    if (lane == 0) sm.red[warp] = make_float2(mn, mx);
+    __syncthreads();
+    if (tid < C) {
+      float lo = sm.red[0].x, hi = sm.red[0].y;
+  #pragma unroll
+      for (int w = 1; w < kAttnWarps; ++w) {
+        lo = fminf(lo, sm.red[w].x);
+        hi = fmaxf(hi, sm.red[w].y);
+      }
+      const uint32_t dst = map_to_rank(smem_u32(&sm.mmbox[rank]), (uint32_t)tid);
+      st_cluster_f32(dst, lo);
+      st_cluster_f32(dst + 4u, hi);
+    }
+    cluster_arrive();  // phase 2
+    cluster_wait();
+    if (tracer && live) p.trace[7] = global_timer_ns();
+    float lo = sm.mmbox[0].x, hi = sm.mmbox[0].y;
+  #pragma unroll
+    for (int c = 1; c < C; ++c) {
+      lo = fminf(lo, sm.mmbox[c].x);
+      hi = fmaxf(hi, sm.mmbox[c].y);
+    }
+    float sf, inv;
+    int zp, zero_row;
+    row_quant_params(lo, hi, true, &sf, &inv, &zp, &zero_row);
+    const float zpf = (float)zp;
+    if (owner) {
+      for (int d4 = tid * 4; d4 < H; d4 += kAttnWarps * 32 * 4) {
+        uint32_t word = 0;
+  #pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (!zero_row) word |= quantize_value(sm.own[d4 + e], inv, zpf, true) << (8 * e);
+        if (live) *reinterpret_cast<uint32_t*>(p.q_tiled_out + q_tiled_offset(b, rank * H + d4, p.m_alloc)) = word;
+      }
+    }
+    if (rank == 0 && live) {
+      const int width = p.n * H, k_pad = (width + 127) / 128 * 128;
+      for (int k4 = width + tid * 4; k4 < k_pad; k4 += kAttnWarps * 32 * 4)
+        *reinterpret_cast<uint32_t*>(p.q_tiled_out + q_tiled_offset(b, k4, p.m_alloc)) = 0u;
+      if (tid == 0) {
+        p.out_scales[b] = sf;
+        p.out_zps[b] = zp;
+      }
+    }
+    if (tracer && live) p.trace[8] = global_timer_ns();
+
+    __syncthreads();  // the next pass reuses the shared buffers
   }
-  if (tracer) p.trace[8] = global_timer_ns();
 }
 
 // Reduces the per-chunk partials of one (batch, query head): grid (n, b),
@@ -964,17 +993,15 @@ cudaError_t launch_kv(const SdpaParams& p, cudaStream_t s) {
 
 template <int KV, int H>
 cudaError_t launch_attn_step_h(const AttnStepParams& p, cudaStream_t s) {
-  constexpr size_t kBudget = 200 * 1024;
-  const size_t fixed = ((sizeof(AttnStepSmem<H>) + 127) / 128) * 128;
+  constexpr size_t kBudget = 224 * 1024;
+  const size_t fixed = ((sizeof(AttnStepSmem<H>) + 127) / 128) * 128 + attn_park_bytes<H>();
   const int pitch = attn_row_pitch<KV, H>();
-  // as many staged rows as a CTA's share of the longest cache needs, within the budget; the
-  // staging area is never smaller than the warps' parked outputs that reuse it
+  // as many staged rows as a CTA's share of the longest cache needs, within the budget
   const int per_max = ((p.s_max + kAttnCluster - 1) / kAttnCluster + 15) / 16 * 16;
   int rows = (int)((kBudget - fixed) / (2 * (size_t)pitch));
+  rows = rows / 8 * 8;  // keeps the parked outputs 128-byte aligned
   if (rows > per_max) rows = per_max;
-  size_t stage = 2 * (size_t)rows * pitch;
-  if (stage < attn_park_bytes<H>()) stage = attn_park_bytes<H>();
-  const size_t smem = fixed + stage;
+  const size_t smem = fixed + 2 * (size_t)rows * pitch;
   auto go = [&](auto kernel) -> cudaError_t {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -985,7 +1012,7 @@ cudaError_t launch_attn_step_h(const AttnStepParams& p, cudaStream_t s) {
   // Staged rows are read from shared memory: passes are cheap, and the smallest loop body (16
   // tokens per warp and pass) costs the fewest instruction-cache misses, which dominate a kernel
   // that runs once per layer between large GEMVs. Rows read from the cache want long passes.
-  if (rows >= per_max || per_max <= 64) return go(attn_step_cluster_kernel<KV, H, 1>);
+  if (per_max <= rows + 16 || per_max <= 64) return go(attn_step_cluster_kernel<KV, H, 1>);
   if (per_max <= 128) return go(attn_step_cluster_kernel<KV, H, 2>);
   return go(attn_step_cluster_kernel<KV, H, 4>);
 }
