@@ -18,3 +18,14 @@ def oracle():
 
     orc.build()
     return orc
+
+
+@pytest.fixture(scope="session")
+def plugin_path():
+    """The delegate plugin, built on first use (skips where neither the library nor the headers exist)."""
+    from litert_b200 import build_delegate
+
+    p = build_delegate.build()
+    if p is None:
+        pytest.skip("delegate library not built and LiteRT headers absent")
+    return p

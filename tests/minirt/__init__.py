@@ -16,7 +16,8 @@ LIB = os.path.join(HERE, "libminirt.so")
 
 # TfLiteType values (tflite/core/c/c_api_types.h)
 F32, I32, U8, I64, I16, I8, F16, I4 = 1, 2, 3, 4, 7, 9, 10, 18
-_NP = {F32: np.float32, I32: np.int32, U8: np.uint8, I8: np.int8, F16: np.float16, I4: np.uint8}
+_NP = {F32: np.float32, I32: np.int32, U8: np.uint8, I8: np.int8, F16: np.float16, I4: np.uint8, I64: np.int64,
+       I16: np.int16, 6: np.bool_, 11: np.float64}
 # builtin operator codes (tflite/builtin_ops.h)
 OP_ADD, OP_FULLY_CONNECTED, OP_SOFTMAX = 0, 9, 25
 
@@ -226,3 +227,57 @@ def flex_map(values):
     buf += struct.pack("<I", root - map_pos)
     buf += bytes([(9 << 2) | 2, 4])  # MAP with 4-byte elements; root width 4
     return bytes(buf)
+
+
+# schema TensorType -> TfLiteType (ConvertTensorType, tflite/core/api/flatbuffer_conversions.cc)
+_SCHEMA_TO_TFLITE = {0: 1, 1: 10, 2: 2, 3: 3, 4: 4, 5: 5, 6: 6, 7: 7, 8: 8, 9: 9, 10: 11, 11: 12, 12: 13, 13: 14, 14: 15,
+                     15: 16, 16: 17, 17: 18, 18: 19, 19: 20}
+
+
+def load_model(model, subgraph=0):
+    """Builds a MiniRuntime graph from a parsed `.tflite` model (litert_b200.tflite_model.Model): what
+    InterpreterBuilder does for the tensors, quantization and nodes of one subgraph
+    (tflite/core/interpreter_builder.cc:334-518, 711-900), for the node kinds the delegate can claim;
+    every other builtin becomes a node for the test's CPU callback."""
+    from litert_b200 import tflite_model as tm
+
+    sg = model.subgraphs[subgraph]
+    rt = MiniRuntime()
+    for t in sg.tensors:
+        ttype = _SCHEMA_TO_TFLITE[t.type]
+        if ttype not in _NP:
+            raise ValueError(f"tensor type {t.type_name} is not handled by the mini runtime")
+        data = None
+        if t.data is not None:
+            data = np.frombuffer(t.data, np.uint8) if ttype == I4 else np.frombuffer(t.data, _NP[ttype])
+        q = t.quantization
+        scale, zp, cs, qdim = 0.0, 0, None, 0
+        if q is not None and q.scale.size == 1:
+            scale, zp = float(q.scale[0]), int(q.zero_point[0]) if q.zero_point.size else 0
+        elif q is not None and q.scale.size > 1:
+            cs, qdim = q.scale, q.quantized_dimension
+        shape = list(t.shape) if t.shape else [1]
+        rt.tensor(ttype, shape, data, scale, zp, cs, qdim)
+    for i, t in enumerate(sg.tensors):
+        q = t.quantization
+        if q is not None and q.blockwise_scales >= 0:
+            rt.set_blockwise(i, q.blockwise_scales, q.block_size)
+    for op in sg.operators:
+        o = op.options
+        if op.builtin_code == tm.BUILTIN_FULLY_CONNECTED:
+            bias = op.inputs[2] if len(op.inputs) > 2 and op.inputs[2] >= 0 else None
+            rt.fully_connected(op.inputs[0], op.inputs[1], bias, op.outputs[0], o.get("fused_activation_function", 0),
+                               o.get("keep_num_dims", False), o.get("asymmetric_quantize_inputs", False),
+                               o.get("weights_format", 0))
+        elif op.builtin_code == tm.BUILTIN_BATCH_MATMUL:
+            rt.batch_matmul(op.inputs[0], op.inputs[1], op.outputs[0], o.get("adj_x", False), o.get("adj_y", False),
+                            o.get("asymmetric_quantize_inputs", False))
+        elif op.builtin_code == tm.BUILTIN_STABLEHLO_COMPOSITE:
+            rt.composite(o.get("name", ""), o.get("composite_attributes", b""), op.inputs, op.outputs[0])
+        elif op.builtin_code == tm.BUILTIN_CUSTOM:
+            rt.custom(op.custom_code, op.custom_options, op.inputs, op.outputs[0])
+        else:
+            rt.other(op.builtin_code, [i for i in op.inputs if i >= 0], op.outputs[0])
+    rt.set_io(sg.inputs, sg.outputs)
+    return rt
+

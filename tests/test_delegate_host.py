@@ -15,16 +15,6 @@ from tests.minirt import F16, F32, I4, I8, I32
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.fixture(scope="module")
-def plugin_path():
-    from litert_b200 import build_delegate
-
-    p = build_delegate.build()
-    if p is None:
-        pytest.skip("delegate library not built and LiteRT headers absent")
-    return p
-
-
 def test_plugin_exports_the_external_delegate_symbols(plugin_path):
     lib = ctypes.CDLL(plugin_path)
     text = open(os.path.join(ROOT, "include", "litert_b200_delegate.h")).read()

@@ -279,3 +279,60 @@ def test_injected_invoke_failure_is_reported(rt):
     assert rt.invoke() == 2
     assert "injected failure in invoke" in rt.error
     d.close()
+
+
+# ---- graphs ingested from `.tflite` files -------------------------------------------------------
+def _model_from_file(kind, seed, m=5, n=200, k=320):
+    """A `.tflite` file written and parsed again (litert_b200.tflite_model), so that every tensor, scale
+    and option below reaches the delegate through the flatbuffer, as a user's model would."""
+    import test_tflite_model as tt
+    from litert_b200 import tflite_model as tm
+
+    return tm.read_model(tm.write_model(tt._fc_model(np.random.default_rng(seed), m=m, n=n, k=k, kind=kind)))
+
+
+def test_hybrid_fc_from_tflite_file(delegate, oracle):
+    model = _model_from_file("hybrid", 21)
+    sg = model.subgraphs[0]
+    rt = minirt.load_model(model)
+    x = np.random.default_rng(5).standard_normal((5, 320)).astype(np.float32)
+    rt.write(sg.inputs[0], x)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.partitions == 1 and rt.cpu_nodes == 0
+    assert rt.invoke() == 0, rt.error
+    w = sg.tensors[1]
+    want = oracle.fc_hybrid(x, w.array(), w.quantization.scale, None, True, oracle.ACT_NONE)
+    assert np.array_equal(rt.view(sg.outputs[0]).reshape(5, 200), want)
+    rt.close()
+
+
+def test_int8_fc_from_tflite_file(delegate, oracle):
+    model = _model_from_file("int8", 22)
+    sg = model.subgraphs[0]
+    rt = minirt.load_model(model)
+    xq = np.random.default_rng(6).integers(-128, 128, (5, 320)).astype(np.int8)
+    rt.write(sg.inputs[0], xq)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.invoke() == 0, rt.error
+    xt, wt, bt, yt = sg.tensors
+    want = oracle.fc_int8_per_channel(xq, wt.array(), bt.array(), int(xt.quantization.zero_point[0]),
+                                      float(xt.quantization.scale[0]), wt.quantization.scale,
+                                      float(yt.quantization.scale[0]), int(yt.quantization.zero_point[0]),
+                                      oracle.ACT_RELU)
+    assert np.array_equal(rt.view(sg.outputs[0]).reshape(5, 200), want)
+    rt.close()
+
+
+def test_blockwise_int4_fc_from_tflite_file(delegate, oracle):
+    model = _model_from_file("w4", 23)
+    sg = model.subgraphs[0]
+    rt = minirt.load_model(model)
+    x = np.random.default_rng(7).standard_normal((5, 320)).astype(np.float32)
+    rt.write(sg.inputs[0], x)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.invoke() == 0, rt.error
+    w4 = np.frombuffer(sg.tensors[1].data, np.uint8).reshape(200, 160)
+    scales = sg.tensors[3].array()
+    want = oracle.fc_blockwise4(x, w4, scales, 32, None)
+    np.testing.assert_allclose(rt.view(sg.outputs[0]).reshape(5, 200), want, rtol=1e-3, atol=1e-3 * np.abs(want).max())
+    rt.close()
