@@ -88,7 +88,9 @@ __device__ __forceinline__ void store_output(const FcParams& p, int m, int n, in
 
 
 template <int NB, int EPI>
-__global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams p, const int m_base) {
+__global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams p, const int m_base_first) {
+  // grid.y = passes of NB activation rows (whole-tile mode only: the stream-K scratch is per grid.x)
+  const int m_base = m_base_first + (int)blockIdx.y * NB;
   using L = UmmaLayout<NB>;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
@@ -622,13 +624,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
 // reduction; CTAs with one tile fewer finish early and the kernel stays HBM-bound); with fewer,
 // one SM per n tile cannot pull more than ~80 GB/s, so the flat (n tile, k tile) sequence is cut
 // into equal ranges over all SMs (stream-K) and the partials are merged by the last arriver.
-int plan_ctas(FcParams* p) {
+int plan_ctas(FcParams* p, int passes) {
   const int sms = device_sm_count();
   const long long total = (long long)p->n_tiles * p->k_tiles;
   int mode = -1;  // -1 auto, 0 stream-K, 1 whole tiles
   if (const char* e = getenv("B200_FC_SPLIT")) mode = atoi(e) ? 0 : 1;  // measurement knob
   int ctas;
-  if (mode == 1 || (mode < 0 && p->n_tiles * 2 >= sms)) {
+  // several passes of activation rows share one launch: no cross-CTA reduction then
+  if (mode == 1 || passes > 1 || p->force_whole_tiles || (mode < 0 && p->n_tiles * 2 >= sms)) {
     p->whole_tiles = 1;
     ctas = p->n_tiles < sms ? p->n_tiles : sms;
   } else {
@@ -648,7 +651,7 @@ int plan_ctas(FcParams* p) {
 }
 
 template <int NB, int EPI>
-cudaError_t launch_umma_one(const FcParams& p, int m_base, cudaStream_t s) {
+cudaError_t launch_umma_one(const FcParams& p, int m_base, int passes, cudaStream_t s) {
   using L = UmmaLayout<NB>;
   static bool configured[64] = {false};
   auto kernel = fc_umma_kernel<NB, EPI>;
@@ -661,25 +664,25 @@ cudaError_t launch_umma_one(const FcParams& p, int m_base, cudaStream_t s) {
     configured[dev] = true;
   }
   FcParams q = p;
-  const int ctas = plan_ctas(&q);
+  const int ctas = plan_ctas(&q, passes);
   size_t smem = (size_t)L::kSmemBytes;
   if (p.prologue) {
     if (!fc_prologue_supported(p.m, p.k) || NB != 16 || m_base != 0) return cudaErrorInvalidValue;
     smem += (size_t)p.k_tiles * L::kQBytes;
   }
-  return launch_chained(kernel, dim3(ctas), dim3(kUmmaThreads), smem, s, q, m_base);
+  return launch_chained(kernel, dim3(ctas, passes), dim3(kUmmaThreads), smem, s, q, m_base);
 }
 
 template <int EPI>
-cudaError_t launch_umma_nb(const FcParams& p_in, int m_base, int nb, cudaStream_t s) {
+cudaError_t launch_umma_nb(const FcParams& p_in, int m_base, int nb, int passes, cudaStream_t s) {
   FcParams p = p_in;
   if (const char* e = getenv("B200_FC_DEBUG")) p.debug_flags = atoi(e);
   switch (nb) {
-    case 16: return launch_umma_one<16, EPI>(p, m_base, s);
-    case 32: return launch_umma_one<32, EPI>(p, m_base, s);
-    case 64: return launch_umma_one<64, EPI>(p, m_base, s);
-    case 128: return launch_umma_one<128, EPI>(p, m_base, s);
-    default: return launch_umma_one<256, EPI>(p, m_base, s);
+    case 16: return launch_umma_one<16, EPI>(p, m_base, passes, s);
+    case 32: return launch_umma_one<32, EPI>(p, m_base, passes, s);
+    case 64: return launch_umma_one<64, EPI>(p, m_base, passes, s);
+    case 128: return launch_umma_one<128, EPI>(p, m_base, passes, s);
+    default: return launch_umma_one<256, EPI>(p, m_base, passes, s);
   }
 }
 
@@ -775,10 +778,36 @@ cudaError_t try_cluster_pass(const FcParams& p, int m_base, int nb, cudaStream_t
 }
 
 template <int EPI>
-cudaError_t launch_pass(const FcParams& p, int m_base, int nb, cudaStream_t s) {
-  const cudaError_t e = try_cluster_pass<EPI>(p, m_base, nb, s);
-  if (e != cudaErrorNotSupported) return e;
-  return launch_umma_nb<EPI>(p, m_base, nb, s);
+cudaError_t launch_all(const FcParams& p, cudaStream_t s) {
+  int nb = umma_rows_per_pass(p.m);
+  if (nb <= 64) {  // decode-sized: one pass, cluster split-K where the shape suits it
+    const cudaError_t e = try_cluster_pass<EPI>(p, 0, nb, s);
+    if (e != cudaErrorNotSupported) return e;
+    return launch_umma_nb<EPI>(p, 0, nb, 1, s);
+  }
+  const int sms = device_sm_count();
+  if (p.m <= 128 && p.n_tiles * 2 < sms && p.m_alloc % 64 == 0) {
+    // a little over one decode pass, few n tiles: 64 rows at a time through the cluster kernel
+    for (int m_base = 0; m_base < p.m; m_base += 64) {
+      const cudaError_t e = try_cluster_pass<EPI>(p, m_base, 64, s);
+      if (e == cudaErrorNotSupported && m_base == 0) break;
+      if (e != cudaSuccess) return e;
+      if (m_base + 64 >= p.m) return cudaSuccess;
+    }
+  }
+  // Prefill-sized: every (n tile range, pass of nb activation rows) is a CTA of one launch, whole n
+  // tiles per CTA (merging split-K partials of 128+ columns through memory costs more than it
+  // saves). 128 rows per pass when 256 would leave SMs idle (few n tiles).
+  if (nb == 256 && p.n_tiles * ((p.m + 255) / 256) < sms) nb = 128;
+  if (const char* e = getenv("B200_FC_NB")) {  // measurement knob
+    const int v = atoi(e);
+    if (v == 128 || v == 256) nb = v;
+  }
+  if (p.m_alloc % nb != 0) return cudaErrorInvalidValue;
+  const int passes = (p.m + nb - 1) / nb;
+  FcParams q = p;
+  q.force_whole_tiles = 1;
+  return launch_umma_nb<EPI>(q, 0, nb, passes, s);
 }
 
 }  // namespace
@@ -792,19 +821,9 @@ int umma_rows_per_pass(int m) {
 }
 
 cudaError_t launch_fc_i8_umma(const FcParams& p, FcEpilogue epi, cudaStream_t s) {
-  const int nb = umma_rows_per_pass(p.m);
-  for (int m_base = 0; m_base < p.m; m_base += nb) {
-    cudaError_t e;
-    if (epi == kEpiHybridF32) {
-      e = launch_pass<kEpiHybridF32>(p, m_base, nb, s);
-    } else if (epi == kEpiRequantI8) {
-      e = launch_pass<kEpiRequantI8>(p, m_base, nb, s);
-    } else {
-      e = launch_pass<kEpiRawI32>(p, m_base, nb, s);
-    }
-    if (e != cudaSuccess) return e;
-  }
-  return cudaSuccess;
+  if (epi == kEpiHybridF32) return launch_all<kEpiHybridF32>(p, s);
+  if (epi == kEpiRequantI8) return launch_all<kEpiRequantI8>(p, s);
+  return launch_all<kEpiRawI32>(p, s);
 }
 
 }  // namespace b200

@@ -86,6 +86,7 @@ struct FcParams {
   unsigned long long* trace;
   int max_ctas;              // 0 = chosen per shape
   int whole_tiles;           // set by the launcher: CTAs own whole n tiles (no split-K)
+  int force_whole_tiles;     // set by the launcher for prefill-sized passes
   int debug_flags;           // measurement only: 1 = skip the MMAs, 2 = skip the epilogue
 };
 
