@@ -163,9 +163,12 @@ __global__ void __launch_bounds__(kThreads, 1) fc_stream_kernel(const FcParams p
   }
   __syncthreads();
 
+  // whole n tiles per CTA (no cross-CTA reduction) or equal ranges of the flat (n tile, k tile) sequence
   const long long total = (long long)p.n_tiles * p.k_tiles;
-  const long long t_begin = total * blockIdx.x / gridDim.x;
-  const long long t_end = total * (blockIdx.x + 1) / gridDim.x;
+  const long long t_begin = p.whole_tiles ? ((long long)p.n_tiles * blockIdx.x / gridDim.x) * p.k_tiles
+                                          : total * blockIdx.x / gridDim.x;
+  const long long t_end = p.whole_tiles ? ((long long)p.n_tiles * (blockIdx.x + 1) / gridDim.x) * p.k_tiles
+                                        : total * (blockIdx.x + 1) / gridDim.x;
   const int m_groups_alloc = p.m_alloc / 8;
   const int mg_base = m_base / 8;
 
@@ -330,15 +333,21 @@ cudaError_t launch_one(const FcParams& p, int m_base, cudaStream_t s) {
     configured[dev] = true;
   }
   const long long total = (long long)p.n_tiles * p.k_tiles;
-  int ctas = p.max_ctas > 0 ? p.max_ctas : device_sm_count();
+  const int sms = device_sm_count();
+  int ctas = p.max_ctas > 0 ? p.max_ctas : sms;
   if (const char* e = getenv("B200_FC_MAX_CTAS")) {  // tuning knob
     const int v = atoi(e);
     if (v > 0) ctas = v;
   }
+  FcParams q = p;
+  // with at least half as many n tiles as SMs, whole tiles per CTA: nothing to merge across CTAs
+  q.whole_tiles = (p.n_tiles * 2 >= sms && p.max_ctas <= 0 && !getenv("B200_FC_MAX_CTAS")) ? 1 : 0;
+  if (const char* e = getenv("B200_FC_SPLIT")) q.whole_tiles = atoi(e) ? 0 : 1;  // measurement knob
+  if (q.whole_tiles && ctas > p.n_tiles) ctas = p.n_tiles;
   if (ctas > kAccSlots) ctas = kAccSlots;
   if (ctas > total) ctas = (int)total;
   if (ctas < 1) ctas = 1;
-  kernel<<<ctas, kThreads, L::kSmemBytes, s>>>(p, m_base);
+  kernel<<<ctas, kThreads, L::kSmemBytes, s>>>(q, m_base);
   return cudaGetLastError();
 }
 

@@ -619,6 +619,213 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
   }
 }
 
+// ---- prefill-sized variant: two n tiles per activation tile ---------------------------------------
+// With 256 activation rows per pass a CTA's traffic is dominated by the activation operand (32 KB
+// per k tile against a 16 KB weight tile), and every CTA re-reads it from L2. Here one stage holds
+// TWO weight tiles (consecutive n tiles, same k tile) and the activation tile once: 64 KB per stage
+// for twice the MMAs, a third less traffic per MAC. The two accumulators (128 x 256 int32 each)
+// fill all 512 TMEM columns, so a CTA's next unit waits for the epilogue of the previous one.
+// Work units = (pair of n tiles, pass of 256 rows), whole units per CTA, no cross-CTA reduction.
+struct PrefillLayout {
+  static constexpr int kNB = 256;
+  static constexpr int kQBytes = kNB * kTileK8;                  // 32 KiB
+  static constexpr int kStageBytes = 2 * kTileBytes + kQBytes;   // 64 KiB
+  static constexpr int kStages = 3;
+  static constexpr int kBarriers = 2 * kStages + 2;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarriers * 8 + (int)sizeof(UmmaShared) + 16;
+  static constexpr int kTmemCols = 512;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcParams p, const int pairs, const int passes) {
+  using L = PrefillLayout;
+  constexpr int NB = L::kNB;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
+  uint64_t* empty_bar = full_bar + L::kStages;
+  uint64_t* acc_full = empty_bar + L::kStages;
+  uint64_t* acc_empty = acc_full + 1;
+  UmmaShared* sh = reinterpret_cast<UmmaShared*>(acc_empty + 1);
+  volatile int* abort_flag = &sh->abort_flag;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 4);  // one arrival per epilogue warp
+    sh->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&sh->tmem_base, L::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+  const int units = pairs * passes;
+  const int m_groups_alloc = p.m_alloc / 8;
+  // unit u -> pass (slow index) and pair (fast): neighbouring CTAs share the activation rows
+
+  if (warp == 0) {
+    if (lane == 0) {
+      pdl_launch_dependents();
+      const uint64_t stream_policy = l2_policy_evict_first();
+      pdl_wait();
+      uint32_t it = 0;
+      for (int u = blockIdx.x; u < units; u += gridDim.x) {
+        const int pass = u / pairs, pair = u % pairs;
+        const int nt0 = pair * 2;
+        const int tiles = nt0 + 1 < p.n_tiles ? 2 : 1;
+        const int mg_base = pass * (NB / 8);
+        for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
+          const int s = it % L::kStages;
+          const uint32_t ph = (it / L::kStages) & 1u;
+          mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, p.status, kStatusWaitTimeoutEmpty);
+          uint8_t* dst = smem + (size_t)s * L::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(tiles * kTileBytes + L::kQBytes));
+          for (int j = 0; j < tiles; ++j)
+            bulk_g2s_hint(dst + j * kTileBytes, p.w_packed + ((size_t)(nt0 + j) * p.k_tiles + kt) * kTileBytes, kTileBytes,
+                          &full_bar[s], stream_policy);
+          const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
+          bulk_g2s(dst + 2 * kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[s]);
+        }
+      }
+      const uint32_t issued = it;  // never leave with copies in flight (only possible after an abort)
+      for (uint32_t back = 0; back < (uint32_t)L::kStages && back < issued; ++back) {
+        const uint32_t j = issued - 1 - back;
+        mbar_wait_bounded(&full_bar[j % L::kStages], (j / L::kStages) & 1u, abort_flag, p.status, kStatusWaitTimeoutFull);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_s8(NB);
+      uint32_t it = 0, done = 0;
+      for (int u = blockIdx.x; u < units; u += gridDim.x, ++done) {
+        const int pair = u % pairs;
+        const int tiles = pair * 2 + 1 < p.n_tiles ? 2 : 1;
+        // both accumulators are free once the epilogue has drained the previous unit
+        mbar_wait_bounded(acc_empty, (done & 1u) ^ 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
+        tc_fence_after();
+        for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
+          const int s = it % L::kStages;
+          const uint32_t ph = (it / L::kStages) & 1u;
+          mbar_wait_bounded(&full_bar[s], ph, abort_flag, p.status, kStatusWaitTimeoutFull);
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * L::kStageBytes);
+          const uint32_t b_addr = a_addr + 2 * kTileBytes;
+          for (int j = 0; j < tiles; ++j) {
+#pragma unroll
+            for (int ks = 0; ks < kTileK8 / 32; ++ks) {
+              const uint64_t a_desc = umma_smem_desc(a_addr + j * kTileBytes + ks * 256, 128, 1024);
+              const uint64_t b_desc = umma_smem_desc(b_addr + ks * 256, 128, 1024);
+              umma_s8(tmem_base + j * NB, a_desc, b_desc, idesc, (kt == 0 && ks == 0) ? 0u : 1u);
+            }
+          }
+          umma_commit(&empty_bar[s]);
+        }
+        umma_commit(acc_full);
+      }
+      if (done > 0) mbar_wait_bounded(acc_full, (done - 1) & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int etid = tid - 64;
+    pdl_wait();
+    uint32_t done = 0;
+    int staged_pass = -1;
+    for (int u = blockIdx.x; u < units; u += gridDim.x, ++done) {
+      const int pass = u / pairs, pair = u % pairs;
+      const int tiles = pair * 2 + 1 < p.n_tiles ? 2 : 1;
+      const int m_base = pass * NB;
+      const int m_valid = p.m - m_base < NB ? p.m - m_base : NB;
+      if (pass != staged_pass) {  // per-row scale and zero point (or row sum) of this pass
+        named_barrier(1, kEpiThreads);
+        for (int i = etid; i < NB; i += kEpiThreads) {
+          const int m = m_base + i;
+          const bool ok = m < p.m;
+          sh->in_scale[i] = (ok && p.in_scales) ? p.in_scales[m] : 0.0f;
+          if constexpr (EPI == kEpiHybridF32) {
+            sh->in_aux[i] = (ok && p.in_zps) ? p.in_zps[m] : 0;
+          } else {
+            sh->in_aux[i] = (ok && p.x_sums) ? p.x_sums[m] : 0;
+          }
+        }
+        named_barrier(1, kEpiThreads);
+        staged_pass = pass;
+      }
+      int32_t rs[2] = {0, 0}, base_i[2] = {0, 0}, mult[2] = {0, 0}, shift[2] = {0, 0};
+      float wsc[2] = {0.0f, 0.0f}, bias_f[2] = {0.0f, 0.0f};
+      for (int j = 0; j < tiles; ++j) {
+        const int n = (pair * 2 + j) * kTileN + row_in_tile;
+        if (n >= p.n) continue;
+        rs[j] = p.row_sums ? p.row_sums[n] : 0;
+        if constexpr (EPI == kEpiHybridF32) {
+          wsc[j] = p.per_channel ? p.w_scales[n] : p.w_scales[0];
+          bias_f[j] = p.bias_f32 ? p.bias_f32[n] : 0.0f;
+        } else {
+          base_i[j] = p.input_offset * rs[j] + p.k * p.filter_offset * p.input_offset + (p.bias_i32 ? p.bias_i32[n] : 0);
+          if (p.multipliers) {
+            mult[j] = p.multipliers[p.per_channel ? n : 0];
+            shift[j] = p.shifts[p.per_channel ? n : 0];
+          }
+        }
+      }
+      mbar_wait_bounded(acc_full, done & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
+      tc_fence_after();
+      for (int j = 0; j < tiles; ++j) {
+        const int n = (pair * 2 + j) * kTileN + row_in_tile;
+        const uint32_t taddr = tmem_base + j * NB + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+        for (int c = 0; c < NB / 16; ++c) {
+          if (c * 16 >= m_valid) break;
+          int r[16];
+          tmem_ld16(taddr + c * 16, r);
+          tmem_ld_wait();
+          if (n < p.n) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const int m = c * 16 + e;
+              if (m < m_valid)
+                store_output<EPI>(p, m_base + m, n, r[e], rs[j], wsc[j], bias_f[j], base_i[j], mult[j], shift[j],
+                                  sh->in_scale[m], sh->in_aux[m]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, L::kTmemCols);
+}
+
+template <int EPI>
+cudaError_t launch_prefill(const FcParams& p, cudaStream_t s) {
+  using L = PrefillLayout;
+  static bool configured[64] = {false};
+  auto kernel = fc_prefill_kernel<EPI>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const int pairs = (p.n_tiles + 1) / 2;
+  const int passes = (p.m + L::kNB - 1) / L::kNB;
+  const int sms = device_sm_count();
+  const int units = pairs * passes;
+  const int ctas = units < sms ? units : sms;
+  return launch_chained(kernel, dim3(ctas), dim3(kUmmaThreads), (size_t)L::kSmemBytes, s, p, pairs, passes);
+}
+
 // Chooses the number of CTAs and the split for one launch (measured on B200, batch 1, graph
 // replays): with at least half as many n tiles as SMs, whole n tiles per CTA win (no cross-CTA
 // reduction; CTAs with one tile fewer finish early and the kernel stays HBM-bound); with fewer,
@@ -804,6 +1011,8 @@ cudaError_t launch_all(const FcParams& p, cudaStream_t s) {
     if (v == 128 || v == 256) nb = v;
   }
   if (p.m_alloc % nb != 0) return cudaErrorInvalidValue;
+  const char* dual_env = getenv("B200_FC_DUAL");  // 1: two n tiles per stage (fc_prefill_kernel)
+  if (nb == 256 && p.n_tiles >= 2 && dual_env && dual_env[0] == '1') return launch_prefill<EPI>(p, s);
   const int passes = (p.m + nb - 1) / nb;
   FcParams q = p;
   q.force_whole_tiles = 1;
