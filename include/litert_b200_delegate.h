@@ -41,6 +41,14 @@ __attribute__((visibility("default"))) struct TfLiteDelegate* tflite_plugin_crea
 /* NULL is allowed (external_delegate_interface.h:70-73). */
 __attribute__((visibility("default"))) void tflite_plugin_destroy_delegate(struct TfLiteDelegate* delegate);
 
+/* A second library, libLiteRtGpuAccelerator.so (litert_b200/csrc/delegate/litert_accelerator.cc),
+ * exports the DATA symbol
+ *     extern "C" const LiteRtAcceleratorDef LiteRtAcceleratorImpl;
+ * (litert/c/internal/litert_accelerator_def.h:40-66), which the LiteRT environment looks up with dlsym()
+ * (litert/runtime/accelerators/gpu_registry.cc:121-134). Its create_delegate calls
+ * tflite_plugin_create_delegate above and wraps the result with LiteRtRuntimeContext::wrap_delegate.
+ * It is not declared here because its type lives in the LiteRT headers. */
+
 /* Number of graph nodes the last Prepare claimed (what
  * SingleOpModel::CountOpsExecutedByCpuKernel, tflite/kernels/test_util.cc:697-703,
  * lets tests assert from the other side); -1 for NULL. */

@@ -66,6 +66,9 @@ def build_all(force=False, verbose=False):
         p = build_delegate.build(force)
         if p:
             paths.append(p)
+        a = build_delegate.build_accelerator(force)
+        if a:
+            paths.append(a)
     return paths
 
 

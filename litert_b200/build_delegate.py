@@ -13,6 +13,39 @@ LIB = os.path.join(HERE, "lib")
 LITERT_ROOT = os.environ.get("LITERT_ROOT", "/root/reference")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 OUT = os.path.join(LIB, "libtflite_b200_delegate.so")
+# the LiteRT accelerator definition, under the file name the LiteRT environment loads
+ACCELERATOR = os.path.join(LIB, "libLiteRtGpuAccelerator.so")
+GEN = os.path.join(LIB, "gen")
+
+
+def generated_include_dir():
+    """litert/build_common/build_config.h is a generated header in the reference build (from
+    build_config.h.in, two 0/1 switches): produce it the same way, with GPU and NPU enabled."""
+    src = os.path.join(LITERT_ROOT, "litert", "build_common", "build_config.h.in")
+    dst = os.path.join(GEN, "litert", "build_common", "build_config.h")
+    if os.path.exists(src) and (not os.path.exists(dst) or os.path.getmtime(dst) < os.path.getmtime(src)):
+        os.makedirs(os.path.dirname(dst), exist_ok=True)
+        text = open(src).read()
+        for name in ("LITERT_BUILD_CONFIG_DISABLE_GPU", "LITERT_BUILD_CONFIG_DISABLE_NPU"):
+            text = text.replace(f"#cmakedefine01 {name}", f"#define {name} 0")
+        with open(dst, "w") as out:
+            out.write(text)
+    return GEN
+
+
+def build_accelerator(force=False):
+    """libLiteRtGpuAccelerator.so exporting LiteRtAcceleratorImpl; needs the LiteRT headers."""
+    header = os.path.join(LITERT_ROOT, "litert", "c", "internal", "litert_accelerator_def.h")
+    if not os.path.exists(header):
+        return ACCELERATOR if os.path.exists(ACCELERATOR) else None
+    delegate = build(force)
+    src = os.path.join(CSRC, "litert_accelerator.cc")
+    if not force and not _newer(ACCELERATOR, [src, delegate]):
+        return ACCELERATOR
+    subprocess.check_call(["g++", "-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-shared", "-o", ACCELERATOR, src,
+                           "-I" + generated_include_dir(), "-I" + LITERT_ROOT, "-L" + LIB, "-ltflite_b200_delegate",
+                           "-Wl,-rpath,$ORIGIN"])
+    return ACCELERATOR
 
 
 def _newer(target, deps):

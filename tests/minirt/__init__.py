@@ -23,6 +23,8 @@ OP_ADD, OP_FULLY_CONNECTED, OP_SOFTMAX = 0, 9, 25
 
 
 def build():
+    from litert_b200 import build_delegate
+
     src = os.path.join(HERE, "minirt.cc")
     have = os.path.exists(os.path.join(LITERT_ROOT, "tflite", "core", "c", "common.h"))
     if not have:
@@ -33,7 +35,8 @@ def build():
         return LIB
     subprocess.check_call(["g++", "-O1", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-shared", "-o", LIB, src,
                            os.path.join(LITERT_ROOT, "tflite", "core", "c", "common.cc"),
-                           os.path.join(LITERT_ROOT, "tflite", "array.cc"), "-I" + LITERT_ROOT])
+                           os.path.join(LITERT_ROOT, "tflite", "array.cc"), "-I" + LITERT_ROOT,
+                           "-I" + build_delegate.generated_include_dir(), "-ldl"])
     return LIB
 
 
@@ -70,6 +73,36 @@ class Delegate:
         if self.ptr:
             self.lib.tflite_plugin_destroy_delegate(self.ptr)
             self.ptr = None
+
+
+class Accelerator:
+    """The LiteRT accelerator library loaded the way the LiteRT environment loads it; `.ptr` is the
+    TfLiteDelegate it created (usable with MiniRuntime.apply)."""
+
+    def __init__(self, path=None):
+        from litert_b200 import build_delegate
+
+        path = path or build_delegate.build_accelerator()
+        self.lib = ctypes.CDLL(build())
+        name = ctypes.create_string_buffer(64)
+        version = (ctypes.c_int * 3)()
+        hw, size = ctypes.c_int(), ctypes.c_int()
+        wrapped, delegate = ctypes.c_void_p(), ctypes.c_void_p()
+        self.lib.mrt_accelerator_probe.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int,
+                                                   ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                                   ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_void_p),
+                                                   ctypes.POINTER(ctypes.c_void_p)]
+        self.lib.mrt_accelerator_release.argtypes = [ctypes.c_void_p]
+        self.rc = self.lib.mrt_accelerator_probe(path.encode(), name, 64, version, ctypes.byref(hw), ctypes.byref(size),
+                                                 ctypes.byref(wrapped), ctypes.byref(delegate))
+        self.name, self.version, self.hardware, self.struct_size = name.value.decode(), tuple(version), hw.value, size.value
+        self._wrapped = wrapped
+        self.ptr = delegate.value
+
+    def close(self):
+        if self._wrapped:
+            self.lib.mrt_accelerator_release(self._wrapped)
+            self._wrapped = None
 
 
 class MiniRuntime:

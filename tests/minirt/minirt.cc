@@ -19,6 +19,9 @@
 #include <string>
 #include <vector>
 
+#include <dlfcn.h>
+
+#include "litert/c/internal/litert_accelerator_def.h"
 #include "tflite/builtin_ops.h"
 #include "tflite/core/c/builtin_op_data.h"
 #include "tflite/core/c/common.h"
@@ -465,6 +468,68 @@ MRT_API int mrt_num_cpu_nodes_in_plan(void* h) {
   int c = 0;
   for (int n : g->plan) c += g->nodes[n]->is_delegate ? 0 : 1;
   return c;
+}
+
+// ---- LiteRT accelerator probe ------------------------------------------------------------------
+// What the LiteRT environment does with libLiteRtGpuAccelerator.so
+// (litert/runtime/accelerators/registration_helper.cc:111-126): dlopen, look the data symbol
+// LiteRtAcceleratorImpl up, check its ABI header, ask it for a delegate through a runtime context.
+// Only wrap_delegate of the context is live here: it records the delegate and its deleter.
+struct WrappedDelegate {
+  TfLiteOpaqueDelegate* delegate;
+  void (*deleter)(TfLiteOpaqueDelegate*);
+};
+static LiteRtStatus FakeWrapDelegate(TfLiteOpaqueDelegate* delegate, void (*deleter)(TfLiteOpaqueDelegate*),
+                                     LiteRtDelegateWrapper* wrapper) {
+  auto* w = new WrappedDelegate{delegate, deleter};
+  *wrapper = reinterpret_cast<LiteRtDelegateWrapper>(w);
+  return kLiteRtStatusOk;
+}
+
+// Returns 0 and fills the outputs, or a negative step number that failed.
+MRT_API int mrt_accelerator_probe(const char* path, char* name_out, int name_cap, int* version3, int* hw_set,
+                                  int* struct_size, void** wrapped_out, TfLiteDelegate** delegate_out) {
+  void* lib = dlopen(path, RTLD_NOW | RTLD_LOCAL);
+  if (!lib) return -1;
+  auto* def = static_cast<const LiteRtAcceleratorDef*>(dlsym(lib, "LiteRtAcceleratorImpl"));
+  if (!def) return -2;
+  *struct_size = def->abi_header.struct_size;
+  if (def->abi_header.struct_size != sizeof(LiteRtAcceleratorDefV1) ||
+      def->abi_header.major_version != LITERT_ACCELERATOR_DEF_CURRENT_VERSION)
+    return -3;
+  const char* name = nullptr;
+  if (!def->get_name || def->get_name(nullptr, &name) != kLiteRtStatusOk || !name) return -4;
+  snprintf(name_out, name_cap, "%s", name);
+  LiteRtApiVersion v;
+  if (!def->get_version || def->get_version(nullptr, &v) != kLiteRtStatusOk) return -5;
+  version3[0] = v.major, version3[1] = v.minor, version3[2] = v.patch;
+  LiteRtHwAcceleratorSet hw = 0;
+  if (!def->get_hardware_support || def->get_hardware_support(nullptr, &hw) != kLiteRtStatusOk) return -6;
+  *hw_set = hw;
+  bool jit = false;
+  if (!def->is_tflite_delegate_responsible_for_jit_compilation ||
+      def->is_tflite_delegate_responsible_for_jit_compilation(nullptr, &jit) != kLiteRtStatusOk)
+    return -7;
+  if (def->get_name(nullptr, nullptr) == kLiteRtStatusOk) return -8;  // null output must be refused
+  LiteRtRuntimeContext ctx;
+  memset(&ctx, 0, sizeof(ctx));
+  ctx.abi_header.struct_size = sizeof(ctx);
+  ctx.wrap_delegate = FakeWrapDelegate;
+  LiteRtDelegateWrapper wrapper = nullptr;
+  if (!def->create_delegate || def->create_delegate(&ctx, nullptr, nullptr, nullptr, &wrapper) != kLiteRtStatusOk ||
+      !wrapper)
+    return -9;
+  auto* w = reinterpret_cast<WrappedDelegate*>(wrapper);
+  *wrapped_out = w;
+  *delegate_out = reinterpret_cast<TfLiteDelegate*>(w->delegate);
+  return 0;
+}
+
+MRT_API void mrt_accelerator_release(void* wrapped) {
+  auto* w = static_cast<WrappedDelegate*>(wrapped);
+  if (!w) return;
+  if (w->deleter) w->deleter(w->delegate);
+  delete w;
 }
 
 }  // extern "C"

@@ -199,3 +199,37 @@ def test_flex_map_reader_through_the_predicate(plugin_path):
     assert blob[-1] == 4 and blob[-2] >> 2 == 9
     assert b"logit_cap\0" in blob and b"scale\0" in blob
     assert blob.index(b"logit_cap") < blob.index(b"scale")  # keys sorted
+
+
+def test_litert_accelerator_definition(plugin_path):
+    """libLiteRtGpuAccelerator.so as the LiteRT environment sees it: the LiteRtAcceleratorImpl table
+    (litert/c/internal/litert_accelerator_def.h:40-66), its ABI header, and a delegate out of
+    create_delegate through the runtime context's wrap_delegate."""
+    import subprocess
+
+    from litert_b200 import build_delegate
+
+    path = build_delegate.build_accelerator()
+    if path is None:
+        pytest.skip("accelerator library not built and LiteRT headers absent")
+    exported = subprocess.run(["nm", "-D", "--defined-only", path], capture_output=True, text=True).stdout
+    names = {line.split()[-1] for line in exported.splitlines() if line.strip()}
+    assert "LiteRtAcceleratorImpl" in names
+    acc = minirt.Accelerator(path)
+    assert acc.rc == 0
+    assert acc.name == "B200" and acc.version == (1, 0, 0)
+    assert acc.hardware == 2          # kLiteRtHwAcceleratorGpu
+    assert acc.struct_size == 200     # sizeof(LiteRtAcceleratorDefV1), asserted by the reference header too
+    assert acc.ptr
+    # the delegate it hands out is the plugin's: it partitions like the external delegate does
+    m = minirt.MiniRuntime()
+    w = m.tensor(minirt.I8, (4, 32), np.ones((4, 32), np.int8), channel_scales=np.full(4, 0.01, np.float32))
+    x = m.tensor(minirt.F32, (2, 32))
+    y = m.tensor(minirt.F32, (2, 4))
+    m.fully_connected(x, w, None, y)
+    m.set_io([x], [y])
+    m.apply(acc)   # without a CUDA device: claimed in Prepare, kernel init fails, the plan is restored
+    assert m.cpu_nodes + m.partitions >= 1
+    m.close()
+    acc.close()
+

@@ -336,3 +336,26 @@ def test_blockwise_int4_fc_from_tflite_file(delegate, oracle):
     want = oracle.fc_blockwise4(x, w4, scales, 32, None)
     np.testing.assert_allclose(rt.view(sg.outputs[0]).reshape(5, 200), want, rtol=1e-3, atol=1e-3 * np.abs(want).max())
     rt.close()
+
+
+def test_hybrid_fc_through_the_litert_accelerator(rt, oracle):
+    """The same delegate reached the LiteRT way: LiteRtAcceleratorImpl.create_delegate."""
+    acc = minirt.Accelerator()
+    assert acc.rc == 0 and acc.ptr
+    rng = np.random.default_rng(31)
+    wq = rng.integers(-127, 128, (48, 96)).astype(np.int8)
+    scales = rng.uniform(1e-3, 1e-2, 48).astype(np.float32)
+    xin = rng.standard_normal((3, 96)).astype(np.float32)
+    w = rt.tensor(I8, wq.shape, wq, channel_scales=scales)
+    x = rt.tensor(F32, xin.shape)
+    y = rt.tensor(F32, (3, 48))
+    rt.fully_connected(x, w, None, y, asymmetric=True)
+    rt.set_io([x], [y])
+    rt.write(x, xin)
+    assert rt.apply(acc) == 0, rt.error
+    assert rt.partitions == 1 and rt.cpu_nodes == 0
+    assert rt.invoke() == 0, rt.error
+    assert np.array_equal(rt.view(y), oracle.fc_hybrid(xin, wq, scales, None, True, oracle.ACT_NONE))
+    rt.close()
+    acc.close()
+
