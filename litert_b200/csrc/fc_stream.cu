@@ -10,8 +10,8 @@
 //  * one producer lane keeps a ring of stages filled with linear bulk copies
 //    (16 KiB weight tile + the matching activation tile) signalled through
 //    mbarriers; eight consumer warps read MMA fragments from shared memory
-//    with conflict-free 32-bit loads (each core matrix is 128 contiguous
-//    bytes, lane l reads word l) and issue m16n8k32 int8 MMAs, weights as
+//    with conflict-free 32-bit loads (thread (g, t) reads word t of chunk c
+//    of row g at swizzled chunk position c ^ g) and issue m16n8k32 int8 MMAs, weights as
 //    the 16-row operand, activation rows as the 8 columns;
 //  * a CTA that owns only part of an n tile's reduction adds its int32
 //    partials into a global accumulator with coalesced reductions and bumps a
@@ -216,19 +216,23 @@ __global__ void __launch_bounds__(kThreads, 1) fc_stream_kernel(const FcParams p
     const uint8_t* sw = smem + (size_t)s * L::kStageBytes;
     const uint8_t* sq = sw + L::kWBytes;
     if constexpr (!W4) {
-      // weight rows 16*warp .. +15 = row groups 2*warp, 2*warp+1
-      const uint32_t* wa = reinterpret_cast<const uint32_t*>(sw + (size_t)(2 * warp) * kChunks8 * 128) + lane;
-      const uint32_t* qa = reinterpret_cast<const uint32_t*>(sq) + lane;
+      // weight rows 16*warp .. +15 = row groups 2*warp, 2*warp+1; thread (g, t) reads word t of the
+      // 16-byte chunk `c` of row g, which the swizzled layout keeps at chunk position c ^ g
+      const int g = lane >> 2, t4 = lane & 3;
+      const uint32_t* wg0 = reinterpret_cast<const uint32_t*>(sw + (size_t)(2 * warp) * 1024) + g * 32 + t4;
+      const uint32_t* wg1 = wg0 + 256;
+      const uint32_t* qg = reinterpret_cast<const uint32_t*>(sq) + g * 32 + t4;
 #pragma unroll
       for (int ks = 0; ks < kTileK8 / 32; ++ks) {
-        const uint32_t a0 = wa[(2 * ks) * 32];
-        const uint32_t a1 = wa[(kChunks8 + 2 * ks) * 32];
-        const uint32_t a2 = wa[(2 * ks + 1) * 32];
-        const uint32_t a3 = wa[(kChunks8 + 2 * ks + 1) * 32];
+        const int c0 = ((2 * ks) ^ g) * 4, c1 = ((2 * ks + 1) ^ g) * 4;
+        const uint32_t a0 = wg0[c0];
+        const uint32_t a1 = wg1[c0];
+        const uint32_t a2 = wg0[c1];
+        const uint32_t a3 = wg1[c1];
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
-          const uint32_t b0 = qa[(j * kChunks8 + 2 * ks) * 32];
-          const uint32_t b1 = qa[(j * kChunks8 + 2 * ks + 1) * 32];
+          const uint32_t b0 = qg[j * 256 + c0];
+          const uint32_t b1 = qg[j * 256 + c1];
           mma_s8(reinterpret_cast<int(&)[4]>(acc[j]), a0, a1, a2, a3, b0, b1);
         }
       }
@@ -245,13 +249,14 @@ __global__ void __launch_bounds__(kThreads, 1) fc_stream_kernel(const FcParams p
         const float s0 = __half2float(sc[blk * kTileN + warp * 16 + g]);
         const float s1 = __half2float(sc[blk * kTileN + warp * 16 + g + 8]);
         // activation tile h = blk / 4 (128 k each), chunks 2*(blk%4), +1
-        const uint32_t* qa = reinterpret_cast<const uint32_t*>(sq + (blk >> 2) * MT * 1024) + lane;
+        const uint32_t* qa = reinterpret_cast<const uint32_t*>(sq + (blk >> 2) * MT * 1024) + g * 32 + (lane & 3);
         const int kc = 2 * (blk & 3);
+        const int c0 = (kc ^ g) * 4, c1 = ((kc + 1) ^ g) * 4;  // swizzled chunk positions of row g
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
           int d[4] = {0, 0, 0, 0};
-          const uint32_t b0 = qa[(j * kChunks8 + kc) * 32];
-          const uint32_t b1 = qa[(j * kChunks8 + kc + 1) * 32];
+          const uint32_t b0 = qa[j * 256 + c0];
+          const uint32_t b1 = qa[j * 256 + c1];
           mma_s8(d, a0, a1, a2, a3, b0, b1);
           // operands carry 16x the 4-bit value; the shift is exact
           acc[j][0] = __fadd_rn(acc[j][0], __fmul_rn((float)(d[0] >> 4), s0));

@@ -53,14 +53,39 @@ template <int NB>
 struct UmmaLayout {
   static constexpr int kQBytes = NB * kTileK8;  // NB/8 row groups x 1 KiB
   static constexpr int kStageBytes = kTileBytes + kQBytes;
-  static constexpr int kStagesRaw = 200 * 1024 / kStageBytes;
+  static constexpr int kStagesRaw = (NB >= 64 ? 206 : 200) * 1024 / kStageBytes;
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
   static constexpr int kBarriers = 2 * kStages + 5;
   // without the fused prologue's operand buffer, which the launcher adds (k tiles x kQBytes)
-  static constexpr int kSmemBytes =
-      kStages * kStageBytes + kBarriers * 8 + (int)sizeof(UmmaShared) + 2 * (int)sizeof(PrologueShared) + 128 + 16;
+  static constexpr int kOutStageBytes = NB >= 64 ? 2 * 16 * kTileN * 4 : 0;  // two 16-row output blocks
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarriers * 8 + (int)sizeof(UmmaShared) +
+                                    2 * (int)sizeof(PrologueShared) + 1024 + 16 + kOutStageBytes + 16;
   static constexpr int kTmemCols = 2 * NB < 32 ? 32 : 2 * NB;
 };
+
+// Value of one output element from its exact int32 dot product: the float's bits (hybrid), the
+// int32 (raw) or the requantized int8 (sign-extended).
+template <int EPI>
+__device__ __forceinline__ int32_t compute_output(const FcParams& p, int32_t total, int32_t rs, float ws, float bias_f,
+                                                  int32_t base_i, int32_t mult, int32_t shift, float in_scale,
+                                                  int32_t in_aux) {
+  if constexpr (EPI == kEpiHybridF32) {
+    const int32_t dot = total - rs * in_aux;  // in_aux: the row's zero point
+    // reference order: scale = in_scale * w_scale; out = bias + dot * scale (no fused multiply-add)
+    const float scale = __fmul_rn(in_scale, ws);
+    float out = __fadd_rn(bias_f, __fmul_rn((float)dot, scale));
+    out = apply_activation(out, p.activation);
+    return __float_as_int(out);
+  } else {
+    const int32_t t = total + base_i + p.filter_offset * in_aux;  // in_aux: the row's sum
+    if constexpr (EPI == kEpiRawI32) {
+      return t;
+    } else {
+      int32_t v = requantize_mbqm(t, mult, shift) + p.output_offset;
+      return max(p.act_min, min(p.act_max, v));
+    }
+  }
+}
 
 // Epilogue for one output element; `total` is the exact int32 dot product.
 template <int EPI>
@@ -100,7 +125,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
   uint64_t* b_ready = acc_empty + 2;            // fused prologue: the operand rows are in place
   UmmaShared* sh = reinterpret_cast<UmmaShared*>(b_ready + 1);
   PrologueShared* ps = reinterpret_cast<PrologueShared*>(sh + 1);
-  uint8_t* bbuf = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ps + 2) + 127) & ~uintptr_t(127));
+  uint8_t* bbuf = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ps + 2) + 1023) & ~uintptr_t(1023));
+  // output staging of the many-row epilogue (never together with the fused prologue's operand buffer)
+  uint8_t* out_stage = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ps + 2) + 15) & ~uintptr_t(15));
   volatile int* abort_flag = &sh->abort_flag;
 
   const int tid = threadIdx.x;
@@ -210,9 +237,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
               p.prologue ? smem_u32(bbuf) + (uint32_t)(t % p.k_tiles) * (uint32_t)L::kQBytes : a_addr + kTileBytes;
 #pragma unroll
           for (int ks = 0; ks < kTileK8 / 32; ++ks) {
-            // two 16-byte K chunks per MMA: 128 B apart; 8-row groups 1 KiB apart
-            const uint64_t a_desc = umma_smem_desc(a_addr + ks * 256, 128, 1024);
-            const uint64_t b_desc = umma_smem_desc(b_addr + ks * 256, 128, 1024);
+            // 32 reduction bytes per MMA: 32 B further along the swizzled rows; 8-row groups 1 KiB apart
+            const uint64_t a_desc = umma_smem_desc(a_addr + ks * 32);
+            const uint64_t b_desc = umma_smem_desc(b_addr + ks * 32);
             if (!(p.debug_flags & 1)) umma_s8(d_tmem, a_desc, b_desc, idesc, (first && ks == 0) ? 0u : 1u);
           }
           first = false;
@@ -299,15 +326,62 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         for (int c = 0; c < NB / 16; ++c) {
           if (c * 16 >= m_valid) break;
           int r[16];
-          tmem_ld16(taddr + c * 16, r);
-          tmem_ld_wait();
-          if (row_ok) {
+          if (!(p.debug_flags & 8)) {
+            tmem_ld16(taddr + c * 16, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = c + j;
+          }
+          if constexpr (NB >= 64) {
+            // Many activation rows: a thread storing its own output channel writes 4 bytes (1 for int8)
+            // per row and a warp 128 (32) bytes per store instruction, 57 KB apart from the next; at
+            // 256 rows that costs more than the MMAs. The 16 x 128 block goes through shared memory
+            // instead and leaves as whole 512-byte (128-byte) row segments, 16 bytes per thread.
+            if (!(p.debug_flags & 4)) {
+              constexpr int kElem = EPI == kEpiRequantI8 ? 1 : 4;
+              uint8_t* st = out_stage + (c & 1) * (16 * kTileN * 4);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int m = c * 16 + j;
+                const int32_t v = compute_output<EPI>(p, r[j], rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[m], sh->in_aux[m]);
+                if constexpr (kElem == 4) {
+                  reinterpret_cast<int32_t*>(st)[j * kTileN + row_in_tile] = v;
+                } else {
+                  reinterpret_cast<int8_t*>(st)[j * kTileN + row_in_tile] = (int8_t)v;
+                }
+              }
+              named_barrier(2, kEpiThreads);  // the block is complete (and the other buffer's readers are done)
+              const int n0 = (int)nt * kTileN;
+              constexpr int kChunksPerRow = kTileN * kElem / 16;        // 16-byte pieces per output row segment
+              constexpr int kPieces = 16 * kChunksPerRow;
+              const bool vec_ok = (((size_t)p.n * kElem) % 16 == 0) && (n0 + kTileN <= p.n) &&
+                                  ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
+              for (int idx = etid; idx < kPieces; idx += kEpiThreads) {
+                const int rr = idx / kChunksPerRow, cc = idx % kChunksPerRow;
+                const int m = c * 16 + rr;
+                if (m >= m_valid) continue;
+                size_t off = ((size_t)(m_base + m) * p.n + n0) * kElem + cc * 16;
+                if (p.debug_flags & 16) off &= (1u << 20) - 16;  // measurement: every store lands in one MiB
+                uint8_t* dst = static_cast<uint8_t*>(p.y) + off;
+                const uint8_t* src = st + (size_t)rr * kTileN * kElem + cc * 16;
+                if (vec_ok) {
+                  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+                } else {
+                  for (int b = 0; b < 16; ++b)
+                    if (n0 + (cc * 16 + b) / kElem < p.n) dst[b] = src[b];
+                }
+              }
+            }
+          } else if (row_ok && !(p.debug_flags & 4)) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int m = c * 16 + j;
               if (m < m_valid)
                 store_output<EPI>(p, m_base + m, n, r[j], rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[m], sh->in_aux[m]);
             }
+          } else if (row_ok && r[3] == 0x7fffffff) {
+            store_output<EPI>(p, m_base, n, r[0], rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[0], sh->in_aux[0]);
           }
         }
         tc_fence_before();
@@ -406,7 +480,7 @@ struct ClusterLayout {
   static constexpr int kBarriers = 2 * kStages + 2;
   // without the fused prologue's operand buffer, which the launcher adds
   static constexpr int kSmemBytes = kStages * kStageBytes + kRedBytes + kBarriers * 8 + (int)sizeof(UmmaShared) +
-                                    2 * (int)sizeof(PrologueShared) + 128 + 16;
+                                    2 * (int)sizeof(PrologueShared) + 1024 + 16;
   static constexpr int kTmemCols = NB < 32 ? 32 : NB;
 };
 
@@ -421,7 +495,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
   uint64_t* b_ready = acc_full + 1;  // fused prologue: the operand rows are in place
   UmmaShared* sh = reinterpret_cast<UmmaShared*>(b_ready + 1);
   PrologueShared* ps = reinterpret_cast<PrologueShared*>(sh + 1);
-  uint8_t* bbuf = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ps + 2) + 127) & ~uintptr_t(127));
+  uint8_t* bbuf = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ps + 2) + 1023) & ~uintptr_t(1023));
   volatile int* abort_flag = &sh->abort_flag;
 
   const int tid = threadIdx.x;
@@ -512,8 +586,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
             p.prologue ? smem_u32(bbuf) + (uint32_t)(kt - kt_begin) * (uint32_t)L::kQBytes : a_addr + kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < kTileK8 / 32; ++ks) {
-          const uint64_t a_desc = umma_smem_desc(a_addr + ks * 256, 128, 1024);
-          const uint64_t b_desc = umma_smem_desc(b_addr + ks * 256, 128, 1024);
+          const uint64_t a_desc = umma_smem_desc(a_addr + ks * 32);
+          const uint64_t b_desc = umma_smem_desc(b_addr + ks * 32);
           umma_s8(tmem_base, a_desc, b_desc, idesc, (kt == kt_begin && ks == 0) ? 0u : 1u);
         }
         umma_commit(&empty_bar[s]);
@@ -718,8 +792,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
           for (int j = 0; j < tiles; ++j) {
 #pragma unroll
             for (int ks = 0; ks < kTileK8 / 32; ++ks) {
-              const uint64_t a_desc = umma_smem_desc(a_addr + j * kTileBytes + ks * 256, 128, 1024);
-              const uint64_t b_desc = umma_smem_desc(b_addr + ks * 256, 128, 1024);
+              const uint64_t a_desc = umma_smem_desc(a_addr + j * kTileBytes + ks * 32);
+              const uint64_t b_desc = umma_smem_desc(b_addr + ks * 32);
               umma_s8(tmem_base + j * NB, a_desc, b_desc, idesc, (kt == 0 && ks == 0) ? 0u : 1u);
             }
           }

@@ -87,7 +87,7 @@ struct FcParams {
   int max_ctas;              // 0 = chosen per shape
   int whole_tiles;           // set by the launcher: CTAs own whole n tiles (no split-K)
   int force_whole_tiles;     // set by the launcher for prefill-sized passes
-  int debug_flags;           // measurement only: 1 = skip the MMAs, 2 = skip the epilogue
+  int debug_flags;           // measurement only: 1 = skip the MMAs, 2 = the epilogue, 4 = the output stores, 8 = the TMEM loads
 };
 
 // Streamed-weights GEMM on the packed int8 tiles (any m; m > 64 runs in

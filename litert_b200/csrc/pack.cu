@@ -40,7 +40,8 @@ __global__ void pack_w8_kernel(const int8_t* __restrict__ w, int n, int k, int n
         if (k0 + b < k) v[b >> 2] |= (uint32_t)(uint8_t)src[b] << (8 * (b & 3));
       }
     }
-    *reinterpret_cast<uint4*>(packed + idx * 16) = make_uint4(v[0], v[1], v[2], v[3]);
+    uint8_t* dst = packed + (size_t)tile * kTileBytes + rg * 1024 + swz_chunk_offset(r, c);
+    *reinterpret_cast<uint4*>(dst) = make_uint4(v[0], v[1], v[2], v[3]);
   }
 }
 

@@ -26,7 +26,7 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 
 // Called by the kPrologueThreads epilogue threads (etid 0..127) after the dependency wait.
 //   bbuf: operand rows for k tiles [kt_begin, kt_end): per k tile nb_rows/8 row groups of 1 KiB in
-//         the tiled activation layout ([row group][16-byte chunk][row % 8][16 bytes]).
+//         the tiled activation layout (128-byte-swizzled K-major groups, see common.cuh).
 //   in_scale / in_aux: per-row scale and zero point for the kernel's own epilogue.
 //   writer: this CTA stores the updated residual stream (exactly one CTA per launch does).
 // Uses named barrier `bar_id` among the 128 threads.
@@ -41,11 +41,12 @@ __device__ __forceinline__ void prologue_norm_quant(const FcParams& p, uint8_t* 
   const bool in_range = kt >= kt_begin && kt < kt_end;  // chunk belongs to a k tile this CTA multiplies
   const bool have = k0 < d;
   const bool vec = have && k0 + 16 <= d && (d & 3) == 0;  // whole chunk inside the row: 128-bit accesses
-  uint8_t* chunk = bbuf + (size_t)(kt - kt_begin) * q_bytes + ((k0 % kTileK8) / 16) * 128;
+  uint8_t* tile = bbuf + (size_t)(kt - kt_begin) * q_bytes;  // this chunk's k tile
+  const int cc = (k0 % kTileK8) / 16;                         // its 16-byte chunk inside the tile's rows
   // rows beyond m, and chunks in the zero padding of the last k tile, multiply as zeros
   if (in_range)
     for (int m = have ? p.m : 0; m < nb_rows; ++m)
-      *reinterpret_cast<uint4*>(chunk + (m / 8) * 1024 + (m % 8) * 16) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(tile + (m / 8) * 1024 + swz_chunk_offset(m % 8, cc)) = make_uint4(0, 0, 0, 0);
   float g[16];
   if (vec) {
 #pragma unroll
@@ -158,7 +159,8 @@ __device__ __forceinline__ void prologue_norm_quant(const FcParams& p, uint8_t* 
         for (int e = 0; e < 4; ++e)
           if (!zero_row && k0 + q * 4 + e < d) word[q] |= quantize_value(v[q * 4 + e], inv, zpf, true) << (8 * e);
       }
-      *reinterpret_cast<uint4*>(chunk + (m / 8) * 1024 + (m % 8) * 16) = make_uint4(word[0], word[1], word[2], word[3]);
+      *reinterpret_cast<uint4*>(tile + (m / 8) * 1024 + swz_chunk_offset(m % 8, cc)) =
+          make_uint4(word[0], word[1], word[2], word[3]);
     }
   }
   for (int m = p.m + etid; m < nb_rows; m += kPrologueThreads) {

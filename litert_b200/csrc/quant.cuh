@@ -6,11 +6,11 @@
 
 namespace b200 {
 
-// Tiled activation layout shared by all MMA kernels: [k tile][row group of 8]
-// [16-byte chunk (8)][row (8)][16 bytes]; m_alloc rows are allocated.
+// Tiled activation layout shared by all MMA kernels: [k tile][row group of 8][1 KiB group in the
+// 128-byte-swizzled K-major layout of common.cuh]; m_alloc rows are allocated.
 __device__ __forceinline__ size_t q_tiled_offset(int m, int kk, int m_alloc) {
   const int kt = kk / kTileK8, c = (kk % kTileK8) / 16, b = kk % 16;
-  return (((size_t)kt * (m_alloc / 8) + (m / 8)) * kChunks8 + c) * 128 + (m % 8) * 16 + b;
+  return ((size_t)kt * (m_alloc / 8) + (m / 8)) * 1024 + swz_chunk_offset(m % 8, c) + b;
 }
 
 template <typename T, typename Op>
