@@ -341,10 +341,16 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
             if (!(p.debug_flags & 4)) {
               constexpr int kElem = EPI == kEpiRequantI8 ? 1 : 4;
               uint8_t* st = out_stage + (c & 1) * (16 * kTileN * 4);
+              float sc[16];  // the rows' parameters first: behind the staging stores they would be reloaded one by one
+              int32_t ax[16];
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                const int m = c * 16 + j;
-                const int32_t v = compute_output<EPI>(p, r[j], rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[m], sh->in_aux[m]);
+                sc[j] = sh->in_scale[c * 16 + j];
+                ax[j] = sh->in_aux[c * 16 + j];
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int32_t v = compute_output<EPI>(p, r[j], rs, wsc, bias_f, base_i, mult, shift, sc[j], ax[j]);
                 if constexpr (kElem == 4) {
                   reinterpret_cast<int32_t*>(st)[j * kTileN + row_in_tile] = v;
                 } else {
@@ -352,6 +358,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
                 }
               }
               named_barrier(2, kEpiThreads);  // the block is complete (and the other buffer's readers are done)
+              if (p.debug_flags & 32) continue;  // measurement: values computed and staged, never written out
               const int n0 = (int)nt * kTileN;
               constexpr int kChunksPerRow = kTileN * kElem / 16;        // 16-byte pieces per output row segment
               constexpr int kPieces = 16 * kChunksPerRow;
@@ -374,11 +381,17 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
               }
             }
           } else if (row_ok && !(p.debug_flags & 4)) {
+            float sc[16];  // parameters of the 16 rows, read before the first output store
+            int32_t ax[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              sc[j] = sh->in_scale[c * 16 + j];
+              ax[j] = sh->in_aux[c * 16 + j];
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int m = c * 16 + j;
-              if (m < m_valid)
-                store_output<EPI>(p, m_base + m, n, r[j], rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[m], sh->in_aux[m]);
+              if (m < m_valid) store_output<EPI>(p, m_base + m, n, r[j], rs, wsc, bias_f, base_i, mult, shift, sc[j], ax[j]);
             }
           } else if (row_ok && r[3] == 0x7fffffff) {
             store_output<EPI>(p, m_base, n, r[0], rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[0], sh->in_aux[0]);
@@ -693,33 +706,38 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
   }
 }
 
-// ---- prefill-sized variant: two n tiles per activation tile ---------------------------------------
-// With 256 activation rows per pass a CTA's traffic is dominated by the activation operand (32 KB
-// per k tile against a 16 KB weight tile), and every CTA re-reads it from L2. Here one stage holds
-// TWO weight tiles (consecutive n tiles, same k tile) and the activation tile once: 64 KB per stage
-// for twice the MMAs, a third less traffic per MAC. The two accumulators (128 x 256 int32 each)
-// fill all 512 TMEM columns, so a CTA's next unit waits for the epilogue of the previous one.
-// Work units = (pair of n tiles, pass of 256 rows), whole units per CTA, no cross-CTA reduction.
+// ---- prefill-sized variant ------------------------------------------------------------------------
+// 256 activation rows per pass, whole work units per CTA, persistent CTAs: a unit is (n tile or pair
+// of n tiles, pass of 256 rows) and a CTA takes units blockIdx.x, blockIdx.x + gridDim.x, ...
+//  * TILES = 1: one 16 KiB weight tile + the 32 KiB activation tile per stage; the two 256-column
+//    accumulators alternate, so the epilogue of a unit (writing 128 x 256 outputs takes longer than
+//    its MMAs) runs under the MMAs of the CTA's next unit.
+//  * TILES = 2: two weight tiles of consecutive n tiles share one activation tile per stage (a third
+//    less traffic per MAC); both accumulators belong to one unit, so epilogues do not overlap.
+// Outputs leave through a shared-memory staging block as whole row segments (see fc_umma_kernel).
+template <int TILES>
 struct PrefillLayout {
   static constexpr int kNB = 256;
-  static constexpr int kQBytes = kNB * kTileK8;                  // 32 KiB
-  static constexpr int kStageBytes = 2 * kTileBytes + kQBytes;   // 64 KiB
-  static constexpr int kStages = 3;
-  static constexpr int kBarriers = 2 * kStages + 2;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarriers * 8 + (int)sizeof(UmmaShared) + 16;
+  static constexpr int kQBytes = kNB * kTileK8;                      // 32 KiB
+  static constexpr int kStageBytes = TILES * kTileBytes + kQBytes;
+  static constexpr int kStages = 206 * 1024 / kStageBytes - (TILES == 2 ? 0 : 0);
+  static constexpr int kOutStageBytes = 2 * 16 * kTileN * 4;
+  static constexpr int kBarriers = 2 * kStages + 4;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarriers * 8 + (int)sizeof(UmmaShared) + 32 + kOutStageBytes;
   static constexpr int kTmemCols = 512;
 };
 
-template <int EPI>
-__global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcParams p, const int pairs, const int passes) {
-  using L = PrefillLayout;
+template <int EPI, int TILES>
+__global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcParams p, const int n_units, const int passes) {
+  using L = PrefillLayout<TILES>;
   constexpr int NB = L::kNB;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
   uint64_t* empty_bar = full_bar + L::kStages;
-  uint64_t* acc_full = empty_bar + L::kStages;
-  uint64_t* acc_empty = acc_full + 1;
-  UmmaShared* sh = reinterpret_cast<UmmaShared*>(acc_empty + 1);
+  uint64_t* acc_full = empty_bar + L::kStages;  // [2]
+  uint64_t* acc_empty = acc_full + 2;           // [2]
+  UmmaShared* sh = reinterpret_cast<UmmaShared*>(acc_empty + 2);
+  uint8_t* out_stage = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));
   volatile int* abort_flag = &sh->abort_flag;
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -728,8 +746,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 4);  // one arrival per epilogue warp
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+    }
     sh->abort_flag = 0;
     mbar_fence_init();
   }
@@ -738,9 +758,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
-  const int units = pairs * passes;
+  const int units = n_units * passes;
   const int m_groups_alloc = p.m_alloc / 8;
-  // unit u -> pass (slow index) and pair (fast): neighbouring CTAs share the activation rows
+  // accumulator set of the CTA's i-th unit, and how often that set has been used before
+  auto acc_of = [](uint32_t i) { return TILES == 2 ? 0u : (i & 1u); };
+  auto use_of = [](uint32_t i) { return TILES == 2 ? i : (i >> 1); };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -749,9 +771,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
       pdl_wait();
       uint32_t it = 0;
       for (int u = blockIdx.x; u < units; u += gridDim.x) {
-        const int pass = u / pairs, pair = u % pairs;
-        const int nt0 = pair * 2;
-        const int tiles = nt0 + 1 < p.n_tiles ? 2 : 1;
+        const int pass = u / n_units, idx = u % n_units;
+        const int nt0 = idx * TILES;
+        const int tiles = (TILES == 2 && nt0 + 1 < p.n_tiles) ? 2 : 1;
         const int mg_base = pass * (NB / 8);
         for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
           const int s = it % L::kStages;
@@ -763,7 +785,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
             bulk_g2s_hint(dst + j * kTileBytes, p.w_packed + ((size_t)(nt0 + j) * p.k_tiles + kt) * kTileBytes, kTileBytes,
                           &full_bar[s], stream_policy);
           const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
-          bulk_g2s(dst + 2 * kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[s]);
+          bulk_g2s(dst + TILES * kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[s]);
         }
       }
       const uint32_t issued = it;  // never leave with copies in flight (only possible after an abort)
@@ -777,10 +799,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
       constexpr uint32_t idesc = umma_idesc_s8(NB);
       uint32_t it = 0, done = 0;
       for (int u = blockIdx.x; u < units; u += gridDim.x, ++done) {
-        const int pair = u % pairs;
-        const int tiles = pair * 2 + 1 < p.n_tiles ? 2 : 1;
-        // both accumulators are free once the epilogue has drained the previous unit
-        mbar_wait_bounded(acc_empty, (done & 1u) ^ 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
+        const int idx = u % n_units;
+        const int tiles = (TILES == 2 && idx * TILES + 1 < p.n_tiles) ? 2 : 1;
+        const uint32_t ab = acc_of(done), use = use_of(done);
+        // the accumulator set is free once the epilogue has drained its previous unit
+        mbar_wait_bounded(&acc_empty[ab], (use & 1u) ^ 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
         tc_fence_after();
         for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
           const int s = it % L::kStages;
@@ -788,33 +811,40 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
           mbar_wait_bounded(&full_bar[s], ph, abort_flag, p.status, kStatusWaitTimeoutFull);
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + (size_t)s * L::kStageBytes);
-          const uint32_t b_addr = a_addr + 2 * kTileBytes;
+          const uint32_t b_addr = a_addr + TILES * kTileBytes;
           for (int j = 0; j < tiles; ++j) {
+            const uint32_t d_tmem = tmem_base + (TILES == 2 ? j : ab) * NB;
 #pragma unroll
             for (int ks = 0; ks < kTileK8 / 32; ++ks) {
               const uint64_t a_desc = umma_smem_desc(a_addr + j * kTileBytes + ks * 32);
               const uint64_t b_desc = umma_smem_desc(b_addr + ks * 32);
-              umma_s8(tmem_base + j * NB, a_desc, b_desc, idesc, (kt == 0 && ks == 0) ? 0u : 1u);
+              umma_s8(d_tmem, a_desc, b_desc, idesc, (kt == 0 && ks == 0) ? 0u : 1u);
             }
           }
           umma_commit(&empty_bar[s]);
         }
-        umma_commit(acc_full);
+        umma_commit(&acc_full[ab]);
       }
-      if (done > 0) mbar_wait_bounded(acc_full, (done - 1) & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
+      // wait for the last accumulators to be complete before the CTA tears TMEM down
+      for (uint32_t back = 0; back < 2 && back < done; ++back) {
+        const uint32_t i = done - 1 - back;
+        mbar_wait_bounded(&acc_full[acc_of(i)], use_of(i) & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
+      }
     }
   } else {
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const int etid = tid - 64;
+    constexpr int kElem = EPI == kEpiRequantI8 ? 1 : 4;
     pdl_wait();
     uint32_t done = 0;
     int staged_pass = -1;
     for (int u = blockIdx.x; u < units; u += gridDim.x, ++done) {
-      const int pass = u / pairs, pair = u % pairs;
-      const int tiles = pair * 2 + 1 < p.n_tiles ? 2 : 1;
+      const int pass = u / n_units, idx = u % n_units;
+      const int tiles = (TILES == 2 && idx * TILES + 1 < p.n_tiles) ? 2 : 1;
       const int m_base = pass * NB;
       const int m_valid = p.m - m_base < NB ? p.m - m_base : NB;
+      const uint32_t ab = acc_of(done), use = use_of(done);
       if (pass != staged_pass) {  // per-row scale and zero point (or row sum) of this pass
         named_barrier(1, kEpiThreads);
         for (int i = etid; i < NB; i += kEpiThreads) {
@@ -830,11 +860,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
         named_barrier(1, kEpiThreads);
         staged_pass = pass;
       }
-      int32_t rs[2] = {0, 0}, base_i[2] = {0, 0}, mult[2] = {0, 0}, shift[2] = {0, 0};
-      float wsc[2] = {0.0f, 0.0f}, bias_f[2] = {0.0f, 0.0f};
-      for (int j = 0; j < tiles; ++j) {
-        const int n = (pair * 2 + j) * kTileN + row_in_tile;
-        if (n >= p.n) continue;
+      int32_t rs[TILES], base_i[TILES], mult[TILES], shift[TILES];
+      float wsc[TILES], bias_f[TILES];
+#pragma unroll
+      for (int j = 0; j < TILES; ++j) {
+        rs[j] = base_i[j] = mult[j] = shift[j] = 0;
+        wsc[j] = bias_f[j] = 0.0f;
+        const int n = (idx * TILES + j) * kTileN + row_in_tile;
+        if (j >= tiles || n >= p.n) continue;
         rs[j] = p.row_sums ? p.row_sums[n] : 0;
         if constexpr (EPI == kEpiHybridF32) {
           wsc[j] = p.per_channel ? p.w_scales[n] : p.w_scales[0];
@@ -847,31 +880,62 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
           }
         }
       }
-      mbar_wait_bounded(acc_full, done & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
+      mbar_wait_bounded(&acc_full[ab], use & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
       tc_fence_after();
-      for (int j = 0; j < tiles; ++j) {
-        const int n = (pair * 2 + j) * kTileN + row_in_tile;
-        const uint32_t taddr = tmem_base + j * NB + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+      for (int j = 0; j < TILES; ++j) {
+        if (j >= tiles) break;
+        const int n0 = (idx * TILES + j) * kTileN;
+        const uint32_t taddr = tmem_base + (TILES == 2 ? j : ab) * NB + ((uint32_t)(quarter * 32) << 16);
+        const bool vec_ok = (((size_t)p.n * kElem) % 16 == 0) && (n0 + kTileN <= p.n) &&
+                            ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
 #pragma unroll 1
         for (int c = 0; c < NB / 16; ++c) {
           if (c * 16 >= m_valid) break;
           int r[16];
           tmem_ld16(taddr + c * 16, r);
           tmem_ld_wait();
-          if (n < p.n) {
+          uint8_t* st = out_stage + (c & 1) * (16 * kTileN * 4);
+          // the rows' parameters first, all at once: behind the staging stores the compiler would have
+          // to reload them one by one (it cannot rule out that the stores change them)
+          float sc[16];
+          int32_t ax[16];
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const int m = c * 16 + e;
-              if (m < m_valid)
-                store_output<EPI>(p, m_base + m, n, r[e], rs[j], wsc[j], bias_f[j], base_i[j], mult[j], shift[j],
-                                  sh->in_scale[m], sh->in_aux[m]);
+          for (int e = 0; e < 16; ++e) {
+            sc[e] = sh->in_scale[c * 16 + e];
+            ax[e] = sh->in_aux[c * 16 + e];
+          }
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int32_t v = compute_output<EPI>(p, r[e], rs[j], wsc[j], bias_f[j], base_i[j], mult[j], shift[j],
+                                                  sc[e], ax[e]);
+            if constexpr (kElem == 4) {
+              reinterpret_cast<int32_t*>(st)[e * kTileN + row_in_tile] = v;
+            } else {
+              reinterpret_cast<int8_t*>(st)[e * kTileN + row_in_tile] = (int8_t)v;
+            }
+          }
+          named_barrier(2, kEpiThreads);  // the block is complete (and the other buffer's readers are done)
+          constexpr int kChunksPerRow = kTileN * kElem / 16;
+          constexpr int kPieces = 16 * kChunksPerRow;
+          for (int i = etid; i < kPieces; i += kEpiThreads) {
+            const int rr = i / kChunksPerRow, cc = i % kChunksPerRow;
+            const int m = c * 16 + rr;
+            if (m >= m_valid) continue;
+            uint8_t* dst = static_cast<uint8_t*>(p.y) + ((size_t)(m_base + m) * p.n + n0) * kElem + cc * 16;
+            const uint8_t* src = st + (size_t)rr * kTileN * kElem + cc * 16;
+            if (vec_ok) {
+              *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+            } else {
+              for (int bb = 0; bb < 16; ++bb)
+                if (n0 + (cc * 16 + bb) / kElem < p.n) dst[bb] = src[bb];
             }
           }
         }
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty);
+      if (lane == 0) mbar_arrive(&acc_empty[ab]);
     }
   }
   tc_fence_before();
@@ -879,11 +943,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
   if (warp == 1) tmem_dealloc(tmem_base, L::kTmemCols);
 }
 
-template <int EPI>
+template <int EPI, int TILES>
 cudaError_t launch_prefill(const FcParams& p, cudaStream_t s) {
-  using L = PrefillLayout;
+  using L = PrefillLayout<TILES>;
   static bool configured[64] = {false};
-  auto kernel = fc_prefill_kernel<EPI>;
+  auto kernel = fc_prefill_kernel<EPI, TILES>;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
@@ -892,12 +956,16 @@ cudaError_t launch_prefill(const FcParams& p, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const int pairs = (p.n_tiles + 1) / 2;
+  const int n_units = (p.n_tiles + TILES - 1) / TILES;
   const int passes = (p.m + L::kNB - 1) / L::kNB;
   const int sms = device_sm_count();
-  const int units = pairs * passes;
-  const int ctas = units < sms ? units : sms;
-  return launch_chained(kernel, dim3(ctas), dim3(kUmmaThreads), (size_t)L::kSmemBytes, s, p, pairs, passes);
+  const int units = n_units * passes;
+  int ctas = units < sms ? units : sms;
+  if (const char* e = getenv("B200_FC_MAX_CTAS")) {  // measurement knob
+    const int v = atoi(e);
+    if (v > 0 && v < ctas) ctas = v;
+  }
+  return launch_chained(kernel, dim3(ctas), dim3(kUmmaThreads), (size_t)L::kSmemBytes, s, p, n_units, passes);
 }
 
 // Chooses the number of CTAs and the split for one launch (measured on B200, batch 1, graph
@@ -1085,8 +1153,14 @@ cudaError_t launch_all(const FcParams& p, cudaStream_t s) {
     if (v == 128 || v == 256) nb = v;
   }
   if (p.m_alloc % nb != 0) return cudaErrorInvalidValue;
-  const char* dual_env = getenv("B200_FC_DUAL");  // 1: two n tiles per stage (fc_prefill_kernel)
-  if (nb == 256 && p.n_tiles >= 2 && dual_env && dual_env[0] == '1') return launch_prefill<EPI>(p, s);
+  if (nb == 256) {
+    // persistent CTAs over (n tile, pass) units; B200_FC_PREFILL=0 keeps the one-unit-per-CTA launch
+    // below, =2 pairs n tiles (measurement knobs)
+    const char* e = getenv("B200_FC_PREFILL");
+    const int mode = e ? atoi(e) : 1;
+    if (mode == 2 && p.n_tiles >= 2) return launch_prefill<EPI, 2>(p, s);
+    if (mode == 1) return launch_prefill<EPI, 1>(p, s);
+  }
   const int passes = (p.m + nb - 1) / nb;
   FcParams q = p;
   q.force_whole_tiles = 1;
