@@ -707,28 +707,34 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
 }
 
 // ---- prefill-sized variant ------------------------------------------------------------------------
-// 256 activation rows per pass, whole work units per CTA, persistent CTAs: a unit is (n tile or pair
-// of n tiles, pass of 256 rows) and a CTA takes units blockIdx.x, blockIdx.x + gridDim.x, ...
-//  * TILES = 1: one 16 KiB weight tile + the 32 KiB activation tile per stage; the two 256-column
-//    accumulators alternate, so the epilogue of a unit (writing 128 x 256 outputs takes longer than
-//    its MMAs) runs under the MMAs of the CTA's next unit.
-//  * TILES = 2: two weight tiles of consecutive n tiles share one activation tile per stage (a third
-//    less traffic per MAC); both accumulators belong to one unit, so epilogues do not overlap.
-// Outputs leave through a shared-memory staging block as whole row segments (see fc_umma_kernel).
+// 256 activation rows per pass, whole work units per CTA, persistent CTAs: a unit is (n tile, pass of
+// 256 rows) and a CTA takes units blockIdx.x, blockIdx.x + gridDim.x, ... One 16 KiB weight tile +
+// the 32 KiB activation tile per stage; the two 256-column accumulators alternate, so the epilogue of
+// a unit runs under the MMAs of the CTA's next unit. The epilogue is the expensive part (128 x 256
+// outputs per unit, ~10 instructions each): eight warps share it, two per TMEM lane quarter, and the
+// outputs leave through shared-memory staging blocks as whole row segments (see fc_umma_kernel).
+// Measured, config 2 at M = 512: 86 us one unit per CTA -> 68 persistent -> 63 row parameters
+// preloaded -> 43 with eight epilogue warps (34 with the epilogue left out).
+// (TILES = 2, two weight tiles of consecutive n tiles per activation tile, is written into the
+// kernel but not instantiated: with four epilogue warps it measured slower, 73 us, since a unit
+// then owns both accumulators and nothing overlaps; it has not been run with eight.)
 template <int TILES>
 struct PrefillLayout {
   static constexpr int kNB = 256;
   static constexpr int kQBytes = kNB * kTileK8;                      // 32 KiB
   static constexpr int kStageBytes = TILES * kTileBytes + kQBytes;
   static constexpr int kStages = 206 * 1024 / kStageBytes - (TILES == 2 ? 0 : 0);
-  static constexpr int kOutStageBytes = 2 * 16 * kTileN * 4;
+  static constexpr int kEpiWarps = 8;                                 // two per TMEM lane quarter
+  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  static constexpr int kOutStageBytes = 2 * 2 * 16 * kTileN * 4;      // two blocks per half of the epilogue warps
   static constexpr int kBarriers = 2 * kStages + 4;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarriers * 8 + (int)sizeof(UmmaShared) + 32 + kOutStageBytes;
   static constexpr int kTmemCols = 512;
+  static_assert(kSmemBytes <= kMaxDynamicSmem, "prefill kernel: shared memory over the per-CTA limit");
 };
 
 template <int EPI, int TILES>
-__global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcParams p, const int n_units, const int passes) {
+__global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_kernel(const FcParams p, const int n_units, const int passes) {
   using L = PrefillLayout<TILES>;
   constexpr int NB = L::kNB;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -748,7 +754,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[a], L::kEpiWarps);  // one arrival per epilogue warp
     }
     sh->abort_flag = 0;
     mbar_fence_init();
@@ -832,9 +838,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
       }
     }
   } else {
+    // eight epilogue warps: the TMEM lane quarter is warp % 4, and the two warps of a quarter take
+    // the even and the odd 16-row blocks; each half works through its own pair of staging blocks
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
-    const int etid = tid - 64;
+    const int half = (warp - 2) >> 2;
+    const int etid = (tid - 64) & 127;   // thread index within the half
+    const int etid_all = tid - 64;
+    constexpr int kHalfThreads = 128;
+    constexpr int kAllEpi = L::kEpiWarps * 32;
     constexpr int kElem = EPI == kEpiRequantI8 ? 1 : 4;
     pdl_wait();
     uint32_t done = 0;
@@ -846,8 +858,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
       const int m_valid = p.m - m_base < NB ? p.m - m_base : NB;
       const uint32_t ab = acc_of(done), use = use_of(done);
       if (pass != staged_pass) {  // per-row scale and zero point (or row sum) of this pass
-        named_barrier(1, kEpiThreads);
-        for (int i = etid; i < NB; i += kEpiThreads) {
+        named_barrier(1, kAllEpi);
+        for (int i = etid_all; i < NB; i += kAllEpi) {
           const int m = m_base + i;
           const bool ok = m < p.m;
           sh->in_scale[i] = (ok && p.in_scales) ? p.in_scales[m] : 0.0f;
@@ -857,7 +869,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
             sh->in_aux[i] = (ok && p.x_sums) ? p.x_sums[m] : 0;
           }
         }
-        named_barrier(1, kEpiThreads);
+        named_barrier(1, kAllEpi);
         staged_pass = pass;
       }
       int32_t rs[TILES], base_i[TILES], mult[TILES], shift[TILES];
@@ -890,12 +902,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
         const bool vec_ok = (((size_t)p.n * kElem) % 16 == 0) && (n0 + kTileN <= p.n) &&
                             ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
 #pragma unroll 1
-        for (int c = 0; c < NB / 16; ++c) {
+        for (int c = half; c < NB / 16; c += 2) {
           if (c * 16 >= m_valid) break;
           int r[16];
           tmem_ld16(taddr + c * 16, r);
           tmem_ld_wait();
-          uint8_t* st = out_stage + (c & 1) * (16 * kTileN * 4);
+          uint8_t* st = out_stage + (half * 2 + ((c >> 1) & 1)) * (16 * kTileN * 4);
           // the rows' parameters first, all at once: behind the staging stores the compiler would have
           // to reload them one by one (it cannot rule out that the stores change them)
           float sc[16];
@@ -915,10 +927,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_prefill_kernel(const FcPar
               reinterpret_cast<int8_t*>(st)[e * kTileN + row_in_tile] = (int8_t)v;
             }
           }
-          named_barrier(2, kEpiThreads);  // the block is complete (and the other buffer's readers are done)
+          named_barrier(2 + half, kHalfThreads);  // the block is complete (and the other block's readers are done)
           constexpr int kChunksPerRow = kTileN * kElem / 16;
           constexpr int kPieces = 16 * kChunksPerRow;
-          for (int i = etid; i < kPieces; i += kEpiThreads) {
+          for (int i = etid; i < kPieces; i += kHalfThreads) {
             const int rr = i / kChunksPerRow, cc = i % kChunksPerRow;
             const int m = c * 16 + rr;
             if (m >= m_valid) continue;
@@ -965,7 +977,7 @@ cudaError_t launch_prefill(const FcParams& p, cudaStream_t s) {
     const int v = atoi(e);
     if (v > 0 && v < ctas) ctas = v;
   }
-  return launch_chained(kernel, dim3(ctas), dim3(kUmmaThreads), (size_t)L::kSmemBytes, s, p, n_units, passes);
+  return launch_chained(kernel, dim3(ctas), dim3(L::kThreads), (size_t)L::kSmemBytes, s, p, n_units, passes);
 }
 
 // Chooses the number of CTAs and the split for one launch (measured on B200, batch 1, graph
@@ -1155,11 +1167,9 @@ cudaError_t launch_all(const FcParams& p, cudaStream_t s) {
   if (p.m_alloc % nb != 0) return cudaErrorInvalidValue;
   if (nb == 256) {
     // persistent CTAs over (n tile, pass) units; B200_FC_PREFILL=0 keeps the one-unit-per-CTA launch
-    // below, =2 pairs n tiles (measurement knobs)
+    // below (measurement knob)
     const char* e = getenv("B200_FC_PREFILL");
-    const int mode = e ? atoi(e) : 1;
-    if (mode == 2 && p.n_tiles >= 2) return launch_prefill<EPI, 2>(p, s);
-    if (mode == 1) return launch_prefill<EPI, 1>(p, s);
+    if (!(e && e[0] == '0')) return launch_prefill<EPI, 1>(p, s);
   }
   const int passes = (p.m + nb - 1) / nb;
   FcParams q = p;
