@@ -1,7 +1,7 @@
 """Builds libtflite_b200_delegate.so (the TfLiteDelegate plugin) in-tree.
 
 The delegate is compiled against the LiteRT C headers where they lie in a LiteRT checkout
-(LITERT_ROOT, default /root/reference); two of its small C sources (TfLiteIntArray helpers) are
+(environment variable LITERT_ROOT); two of its small C sources (TfLiteIntArray helpers) are
 compiled from there too. Without the checkout an already built library is kept as is.
 """
 import os

@@ -26,10 +26,11 @@ def build(force=False):
                     for t in targets)
     if force or stale:
         subprocess.check_call(["make", "-C", _HERE, "-s", "liboracle.so", "liboracle_fast.so"])
-    if os.path.isdir("/root/reference/tflite") and (
+    ref_root = os.environ.get("LITERT_ROOT", "/root/reference")
+    if os.path.isdir(os.path.join(ref_root, "tflite")) and (
         force or not os.path.exists(os.path.join(_HERE, "_ref", "libref_quant.so"))
     ):
-        subprocess.check_call(["make", "-C", _HERE, "-s", "ref"])
+        subprocess.check_call(["make", "-C", _HERE, "-s", "ref", "REF=" + ref_root])
 
 
 _lib = None

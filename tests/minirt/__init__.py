@@ -1,7 +1,7 @@
 """Python handle on the mini runtime (tests/minirt/minirt.cc) and on the delegate plugin.
 
 TEST INFRASTRUCTURE ONLY. The mini runtime is compiled against the LiteRT C headers where they
-lie (LITERT_ROOT, default /root/reference); a prebuilt libminirt.so is used when they are absent.
+lie (environment variable LITERT_ROOT); a prebuilt libminirt.so is used when they are absent.
 """
 import ctypes
 import os
