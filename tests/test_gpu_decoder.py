@@ -47,6 +47,31 @@ def test_decoder_matches_cpu_graph(oracle, kv_dtype, tol):
     ref.close()
 
 
+@pytest.mark.parametrize("kv_dtype,tol", [("f16", 8e-2), ("i8", 2.5e-1)])
+def test_decoder_long_context_attention_step(oracle, kv_dtype, tol):
+    """Seventy tokens deep: the one-launch attention step then gives every CTA of its cluster several
+    16-token groups (first CTAs) or none (last ones), and the warps of a CTA unequal shares. The
+    bound is looser than above because the divergence of two int8-requantizing graphs grows with depth."""
+    from litert_b200 import decoder as dec
+
+    cfg = dict(dec.TINY)
+    batch, steps, max_seq = 2, 70, 96
+    weights = dec.make_weights(cfg, seed=12)
+    gpu = dec.Decoder(cfg, max_seq=max_seq, max_batch=batch, weights=weights, kv_dtype=kv_dtype)
+    ref = oracle.DecoderRef(cfg, _host(weights), batch, max_seq, fast=True)
+    tokens = np.random.default_rng(6).integers(0, cfg["vocab"], batch).astype(np.int32)
+    for s in range(steps):
+        check = s in (0, 17, 33, 50, 69)
+        _, logits_g = gpu.step(tokens, want_logits=check)
+        nxt_r, logits_r = ref.step(tokens, want_logits=True)
+        if check:
+            err = np.linalg.norm(logits_g.cpu().numpy() - logits_r) / np.linalg.norm(logits_r)
+            assert err <= tol, (s, err)
+        tokens = nxt_r
+    gpu.close()
+    ref.close()
+
+
 def test_decoder_wide_batch_uses_chunked_attention(oracle):
     """Twelve sequences: past the size where one cluster per sequence pays, the step goes through the
     rotary / flash-decode / merge kernels instead. Same bound as above."""

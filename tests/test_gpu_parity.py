@@ -86,8 +86,15 @@ def test_fc_int8_config1_bit_exact(ops, oracle, ws):
     assert len(np.unique(got)) > 100  # not saturated: the comparison means something
 
 
+# The last two rows aim at the kernels chosen by shape: few n tiles with a long reduction (cluster
+# split-K, splits of 8 / 6 / 3 / 2 and a k range that leaves some CTAs of a cluster without work), and
+# more than 128 activation rows (the persistent prefill kernel: partial last pass, partial last n tile,
+# an output row length that rules out 16-byte stores).
 @pytest.mark.parametrize("m,n,k", [(1, 1, 1), (1, 130, 100), (5, 64, 16), (17, 257, 333), (33, 128, 128),
-                                   (64, 300, 2048), (65, 129, 257), (130, 40, 70)])
+                                   (64, 300, 2048), (65, 129, 257), (130, 40, 70),
+                                   (1, 384, 4096), (5, 2560, 2048), (17, 2000, 300), (33, 1000, 1100), (64, 128, 8200),
+                                   (100, 2048, 2048), (128, 300, 700),
+                                   (257, 20000, 256), (300, 19001, 130), (512, 18944, 384), (600, 37890, 100)])
 def test_fc_int8_ragged_shapes_bit_exact(ops, oracle, ws, m, n, k):
     c = workloads.config1(m, n, k, seed=7 + m + n + k)
     if (m + n) % 2:
@@ -178,7 +185,9 @@ def test_fc_hybrid_config2_m512(ops, oracle, ws):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 3, 10), (2, 130, 100), (9, 257, 333), (16, 128, 4096), (40, 77, 129),
-                                   (70, 200, 64)])
+                                   (70, 200, 64),
+                                   (1, 2048, 16384), (3, 1536, 2048), (32, 2049, 1000), (64, 640, 260), (128, 1030, 520),
+                                   (200, 19000, 200), (513, 18945, 96)])
 @pytest.mark.parametrize("asymmetric,per_channel", [(True, True), (False, True), (True, False)])
 def test_fc_hybrid_ragged_shapes(ops, oracle, ws, m, n, k, asymmetric, per_channel):
     rng = np.random.default_rng(m * 1000 + n + k)
