@@ -236,6 +236,16 @@ B200_API int b200_decoder_set_positions(b200_decoder* dec, const int32_t* h_posi
  * when h_next_tokens is given. */
 B200_API int b200_decoder_step(b200_decoder* dec, const int32_t* h_tokens, int batch, int32_t* h_next_tokens,
                                float* d_logits);
+/* Prompt pass: runs the n_tokens prompt tokens (HOST array) of sequence `seq` through the layers in
+ * chunks of up to 512 rows, every projection as one GEMM over the chunk, appends their keys and
+ * values to the sequence's cache behind the tokens already there, and predicts the first generated
+ * token from the last prompt token (greedy; written to *h_next_token when given, and kept on the
+ * device so that b200_decoder_run(dec, NULL, ...) continues from it). Results are those of
+ * n_tokens single steps of that sequence. Other sequences are untouched. With tp_size > 1 the
+ * partial sums go through the all-reduce (b200_decoder_init_nccl / b200_decoder_set_allreduce).
+ * Synchronises the stream. */
+B200_API int b200_decoder_prefill(b200_decoder* dec, int seq, const int32_t* h_tokens, int n_tokens,
+                                  int32_t* h_next_token);
 /* Device-resident variant: feeds the previous step's greedy tokens back without
  * touching the host (first call after a reset uses h_first_tokens). Runs `steps`
  * steps; the last tokens are copied to h_next_tokens when given. */

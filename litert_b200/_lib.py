@@ -47,6 +47,7 @@ SIGNATURES = {
     "b200_decoder_set_positions": (_i, [_vp, _vp, _i]),
     "b200_decoder_step": (_i, [_vp, _vp, _i, _vp, _vp]),
     "b200_decoder_run": (_i, [_vp, _vp, _i, _i, _vp]),
+    "b200_decoder_prefill": (_i, [_vp, _i, _vp, _i, _vp]),
     "b200_decoder_launches_per_step": (_i, [_vp]),
     "b200_decoder_profile_step": (_i, [_vp, _vp, _i, _vp, _vp]),
     "b200_decoder_time_gemv": (_i, [_vp, _i, _i, _vp, _vp]),

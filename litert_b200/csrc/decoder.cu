@@ -51,6 +51,17 @@ struct Layer {
   DevBuf k_cache, v_cache, k_scale, v_scale;
 };
 
+// Scratch of a prompt pass: the decode step's buffers hold max_batch rows, a prompt chunk up to `rows`.
+struct PrefillBufs {
+  int rows = 0;
+  DevBuf tokens, positions, attn_len, h, qkv, q, gate_up, proj, down_out;
+  DevBuf q_d, q_a, q_f, sc_d, sc_a, sc_f, zp_d, zp_a, zp_f, sdpa_ws;
+  int32_t* h_stage = nullptr;  // pinned: tokens then positions of one chunk
+  ~PrefillBufs() {
+    if (h_stage) cudaFreeHost(h_stage);
+  }
+};
+
 }  // namespace
 
 struct b200_decoder {
@@ -82,6 +93,7 @@ struct b200_decoder {
   void* allreduce_user = nullptr;
   void* nccl_comm = nullptr;
   cudaGraphExec_t graph[257] = {nullptr};  // indexed by batch
+  std::unique_ptr<PrefillBufs> pf;         // allocated by the first prompt pass
   int launches = 0;
   // per-kernel-class timing of one eager step (b200_decoder_profile_step)
   bool profiling = false;
@@ -369,7 +381,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
     } else {
       if (!(skip & 2)) GLUE_CUDA(launch_rope_cache(d->qkv.as<float>(), batch, d->hl, d->kvl, c.head_dim, c.rope_base,
                                  d->positions.as<int32_t>(), c.max_seq, d->q.as<float>(), L.k_cache.p, L.v_cache.p,
-                                 L.k_scale.as<float>(), L.v_scale.as<float>(), c.kv_dtype == B200_DTYPE_I8, s));
+                                 L.k_scale.as<float>(), L.v_scale.as<float>(), c.kv_dtype == B200_DTYPE_I8, 0, s));
       count();
       SdpaParams sp;
       memset(&sp, 0, sizeof(sp));
@@ -462,6 +474,129 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
                                 c.max_seq, nullptr, s));
   }
   count(3);
+  return B200_OK;
+}
+
+// Rows of one prompt chunk: enough for the 256-row passes of the prefill GEMM kernel to fill the
+// machine at every projection shape, small enough that the feed-forward scratch stays modest.
+constexpr int kPrefillRows = 512;
+
+int ensure_prefill_bufs(b200_decoder* d) {
+  if (d->pf) return B200_OK;
+  const b200_decoder_config& c = d->cfg;
+  auto pf = std::make_unique<PrefillBufs>();
+  const int R = kPrefillRows, m_alloc = m_alloc_for(R), qdim = d->hl * c.head_dim, kvdim = d->kvl * c.head_dim;
+  pf->rows = R;
+  DEC_CUDA(pf->tokens.alloc(sizeof(int32_t) * R));
+  DEC_CUDA(pf->positions.alloc(sizeof(int32_t) * R));
+  DEC_CUDA(pf->attn_len.alloc(sizeof(int32_t) * R));
+  DEC_CUDA(pf->h.alloc(sizeof(float) * R * c.d_model));
+  DEC_CUDA(pf->qkv.alloc(sizeof(float) * R * (qdim + 2 * kvdim)));
+  DEC_CUDA(pf->q.alloc(sizeof(float) * R * qdim));
+  DEC_CUDA(pf->gate_up.alloc(sizeof(float) * (size_t)R * 2 * d->fl));
+  DEC_CUDA(pf->proj.alloc(sizeof(float) * R * c.d_model));
+  DEC_CUDA(pf->down_out.alloc(sizeof(float) * R * c.d_model));
+  DEC_CUDA(pf->q_d.alloc(q_tiled_bytes(m_alloc, c.d_model)));
+  DEC_CUDA(pf->q_a.alloc(q_tiled_bytes(m_alloc, qdim)));
+  DEC_CUDA(pf->q_f.alloc(q_tiled_bytes(m_alloc, d->fl)));
+  for (DevBuf* b : {&pf->sc_d, &pf->sc_a, &pf->sc_f, &pf->zp_d, &pf->zp_a, &pf->zp_f}) DEC_CUDA(b->alloc(sizeof(float) * m_alloc));
+  size_t sdpa_bytes = 0;  // the chunking depends on the row count
+  for (int b = 1; b <= R; ++b) sdpa_bytes = std::max(sdpa_bytes, sdpa_workspace_bytes(b, d->hl, d->kvl, c.head_dim, c.max_seq));
+  DEC_CUDA(pf->sdpa_ws.alloc(sdpa_bytes));
+  DEC_CUDA(cudaMallocHost(&pf->h_stage, sizeof(int32_t) * 2 * R));
+  d->pf = std::move(pf);
+  return B200_OK;
+}
+
+// Enqueues the layers over `rows` consecutive prompt tokens of sequence `seq` (tokens and positions
+// already in the prompt scratch). Every projection is one GEMM over all the rows; the rows' keys and
+// values are appended first, then row t attends over the cache up to its own position, which is the
+// causal mask. With `pick`, the last row goes through the final norm, the LM head and the arg-max,
+// whose token lands in next_tokens[seq].
+int enqueue_prefill_chunk(b200_decoder* d, int seq, int rows, bool pick) {
+  const b200_decoder_config& c = d->cfg;
+  PrefillBufs& f = *d->pf;
+  cudaStream_t s = d->stream;
+  const int m_alloc = m_alloc_for(rows);
+  const bool tp = c.tp_size > 1;
+  const bool i8 = c.kv_dtype == B200_DTYPE_I8;
+  auto reduce = [&](float* buf, size_t n) -> int {
+    if (!tp) return B200_OK;
+    if (d->allreduce(d->allreduce_user, buf, n, s) != 0) return dec_fail(B200_ERR_CUDA, "all-reduce callback failed");
+    return B200_OK;
+  };
+  const size_t kv_first = (size_t)seq * c.max_seq * d->kvl;  // first token row of this sequence's cache
+  const size_t kv_row = (size_t)c.head_dim * (i8 ? 1 : 2);
+  DEC_CUDA(launch_embed(f.tokens.as<int32_t>(), d->embed_table.as<int8_t>(), d->embed_scales.as<float>(), rows, c.d_model,
+                        c.embed_scale, f.h.as<float>(), f.positions.as<int32_t>(), f.attn_len.as<int32_t>(), nullptr, s));
+  for (int l = 0; l < c.n_layers; ++l) {
+    Layer& L = *d->layers[l];
+    void* kc = L.k_cache.as<uint8_t>() + kv_first * kv_row;
+    void* vc = L.v_cache.as<uint8_t>() + kv_first * kv_row;
+    float* ks = i8 ? L.k_scale.as<float>() + kv_first : nullptr;
+    float* vs = i8 ? L.v_scale.as<float>() + kv_first : nullptr;
+    DEC_CUDA(launch_add_norm_quant(f.h.as<float>(), l == 0 ? nullptr : f.down_out.as<float>(), L.norm1.as<float>(), rows, c.d_model,
+                                   c.rms_eps, m_alloc, f.q_d.as<int8_t>(), f.sc_d.as<float>(), f.zp_d.as<int32_t>(), nullptr, s));
+    DEC_CUDA(run_fc(d, L.qkv, rows, f.q_d.as<int8_t>(), f.sc_d.as<float>(), f.zp_d.as<int32_t>(), f.qkv.as<float>()));
+    DEC_CUDA(launch_rope_cache(f.qkv.as<float>(), rows, d->hl, d->kvl, c.head_dim, c.rope_base, f.positions.as<int32_t>(),
+                               c.max_seq, f.q.as<float>(), kc, vc, ks, vs, i8, 1, s));
+    SdpaParams sp;
+    memset(&sp, 0, sizeof(sp));
+    sp.q = f.q.p;
+    sp.k = kc;
+    sp.v = vc;
+    sp.k_scale = ks;
+    sp.v_scale = vs;
+    sp.shared_kv = 1;
+    sp.lengths = f.attn_len.as<int32_t>();
+    sp.q_tiled_out = f.q_a.as<int8_t>();
+    sp.out_scales = f.sc_a.as<float>();
+    sp.out_zps = f.zp_a.as<int32_t>();
+    sp.m_alloc = m_alloc;
+    sp.b = rows;
+    sp.n = d->hl;
+    sp.nkv = d->kvl;
+    sp.h = c.head_dim;
+    sp.s_max = c.max_seq;
+    sp.q_dtype = 1;
+    sp.kv_dtype = i8 ? 1 : 0;
+    sp.scale = 1.0f / sqrtf((float)c.head_dim);
+    sp.ws = f.sdpa_ws.as<float>();
+    sp.ws_bytes = f.sdpa_ws.bytes;
+    sp.status = d->zero_ws.as<int>();
+    DEC_CUDA(launch_sdpa_decode(sp, s));
+    DEC_CUDA(run_fc(d, L.o, rows, f.q_a.as<int8_t>(), f.sc_a.as<float>(), f.zp_a.as<int32_t>(), f.proj.as<float>()));
+    if (int rc = reduce(f.proj.as<float>(), (size_t)rows * c.d_model)) return rc;
+    DEC_CUDA(launch_add_norm_quant(f.h.as<float>(), f.proj.as<float>(), L.norm2.as<float>(), rows, c.d_model, c.rms_eps, m_alloc,
+                                   f.q_d.as<int8_t>(), f.sc_d.as<float>(), f.zp_d.as<int32_t>(), nullptr, s));
+    DEC_CUDA(run_fc(d, L.gate_up, rows, f.q_d.as<int8_t>(), f.sc_d.as<float>(), f.zp_d.as<int32_t>(), f.gate_up.as<float>()));
+    DEC_CUDA(launch_geglu_quant(f.gate_up.as<float>(), rows, d->fl, m_alloc, f.q_f.as<int8_t>(), f.sc_f.as<float>(),
+                                f.zp_f.as<int32_t>(), s));
+    DEC_CUDA(run_fc(d, L.down, rows, f.q_f.as<int8_t>(), f.sc_f.as<float>(), f.zp_f.as<int32_t>(), f.down_out.as<float>()));
+    if (int rc = reduce(f.down_out.as<float>(), (size_t)rows * c.d_model)) return rc;
+  }
+  if (!pick) return B200_OK;
+  // the last prompt token predicts the first generated one: one row through the head
+  const size_t last = (size_t)(rows - 1) * c.d_model;
+  DEC_CUDA(launch_add_norm_quant(f.h.as<float>() + last, f.down_out.as<float>() + last, d->final_norm.as<float>(), 1, c.d_model,
+                                 c.rms_eps, m_alloc_for(1), f.q_d.as<int8_t>(), f.sc_d.as<float>(), f.zp_d.as<int32_t>(), nullptr, s));
+  float* logits = d->logits.as<float>();
+  DEC_CUDA(run_fc(d, d->lm_head, 1, f.q_d.as<int8_t>(), f.sc_d.as<float>(), f.zp_d.as<int32_t>(), logits));
+  int32_t* scratch_pos = f.attn_len.as<int32_t>();  // the arg-max advances a position: not the sequence's, set by the caller
+  if (!tp) {
+    DEC_CUDA(launch_argmax(logits, 1, c.vocab, 0, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
+                           d->next_tokens.as<int32_t>() + seq, scratch_pos, c.max_seq, nullptr, s));
+    return B200_OK;
+  }
+  // every rank proposes the best of its vocabulary rows through the sum collective (zeroed table, own slot)
+  float2* table = d->gather.as<float2>();
+  DEC_CUDA(cudaMemsetAsync(table, 0, sizeof(float2) * c.tp_size * c.max_batch, s));
+  DEC_CUDA(launch_argmax(logits, 1, d->vl, c.tp_rank * d->vl, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(), nullptr, nullptr,
+                         c.max_seq, table + (size_t)c.tp_rank * c.max_batch, s));
+  if (int rc = reduce(reinterpret_cast<float*>(table), (size_t)2 * c.tp_size * c.max_batch)) return rc;
+  const float2* pairs[kMaxTpRanks] = {nullptr};
+  for (int j = 0; j < c.tp_size; ++j) pairs[j] = table + (size_t)j * c.max_batch;
+  DEC_CUDA(launch_argmax_pick(pairs, c.tp_size, 1, d->next_tokens.as<int32_t>() + seq, scratch_pos, c.max_seq, nullptr, s));
   return B200_OK;
 }
 
@@ -761,6 +896,57 @@ int b200_decoder_step(b200_decoder* d, const int32_t* h_tokens, int batch, int32
     DEC_CUDA(cudaMemcpy(&status, d->zero_ws.p, sizeof(int), cudaMemcpyDeviceToHost));
     if (status != 0) return dec_fail(B200_ERR_KERNEL_TIMEOUT, "b200_decoder_step: a device-side wait ran out");
   }
+  return B200_OK;
+}
+
+int b200_decoder_prefill(b200_decoder* d, int seq, const int32_t* h_tokens, int n_tokens, int32_t* h_next_token) {
+  if (!d || !h_tokens || seq < 0 || seq >= d->cfg.max_batch || n_tokens <= 0)
+    return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_prefill: bad argument");
+  if (d->lm_head.n == 0) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_prefill: weights not set");
+  const b200_decoder_config& c = d->cfg;
+  if (c.tp_size > 1 && !d->allreduce)
+    return dec_fail(B200_ERR_UNSUPPORTED, "b200_decoder_prefill: a tensor-parallel prompt pass sums through the all-reduce (b200_decoder_init_nccl or b200_decoder_set_allreduce)");
+  for (int i = 0; i < n_tokens; ++i)
+    if (h_tokens[i] < 0 || h_tokens[i] >= c.vocab) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_prefill: token id out of range");
+  int rc = ensure_prefill_bufs(d);
+  if (rc) return rc;
+  int32_t start = 0;
+  DEC_CUDA(cudaMemcpyAsync(&start, d->positions.as<int32_t>() + seq, sizeof(int32_t), cudaMemcpyDeviceToHost, d->stream));
+  DEC_CUDA(cudaStreamSynchronize(d->stream));
+  if ((long long)start + n_tokens > c.max_seq) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_prefill: the prompt does not fit the cache");
+  PrefillBufs& f = *d->pf;
+  // the per-step launch count and the GEMV trace describe decode steps: a prompt pass leaves them alone
+  const int saved_launches = d->launches, saved_trace = d->trace_next;
+  d->trace_next = kTraceSlots;
+  struct Restore {
+    b200_decoder* d;
+    int launches, trace;
+    ~Restore() {
+      d->launches = launches;
+      d->trace_next = trace;
+    }
+  } restore{d, saved_launches, saved_trace};
+  for (int done = 0; done < n_tokens;) {
+    const int rows = std::min(f.rows, n_tokens - done);
+    for (int i = 0; i < rows; ++i) {
+      f.h_stage[i] = h_tokens[done + i];
+      f.h_stage[f.rows + i] = start + done + i;
+    }
+    DEC_CUDA(cudaMemcpyAsync(f.tokens.p, f.h_stage, sizeof(int32_t) * rows, cudaMemcpyHostToDevice, d->stream));
+    DEC_CUDA(cudaMemcpyAsync(f.positions.p, f.h_stage + f.rows, sizeof(int32_t) * rows, cudaMemcpyHostToDevice, d->stream));
+    rc = enqueue_prefill_chunk(d, seq, rows, done + rows == n_tokens);
+    if (rc) return rc;
+    done += rows;
+    DEC_CUDA(cudaStreamSynchronize(d->stream));  // the staging buffer is reused by the next chunk
+  }
+  const int32_t end = start + n_tokens;
+  DEC_CUDA(cudaMemcpy(d->positions.as<int32_t>() + seq, &end, sizeof(int32_t), cudaMemcpyHostToDevice));
+  int32_t next = 0;
+  DEC_CUDA(cudaMemcpy(&next, d->next_tokens.as<int32_t>() + seq, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  if (h_next_token) *h_next_token = next;
+  int status = 0;
+  DEC_CUDA(cudaMemcpy(&status, d->zero_ws.p, sizeof(int), cudaMemcpyDeviceToHost));
+  if (status != 0) return dec_fail(B200_ERR_KERNEL_TIMEOUT, "b200_decoder_prefill: a device-side wait ran out");
   return B200_OK;
 }
 

@@ -224,12 +224,13 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
 }
 
 // Rotary embedding of q and k from the fused qkv projection output, and the
-// cache append. grid (b, heads + kv_heads + kv_heads), head_dim / 2 threads.
+// cache append. grid (b, heads + kv_heads + kv_heads), head_dim / 2 threads. Row b appends to the
+// cache of sequence b, or, with one_sequence (a prompt pass), every row to the cache passed in.
 template <bool KV_I8>
 __global__ void rope_cache_kernel(const float* __restrict__ qkv, int heads, int kv_heads, int head_dim,
                                   float rope_base, const int32_t* __restrict__ positions, int max_seq,
                                   float* __restrict__ q_out, void* __restrict__ k_cache, void* __restrict__ v_cache,
-                                  float* __restrict__ k_scale, float* __restrict__ v_scale) {
+                                  float* __restrict__ k_scale, float* __restrict__ v_scale, int one_sequence) {
   __shared__ float red[32];
   pdl_enter();
   const int b = blockIdx.x, slot = blockIdx.y, i = threadIdx.x, half = head_dim / 2;
@@ -253,7 +254,7 @@ __global__ void rope_cache_kernel(const float* __restrict__ qkv, int heads, int 
   }
   const int kvh = is_v ? slot - heads - kv_heads : slot - heads;
   if (pos >= max_seq) return;  // cache full: the step is ignored for this sequence
-  const size_t tok = ((size_t)b * max_seq + pos) * kv_heads + kvh;
+  const size_t tok = ((size_t)(one_sequence ? 0 : b) * max_seq + pos) * kv_heads + kvh;
   if constexpr (KV_I8) {
     // symmetric per token and kv head: scale = max|row| / 127
     float amax = fmaxf(fabsf(x1), fabsf(x2));
@@ -397,14 +398,14 @@ cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_all
 
 cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, float rope_base,
                               const int32_t* positions, int max_seq, float* q_out, void* k_cache, void* v_cache,
-                              float* k_scale, float* v_scale, int kv_int8, cudaStream_t s) {
+                              float* k_scale, float* v_scale, int kv_int8, int one_sequence, cudaStream_t s) {
   dim3 grid(batch, heads + 2 * kv_heads);
   if (kv_int8) {
     return launch_chained(rope_cache_kernel<true>, grid, dim3(head_dim / 2), 0, s, qkv, heads, kv_heads, head_dim, rope_base,
-                          positions, max_seq, q_out, k_cache, v_cache, k_scale, v_scale);
+                          positions, max_seq, q_out, k_cache, v_cache, k_scale, v_scale, one_sequence);
   }
   return launch_chained(rope_cache_kernel<false>, grid, dim3(head_dim / 2), 0, s, qkv, heads, kv_heads, head_dim, rope_base,
-                        positions, max_seq, q_out, k_cache, v_cache, k_scale, v_scale);
+                        positions, max_seq, q_out, k_cache, v_cache, k_scale, v_scale, one_sequence);
 }
 
 cudaError_t launch_argmax(const float* logits, int batch, int n, int idx_offset, float* part_val, int32_t* part_idx,

@@ -37,9 +37,11 @@ cudaError_t launch_add_norm_quant(float* h, const float* delta, const float* gai
                                   cudaStream_t s);
 cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_alloc, int8_t* q_tiled, float* scales,
                                int32_t* zps, cudaStream_t s);
+// one_sequence: the rows are consecutive tokens of ONE sequence (a prompt pass) and k_cache / v_cache /
+// k_scale / v_scale point at that sequence's cache; otherwise row b belongs to sequence b.
 cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, float rope_base,
                               const int32_t* positions, int max_seq, float* q_out, void* k_cache, void* v_cache,
-                              float* k_scale, float* v_scale, int kv_int8, cudaStream_t s);
+                              float* k_scale, float* v_scale, int kv_int8, int one_sequence, cudaStream_t s);
 // First-index argmax of each row; advances positions. idx_offset is added to the winning column.
 // With pair_out the winner goes to pair_out[b] = {value, index as float} instead, and neither
 // next_tokens nor positions change (launch_argmax_pick finishes the job across ranks).

@@ -137,6 +137,9 @@ struct SdpaParams {
   int m_alloc;
   size_t ws_bytes;
   int* status;
+  // 1: every row of the batch attends over the SAME cache (k / v / scales of one sequence, [s_max, nkv, h]),
+  // row b up to lengths[b] tokens: a prompt pass, whose rows are consecutive tokens of one sequence
+  int shared_kv;
 };
 // One decode step of a decoder layer's attention in one launch (multi-query attention, at most
 // eight query heads): rotary embedding of q and of the new key, cache append, attention over the

@@ -159,10 +159,11 @@ struct WarpAttention {
   static __device__ __forceinline__ Rows cache_rows(const SdpaParams& p, int b, int kvh) {
     Rows r;
     r.stride = (size_t)p.nkv * H * kv_elem_bytes<KV>();
-    r.k = static_cast<const uint8_t*>(p.k) + ((size_t)b * p.s_max * p.nkv + kvh) * H * kv_elem_bytes<KV>();
-    r.v = static_cast<const uint8_t*>(p.v) + ((size_t)b * p.s_max * p.nkv + kvh) * H * kv_elem_bytes<KV>();
-    r.k_scale = p.k_scale ? p.k_scale + (size_t)b * p.s_max * p.nkv + kvh : nullptr;
-    r.v_scale = p.v_scale ? p.v_scale + (size_t)b * p.s_max * p.nkv + kvh : nullptr;
+    const size_t first = (p.shared_kv ? (size_t)0 : (size_t)b * p.s_max) * p.nkv + kvh;
+    r.k = static_cast<const uint8_t*>(p.k) + first * H * kv_elem_bytes<KV>();
+    r.v = static_cast<const uint8_t*>(p.v) + first * H * kv_elem_bytes<KV>();
+    r.k_scale = p.k_scale ? p.k_scale + first : nullptr;
+    r.v_scale = p.v_scale ? p.v_scale + first : nullptr;
     r.scale_stride = p.nkv;
     return r;
   }
@@ -897,10 +898,11 @@ __global__ void sdpa_decode_generic_kernel(const SdpaParams p) {
   }
   __syncwarp();
   auto kv_at = [&](const void* basep, const float* sc, int s, int d) -> float {
-    const size_t idx = (((size_t)b * p.s_max + s) * p.nkv + kvh) * h + d;
+    const size_t tok = ((size_t)(p.shared_kv ? 0 : b) * p.s_max + s) * p.nkv + kvh;
+    const size_t idx = tok * h + d;
     if (KV == kKvF16) return __half2float(static_cast<const __half*>(basep)[idx]);
     if (KV == kKvF32) return static_cast<const float*>(basep)[idx];
-    return (float)static_cast<const int8_t*>(basep)[idx] * sc[((size_t)b * p.s_max + s) * p.nkv + kvh];
+    return (float)static_cast<const int8_t*>(basep)[idx] * sc[tok];
   };
   float mx = -CUDART_INF_F;
   for (int s = lane; s < len; s += 32) {

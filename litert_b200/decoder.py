@@ -93,6 +93,7 @@ class Decoder:
             kv_dtype=1 if kv_dtype == "i8" else 0, tp_size=tp_size, tp_rank=tp_rank)
         self.config_struct = c
         self.rms_eps, self.rope_base, self.max_seq, self.max_batch = rms_eps, rope_base, max_seq, max_batch
+        self._batch = None
         self.handle = ctypes.c_void_p()
         with torch.cuda.device(self.device):
             self.stream = torch.cuda.Stream()
@@ -161,9 +162,22 @@ class Decoder:
                                               None if logits is None else ctypes.c_void_p(logits.data_ptr())))
         return nxt, logits
 
-    def run(self, first_tokens, steps, fetch=True):
+    def prefill(self, tokens, seq=0):
+        """Prompt pass of sequence `seq` over the host int32 array `tokens`: fills the sequence's cache
+        behind what is already there and returns the first generated token (also kept on the device,
+        where run(None, ...) picks it up)."""
+        tok = np.ascontiguousarray(tokens, np.int32).reshape(-1)
+        nxt = ctypes.c_int32()
+        with torch.cuda.device(self.device):
+            _check(self.lib.b200_decoder_prefill(self.handle, int(seq), tok.ctypes.data_as(ctypes.c_void_p), tok.size,
+                                                 ctypes.byref(nxt)))
+        return int(nxt.value)
+
+    def run(self, first_tokens, steps, fetch=True, batch=None):
+        """`steps` greedy steps on the device. first_tokens None: continue from the tokens the last step
+        or prompt pass left there (give `batch` when no step has run yet)."""
         tok = None if first_tokens is None else np.ascontiguousarray(first_tokens, np.int32)
-        batch = self._batch if tok is None else tok.size
+        batch = (batch or self._batch) if tok is None else tok.size
         self._batch = batch
         nxt = np.empty(batch, np.int32) if fetch else None
         with torch.cuda.device(self.device):

@@ -116,3 +116,90 @@ def test_decoder_graph_path_equals_eager_path_and_is_repeatable():
     assert np.array_equal(a, b) and np.array_equal(a, c)
     assert d.launches_per_step > 0
     d.close()
+
+
+@pytest.mark.parametrize("kv_dtype,tol", [("f16", 8e-2), ("i8", 2.5e-1)])
+def test_prefill_matches_token_by_token_cpu_graph(oracle, kv_dtype, tol):
+    """A prompt pass (all prompt rows through each projection as one GEMM, causal attention over the
+    rows just appended) must leave the caches and predict the token that the CPU graph reaches by
+    stepping the same prompt one token at a time; the decode steps after it are compared as above."""
+    from litert_b200 import decoder as dec
+
+    cfg = dict(dec.TINY)
+    batch, prompt_len, max_seq = 2, 45, 64
+    weights = dec.make_weights(cfg, seed=21)
+    gpu = dec.Decoder(cfg, max_seq=max_seq, max_batch=batch, weights=weights, kv_dtype=kv_dtype)
+    ref = oracle.DecoderRef(cfg, _host(weights), batch, max_seq, fast=True)
+    prompts = np.random.default_rng(8).integers(0, cfg["vocab"], (batch, prompt_len)).astype(np.int32)
+    for t in range(prompt_len):
+        nxt_r, logits_r = ref.step(prompts[:, t], want_logits=True)
+    first = np.array([gpu.prefill(prompts[b], seq=b) for b in range(batch)], np.int32)
+    top2 = np.sort(logits_r, axis=-1)[:, -2:]
+    spread = logits_r.max(axis=-1) - logits_r.min(axis=-1)
+    clear = (top2[:, 1] - top2[:, 0]) > 0.1 * spread
+    assert np.array_equal(first[clear], nxt_r[clear])
+    tokens = nxt_r
+    for s in range(4):
+        _, logits_g = gpu.step(tokens, want_logits=True)
+        nxt_r, logits_r = ref.step(tokens, want_logits=True)
+        err = np.linalg.norm(logits_g.cpu().numpy() - logits_r) / np.linalg.norm(logits_r)
+        assert err <= tol, (s, err)
+        tokens = nxt_r
+    gpu.close()
+    ref.close()
+
+
+@pytest.mark.parametrize("kv_dtype", ["f16", "i8"])
+@pytest.mark.parametrize("split", [(530,), (300, 230), (1, 129, 400)])
+def test_prefill_equals_stepping_on_the_device(kv_dtype, split):
+    """Prompts longer than one 512-row chunk, and prompts fed in several calls (each behind the
+    tokens already cached), against the same decoder fed one token per step. The integer GEMMs are
+    exact in either form; attention sums in a different order, hence a bound and not equality."""
+    from litert_b200 import decoder as dec
+
+    cfg = dict(dec.TINY)
+    total, max_seq = sum(split), 560
+    weights = dec.make_weights(cfg, seed=5)
+    prompt = np.random.default_rng(11).integers(0, cfg["vocab"], total).astype(np.int32)
+    stepped = dec.Decoder(cfg, max_seq=max_seq, max_batch=2, weights=weights, kv_dtype=kv_dtype)
+    for t in range(total):
+        nxt_s, logits_s = stepped.step(prompt[t:t + 1], want_logits=(t == total - 1))
+    filled = dec.Decoder(cfg, max_seq=max_seq, max_batch=2, weights=weights, kv_dtype=kv_dtype)
+    filled.set_positions(np.array([7, 0], np.int32))  # another sequence's state must not matter
+    done = 0
+    for part in split:
+        first = filled.prefill(prompt[done:done + part], seq=1)
+        done += part
+    # the stepped decoder holds the prompt in sequence 0, the filled one in sequence 1
+    ls = logits_s.cpu().numpy()[0]
+    top2 = np.sort(ls)[-2:]
+    if top2[1] - top2[0] > 0.05 * (ls.max() - ls.min()):
+        assert first == int(nxt_s[0])
+    tok = nxt_s[:1]
+    for s in range(3):
+        nxt_s, logits_s = stepped.step(tok, want_logits=True)
+        _, logits_f = filled.step(np.array([3, tok[0]], np.int32), want_logits=True)
+        a, b = logits_f.cpu().numpy()[1], logits_s.cpu().numpy()[0]
+        err = np.linalg.norm(a - b) / np.linalg.norm(b)
+        assert err <= 3e-2, (s, err)
+        tok = nxt_s[:1]
+    stepped.close()
+    filled.close()
+
+
+def test_prefill_rejects_what_does_not_fit():
+    from litert_b200 import decoder as dec
+    from litert_b200._lib import B200Error
+
+    cfg = dict(dec.TINY)
+    d = dec.Decoder(cfg, max_seq=32, max_batch=1, weights=dec.make_weights(cfg, seed=1))
+    with pytest.raises(B200Error):
+        d.prefill(np.zeros(33, np.int32))
+    with pytest.raises(B200Error):
+        d.prefill(np.array([cfg["vocab"]], np.int32))
+    with pytest.raises(B200Error):
+        d.prefill(np.zeros(4, np.int32), seq=1)
+    d.prefill(np.zeros(30, np.int32))
+    with pytest.raises(B200Error):
+        d.prefill(np.zeros(3, np.int32))  # 30 cached + 3 > 32
+    d.close()
