@@ -194,7 +194,7 @@ def weight_bytes(cfg):
 
 def workload_config(args, cfg):
     return {"workload": f"config 5: Gemma-2B-shaped decoder, decode step, batch {args.batch} per GPU, "
-                        f"{args.context}-token KV context" if args.model == "gemma2b" else f"tiny decoder, batch {args.batch}",
+                        f"{args.context}-token prompt pass then decode" if args.model == "gemma2b" else f"tiny decoder, batch {args.batch}",
             "layers": cfg["n_layers"], "d_model": cfg["d_model"], "heads": cfg["n_heads"], "kv_heads": cfg["n_kv_heads"],
             "head_dim": cfg["head_dim"], "d_ff": cfg["d_ff"], "vocab": cfg["vocab"], "batch_per_gpu": args.batch,
             "context": args.context, "kv_cache": args.kv, "parallelism": f"replica x{args.gpus} (independent batches)",
@@ -260,10 +260,27 @@ def run_ours(args):
     d = dec.Decoder(cfg, max_seq=max_seq, max_batch=max(args.batch, side_batch), kv_dtype=args.kv, seed=1005 + rank,
                     device=f"cuda:{local}")
     rng = np.random.default_rng(1005 + rank)
-    first = rng.integers(0, cfg["vocab"], args.batch).astype(np.int32)
-    # prefill stand-in: fill the cache by decoding `context` tokens (untimed)
-    d.run(first, args.context, fetch=True)
     stream = d.stream
+
+    def prompt_pass(batch):
+        """Prompt pass of `context` random token ids for each of `batch` sequences (one call per sequence,
+        host tokens in, first generated token out); returns prompt tokens per second."""
+        prompts = rng.integers(0, cfg["vocab"], (batch, args.context)).astype(np.int32)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for b in range(batch):
+            d.prefill(prompts[b], seq=b)
+        torch.cuda.synchronize()
+        return batch * args.context / (time.perf_counter() - t0)
+
+    prefill = None
+    if args.context > 0:
+        prompt_pass(1)  # untimed: scratch allocation and one-time kernel setup at the timed shapes
+        d.reset()
+        prefill = {"tokens_per_s_per_gpu": prompt_pass(args.batch), "prompt_tokens": args.context, "sequences": args.batch,
+                   "timing": "host clock around b200_decoder_prefill per sequence (host token ids in, first token out)"}
+    else:
+        d.run(rng.integers(0, cfg["vocab"], args.batch).astype(np.int32), 1, fetch=True)
 
     def barrier():
         torch.cuda.synchronize()
@@ -272,7 +289,7 @@ def run_ours(args):
             torch.cuda.synchronize()
 
     # ---- device-resident timing: K steps of the captured graph, tokens fed back on the device
-    d.run(None, args.warmup, fetch=True)
+    d.run(None, args.warmup, fetch=True, batch=args.batch)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -300,11 +317,16 @@ def run_ours(args):
     # ---- the dominant kernel alone: the step's GEMV launches replayed back to back as one graph
     gemv_ms, gemv_launches = d.time_gemv(args.batch, reps=max(8, min(64, args.steps)))
 
-    # ---- the other batch size of the workload, same decoder (cache depth declared, rows hold zeros)
+    # ---- the other batch size of the workload, same decoder, its own prompt pass
     side = None
+    side_prefill = None
     if side_batch > 0:
-        d.set_positions(np.full(side_batch, args.context, np.int32))
-        d.run(rng.integers(0, cfg["vocab"], side_batch).astype(np.int32), max(3, args.warmup), fetch=True)
+        d.reset()
+        if args.context > 0:
+            side_prefill = prompt_pass(side_batch)
+            d.run(None, max(3, args.warmup), fetch=True, batch=side_batch)
+        else:
+            d.run(rng.integers(0, cfg["vocab"], side_batch).astype(np.int32), max(3, args.warmup), fetch=True)
         barrier()
         s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(stream):
@@ -316,7 +338,8 @@ def run_ours(args):
         side_gemv_ms, _ = d.time_gemv(side_batch, reps=8)
         side = {"batch_per_gpu": side_batch, "tokens_per_s_per_gpu": side_batch / (side_ms * 1e-3),
                 "ms_per_step": side_ms, "gemv_ms_per_step": side_gemv_ms,
-                "gemv_gbs": weight_bytes(cfg) / (side_gemv_ms * 1e-3) / 1e9}
+                "gemv_gbs": weight_bytes(cfg) / (side_gemv_ms * 1e-3) / 1e9,
+                "prefill_tokens_per_s_per_gpu": side_prefill}
 
     times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -360,6 +383,11 @@ def run_ours(args):
         }
         if side:
             line["side_batch"] = side
+        if prefill:
+            # 2 int8 operations per weight and prompt token (the LM head runs for the last token only)
+            ops = 2.0 * (wbytes - cfg["vocab"] * cfg["d_model"])
+            prefill["int8_pops"] = prefill["tokens_per_s_per_gpu"] * ops / 1e15
+            line["prefill"] = prefill
         try:
             if world > 1:
                 raise RuntimeError("timed at --gpus 1 only")

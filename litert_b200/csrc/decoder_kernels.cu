@@ -79,6 +79,10 @@ __global__ void __launch_bounds__(kRowThreads) embed_kernel(const int32_t* __res
   if (threadIdx.x == 0) attn_len[b] = positions[b] + 1;
 }
 
+// Up to this many rows a glue kernel is one link of a latency chain (widest blocks, dry run, a cluster
+// per row); above it, a throughput kernel (several rows per SM, one pass).
+constexpr int kLatencyRows = 32;
+
 // h += delta (optional); x = h * rsqrt(mean(h^2) + eps) * gain; quantize x.
 __global__ void __launch_bounds__(kNormThreads) add_norm_quant_kernel(float* __restrict__ h,
                                                                      const float* __restrict__ delta,
@@ -86,7 +90,8 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_kernel(float* __r
                                                                      float eps, int m_alloc,
                                                                      int8_t* __restrict__ q_tiled,
                                                                      float* __restrict__ scales,
-                                                                     int32_t* __restrict__ zps, TpExchange xch) {
+                                                                     int32_t* __restrict__ zps, TpExchange xch,
+                                                                     int first_pass) {
   extern __shared__ float xs[];
   __shared__ float red[32];
   pdl_launch_dependents();
@@ -96,9 +101,10 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_kernel(float* __r
   // Two passes over the same code. The first runs while the producing kernel is still busy, on
   // whatever the inputs hold, and stores nothing: it only pulls the instructions (and the gain
   // vector) into the caches, which is most of what this short kernel otherwise waits for. The
-  // second, after the dependency wait, is the real one.
+  // second, after the dependency wait, is the real one. (first_pass 1: no dry run -- with hundreds of
+  // rows the kernel is no longer a latency chain and the dry run would only double its work.)
 #pragma unroll 1
-  for (int pass = 0; pass < 2; ++pass) {
+  for (int pass = first_pass; pass < 2; ++pass) {
     const bool live = pass == 1;
     if (live) {
       pdl_wait();
@@ -149,9 +155,11 @@ __device__ __forceinline__ float gelu_tanh(float v) {
 // A row (16384 elements at the benchmark's size) is spread over a cluster of kGegluCluster CTAs:
 // each computes its slice into shared memory with its local min / max, the CTAs exchange those
 // through distributed shared memory, and each then quantizes its slice with the row's parameters.
+// With many rows (a prompt chunk) one CTA takes a whole row (CL = 1) and there is no dry run.
 constexpr int kGegluCluster = 8;
 constexpr int kGegluThreads = 512;
 
+template <int CL>
 __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float* __restrict__ gate_up, int f, int f_pad,
                                                                     int per_cta, int m_alloc,
                                                                     int8_t* __restrict__ q_tiled,
@@ -164,24 +172,40 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
   __shared__ float s_inv;
   __shared__ int s_zp, s_zero;
   cg::cluster_group cluster = cg::this_cluster();
-  const int rank = (int)cluster.block_rank();
-  const int b = blockIdx.x / kGegluCluster;
+  const int rank = CL > 1 ? (int)cluster.block_rank() : 0;
+  const int b = blockIdx.x / CL;
   pdl_launch_dependents();
   const float* g = gate_up + (size_t)b * 2 * f;
   const float* u = g + f;
   const int lo = rank * per_cta, hi = min(f, lo + per_cta);
+  const bool vec = (f & 3) == 0;  // rows and slices then start on 16-byte boundaries
   // two passes over the same code: a dry run that warms the instruction caches while the producing
   // kernel is still busy (nothing stored), then the real one after the dependency wait
 #pragma unroll 1
-  for (int pass = 0; pass < 2; ++pass) {
+  for (int pass = CL > 1 ? 0 : 1; pass < 2; ++pass) {
     const bool live = pass == 1;
     if (live) pdl_wait();
     float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-      const float v = __fmul_rn(gelu_tanh(__ldcg(g + i)), __ldcg(u + i));  // past L1: see add_norm_quant_kernel
-      xs[i - lo] = v;
-      mn = fminf(mn, v);
-      mx = fmaxf(mx, v);
+    if (vec) {
+      for (int i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
+        const float4 gv = __ldcg(reinterpret_cast<const float4*>(g + i));  // past L1: see add_norm_quant_kernel
+        const float4 uv = __ldcg(reinterpret_cast<const float4*>(u + i));
+        float4 v;
+        v.x = __fmul_rn(gelu_tanh(gv.x), uv.x);
+        v.y = __fmul_rn(gelu_tanh(gv.y), uv.y);
+        v.z = __fmul_rn(gelu_tanh(gv.z), uv.z);
+        v.w = __fmul_rn(gelu_tanh(gv.w), uv.w);
+        *reinterpret_cast<float4*>(xs + (i - lo)) = v;
+        mn = fminf(fminf(mn, fminf(v.x, v.y)), fminf(v.z, v.w));
+        mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+      }
+    } else {
+      for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = __fmul_rn(gelu_tanh(__ldcg(g + i)), __ldcg(u + i));
+        xs[i - lo] = v;
+        mn = fminf(mn, v);
+        mx = fmaxf(mx, v);
+      }
     }
     mn = block_reduce(mn, [](float a, float c) { return fminf(a, c); }, mn, red);
     mx = block_reduce(mx, [](float a, float c) { return fmaxf(a, c); }, mx, red);
@@ -189,10 +213,10 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
       s_minmax[0] = mn;
       s_minmax[1] = mx;
     }
-    cluster.sync();
+    if (CL > 1) cluster.sync();
     if (threadIdx.x == 0) {
-      float rmn = 3.402823466e+38f, rmx = -3.402823466e+38f;
-      for (int r = 0; r < kGegluCluster; ++r) {
+      float rmn = mn, rmx = mx;
+      for (int r = 0; r < CL && CL > 1; ++r) {
         const float* remote = cluster.map_shared_rank(s_minmax, r);
         rmn = fminf(rmn, remote[0]);
         rmx = fmaxf(rmx, remote[1]);
@@ -219,7 +243,7 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
         if (k4 + e < f && !zero) word |= quantize_value(xs[k4 + e - lo], inv, zpf, true) << (8 * e);
       if (live) *reinterpret_cast<uint32_t*>(q_tiled + q_tiled_offset(b, k4, m_alloc)) = word;
     }
-    cluster.sync();  // neighbours are done with this CTA's min / max (and no CTA exits before that)
+    if (CL > 1) cluster.sync();  // neighbours are done with this CTA's min / max (and no CTA exits before that)
   }
 }
 
@@ -372,28 +396,42 @@ cudaError_t launch_add_norm_quant(float* h, const float* delta, const float* gai
                                   cudaStream_t s) {
   const int d_pad = (d + 127) / 128 * 128;
   const TpExchange x = xch ? *xch : TpExchange();
-  return launch_chained(add_norm_quant_kernel, dim3(batch), dim3(kNormThreads), sizeof(float) * d, s, h, delta, gain, d, d_pad,
-                        eps, m_alloc, q_tiled, scales, zps, x);
+  // a decode step's few rows: the widest block and a dry run; a prompt chunk's many rows: several rows per SM
+  const bool many = batch > kLatencyRows;
+  return launch_chained(add_norm_quant_kernel, dim3(batch), dim3(many ? 256 : kNormThreads), sizeof(float) * d, s, h, delta, gain,
+                        d, d_pad, eps, m_alloc, q_tiled, scales, zps, x, many ? 1 : 0);
 }
 
 cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_alloc, int8_t* q_tiled, float* scales,
                                int32_t* zps, cudaStream_t s) {
   const int f_pad = (f + 127) / 128 * 128;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (batch > kLatencyRows && sizeof(float) * f_pad <= 160 * 1024) {
+    // many rows: a CTA per row
+    const size_t smem = sizeof(float) * f_pad;
+    static bool configured1[64] = {false};
+    if (!configured1[dev] && smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(geglu_quant_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (e != cudaSuccess) return e;
+      configured1[dev] = true;
+    }
+    return launch_chained(geglu_quant_kernel<1>, dim3(batch), dim3(kGegluThreads), smem, s, gate_up, f, f_pad, f_pad, m_alloc,
+                          q_tiled, scales, zps);
+  }
   // slice per CTA: a multiple of 128 elements so that slices tile the padded row exactly
   const int per_cta = ((f_pad / 128 + kGegluCluster - 1) / kGegluCluster) * 128;
   const size_t smem = sizeof(float) * per_cta;
   if (smem > 160 * 1024) return cudaErrorInvalidValue;
   static bool configured[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
   if (!configured[dev] && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(geglu_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(geglu_quant_kernel<kGegluCluster>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  return launch_chained_cluster(geglu_quant_kernel, dim3(batch * kGegluCluster), dim3(kGegluThreads), smem, kGegluCluster,
-                                s, gate_up, f, f_pad, per_cta, m_alloc, q_tiled, scales, zps);
+  return launch_chained_cluster(geglu_quant_kernel<kGegluCluster>, dim3(batch * kGegluCluster), dim3(kGegluThreads), smem,
+                                kGegluCluster, s, gate_up, f, f_pad, per_cta, m_alloc, q_tiled, scales, zps);
 }
 
 cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, float rope_base,

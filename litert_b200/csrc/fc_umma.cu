@@ -49,12 +49,36 @@ struct UmmaShared {
   int32_t in_aux[256];
 };
 
+// Shared-memory budget of a GEMV CTA, by activation rows per pass. For up to 16 rows (NB = 16) a CTA
+// keeps a short ring (4 stages of 18 KB) and two CTAs per SM are launched: three fit, so the next
+// kernel of a programmatically chained sequence gets a CTA onto every SM and fills its ring while
+// this kernel's CTAs are still streaming. Measured on B200 on the batch-1 decode step (18 layers +
+// LM head, 1024-token context): one 180 KB CTA per SM 1.100 ms, one 108 KB CTA 1.070 ms, two 72 KB
+// CTAs 0.97-1.00 ms, three 54 KB CTAs 1.022 ms. With more rows per pass the stages are larger and
+// the deep ring of a single CTA per SM does better (batch 32: 1.667 ms against 1.70 ms).
+#ifndef B200_UMMA_KB16
+#define B200_UMMA_KB16 72
+#endif
+#ifndef B200_CLUSTER_KB16
+#define B200_CLUSTER_KB16 72
+#endif
+#ifndef B200_PER_SM16
+#define B200_PER_SM16 2
+#endif
+template <int NB>
+struct UmmaBudget {
+  static constexpr int kUmmaKB = NB <= 16 ? B200_UMMA_KB16 : (NB >= 64 ? 206 : 200);
+  static constexpr int kClusterKB = NB <= 16 ? B200_CLUSTER_KB16 : 200;
+  static constexpr int kCtasPerSm = NB <= 16 ? B200_PER_SM16 : 1;
+};
+
 template <int NB>
 struct UmmaLayout {
   static constexpr int kQBytes = NB * kTileK8;  // NB/8 row groups x 1 KiB
   static constexpr int kStageBytes = kTileBytes + kQBytes;
-  static constexpr int kStagesRaw = (NB >= 64 ? 206 : 200) * 1024 / kStageBytes;
+  static constexpr int kStagesRaw = UmmaBudget<NB>::kUmmaKB * 1024 / kStageBytes;
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+  static_assert(kStages >= 2, "the ring needs two stages");
   static constexpr int kBarriers = 2 * kStages + 5;
   // without the fused prologue's operand buffer, which the launcher adds (k tiles x kQBytes)
   static constexpr int kOutStageBytes = NB >= 64 ? 2 * 16 * kTileN * 4 : 0;  // two 16-row output blocks
@@ -114,8 +138,10 @@ __device__ __forceinline__ void store_output(const FcParams& p, int m, int n, in
 
 template <int NB, int EPI>
 __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams p, const int m_base_first) {
-  // grid.y = passes of NB activation rows (whole-tile mode only: the stream-K scratch is per grid.x)
+  // grid.y = passes of NB activation rows; the stream-K scratch (slots, counters) is numbered over
+  // the whole grid, so every pass merges its own split tiles
   const int m_base = m_base_first + (int)blockIdx.y * NB;
+  const int cta_base = (int)(blockIdx.y * gridDim.x);
   using L = UmmaLayout<NB>;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
@@ -411,7 +437,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         const int c_first = (int)(((tile_first + 1) * g - 1) / total);
         const int c_last = (int)(((tile_last + 1) * g - 1) / total);
         const int which = (t_begin <= tile_first) ? 1 : 0;
-        int32_t* mine = p.ws_part + (size_t)(blockIdx.x * 2 + which) * kZeroWsSlotInts;
+        int32_t* mine = p.ws_part + (size_t)((cta_base + blockIdx.x) * 2 + which) * kZeroWsSlotInts;
 #pragma unroll 1
         for (int c = 0; c < NB / 16; ++c) {
           if (c * 16 >= m_valid) break;
@@ -430,7 +456,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         named_barrier(1, kEpiThreads);
         if (etid == 0) {
           __threadfence();
-          const int old = atomicAdd(&p.ws_count[c_first], seg_tiles);
+          const int old = atomicAdd(&p.ws_count[cta_base + c_first], seg_tiles);
           sh->last = (old + seg_tiles == p.k_tiles) ? 1 : 0;
         }
         named_barrier(1, kEpiThreads);
@@ -443,7 +469,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
             int32_t v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             for (int c = c_first; c <= c_last; ++c) {
               const int w = (c == c_first) ? 1 : 0;
-              const int32_t* slot = p.ws_part + (size_t)(c * 2 + w) * kZeroWsSlotInts + row_in_tile;
+              const int32_t* slot = p.ws_part + (size_t)((cta_base + c) * 2 + w) * kZeroWsSlotInts + row_in_tile;
 #pragma unroll
               for (int j = 0; j < 8; ++j)
                 if (m0 + j < m_valid) v[j] += __ldcg(slot + (m0 + j) * kTileN);
@@ -456,7 +482,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
                                     sh->in_aux[m0 + j]);
             }
           }
-          if (etid == 0) p.ws_count[c_first] = 0;
+          if (etid == 0) p.ws_count[cta_base + c_first] = 0;
         }
         named_barrier(1, kEpiThreads);  // sh->last is rewritten by the next split tile
       }
@@ -488,8 +514,9 @@ struct ClusterLayout {
   static constexpr int kQBytes = NB * kTileK8;
   static constexpr int kStageBytes = kTileBytes + kQBytes;
   static constexpr int kRedBytes = (kTileN + 8) * NB * 4;  // split x ceil(128 / split) rows x NB columns of int32
-  static constexpr int kStagesRaw = (200 * 1024 - kRedBytes) / kStageBytes;
+  static constexpr int kStagesRaw = (UmmaBudget<NB>::kClusterKB * 1024 - kRedBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+  static_assert(kStages >= 2, "the ring needs two stages");
   static constexpr int kBarriers = 2 * kStages + 2;
   // without the fused prologue's operand buffer, which the launcher adds
   static constexpr int kSmemBytes = kStages * kStageBytes + kRedBytes + kBarriers * 8 + (int)sizeof(UmmaShared) +
@@ -985,26 +1012,32 @@ cudaError_t launch_prefill(const FcParams& p, cudaStream_t s) {
 // reduction; CTAs with one tile fewer finish early and the kernel stays HBM-bound); with fewer,
 // one SM per n tile cannot pull more than ~80 GB/s, so the flat (n tile, k tile) sequence is cut
 // into equal ranges over all SMs (stream-K) and the partials are merged by the last arriver.
-int plan_ctas(FcParams* p, int passes) {
+int plan_ctas(FcParams* p, int passes, int ctas_per_sm) {
   const int sms = device_sm_count();
   const long long total = (long long)p->n_tiles * p->k_tiles;
   int mode = -1;  // -1 auto, 0 stream-K, 1 whole tiles
   if (const char* e = getenv("B200_FC_SPLIT")) mode = atoi(e) ? 0 : 1;  // measurement knob
   int ctas;
-  // several passes of activation rows share one launch: no cross-CTA reduction then
-  if (mode == 1 || passes > 1 || p->force_whole_tiles || (mode < 0 && p->n_tiles * 2 >= sms)) {
+  if (p->split_passes && passes > 1 && mode != 1) {
+    // few n tiles, a long reduction, several passes of activation rows: the SMs are shared out
+    // among the passes and each pass cuts its (n tile, k tile) sequence into equal ranges
+    p->whole_tiles = 0;
+    ctas = (sms < kZeroWsSlots / 2 ? sms : kZeroWsSlots / 2) / passes;
+  } else if (mode == 1 || passes > 1 || p->force_whole_tiles || (mode < 0 && p->n_tiles * 2 >= sms)) {
+    // (several passes otherwise share one launch as whole n tiles: no cross-CTA reduction)
     p->whole_tiles = 1;
-    ctas = p->n_tiles < sms ? p->n_tiles : sms;
+    const int cap = passes > 1 ? sms : sms * ctas_per_sm;
+    ctas = p->n_tiles < cap ? p->n_tiles : cap;
   } else {
     p->whole_tiles = 0;
-    ctas = sms;
+    ctas = sms * ctas_per_sm;
   }
   if (p->max_ctas > 0) ctas = p->max_ctas;
   if (const char* e = getenv("B200_FC_MAX_CTAS")) {  // measurement knob
     const int v = atoi(e);
     if (v > 0) ctas = v;
   }
-  if (ctas > kZeroWsSlots / 2) ctas = kZeroWsSlots / 2;  // two scratch slots per CTA
+  if (!p->whole_tiles && ctas * passes > kZeroWsSlots / 2) ctas = kZeroWsSlots / 2 / passes;  // two scratch slots per CTA
   if (p->whole_tiles && ctas > p->n_tiles) ctas = p->n_tiles;
   if (ctas > total) ctas = (int)total;
   if (ctas < 1) ctas = 1;
@@ -1025,7 +1058,7 @@ cudaError_t launch_umma_one(const FcParams& p, int m_base, int passes, cudaStrea
     configured[dev] = true;
   }
   FcParams q = p;
-  const int ctas = plan_ctas(&q, passes);
+  const int ctas = plan_ctas(&q, passes, UmmaBudget<NB>::kCtasPerSm);
   size_t smem = (size_t)L::kSmemBytes;
   if (p.prologue) {
     if (!fc_prologue_supported(p.m, p.k) || NB != 16 || m_base != 0) return cudaErrorInvalidValue;
@@ -1098,7 +1131,9 @@ int plan_cluster_split(const FcParams& p) {
       capacity[dev][split] = n;
       if (getenv("B200_FC_VERBOSE")) fprintf(stderr, "[b200] cluster size %d: %d clusters resident (NB=%d)\n", split, n, NB);
     }
-    if (capacity[dev][split] >= p.n_tiles) {
+    // (the query counts one CTA per SM; CTAs this small share an SM, and clusters beyond the
+    // resident ones simply start as earlier ones finish: nothing waits across clusters)
+    if (capacity[dev][split] * UmmaBudget<NB>::kCtasPerSm >= p.n_tiles) {
       best = split;
       break;
     }
@@ -1173,7 +1208,14 @@ cudaError_t launch_all(const FcParams& p, cudaStream_t s) {
   }
   const int passes = (p.m + nb - 1) / nb;
   FcParams q = p;
-  q.force_whole_tiles = 1;
+  // Whole n tiles per CTA. B200_FC_SPLIT_PASSES=1 (measurement knob) instead shares the SMs out among
+  // the passes and splits each pass's reduction (stream-K): measured slower on B200 for the shapes
+  // that leave SMs idle here (prompt chunk of 512 rows; qkv / o / down projections 26 / 17 / 77 us as
+  // whole tiles, 57 us on average when split): the merge of 128-row partials through memory costs
+  // more than the idle SMs.
+  q.split_passes = 0;
+  if (const char* e = getenv("B200_FC_SPLIT_PASSES")) q.split_passes = atoi(e) ? 1 : 0;
+  q.force_whole_tiles = q.split_passes ? 0 : 1;
   return launch_umma_nb<EPI>(q, 0, nb, passes, s);
 }
 

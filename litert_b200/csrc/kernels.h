@@ -87,6 +87,7 @@ struct FcParams {
   int max_ctas;              // 0 = chosen per shape
   int whole_tiles;           // set by the launcher: CTAs own whole n tiles (no split-K)
   int force_whole_tiles;     // set by the launcher for prefill-sized passes
+  int split_passes;       // several passes in one launch, each split over its share of the SMs (stream-K)
   int debug_flags;           // measurement only: 1 = skip the MMAs, 2 = the epilogue, 4 = the output stores, 8 = the TMEM loads
 };
 

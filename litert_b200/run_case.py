@@ -8,6 +8,7 @@ most on the device), and a quick way to exercise a single op from a shell:
     python -m litert_b200.run_case fc_w4     --m 1
     python -m litert_b200.run_case sdpa      --kv f16
     python -m litert_b200.run_case decode    --batch 1 --context 1024 --steps 3
+    python -m litert_b200.run_case prefill   --context 1024 --layers 2
 
 Every case prints one line with the shapes it ran and "ok".
 """
@@ -98,8 +99,20 @@ def case_decode(a):
     return f"decode model={a.model} batch={a.batch} context={a.context} steps={a.steps} launches/step={d.launches_per_step}"
 
 
+def case_prefill(a):
+    cfg = dict(dec.GEMMA_2B if a.model == "gemma2b" else dec.TINY)
+    if a.layers:
+        cfg["n_layers"] = a.layers
+    d = dec.Decoder(cfg, max_seq=a.context + 8, max_batch=1, kv_dtype=a.kv)
+    prompt = np.random.default_rng(3).integers(0, cfg["vocab"], a.context).astype(np.int32)
+    for _ in range(a.reps):
+        d.reset()
+        d.prefill(prompt)
+    return f"prefill model={a.model} layers={cfg['n_layers']} prompt={a.context} reps={a.reps}"
+
+
 CASES = {"fc_hybrid": case_fc_hybrid, "fc_int8": case_fc_int8, "fc_w4": case_fc_w4, "sdpa": case_sdpa,
-         "decode": case_decode}
+         "decode": case_decode, "prefill": case_prefill}
 
 
 def main(argv=None):
@@ -114,6 +127,7 @@ def main(argv=None):
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--model", default="gemma2b", choices=["gemma2b", "tiny"])
+    ap.add_argument("--layers", type=int, default=0, help="prefill: layer count override (0 = the model's)")
     a = ap.parse_args(argv)
     default_nk = {"fc_int8": (2048, 2048)}.get(a.case, (14336, 4096))
     a.n = a.n or default_nk[0]
