@@ -640,16 +640,36 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
     const int wper = ((((c1 - c0) + kAttnWarps - 1) / kAttnWarps) + 15) / 16 * 16;
     const int first = c0 + warp * wper;
     const int last = min(c1, first + wper);
-    WA wa;
-    if (first >= last) {
-      wa.clear();
-    } else if (staged) {
-      wa.template run<kSrcShared>(sp, qf, rows, b, first, WA::kTokensPerWarpIter, last, lane);
-    } else {
-      wa.template run<kSrcGlobalCoherent>(sp, qf, rows, b, first, WA::kTokensPerWarpIter, last, lane);
-    }
-    if (tracer && live) p.trace[4] = global_timer_ns();
+    // Staged rows are read from shared memory, where passes are cheap: the smallest loop body (16
+    // tokens per pass) whatever the cache's capacity. Rows read from the cache itself (a share
+    // longer than the staging area) want the long passes the kernel was instantiated with.
+    if (staged) {
+      using WA1 = WarpAttention<KV, H, 1>;
+      WA1 wa;
+      typename WA1::Rows rows1;
+      rows1.k = rows.k;
+      rows1.v = rows.v;
+      rows1.stride = rows.stride;
+      rows1.k_scale = rows.k_scale;
+      rows1.v_scale = rows.v_scale;
+      rows1.scale_stride = rows.scale_stride;
+      if (first >= last) {
+        wa.clear();
+      } else {
+        wa.template run<kSrcShared>(sp, qf, rows1, b, first, 16, last, lane);
+      }
+      if (tracer && live) p.trace[4] = global_timer_ns();
       wa.park(sm.sm_m, sm.sm_l, sm_o, warp, lane);
+    } else {
+      WA wa;
+      if (first >= last) {
+        wa.clear();
+      } else {
+        wa.template run<kSrcGlobalCoherent>(sp, qf, rows, b, first, WA::kTokensPerWarpIter, last, lane);
+      }
+      if (tracer && live) p.trace[4] = global_timer_ns();
+      wa.park(sm.sm_m, sm.sm_l, sm_o, warp, lane);
+    }
     __syncthreads();
     // this CTA's state per head: the warps merged (weights per warp and head computed once)
     if (tid < 8) {
