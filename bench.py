@@ -174,7 +174,7 @@ def run_reference(args):
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # DRAM bytes moved per algorithmic byte by the GEMV kernels, from ncu captures of single launches
@@ -412,13 +412,32 @@ def run_ours(args):
     if rank == 0:
         if tp:
             line["tensor_parallel"] = tp
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+_RESULT_FD = None
+
+
+def emit(line):
+    """Writes the result line to the process's original standard output."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    global _RESULT_FD
     args = parse_args()
+    # Standard output carries the one result line and nothing else: libraries that print there
+    # (NCCL's version banner, for one) are sent to standard error for the length of the run.
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:
