@@ -237,7 +237,7 @@ B200_API int b200_decoder_set_positions(b200_decoder* dec, const int32_t* h_posi
 B200_API int b200_decoder_step(b200_decoder* dec, const int32_t* h_tokens, int batch, int32_t* h_next_tokens,
                                float* d_logits);
 /* Prompt pass: runs the n_tokens prompt tokens (HOST array) of sequence `seq` through the layers in
- * chunks of up to 512 rows, every projection as one GEMM over the chunk, appends their keys and
+ * chunks of up to 1024 rows, every projection as one GEMM over the chunk, appends their keys and
  * values to the sequence's cache behind the tokens already there, and predicts the first generated
  * token from the last prompt token (greedy; written to *h_next_token when given, and kept on the
  * device so that b200_decoder_run(dec, NULL, ...) continues from it). Results are those of

@@ -477,15 +477,22 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
   return B200_OK;
 }
 
-// Rows of one prompt chunk: enough for the 256-row passes of the prefill GEMM kernel to fill the
-// machine at every projection shape, small enough that the feed-forward scratch stays modest.
-constexpr int kPrefillRows = 512;
+// Rows of one prompt chunk. The projections with few n tiles (attention output and down: 16 tiles
+// of 128 channels) only fill the SMs when there are many passes of activation rows, so the chunk is
+// large; the scratch is 140 KB per row at the benchmark's sizes. B200_PREFILL_ROWS overrides it
+// (measurement knob, read when the first prompt pass allocates the scratch).
+constexpr int kPrefillRows = 1024;
 
 int ensure_prefill_bufs(b200_decoder* d) {
   if (d->pf) return B200_OK;
   const b200_decoder_config& c = d->cfg;
   auto pf = std::make_unique<PrefillBufs>();
-  const int R = kPrefillRows, m_alloc = m_alloc_for(R), qdim = d->hl * c.head_dim, kvdim = d->kvl * c.head_dim;
+  int R = kPrefillRows;
+  if (const char* e = getenv("B200_PREFILL_ROWS")) {
+    const int v = atoi(e);
+    if (v >= 1 && v <= 8192) R = v;
+  }
+  const int m_alloc = m_alloc_for(R), qdim = d->hl * c.head_dim, kvdim = d->kvl * c.head_dim;
   pf->rows = R;
   DEC_CUDA(pf->tokens.alloc(sizeof(int32_t) * R));
   DEC_CUDA(pf->positions.alloc(sizeof(int32_t) * R));
@@ -500,9 +507,7 @@ int ensure_prefill_bufs(b200_decoder* d) {
   DEC_CUDA(pf->q_a.alloc(q_tiled_bytes(m_alloc, qdim)));
   DEC_CUDA(pf->q_f.alloc(q_tiled_bytes(m_alloc, d->fl)));
   for (DevBuf* b : {&pf->sc_d, &pf->sc_a, &pf->sc_f, &pf->zp_d, &pf->zp_a, &pf->zp_f}) DEC_CUDA(b->alloc(sizeof(float) * m_alloc));
-  size_t sdpa_bytes = 0;  // the chunking depends on the row count
-  for (int b = 1; b <= R; ++b) sdpa_bytes = std::max(sdpa_bytes, sdpa_workspace_bytes(b, d->hl, d->kvl, c.head_dim, c.max_seq));
-  DEC_CUDA(pf->sdpa_ws.alloc(sdpa_bytes));
+  DEC_CUDA(pf->sdpa_ws.alloc(sdpa_workspace_bytes(R, d->hl, d->kvl, c.head_dim, c.max_seq, 1)));
   DEC_CUDA(cudaMallocHost(&pf->h_stage, sizeof(int32_t) * 2 * R));
   d->pf = std::move(pf);
   return B200_OK;

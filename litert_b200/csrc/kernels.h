@@ -165,6 +165,6 @@ struct AttnStepParams {
 bool attn_step_supported(int n, int nkv, int h, int kv_dtype);
 cudaError_t launch_attn_step(const AttnStepParams& p, cudaStream_t s);
 cudaError_t launch_sdpa_decode(const SdpaParams& p, cudaStream_t s);
-size_t sdpa_workspace_bytes(int b, int n, int nkv, int h, int s_max);
+size_t sdpa_workspace_bytes(int b, int n, int nkv, int h, int s_max, int shared_kv = 0);
 
 }  // namespace b200

@@ -422,6 +422,62 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
   }
 }
 
+// Prompt-pass variant (SdpaParams::shared_kv): the rows of the batch are consecutive tokens of ONE
+// sequence and all read the same cache, row b up to lengths[b]. Here a WARP owns a row: the warps of a
+// CTA walk the same chunk of the cache for kWarps neighbouring rows at nearly the same pace, so the
+// chunk comes through L2 once per CTA instead of once per row. Every warp writes the partial record
+// of its own (row, chunk); the merge kernels are the same.
+template <int KV, int H, bool QF32, int GPI>
+__global__ void __launch_bounds__(kWarps * 32) sdpa_rows_kernel(const SdpaParams p, const int chunk_tokens,
+                                                                const int chunks_max) {
+  using WA = WarpAttention<KV, H, GPI>;
+  constexpr int KSTEPS = WA::KSTEPS;
+  __shared__ float sm_m[kWarps][8], sm_l[kWarps][8];
+  __shared__ float sm_o[kWarps][8][H + 4];
+  pdl_enter();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = (int)blockIdx.z * kWarps + warp, kvh = blockIdx.y, chunk = blockIdx.x;
+  if (b >= p.b) return;  // (no block-wide barrier below)
+  const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
+  const int c0 = chunk * chunk_tokens;
+  if (c0 >= len) return;
+  const int c1 = min(len, c0 + chunk_tokens);
+  const int g = lane >> 2, t = lane & 3;
+  const int group = p.n / p.nkv;
+  uint32_t qf[KSTEPS][4];
+  {
+    const bool head_ok = g < group;
+    const int head = kvh * group + (head_ok ? g : 0);
+#pragma unroll
+    for (int i = 0; i < KSTEPS; ++i) {
+      const int d0 = 8 * (t + 4 * i);
+      if (!head_ok) {
+        qf[i][0] = qf[i][1] = qf[i][2] = qf[i][3] = 0u;
+      } else if constexpr (QF32) {
+        const float* q = static_cast<const float*>(p.q) + ((size_t)b * p.n + head) * H + d0;
+        load8<kKvF32>(q, 0, true, qf[i]);
+      } else {
+        const __half* q = static_cast<const __half*>(p.q) + ((size_t)b * p.n + head) * H + d0;
+        load8<kKvF16>(q, 0, true, qf[i]);
+      }
+    }
+  }
+  WA wa;
+  wa.template run<kSrcGlobal>(p, qf, WA::cache_rows(p, b, kvh), b, c0, WA::kTokensPerWarpIter, c1, lane);
+  wa.park(sm_m, sm_l, sm_o, warp, lane);
+  __syncwarp();
+  float* part = p.ws + ((((size_t)b * p.nkv + kvh) * chunks_max + chunk) * 8) * partial_stride(H);
+  for (int idx = lane; idx < group * H; idx += 32) {
+    const int head = idx / H, d = idx % H;
+    float* rec = part + (size_t)head * partial_stride(H);
+    rec[d] = sm_o[warp][head][d];
+    if (d == 0) {
+      rec[H] = sm_m[warp][head];
+      rec[H + 1] = sm_l[warp][head];
+    }
+  }
+}
+
 // ---- one decode step of a decoder layer's attention in ONE launch -------------------------------
 // For a fused q/k/v projection output with a single KV head (multi-query attention) and at most
 // eight query heads: rotary embedding of q and of the new key, append of the new key / value row to
@@ -959,7 +1015,17 @@ __global__ void sdpa_decode_generic_kernel(const SdpaParams p) {
 // reads ~1 MB) and bandwidth-bound on long ragged batches: small chunks give many warps one short
 // pass each, large chunks amortise the partial records. Depends only on (batch, s_max) so that the
 // workspace size can be computed without the lengths.
-int pick_chunk_tokens(int b, int s_max) {
+int pick_chunk_tokens(int b, int s_max, int shared_kv) {
+  // prompt pass (a warp per row and chunk): measured on B200 (1024 rows of one sequence, 8 query
+  // heads x 256): 64-token chunks 128 us, 128 tokens 101 us, 256 tokens 95 us per layer
+  if (shared_kv) {
+    static const int chunk = [] {  // B200_ROWS_CHUNK: measurement knob
+      const char* e = getenv("B200_ROWS_CHUNK");
+      const int v = e ? atoi(e) : 0;
+      return (v == 64 || v == 128 || v == 256 || v == 512) ? v : 256;
+    }();
+    return chunk;
+  }
   const long long tokens = (long long)b * s_max;
   if (tokens <= 16384) return 64;
   if (tokens <= 65536) return 128;
@@ -969,11 +1035,25 @@ int pick_chunk_tokens(int b, int s_max) {
 
 template <int KV, int H, bool QF32>
 cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
-  const int chunk_tokens = pick_chunk_tokens(p.b, p.s_max);
+  const int chunk_tokens = pick_chunk_tokens(p.b, p.s_max, p.shared_kv);
   const int chunks_max = (p.s_max + chunk_tokens - 1) / chunk_tokens;
   dim3 grid(chunks_max, p.nkv, p.b);
   cudaError_t e;
-  if (chunk_tokens == 64) {
+  if (p.shared_kv) {
+    // prompt pass: a warp per row, the CTA's rows share the chunk's traffic; long passes
+    const dim3 rgrid(chunks_max, p.nkv, (p.b + kWarps - 1) / kWarps);
+    static const int gpi = [] {  // B200_ROWS_GPI: measurement knob
+      const char* e = getenv("B200_ROWS_GPI");
+      return e ? atoi(e) : 4;
+    }();
+    if (gpi == 1) {
+      e = launch_chained(sdpa_rows_kernel<KV, H, QF32, 1>, rgrid, dim3(kWarps * 32), 0, s, p, chunk_tokens, chunks_max);
+    } else if (gpi == 4) {
+      e = launch_chained(sdpa_rows_kernel<KV, H, QF32, 4>, rgrid, dim3(kWarps * 32), 0, s, p, chunk_tokens, chunks_max);
+    } else {
+      e = launch_chained(sdpa_rows_kernel<KV, H, QF32, 2>, rgrid, dim3(kWarps * 32), 0, s, p, chunk_tokens, chunks_max);
+    }
+  } else if (chunk_tokens == 64) {
     e = launch_chained(sdpa_decode_kernel<KV, H, QF32, 1>, grid, dim3(kWarps * 32), 0, s, p, chunk_tokens, chunks_max);
   } else if (chunk_tokens == 128) {
     e = launch_chained(sdpa_decode_kernel<KV, H, QF32, 2>, grid, dim3(kWarps * 32), 0, s, p, chunk_tokens, chunks_max);
@@ -997,7 +1077,7 @@ template <int KV, bool QF32>
 cudaError_t launch_kv(const SdpaParams& p, cudaStream_t s) {
   const int group = p.nkv > 0 ? p.n / p.nkv : 0;
   const bool fast = group >= 1 && group <= 8 && p.n % p.nkv == 0 && p.ws != nullptr &&
-                    p.ws_bytes >= sdpa_workspace_bytes(p.b, p.n, p.nkv, p.h, p.s_max);
+                    p.ws_bytes >= sdpa_workspace_bytes(p.b, p.n, p.nkv, p.h, p.s_max, p.shared_kv);
   if (p.q_tiled_out && (!fast || !QF32 || (p.h != 256 && p.h != 128 && p.h != 64)))
     return cudaErrorInvalidValue;  // fused output quantization exists on the fast f32-query path only
   if (fast && p.h == 256) return launch_fast<KV, 256, QF32>(p, s);
@@ -1041,9 +1121,9 @@ cudaError_t launch_attn_step_h(const AttnStepParams& p, cudaStream_t s) {
 
 }  // namespace
 
-size_t sdpa_workspace_bytes(int b, int n, int nkv, int h, int s_max) {
+size_t sdpa_workspace_bytes(int b, int n, int nkv, int h, int s_max, int shared_kv) {
   (void)n;
-  const int chunk_tokens = pick_chunk_tokens(b, s_max);
+  const int chunk_tokens = pick_chunk_tokens(b, s_max, shared_kv);
   const int chunks_max = (s_max + chunk_tokens - 1) / chunk_tokens;
   // [b][nkv][chunks][8 (query heads of the group, padded)][h + 2] floats
   return (size_t)b * nkv * chunks_max * 8 * partial_stride(h) * sizeof(float);
