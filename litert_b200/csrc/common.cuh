@@ -99,6 +99,16 @@ __device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity
   atomicCAS(status, 0, code);
 }
 
+// Last resort after an abort: waits (10 ms at most, whatever the abort flag says) for a copy that was
+// issued towards `bar`, so that a CTA does not exit with copies into its shared memory in flight.
+__device__ __forceinline__ void mbar_drain_bounded(uint64_t* bar, uint32_t parity) {
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((i & 63u) == 63u && global_timer_ns() - t0 > 10ull * 1000ull * 1000ull) return;
+  }
+}
+
 // ---- bulk async copy (TMA engine, linear form) ------------------------------
 // Both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {

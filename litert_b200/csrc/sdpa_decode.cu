@@ -169,11 +169,13 @@ struct WarpAttention {
   }
 
   // Tokens first, first + step, ... (blocks of kTokensPerWarpIter) below `c1`.
+    // `fresh` false continues the running softmax state of an earlier call; `finish` false leaves the
+  // denominators per thread for a later call to complete (calls over consecutive pieces of a chunk).
   template <int SRC>
   __device__ __forceinline__ void run(const SdpaParams& p, const uint32_t (&qf)[KSTEPS][4], const Rows& rows_src, int b,
-                                      int first, int step, int c1, int lane) {
+                                      int first, int step, int c1, int lane, bool fresh = true, bool finish = true) {
     const int g = lane >> 2, t = lane & 3;
-    clear();
+    if (fresh) clear();
   const size_t row_stride = rows_src.stride;
   const uint8_t* kbase = rows_src.k;
   const uint8_t* vbase = rows_src.v;
@@ -324,6 +326,10 @@ struct WarpAttention {
   }
 
     // l is still per-thread; reduce over the token lanes
+    if (finish) finish_sums();
+  }
+
+  __device__ __forceinline__ void finish_sums() {
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       float v = l_run[e];
@@ -397,6 +403,152 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
   // ---- merge the warps of this CTA ----
   __shared__ float sm_m[kWarps][8], sm_l[kWarps][8];
   __shared__ float sm_o[kWarps][8][H + 4];
+  wa.park(sm_m, sm_l, sm_o, warp, lane);
+  __syncthreads();
+  float* part = p.ws + ((((size_t)b * p.nkv + kvh) * chunks_max + chunk) * 8) * partial_stride(H);
+  for (int idx = tid; idx < group * H; idx += kWarps * 32) {
+    const int head = idx / H, d = idx % H;
+    float mm = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, sm_m[w][head]);
+    const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
+    float acc = 0.0f, l = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float f = exp2f(sm_m[w][head] - muse);
+      acc += f * sm_o[w][head][d];
+      l += f * sm_l[w][head];
+    }
+    float* rec = part + (size_t)head * partial_stride(H);
+    rec[d] = acc;
+    if (d == 0) {
+      rec[H] = mm;
+      rec[H + 1] = l;
+    }
+  }
+}
+
+// Staged variant of the kernel above for fp16 / int8 caches: the CTA's chunk goes through a ring of
+// shared-memory stages of kRingTokens tokens, every cached row fetched by one bulk asynchronous copy
+// (one row per thread and stage: keys by the lower half of the CTA, values by the upper), so a
+// CTA keeps up to stages x 64 KB in flight without holding registers for it, and the warps read
+// their MMA fragments from shared memory (the loads straight from global memory of the kernel
+// above leave the SMs waiting on the long scoreboard with ~7 warps each). Same chunking, same
+// partial records.
+constexpr int kRingTokens = 64;
+constexpr int kRingStagesMax = 3;
+
+template <int KV, int H>
+struct RingLayout {
+  static constexpr int kRowBytes = H * (KV == kKvI8 ? 1 : 2);
+  static constexpr int kPitch = kRowBytes + 16;  // rows 16 bytes apart in the banks
+  static constexpr int kStageBytes = 2 * kRingTokens * kPitch;
+  static constexpr int kParkBytes = (int)sizeof(float) * kWarps * 8 * (H + 4);
+  static size_t smem_bytes(int stages) {
+    const size_t ring = (size_t)stages * kStageBytes;
+    return (ring > (size_t)kParkBytes ? ring : (size_t)kParkBytes) + 128;
+  }
+};
+
+template <int KV, int H, bool QF32>
+__global__ void __launch_bounds__(kWarps * 32) sdpa_decode_ring_kernel(const SdpaParams p, const int chunk_tokens,
+                                                                       const int chunks_max, const int stages) {
+  using WA = WarpAttention<KV, H, 1>;
+  using L = RingLayout<KV, H>;
+  constexpr int KSTEPS = WA::KSTEPS;
+  static_assert(kWarps * 32 == 2 * kRingTokens, "one row copy per thread and stage");
+  static_assert(kWarps * 16 == kRingTokens, "one 16-token group per warp and stage");
+  extern __shared__ __align__(128) uint8_t ring_smem[];
+  __shared__ float sm_m[kWarps][8], sm_l[kWarps][8];
+  __shared__ int s_abort;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring_smem);  // [kRingStagesMax], 128 bytes reserved
+  uint8_t* ring = ring_smem + 128;
+  float (*sm_o)[8][H + 4] = reinterpret_cast<float (*)[8][H + 4]>(ring);  // after the loop
+  volatile int* abort_flag = &s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int i = 0; i < kRingStagesMax; ++i) mbar_init(&full_bar[i], 1);
+    s_abort = 0;
+    mbar_fence_init();
+  }
+  pdl_enter();
+  __syncthreads();
+  const int b = blockIdx.z, kvh = blockIdx.y, chunk = blockIdx.x;
+  const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
+  const int c0 = chunk * chunk_tokens;
+  if (c0 >= len) return;  // uniform over the CTA, nothing in flight
+  const int c1 = min(len, c0 + chunk_tokens);
+  const int n_sub = (c1 - c0 + kRingTokens - 1) / kRingTokens;
+  const int g = lane >> 2, t = lane & 3;
+  const int group = p.n / p.nkv;
+  const typename WA::Rows cache = WA::cache_rows(p, b, kvh);
+
+  // stage `s` <- tokens [c0 + j * 64, ...): thread r (< 64) fetches key row r, thread 64 + r value row r
+  auto issue = [&](int j) {
+    const int s = j % stages;
+    const int t0 = c0 + j * kRingTokens;
+    const int rows = min(kRingTokens, c1 - t0);
+    uint8_t* stage = ring + (size_t)s * L::kStageBytes;
+    if (tid == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(2 * rows * L::kRowBytes));
+    const int r = tid & (kRingTokens - 1);
+    if (r < rows) {
+      const bool is_v = tid >= kRingTokens;
+      const uint8_t* src = (is_v ? cache.v : cache.k) + (size_t)(t0 + r) * cache.stride;
+      bulk_g2s(stage + (size_t)(is_v ? kRingTokens : 0) * L::kPitch + (size_t)r * L::kPitch, src, L::kRowBytes, &full_bar[s]);
+    }
+  };
+  int issued = min(stages, n_sub);
+  for (int j = 0; j < issued; ++j) issue(j);
+
+  // ---- Q fragments (as above) while the first stages land ----
+  uint32_t qf[KSTEPS][4];
+  {
+    const bool head_ok = g < group;
+    const int head = kvh * group + (head_ok ? g : 0);
+#pragma unroll
+    for (int i = 0; i < KSTEPS; ++i) {
+      const int d0 = 8 * (t + 4 * i);
+      if (!head_ok) {
+        qf[i][0] = qf[i][1] = qf[i][2] = qf[i][3] = 0u;
+      } else if constexpr (QF32) {
+        const float* q = static_cast<const float*>(p.q) + ((size_t)b * p.n + head) * H + d0;
+        load8<kKvF32>(q, 0, true, qf[i]);
+      } else {
+        const __half* q = static_cast<const __half*>(p.q) + ((size_t)b * p.n + head) * H + d0;
+        load8<kKvF16>(q, 0, true, qf[i]);
+      }
+    }
+  }
+  WA wa;
+  wa.clear();
+  for (int j = 0; j < n_sub; ++j) {
+    const int s = j % stages;
+    mbar_wait_bounded(&full_bar[s], (uint32_t)(j / stages) & 1u, abort_flag, p.status, kStatusWaitTimeoutFull);
+    const int t0 = c0 + j * kRingTokens;
+    const int t1 = min(c1, t0 + kRingTokens);
+    const int first = t0 + warp * 16;
+    if (first < t1 && !*abort_flag) {
+      typename WA::Rows rows = cache;  // scales stay in global memory
+      const uint8_t* stage = ring + (size_t)s * L::kStageBytes;
+      rows.k = stage - (ptrdiff_t)t0 * L::kPitch;  // indexed by absolute token
+      rows.v = stage + (size_t)kRingTokens * L::kPitch - (ptrdiff_t)t0 * L::kPitch;
+      rows.stride = L::kPitch;
+      wa.template run<kSrcShared>(p, qf, rows, b, first, kRingTokens, t1, lane, /*fresh=*/false, /*finish=*/false);
+    }
+    __syncthreads();  // every warp is done with stage s
+    if (issued < n_sub && !*abort_flag) {  // (abort_flag cannot change between the barrier above and here)
+      issue(issued);
+      ++issued;
+    }
+  }
+  wa.finish_sums();
+  // after an abort: the latest copies towards each stage may still be in flight
+  if (*abort_flag)
+    for (int j = max(0, issued - stages); j < issued; ++j) mbar_drain_bounded(&full_bar[j % stages], (uint32_t)(j / stages) & 1u);
+  __syncthreads();
+
+  // ---- merge the warps of this CTA (the parked outputs reuse the ring) ----
   wa.park(sm_m, sm_l, sm_o, warp, lane);
   __syncthreads();
   float* part = p.ws + ((((size_t)b * p.nkv + kvh) * chunks_max + chunk) * 8) * partial_stride(H);
@@ -1026,6 +1178,12 @@ int pick_chunk_tokens(int b, int s_max, int shared_kv) {
     }();
     return chunk;
   }
+  static const int forced = [] {  // B200_SDPA_CHUNK: measurement knob
+    const char* e = getenv("B200_SDPA_CHUNK");
+    const int v = e ? atoi(e) : 0;
+    return (v == 64 || v == 128 || v == 256 || v == 512) ? v : 0;
+  }();
+  if (forced) return forced;
   const long long tokens = (long long)b * s_max;
   if (tokens <= 16384) return 64;
   if (tokens <= 65536) return 128;
@@ -1039,7 +1197,44 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
   const int chunks_max = (p.s_max + chunk_tokens - 1) / chunk_tokens;
   dim3 grid(chunks_max, p.nkv, p.b);
   cudaError_t e;
-  if (p.shared_kv) {
+  bool staged = false;
+  static const bool ring_env = [] {  // B200_SDPA_RING=0: measurement knob, keeps the register-fed kernel
+    const char* e = getenv("B200_SDPA_RING");
+    return !(e && e[0] == '0');
+  }();
+  if constexpr (KV != kKvF32) {
+    const bool aligned = ((reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v)) & 15) == 0;
+    if (ring_env && !p.shared_kv && aligned && chunk_tokens % kRingTokens == 0) {
+      using L = RingLayout<KV, H>;
+      // As many stages as keep two or three CTAs on an SM: the token loop is latency-bound and wants
+      // warps more than it wants depth. Measured on B200, 16 ragged sequences up to 8192 tokens, head
+      // size 256: fp16 rows (68 KB per stage) 23.4 us with one stage, 31.4 with three (one CTA per
+      // SM); int8 rows (35 KB) 18.4 us with three, 21.9 with one. The register-fed kernel: 24.8 / 68 us.
+      int stages = std::min(kRingStagesMax, chunk_tokens / kRingTokens);
+      stages = std::min(stages, std::max(1, (104 * 1024) / L::kStageBytes));
+      static const int stages_env = [] {  // B200_SDPA_STAGES: measurement knob
+        const char* e = getenv("B200_SDPA_STAGES");
+        return e ? atoi(e) : 0;
+      }();
+      if (stages_env >= 1 && stages_env <= kRingStagesMax) stages = std::min(stages, stages_env);
+      const size_t smem = L::smem_bytes(stages);
+      auto kernel = sdpa_decode_ring_kernel<KV, H, QF32>;
+      static size_t configured[64] = {0};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev < 0 || dev >= 64) dev = 0;
+      if (configured[dev] < smem) {
+        cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::smem_bytes(kRingStagesMax));
+        if (ea != cudaSuccess) return ea;
+        configured[dev] = L::smem_bytes(kRingStagesMax);
+      }
+      e = launch_chained(kernel, grid, dim3(kWarps * 32), smem, s, p, chunk_tokens, chunks_max, stages);
+      staged = true;
+    }
+  }
+  if (staged) {
+    // (the merge below is common to all variants)
+  } else if (p.shared_kv) {
     // prompt pass: a warp per row, the CTA's rows share the chunk's traffic; long passes
     const dim3 rgrid(chunks_max, p.nkv, (p.b + kWarps - 1) / kWarps);
     static const int gpi = [] {  // B200_ROWS_GPI: measurement knob
