@@ -36,3 +36,15 @@ def test_two_gpu_ranks_match_oracle_shards(tmp_path, oracle, mode):
     assert np.array_equal(got[0]["replay"], got[1]["replay"])
     assert np.array_equal(got[0]["replay"], got[0]["tokens"][-1])
     ref.close()
+    if mode == "nccl":
+        # the prompt pass (partial sums through the all-reduce) against stepping the same prompts
+        assert np.array_equal(got[0]["prefill_tok"], got[1]["prefill_tok"])
+        lg = np.concatenate([got[0]["stepped_logits"], got[1]["stepped_logits"]], axis=1)
+        top2 = np.sort(lg, axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 0.05 * (lg.max(axis=1) - lg.min(axis=1))
+        assert np.array_equal(got[0]["prefill_tok"][clear], got[0]["stepped_tok"][clear])
+        a = np.concatenate([got[0]["filled_next"], got[1]["filled_next"]], axis=1)
+        b = np.concatenate([got[0]["stepped_next"], got[1]["stepped_next"]], axis=1)
+        assert np.linalg.norm(a - b) / np.linalg.norm(b) <= 3e-2
+    else:
+        assert int(got[0]["prefill_refused"]) == 1 and int(got[1]["prefill_refused"]) == 1

@@ -14,6 +14,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 CFG = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=1, head_dim=64, d_ff=512, vocab=1000)
 BATCH, STEPS, MAX_SEQ, SEED = 3, 5, 16, 11
+PROMPT = 9
 
 
 def host_weights(seed=SEED):
@@ -72,7 +73,30 @@ def run_gpu(rank, world, port, out_dir, mode, kv):
     d.reset()
     dist.barrier()
     replay = d.run(first_tokens(), STEPS)
-    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), tokens=np.stack(toks), logits=np.stack(logits), replay=replay)
+    # prompt pass against stepping the same prompts: sequences 0 and 1, PROMPT tokens each
+    extra = {}
+    prompts = np.random.default_rng(9).integers(0, CFG["vocab"], (2, PROMPT)).astype(np.int32)
+    d.reset()
+    dist.barrier()
+    for t in range(PROMPT):
+        stepped_tok, stepped_logits = d.step(prompts[:, t], want_logits=True)
+    _, stepped_next = d.step(stepped_tok, want_logits=True)
+    d.reset()
+    dist.barrier()
+    if mode == "nccl":
+        first = np.array([d.prefill(prompts[b], seq=b) for b in range(2)], np.int32)
+        _, filled_next = d.step(stepped_tok, want_logits=True)
+        extra = dict(stepped_tok=stepped_tok, stepped_logits=stepped_logits.cpu().numpy(), prefill_tok=first,
+                     stepped_next=stepped_next.cpu().numpy(), filled_next=filled_next.cpu().numpy())
+    else:
+        # the peer exchange is a decode-step mechanism: a prompt pass needs the all-reduce
+        from litert_b200._lib import B200Error
+        try:
+            d.prefill(prompts[0], seq=0)
+            extra = dict(prefill_refused=np.array(0))
+        except B200Error:
+            extra = dict(prefill_refused=np.array(1))
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), tokens=np.stack(toks), logits=np.stack(logits), replay=replay, **extra)
     dist.barrier()
     d.close()
     dist.destroy_process_group()
