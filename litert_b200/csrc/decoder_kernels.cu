@@ -147,8 +147,12 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_kernel(float* __r
 }
 
 __device__ __forceinline__ float gelu_tanh(float v) {
+  // every product and sum rounded on its own, in the order a C compiler without contraction gives
+  // (left to right): the row is quantized to int8 next, where one ulp can flip a value
   const float k0 = 0.7978845608028654f;
-  return 0.5f * v * (1.0f + tanhf(k0 * (v + 0.044715f * v * v * v)));
+  const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v);
+  const float th = tanhf(__fmul_rn(k0, __fadd_rn(v, cube)));
+  return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, th));
 }
 
 // f = gelu_tanh(gate) * up from the fused projection output [b, 2 f]; quantize f per row.

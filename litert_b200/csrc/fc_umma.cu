@@ -1104,7 +1104,18 @@ int plan_cluster_split(const FcParams& p) {
   }
   if (const char* e = getenv("B200_FC_CLUSTER")) {  // measurement knob: force a split
     const int v = atoi(e);
-    if (v >= 2 && v <= 8 && v <= p.k_tiles) return v;
+    if (v >= 2 && v <= 16 && v <= p.k_tiles) {
+      // beyond 8 the cluster size is "non-portable": the kernel has to opt in
+      static bool opted[64] = {false};
+      if (v > 8 && !opted[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+          cudaGetLastError();
+          return 0;
+        }
+        opted[dev] = true;
+      }
+      return v;
+    }
   }
   // the split that puts the most SMs to work with every cluster resident at once
   int best = 0;
