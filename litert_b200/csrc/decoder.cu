@@ -713,7 +713,7 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
   DEC_CUDA(d->arg_idx.alloc(sizeof(int32_t) * B * kArgmaxParts));
   DEC_CUDA(cudaMemsetAsync(d->positions.p, 0, sizeof(int32_t) * B, d->stream));
   DEC_CUDA(cudaMallocHost(&d->h_tokens_pinned, sizeof(int32_t) * B));
-  DEC_CUDA(cudaMallocHost(&d->h_next_pinned, sizeof(int32_t) * B));
+  DEC_CUDA(cudaMallocHost(&d->h_next_pinned, sizeof(int32_t) * (B + 1)));  // + the status word read back with the tokens
   const size_t kv_elems = (size_t)B * c.max_seq * kvdim;
   const size_t kv_bytes = kv_elems * (c.kv_dtype == B200_DTYPE_I8 ? 1 : 2);
   for (int l = 0; l < c.n_layers; ++l) {
@@ -894,12 +894,14 @@ int b200_decoder_step(b200_decoder* d, const int32_t* h_tokens, int batch, int32
     DEC_CUDA(cudaGraphLaunch(d->graph[batch], d->stream));
   }
   if (h_next_tokens) {
+    // tokens and the device status word come back behind the step, one synchronisation for both
+    // (the status word's slot in the pinned buffer follows the max_batch token slots)
+    int32_t* h_status = d->h_next_pinned + d->cfg.max_batch;
     DEC_CUDA(cudaMemcpyAsync(d->h_next_pinned, d->next_tokens.p, sizeof(int32_t) * batch, cudaMemcpyDeviceToHost, d->stream));
+    DEC_CUDA(cudaMemcpyAsync(h_status, d->zero_ws.p, sizeof(int32_t), cudaMemcpyDeviceToHost, d->stream));
     DEC_CUDA(cudaStreamSynchronize(d->stream));
     memcpy(h_next_tokens, d->h_next_pinned, sizeof(int32_t) * batch);
-    int status = 0;
-    DEC_CUDA(cudaMemcpy(&status, d->zero_ws.p, sizeof(int), cudaMemcpyDeviceToHost));
-    if (status != 0) return dec_fail(B200_ERR_KERNEL_TIMEOUT, "b200_decoder_step: a device-side wait ran out");
+    if (*h_status != 0) return dec_fail(B200_ERR_KERNEL_TIMEOUT, "b200_decoder_step: a device-side wait ran out");
   }
   return B200_OK;
 }
