@@ -630,6 +630,123 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_rows_kernel(const SdpaParams
   }
 }
 
+// Prompt pass with staging (fp16 / int8 caches): a CTA takes kWarps neighbouring rows and one chunk of
+// the shared cache; the chunk goes through the 64-token ring stages of sdpa_decode_ring_kernel ONCE
+// for all the CTA's rows, and every warp runs its own row (its own query, softmax state and partial
+// record) over each stage, masked at the row's own length.
+template <int KV, int H, bool QF32>
+__global__ void __launch_bounds__(kWarps * 32) sdpa_rows_ring_kernel(const SdpaParams p, const int chunk_tokens,
+                                                                     const int chunks_max, const int stages) {
+  using WA = WarpAttention<KV, H, 4>;  // one pass of 64 tokens per stage
+  using L = RingLayout<KV, H>;
+  constexpr int KSTEPS = WA::KSTEPS;
+  static_assert(WA::kTokensPerWarpIter == kRingTokens, "a warp takes a whole stage per pass");
+  extern __shared__ __align__(128) uint8_t ring_smem[];
+  __shared__ float sm_m[kWarps][8], sm_l[kWarps][8];
+  __shared__ int s_abort;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring_smem);
+  uint8_t* ring = ring_smem + 128;
+  float (*sm_o)[8][H + 4] = reinterpret_cast<float (*)[8][H + 4]>(ring);  // after the loop
+  volatile int* abort_flag = &s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int i = 0; i < kRingStagesMax; ++i) mbar_init(&full_bar[i], 1);
+    s_abort = 0;
+    mbar_fence_init();
+  }
+  pdl_enter();
+  __syncthreads();
+  const int row0 = (int)blockIdx.z * kWarps, kvh = blockIdx.y, chunk = blockIdx.x;
+  const int b = min(row0 + warp, p.b - 1);          // this warp's row (a surplus warp repeats the last one, unused)
+  const bool row_ok = row0 + warp < p.b;
+  const int b_last = min(row0 + kWarps, p.b) - 1;   // lengths grow with the row: the CTA's longest
+  auto length_of = [&](int r) { return p.lengths ? min(p.lengths[r], p.s_max) : p.s_max; };
+  int len_cta = 0;
+  for (int r = row0; r <= b_last; ++r) len_cta = max(len_cta, length_of(r));
+  const int c0 = chunk * chunk_tokens;
+  if (c0 >= len_cta) return;  // uniform over the CTA, nothing in flight
+  const int c1 = min(len_cta, c0 + chunk_tokens);
+  const int len_w = row_ok ? length_of(b) : 0;
+  const int n_sub = (c1 - c0 + kRingTokens - 1) / kRingTokens;
+  const int g = lane >> 2, t = lane & 3;
+  const int group = p.n / p.nkv;
+  const typename WA::Rows cache = WA::cache_rows(p, 0, kvh);  // shared_kv: one cache for all rows
+
+  auto issue = [&](int j) {
+    const int s = j % stages;
+    const int t0 = c0 + j * kRingTokens;
+    const int rows = min(kRingTokens, c1 - t0);
+    uint8_t* stage = ring + (size_t)s * L::kStageBytes;
+    if (tid == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(2 * rows * L::kRowBytes));
+    const int r = tid & (kRingTokens - 1);
+    if (r < rows) {
+      const bool is_v = tid >= kRingTokens;
+      const uint8_t* src = (is_v ? cache.v : cache.k) + (size_t)(t0 + r) * cache.stride;
+      bulk_g2s(stage + (size_t)(is_v ? kRingTokens : 0) * L::kPitch + (size_t)r * L::kPitch, src, L::kRowBytes, &full_bar[s]);
+    }
+  };
+  int issued = min(stages, n_sub);
+  for (int j = 0; j < issued; ++j) issue(j);
+
+  uint32_t qf[KSTEPS][4];
+  {
+    const bool head_ok = g < group;
+    const int head = kvh * group + (head_ok ? g : 0);
+#pragma unroll
+    for (int i = 0; i < KSTEPS; ++i) {
+      const int d0 = 8 * (t + 4 * i);
+      if (!head_ok) {
+        qf[i][0] = qf[i][1] = qf[i][2] = qf[i][3] = 0u;
+      } else if constexpr (QF32) {
+        const float* q = static_cast<const float*>(p.q) + ((size_t)b * p.n + head) * H + d0;
+        load8<kKvF32>(q, 0, true, qf[i]);
+      } else {
+        const __half* q = static_cast<const __half*>(p.q) + ((size_t)b * p.n + head) * H + d0;
+        load8<kKvF16>(q, 0, true, qf[i]);
+      }
+    }
+  }
+  WA wa;
+  wa.clear();
+  for (int j = 0; j < n_sub; ++j) {
+    const int s = j % stages;
+    mbar_wait_bounded(&full_bar[s], (uint32_t)(j / stages) & 1u, abort_flag, p.status, kStatusWaitTimeoutFull);
+    const int t0 = c0 + j * kRingTokens;
+    const int t1 = min(min(c1, t0 + kRingTokens), len_w);  // this row's own causal limit
+    if (t0 < t1 && !*abort_flag) {
+      typename WA::Rows rows = cache;
+      const uint8_t* stage = ring + (size_t)s * L::kStageBytes;
+      rows.k = stage - (ptrdiff_t)t0 * L::kPitch;
+      rows.v = stage + (size_t)kRingTokens * L::kPitch - (ptrdiff_t)t0 * L::kPitch;
+      rows.stride = L::kPitch;
+      wa.template run<kSrcShared>(p, qf, rows, b, t0, kRingTokens, t1, lane, /*fresh=*/false, /*finish=*/false);
+    }
+    __syncthreads();  // every warp is done with stage s
+    if (issued < n_sub && !*abort_flag) {
+      issue(issued);
+      ++issued;
+    }
+  }
+  wa.finish_sums();
+  if (*abort_flag)
+    for (int j = max(0, issued - stages); j < issued; ++j) mbar_drain_bounded(&full_bar[j % stages], (uint32_t)(j / stages) & 1u);
+  __syncthreads();
+  wa.park(sm_m, sm_l, sm_o, warp, lane);
+  __syncwarp();
+  if (!row_ok || c0 >= len_w) return;  // (the merge reads only the chunks below the row's length)
+  float* part = p.ws + ((((size_t)b * p.nkv + kvh) * chunks_max + chunk) * 8) * partial_stride(H);
+  for (int idx = lane; idx < group * H; idx += 32) {
+    const int head = idx / H, d = idx % H;
+    float* rec = part + (size_t)head * partial_stride(H);
+    rec[d] = sm_o[warp][head][d];
+    if (d == 0) {
+      rec[H] = sm_m[warp][head];
+      rec[H + 1] = sm_l[warp][head];
+    }
+  }
+}
+
 // ---- one decode step of a decoder layer's attention in ONE launch -------------------------------
 // For a fused q/k/v projection output with a single KV head (multi-query attention) and at most
 // eight query heads: rotary embedding of q and of the new key, append of the new key / value row to
@@ -1232,6 +1349,28 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
       staged = true;
     }
   }
+  if constexpr (KV != kKvF32) {
+    const bool aligned = ((reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v)) & 15) == 0;
+    if (ring_env && p.shared_kv && aligned && chunk_tokens % kRingTokens == 0) {
+      using L = RingLayout<KV, H>;
+      int stages = std::min(kRingStagesMax, chunk_tokens / kRingTokens);
+      stages = std::min(stages, std::max(1, (104 * 1024) / L::kStageBytes));
+      const size_t smem = L::smem_bytes(stages);
+      auto kernel = sdpa_rows_ring_kernel<KV, H, QF32>;
+      static bool configured[64] = {false};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev < 0 || dev >= 64) dev = 0;
+      if (!configured[dev]) {
+        cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::smem_bytes(kRingStagesMax));
+        if (ea != cudaSuccess) return ea;
+        configured[dev] = true;
+      }
+      const dim3 rgrid(chunks_max, p.nkv, (p.b + kWarps - 1) / kWarps);
+      e = launch_chained(kernel, rgrid, dim3(kWarps * 32), smem, s, p, chunk_tokens, chunks_max, stages);
+      staged = true;
+    }
+  }
   if (staged) {
     // (the merge below is common to all variants)
   } else if (p.shared_kv) {
@@ -1263,7 +1402,8 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
       cudaError_t ea = cudaFuncSetAttribute(sdpa_merge_quant_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (ea != cudaSuccess) return ea;
     }
-    return launch_chained(sdpa_merge_quant_kernel<H>, dim3(p.b), dim3(1024), smem, s, p, chunk_tokens, chunks_max);
+    // a few rows (a decode step): the widest block per row; many rows (a prompt chunk): several rows per SM
+    return launch_chained(sdpa_merge_quant_kernel<H>, dim3(p.b), dim3(p.b > 32 ? 256 : 1024), smem, s, p, chunk_tokens, chunks_max);
   }
   return launch_chained(sdpa_merge_kernel<H, QF32>, dim3(p.n, p.b), dim3(H), 0, s, p, chunk_tokens, chunks_max);
 }
