@@ -96,7 +96,7 @@ __device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
   }
   *abort_flag = 1;
-  atomicCAS(status, 0, code);
+  if (status) atomicCAS(status, 0, code);  // (entry points without a status word still end in bounded time)
 }
 
 // Last resort after an abort: waits (10 ms at most, whatever the abort flag says) for a copy that was
