@@ -138,6 +138,18 @@ B200_API int b200_sdpa_decode(const void* d_q, const void* d_k, const void* d_v,
                               float scale, float logit_cap, void* d_workspace, size_t workspace_bytes,
                               void* stream);
 
+/* Prompt-shaped attention: `rows` query tokens of ONE sequence (q and out [rows, n, h]) over that
+ * sequence's cache (k / v [s_max, nkv, h], scales [s_max, nkv] for int8), row r attending over the
+ * first d_lengths[r] cached tokens. With d_lengths[r] = start + r + 1 this is the causal composite
+ * with several query tokens (tflite/delegates/xnnpack/xnnpack_delegate.cc:6639-6678 with the
+ * lower-triangular mask the converter emits). At most 8 query heads per KV head, head size 64, 128
+ * or 256; no additive mask. Workspace: b200_sdpa_rows_workspace_bytes. */
+B200_API size_t b200_sdpa_rows_workspace_bytes(int rows, int n, int nkv, int h, int s_max);
+B200_API int b200_sdpa_rows(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale,
+                            const float* d_v_scale, const int32_t* d_lengths, void* d_out, int rows, int n,
+                            int nkv, int h, int s_max, int q_dtype, int kv_dtype, float scale, float logit_cap,
+                            void* d_workspace, size_t workspace_bytes, void* stream);
+
 /* ---- attention decode step without any allocation --------------------------
  * No counterpart in the reference: this entry point exists for callers of THIS
  * library that are not allowed to allocate device memory (a serving loop that

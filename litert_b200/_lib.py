@@ -29,6 +29,8 @@ SIGNATURES = {
     "b200_fc_hybrid": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "b200_fc_w4": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "b200_sdpa_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "b200_sdpa_rows_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "b200_sdpa_rows": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _sz, _vp]),
     "b200_sdpa_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _sz,
                               _vp]),
     "b200_sdpa_static_workspace_limit": (_sz, []),

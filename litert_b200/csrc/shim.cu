@@ -292,4 +292,38 @@ int b200_sdpa_decode(const void* d_q, const void* d_k, const void* d_v, const fl
   return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_sdpa_decode");
 }
 
+size_t b200_sdpa_rows_workspace_bytes(int rows, int n, int nkv, int h, int s_max) {
+  if (rows <= 0 || n <= 0 || nkv <= 0 || h <= 0 || s_max <= 0) return 0;
+  return b200::sdpa_workspace_bytes(rows, n, nkv, h, s_max, 1);
+}
+
+int b200_sdpa_rows(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale, const float* d_v_scale,
+                   const int32_t* d_lengths, void* d_out, int rows, int n, int nkv, int h, int s_max, int q_dtype,
+                   int kv_dtype, float scale, float logit_cap, void* d_workspace, size_t workspace_bytes, void* stream) {
+  if (!d_q || !d_k || !d_v || !d_out || !d_lengths) return fail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa_rows: null pointer");
+  if (rows <= 0 || n <= 0 || nkv <= 0 || h <= 0 || s_max <= 0 || n % nkv != 0)
+    return fail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa_rows: bad shape rows=%d n=%d nkv=%d h=%d s=%d", rows, n, nkv, h, s_max);
+  if (q_dtype != B200_DTYPE_F16 && q_dtype != B200_DTYPE_F32) return fail(B200_ERR_UNSUPPORTED, "b200_sdpa_rows: q dtype %d", q_dtype);
+  if (kv_dtype < B200_DTYPE_F16 || kv_dtype > B200_DTYPE_F32) return fail(B200_ERR_UNSUPPORTED, "b200_sdpa_rows: kv dtype %d", kv_dtype);
+  if (kv_dtype == B200_DTYPE_I8 && (!d_k_scale || !d_v_scale)) return fail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa_rows: int8 cache needs scales");
+  if (n / nkv > 8 || (h != 64 && h != 128 && h != 256))
+    return fail(B200_ERR_UNSUPPORTED, "b200_sdpa_rows: at most 8 query heads per KV head, head size 64, 128 or 256");
+  if (!d_workspace || workspace_bytes < b200::sdpa_workspace_bytes(rows, n, nkv, h, s_max, 1))
+    return fail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa_rows: workspace too small (b200_sdpa_rows_workspace_bytes)");
+  b200::SdpaParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = d_q; p.k = d_k; p.v = d_v; p.k_scale = d_k_scale; p.v_scale = d_v_scale;
+  p.lengths = d_lengths; p.out = d_out;
+  p.b = rows; p.n = n; p.nkv = nkv; p.h = h; p.s_max = s_max;
+  p.q_dtype = q_dtype == B200_DTYPE_F32 ? 1 : 0;
+  p.kv_dtype = kv_dtype;
+  p.scale = scale > 0.0f ? scale : 1.0f / sqrtf((float)h);
+  p.logit_cap = logit_cap;
+  p.ws = static_cast<float*>(d_workspace);
+  p.ws_bytes = workspace_bytes;
+  p.shared_kv = 1;
+  cudaError_t e = b200::launch_sdpa_decode(p, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_sdpa_rows");
+}
+
 }  // extern "C"

@@ -190,3 +190,25 @@ def sdpa_decode(q, k, v, lengths=None, mask=None, scale=None, logit_cap=0.0, k_s
                                _ptr(out), b, n, nkv, h, s_max, _DT[q.dtype], _DT[k.dtype],
                                float(scale) if scale else 0.0, float(logit_cap), _ptr(wsb), wsb.numel(), _stream()))
     return out
+
+
+def sdpa_rows(q, k, v, lengths, scale=None, logit_cap=0.0, k_scale=None, v_scale=None):
+    """The composite with several query tokens of ONE sequence: q [rows, n, h]; k, v [s_max, nkv, h] (that
+    sequence's cache); row r attends over the first lengths[r] cached tokens (lengths[r] = start + r + 1 is
+    the causal mask). Returns [rows, n, h] in q's dtype."""
+    lib = _lib.load()
+    if q.dtype not in (torch.float16, torch.float32) or k.dtype not in _DT or v.dtype != k.dtype:
+        raise B200Error("unsupported dtypes for sdpa_rows")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    rows, n, h = q.shape
+    s_max, nkv = k.shape[0], k.shape[1]
+    lengths = _need(lengths, torch.int32, "lengths")
+    k_scale = _need(k_scale, torch.float32, "k_scale")
+    v_scale = _need(v_scale, torch.float32, "v_scale")
+    out = torch.empty_like(q)
+    need = lib.b200_sdpa_rows_workspace_bytes(rows, n, nkv, h, s_max)
+    wsb = torch.empty(max(int(need), 16), dtype=torch.uint8, device=q.device)
+    check(lib.b200_sdpa_rows(_ptr(q), _ptr(k), _ptr(v), _ptr(k_scale), _ptr(v_scale), _ptr(lengths), _ptr(out), rows, n,
+                             nkv, h, s_max, _DT[q.dtype], _DT[k.dtype], float(scale) if scale else 0.0,
+                             float(logit_cap), _ptr(wsb), wsb.numel(), _stream()))
+    return out

@@ -203,3 +203,39 @@ def test_prefill_rejects_what_does_not_fit():
     with pytest.raises(B200Error):
         d.prefill(np.zeros(3, np.int32))  # 30 cached + 3 > 32
     d.close()
+
+
+@pytest.mark.parametrize("head_dim,heads", [(128, 4), (256, 8), (256, 3)])
+@pytest.mark.parametrize("kv_dtype", ["f16", "i8"])
+def test_prefill_at_wide_heads_equals_stepping(kv_dtype, head_dim, heads):
+    """The benchmark's head size (256, eight query heads on one KV head) and 128, which the small test
+    model above does not reach: prompt pass against the same decoder fed one token per step. The two
+    differ only in the order attention sums over tokens, but this shape (a 2048-wide attention output
+    quantized to int8 in front of a 256-wide model) turns those last-bit differences into int8 flips
+    more often than the small model: 0.02-0.04 relative L2 measured for every attention kernel variant
+    against every other, hence the whole-graph bound used against the CPU graph."""
+    from litert_b200 import decoder as dec
+
+    cfg = dict(n_layers=2, d_model=256, n_heads=heads, n_kv_heads=1, head_dim=head_dim, d_ff=512, vocab=800)
+    total, max_seq = 333, 352
+    weights = dec.make_weights(cfg, seed=17)
+    prompt = np.random.default_rng(23).integers(0, cfg["vocab"], total).astype(np.int32)
+    stepped = dec.Decoder(cfg, max_seq=max_seq, max_batch=1, weights=weights, kv_dtype=kv_dtype)
+    for t in range(total):
+        nxt_s, logits_s = stepped.step(prompt[t:t + 1], want_logits=(t == total - 1))
+    filled = dec.Decoder(cfg, max_seq=max_seq, max_batch=1, weights=weights, kv_dtype=kv_dtype)
+    first = filled.prefill(prompt)
+    ls = logits_s.cpu().numpy()[0]
+    top2 = np.sort(ls)[-2:]
+    if top2[1] - top2[0] > 0.05 * (ls.max() - ls.min()):
+        assert first == int(nxt_s[0])
+    tok = nxt_s[:1]
+    for s in range(3):
+        nxt_s, logits_s = stepped.step(tok, want_logits=True)
+        _, logits_f = filled.step(tok, want_logits=True)
+        a, b = logits_f.cpu().numpy()[0], logits_s.cpu().numpy()[0]
+        err = np.linalg.norm(a - b) / np.linalg.norm(b)
+        assert err <= 6e-2, (s, err)
+        tok = nxt_s[:1]
+    stepped.close()
+    filled.close()

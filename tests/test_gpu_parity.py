@@ -365,3 +365,35 @@ def test_sdpa_f32_cache_mask_and_logit_cap_fast_path(ops, oracle, ws):
     out = ops.sdpa_decode(dev(q), dev(k), dev(v), None, dev(mask), logit_cap=30.0, ws=ws).cpu().numpy()
     want = oracle.sdpa_f32(q, k, v, mask, None, 30.0)
     assert rel_err(out, want) <= 2e-2
+
+
+@pytest.mark.parametrize("n,nkv,h", [(8, 1, 256), (8, 1, 128), (4, 2, 64), (3, 1, 256), (16, 2, 128)])
+@pytest.mark.parametrize("kv", ["f16", "i8", "f32"])
+def test_sdpa_rows_causal_prompt(ops, oracle, n, nkv, h, kv):
+    """Several query tokens of one sequence (the prompt pass): row r attends over the cached tokens up to
+    its own position, start + r. 301 rows behind 37 cached tokens: a last CTA with one row, chunks that
+    end inside a 64-token stage, rows whose limit falls inside the CTA's first stage."""
+    rng = np.random.default_rng(n * 1000 + h + nkv)
+    rows, start, s_max = 301, 37, 400
+    q = rng.standard_normal((rows, n, h)).astype(np.float16)
+    k = rng.standard_normal((s_max, nkv, h)).astype(np.float16)
+    v = rng.standard_normal((s_max, nkv, h)).astype(np.float16)
+    lengths = (start + 1 + np.arange(rows)).astype(np.int32)
+    scale = 1.0 / np.sqrt(h)
+    ksc = vsc = None
+    kd, vd = k, v
+    if kv == "i8":
+        kd, ksc = workloads.quantize_kv_per_token(k[None])
+        vd, vsc = workloads.quantize_kv_per_token(v[None])
+        kd, vd, ksc, vsc = kd[0], vd[0], ksc[0], vsc[0]
+    elif kv == "f32":
+        kd, vd = k.astype(np.float32), v.astype(np.float32)
+    out = ops.sdpa_rows(dev(q), dev(kd), dev(vd), dev(lengths), scale=scale,
+                        k_scale=None if ksc is None else dev(ksc), v_scale=None if vsc is None else dev(vsc))
+    kf = kd.astype(np.float32) if ksc is None else kd.astype(np.float32) * ksc[..., None]
+    vf = vd.astype(np.float32) if vsc is None else vd.astype(np.float32) * vsc[..., None]
+    got = out.float().cpu().numpy()
+    for r in list(range(0, rows, 7)) + [rows - 1]:
+        L = int(lengths[r])
+        want = oracle.sdpa_f32(q[r][None, None].astype(np.float32), kf[None, :L], vf[None, :L], None, scale)[0, 0]
+        assert rel_err(got[r], want) <= 2e-2, r
