@@ -68,6 +68,15 @@ B200_API int b200_zero_workspace_init(void* d_zero_ws, void* stream);
 B200_API size_t b200_fc_scratch_bytes(int m, int k);
 /* Copies the status word to the host (synchronises the stream). 0 = ok. */
 B200_API int b200_read_status(void* d_zero_ws, void* stream, int* status_out);
+/* Every wait inside a kernel (on a pipeline stage, an accumulator, a tensor-
+ * parallel peer) gives up after a budget, one second unless set here: the kernel
+ * then records a status code, finishes without waiting and the host sees
+ * B200_ERR_KERNEL_TIMEOUT. The status word is sticky (later waits give up at
+ * once, so a broken step ends fast) and an aborted launch may leave split-K
+ * counters behind: after a time-out call b200_clear_status before the workspace
+ * is used again. b200_set_wait_budget synchronises the stream. */
+B200_API int b200_set_wait_budget(void* d_zero_ws, unsigned long long nanoseconds, void* stream);
+B200_API int b200_clear_status(void* d_zero_ws, void* stream);
 
 /* ---- weight preparation (once per constant tensor) ----------------------
  * int8 weights [n,k] row-major, as a FULLY_CONNECTED filter tensor lies in
@@ -170,6 +179,93 @@ B200_API int b200_sdpa_decode_static(const void* d_q, const void* d_k, const voi
                                      float scale, float logit_cap, void* stream);
 B200_API const char* b200_sdpa_static_last_error(void);
 
+/* ---- decoder glue ops -------------------------------------------------------
+ * The ops a decoder-only graph has between its projections, as
+ * tensor/examples/gemma3/gemma3_graph.cc authors them out of TFLite builtins and
+ * composites, each fused with the per-row int8 quantization of the hybrid
+ * FULLY_CONNECTED that consumes its result (tensor_utils::BatchQuantizeFloats,
+ * tflite/kernels/internal/reference/portable_tensor_utils.cc:74-119, asymmetric).
+ * Quantized rows are written in the tiled layout the GEMM kernels stream
+ * ("tiled rows": b200_tiled_rows_bytes(m, k) bytes, 128-byte aligned, m rows of
+ * k int8 values; b200_untile_rows gives the row-major view) and go straight into
+ * b200_fc_hybrid_quantized, so that a float activation row is never written. */
+B200_API const char* b200_glue_last_error(void);
+B200_API size_t b200_tiled_rows_bytes(int m, int k);
+B200_API int b200_untile_rows(const int8_t* d_q_tiled, int m, int k, int8_t* d_q_rowmajor, void* stream);
+
+/* Hybrid EMBEDDING_LOOKUP (tflite/kernels/embedding_lookup.cc:EvalHybrid:
+ * out[r,:] = table[ids[r],:] * row_scale[ids[r]]) followed by the graph's MUL by
+ * a constant (out_scale; 1 for none). An id outside [0, vocab) reads row 0. */
+B200_API int b200_embedding_lookup(const int32_t* d_ids, int rows, const int8_t* d_table, const float* d_row_scales,
+                                   int vocab, int d, float out_scale, float* d_out, void* stream);
+
+/* Residual ADD + RMS norm (odml.rms_norm / the MUL-MEAN-RSQRT-MUL chain,
+ * gemma3_graph.cc RmsNorm) + row quantization: h += delta (delta may be NULL),
+ * x = h * rsqrt(mean(h^2) + eps) * gain, x quantized per row. h [rows, d] is
+ * updated in place; d <= 12288. */
+B200_API int b200_add_rmsnorm_quantize(float* d_h, const float* d_delta, const float* d_gain, int rows, int d, float eps,
+                                       int8_t* d_q_tiled, float* d_scales, int32_t* d_zero_points, void* stream);
+
+/* GELU(approximate = tanh) * up (gemma3_graph.cc:118-146) + row quantization.
+ * d_gate_up [rows, 2 f]: the gate then the up projection of each row. */
+B200_API int b200_geglu_quantize(const float* d_gate_up, int rows, int f, int8_t* d_q_tiled, float* d_scales,
+                                 int32_t* d_zero_points, void* stream);
+
+/* Rotary embedding. In the reference graph cos and sin are INPUT tensors the host
+ * side prepares (gemma3_graph.cc:150-176: x * cos + rotate_half(x) * sin);
+ * b200_rope_table fills such a table on the host: h_cos_sin[(pos * head_dim / 2
+ * + i) * 2 + {0, 1}] = {cos, sin}(pos * base^(-2 i / head_dim)), pos < positions.
+ * b200_rope_kv_append rotates the query and key heads of d_qkv [rows, (heads + 2
+ * kv_heads) * head_dim] (row r at d_positions[r]; the table must cover positions
+ * 0..max_seq), writes the queries to d_q_out [rows, heads, head_dim] and appends
+ * key and value to the caches [batch, max_seq, kv_heads, head_dim] at that
+ * position: odml.update_kv_cache semantics
+ * (tflite/experimental/genai/kvcache.cc:230-340) on a device-resident fp16 or
+ * int8 cache (int8: one symmetric scale per token and KV head, max|row| / 127).
+ * one_sequence != 0: all rows are consecutive tokens of the sequence whose cache
+ * is passed. A position >= max_seq leaves the cache alone. */
+B200_API int b200_rope_table(float* h_cos_sin, int positions, int head_dim, float base);
+B200_API int b200_rope_kv_append(const float* d_qkv, int rows, int heads, int kv_heads, int head_dim,
+                                 const float* d_cos_sin, const int32_t* d_positions, int max_seq, float* d_q_out,
+                                 void* d_k_cache, void* d_v_cache, float* d_k_scale, float* d_v_scale, int kv_dtype,
+                                 int one_sequence, void* stream);
+
+/* Greedy pick per row of d_logits [rows, n]: the first index of the maximum, with
+ * the NaN rule of litert/vendors/nvidia/dispatch/greedy_sampler_kernel.cu:31-50
+ * (a NaN at index 0 wins, a NaN elsewhere never does). soft_cap > 0 compares
+ * cap * tanh(logit / cap) (litert/vendors/nvidia/trtllm/head_kernels.cu:35-43). */
+B200_API size_t b200_argmax_workspace_bytes(int rows);
+B200_API int b200_argmax_rows(const float* d_logits, int rows, int n, float soft_cap, int32_t* d_out,
+                              void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* One decode step of a layer's attention in ONE launch, for multi-query
+ * attention (one KV head, at most 8 query heads, head size 64/128/256, at most
+ * 9 sequences): b200_rope_kv_append + b200_sdpa_decode over the first
+ * d_positions[b] + 1 cached tokens + row quantization of the [batch, heads *
+ * head_dim] result. d_qkv [batch, (heads + 2) * head_dim]. */
+B200_API int b200_attention_step_supported(int heads, int kv_heads, int head_dim, int kv_dtype);
+B200_API int b200_attention_step(const float* d_qkv, const int32_t* d_positions, const float* d_cos_sin,
+                                 void* d_k_cache, void* d_v_cache, float* d_k_scale, float* d_v_scale, int batch,
+                                 int heads, int head_dim, int max_seq, int kv_dtype, float scale, int8_t* d_q_tiled,
+                                 float* d_scales, int32_t* d_zero_points, void* stream);
+
+/* b200_sdpa_decode whose [b, n * h] result leaves as quantized tiled rows (the
+ * attention-output projection's input) instead of floats. fp16 / int8 caches,
+ * at most 8 query heads per KV head, head size 64/128/256. */
+B200_API int b200_sdpa_decode_quantized(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale,
+                                        const float* d_v_scale, const int32_t* d_lengths, int b, int n, int nkv, int h,
+                                        int s_max, int q_dtype, int kv_dtype, float scale, int8_t* d_q_tiled,
+                                        float* d_scales, int32_t* d_zero_points, void* d_workspace,
+                                        size_t workspace_bytes, void* stream);
+
+/* b200_fc_hybrid on rows that are already quantized (tiled rows + per-row scale
+ * and zero point from one of the ops above): the second half of EvalHybridDense
+ * (tflite/kernels/fully_connected.cc:797-858). */
+B200_API int b200_fc_hybrid_quantized(const int8_t* d_q_tiled, const float* d_scales, const int32_t* d_zero_points,
+                                      int m, int k, const void* d_w_packed, int n, const int32_t* d_row_sums,
+                                      const float* d_w_scales, int per_channel, const float* d_bias, int activation,
+                                      float* d_y, void* d_zero_ws, void* stream);
+
 /* ---- Gemma-shaped decoder, one decode step per call ---------------------------
  * A resident decoder for the decode benchmark: every projection is a dynamic-range
  * hybrid FULLY_CONNECTED (b200_fc_hybrid semantics: per-row asymmetric input
@@ -238,7 +334,22 @@ B200_API int b200_decoder_init_nccl(b200_decoder* dec, const void* unique_id);
 B200_API int b200_decoder_exchange_handle(b200_decoder* dec, void* handle_out, size_t bytes);
 /* handles: tp_size handles, bytes_per_handle apart, in rank order (the own entry is ignored). */
 B200_API int b200_decoder_connect_peers(b200_decoder* dec, const void* handles, size_t bytes_per_handle);
+/* The same for ranks that live in ONE process (one thread per GPU with peer access enabled, or a
+ * test): d_exchange_buffers[j] is rank j's b200_decoder_exchange_buffer as addressable from this
+ * rank's device (the own entry is ignored), each b200_decoder_exchange_bytes long. */
+B200_API size_t b200_decoder_exchange_bytes(const b200_decoder* dec);
+B200_API void* b200_decoder_exchange_buffer(b200_decoder* dec);
+B200_API int b200_decoder_connect_peer_pointers(b200_decoder* dec, void* const* d_exchange_buffers);
+/* Forgets every sequence (positions to zero) and clears the fault state below. */
 B200_API int b200_decoder_reset(b200_decoder* dec);
+/* Bounded waits: a kernel that waits longer than the budget (one second unless set here) for a
+ * pipeline stage or for a tensor-parallel peer records a status code and finishes without waiting;
+ * the step or prompt pass that notices it returns B200_ERR_KERNEL_TIMEOUT, its results are void, and
+ * it has already cleared the fault state (status word, split-K counters) so that the next call
+ * starts clean. b200_decoder_clear_fault does the same on demand (synchronises). After a peer
+ * time-out the ranks' step counters may differ: reset every rank before going on. */
+B200_API int b200_decoder_set_wait_budget(b200_decoder* dec, unsigned long long nanoseconds);
+B200_API int b200_decoder_clear_fault(b200_decoder* dec);
 /* Declares h_positions[i] tokens already cached for sequence i (cache rows never written hold
  * zeros): lets a caller resume from a cache filled elsewhere, or time a step at a given depth. */
 B200_API int b200_decoder_set_positions(b200_decoder* dec, const int32_t* h_positions, int batch);

@@ -19,6 +19,8 @@ SIGNATURES = {
     "b200_zero_workspace_init": (_i, [_vp, _vp]),
     "b200_fc_scratch_bytes": (_sz, [_i, _i]),
     "b200_read_status": (_i, [_vp, _vp, ctypes.POINTER(_i)]),
+    "b200_set_wait_budget": (_i, [_vp, ctypes.c_ulonglong, _vp]),
+    "b200_clear_status": (_i, [_vp, _vp]),
     "b200_packed_w8_bytes": (_sz, [_i, _i]),
     "b200_pack_w8": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "b200_packed_w4_bytes": (_sz, [_i, _i]),
@@ -36,6 +38,21 @@ SIGNATURES = {
     "b200_sdpa_static_workspace_limit": (_sz, []),
     "b200_sdpa_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
     "b200_sdpa_static_last_error": (ctypes.c_char_p, []),
+    "b200_glue_last_error": (ctypes.c_char_p, []),
+    "b200_tiled_rows_bytes": (_sz, [_i, _i]),
+    "b200_untile_rows": (_i, [_vp, _i, _i, _vp, _vp]),
+    "b200_embedding_lookup": (_i, [_vp, _i, _vp, _vp, _i, _i, _f, _vp, _vp]),
+    "b200_add_rmsnorm_quantize": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp, _vp, _vp, _vp]),
+    "b200_geglu_quantize": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp]),
+    "b200_rope_table": (_i, [_vp, _i, _i, _f]),
+    "b200_rope_kv_append": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "b200_argmax_workspace_bytes": (_sz, [_i]),
+    "b200_argmax_rows": (_i, [_vp, _i, _i, _f, _vp, _vp, _sz, _vp]),
+    "b200_attention_step_supported": (_i, [_i, _i, _i, _i]),
+    "b200_attention_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp]),
+    "b200_sdpa_decode_quantized": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp,
+                                        _vp, _sz, _vp]),
+    "b200_fc_hybrid_quantized": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp]),
     "b200_decoder_create": (_i, [_vp, _vp, ctypes.POINTER(_vp)]),
     "b200_decoder_destroy": (None, [_vp]),
     "b200_decoder_set_layer": (_i, [_vp, _i, _vp]),
@@ -45,6 +62,11 @@ SIGNATURES = {
     "b200_decoder_init_nccl": (_i, [_vp, _vp]),
     "b200_decoder_exchange_handle": (_i, [_vp, _vp, _sz]),
     "b200_decoder_connect_peers": (_i, [_vp, _vp, _sz]),
+    "b200_decoder_exchange_bytes": (_sz, [_vp]),
+    "b200_decoder_exchange_buffer": (_vp, [_vp]),
+    "b200_decoder_connect_peer_pointers": (_i, [_vp, _vp]),
+    "b200_decoder_set_wait_budget": (_i, [_vp, ctypes.c_ulonglong]),
+    "b200_decoder_clear_fault": (_i, [_vp]),
     "b200_decoder_reset": (_i, [_vp]),
     "b200_decoder_set_positions": (_i, [_vp, _vp, _i]),
     "b200_decoder_step": (_i, [_vp, _vp, _i, _vp, _vp]),

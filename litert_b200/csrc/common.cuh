@@ -75,7 +75,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // the wait had succeeded: control flow stays uniform (every barrier is still
 // reached, every accumulator still freed), later waits return at once, the
 // kernel ends, and the host sees a non-zero status instead of a hung GPU.
+// The budget of one wait is one second unless the host wrote another value (nanoseconds, non-zero)
+// into the 64-bit word that follows the status word's 8 bytes (b200_set_wait_budget): read on the
+// slow path only, after the first polls have failed.
 constexpr unsigned long long kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // one second per wait
+constexpr int kStatusBudgetWordOffsetInts = 2;
+
+__device__ __forceinline__ unsigned long long wait_budget_ns(const int* status) {
+  if (!status) return kWaitBudgetNs;
+  const unsigned long long b =
+      *reinterpret_cast<const volatile unsigned long long*>(status + kStatusBudgetWordOffsetInts);
+  return b ? b : kWaitBudgetNs;
+}
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
@@ -88,11 +99,12 @@ __device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity
   if (*abort_flag) return;
   if (mbar_try_wait(bar, parity)) return;
   const unsigned long long t0 = global_timer_ns();
+  const unsigned long long budget = wait_budget_ns(status);
   for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return;
     if ((i & 63u) == 63u) {
       if (*abort_flag) return;
-      if (global_timer_ns() - t0 > kWaitBudgetNs) break;
+      if (global_timer_ns() - t0 > budget) break;
     }
   }
   *abort_flag = 1;

@@ -71,6 +71,7 @@ struct b200_decoder {
   std::vector<std::unique_ptr<Layer>> layers;
   Projection lm_head;
   DevBuf embed_table, embed_scales, final_norm;
+  DevBuf rope_cs;  // {cos, sin} of the rotation angles, [max_seq + 1][head_dim / 2], computed on the host
   // activations and scratch
   DevBuf tokens, next_tokens, positions, attn_len;
   DevBuf h, h2, qkv, q, attn, gate_up, logits;  // h / h2: residual stream, ping-pong when the norm is fused into a GEMV
@@ -89,6 +90,7 @@ struct b200_decoder {
   size_t off_epoch = 0, off_part_a = 0, off_part_b = 0, off_pairs = 0;
   uint8_t* peer_comm[b200::kMaxTpRanks] = {nullptr};  // peers' exchange buffers mapped here (own entry: comm.p)
   bool peers_connected = false;
+  bool peers_are_ipc = true;  // peer_comm entries came from cudaIpcOpenMemHandle (closed at destroy)
   b200_allreduce_fn allreduce = nullptr;
   void* allreduce_user = nullptr;
   void* nccl_comm = nullptr;
@@ -302,7 +304,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
   };
   unsigned long long* epoch = fused ? reinterpret_cast<unsigned long long*>(d->comm.as<uint8_t>() + d->off_epoch) : nullptr;
   GLUE_CUDA(launch_embed(d->tokens.as<int32_t>(), d->embed_table.as<int8_t>(), d->embed_scales.as<float>(), batch,
-                        c.d_model, c.embed_scale, d->h.as<float>(), d->positions.as<int32_t>(),
+                        c.vocab, c.d_model, c.embed_scale, d->h.as<float>(), d->positions.as<int32_t>(),
                         d->attn_len.as<int32_t>(), epoch, s));
   count();
   // Opt-in (B200_FUSED_PROLOGUE=1): with one GPU and a decode-sized batch the residual add, RMS norm
@@ -365,7 +367,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
       ap.h = c.head_dim;
       ap.s_max = c.max_seq;
       ap.kv_dtype = c.kv_dtype == B200_DTYPE_I8 ? 1 : 0;
-      ap.rope_base = c.rope_base;
+      ap.rope_cs = d->rope_cs.as<float2>();
       ap.scale = 1.0f / sqrtf((float)c.head_dim);
       ap.q_tiled_out = d->q_a.as<int8_t>();
       ap.out_scales = d->sc_a.as<float>();
@@ -379,7 +381,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
       }
       count();
     } else {
-      if (!(skip & 2)) GLUE_CUDA(launch_rope_cache(d->qkv.as<float>(), batch, d->hl, d->kvl, c.head_dim, c.rope_base,
+      if (!(skip & 2)) GLUE_CUDA(launch_rope_cache(d->qkv.as<float>(), batch, d->hl, d->kvl, c.head_dim, d->rope_cs.as<float2>(),
                                  d->positions.as<int32_t>(), c.max_seq, d->q.as<float>(), L.k_cache.p, L.v_cache.p,
                                  L.k_scale.as<float>(), L.v_scale.as<float>(), c.kv_dtype == B200_DTYPE_I8, 0, s));
       count();
@@ -447,7 +449,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
     if (!(skip & 256)) DEC_CUDA(run_fc(d, d->lm_head, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), logits));
   }
   if (!tp) {
-    GLUE_CUDA(launch_argmax(logits, batch, c.vocab, 0, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
+    GLUE_CUDA(launch_argmax(logits, batch, c.vocab, 0, 0.0f, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
                            d->next_tokens.as<int32_t>(), d->positions.as<int32_t>(), c.max_seq, nullptr, s));
     count(2);
     return B200_OK;
@@ -456,7 +458,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
   const float2* pairs[kMaxTpRanks] = {nullptr};
   if (fused) {
     float2* own = reinterpret_cast<float2*>(d->comm.as<uint8_t>() + d->off_pairs);
-    GLUE_CUDA(launch_argmax(logits, batch, d->vl, c.tp_rank * d->vl, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
+    GLUE_CUDA(launch_argmax(logits, batch, d->vl, c.tp_rank * d->vl, 0.0f, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
                            nullptr, nullptr, c.max_seq, own, s));
     for (int j = 0; j < c.tp_size; ++j) pairs[j] = reinterpret_cast<const float2*>(d->peer_comm[j] + d->off_pairs);
     const TpExchange x = make_exchange(d, 2 * c.n_layers, d->off_pairs);
@@ -466,7 +468,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
     // gather through the sum collective: every rank fills its own slot of a zeroed table
     float2* table = d->gather.as<float2>();
     DEC_CUDA(cudaMemsetAsync(table, 0, sizeof(float2) * c.tp_size * c.max_batch, s));
-    GLUE_CUDA(launch_argmax(logits, batch, d->vl, c.tp_rank * d->vl, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
+    GLUE_CUDA(launch_argmax(logits, batch, d->vl, c.tp_rank * d->vl, 0.0f, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
                            nullptr, nullptr, c.max_seq, table + (size_t)c.tp_rank * c.max_batch, s));
     if (int rc = reduce(reinterpret_cast<float*>(table), (size_t)2 * c.tp_size * c.max_batch)) return rc;
     for (int j = 0; j < c.tp_size; ++j) pairs[j] = table + (size_t)j * c.max_batch;
@@ -532,7 +534,7 @@ int enqueue_prefill_chunk(b200_decoder* d, int seq, int rows, bool pick) {
   };
   const size_t kv_first = (size_t)seq * c.max_seq * d->kvl;  // first token row of this sequence's cache
   const size_t kv_row = (size_t)c.head_dim * (i8 ? 1 : 2);
-  DEC_CUDA(launch_embed(f.tokens.as<int32_t>(), d->embed_table.as<int8_t>(), d->embed_scales.as<float>(), rows, c.d_model,
+  DEC_CUDA(launch_embed(f.tokens.as<int32_t>(), d->embed_table.as<int8_t>(), d->embed_scales.as<float>(), rows, c.vocab, c.d_model,
                         c.embed_scale, f.h.as<float>(), f.positions.as<int32_t>(), f.attn_len.as<int32_t>(), nullptr, s));
   for (int l = 0; l < c.n_layers; ++l) {
     Layer& L = *d->layers[l];
@@ -543,7 +545,7 @@ int enqueue_prefill_chunk(b200_decoder* d, int seq, int rows, bool pick) {
     DEC_CUDA(launch_add_norm_quant(f.h.as<float>(), l == 0 ? nullptr : f.down_out.as<float>(), L.norm1.as<float>(), rows, c.d_model,
                                    c.rms_eps, m_alloc, f.q_d.as<int8_t>(), f.sc_d.as<float>(), f.zp_d.as<int32_t>(), nullptr, s));
     DEC_CUDA(run_fc(d, L.qkv, rows, f.q_d.as<int8_t>(), f.sc_d.as<float>(), f.zp_d.as<int32_t>(), f.qkv.as<float>()));
-    DEC_CUDA(launch_rope_cache(f.qkv.as<float>(), rows, d->hl, d->kvl, c.head_dim, c.rope_base, f.positions.as<int32_t>(),
+    DEC_CUDA(launch_rope_cache(f.qkv.as<float>(), rows, d->hl, d->kvl, c.head_dim, d->rope_cs.as<float2>(), f.positions.as<int32_t>(),
                                c.max_seq, f.q.as<float>(), kc, vc, ks, vs, i8, 1, s));
     SdpaParams sp;
     memset(&sp, 0, sizeof(sp));
@@ -589,19 +591,29 @@ int enqueue_prefill_chunk(b200_decoder* d, int seq, int rows, bool pick) {
   DEC_CUDA(run_fc(d, d->lm_head, 1, f.q_d.as<int8_t>(), f.sc_d.as<float>(), f.zp_d.as<int32_t>(), logits));
   int32_t* scratch_pos = f.attn_len.as<int32_t>();  // the arg-max advances a position: not the sequence's, set by the caller
   if (!tp) {
-    DEC_CUDA(launch_argmax(logits, 1, c.vocab, 0, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
+    DEC_CUDA(launch_argmax(logits, 1, c.vocab, 0, 0.0f, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
                            d->next_tokens.as<int32_t>() + seq, scratch_pos, c.max_seq, nullptr, s));
     return B200_OK;
   }
   // every rank proposes the best of its vocabulary rows through the sum collective (zeroed table, own slot)
   float2* table = d->gather.as<float2>();
   DEC_CUDA(cudaMemsetAsync(table, 0, sizeof(float2) * c.tp_size * c.max_batch, s));
-  DEC_CUDA(launch_argmax(logits, 1, d->vl, c.tp_rank * d->vl, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(), nullptr, nullptr,
+  DEC_CUDA(launch_argmax(logits, 1, d->vl, c.tp_rank * d->vl, 0.0f, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(), nullptr, nullptr,
                          c.max_seq, table + (size_t)c.tp_rank * c.max_batch, s));
   if (int rc = reduce(reinterpret_cast<float*>(table), (size_t)2 * c.tp_size * c.max_batch)) return rc;
   const float2* pairs[kMaxTpRanks] = {nullptr};
   for (int j = 0; j < c.tp_size; ++j) pairs[j] = table + (size_t)j * c.max_batch;
   DEC_CUDA(launch_argmax_pick(pairs, c.tp_size, 1, d->next_tokens.as<int32_t>() + seq, scratch_pos, c.max_seq, nullptr, s));
+  return B200_OK;
+}
+
+// After a wait has run out: the status word is sticky and an aborted launch may have left split-K
+// counters or accumulator slots non-zero. Clears them (keeping the wait budget) so that the next call
+// starts from a clean workspace.
+int clear_fault(b200_decoder* d) {
+  uint8_t* z = d->zero_ws.as<uint8_t>();
+  DEC_CUDA(cudaMemsetAsync(z, 0, 8, d->stream));
+  DEC_CUDA(cudaMemsetAsync(z + 16, 0, zero_ws_part_off() - 16, d->stream));
   return B200_OK;
 }
 
@@ -731,6 +743,13 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
     DEC_CUDA(L.norm2.alloc(sizeof(float) * c.d_model));
   }
   DEC_CUDA(d->final_norm.alloc(sizeof(float) * c.d_model));
+  {
+    // the graph's cos / sin inputs: prepared once on the host, as the reference's host side does
+    std::vector<float> cs((size_t)(c.max_seq + 1) * (c.head_dim / 2) * 2);
+    fill_rope_table(cs.data(), c.max_seq + 1, c.head_dim, c.rope_base);
+    DEC_CUDA(d->rope_cs.alloc(sizeof(float) * cs.size()));
+    DEC_CUDA(cudaMemcpy(d->rope_cs.p, cs.data(), sizeof(float) * cs.size(), cudaMemcpyHostToDevice));
+  }
   DEC_CUDA(cudaStreamSynchronize(d->stream));
   *out = d.release();
   return B200_OK;
@@ -758,7 +777,7 @@ void b200_decoder_destroy(b200_decoder* d) {
   }
   for (auto& g : d->graph)
     if (g) cudaGraphExecDestroy(g);
-  if (d->peers_connected)
+  if (d->peers_connected && d->peers_are_ipc)
     for (int j = 0; j < d->cfg.tp_size; ++j)
       if (j != d->cfg.tp_rank && d->peer_comm[j]) cudaIpcCloseMemHandle(d->peer_comm[j]);
   nccl_release(d);
@@ -868,8 +887,42 @@ int b200_decoder_connect_peers(b200_decoder* d, const void* handles, size_t byte
 int b200_decoder_reset(b200_decoder* d) {
   if (!d) return dec_fail(B200_ERR_INVALID_ARGUMENT, "null decoder");
   DEC_CUDA(cudaMemsetAsync(d->positions.p, 0, sizeof(int32_t) * d->cfg.max_batch, d->stream));
+  return clear_fault(d);
+}
+
+int b200_decoder_clear_fault(b200_decoder* d) {
+  if (!d) return dec_fail(B200_ERR_INVALID_ARGUMENT, "null decoder");
+  int rc = clear_fault(d);
+  if (rc) return rc;
+  DEC_CUDA(cudaStreamSynchronize(d->stream));
   return B200_OK;
 }
+
+int b200_decoder_set_wait_budget(b200_decoder* d, unsigned long long nanoseconds) {
+  if (!d) return dec_fail(B200_ERR_INVALID_ARGUMENT, "null decoder");
+  DEC_CUDA(cudaMemcpyAsync(d->zero_ws.as<uint8_t>() + 4 * kStatusBudgetWordOffsetInts, &nanoseconds, sizeof(nanoseconds),
+                           cudaMemcpyHostToDevice, d->stream));
+  DEC_CUDA(cudaStreamSynchronize(d->stream));
+  return B200_OK;
+}
+
+size_t b200_decoder_exchange_bytes(const b200_decoder* d) { return d ? d->comm.bytes : 0; }
+
+int b200_decoder_connect_peer_pointers(b200_decoder* d, void* const* d_exchange_buffers) {
+  if (!d || !d_exchange_buffers) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_connect_peer_pointers: null argument");
+  if (d->peers_connected) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_connect_peer_pointers: already connected");
+  const int T = d->cfg.tp_size;
+  for (int j = 0; j < T; ++j) {
+    if (j == d->cfg.tp_rank) continue;
+    if (!d_exchange_buffers[j]) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_connect_peer_pointers: null peer buffer");
+    d->peer_comm[j] = static_cast<uint8_t*>(d_exchange_buffers[j]);
+  }
+  d->peers_connected = T > 1;
+  d->peers_are_ipc = false;
+  return B200_OK;
+}
+
+void* b200_decoder_exchange_buffer(b200_decoder* d) { return d ? d->comm.p : nullptr; }
 
 int b200_decoder_set_positions(b200_decoder* d, const int32_t* h_positions, int batch) {
   if (!d || !h_positions || batch <= 0 || batch > d->cfg.max_batch) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_set_positions: bad argument");
@@ -901,7 +954,12 @@ int b200_decoder_step(b200_decoder* d, const int32_t* h_tokens, int batch, int32
     DEC_CUDA(cudaMemcpyAsync(h_status, d->zero_ws.p, sizeof(int32_t), cudaMemcpyDeviceToHost, d->stream));
     DEC_CUDA(cudaStreamSynchronize(d->stream));
     memcpy(h_next_tokens, d->h_next_pinned, sizeof(int32_t) * batch);
-    if (*h_status != 0) return dec_fail(B200_ERR_KERNEL_TIMEOUT, "b200_decoder_step: a device-side wait ran out");
+    if (*h_status != 0) {
+      const int code = *h_status;
+      clear_fault(d);  // this step's results are void; the next call finds a clean workspace
+      snprintf(g_dec_error, sizeof(g_dec_error), "b200_decoder_step: a device-side wait ran out (status %d)", code);
+      return B200_ERR_KERNEL_TIMEOUT;
+    }
   }
   return B200_OK;
 }
@@ -953,7 +1011,10 @@ int b200_decoder_prefill(b200_decoder* d, int seq, const int32_t* h_tokens, int 
   if (h_next_token) *h_next_token = next;
   int status = 0;
   DEC_CUDA(cudaMemcpy(&status, d->zero_ws.p, sizeof(int), cudaMemcpyDeviceToHost));
-  if (status != 0) return dec_fail(B200_ERR_KERNEL_TIMEOUT, "b200_decoder_prefill: a device-side wait ran out");
+  if (status != 0) {
+    clear_fault(d);
+    return dec_fail(B200_ERR_KERNEL_TIMEOUT, "b200_decoder_prefill: a device-side wait ran out");
+  }
   return B200_OK;
 }
 

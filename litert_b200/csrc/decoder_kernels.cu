@@ -9,6 +9,7 @@
 // :150-176), GELU(tanh) * up (:118-146), residual add, hybrid embedding lookup
 // (tflite/kernels/embedding_lookup.cc), first-index argmax.
 #include <cooperative_groups.h>
+#include <math_constants.h>
 
 #include "common.cuh"
 #include "decoder_kernels.h"
@@ -48,9 +49,10 @@ __device__ __forceinline__ void tp_handshake(const TpExchange& x, bool signaller
     }
     // after one wait has run out the status stays set and later waits give up at once
     const unsigned long long t0 = global_timer_ns();
+    const unsigned long long budget = wait_budget_ns(x.status);
     while (ld_acquire_sys(x.flags_in + j) < epoch) {
       if (*reinterpret_cast<volatile int*>(x.status) != 0) break;
-      if (global_timer_ns() - t0 > kWaitBudgetNs) {
+      if (global_timer_ns() - t0 > budget) {
         atomicCAS(x.status, 0, kStatusTimeoutPeer);
         break;
       }
@@ -63,7 +65,7 @@ __device__ __forceinline__ void tp_handshake(const TpExchange& x, bool signaller
 // h[b,:] = int8 embedding row * its scale * embed_scale; also attn_len = positions + 1.
 __global__ void __launch_bounds__(kRowThreads) embed_kernel(const int32_t* __restrict__ tokens,
                                                             const int8_t* __restrict__ table,
-                                                            const float* __restrict__ row_scales, int d,
+                                                            const float* __restrict__ row_scales, int vocab, int d,
                                                             float embed_scale, float* __restrict__ h,
                                                             const int32_t* __restrict__ positions,
                                                             int32_t* __restrict__ attn_len,
@@ -71,12 +73,15 @@ __global__ void __launch_bounds__(kRowThreads) embed_kernel(const int32_t* __res
   pdl_enter();
   if (step_epoch && blockIdx.x == 0 && threadIdx.x == 0) *step_epoch += 1ull;
   const int b = blockIdx.x;
-  const int tok = tokens[b];
+  // an id outside the table reads row 0 (the reference's op fails the invocation instead,
+  // tflite/kernels/embedding_lookup.cc: a kernel cannot, and must not read out of bounds)
+  int tok = tokens[b];
+  if (tok < 0 || tok >= vocab) tok = 0;
   const float s = row_scales[tok];
   const int8_t* row = table + (size_t)tok * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x)
     h[(size_t)b * d + i] = __fmul_rn(__fmul_rn((float)row[i], s), embed_scale);
-  if (threadIdx.x == 0) attn_len[b] = positions[b] + 1;
+  if (attn_len && threadIdx.x == 0) attn_len[b] = positions[b] + 1;
 }
 
 // Up to this many rows a glue kernel is one link of a latency chain (widest blocks, dry run, a cluster
@@ -254,9 +259,12 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
 // Rotary embedding of q and k from the fused qkv projection output, and the
 // cache append. grid (b, heads + kv_heads + kv_heads), head_dim / 2 threads. Row b appends to the
 // cache of sequence b, or, with one_sequence (a prompt pass), every row to the cache passed in.
+// The rotation is the graph's x * cos + rotate_half(x) * sin over the cos / sin tensors the host side
+// prepares (tensor/examples/gemma3/gemma3_graph.cc:150-176): rope_cs[pos][i] = {cos, sin} of pair i,
+// max_seq + 1 positions; every product and sum rounded on its own, as separate MUL and ADD ops give.
 template <bool KV_I8>
 __global__ void rope_cache_kernel(const float* __restrict__ qkv, int heads, int kv_heads, int head_dim,
-                                  float rope_base, const int32_t* __restrict__ positions, int max_seq,
+                                  const float2* __restrict__ rope_cs, const int32_t* __restrict__ positions, int max_seq,
                                   float* __restrict__ q_out, void* __restrict__ k_cache, void* __restrict__ v_cache,
                                   float* __restrict__ k_scale, float* __restrict__ v_scale, int one_sequence) {
   __shared__ float red[32];
@@ -267,10 +275,9 @@ __global__ void rope_cache_kernel(const float* __restrict__ qkv, int heads, int 
   float x1 = src[i], x2 = src[i + half];
   const bool is_v = slot >= heads + kv_heads;
   if (!is_v) {
-    const float freq = powf(rope_base, -2.0f * (float)i / (float)head_dim);
-    float sn, cs;
-    sincosf((float)pos * freq, &sn, &cs);
-    const float r1 = x1 * cs - x2 * sn, r2 = x2 * cs + x1 * sn;
+    const float2 r = rope_cs[(size_t)min(pos, max_seq) * half + i];
+    const float r1 = __fsub_rn(__fmul_rn(x1, r.x), __fmul_rn(x2, r.y));
+    const float r2 = __fadd_rn(__fmul_rn(x2, r.x), __fmul_rn(x1, r.y));
     x1 = r1;
     x2 = r2;
   }
@@ -287,10 +294,10 @@ __global__ void rope_cache_kernel(const float* __restrict__ qkv, int heads, int 
     // symmetric per token and kv head: scale = max|row| / 127
     float amax = fmaxf(fabsf(x1), fabsf(x2));
     amax = block_reduce(amax, [](float a, float c) { return fmaxf(a, c); }, 0.0f, red);
-    const float sc = amax > 0.0f ? amax / 127.0f : 1.0f;
+    const float sc = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
     int8_t* dst = static_cast<int8_t*>(is_v ? v_cache : k_cache) + tok * head_dim;
-    dst[i] = (int8_t)max(-127, min(127, __float2int_rn(x1 / sc)));
-    dst[i + half] = (int8_t)max(-127, min(127, __float2int_rn(x2 / sc)));
+    dst[i] = (int8_t)max(-127, min(127, __float2int_rn(__fdiv_rn(x1, sc))));
+    dst[i + half] = (int8_t)max(-127, min(127, __float2int_rn(__fdiv_rn(x2, sc))));
     if (i == 0) (is_v ? v_scale : k_scale)[tok] = sc;
   } else {
     __half* dst = static_cast<__half*>(is_v ? v_cache : k_cache) + tok * head_dim;
@@ -304,14 +311,25 @@ struct BestPair {
   int i;
 };
 __device__ __forceinline__ BestPair better(BestPair a, BestPair b) {
-  // larger value wins; ties go to the lower index (first-index argmax)
+  // The serial scan `if (x[i] > x[best]) best = i` from best = 0, whatever the order pairs are
+  // combined in (litert/vendors/nvidia/dispatch/greedy_sampler_kernel.cu:31-50): a NaN at index 0
+  // wins outright, a NaN anywhere else never does; otherwise the larger value, ties to the lower index.
+  if (a.i == 0 && isnan(a.v)) return a;
+  if (b.i == 0 && isnan(b.v)) return b;
+  if (isnan(a.v)) return b;
+  if (isnan(b.v)) return a;
   if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
   return a;
 }
 
 // grid (parts, b): each CTA scans a slice of the row.
+__device__ __forceinline__ float soft_capped(float v, float inv_cap, float cap) {
+  // litert/vendors/nvidia/trtllm/head_kernels.cu:35-43: tanh(logit / cap) * cap
+  return cap > 0.0f ? __fmul_rn(tanhf(__fmul_rn(v, inv_cap)), cap) : v;
+}
+
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ logits, int n, int parts,
-                                                             float* __restrict__ part_val,
+                                                             float soft_cap, float* __restrict__ part_val,
                                                              int32_t* __restrict__ part_idx) {
   __shared__ float sv[8];
   __shared__ int si[8];
@@ -320,8 +338,10 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
   const int per = (n + parts - 1) / parts;
   const int lo = part * per, hi = min(n, lo + per);
   const float* row = logits + (size_t)b * n;
-  BestPair best{lo < n ? row[lo] : -3.402823466e+38f, lo < n ? lo : 0x7fffffff};
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) best = better(best, BestPair{row[i], i});
+  const float inv_cap = soft_cap > 0.0f ? __fdiv_rn(1.0f, soft_cap) : 0.0f;
+  BestPair best{lo < n ? soft_capped(row[lo], inv_cap, soft_cap) : -CUDART_INF_F, lo < n ? lo : 0x7fffffff};
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x)
+    best = better(best, BestPair{soft_capped(row[i], inv_cap, soft_cap), i});
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     BestPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
@@ -358,7 +378,7 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val, const in
       pair_out[b] = make_float2(best.v, (float)(best.i + idx_offset));  // exact below 2^24
     } else {
       next_tokens[b] = best.i + idx_offset;
-      if (positions[b] < max_seq) positions[b] += 1;
+      if (positions && positions[b] < max_seq) positions[b] += 1;
     }
   }
 }
@@ -374,7 +394,7 @@ __global__ void argmax_pick_kernel(PairTable pairs, int tp_size, int32_t* __rest
   if (xch.tp_size > 1) tp_handshake(xch, blockIdx.x == 0);
   const int b = blockIdx.x;
   if (threadIdx.x == 0) {
-    BestPair best{-3.402823466e+38f, 0x7fffffff};
+    BestPair best{-CUDART_INF_F, 0x7fffffff};
     for (int j = 0; j < tp_size; ++j) {
       const float* pj = reinterpret_cast<const float*>(pairs.p[j] + b);
       const float v = ld_peer(pj), fi = ld_peer(pj + 1);
@@ -388,10 +408,21 @@ __global__ void argmax_pick_kernel(PairTable pairs, int tp_size, int32_t* __rest
 
 }  // namespace
 
-cudaError_t launch_embed(const int32_t* tokens, const int8_t* table, const float* row_scales, int batch, int d,
+void fill_rope_table(float* cs, int positions, int head_dim, float base) {
+  const int half = head_dim / 2;
+  for (int pos = 0; pos < positions; ++pos)
+    for (int i = 0; i < half; ++i) {
+      const float freq = powf(base, -2.0f * (float)i / (float)head_dim);
+      const float ang = (float)pos * freq;
+      cs[((size_t)pos * half + i) * 2] = cosf(ang);
+      cs[((size_t)pos * half + i) * 2 + 1] = sinf(ang);
+    }
+}
+
+cudaError_t launch_embed(const int32_t* tokens, const int8_t* table, const float* row_scales, int batch, int vocab, int d,
                          float embed_scale, float* h, const int32_t* positions, int32_t* attn_len,
                          unsigned long long* step_epoch, cudaStream_t s) {
-  return launch_chained(embed_kernel, dim3(batch), dim3(kRowThreads), 0, s, tokens, table, row_scales, d, embed_scale, h, positions,
+  return launch_chained(embed_kernel, dim3(batch), dim3(kRowThreads), 0, s, tokens, table, row_scales, vocab, d, embed_scale, h, positions,
                         attn_len, step_epoch);
 }
 
@@ -438,22 +469,23 @@ cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_all
                                 kGegluCluster, s, gate_up, f, f_pad, per_cta, m_alloc, q_tiled, scales, zps);
 }
 
-cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, float rope_base,
+cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, const float2* rope_cs,
                               const int32_t* positions, int max_seq, float* q_out, void* k_cache, void* v_cache,
                               float* k_scale, float* v_scale, int kv_int8, int one_sequence, cudaStream_t s) {
   dim3 grid(batch, heads + 2 * kv_heads);
   if (kv_int8) {
-    return launch_chained(rope_cache_kernel<true>, grid, dim3(head_dim / 2), 0, s, qkv, heads, kv_heads, head_dim, rope_base,
+    return launch_chained(rope_cache_kernel<true>, grid, dim3(head_dim / 2), 0, s, qkv, heads, kv_heads, head_dim, rope_cs,
                           positions, max_seq, q_out, k_cache, v_cache, k_scale, v_scale, one_sequence);
   }
-  return launch_chained(rope_cache_kernel<false>, grid, dim3(head_dim / 2), 0, s, qkv, heads, kv_heads, head_dim, rope_base,
+  return launch_chained(rope_cache_kernel<false>, grid, dim3(head_dim / 2), 0, s, qkv, heads, kv_heads, head_dim, rope_cs,
                         positions, max_seq, q_out, k_cache, v_cache, k_scale, v_scale, one_sequence);
 }
 
-cudaError_t launch_argmax(const float* logits, int batch, int n, int idx_offset, float* part_val, int32_t* part_idx,
-                          int32_t* next_tokens, int32_t* positions, int max_seq, float2* pair_out, cudaStream_t s) {
+cudaError_t launch_argmax(const float* logits, int batch, int n, int idx_offset, float soft_cap, float* part_val,
+                          int32_t* part_idx, int32_t* next_tokens, int32_t* positions, int max_seq, float2* pair_out,
+                          cudaStream_t s) {
   cudaError_t e = launch_chained(argmax_partial_kernel, dim3(kArgmaxParts, batch), dim3(256), 0, s, logits, n, (int)kArgmaxParts,
-                                 part_val, part_idx);
+                                 soft_cap, part_val, part_idx);
   if (e != cudaSuccess) return e;
   return launch_chained(argmax_final_kernel, dim3(batch), dim3(32), 0, s, (const float*)part_val, (const int32_t*)part_idx,
                         (int)kArgmaxParts, idx_offset, next_tokens, positions, max_seq, pair_out);

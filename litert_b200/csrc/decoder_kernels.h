@@ -27,7 +27,8 @@ struct TpExchange {
 };
 
 // step_epoch (optional): device counter advanced by one, the clock of the cross-rank exchanges.
-cudaError_t launch_embed(const int32_t* tokens, const int8_t* table, const float* row_scales, int batch, int d,
+// positions / attn_len (optional): attn_len[b] = positions[b] + 1.
+cudaError_t launch_embed(const int32_t* tokens, const int8_t* table, const float* row_scales, int batch, int vocab, int d,
                          float embed_scale, float* h, const int32_t* positions, int32_t* attn_len,
                          unsigned long long* step_epoch, cudaStream_t s);
 // h += delta; x = rms_norm(h) * gain; quantize x. With xch (tp_size > 1) delta is the sum over ranks of
@@ -39,14 +40,20 @@ cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_all
                                int32_t* zps, cudaStream_t s);
 // one_sequence: the rows are consecutive tokens of ONE sequence (a prompt pass) and k_cache / v_cache /
 // k_scale / v_scale point at that sequence's cache; otherwise row b belongs to sequence b.
-cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, float rope_base,
+// Host side of the rotary embedding: cs[(pos * (head_dim / 2) + i) * 2 + {0, 1}] = {cos, sin} of
+// pos * base^(-2 i / head_dim) for pos < positions, in float with the C library's powf / cosf / sinf.
+void fill_rope_table(float* cs, int positions, int head_dim, float base);
+// rope_cs: {cos, sin} per (position, rotation pair), [max_seq + 1][head_dim / 2] (fill_rope_table).
+cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_heads, int head_dim, const float2* rope_cs,
                               const int32_t* positions, int max_seq, float* q_out, void* k_cache, void* v_cache,
                               float* k_scale, float* v_scale, int kv_int8, int one_sequence, cudaStream_t s);
 // First-index argmax of each row; advances positions. idx_offset is added to the winning column.
 // With pair_out the winner goes to pair_out[b] = {value, index as float} instead, and neither
 // next_tokens nor positions change (launch_argmax_pick finishes the job across ranks).
-cudaError_t launch_argmax(const float* logits, int batch, int n, int idx_offset, float* part_val, int32_t* part_idx,
-                          int32_t* next_tokens, int32_t* positions, int max_seq, float2* pair_out, cudaStream_t s);
+// soft_cap > 0: the comparison runs on cap * tanh(logit / cap). positions may be null.
+cudaError_t launch_argmax(const float* logits, int batch, int n, int idx_offset, float soft_cap, float* part_val,
+                          int32_t* part_idx, int32_t* next_tokens, int32_t* positions, int max_seq, float2* pair_out,
+                          cudaStream_t s);
 // Picks the best of tp_size candidate pairs per row. pairs[j] = rank j's float2[batch]; when xch is given
 // they are peers' memory and the exchange handshake runs first, otherwise they are local.
 cudaError_t launch_argmax_pick(const float2* const* pairs, int tp_size, int batch, int32_t* next_tokens,

@@ -162,7 +162,13 @@ OpKind Classify(TfLiteContext* ctx, const TfLiteNode* node, const TfLiteRegistra
     if (w->sparsity) return *why = "sparse weights", OpKind::kNone;
     if (!IsConst(*w) || w->dims->size != 2) return *why = "weights not a constant matrix", OpKind::kNone;
     if (b && !IsConst(*b)) return *why = "bias not constant", OpKind::kNone;
-    if (x->dims->size < 1 || NumElements(*x) % w->dims->data[1] != 0) return *why = "input shape", OpKind::kNone;
+    // a constant input would never be uploaded (the arena holds run-time tensors only): leave such a
+    // node to the runtime, which folds or evaluates it on the CPU
+    if (IsConst(*x)) return *why = "constant input", OpKind::kNone;
+    if (x->dims->size < 1 || w->dims->data[1] <= 0 || NumElements(*x) % w->dims->data[1] != 0)
+      return *why = "input shape", OpKind::kNone;
+    if (b && NumElements(*b) != w->dims->data[0]) return *why = "bias length", OpKind::kNone;
+    if (NumElements(*y) != NumElements(*x) / w->dims->data[1] * w->dims->data[0]) return *why = "output shape", OpKind::kNone;
     if (x->type == kTfLiteInt8 && w->type == kTfLiteInt8 && y->type == kTfLiteInt8) {
       const auto* q = Affine(*w);
       if (!q || !q->scale || q->scale->size < 1) return *why = "weights lack affine quantization", OpKind::kNone;
@@ -200,6 +206,7 @@ OpKind Classify(TfLiteContext* ctx, const TfLiteNode* node, const TfLiteRegistra
     if (!p || !x || !w) return *why = "missing operands", OpKind::kNone;
     if (p->adj_x) return *why = "adj_x", OpKind::kNone;
     if (!IsConst(*w) || w->dims->size != 2) return *why = "rhs not a constant matrix", OpKind::kNone;
+    if (IsConst(*x)) return *why = "constant lhs", OpKind::kNone;
     if (x->dims->size < 2) return *why = "lhs rank", OpKind::kNone;
     if (x->type == kTfLiteFloat32 && w->type == kTfLiteInt8 && y->type == kTfLiteFloat32) {
       const auto* q = Affine(*w);
@@ -214,6 +221,8 @@ OpKind Classify(TfLiteContext* ctx, const TfLiteNode* node, const TfLiteRegistra
     const TfLiteTensor *q = in(0), *k = in(1), *v = in(2), *m = in(3);
     const TfLiteTensor* y = &T[node->outputs->data[0]];
     if (!q || !k || !v) return *why = "sdpa operands", OpKind::kNone;
+    for (const TfLiteTensor* t : {q, k, v, m})
+      if (t && IsConst(*t)) return *why = "sdpa with a constant operand", OpKind::kNone;
     for (const TfLiteTensor* t : {q, k, v, y})
       if (t->type != kTfLiteFloat32 || t->dims->size != 4) return *why = "sdpa wants 4-D float32", OpKind::kNone;
     if (m && (m->type != kTfLiteFloat32 || m->dims->size != 4)) return *why = "sdpa mask", OpKind::kNone;
@@ -421,7 +430,13 @@ class DelegateKernel {
       }
     }
     int status = 0;
-    B200_OK_OR_RETURN(ctx, b200_read_status(st_->zero_ws.ptr, s, &status));  // synchronises the stream
+    if (b200_read_status(st_->zero_ws.ptr, s, &status) != B200_OK) {  // synchronises the stream
+      TF_LITE_KERNEL_LOG(ctx, "B200 delegate: %s", b200_last_error());
+      // a wait ran out inside a kernel: this invocation's outputs are void; leave the workspace clean
+      // so that the next invocation does not inherit the sticky status word or stale split-K counters
+      b200_clear_status(st_->zero_ws.ptr, s);
+      return kTfLiteDelegateError;
+    }
     return kTfLiteOk;
   }
 

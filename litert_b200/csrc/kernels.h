@@ -154,7 +154,8 @@ struct AttnStepParams {
   float* v_scale;
   int b, n, h, s_max;
   int kv_dtype;               // 0 fp16, 1 int8
-  float rope_base, scale;
+  const float2* rope_cs;      // {cos, sin} per (position, rotation pair): [s_max + 1][h / 2]
+  float scale;
   int8_t* q_tiled_out;        // tiled rows of width n * h
   float* out_scales;
   int32_t* out_zps;

@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_kernel(const SdpaPara
   constexpr int KSTEPS = WA::KSTEPS;
   pdl_enter();
   const int b = blockIdx.z, kvh = blockIdx.y, chunk = blockIdx.x;
-  const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
+  const int len = p.lengths ? max(0, min(p.lengths[b], p.s_max)) : p.s_max;
   const int c0 = chunk * chunk_tokens;
   if (c0 >= len) return;
   const int c1 = min(len, c0 + chunk_tokens);
@@ -475,7 +475,7 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_ring_kernel(const Sdp
   pdl_enter();
   __syncthreads();
   const int b = blockIdx.z, kvh = blockIdx.y, chunk = blockIdx.x;
-  const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
+  const int len = p.lengths ? max(0, min(p.lengths[b], p.s_max)) : p.s_max;
   const int c0 = chunk * chunk_tokens;
   if (c0 >= len) return;  // uniform over the CTA, nothing in flight
   const int c1 = min(len, c0 + chunk_tokens);
@@ -590,7 +590,7 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_rows_kernel(const SdpaParams
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = (int)blockIdx.z * kWarps + warp, kvh = blockIdx.y, chunk = blockIdx.x;
   if (b >= p.b) return;  // (no block-wide barrier below)
-  const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
+  const int len = p.lengths ? max(0, min(p.lengths[b], p.s_max)) : p.s_max;
   const int c0 = chunk * chunk_tokens;
   if (c0 >= len) return;
   const int c1 = min(len, c0 + chunk_tokens);
@@ -661,7 +661,7 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_rows_ring_kernel(const SdpaP
   const int b = min(row0 + warp, p.b - 1);          // this warp's row (a surplus warp repeats the last one, unused)
   const bool row_ok = row0 + warp < p.b;
   const int b_last = min(row0 + kWarps, p.b) - 1;   // lengths grow with the row: the CTA's longest
-  auto length_of = [&](int r) { return p.lengths ? min(p.lengths[r], p.s_max) : p.s_max; };
+  auto length_of = [&](int r) { return p.lengths ? max(0, min(p.lengths[r], p.s_max)) : p.s_max; };
   int len_cta = 0;
   for (int r = row0; r <= b_last; ++r) len_cta = max(len_cta, length_of(r));
   const int c0 = chunk * chunk_tokens;
@@ -785,6 +785,15 @@ constexpr size_t attn_park_bytes() {
   return sizeof(float) * kAttnWarps * 8 * (H + 4);
 }
 
+// x * cos + rotate_half(x) * sin, every product and sum rounded on its own (separate MUL and ADD ops
+// in the graph, tensor/examples/gemma3/gemma3_graph.cc:150-176); r = {cos, sin}.
+__device__ __forceinline__ float rope_lo(float x1, float x2, float2 r) {
+  return __fsub_rn(__fmul_rn(x1, r.x), __fmul_rn(x2, r.y));
+}
+__device__ __forceinline__ float rope_hi(float x1, float x2, float2 r) {
+  return __fadd_rn(__fmul_rn(x2, r.x), __fmul_rn(x1, r.y));
+}
+
 template <int KV, int H, int GPI>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(const AttnStepParams p, const int stage_rows) {
   using WA = WarpAttention<KV, H, GPI>;
@@ -833,12 +842,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
     cp_async_commit();
   }
   if (tracer) p.trace[10] = global_timer_ns();
-  for (int i = tid; i < HALF; i += kAttnWarps * 32) {
-    const float freq = powf(p.rope_base, -2.0f * (float)i / (float)H);
-    float sn, cs;
-    sincosf((float)pos * freq, &sn, &cs);
-    sm.cs[i] = make_float2(cs, sn);
-  }
+  // cos / sin of this position's rotation angles, from the table the host side prepared
+  for (int i = tid; i < HALF; i += kAttnWarps * 32) sm.cs[i] = p.rope_cs[(size_t)min(pos, p.s_max) * HALF + i];
   if (tracer) p.trace[11] = global_timer_ns();
   // With kAttnDryRun the code below runs twice: first at once, on stale q / k / v, storing nothing
   // outside the CTAs' shared memory, to pull instructions into the caches while the projection
@@ -858,8 +863,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
       const int head = idx / HALF, i = idx % HALF;
       const float x1 = __ldcg(src + head * H + i), x2 = __ldcg(src + head * H + i + HALF);  // past L1: the dry run read them too
       const float2 r = sm.cs[i];
-      sm.q[head][i] = x1 * r.x - x2 * r.y;
-      sm.q[head][i + HALF] = x2 * r.x + x1 * r.y;
+      sm.q[head][i] = rope_lo(x1, x2, r);
+      sm.q[head][i + HALF] = rope_hi(x1, x2, r);
     }
     if (append && pos >= c0 && pos < c1) {
       // The CTA whose share holds the new token writes its row: to the cache, and to the staged
@@ -873,7 +878,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
         for (int i = tid; i < HALF; i += kAttnWarps * 32) {
           const float2 r = sm.cs[i];
           const float x1 = __ldcg(ksrc + i), x2 = __ldcg(ksrc + i + HALF);
-          ka = fmaxf(ka, fmaxf(fabsf(x1 * r.x - x2 * r.y), fabsf(x2 * r.x + x1 * r.y)));
+          ka = fmaxf(ka, fmaxf(fabsf(rope_lo(x1, x2, r)), fabsf(rope_hi(x1, x2, r))));
           va = fmaxf(va, fmaxf(fabsf(__ldcg(vsrc + i)), fabsf(__ldcg(vsrc + i + HALF))));
         }
   #pragma unroll
@@ -889,7 +894,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
           ka = fmaxf(ka, sm.red[w].x);
           va = fmaxf(va, sm.red[w].y);
         }
-        const float ks = ka > 0.0f ? ka / 127.0f : 1.0f, vs = va > 0.0f ? va / 127.0f : 1.0f;
+        const float ks = ka > 0.0f ? __fdiv_rn(ka, 127.0f) : 1.0f, vs = va > 0.0f ? __fdiv_rn(va, 127.0f) : 1.0f;
         int8_t* kd = static_cast<int8_t*>(p.k_cache) + tok * H;
         int8_t* vd = static_cast<int8_t*>(p.v_cache) + tok * H;
         int8_t* ks_row = reinterpret_cast<int8_t*>(stage_k + (size_t)(pos - c0) * PITCH);
@@ -897,10 +902,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
         for (int i = tid; i < HALF; i += kAttnWarps * 32) {
           const float2 r = sm.cs[i];
           const float x1 = __ldcg(ksrc + i), x2 = __ldcg(ksrc + i + HALF);
-          const int8_t k1 = (int8_t)max(-127, min(127, __float2int_rn((x1 * r.x - x2 * r.y) / ks)));
-          const int8_t k2 = (int8_t)max(-127, min(127, __float2int_rn((x2 * r.x + x1 * r.y) / ks)));
-          const int8_t v1 = (int8_t)max(-127, min(127, __float2int_rn(__ldcg(vsrc + i) / vs)));
-          const int8_t v2 = (int8_t)max(-127, min(127, __float2int_rn(__ldcg(vsrc + i + HALF) / vs)));
+          const int8_t k1 = (int8_t)max(-127, min(127, __float2int_rn(__fdiv_rn(rope_lo(x1, x2, r), ks))));
+          const int8_t k2 = (int8_t)max(-127, min(127, __float2int_rn(__fdiv_rn(rope_hi(x1, x2, r), ks))));
+          const int8_t v1 = (int8_t)max(-127, min(127, __float2int_rn(__fdiv_rn(__ldcg(vsrc + i), vs))));
+          const int8_t v2 = (int8_t)max(-127, min(127, __float2int_rn(__fdiv_rn(__ldcg(vsrc + i + HALF), vs))));
           if (live) kd[i] = k1, kd[i + HALF] = k2, vd[i] = v1, vd[i + HALF] = v2;
           if (staged) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
         }
@@ -916,7 +921,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
         for (int i = tid; i < HALF; i += kAttnWarps * 32) {
           const float2 r = sm.cs[i];
           const float x1 = __ldcg(ksrc + i), x2 = __ldcg(ksrc + i + HALF);
-          const __half k1 = __float2half_rn(x1 * r.x - x2 * r.y), k2 = __float2half_rn(x2 * r.x + x1 * r.y);
+          const __half k1 = __float2half_rn(rope_lo(x1, x2, r)), k2 = __float2half_rn(rope_hi(x1, x2, r));
           const __half v1 = __float2half_rn(__ldcg(vsrc + i)), v2 = __float2half_rn(__ldcg(vsrc + i + HALF));
           if (live) kd[i] = k1, kd[i + HALF] = k2, vd[i] = v1, vd[i + HALF] = v2;
           if (staged) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
@@ -1118,7 +1123,7 @@ __global__ void sdpa_merge_kernel(const SdpaParams p, const int chunk_tokens, co
   const int b = blockIdx.y, head = blockIdx.x, d = threadIdx.x;
   const int group = p.n / p.nkv;
   const int kvh = head / group, hg = head % group;
-  const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
+  const int len = p.lengths ? max(0, min(p.lengths[b], p.s_max)) : p.s_max;
   const int chunks = (len + chunk_tokens - 1) / chunk_tokens;
   const float* base = p.ws + ((((size_t)b * p.nkv + kvh) * chunks_max) * 8 + hg) * partial_stride(H);
   const size_t cstride = 8 * partial_stride(H);
@@ -1131,7 +1136,7 @@ __global__ void sdpa_merge_kernel(const SdpaParams p, const int chunk_tokens, co
     acc += f * base[c * cstride + d];
     l += f * base[c * cstride + H + 1];
   }
-  const float out = acc / l;
+  const float out = l > 0.0f ? acc / l : 0.0f;  // no cached token (or every key masked out): zeros, not 0 / 0
   const size_t oi = ((size_t)b * p.n + head) * H + d;
   if constexpr (QF32) {
     static_cast<float*>(p.out)[oi] = out;
@@ -1152,7 +1157,7 @@ __global__ void __launch_bounds__(1024) sdpa_merge_quant_kernel(const SdpaParams
   pdl_enter();
   const int b = blockIdx.x;
   const int group = p.n / p.nkv;
-  const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
+  const int len = p.lengths ? max(0, min(p.lengths[b], p.s_max)) : p.s_max;
   const int chunks = (len + chunk_tokens - 1) / chunk_tokens;
   const size_t cstride = 8 * partial_stride(H);
   const int width = p.n * H;
@@ -1215,7 +1220,8 @@ __global__ void __launch_bounds__(1024) sdpa_merge_quant_kernel(const SdpaParams
       for (int j = 0; j < 8; ++j) acc += w[c + j] * a[j];
     }
     for (; c < chunks; ++c) acc += w[c] * base[c * cstride];
-    const float v = acc / s_linv[head & 63];
+    const float l = s_linv[head & 63];
+    const float v = l > 0.0f ? acc / l : 0.0f;  // an empty sequence gives a zero row
     xs[idx] = v;
     if (p.out) static_cast<float*>(p.out)[(size_t)b * width + idx] = v;
     mn = fminf(mn, v);
@@ -1232,7 +1238,7 @@ template <int KV, bool QF32>
 __global__ void sdpa_decode_generic_kernel(const SdpaParams p) {
   const int b = blockIdx.y, head = blockIdx.x, lane = threadIdx.x;
   const int group = p.n / p.nkv, kvh = head / group;
-  const int len = p.lengths ? min(p.lengths[b], p.s_max) : p.s_max;
+  const int len = p.lengths ? max(0, min(p.lengths[b], p.s_max)) : p.s_max;
   const int h = p.h;
   extern __shared__ float sh[];  // h floats of q, then s_max logits
   float* q = sh;
@@ -1270,7 +1276,7 @@ __global__ void sdpa_decode_generic_kernel(const SdpaParams p) {
   for (int d = lane; d < h; d += 32) {
     float acc = 0.0f;
     for (int s = 0; s < len; ++s) acc += logits[s] * kv_at(p.v, p.v_scale, s, d);
-    const float out = acc / sum;
+    const float out = sum > 0.0f ? acc / sum : 0.0f;
     const size_t oi = ((size_t)b * p.n + head) * h + d;
     if (QF32) {
       static_cast<float*>(p.out)[oi] = out;

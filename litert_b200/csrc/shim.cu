@@ -96,6 +96,26 @@ int b200_zero_workspace_init(void* d_zero_ws, void* stream) {
   return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_zero_workspace_init");
 }
 
+int b200_set_wait_budget(void* d_zero_ws, unsigned long long nanoseconds, void* stream) {
+  if (!d_zero_ws) return fail(B200_ERR_INVALID_ARGUMENT, "zero workspace is null");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(static_cast<uint8_t*>(d_zero_ws) + 4 * b200::kStatusBudgetWordOffsetInts, &nanoseconds,
+                                  sizeof(nanoseconds), cudaMemcpyHostToDevice, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);  // the source is a stack variable
+  return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_set_wait_budget");
+}
+
+int b200_clear_status(void* d_zero_ws, void* stream) {
+  if (!d_zero_ws) return fail(B200_ERR_INVALID_ARGUMENT, "zero workspace is null");
+  // the status word, and whatever an aborted launch left in the split-K counters and the accumulator
+  // slots that must be zero between calls; the wait budget (bytes 8..15) is kept
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t* z = static_cast<uint8_t*>(d_zero_ws);
+  cudaError_t e = cudaMemsetAsync(z, 0, 8, s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(z + 16, 0, b200::zero_ws_part_off() - 16, s);
+  return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_clear_status");
+}
+
 size_t b200_fc_scratch_bytes(int m, int k) {
   if (m <= 0 || k <= 0) return 0;
   // sized for either weight format: 4-bit tiles are 256 wide

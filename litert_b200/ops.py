@@ -212,3 +212,144 @@ def sdpa_rows(q, k, v, lengths, scale=None, logit_cap=0.0, k_scale=None, v_scale
                              nkv, h, s_max, _DT[q.dtype], _DT[k.dtype], float(scale) if scale else 0.0,
                              float(logit_cap), _ptr(wsb), wsb.numel(), _stream()))
     return out
+
+
+# ---- decoder glue ops (include/litert_b200.h, "decoder glue ops") ---------------------------------------
+def _gcheck(rc):
+    if rc != 0:
+        raise B200Error(f"litert_b200 error {rc}: {_lib.load().b200_glue_last_error().decode()}")
+
+
+class QuantizedRows:
+    """m activation rows of k int8 values in the tiled layout the GEMM kernels stream, with one scale and
+    zero point per row: the output of the fused glue ops and the input of fully_connected_hybrid_quantized."""
+
+    def __init__(self, m, k, device):
+        self.m, self.k = m, k
+        self.tiled = torch.empty(max(int(_lib.load().b200_tiled_rows_bytes(m, k)), 128), dtype=torch.uint8, device=device)
+        self.scales = torch.zeros(max(m, 256), dtype=torch.float32, device=device)
+        self.zero_points = torch.zeros(max(m, 256), dtype=torch.int32, device=device)
+
+    def rows(self):
+        """Row-major int8 [m, k] view of the quantized values."""
+        out = torch.empty((self.m, self.k), dtype=torch.int8, device=self.tiled.device)
+        _gcheck(_lib.load().b200_untile_rows(_ptr(self.tiled), self.m, self.k, _ptr(out), _stream()))
+        return out
+
+
+def embedding_lookup(ids, table, row_scales, out_scale=1.0):
+    """Hybrid EMBEDDING_LOOKUP (tflite/kernels/embedding_lookup.cc, EvalHybrid) times a constant."""
+    ids = _need(ids, torch.int32, "ids").reshape(-1)
+    table = _need(table, torch.int8, "table")
+    row_scales = _need(row_scales, torch.float32, "row_scales")
+    vocab, d = table.shape
+    out = torch.empty((ids.numel(), d), dtype=torch.float32, device=table.device)
+    _gcheck(_lib.load().b200_embedding_lookup(_ptr(ids), ids.numel(), _ptr(table), _ptr(row_scales), vocab, d,
+                                              float(out_scale), _ptr(out), _stream()))
+    return out
+
+
+def add_rmsnorm_quantize(h, delta, gain, eps=1e-6):
+    """h += delta (in place; delta may be None); returns the quantized rows of rms_norm(h) * gain."""
+    h = _need(h, torch.float32, "h")
+    if not h.is_contiguous():
+        raise B200Error("h must be contiguous (it is updated in place)")
+    delta = _need(delta, torch.float32, "delta")
+    gain = _need(gain, torch.float32, "gain")
+    rows, d = h.shape
+    q = QuantizedRows(rows, d, h.device)
+    _gcheck(_lib.load().b200_add_rmsnorm_quantize(_ptr(h), _ptr(delta), _ptr(gain), rows, d, float(eps), _ptr(q.tiled),
+                                                  _ptr(q.scales), _ptr(q.zero_points), _stream()))
+    return q
+
+
+def geglu_quantize(gate_up):
+    """gate_up [rows, 2 f] (gate then up) -> quantized rows of gelu_tanh(gate) * up."""
+    gate_up = _need(gate_up, torch.float32, "gate_up")
+    rows, f2 = gate_up.shape
+    q = QuantizedRows(rows, f2 // 2, gate_up.device)
+    _gcheck(_lib.load().b200_geglu_quantize(_ptr(gate_up), rows, f2 // 2, _ptr(q.tiled), _ptr(q.scales),
+                                            _ptr(q.zero_points), _stream()))
+    return q
+
+
+def rope_table(positions, head_dim, base=10000.0, device="cuda"):
+    """float32 [positions, head_dim / 2, 2] = (cos, sin), computed on the host as the reference's host side does."""
+    import numpy as np
+    cs = np.empty((positions, head_dim // 2, 2), np.float32)
+    _gcheck(_lib.load().b200_rope_table(cs.ctypes.data_as(ctypes.c_void_p), positions, head_dim, float(base)))
+    return torch.from_numpy(cs).to(device)
+
+
+def rope_kv_append(qkv, heads, kv_heads, head_dim, table, positions, k_cache, v_cache, k_scale=None, v_scale=None,
+                   one_sequence=False):
+    """Rotates q and k of qkv [rows, (heads + 2 kv_heads) * head_dim], appends k and v to the caches
+    [batch, max_seq, kv_heads, head_dim] (fp16 or int8) at `positions`; returns q [rows, heads, head_dim]."""
+    qkv = _need(qkv, torch.float32, "qkv")
+    positions = _need(positions, torch.int32, "positions")
+    table = _need(table, torch.float32, "table")
+    rows = qkv.shape[0]
+    max_seq = k_cache.shape[-3]
+    if table.shape[0] < max_seq + 1:
+        raise B200Error("the rope table must cover positions 0..max_seq")
+    q = torch.empty((rows, heads, head_dim), dtype=torch.float32, device=qkv.device)
+    _gcheck(_lib.load().b200_rope_kv_append(_ptr(qkv), rows, heads, kv_heads, head_dim, _ptr(table), _ptr(positions),
+                                            max_seq, _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale),
+                                            _DT[k_cache.dtype], 1 if one_sequence else 0, _stream()))
+    return q
+
+
+def argmax_rows(logits, soft_cap=0.0):
+    logits = _need(logits, torch.float32, "logits")
+    rows, n = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    need = int(_lib.load().b200_argmax_workspace_bytes(rows))
+    wsb = torch.empty(need, dtype=torch.uint8, device=logits.device)
+    _gcheck(_lib.load().b200_argmax_rows(_ptr(logits), rows, n, float(soft_cap), _ptr(out), _ptr(wsb), need, _stream()))
+    return out
+
+
+def attention_step(qkv, positions, table, k_cache, v_cache, heads, head_dim, k_scale=None, v_scale=None, scale=0.0):
+    """One decode step of a multi-query layer's attention in one launch: rotation, cache append, attention
+    over the cached prefix and the new token, row quantization. Returns QuantizedRows [batch, heads * head_dim]."""
+    qkv = _need(qkv, torch.float32, "qkv")
+    positions = _need(positions, torch.int32, "positions")
+    batch = qkv.shape[0]
+    max_seq = k_cache.shape[1]
+    q = QuantizedRows(batch, heads * head_dim, qkv.device)
+    _gcheck(_lib.load().b200_attention_step(_ptr(qkv), _ptr(positions), _ptr(table), _ptr(k_cache), _ptr(v_cache),
+                                            _ptr(k_scale), _ptr(v_scale), batch, heads, head_dim, max_seq,
+                                            _DT[k_cache.dtype], float(scale), _ptr(q.tiled), _ptr(q.scales),
+                                            _ptr(q.zero_points), _stream()))
+    return q
+
+
+def sdpa_decode_quantized(q, k, v, lengths, scale=0.0, k_scale=None, v_scale=None):
+    """sdpa_decode whose result leaves as quantized rows [b, n * h]."""
+    lib = _lib.load()
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    b, t, n, h = q.shape
+    s_max, nkv = k.shape[1], k.shape[2]
+    lengths = _need(lengths, torch.int32, "lengths")
+    out = QuantizedRows(b, n * h, q.device)
+    need = int(lib.b200_sdpa_workspace_bytes(b, n, nkv, h, s_max))
+    wsb = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    _gcheck(lib.b200_sdpa_decode_quantized(_ptr(q), _ptr(k), _ptr(v), _ptr(k_scale), _ptr(v_scale), _ptr(lengths), b, n,
+                                           nkv, h, s_max, _DT[q.dtype], _DT[k.dtype], float(scale), _ptr(out.tiled),
+                                           _ptr(out.scales), _ptr(out.zero_points), _ptr(wsb), wsb.numel(), _stream()))
+    return out
+
+
+def fully_connected_hybrid_quantized(rows, weights, filter_scales, bias=None, activation=ACT_NONE, ws=None):
+    """The int8 dot products and dequantization of EvalHybridDense on rows that are already quantized."""
+    fs = _need(filter_scales, torch.float32, "filter_scales").reshape(-1)
+    bias = _need(bias, torch.float32, "bias")
+    ws = ws or Workspace(rows.tiled.device)
+    if rows.k != weights.k:
+        raise B200Error("row width does not match the weights")
+    y = torch.empty((rows.m, weights.n), dtype=torch.float32, device=rows.tiled.device)
+    _gcheck(_lib.load().b200_fc_hybrid_quantized(_ptr(rows.tiled), _ptr(rows.scales), _ptr(rows.zero_points), rows.m,
+                                                 rows.k, _ptr(weights.packed), weights.n, _ptr(weights.row_sums),
+                                                 _ptr(fs), 1 if fs.numel() > 1 else 0, _ptr(bias), int(activation),
+                                                 _ptr(y), _ptr(ws.zero), _stream()))
+    return y

@@ -279,6 +279,76 @@ def sdpa_f32(q, k, v, mask=None, scale=None, logit_cap=0.0):
     return out
 
 
+# ---- stages of the decoder graph, one function each (oracle/decoder_ref.c) -----------------
+def stage_embed(tokens, table, row_scales, embed_scale):
+    tok = _c(tokens, np.int32)
+    table = _c(table, np.int8)
+    rs = _c(row_scales, np.float32)
+    d = table.shape[1]
+    h = np.empty((tok.size, d), np.float32)
+    fast().orc_stage_embed(_p(tok), _i(tok.size), _p(table), _p(rs), _i(d), _f(embed_scale), _p(h))
+    return h
+
+
+def stage_add_rmsnorm(h, delta, gain, eps):
+    """Returns (h + delta, rms_norm(h + delta) * gain); delta may be None."""
+    h = np.array(h, np.float32, copy=True, order="C")
+    delta = _c(delta, np.float32)
+    gain = _c(gain, np.float32)
+    rows, d = h.shape
+    x = np.empty_like(h)
+    fast().orc_stage_add_rmsnorm(_p(h), _p(delta), _p(gain), _i(rows), _i(d), _f(eps), _p(x))
+    return h, x
+
+
+def rope_table(max_seq, head_dim, base=10000.0):
+    """float32 [max_seq, head_dim / 2, 2] = (cos, sin) of the rotation angles."""
+    cs = np.empty((max_seq, head_dim // 2, 2), np.float32)
+    fast().orc_rope_table(_i(max_seq), _i(head_dim), _f(base), _p(cs))
+    return cs
+
+
+def stage_rope(x, positions, base=10000.0):
+    """x [rows, heads, head_dim] rotated (copy), row r at positions[r]."""
+    x = np.array(x, np.float32, copy=True, order="C")
+    pos = _c(positions, np.int32)
+    rows, heads, hd = x.shape
+    fast().orc_stage_rope(_p(x), _i(rows), _i(heads), _i(hd), _p(pos), _f(base))
+    return x
+
+
+def stage_kv_round(rows, mode):
+    """Cache rows [..., head_dim] as the device keeps them (1: binary16, 2: int8 per row), as float32."""
+    x = np.array(rows, np.float32, copy=True, order="C")
+    hd = x.shape[-1]
+    flat = x.reshape(-1, hd)
+    for r in range(flat.shape[0]):
+        fast().orc_stage_kv_round(flat[r].ctypes.data_as(ctypes.c_void_p), _i(hd), _i(mode))
+    return x
+
+
+def stage_geglu(gate, up):
+    gate = _c(gate, np.float32)
+    up = _c(up, np.float32)
+    out = np.empty_like(gate)
+    fast().orc_stage_geglu(_p(gate), _p(up), ctypes.c_size_t(gate.size), _p(out))
+    return out
+
+
+def stage_softcap(logits, cap):
+    x = np.array(logits, np.float32, copy=True, order="C")
+    fast().orc_stage_softcap(_p(x), ctypes.c_size_t(x.size), _f(cap))
+    return x
+
+
+def stage_argmax(logits):
+    lg = _c(logits, np.float32)
+    rows, n = lg.shape
+    out = np.empty(rows, np.int32)
+    fast().orc_stage_argmax(_p(lg), _i(rows), _i(n), _p(out))
+    return out
+
+
 # ---- Gemma-shaped decoder (oracle/decoder_ref.c) ------------------------------------------
 class _DecCfg(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in ("n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim", "d_ff",
@@ -329,7 +399,7 @@ class DecoderRef:
     the key names of _DecLayer). fast=True uses the vectorised multi-threaded kernels."""
 
     def __init__(self, cfg, weights, batch, max_seq, rms_eps=1e-6, rope_base=10000.0, fast=False, reduce=None,
-                 lm_rows=None):
+                 lm_rows=None, kv_mode=0):
         """reduce(arr): sums a float32 array over tensor-parallel ranks in place (shard decoders only);
         lm_rows=(first, rows) limits the LM head to those rows of the table."""
         use_fast = bool(fast)
@@ -353,6 +423,8 @@ class DecoderRef:
         fn = np.ascontiguousarray(weights["final_norm"], np.float32)
         self._keep += [e, es, fn]
         fast_lib.orc_decoder_set_embedding(self.h, _p(e), _p(es), _p(fn))
+        if kv_mode:  # keep cache rows as the device does: 1 binary16, 2 int8 per token
+            fast_lib.orc_decoder_set_kv_mode(self.h, int(kv_mode))
         self.lm_rows = cfg["vocab"]
         if lm_rows is not None:
             self.lm_rows = int(lm_rows[1])

@@ -57,6 +57,7 @@ typedef struct {
   void (*reduce)(void* user, float* buf, size_t count); /* in-place sum over ranks, or NULL */
   void* reduce_user;
   int lm_first, lm_rows; /* LM head rows [lm_first, lm_first + lm_rows) of the table */
+  int kv_mode;           /* how a row is kept in the cache: 0 float32, 1 rounded to binary16, 2 int8 per token */
 } orc_decoder;
 
 static void fc(const orc_decoder* d, int m, int n, int k, const float* x, const int8_t* w, const float* s, float* y) {
@@ -67,6 +68,20 @@ static void fc(const orc_decoder* d, int m, int n, int k, const float* x, const 
   }
 }
 
+/* ---- the stages between the projections, one function each (also called on their own by the
+ * per-kernel parity tests) ------------------------------------------------------------------- */
+
+/* Hybrid EMBEDDING_LOOKUP (tflite/kernels/embedding_lookup.cc:EvalHybrid: value * row scale), then the
+ * embedding scale the graph applies as a MUL (tensor/examples/gemma3/gemma3_graph.cc). */
+void orc_stage_embed(const int32_t* tokens, int rows, const int8_t* table, const float* row_scales, int d,
+                     float embed_scale, float* h) {
+  for (int b = 0; b < rows; ++b) {
+    const int8_t* row = table + (size_t)tokens[b] * d;
+    const float s = row_scales[tokens[b]];
+    for (int i = 0; i < d; ++i) h[(size_t)b * d + i] = (float)row[i] * s * embed_scale;
+  }
+}
+
 static void rms_norm(const float* x, const float* gain, int n, float eps, float* y) {
   float ss = 0.0f;
   for (int i = 0; i < n; ++i) ss += x[i] * x[i];
@@ -74,7 +89,28 @@ static void rms_norm(const float* x, const float* gain, int n, float eps, float*
   for (int i = 0; i < n; ++i) y[i] = x[i] * inv * gain[i];
 }
 
-/* x*cos + rotate_half(x)*sin with rotate_half(x) = cat(-x2, x1); angle of pair i = pos * base^(-2i/hd) */
+/* h += delta (residual ADD, skipped when delta is NULL); x = rms_norm(h) * gain. */
+void orc_stage_add_rmsnorm(float* h, const float* delta, const float* gain, int rows, int d, float eps, float* x) {
+  if (delta)
+    for (size_t i = 0; i < (size_t)rows * d; ++i) h[i] += delta[i];
+  for (int b = 0; b < rows; ++b) rms_norm(h + (size_t)b * d, gain, d, eps, x + (size_t)b * d);
+}
+
+/* Rotation angles as the graph's host side prepares them: the cos and sin tensors are INPUTS of the
+ * graph (gemma3_graph.cc:150-176 multiplies by them), angle of pair i at position pos =
+ * pos * base^(-2i/head_dim). cs[pos][i] = {cos, sin}, i < head_dim / 2. */
+void orc_rope_table(int max_seq, int head_dim, float base, float* cs) {
+  const int half = head_dim / 2;
+  for (int pos = 0; pos < max_seq; ++pos)
+    for (int i = 0; i < half; ++i) {
+      const float freq = powf(base, -2.0f * (float)i / (float)head_dim);
+      const float ang = (float)pos * freq;
+      cs[((size_t)pos * half + i) * 2] = cosf(ang);
+      cs[((size_t)pos * half + i) * 2 + 1] = sinf(ang);
+    }
+}
+
+/* x*cos + rotate_half(x)*sin with rotate_half(x) = cat(-x2, x1) */
 static void rope(float* x, int head_dim, int pos, float base) {
   const int half = head_dim / 2;
   for (int i = 0; i < half; ++i) {
@@ -87,9 +123,39 @@ static void rope(float* x, int head_dim, int pos, float base) {
   }
 }
 
+/* Rotates `heads` heads per row in place, row r at positions[r]. */
+void orc_stage_rope(float* x, int rows, int heads, int head_dim, const int32_t* positions, float base) {
+  for (int r = 0; r < rows; ++r)
+    for (int hh = 0; hh < heads; ++hh) rope(x + ((size_t)r * heads + hh) * head_dim, head_dim, positions[r], base);
+}
+
 static float gelu_tanh(float v) {
   const float k0 = 0.7978845608028654f; /* sqrt(2/pi) */
   return 0.5f * v * (1.0f + tanhf(k0 * (v + 0.044715f * v * v * v)));
+}
+
+/* out = gelu_tanh(gate) * up (GELU approximate=true then MUL, gemma3_graph.cc:118-146). */
+void orc_stage_geglu(const float* gate, const float* up, size_t count, float* out) {
+  for (size_t i = 0; i < count; ++i) out[i] = gelu_tanh(gate[i]) * up[i];
+}
+
+/* Logit soft-cap: tanh(x / cap) * cap (litert/vendors/nvidia/trtllm/head_kernels.cu:35-43). */
+void orc_stage_softcap(float* logits, size_t count, float cap) {
+  const float inv = 1.0f / cap;
+  for (size_t i = 0; i < count; ++i) logits[i] = tanhf(logits[i] * inv) * cap;
+}
+
+/* Greedy pick per row: the serial scan of the CPU sampler, whose behaviour with NaNs the reference's GPU
+ * sampler preserves (litert/vendors/nvidia/dispatch/greedy_sampler_kernel.cu:31-50): a NaN at index 0
+ * wins, a NaN anywhere else never does, ties go to the lower index. */
+void orc_stage_argmax(const float* logits, int rows, int n, int32_t* out) {
+  for (int b = 0; b < rows; ++b) {
+    const float* lg = logits + (size_t)b * n;
+    int best = 0;
+    for (int i = 1; i < n; ++i)
+      if (lg[i] > lg[best]) best = i;
+    out[b] = best;
+  }
 }
 
 orc_decoder* orc_decoder_create(const orc_decoder_config* cfg, int batch, int fast) {
@@ -129,6 +195,25 @@ void orc_decoder_set_lm_rows(orc_decoder* d, int first, int rows) {
   d->lm_first = first;
   d->lm_rows = rows;
 }
+/* The device keeps its cache in binary16 or int8 (one symmetric scale per token and KV head, scale =
+ * max|row| / 127): with kv_mode 1 / 2 the CPU graph stores the same rounded values (as float32). */
+void orc_decoder_set_kv_mode(orc_decoder* d, int mode) { d->kv_mode = mode; }
+
+void orc_stage_kv_round(float* row, int n, int mode) {
+  if (mode == 1) {
+    for (int i = 0; i < n; ++i) row[i] = orc_half_to_float(orc_float_to_half(row[i]));
+  } else if (mode == 2) {
+    float amax = 0.0f;
+    for (int i = 0; i < n; ++i) amax = fmaxf(amax, fabsf(row[i]));
+    const float sc = amax > 0.0f ? amax / 127.0f : 1.0f;
+    for (int i = 0; i < n; ++i) {
+      float q = nearbyintf(row[i] / sc);
+      q = q > 127.0f ? 127.0f : (q < -127.0f ? -127.0f : q);
+      row[i] = q * sc;
+    }
+  }
+}
+
 void orc_decoder_reset(orc_decoder* d) { memset(d->lengths, 0, sizeof(int) * (size_t)d->batch); }
 
 /* One token per sequence: tokens [batch] -> logits [batch, lm_rows] (may be NULL) and the greedy next
@@ -147,11 +232,7 @@ void orc_decoder_step(orc_decoder* d, const int32_t* tokens, float* logits_out, 
   float* up = (float*)malloc(sizeof(float) * (size_t)B * F);
   float* logits = logits_out ? logits_out : (float*)malloc(sizeof(float) * (size_t)B * d->lm_rows);
 
-  for (int b = 0; b < B; ++b) {
-    const int8_t* row = d->embed + (size_t)tokens[b] * D;
-    const float s = d->embed_scales[tokens[b]];
-    for (int i = 0; i < D; ++i) h[(size_t)b * D + i] = (float)row[i] * s * c->embed_scale;
-  }
+  orc_stage_embed(tokens, B, d->embed, d->embed_scales, D, c->embed_scale, h);
   const size_t per_seq = (size_t)c->max_seq * KVH * HD;
   for (int l = 0; l < c->n_layers; ++l) {
     const orc_decoder_layer* w = &d->layers[l];
@@ -167,6 +248,11 @@ void orc_decoder_step(orc_decoder* d, const int32_t* tokens, float* logits_out, 
       for (int hh = 0; hh < KVH; ++hh) rope(kk + ((size_t)b * KVH + hh) * HD, HD, pos, c->rope_base);
       memcpy(kc + (size_t)b * per_seq + (size_t)pos * KVH * HD, kk + (size_t)b * KVH * HD, sizeof(float) * KVH * HD);
       memcpy(vc + (size_t)b * per_seq + (size_t)pos * KVH * HD, vv + (size_t)b * KVH * HD, sizeof(float) * KVH * HD);
+      if (d->kv_mode)
+        for (int hh = 0; hh < KVH; ++hh) {
+          orc_stage_kv_round(kc + (size_t)b * per_seq + ((size_t)pos * KVH + hh) * HD, HD, d->kv_mode);
+          orc_stage_kv_round(vc + (size_t)b * per_seq + ((size_t)pos * KVH + hh) * HD, HD, d->kv_mode);
+        }
       const int len = pos + 1;
       const float scale = 1.0f / sqrtf((float)HD);
       if (d->fast) {
@@ -183,7 +269,7 @@ void orc_decoder_step(orc_decoder* d, const int32_t* tokens, float* logits_out, 
     for (int b = 0; b < B; ++b) rms_norm(h + (size_t)b * D, w->norm2, D, c->rms_eps, x + (size_t)b * D);
     fc(d, B, F, D, x, w->wgate, w->sgate, gate);
     fc(d, B, F, D, x, w->wup, w->sup, up);
-    for (size_t i = 0; i < (size_t)B * F; ++i) gate[i] = gelu_tanh(gate[i]) * up[i];
+    orc_stage_geglu(gate, up, (size_t)B * F, gate);
     fc(d, B, D, F, gate, w->wdown, w->sdown, o);
     if (d->reduce) d->reduce(d->reduce_user, o, (size_t)B * D);
     for (size_t i = 0; i < (size_t)B * D; ++i) h[i] += o[i];
@@ -191,10 +277,8 @@ void orc_decoder_step(orc_decoder* d, const int32_t* tokens, float* logits_out, 
   for (int b = 0; b < B; ++b) rms_norm(h + (size_t)b * D, d->final_norm, D, c->rms_eps, x + (size_t)b * D);
   fc(d, B, d->lm_rows, D, x, d->embed + (size_t)d->lm_first * D, d->embed_scales + d->lm_first, logits);
   for (int b = 0; b < B; ++b) {
-    const float* lg = logits + (size_t)b * d->lm_rows;
-    int best = 0;
-    for (int i = 1; i < d->lm_rows; ++i)
-      if (lg[i] > lg[best]) best = i;
+    int32_t best = 0;
+    orc_stage_argmax(logits + (size_t)b * d->lm_rows, 1, d->lm_rows, &best);
     if (next_tokens) next_tokens[b] = d->lm_first + best;
     d->lengths[b] += 1;
   }

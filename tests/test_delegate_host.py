@@ -120,6 +120,53 @@ def test_support_predicate_bmm_and_sdpa(plugin_path):
     d.close()
 
 
+def test_support_predicate_leaves_constant_activations_and_bad_shapes_alone(plugin_path):
+    """A node whose run-time operand is a constant would never see its data on the device (only run-time
+    tensors get arena slots), and a bias or output whose size disagrees with the weights would be read
+    or written out of bounds: none of these is claimed."""
+    def claimed(build):
+        m, d = minirt.MiniRuntime(), minirt.Delegate()
+        build(m)
+        m.apply(d)
+        n = d.claimed
+        m.close()
+        d.close()
+        return n
+
+    def fc(m, x_data=None, bias_len=3, y_cols=3):
+        x = m.tensor(F32, (2, 10), x_data)
+        w = m.tensor(I8, (3, 10), np.ones((3, 10), np.int8), scale=0.25)
+        b = m.tensor(F32, (bias_len,), np.zeros(bias_len, np.float32))
+        y = m.tensor(F32, (2, y_cols))
+        m.fully_connected(x, w, b, y)
+        m.set_io([x] if x_data is None else [], [y])
+
+    assert claimed(lambda m: fc(m)) == 1
+    assert claimed(lambda m: fc(m, x_data=np.ones((2, 10), np.float32))) == 0   # constant input
+    assert claimed(lambda m: fc(m, bias_len=2)) == 0                            # bias shorter than the units
+    assert claimed(lambda m: fc(m, y_cols=4)) == 0                              # output of the wrong size
+
+    def bmm_const_lhs(m):
+        x = m.tensor(F32, (2, 10), np.ones((2, 10), np.float32))
+        w = m.tensor(I8, (10, 3), np.ones((10, 3), np.int8), scale=0.1)
+        y = m.tensor(F32, (2, 3))
+        m.batch_matmul(x, w, y)
+        m.set_io([], [y])
+
+    assert claimed(bmm_const_lhs) == 0
+
+    def sdpa(m, const_k):
+        q = m.tensor(F32, (1, 1, 8, 64))
+        k = m.tensor(F32, (1, 32, 2, 64), np.zeros((1, 32, 2, 64), np.float32) if const_k else None)
+        v = m.tensor(F32, (1, 32, 2, 64))
+        o = m.tensor(F32, (1, 1, 8, 64))
+        m.custom("odml.scaled_dot_product_attention", b"", [q, k, v], o)
+        m.set_io([q, v] if const_k else [q, k, v], [o])
+
+    assert claimed(lambda m: sdpa(m, False)) == 1
+    assert claimed(lambda m: sdpa(m, True)) == 0
+
+
 def test_no_cuda_device_fails_loudly_and_rolls_back(plugin_path):
     """On a host without a usable CUDA device the kernel's init must fail (no CPU fallback inside
     the delegate), and the runtime must be left with its original plan."""

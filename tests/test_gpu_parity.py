@@ -129,6 +129,60 @@ def test_fc_int8_reference_goldens(ops, oracle, ws, name):
     assert y.cpu().numpy().reshape(-1).tolist() == case["expected"]
 
 
+def _requant_on_device(ops, ws, acc, mult, shift, output_offset):
+    """Pushes int32 accumulators through the kernel's fixed-point requantization: one output channel per
+    value, weight 1 x input 0, the accumulator as the channel's bias, so y[n] = clamp(MBQM(acc[n]) + offset)."""
+    n = len(acc)
+    w = ops.PackedInt8Weights(dev(np.ones((n, 1), np.int8)))
+    y = ops.fully_connected_int8(dev(np.zeros((1, 1), np.int8)), w, dev(np.asarray(acc, np.int32)), 0, output_offset,
+                                 dev(np.asarray(mult, np.int32)), dev(np.asarray(shift, np.int32)), -128, 127, ws=ws)
+    return y.cpu().numpy().reshape(-1).astype(np.int64)
+
+
+def test_requantization_known_answers_on_the_device(ops, oracle, ws):
+    """tflite/kernels/internal/quantization_util_test.cc:447-485 through the device's requantize_mbqm: zero
+    multiplier, INT32_MIN / INT32_MAX inputs, negative multipliers, and max x max at shift -3. The int8
+    output clamps, so each case runs with the output offset that brings its expected value to 5."""
+    cases = []
+    for x, real, expected in gv.MBQM_INT32_KATS:
+        q, s = oracle.quantize_multiplier(real)
+        cases.append((x, q, s, expected))
+    m = 2**31 - 1
+    e = int(round(m * m / float(1 << 34)))
+    cases += [(m, m, -3, e), (-m, m, -3, -e)]
+    # left shifts (real multipliers above 1) and the saturating INT32_MIN x INT32_MIN product
+    for x, real in [(25, 3.7), (-25, 3.7), (1000, 1.0), (-7, 100.5), (12345, 2.0**-40)]:
+        q, s = oracle.quantize_multiplier(real)
+        cases.append((x, q, s, oracle.multiply_by_quantized_multiplier(x, q, s)))
+    cases.append((-(2**31), -(2**31), 0, oracle.multiply_by_quantized_multiplier(-(2**31), -(2**31), 0)))
+    for x, q, s, expected in cases:
+        assert oracle.multiply_by_quantized_multiplier(x, q, s) == expected
+        off = 5 - expected
+        if not -(2**31) <= off < 2**31:
+            off = -(2**31) + 1 if off < 0 else 2**31 - 1
+        want = max(-128, min(127, ((expected + off + 2**31) % 2**32) - 2**31))
+        got = _requant_on_device(ops, ws, [x], [q], [s], off)
+        assert got[0] == want, (x, q, s, expected, got[0])
+
+
+def test_requantization_random_sweep_on_the_device(ops, oracle, ws):
+    """4096 channels with random accumulators, multipliers and shifts from -20 to +3, against the oracle."""
+    rng = np.random.default_rng(77)
+    n = 4096
+    shift = rng.integers(-20, 4, n).astype(np.int32)
+    mult = rng.integers(2**30, 2**31, n).astype(np.int64)
+    mult[::7] *= -1
+    mult[5] = 0
+    # accumulators sized so that most results land inside int8
+    mag = np.clip(60.0 * 2.0 ** (-shift.astype(np.float64)), 1, 2**31 - 1)
+    acc = (rng.uniform(-1, 1, n) * mag).astype(np.int64)
+    want = np.asarray([max(-128, min(127, oracle.multiply_by_quantized_multiplier(int(a), int(q), int(s))))
+                       for a, q, s in zip(acc, mult, shift)])
+    got = _requant_on_device(ops, ws, acc, mult, shift, 0)
+    assert np.array_equal(got, want)
+    assert len(np.unique(want)) > 100
+
+
 # --------------------------------------------------------------------------- hybrid FC
 @pytest.mark.parametrize("name", sorted(gv.HYBRID_FC))
 def test_fc_hybrid_reference_goldens(ops, oracle, ws, name):
@@ -309,6 +363,41 @@ def test_sdpa_config4(ops, oracle, ws, kv):
                           k_scale=None if ksc is None else dev(ksc), v_scale=None if vsc is None else dev(vsc), ws=ws)
     want = _sdpa_oracle(oracle, c["q"], k, v, c["lengths"], c["scale"], ksc, vsc)
     assert rel_err(out.float().cpu().numpy(), want) <= 2e-2
+
+
+@pytest.mark.parametrize("kv", ["f16", "i8"])
+def test_sdpa_config4_at_its_stated_size_against_the_oracle(ops, oracle, ws, kv):
+    """16 sequences, ragged lengths uniform in [128, 8192], 8 query heads on one KV head of 256: every
+    sequence against the float32 restatement on the up-converted cache."""
+    c = workloads.config4()
+    assert c["k"].shape == (16, 8192, 1, 256) and c["lengths"].min() >= 128
+    ksc = vsc = None
+    k, v = c["k"], c["v"]
+    if kv == "i8":
+        k, ksc = workloads.quantize_kv_per_token(c["k"])
+        v, vsc = workloads.quantize_kv_per_token(c["v"])
+    out = ops.sdpa_decode(dev(c["q"]), dev(k), dev(v), dev(c["lengths"]), scale=c["scale"],
+                          k_scale=None if ksc is None else dev(ksc), v_scale=None if vsc is None else dev(vsc), ws=ws)
+    want = _sdpa_oracle(oracle, c["q"], k, v, c["lengths"], c["scale"], ksc, vsc)
+    got = out.float().cpu().numpy()
+    worst = max(rel_err(got[i], want[i]) for i in range(16))
+    print(f"config 4 ({kv} cache), {int(c['lengths'].sum())} cached tokens: worst sequence {worst:.3e}")
+    assert worst <= 2e-2
+
+
+def test_sdpa_empty_and_out_of_range_lengths(ops, oracle, ws):
+    """A batch slot with no cached tokens is a normal serving state: its output is zeros, not NaN, and a
+    length beyond the cache is read as the whole cache."""
+    c = workloads.config4(b=4, s_max=512, min_len=5)
+    L = c["lengths"].copy()
+    L[1] = 0
+    L[2] = -3
+    L[3] = 9999
+    out = ops.sdpa_decode(dev(c["q"]), dev(c["k"]), dev(c["v"]), dev(L), scale=c["scale"], ws=ws).float().cpu().numpy()
+    assert np.all(out[1] == 0) and np.all(out[2] == 0)
+    Lc = np.clip(L, 0, 512)
+    want = _sdpa_oracle(oracle, c["q"][[0, 3]], c["k"][[0, 3]], c["v"][[0, 3]], Lc[[0, 3]], c["scale"])
+    assert rel_err(out[[0, 3]], want) <= 2e-2
 
 
 def test_sdpa_config4_full_size_properties(ops, ws):
