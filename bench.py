@@ -1,6 +1,7 @@
 #!/usr/bin/env python
 """Decode benchmark: tokens/s of a Gemma-2B-shaped int8 (dynamic-range) decoder, with the HBM
-roofline of its dominant kernel (the streamed int8 GEMV) and a CPU baseline beside it.
+roofline of its dominant kernel (the streamed int8 GEMV), a parity record against the CPU graph on the
+same weights, the CPU baseline beside it, and one timed record per single-op configuration.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--context C] [--impl ours|reference]
 
@@ -8,11 +9,12 @@ One "step" is one decode step (one new token per sequence) over a KV cache that 
 `context` tokens. All inputs are synthetic: seeded random-init weights of the named architecture and
 random token ids. With --gpus N > 1 (launched under torchrun, one rank per GPU) every rank decodes
 its own batch on its own replica (independent invocations partitioned across GPUs, no data-path
-collective): weak scaling, aggregate tokens/s.
+collective): weak scaling, aggregate tokens/s; the same batch is also run tensor-parallel over all
+ranks and reported with its strong-scaling efficiency.
 
 --impl reference times the CPU implementation of the same graph (the oracle's vectorised,
 multi-threaded restatement of the reference kernels; the reference's own ruy/XNNPACK kernels cannot
-be built offline) on the host cores of the box, on a bounded sample of the workload.
+be built offline) on the host cores of the box, at the same context depth.
 """
 import argparse
 import json
@@ -28,12 +30,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "decode tokens/s (Gemma-2B-shaped int8) + GEMV HBM GB/s vs peak"
+DTYPE = "int8 weights x int8 dynamically quantized activations, int32 accumulate, fp32 outputs"
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--context", type=int, default=1024, help="tokens already in the KV cache when timing starts")
@@ -45,6 +48,8 @@ def parse_args():
                     help="also time this batch size (reported beside the headline; 0 = skip)")
     ap.add_argument("--tp", default="both", choices=["both", "peer", "nccl", "off"],
                     help="with --gpus > 1 also time ONE batch run tensor-parallel over all ranks")
+    ap.add_argument("--configs", default="on", choices=["on", "off"],
+                    help="one timed record per single-op configuration (1-4), at --gpus 1")
     return ap.parse_args()
 
 
@@ -58,8 +63,9 @@ def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
-            return json.load(f).get("hbm_gbs"), "measured"
-    return 6650.0, "fallback"
+            p = json.load(f)
+            return p.get("hbm_gbs"), p.get("bf16_tflops"), "measured"
+    return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -113,12 +119,12 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_reference_run(cfg, batch, steps, warmup, seed=1005):
-    """The CPU arm: all host threads, weights generated on the host with the same distributions."""
-    import oracle
+# ------------------------------------------------------------------------------------------- CPU arm
+def host_weights(cfg, seed=1005):
+    """The same distributions as litert_b200.decoder.make_weights, drawn on the host (used when no GPU
+    arm runs in this process: --impl reference)."""
     import torch
 
-    oracle.build()
     g = torch.Generator()
     g.manual_seed(seed)
 
@@ -140,19 +146,53 @@ def cpu_reference_run(cfg, batch, steps, warmup, seed=1005):
     layers = [dict(wq=w(qd, d), wk=w(kd, d), wv=w(kd, d), wo=w(d, qd), wgate=w(f, d), wup=w(f, d), wdown=w(d, f),
                    sq=s(qd), sk=s(kd), sv=s(kd), so=s(d), sgate=s(f), sup=s(f), sdown=s(d), norm1=gain(d),
                    norm2=gain(d)) for _ in range(cfg["n_layers"])]
-    weights = dict(layers=layers, embed=w(cfg["vocab"], d), embed_scales=s(cfg["vocab"]), final_norm=gain(d))
-    ref = oracle.DecoderRef(cfg, weights, batch, warmup + steps + 2, fast=True)
-    cores = oracle.fast().orcf_num_threads()
-    rng = np.random.default_rng(seed)
-    tok = rng.integers(0, cfg["vocab"], batch).astype(np.int32)
-    for _ in range(warmup):
-        tok, _ = ref.step(tok, want_logits=False)
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        tok, _ = ref.step(tok, want_logits=False)
-    dt = time.perf_counter() - t0
-    ref.close()
-    return batch * steps / dt, dt / steps * 1e3, cores
+    return dict(layers=layers, embed=w(cfg["vocab"], d), embed_scales=s(cfg["vocab"]), final_norm=gain(d))
+
+
+def to_host(weights):
+    out = dict(layers=[{k: v.cpu().numpy() for k, v in lw.items()} for lw in weights["layers"]])
+    for k in ("embed", "embed_scales", "final_norm"):
+        out[k] = weights[k].cpu().numpy()
+    return out
+
+
+def cpu_decode_rate(cfg, weights, batch, context, steps, threads=None, seed=1005):
+    """tokens/s of the CPU graph at `context` cached tokens per sequence (the cache rows hold zeros: the
+    work does not depend on their values). threads None = all host threads."""
+    import oracle
+
+    oracle.build()
+    fast = oracle.fast()
+    all_threads = fast.orcf_num_threads()
+    if threads:
+        fast.orcf_set_num_threads(int(threads))
+    try:
+        ref = oracle.DecoderRef(cfg, weights, batch, context + steps + 4, fast=True)
+        ref.set_lengths(np.full(batch, context, np.int32))
+        tok = np.random.default_rng(seed).integers(0, cfg["vocab"], batch).astype(np.int32)
+        tok, _ = ref.step(tok, want_logits=False)  # warm-up: page the weights in
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            tok, _ = ref.step(tok, want_logits=False)
+        dt = time.perf_counter() - t0
+        ref.close()
+    finally:
+        fast.orcf_set_num_threads(all_threads)
+    return batch * steps / dt, dt / steps * 1e3, (int(threads) if threads else all_threads)
+
+
+def cpu_baseline_record(cfg, weights, args):
+    steps = max(1, args.cpu_steps)
+    tps, ms, cores = cpu_decode_rate(cfg, weights, args.batch, args.context, steps)
+    one_steps = max(1, min(2, steps))
+    tps1, ms1, _ = cpu_decode_rate(cfg, weights, args.batch, args.context, one_steps, threads=1)
+    return {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "ms_per_step": ms,
+            "sample": f"{steps} decode steps after 1 warm-up, batch {args.batch}, {args.context} cached tokens per sequence, "
+                      f"all {cores} host threads (vectorised restatement of the reference kernels; ruy / XNNPACK "
+                      "cannot be built offline)",
+            "one_thread": {"value": tps1, "unit": "tokens/s", "cores": 1, "ms_per_step": ms1, "steps": one_steps,
+                           "note": "the reference's default thread count (kDefaultNumThreadpoolThreads = 1) and "
+                                   "the only mode of its hybrid kernel"}}
 
 
 def run_reference(args):
@@ -161,18 +201,18 @@ def run_reference(args):
         return
     cfg = model_config(args.model)
     steps = max(1, min(args.steps, args.cpu_steps))
-    warm = 1
-    tps, ms, cores = cpu_reference_run(cfg, args.batch, steps, warm)
-    sample = (f"{steps} decode steps after {warm} warm-up, batch {args.batch}, context {warm}..{warm + steps} tokens "
-              f"(attention over a short cache; the {weight_bytes(cfg) / 1e9:.2f} GB of weights per step dominate)")
+    weights = host_weights(cfg)
+    tps, ms, cores = cpu_decode_rate(cfg, weights, args.batch, args.context, steps)
+    sample = (f"{steps} decode steps after 1 warm-up, batch {args.batch}, {args.context} cached tokens per sequence "
+              f"(the {weight_bytes(cfg) / 1e9:.2f} GB of weights per step dominate), all {cores} host threads")
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8 weights x int8 dynamically quantized activations, int32 accumulate, fp32 outputs",
-        "data": "synthetic",
-        "config": workload_config(args, cfg),
+        "warmup": 1, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": DTYPE, "data": "synthetic", "config": workload_config(args, cfg),
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the CPU arm times a bounded sample (its step costs the same at every step of the run: the weights "
+                "dominate), the device arm the requested number of steps; both at the same context depth",
     }
     emit(line)
 
@@ -201,8 +241,240 @@ def workload_config(args, cfg):
             "l2": "inputs larger than L2: every step streams the full weight set (2.5 GB >> 126 MB)"}
 
 
-def tensor_parallel_run(args, cfg, mode, world, rank, local, barrier):
-    """One batch decoded by all ranks together: every rank holds 1/world of each projection."""
+# ------------------------------------------------------------------------------------------- parity
+def parity_record(cfg, d, host, kv):
+    """The device decoder against the CPU graph on the SAME weights, outside every timed region: a
+    16-token prompt through the prompt pass, then two decode steps compared on their logits. The CPU
+    graph keeps its cache rounded as the device does; `cpu_self_rel_l2` is the same CPU graph against
+    itself with a float32 cache, i.e. how far two correct evaluations of this random-init graph drift
+    apart from one rounding per cached value (the attention softmax is nearly a hard maximum)."""
+    import oracle
+
+    mode = 1 if kv == "f16" else 2
+    ref = oracle.DecoderRef(cfg, host, 1, 32, fast=True, kv_mode=mode)
+    ref32 = oracle.DecoderRef(cfg, host, 1, 32, fast=True, kv_mode=0)
+    rng = np.random.default_rng(77)
+    prompt = rng.integers(0, cfg["vocab"], 16).astype(np.int32)
+    for t in range(prompt.size):
+        nxt_r, _ = ref.step(prompt[t:t + 1], want_logits=False)
+        ref32.step(prompt[t:t + 1], want_logits=False)
+    d.reset()
+    first = d.prefill(prompt, seq=0)
+    tok = nxt_r
+    errs, selfs, equal, steps = [], [], int(first == int(nxt_r[0])), 2
+    for _ in range(steps):
+        nxt_g, lg = d.step(tok, want_logits=True)
+        nxt_r, lr = ref.step(tok, want_logits=True)
+        _, ls = ref32.step(tok, want_logits=True)
+        g = lg.cpu().numpy()
+        errs.append(float(np.linalg.norm(g - lr) / np.linalg.norm(lr)))
+        selfs.append(float(np.linalg.norm(ls - lr) / np.linalg.norm(lr)))
+        equal += int(nxt_g[0] == nxt_r[0])
+        tok = nxt_r
+    ref.close()
+    ref32.close()
+    return {"checked": True, "rel_l2": max(errs), "cpu_self_rel_l2": max(selfs), "tokens_equal": equal,
+            "tokens_compared": steps + 1, "against": "CPU restatement of the graph (oracle) on the same weights, "
+            "16-token prompt pass + 2 decode steps, logits over the whole vocabulary",
+            "per_kernel": "bit-exact / 1-LSB parity of every kernel at these widths: tests/test_gpu_glue.py"}
+
+
+# ------------------------------------------------------------------------------------------- single-op configurations
+def _median_launch_us(fn, launches=50, repeats=5, warm=3):
+    """Median over `repeats` of the device time per launch of `launches` back-to-back calls of fn(i),
+    replayed as one CUDA graph (the Python call overhead would otherwise hide kernels of a few us)."""
+    import torch
+
+    s = torch.cuda.Stream()
+    times = []
+    with torch.cuda.stream(s):
+        for i in range(warm):
+            fn(i)
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for i in range(launches):
+                fn(i)
+        g.replay()
+        s.synchronize()
+        for _ in range(repeats):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            g.replay()
+            e1.record(s)
+            s.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3 / launches)
+    return float(np.median(times))
+
+
+def _delegate_invoke_us(build_graph, invokes=10):
+    """The same op end to end through the plugin: tflite_plugin_create_delegate -> Prepare -> invoke with
+    HOST tensors (host-to-device copy of the inputs, launches, device-to-host copy of the outputs and a
+    stream synchronisation inside every invoke), driven by the mini runtime."""
+    try:
+        from tests import minirt
+    except Exception as exc:  # headers and prebuilt runtime both absent
+        return None, f"mini runtime unavailable: {exc}"
+    try:
+        m, d = minirt.MiniRuntime(), minirt.Delegate()
+        build_graph(m, minirt)
+        if m.apply(d) != 0 or m.partitions != 1 or m.cpu_nodes != 0:
+            return None, f"not delegated: {m.error}"
+        for _ in range(2):
+            if m.invoke() != 0:
+                return None, m.error
+        t0 = time.perf_counter()
+        for _ in range(invokes):
+            m.invoke()
+        us = (time.perf_counter() - t0) / invokes * 1e6
+        m.close()
+        d.close()
+        return us, None
+    except Exception as exc:
+        return None, str(exc)[:200]
+
+
+def config_records(hbm_peak, i8_peak_ops):
+    """One record per single-op configuration and row count: device time of the op through the C ABI
+    (median of 5 x 50 graph-replayed launches, distinct weight copies used in turn so that no launch
+    finds its weights in L2), its roofline fraction, and the same op through the delegate with host
+    tensors."""
+    import torch
+
+    from litert_b200 import ops, run_case, workloads
+
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    out = []
+
+    def record(cfg_no, label, m, us, alg_bytes, op_count, bound, copies, e2e, extra=None):
+        gbs = alg_bytes / (us * 1e-6) / 1e9
+        pops = op_count / (us * 1e-6) / 1e15
+        r = {"config": cfg_no, "op": label, "m": m, "us": us, "algorithmic_bytes": alg_bytes, "ops": op_count,
+             "gb_per_s": gbs, "pop_per_s": pops, "bound": bound, "frac_of_hbm_peak": gbs / hbm_peak,
+             "frac_of_int8_tensor_peak": (op_count / (us * 1e-6)) / i8_peak_ops if i8_peak_ops else None,
+             "frac": gbs / hbm_peak if bound == "hbm" else ((op_count / (us * 1e-6)) / i8_peak_ops if i8_peak_ops else None),
+             "weight_copies": copies, "timing": "median of 5 x 50 graph-replayed launches after 3 warm-ups",
+             "delegate_invoke_us": e2e[0], "delegate_invoke_note": e2e[1] or
+             "host tensors in and out through tflite_plugin_create_delegate -> Prepare -> invoke (mini runtime)"}
+        if extra:
+            r.update(extra)
+        out.append(r)
+
+    ws = ops.Workspace("cuda", 64 << 20)
+    # ---- config 1: full-integer int8 [32, 2048] x [2048, 2048]: 64 weight copies (256 MB > L2)
+    c = workloads.config1()
+    real = np.float64(c["input_scale"]) * c["filter_scales"].astype(np.float64) / np.float64(c["output_scale"])
+    mult, shift = (dev(t) for t in run_case._quantize_multipliers(real))
+    wps = [ops.PackedInt8Weights(dev(c["w"])) for _ in range(64)]
+    x, bias = dev(c["x"]), dev(c["bias"])
+    y = torch.empty((32, 2048), dtype=torch.int8, device="cuda")
+    us = _median_launch_us(lambda i: ops.fully_connected_int8(x, wps[i % 64], bias, c["input_zp"], c["output_zp"], mult,
+                                                              shift, ws=ws, out=y), launches=64)
+
+    def g1(m, rt):
+        w = m.tensor(rt.I8, (2048, 2048), c["w"], channel_scales=c["filter_scales"])
+        b = m.tensor(rt.I32, (2048,), c["bias"], channel_scales=c["filter_scales"] * c["input_scale"])
+        xi = m.tensor(rt.I8, (32, 2048), scale=float(c["input_scale"]), zero_point=c["input_zp"])
+        yo = m.tensor(rt.I8, (32, 2048), scale=float(c["output_scale"]), zero_point=c["output_zp"])
+        m.fully_connected(xi, w, b, yo)
+        m.set_io([xi], [yo])
+        m.write(xi, c["x"])
+
+    record(1, "FULLY_CONNECTED full-integer int8 [32,2048]x[2048,2048]", 32, us, 4349952, 2 * 32 * 2048 * 2048, "hbm", 64,
+           _delegate_invoke_us(g1))
+    del wps
+    torch.cuda.empty_cache()
+    # ---- config 2: hybrid [M, 4096] x [14336, 4096]
+    n, k = 14336, 4096
+    c = workloads.config2(512)
+    wps = [ops.PackedInt8Weights(dev(c["w"])) for _ in range(3)]
+    fs = dev(c["filter_scales"])
+    for m_rows in (1, 8, 64, 512):
+        x = dev(c["x"][:m_rows])
+        y = torch.empty((m_rows, n), device="cuda")
+        us = _median_launch_us(lambda i: ops.fully_connected_hybrid(x, wps[i % 3], fs, ws=ws, out=y))
+        alg = 58720256 + 57344 + m_rows * 16384 + m_rows * 57344
+
+        def g2(m, rt, m_rows=m_rows):
+            w = m.tensor(rt.I8, (n, k), c["w"], channel_scales=c["filter_scales"])
+            xi = m.tensor(rt.F32, (m_rows, k))
+            yo = m.tensor(rt.F32, (m_rows, n))
+            m.fully_connected(xi, w, None, yo, asymmetric=True)
+            m.set_io([xi], [yo])
+            m.write(xi, c["x"][:m_rows])
+
+        record(2, "FULLY_CONNECTED hybrid [M,4096]x[14336,4096]", m_rows, us, alg, 2 * m_rows * n * k,
+               "tensor" if m_rows >= 256 else "hbm", 3, _delegate_invoke_us(g2))
+    del wps
+    torch.cuda.empty_cache()
+    # ---- config 3: blockwise int4 [M, 2048] x [16384, 2048]
+    c = workloads.config3(512)
+    wps = [ops.PackedInt4Weights(dev(c["w4"]), dev(c["scales"]), c["blocksize"]) for _ in range(8)]
+    for m_rows in (1, 512):
+        x = dev(c["x"][:m_rows])
+        y = torch.empty((m_rows, 16384), device="cuda")
+        us = _median_launch_us(lambda i: ops.fully_connected_blockwise4(x, wps[i % 8], ws=ws, out=y))
+        alg = 16777216 + 2097152 + m_rows * 8192 + m_rows * 65536
+
+        def g3(m, rt, m_rows=m_rows):
+            w = m.tensor(rt.I4, (16384, 2048), c["w4"])
+            s = m.tensor(rt.F16, (16384, 64), c["scales"])
+            m.set_blockwise(w, s, 32)
+            xi = m.tensor(rt.F32, (m_rows, 2048))
+            yo = m.tensor(rt.F32, (m_rows, 16384))
+            m.fully_connected(xi, w, None, yo, asymmetric=True)
+            m.set_io([xi], [yo])
+            m.write(xi, c["x"][:m_rows])
+
+        record(3, "FULLY_CONNECTED blockwise int4 [M,2048]x[16384,2048]", m_rows, us, alg, 2 * m_rows * 16384 * 2048,
+               "tensor" if m_rows >= 256 else "hbm", 8, _delegate_invoke_us(g3))
+    del wps
+    torch.cuda.empty_cache()
+    # ---- config 4: flash-decode, 16 ragged sequences, 8 heads on one KV head of 256; two copies of the cache
+    c = workloads.config4()
+    total = int(c["lengths"].sum())
+    q, L = dev(c["q"]), dev(c["lengths"])
+    for kv in ("f16", "i8"):
+        if kv == "i8":
+            k8, ks = workloads.quantize_kv_per_token(c["k"])
+            v8, vs = workloads.quantize_kv_per_token(c["v"])
+            caches = [(dev(k8), dev(v8), dev(ks), dev(vs)) for _ in range(2)]
+        else:
+            caches = [(dev(c["k"]), dev(c["v"]), None, None) for _ in range(2)]
+        us = _median_launch_us(lambda i: ops.sdpa_decode(q, caches[i % 2][0], caches[i % 2][1], L, scale=c["scale"],
+                                                         k_scale=caches[i % 2][2], v_scale=caches[i % 2][3], ws=ws))
+        alg = (1024 if kv == "f16" else 520) * total + 131136
+        e2e = (None, "the composite's tensors are float32 in a graph: see the f32 record of the delegate tests")
+        if kv == "f16":
+            def g4(m, rt):
+                qi = m.tensor(rt.F32, (16, 1, 8, 256))
+                ki = m.tensor(rt.F32, (16, 8192, 1, 256))
+                vi = m.tensor(rt.F32, (16, 8192, 1, 256))
+                mk = m.tensor(rt.F32, (16, 1, 1, 8192))
+                yo = m.tensor(rt.F32, (16, 1, 8, 256))
+                m.composite("odml.scaled_dot_product_attention", rt.flex_map({"scale": float(c["scale"])}), [qi, ki, vi, mk], yo)
+                m.set_io([qi, ki, vi, mk], [yo])
+                m.write(qi, c["q"].astype(np.float32))
+                m.write(ki, c["k"].astype(np.float32))
+                m.write(vi, c["v"].astype(np.float32))
+                m.write(mk, np.where(np.arange(8192)[None, None, None, :] < c["lengths"][:, None, None, None], 0.0,
+                                     -1e30).astype(np.float32))
+            e2e = _delegate_invoke_us(g4, invokes=3)
+            if e2e[0] is not None:
+                e2e = (e2e[0], "float32 q / k / v and the additive mask as host tensors (268 MB of cache per invoke), as "
+                               "the composite appears in a graph")
+        record(4, f"odml.scaled_dot_product_attention decode, {kv} cache, 16 sequences, {total} cached tokens", 16, us, alg,
+               8192 * total, "hbm", 2, e2e)
+        del caches
+        torch.cuda.empty_cache()
+    return out
+
+
+# ------------------------------------------------------------------------------------------- device arm
+def tensor_parallel_run(args, cfg, mode, world, rank, local, barrier, one_gpu):
+    """One batch decoded by all ranks together: every rank holds 1/world of each projection. The logits
+    of the first step after the prompt are compared with the one-GPU decoder's (same weights, same
+    prompt): per-shard row quantization makes the sharded graph a different float computation."""
     import torch
     import torch.distributed as dist
 
@@ -212,6 +484,18 @@ def tensor_parallel_run(args, cfg, mode, world, rank, local, barrier):
     d = dec.Decoder(cfg, max_seq=max_seq, max_batch=args.batch, kv_dtype=args.kv, seed=1005, device=f"cuda:{local}",
                     tp_size=world, tp_rank=rank)
     d.connect(mode)
+    rng = np.random.default_rng(4242)
+    probe = rng.integers(0, cfg["vocab"], (12, args.batch)).astype(np.int32)
+    # ---- parity against the one-GPU decoder: 12 fixed tokens per sequence, logits of the last step
+    for t in range(probe.shape[0]):
+        _, lg = d.step(probe[t], want_logits=(t == probe.shape[0] - 1))
+    gathered = [torch.empty_like(lg) for _ in range(world)]
+    dist.all_gather(gathered, lg)
+    rel = None
+    if rank == 0 and one_gpu is not None:
+        full = torch.cat(gathered, dim=1).cpu().numpy()
+        rel = float(np.linalg.norm(full - one_gpu) / np.linalg.norm(one_gpu))
+    d.reset()
     first = np.random.default_rng(1005).integers(0, cfg["vocab"], args.batch).astype(np.int32)
     d.run(first, args.context, fetch=True)
     d.run(None, args.warmup, fetch=True)
@@ -236,6 +520,7 @@ def tensor_parallel_run(args, cfg, mode, world, rank, local, barrier):
     ms = t.item() / args.steps
     return {"tokens_per_s": args.batch / (ms * 1e-3), "ms_per_step": ms, "ranks": world, "scaling": "strong",
             "launches_per_step_per_rank": launches, "ranks_agree_on_tokens": bool(torch.equal(lo, hi)),
+            "max_rel_l2_vs_one_gpu": rel,
             "exchange": ("partial sums read from peer memory inside the consuming kernels (flag handshake, no "
                          "collective launch)") if mode == "peer" else "NCCL all-reduce between the kernels"}
 
@@ -244,6 +529,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
 
+    from litert_b200 import _lib
     from litert_b200 import decoder as dec
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -257,8 +543,15 @@ def run_ours(args):
     cfg = model_config(args.model)
     max_seq = args.context + args.warmup + 2 * args.steps + 16
     side_batch = 0 if args.side_batch == args.batch else args.side_batch
-    d = dec.Decoder(cfg, max_seq=max_seq, max_batch=max(args.batch, side_batch), kv_dtype=args.kv, seed=1005 + rank,
+    # the checks that need the CPU graph (parity, CPU baseline) run on rank 0 of a one-GPU run, on the
+    # SAME weights: drawn once on the device, copied to the host for the CPU side
+    with_cpu = world == 1
+    weights = dec.make_weights(cfg, seed=1005 + rank, device=f"cuda:{local}")
+    host = to_host(weights) if with_cpu else None
+    d = dec.Decoder(cfg, max_seq=max_seq, max_batch=max(args.batch, side_batch), kv_dtype=args.kv, weights=weights,
                     device=f"cuda:{local}")
+    del weights
+    torch.cuda.empty_cache()
     rng = np.random.default_rng(1005 + rank)
     stream = d.stream
 
@@ -341,13 +634,31 @@ def run_ours(args):
                 "gemv_gbs": weight_bytes(cfg) / (side_gemv_ms * 1e-3) / 1e9,
                 "prefill_tokens_per_s_per_gpu": side_prefill}
 
+    # ---- parity of this very decoder against the CPU graph on the same weights (untimed)
+    parity = None
+    if with_cpu and rank == 0:
+        try:
+            parity = parity_record(cfg, d, host, args.kv)
+        except Exception as exc:
+            parity = {"checked": False, "error": str(exc)[:300]}
+
+    # ---- one-GPU logits for the tensor-parallel comparison (rank 0's replica has seed 1005: the TP weights)
+    one_gpu_logits = None
+    if world > 1 and args.tp != "off" and rank == 0:
+        probe = np.random.default_rng(4242).integers(0, cfg["vocab"], (12, args.batch)).astype(np.int32)
+        d.reset()
+        for t in range(probe.shape[0]):
+            _, lg = d.step(probe[t], want_logits=(t == probe.shape[0] - 1))
+        one_gpu_logits = lg.cpu().numpy()
+
     times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = times.tolist()
+    line = None
     if rank == 0:
         tokens = args.batch * args.steps * world
-        peak, peak_kind = measured_peaks()
+        peak, bf16_peak, peak_kind = measured_peaks()
         wbytes = weight_bytes(cfg)
         # algorithmic bytes of the GEMV launches of one step: every int8 weight once, plus per launch the
         # per-channel scales and row sums (8 B per output channel), the quantized activation rows and the
@@ -360,11 +671,11 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": tokens / (dev_ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None,
-            "dtype": "int8 weights x int8 dynamically quantized activations, int32 accumulate, fp32 outputs",
+            "scaling": "weak", "vs_baseline": None, "dtype": DTYPE,
             "data": "synthetic", "config": workload_config(args, cfg),
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
-                    "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": e2e_ms / args.steps},
+                    "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": e2e_ms / args.steps,
+                    "through": "b200_decoder_step: host token ids in, host token ids out, one synchronisation per step"},
             "gpu_launches": launches * args.steps,
             "launches_per_step": launches,
             "clocks": clocks,
@@ -381,32 +692,57 @@ def run_ours(args):
                          "whole_step_frac": (wbytes / (dev_ms / args.steps * 1e-3) / 1e9) / peak},
             "step_breakdown_ms": {k: v[0] for k, v in prof.items()},
         }
+        if parity is not None:
+            line["parity"] = parity
         if side:
             line["side_batch"] = side
         if prefill:
             # 2 int8 operations per weight and prompt token (the LM head runs for the last token only)
-            ops = 2.0 * (wbytes - cfg["vocab"] * cfg["d_model"])
-            prefill["int8_pops"] = prefill["tokens_per_s_per_gpu"] * ops / 1e15
+            ops_per_token = 2.0 * (wbytes - cfg["vocab"] * cfg["d_model"])
+            prefill["int8_pops"] = prefill["tokens_per_s_per_gpu"] * ops_per_token / 1e15
             line["prefill"] = prefill
-        try:
-            if world > 1:
-                raise RuntimeError("timed at --gpus 1 only")
-            steps = max(1, min(args.cpu_steps, args.steps))
-            tps, ms, cores = cpu_reference_run(cfg, args.batch, steps, 1)
-            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
-                                    "sample": f"{steps} decode steps, batch {args.batch}, short context, all host threads"}
-        except Exception as exc:  # the baseline is a report, not part of the product path
-            line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port",
-                                    "sample": f"not run: {exc}"}
     d.close()
     del d
     torch.cuda.empty_cache()
+    if rank == 0 and with_cpu:
+        try:
+            line["cpu_baseline"] = cpu_baseline_record(cfg, host, args)
+        except Exception as exc:  # the baseline is a report, not part of the product path
+            line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port",
+                                    "sample": f"not run: {exc}"}
+        host = None
+        # ---- the int8 tensor peak of this device, and the single-op configurations against it
+        i8_peak = None
+        try:
+            ops_s, ms = ctypes_double(), ctypes_double()
+            if _lib.load().b200_measure_int8_tensor_peak(20000, ops_s, ms) == 0:
+                i8_peak = ops_s.value
+                line["int8_tensor_peak"] = {"pop_per_s": i8_peak / 1e15, "kernel_ms": ms.value,
+                                            "how": "one CTA per SM, resident-operand tcgen05.mma kind::i8 M128 N256 K32 back "
+                                                   "to back (b200_measure_int8_tensor_peak), best of 3",
+                                            "twice_measured_bf16_pop_per_s": 2 * bf16_peak / 1e3}
+                if prefill:
+                    prefill["frac_of_int8_tensor_peak"] = prefill["int8_pops"] * 1e15 / i8_peak
+        except Exception as exc:
+            line["int8_tensor_peak"] = {"error": str(exc)[:200]}
+        if args.configs == "on" and args.model == "gemma2b":
+            try:
+                line["configs"] = config_records(peak, i8_peak)
+            except Exception as exc:
+                line["configs"] = [{"error": str(exc)[:300]}]
+    elif rank == 0:
+        line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port",
+                                "sample": "timed at --gpus 1 only"}
     # ---- the same batch run tensor-parallel over all ranks (strong scaling of one sequence batch)
     tp = {}
     if world > 1 and args.tp != "off":
         for mode in (["peer", "nccl"] if args.tp == "both" else [args.tp]):
             try:
-                tp[mode] = tensor_parallel_run(args, cfg, mode, world, rank, local, barrier)
+                tp[mode] = tensor_parallel_run(args, cfg, mode, world, rank, local, barrier, one_gpu_logits)
+                if rank == 0:
+                    one_ms = dev_ms / args.steps
+                    tp[mode]["speedup_vs_one_gpu"] = one_ms / tp[mode]["ms_per_step"]
+                    tp[mode]["strong_efficiency"] = one_ms / tp[mode]["ms_per_step"] / world
             except Exception as exc:  # reported, the replica line above stands on its own
                 tp[mode] = {"error": str(exc)[:300]}
     if rank == 0:
@@ -415,6 +751,12 @@ def run_ours(args):
         emit(line)
     if world > 1:
         dist.destroy_process_group()
+
+
+def ctypes_double():
+    import ctypes
+
+    return ctypes.c_double(0.0)
 
 
 _RESULT_FD = None

@@ -78,6 +78,13 @@ B200_API int b200_read_status(void* d_zero_ws, void* stream, int* status_out);
 B200_API int b200_set_wait_budget(void* d_zero_ws, unsigned long long nanoseconds, void* stream);
 B200_API int b200_clear_status(void* d_zero_ws, void* stream);
 
+/* Measurement aid: the device's int8 tensor-core peak (operations per second; a
+ * multiply-add counts as two), from one CTA per SM issuing resident-operand
+ * tcgen05.mma kind::i8 instructions back to back, `iters` x 4 each: the
+ * denominator for the prefill GEMM's roofline fraction. Runs on the default
+ * stream, allocates 256 bytes for its duration and synchronises. */
+B200_API int b200_measure_int8_tensor_peak(int iters, double* ops_per_second, double* ms_out);
+
 /* ---- weight preparation (once per constant tensor) ----------------------
  * int8 weights [n,k] row-major, as a FULLY_CONNECTED filter tensor lies in
  * the model (tflite/kernels/fully_connected.cc:498-503). d_row_sums [n]

@@ -21,6 +21,7 @@ SIGNATURES = {
     "b200_read_status": (_i, [_vp, _vp, ctypes.POINTER(_i)]),
     "b200_set_wait_budget": (_i, [_vp, ctypes.c_ulonglong, _vp]),
     "b200_clear_status": (_i, [_vp, _vp]),
+    "b200_measure_int8_tensor_peak": (_i, [_i, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
     "b200_packed_w8_bytes": (_sz, [_i, _i]),
     "b200_pack_w8": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "b200_packed_w4_bytes": (_sz, [_i, _i]),

@@ -3,6 +3,9 @@
 The delegate is compiled against the LiteRT C headers where they lie in a LiteRT checkout
 (environment variable LITERT_ROOT); two of its small C sources (TfLiteIntArray helpers) are
 compiled from there too. Without the checkout an already built library is kept as is.
+
+The checkout is found through LITERT_ROOT or, when that is unset, as a directory named
+`reference` beside this repository.
 """
 import os
 import subprocess
@@ -10,7 +13,18 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc", "delegate")
 LIB = os.path.join(HERE, "lib")
-LITERT_ROOT = os.environ.get("LITERT_ROOT", "/root/reference")
+
+
+def litert_root():
+    """The LiteRT checkout: $LITERT_ROOT, else a sibling directory `reference` of this repository
+    (whether it exists is the caller's question)."""
+    env = os.environ.get("LITERT_ROOT")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+LITERT_ROOT = litert_root()
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 OUT = os.path.join(LIB, "libtflite_b200_delegate.so")
 # the LiteRT accelerator definition, under the file name the LiteRT environment loads

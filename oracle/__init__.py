@@ -26,7 +26,8 @@ def build(force=False):
                     for t in targets)
     if force or stale:
         subprocess.check_call(["make", "-C", _HERE, "-s", "liboracle.so", "liboracle_fast.so"])
-    ref_root = os.environ.get("LITERT_ROOT", "/root/reference")
+    # the LiteRT checkout: $LITERT_ROOT, else a directory `reference` beside this repository
+    ref_root = os.environ.get("LITERT_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
     if os.path.isdir(os.path.join(ref_root, "tflite")) and (
         force or not os.path.exists(os.path.join(_HERE, "_ref", "libref_quant.so"))
     ):
@@ -439,6 +440,12 @@ class DecoderRef:
 
     def reset(self):
         self.lib.orc_decoder_reset(self.h)
+
+    def set_lengths(self, lengths):
+        """Declares that many tokens already cached per sequence (the cache rows keep what they hold)."""
+        L = np.ascontiguousarray(lengths, np.int32)
+        assert L.size == self.batch
+        self.lib.orc_decoder_set_lengths(self.h, _p(L))
 
     def step(self, tokens, want_logits=True):
         tok = np.ascontiguousarray(tokens, np.int32)

@@ -214,6 +214,12 @@ void orc_stage_kv_round(float* row, int n, int mode) {
   }
 }
 
+/* Declares lengths[b] tokens already cached for sequence b (whatever the cache rows hold): lets the
+ * timed CPU baseline step at the same context depth as the device without stepping there first. */
+void orc_decoder_set_lengths(orc_decoder* d, const int32_t* lengths) {
+  for (int b = 0; b < d->batch; ++b) d->lengths[b] = lengths[b] < d->cfg.max_seq ? lengths[b] : d->cfg.max_seq - 1;
+}
+
 void orc_decoder_reset(orc_decoder* d) { memset(d->lengths, 0, sizeof(int) * (size_t)d->batch); }
 
 /* One token per sequence: tokens [batch] -> logits [batch, lm_rows] (may be NULL) and the greedy next

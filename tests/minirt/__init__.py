@@ -11,7 +11,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-LITERT_ROOT = os.environ.get("LITERT_ROOT", "/root/reference")
+LITERT_ROOT = os.environ.get("LITERT_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
 LIB = os.path.join(HERE, "libminirt.so")
 
 # TfLiteType values (tflite/core/c/c_api_types.h)

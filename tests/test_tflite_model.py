@@ -12,7 +12,8 @@ sys.path.insert(0, HERE)
 import minirt  # noqa: E402
 from litert_b200 import tflite_model as tm  # noqa: E402
 
-REF = os.environ.get("LITERT_ROOT", "/root/reference")
+REF = os.environ.get("LITERT_ROOT") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                                                     "reference")
 needs_reference = pytest.mark.skipif(not os.path.isdir(REF + "/tflite"), reason="reference tree not present")
 
 
