@@ -131,6 +131,17 @@ B200_API int b200_fc_hybrid(const float* d_x, int m, int k, const void* d_w_pack
                             const float* d_bias, int asymmetric_inputs, int activation, float* d_y,
                             void* d_zero_ws, void* d_scratch, size_t scratch_bytes, void* stream);
 
+/* BATCH_MATMUL, hybrid, one [m,k] x [k,n] product over a packed right-hand side
+ * ([n,k] as b200_pack_w8 takes it: the reference transposes the RHS to that form
+ * once, tflite/kernels/batch_matmul.cc:791-798). Replaces the hybrid
+ * reference_ops::BatchMatMul (tflite/kernels/internal/reference/batch_matmul.h:
+ * 111-209), including its zero-point correction through float (:189,197), which
+ * b200_fc_hybrid does in int32 as FULLY_CONNECTED's kernel does. */
+B200_API int b200_bmm_hybrid(const float* d_x, int m, int k, const void* d_w_packed, int n,
+                             const int32_t* d_row_sums, const float* d_w_scales, int per_channel,
+                             int asymmetric_inputs, float* d_y, void* d_zero_ws, void* d_scratch,
+                             size_t scratch_bytes, void* stream);
+
 /* Blockwise int4. Replaces EvalBlockwise4Bit
  * (tflite/kernels/fully_connected.cc:1014-1086): always asymmetric inputs, no
  * fused activation. blocksize must be a multiple of 32. */
@@ -153,6 +164,16 @@ B200_API int b200_sdpa_decode(const void* d_q, const void* d_k, const void* d_v,
                               void* d_out, int b, int n, int nkv, int h, int s_max, int q_dtype, int kv_dtype,
                               float scale, float logit_cap, void* d_workspace, size_t workspace_bytes,
                               void* stream);
+
+/* The composite with any number of query tokens: q / out [b,t,n,h], k / v
+ * [b,s_max,nkv,h] (f16 or f32), d_mask [b,1,t,s_max] additive (optional): SDPAEval
+ * as it stands (tflite/experimental/genai/sdpa.cc:361-662), every (sequence,
+ * query token) pair treated as one attention row over its sequence's cache.
+ * Workspace: b200_sdpa_workspace_bytes(b * t, n, nkv, h, s_max). A causal prompt
+ * pass without a mask tensor is faster through b200_sdpa_rows. */
+B200_API int b200_sdpa(const void* d_q, const void* d_k, const void* d_v, const float* d_mask, void* d_out, int b,
+                       int t, int n, int nkv, int h, int s_max, int q_dtype, int kv_dtype, float scale,
+                       float logit_cap, void* d_workspace, size_t workspace_bytes, void* stream);
 
 /* Prompt-shaped attention: `rows` query tokens of ONE sequence (q and out [rows, n, h]) over that
  * sequence's cache (k / v [s_max, nkv, h], scales [s_max, nkv] for int8), row r attending over the
@@ -178,6 +199,9 @@ B200_API int b200_sdpa_rows(const void* d_q, const void* d_k, const void* d_v, c
  * are rejected with B200_ERR_UNSUPPORTED. The first call on a device looks up
  * the array's device address (set-up; make it before any stream capture).
  * Calls share the array: calls that overlap on the GPU race, serialise them.
+ * The array is the current device's: make the stream's device current first (a
+ * stream of another device is refused). Head layouts that the split-K kernels do
+ * not take need no workspace and are not limited by the array's size.
  * Calls no cudaMalloc/cudaFree or allocating routine. */
 B200_API size_t b200_sdpa_static_workspace_limit(void);
 B200_API int b200_sdpa_decode_static(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale,
@@ -199,6 +223,12 @@ B200_API const char* b200_sdpa_static_last_error(void);
 B200_API const char* b200_glue_last_error(void);
 B200_API size_t b200_tiled_rows_bytes(int m, int k);
 B200_API int b200_untile_rows(const int8_t* d_q_tiled, int m, int k, int8_t* d_q_rowmajor, void* stream);
+
+/* Transposes the two minor dimensions of `batches` row-major matrices [rows, cols]
+ * of elem_bytes-byte elements (1 or 4): what TransposeRowsColumns does for
+ * BATCH_MATMUL's adj_x / adj_y (tflite/kernels/batch_matmul.cc:789-808). */
+B200_API int b200_transpose_matrices(const void* d_in, void* d_out, int batches, int rows, int cols, int elem_bytes,
+                                     void* stream);
 
 /* Hybrid EMBEDDING_LOOKUP (tflite/kernels/embedding_lookup.cc:EvalHybrid:
  * out[r,:] = table[ids[r],:] * row_scale[ids[r]]) followed by the graph's MUL by

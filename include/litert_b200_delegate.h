@@ -54,6 +54,11 @@ __attribute__((visibility("default"))) void tflite_plugin_destroy_delegate(struc
  * lets tests assert from the other side); -1 for NULL. */
 __attribute__((visibility("default"))) int b200_delegate_num_claimed_nodes(const struct TfLiteDelegate* delegate);
 
+/* Number of decomposition subgraphs of claimed composites that the last Prepare marked
+ * delegation-skippable through tflite::delegates::MarkSubgraphAsDelegationSkippable
+ * (tflite/delegates/utils.h:62-93), when the process exports that function; -1 for NULL. */
+__attribute__((visibility("default"))) int b200_delegate_num_skippable_subgraphs(const struct TfLiteDelegate* delegate);
+
 /* The delegate's device-arena planner as a pure host function (no CUDA): for n
  * tensors with sizes and [first_use, last_use] op intervals, writes 256-byte
  * aligned offsets and returns the slab size. Same job as ArenaPlanner +

@@ -30,6 +30,9 @@ SIGNATURES = {
     "b200_fc_int8": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _i, _i32, _i32, _vp, _vp, _vp,
                           _sz, _vp]),
     "b200_fc_hybrid": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
+    "b200_bmm_hybrid": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
+    "b200_sdpa": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _sz, _vp]),
+    "b200_transpose_matrices": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "b200_fc_w4": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "b200_sdpa_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "b200_sdpa_rows_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),

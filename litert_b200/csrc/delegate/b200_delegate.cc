@@ -23,6 +23,7 @@
 #include <vector>
 
 #include <cuda_runtime_api.h>
+#include <dlfcn.h>
 
 #include "../../../include/litert_b200.h"
 #include "../../../include/litert_b200_delegate.h"
@@ -63,6 +64,15 @@ struct Options {
     }                                                                                  \
   } while (0)
 
+#define B200_GLUE_OR_RETURN(ctx, expr)                                                 \
+  do {                                                                                 \
+    int _rc = (expr);                                                                  \
+    if (_rc != B200_OK) {                                                              \
+      TF_LITE_KERNEL_LOG((ctx), "B200 delegate: %s", b200_glue_last_error());          \
+      return kTfLiteDelegateError;                                                     \
+    }                                                                                  \
+  } while (0)
+
 // ---------------------------------------------------------------- device helpers
 struct DeviceMem {
   void* ptr = nullptr;
@@ -87,11 +97,12 @@ struct DelegateState {
   TfLiteDelegate delegate;
   cudaStream_t stream = nullptr;
   DeviceMem zero_ws, scratch, sdpa_ws;
+  DeviceMem bmm_lhs, bmm_rhs, bmm_packed, bmm_row_sums;  // BATCH_MATMUL temporaries (transposed operands, run-time RHS)
   bool ready = false;
   // buffer handles: handle id -> (device pointer, bytes)
   std::unordered_map<int, std::pair<const void*, size_t>> handles;
   int next_handle = 1;
-  int delegated_nodes = 0, partitions = 0;
+  int delegated_nodes = 0, partitions = 0, skippable_marked = 0;
 
   TfLiteStatus EnsureDevice(TfLiteContext* ctx) {
     CUDA_OK(ctx, cudaSetDevice(options.device));
@@ -130,6 +141,41 @@ inline const TfLiteAffineQuantization* Affine(const TfLiteTensor& t) {
   return t.quantization.type == kTfLiteAffineQuantization
              ? static_cast<const TfLiteAffineQuantization*>(t.quantization.params)
              : nullptr;
+}
+
+// Geometry of one BATCH_MATMUL: [.., m, k] x [.., k, n] with up to three broadcast batch dimensions
+// (the reference extends both shapes to five, tflite/kernels/internal/reference/batch_matmul.h:
+// 118-135). lhs_mats / rhs_mats: matrices held by each operand; out_mats: products computed.
+struct BmmGeometry {
+  int m = 0, k = 0, n = 0;
+  int lhs_batch[3] = {1, 1, 1}, rhs_batch[3] = {1, 1, 1}, out_batch[3] = {1, 1, 1};
+  int lhs_mats = 1, rhs_mats = 1, out_mats = 1;
+};
+
+bool BmmShapes(const TfLiteTensor& x, const TfLiteTensor& w, bool adj_x, bool adj_y, BmmGeometry* g) {
+  const int xr = x.dims->size, wr = w.dims->size;
+  if (xr < 2 || xr > 5 || wr < 2 || wr > 5) return false;
+  const int xm = x.dims->data[xr - 2], xk = x.dims->data[xr - 1];
+  const int wk = w.dims->data[wr - 2], wn = w.dims->data[wr - 1];
+  g->m = adj_x ? xk : xm;
+  g->k = adj_x ? xm : xk;
+  g->n = adj_y ? wk : wn;
+  if ((adj_y ? wn : wk) != g->k || g->m <= 0 || g->k <= 0 || g->n <= 0) return false;
+  for (int d = 0; d < 3; ++d) {
+    const int xi = xr - 3 - (2 - d), wi = wr - 3 - (2 - d);  // right-aligned batch dimensions
+    g->lhs_batch[d] = xi >= 0 ? x.dims->data[xi] : 1;
+    g->rhs_batch[d] = wi >= 0 ? w.dims->data[wi] : 1;
+    const int l = g->lhs_batch[d], r = g->rhs_batch[d];
+    if (l <= 0 || r <= 0 || (l != r && l != 1 && r != 1)) return false;
+    g->out_batch[d] = l == 1 ? r : l;
+  }
+  // (the reference's hybrid row sums only cover the two inner batch dimensions of the RHS,
+  // batch_matmul.h:151-153: an RHS with an outer one is left to it)
+  if (g->rhs_batch[0] != 1) return false;
+  g->lhs_mats = g->lhs_batch[0] * g->lhs_batch[1] * g->lhs_batch[2];
+  g->rhs_mats = g->rhs_batch[0] * g->rhs_batch[1] * g->rhs_batch[2];
+  g->out_mats = g->out_batch[0] * g->out_batch[1] * g->out_batch[2];
+  return g->out_mats <= 4096;
 }
 
 bool IsSdpaNode(const TfLiteNode* node, const TfLiteRegistration* reg) {
@@ -204,16 +250,25 @@ OpKind Classify(TfLiteContext* ctx, const TfLiteNode* node, const TfLiteRegistra
     const TfLiteTensor *x = in(0), *w = in(1);
     const TfLiteTensor* y = &T[node->outputs->data[0]];
     if (!p || !x || !w) return *why = "missing operands", OpKind::kNone;
-    if (p->adj_x) return *why = "adj_x", OpKind::kNone;
-    if (!IsConst(*w) || w->dims->size != 2) return *why = "rhs not a constant matrix", OpKind::kNone;
     if (IsConst(*x)) return *why = "constant lhs", OpKind::kNone;
-    if (x->dims->size < 2) return *why = "lhs rank", OpKind::kNone;
+    if (w->allocation_type == kTfLiteMmapRo && !w->data.raw) return *why = "rhs without data", OpKind::kNone;
+    BmmGeometry g;
+    if (!BmmShapes(*x, *w, p->adj_x, p->adj_y, &g)) return *why = "batch_matmul shapes", OpKind::kNone;
+    if (NumElements(*y) != static_cast<int64_t>(g.out_mats) * g.m * g.n) return *why = "output shape", OpKind::kNone;
+    const auto* q = Affine(*w);
+    const bool per_channel = q && q->scale && q->scale->size > 1;
     if (x->type == kTfLiteFloat32 && w->type == kTfLiteInt8 && y->type == kTfLiteFloat32) {
-      const auto* q = Affine(*w);
-      if (q && q->scale && q->scale->size > 1) return *why = "per-channel rhs", OpKind::kNone;
+      if (per_channel) {
+        // the scales follow the output columns: the RHS's N axis (tflite/kernels/batch_matmul.cc:701-708, 487-497)
+        const int n_axis = p->adj_y ? w->dims->size - 2 : w->dims->size - 1;
+        if (q->quantized_dimension != n_axis || q->scale->size != g.n) return *why = "per-channel rhs axis", OpKind::kNone;
+      }
       return OpKind::kBmmHybrid;
     }
-    if (x->type == kTfLiteInt8 && w->type == kTfLiteInt8 && y->type == kTfLiteInt8) return OpKind::kBmmInt8;
+    if (x->type == kTfLiteInt8 && w->type == kTfLiteInt8 && y->type == kTfLiteInt8) {
+      if (per_channel) return *why = "per-channel int8 rhs", OpKind::kNone;
+      return OpKind::kBmmInt8;
+    }
     return *why = "tensor types", OpKind::kNone;
   }
   if (opt.claim_sdpa && IsSdpaNode(node, reg)) {
@@ -223,17 +278,25 @@ OpKind Classify(TfLiteContext* ctx, const TfLiteNode* node, const TfLiteRegistra
     if (!q || !k || !v) return *why = "sdpa operands", OpKind::kNone;
     for (const TfLiteTensor* t : {q, k, v, m})
       if (t && IsConst(*t)) return *why = "sdpa with a constant operand", OpKind::kNone;
+    // float32 tensors as the reference op and XNNPACK take them (xnnpack_delegate.cc:6404-6433), or all
+    // float16 (a graph converted with half-precision activations); the additive mask stays float32
     for (const TfLiteTensor* t : {q, k, v, y})
-      if (t->type != kTfLiteFloat32 || t->dims->size != 4) return *why = "sdpa wants 4-D float32", OpKind::kNone;
+      if ((t->type != kTfLiteFloat32 && t->type != kTfLiteFloat16) || t->type != q->type || t->dims->size != 4)
+        return *why = "sdpa wants 4-D float32 or float16 tensors of one type", OpKind::kNone;
     if (m && (m->type != kTfLiteFloat32 || m->dims->size != 4)) return *why = "sdpa mask", OpKind::kNone;
     const int B = q->dims->data[0], Tq = q->dims->data[1], N = q->dims->data[2], H = q->dims->data[3];
     const int S = k->dims->data[1], Nkv = k->dims->data[2];
-    if (Tq != 1) return *why = "sdpa with more than one query token", OpKind::kNone;
+    if (B <= 0 || Tq <= 0 || N <= 0 || H <= 0 || S <= 0) return *why = "sdpa shapes", OpKind::kNone;
     if (k->dims->data[0] != B || v->dims->data[0] != B || k->dims->data[3] != H || v->dims->data[3] != H ||
         v->dims->data[1] != S || v->dims->data[2] != Nkv || Nkv <= 0 || N % Nkv != 0)
       return *why = "sdpa shapes", OpKind::kNone;  // xnnpack_delegate.cc:6433-6459
+    if (y->dims->data[0] != B || y->dims->data[1] != Tq || y->dims->data[2] != N || y->dims->data[3] != H)
+      return *why = "sdpa output shape", OpKind::kNone;
     if (m && (m->dims->data[0] != B || m->dims->data[1] != 1 || m->dims->data[2] != Tq || m->dims->data[3] != S))
       return *why = "sdpa mask shape", OpKind::kNone;
+    // head layouts outside the split-K kernels run on a fallback that keeps S logits in shared memory
+    if (!(N / Nkv <= 8 && (H == 64 || H == 128 || H == 256)) && (static_cast<int64_t>(S) + H) * 4 > 200 * 1024)
+      return *why = "sdpa cache too long for this head layout", OpKind::kNone;
     return OpKind::kSdpa;
   }
   return *why = "op not on the hot path", OpKind::kNone;
@@ -251,8 +314,14 @@ struct OpRecord {
   bool per_channel = false, asymmetric = false;
   int activation = 0;
   int32_t input_offset = 0, filter_offset = 0, output_offset = 0, act_min = -128, act_max = 127;
+  // batch_matmul
+  int w = -1;                       // right-hand side tensor (graph numbering)
+  bool adj_x = false, adj_y = false, rhs_const = true, fold_lhs = false;
+  BmmGeometry g;
+  size_t packed_stride = 0;         // bytes between the packed matrices of a batched RHS
   // sdpa
-  int B = 0, N = 0, Nkv = 0, H = 0, S = 0;
+  int B = 0, T = 1, N = 0, Nkv = 0, H = 0, S = 0;
+  int sdpa_dtype = B200_DTYPE_F32;
   float scale = 0.0f, logit_cap = 0.0f;
 };
 
@@ -365,12 +434,25 @@ class DelegateKernel {
         req[it->second].last_use = op_index;
       }
     };
-    size_t scratch = 0, sdpa = 0;
+    size_t scratch = 0, sdpa = 0, bmm_lhs = 0, bmm_rhs = 0, bmm_packed = 0, bmm_rs = 0;
     for (int i = 0; i < num_ops; ++i) {
       OpRecord& op = *ops_[i];
       if (op.kind == OpKind::kSdpa) {
         for (int t : {op.q, op.k, op.v, op.mask, op.y}) touch(t, i);
-        sdpa = std::max(sdpa, b200_sdpa_workspace_bytes(op.B, op.N, op.Nkv, op.H, op.S));
+        sdpa = std::max(sdpa, b200_sdpa_workspace_bytes(op.B * op.T, op.N, op.Nkv, op.H, op.S));
+      } else if (op.kind == OpKind::kBmmHybrid || op.kind == OpKind::kBmmInt8) {
+        touch(op.x, i);
+        touch(op.w, i);  // a run-time right-hand side lives in the arena (a constant one is skipped)
+        touch(op.y, i);
+        op.m = op.fold_lhs ? op.g.m * op.g.lhs_mats : op.g.m;
+        scratch = std::max(scratch, b200_fc_scratch_bytes(op.m, op.kdim));
+        if (op.adj_x) bmm_lhs = std::max(bmm_lhs, ctx->tensors[op.x].bytes);
+        if (!op.rhs_const) {
+          const size_t mats = static_cast<size_t>(op.g.rhs_mats);
+          if (!op.adj_y) bmm_rhs = std::max(bmm_rhs, ctx->tensors[op.w].bytes);
+          bmm_packed = std::max(bmm_packed, mats * b200_packed_w8_bytes(op.n, op.kdim));
+          bmm_rs = std::max(bmm_rs, mats * sizeof(int32_t) * op.n);
+        }
       } else {
         const TfLiteTensor& x = ctx->tensors[op.x];
         op.m = static_cast<int>(NumElements(x) / op.kdim);  // fully_connected.cc:502
@@ -392,7 +474,8 @@ class DelegateKernel {
       TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device arena allocation of %zu bytes failed", arena_.planned_bytes());
       return kTfLiteDelegateError;
     }
-    if (!st_->scratch.ensure(scratch) || !st_->sdpa_ws.ensure(sdpa)) {
+    if (!st_->scratch.ensure(scratch) || !st_->sdpa_ws.ensure(sdpa) || !st_->bmm_lhs.ensure(bmm_lhs) ||
+        !st_->bmm_rhs.ensure(bmm_rhs) || !st_->bmm_packed.ensure(bmm_packed) || !st_->bmm_row_sums.ensure(bmm_rs)) {
       TF_LITE_KERNEL_LOG(ctx, "B200 delegate: workspace allocation failed");
       return kTfLiteDelegateError;
     }
@@ -545,31 +628,16 @@ class DelegateKernel {
         }
         return kTfLiteOk;
       }
-      case OpKind::kFcHybrid:
-      case OpKind::kBmmHybrid: {
+      case OpKind::kFcHybrid: {
         op->x = idx(0);
         const TfLiteTensor& w = T[idx(1)];
-        const TfLiteTensor* b = nullptr;
-        const bool bmm = op->kind == OpKind::kBmmHybrid;
-        bool transpose = false;
-        if (bmm) {
-          const auto* p = static_cast<const TfLiteBatchMatMulParams*>(node->builtin_data);
-          // rhs [k,n] unless adj_y ([n,k]); the reference transposes a constant rhs once
-          // (tflite/kernels/batch_matmul.cc:791-798)
-          transpose = !p->adj_y;
-          op->n = p->adj_y ? w.dims->data[0] : w.dims->data[1];
-          op->kdim = p->adj_y ? w.dims->data[1] : w.dims->data[0];
-          op->asymmetric = p->asymmetric_quantize_inputs;
-          op->activation = kTfLiteActNone;
-        } else {
-          const auto* p = static_cast<const TfLiteFullyConnectedParams*>(node->builtin_data);
-          op->n = w.dims->data[0];
-          op->kdim = w.dims->data[1];
-          op->asymmetric = p->asymmetric_quantize_inputs;
-          op->activation = p->activation;
-          if (idx(2) >= 0) b = &T[idx(2)];
-        }
-        TF_LITE_ENSURE_STATUS(PackInt8(ctx, w.data.int8, op->n, op->kdim, transpose, op));
+        const auto* p = static_cast<const TfLiteFullyConnectedParams*>(node->builtin_data);
+        op->n = w.dims->data[0];
+        op->kdim = w.dims->data[1];
+        op->asymmetric = p->asymmetric_quantize_inputs;
+        op->activation = p->activation;
+        const TfLiteTensor* b = idx(2) >= 0 ? &T[idx(2)] : nullptr;
+        TF_LITE_ENSURE_STATUS(PackInt8(ctx, w.data.int8, op->n, op->kdim, false, op));
         const auto* q = Affine(w);
         std::vector<float> scales;
         if (q && q->scale && q->scale->size > 1) {
@@ -583,27 +651,74 @@ class DelegateKernel {
         if (b) TF_LITE_ENSURE_STATUS(UploadRaw(ctx, b->data.raw, sizeof(float) * op->n, &op->bias));
         return kTfLiteOk;
       }
+      case OpKind::kBmmHybrid:
       case OpKind::kBmmInt8: {
         const auto* p = static_cast<const TfLiteBatchMatMulParams*>(node->builtin_data);
         op->x = idx(0);
-        const TfLiteTensor &x = T[op->x], &w = T[idx(1)], &y = T[op->y];
-        op->n = p->adj_y ? w.dims->data[0] : w.dims->data[1];
-        op->kdim = p->adj_y ? w.dims->data[1] : w.dims->data[0];
-        TF_LITE_ENSURE_STATUS(PackInt8(ctx, w.data.int8, op->n, op->kdim, !p->adj_y, op));
-        // tflite/kernels/batch_matmul.cc:315-331 and 528-556
-        const double ips = static_cast<double>(x.params.scale * w.params.scale);
-        std::vector<int32_t> mult(1), shift(1);
-        int sh;
-        QuantizeMultiplier(ips / static_cast<double>(y.params.scale), &mult[0], &sh);
-        shift[0] = sh;
-        TF_LITE_ENSURE_STATUS(Upload(ctx, mult, &op->mult));
-        TF_LITE_ENSURE_STATUS(Upload(ctx, shift, &op->shift));
-        op->per_channel = false;
-        op->input_offset = -x.params.zero_point;
-        op->filter_offset = -w.params.zero_point;
-        op->output_offset = y.params.zero_point;
-        op->act_min = -128;
-        op->act_max = 127;
+        op->w = idx(1);
+        const TfLiteTensor &x = T[op->x], &w = T[op->w], &y = T[op->y];
+        if (!BmmShapes(x, w, p->adj_x, p->adj_y, &op->g)) return kTfLiteDelegateError;
+        op->adj_x = p->adj_x;
+        op->adj_y = p->adj_y;
+        op->n = op->g.n;
+        op->kdim = op->g.k;
+        op->rhs_const = IsConst(w);
+        // one right-hand matrix for every left-hand one: the leading dimensions of the LHS fold into its
+        // rows (the reference's own compression, tflite/kernels/batch_matmul.cc:768-788; not with adj_x)
+        op->fold_lhs = op->g.rhs_mats == 1 && !op->adj_x;
+        op->packed_stride = b200_packed_w8_bytes(op->n, op->kdim);
+        if (op->rhs_const) {
+          // the reference transposes a constant RHS once and keeps it (batch_matmul.cc:791-798): here it is
+          // transposed, uploaded and repacked once, matrix by matrix
+          const size_t mat = static_cast<size_t>(op->n) * op->kdim, mats = static_cast<size_t>(op->g.rhs_mats);
+          if (!op->packed.ensure(mats * op->packed_stride) || !op->row_sums.ensure(mats * sizeof(int32_t) * op->n)) {
+            TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed");
+            return kTfLiteDelegateError;
+          }
+          DeviceMem staging;
+          std::vector<int8_t> t(mat);
+          for (size_t i = 0; i < mats; ++i) {
+            const int8_t* host = w.data.int8 + i * mat;
+            if (!op->adj_y) {
+              for (int r = 0; r < op->kdim; ++r)
+                for (int c = 0; c < op->n; ++c) t[static_cast<size_t>(c) * op->kdim + r] = host[static_cast<size_t>(r) * op->n + c];
+              host = t.data();
+            }
+            TF_LITE_ENSURE_STATUS(UploadRaw(ctx, host, mat, &staging));
+            B200_OK_OR_RETURN(ctx, b200_pack_w8(static_cast<const int8_t*>(staging.ptr), op->n, op->kdim,
+                                               static_cast<uint8_t*>(op->packed.ptr) + i * op->packed_stride,
+                                               static_cast<int32_t*>(op->row_sums.ptr) + i * op->n, st_->stream));
+            CUDA_OK(ctx, cudaStreamSynchronize(st_->stream));  // staging and `t` are reused
+          }
+        }
+        if (op->kind == OpKind::kBmmHybrid) {
+          op->asymmetric = p->asymmetric_quantize_inputs;
+          const auto* q = Affine(w);
+          std::vector<float> scales;
+          if (q && q->scale && q->scale->size > 1) {
+            scales.assign(q->scale->data, q->scale->data + q->scale->size);
+            op->per_channel = true;
+          } else {
+            scales.assign(1, w.params.scale);  // batch_matmul.cc:498-503
+            op->per_channel = false;
+          }
+          TF_LITE_ENSURE_STATUS(Upload(ctx, scales, &op->w_scales));
+        } else {
+          // tflite/kernels/batch_matmul.cc:315-331 and 528-556
+          const double ips = static_cast<double>(x.params.scale * w.params.scale);
+          std::vector<int32_t> mult(1), shift(1);
+          int sh;
+          QuantizeMultiplier(ips / static_cast<double>(y.params.scale), &mult[0], &sh);
+          shift[0] = sh;
+          TF_LITE_ENSURE_STATUS(Upload(ctx, mult, &op->mult));
+          TF_LITE_ENSURE_STATUS(Upload(ctx, shift, &op->shift));
+          op->per_channel = false;
+          op->input_offset = -x.params.zero_point;
+          op->filter_offset = -w.params.zero_point;
+          op->output_offset = y.params.zero_point;
+          op->act_min = -128;
+          op->act_max = 127;
+        }
         return kTfLiteOk;
       }
       case OpKind::kFcW4: {
@@ -635,6 +750,8 @@ class DelegateKernel {
         op->mask = node->inputs->size > 3 ? idx(3) : -1;
         const TfLiteTensor &q = T[op->q], &k = T[op->k];
         op->B = q.dims->data[0];
+        op->T = q.dims->data[1];
+        op->sdpa_dtype = q.type == kTfLiteFloat16 ? B200_DTYPE_F16 : B200_DTYPE_F32;
         op->N = q.dims->data[2];
         op->H = q.dims->data[3];
         op->S = k.dims->data[1];
@@ -665,7 +782,6 @@ class DelegateKernel {
     cudaStream_t s = st_->stream;
     switch (op.kind) {
       case OpKind::kFcInt8:
-      case OpKind::kBmmInt8:
         B200_OK_OR_RETURN(ctx, b200_fc_int8(static_cast<const int8_t*>(Dev(op.x)), op.m, op.kdim, op.packed.ptr, op.n,
                                            static_cast<const int32_t*>(op.row_sums.ptr),
                                            static_cast<const int32_t*>(op.bias.ptr), op.input_offset, op.filter_offset,
@@ -675,7 +791,6 @@ class DelegateKernel {
                                            st_->scratch.ptr, st_->scratch.bytes, s));
         return kTfLiteOk;
       case OpKind::kFcHybrid:
-      case OpKind::kBmmHybrid:
         B200_OK_OR_RETURN(ctx, b200_fc_hybrid(static_cast<const float*>(Dev(op.x)), op.m, op.kdim, op.packed.ptr, op.n,
                                              static_cast<const int32_t*>(op.row_sums.ptr),
                                              static_cast<const float*>(op.w_scales.ptr), op.per_channel ? 1 : 0,
@@ -683,6 +798,9 @@ class DelegateKernel {
                                              op.activation, static_cast<float*>(Dev(op.y)), st_->zero_ws.ptr,
                                              st_->scratch.ptr, st_->scratch.bytes, s));
         return kTfLiteOk;
+      case OpKind::kBmmHybrid:
+      case OpKind::kBmmInt8:
+        return LaunchBmm(ctx, op);
       case OpKind::kFcW4:
         B200_OK_OR_RETURN(ctx, b200_fc_w4(static_cast<const float*>(Dev(op.x)), op.m, op.kdim, op.packed.ptr, op.n, 32,
                                          static_cast<const float*>(op.kfsum.ptr),
@@ -690,15 +808,83 @@ class DelegateKernel {
                                          st_->zero_ws.ptr, st_->scratch.ptr, st_->scratch.bytes, s));
         return kTfLiteOk;
       case OpKind::kSdpa:
-        B200_OK_OR_RETURN(ctx, b200_sdpa_decode(Dev(op.q), Dev(op.k), Dev(op.v), nullptr, nullptr, nullptr,
-                                               op.mask >= 0 ? static_cast<const float*>(Dev(op.mask)) : nullptr,
-                                               Dev(op.y), op.B, op.N, op.Nkv, op.H, op.S, B200_DTYPE_F32,
-                                               B200_DTYPE_F32, op.scale, op.logit_cap, st_->sdpa_ws.ptr,
-                                               st_->sdpa_ws.bytes, s));
+        if (op.T == 1) {
+          B200_OK_OR_RETURN(ctx, b200_sdpa_decode(Dev(op.q), Dev(op.k), Dev(op.v), nullptr, nullptr, nullptr,
+                                                 op.mask >= 0 ? static_cast<const float*>(Dev(op.mask)) : nullptr,
+                                                 Dev(op.y), op.B, op.N, op.Nkv, op.H, op.S, op.sdpa_dtype,
+                                                 op.sdpa_dtype, op.scale, op.logit_cap, st_->sdpa_ws.ptr,
+                                                 st_->sdpa_ws.bytes, s));
+        } else {
+          // several query tokens per sequence (a prompt pass): every (sequence, token) pair is one row
+          B200_OK_OR_RETURN(ctx, b200_sdpa(Dev(op.q), Dev(op.k), Dev(op.v),
+                                          op.mask >= 0 ? static_cast<const float*>(Dev(op.mask)) : nullptr, Dev(op.y),
+                                          op.B, op.T, op.N, op.Nkv, op.H, op.S, op.sdpa_dtype, op.sdpa_dtype, op.scale,
+                                          op.logit_cap, st_->sdpa_ws.ptr, st_->sdpa_ws.bytes, s));
+        }
         return kTfLiteOk;
       default:
         return kTfLiteDelegateError;
     }
+  }
+
+  // One BATCH_MATMUL: operands brought to [.., m, k] and packed [n, k] form (transposes as the reference's
+  // TransposeRowsColumns, a run-time RHS repacked every invocation), then one product per output matrix
+  // with the reference's broadcast rule (tflite/kernels/internal/reference/batch_matmul.h:30-51).
+  TfLiteStatus LaunchBmm(TfLiteContext* ctx, OpRecord& op) {
+    cudaStream_t s = st_->stream;
+    const BmmGeometry& g = op.g;
+    const bool hybrid = op.kind == OpKind::kBmmHybrid;
+    const size_t elem = hybrid ? sizeof(float) : 1;
+    const uint8_t* lhs = static_cast<const uint8_t*>(Dev(op.x));
+    if (op.adj_x) {
+      B200_GLUE_OR_RETURN(ctx, b200_transpose_matrices(lhs, st_->bmm_lhs.ptr, g.lhs_mats, g.k, g.m, static_cast<int>(elem), s));
+      lhs = static_cast<const uint8_t*>(st_->bmm_lhs.ptr);
+    }
+    const uint8_t* packed = static_cast<const uint8_t*>(op.packed.ptr);
+    const int32_t* row_sums = static_cast<const int32_t*>(op.row_sums.ptr);
+    if (!op.rhs_const) {
+      const int8_t* rhs = static_cast<const int8_t*>(Dev(op.w));
+      if (!op.adj_y) {
+        B200_GLUE_OR_RETURN(ctx, b200_transpose_matrices(rhs, st_->bmm_rhs.ptr, g.rhs_mats, g.k, g.n, 1, s));
+        rhs = static_cast<const int8_t*>(st_->bmm_rhs.ptr);
+      }
+      for (int i = 0; i < g.rhs_mats; ++i)
+        B200_OK_OR_RETURN(ctx, b200_pack_w8(rhs + static_cast<size_t>(i) * op.n * op.kdim, op.n, op.kdim,
+                                           static_cast<uint8_t*>(st_->bmm_packed.ptr) + i * op.packed_stride,
+                                           static_cast<int32_t*>(st_->bmm_row_sums.ptr) + static_cast<size_t>(i) * op.n, s));
+      packed = static_cast<const uint8_t*>(st_->bmm_packed.ptr);
+      row_sums = static_cast<const int32_t*>(st_->bmm_row_sums.ptr);
+    }
+    uint8_t* out = static_cast<uint8_t*>(Dev(op.y));
+    const int products = op.fold_lhs ? 1 : g.out_mats;
+    for (int o = 0; o < products; ++o) {
+      int li = 0, ri = 0;
+      if (!op.fold_lhs) {
+        const int b2 = o % g.out_batch[2], b1 = (o / g.out_batch[2]) % g.out_batch[1], b0 = o / (g.out_batch[2] * g.out_batch[1]);
+        const int b[3] = {b0, b1, b2};
+        for (int d = 0; d < 3; ++d) {
+          li = li * g.lhs_batch[d] + (g.lhs_batch[d] == 1 ? 0 : b[d]);
+          ri = ri * g.rhs_batch[d] + (g.rhs_batch[d] == 1 ? 0 : b[d]);
+        }
+      }
+      const uint8_t* x = lhs + static_cast<size_t>(li) * g.m * g.k * elem;
+      const uint8_t* w = packed + static_cast<size_t>(ri) * op.packed_stride;
+      const int32_t* rs = row_sums + static_cast<size_t>(ri) * op.n;
+      uint8_t* y = out + static_cast<size_t>(o) * g.m * g.n * elem;
+      if (hybrid) {
+        B200_OK_OR_RETURN(ctx, b200_bmm_hybrid(reinterpret_cast<const float*>(x), op.m, op.kdim, w, op.n, rs,
+                                              static_cast<const float*>(op.w_scales.ptr), op.per_channel ? 1 : 0,
+                                              op.asymmetric ? 1 : 0, reinterpret_cast<float*>(y), st_->zero_ws.ptr,
+                                              st_->scratch.ptr, st_->scratch.bytes, s));
+      } else {
+        B200_OK_OR_RETURN(ctx, b200_fc_int8(reinterpret_cast<const int8_t*>(x), op.m, op.kdim, w, op.n, rs, nullptr,
+                                           op.input_offset, op.filter_offset, op.output_offset,
+                                           static_cast<const int32_t*>(op.mult.ptr), static_cast<const int32_t*>(op.shift.ptr),
+                                           0, op.act_min, op.act_max, reinterpret_cast<int8_t*>(y), st_->zero_ws.ptr,
+                                           st_->scratch.ptr, st_->scratch.bytes, s));
+      }
+    }
+    return kTfLiteOk;
   }
 
   DelegateState* st_;
@@ -735,6 +921,18 @@ TfLiteStatus KernelInvoke(TfLiteContext* ctx, TfLiteNode* node) {
   return static_cast<DelegateKernel*>(node->user_data)->Invoke(ctx, node);
 }
 
+// tflite::delegates::MarkSubgraphAsDelegationSkippable(const TfLiteContext*, int)
+// (tflite/delegates/utils.h:62-93) lives in the runtime, not in TfLiteContext's table of function
+// pointers: a plugin finds it among the symbols of the process that loaded it, and goes without when
+// the runtime does not export it (the composite's decomposition subgraph is then merely unused, as with
+// XNNPACK).
+using MarkSkippableFn = TfLiteStatus (*)(const TfLiteContext*, int);
+MarkSkippableFn FindMarkSkippable() {
+  static MarkSkippableFn fn = reinterpret_cast<MarkSkippableFn>(
+      dlsym(RTLD_DEFAULT, "_ZN6tflite9delegates33MarkSubgraphAsDelegationSkippableEPK13TfLiteContexti"));
+  return fn;
+}
+
 TfLiteStatus DelegatePrepare(TfLiteContext* ctx, TfLiteDelegate* delegate) {
   auto* st = static_cast<DelegateState*>(delegate->data_);
   TfLiteIntArray* plan = nullptr;
@@ -747,7 +945,16 @@ TfLiteStatus DelegatePrepare(TfLiteContext* ctx, TfLiteDelegate* delegate) {
     TfLiteRegistration* reg = nullptr;
     TF_LITE_ENSURE_STATUS(ctx->GetNodeAndRegistration(ctx, node_index, &node, &reg));
     std::string why;
-    if (Classify(ctx, node, reg, st->options, &why) != OpKind::kNone) supported.push_back(node_index);
+    if (Classify(ctx, node, reg, st->options, &why) == OpKind::kNone) continue;
+    supported.push_back(node_index);
+    // a claimed composite carries its decomposition as another subgraph: tell the runtime that this
+    // delegate has taken care of it, so that it is not delegated on its own
+    if (reg->builtin_code == kTfLiteBuiltinStablehloComposite) {
+      const auto* p = static_cast<const TfLiteStablehloCompositeParams*>(node->builtin_data);
+      if (MarkSkippableFn mark = FindMarkSkippable()) {
+        if (p && p->subgraph_index > 0 && mark(ctx, p->subgraph_index) == kTfLiteOk) ++st->skippable_marked;
+      }
+    }
   }
   st->delegated_nodes = static_cast<int>(supported.size());
   if (supported.empty()) return kTfLiteOk;  // nothing to claim is not an error
@@ -866,6 +1073,10 @@ size_t b200_arena_plan(int n, const size_t* bytes, const int* first_use, const i
   const size_t total = b200::PlanArena(req, num_ops, &off);
   for (int i = 0; i < n; ++i) offsets[i] = off[i];
   return total;
+}
+
+int b200_delegate_num_skippable_subgraphs(const TfLiteDelegate* delegate) {
+  return delegate ? static_cast<const DelegateState*>(delegate->data_)->skippable_marked : -1;
 }
 
 int b200_delegate_num_claimed_nodes(const TfLiteDelegate* delegate) {

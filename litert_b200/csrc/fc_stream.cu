@@ -66,7 +66,13 @@ __device__ __forceinline__ void epilogue_hybrid(const FcParams& p, int nt, int m
         const int m = m_base + j * 8 + t4 * 2 + e;
         if (m >= p.m) continue;
         int32_t dot = acc[j][half * 2 + e];
-        if (p.in_zps) dot -= rs * p.in_zps[m];
+        if (p.float_offset) {
+          // BATCH_MATMUL's reference kernel subtracts through float (tflite/kernels/internal/reference/batch_matmul.h:189,197)
+          const float off = p.in_zps ? (float)p.in_zps[m] : 0.0f;
+          dot = __float2int_rz(__fsub_rn((float)dot, __fmul_rn((float)rs, off)));
+        } else if (p.in_zps) {
+          dot -= rs * p.in_zps[m];
+        }
         // reference order: scale = in_scale * w_scale; out = bias + dot*scale
         const float scale = __fmul_rn(p.in_scales[m], ws);
         float out = __fadd_rn(bias, __fmul_rn((float)dot, scale));

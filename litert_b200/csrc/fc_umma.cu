@@ -87,6 +87,17 @@ struct UmmaLayout {
   static constexpr int kTmemCols = 2 * NB < 32 ? 32 : 2 * NB;
 };
 
+// The zero-point correction of the hybrid path. FULLY_CONNECTED subtracts in int32
+// (tflite/kernels/internal/reference/portable_tensor_utils.cc:165-206). BATCH_MATMUL's hybrid kernel
+// writes `total -= row_sum * batch_offset` with a FLOAT batch_offset
+// (tflite/kernels/internal/reference/batch_matmul.h:189,197): the int32 total goes through float, the
+// product is rounded, the difference is rounded and truncated back to int32. Identical until a term
+// passes 2^24; reproduced here bit for bit when the op is a BATCH_MATMUL.
+__device__ __forceinline__ int32_t hybrid_dot(const FcParams& p, int32_t total, int32_t rs, int32_t zp) {
+  if (!p.float_offset) return total - rs * zp;
+  return __float2int_rz(__fsub_rn((float)total, __fmul_rn((float)rs, (float)zp)));
+}
+
 // Value of one output element from its exact int32 dot product: the float's bits (hybrid), the
 // int32 (raw) or the requantized int8 (sign-extended).
 template <int EPI>
@@ -94,7 +105,7 @@ __device__ __forceinline__ int32_t compute_output(const FcParams& p, int32_t tot
                                                   int32_t base_i, int32_t mult, int32_t shift, float in_scale,
                                                   int32_t in_aux) {
   if constexpr (EPI == kEpiHybridF32) {
-    const int32_t dot = total - rs * in_aux;  // in_aux: the row's zero point
+    const int32_t dot = hybrid_dot(p, total, rs, in_aux);  // in_aux: the row's zero point
     // reference order: scale = in_scale * w_scale; out = bias + dot * scale (no fused multiply-add)
     const float scale = __fmul_rn(in_scale, ws);
     float out = __fadd_rn(bias_f, __fmul_rn((float)dot, scale));
@@ -117,7 +128,7 @@ __device__ __forceinline__ void store_output(const FcParams& p, int m, int n, in
                                              float bias_f, int32_t base_i, int32_t mult, int32_t shift,
                                              float in_scale, int32_t in_aux) {
   if constexpr (EPI == kEpiHybridF32) {
-    const int32_t dot = total - rs * in_aux;  // in_aux: the row's zero point
+    const int32_t dot = hybrid_dot(p, total, rs, in_aux);  // in_aux: the row's zero point
     // reference order: scale = in_scale * w_scale; out = bias + dot * scale (no fused multiply-add)
     const float scale = __fmul_rn(in_scale, ws);
     float out = __fadd_rn(bias_f, __fmul_rn((float)dot, scale));

@@ -35,6 +35,22 @@ __global__ void untile_rows_kernel(const int8_t* __restrict__ q_tiled, int m, in
   for (int i = threadIdx.x; i < k; i += blockDim.x) out[(size_t)row * k + i] = q_tiled[q_tiled_offset(row, i, m_alloc)];
 }
 
+template <typename T>
+__global__ void transpose_matrices_kernel(const T* __restrict__ in, T* __restrict__ out, int rows, int cols) {
+  __shared__ T tile[32][33];
+  const size_t base = (size_t)blockIdx.z * rows * cols;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int r = r0 + j, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = in[base + (size_t)r * cols + c];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) out[base + (size_t)c * rows + r] = tile[threadIdx.x][j];
+  }
+}
+
 void fill_fc_ws(FcParams& p, void* d_zero_ws) {
   uint8_t* z = static_cast<uint8_t*>(d_zero_ws);
   p.status = reinterpret_cast<int*>(z);
@@ -58,6 +74,21 @@ int b200_untile_rows(const int8_t* d_q_tiled, int m, int k, int8_t* d_q_rowmajor
   if (!d_q_tiled || !d_q_rowmajor || m <= 0 || k <= 0) return gfail(B200_ERR_INVALID_ARGUMENT, "b200_untile_rows: bad argument");
   untile_rows_kernel<<<m, 256, 0, static_cast<cudaStream_t>(stream)>>>(d_q_tiled, m, k, m_alloc_for(m), d_q_rowmajor);
   return gcuda(cudaGetLastError(), "b200_untile_rows");
+}
+
+int b200_transpose_matrices(const void* d_in, void* d_out, int batches, int rows, int cols, int elem_bytes, void* stream) {
+  if (!d_in || !d_out || batches <= 0 || rows <= 0 || cols <= 0 || batches > 65535)
+    return gfail(B200_ERR_INVALID_ARGUMENT, "b200_transpose_matrices: bad argument");
+  const dim3 grid((cols + 31) / 32, (rows + 31) / 32, batches), block(32, 8);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (elem_bytes == 1) {
+    transpose_matrices_kernel<int8_t><<<grid, block, 0, s>>>(static_cast<const int8_t*>(d_in), static_cast<int8_t*>(d_out), rows, cols);
+  } else if (elem_bytes == 4) {
+    transpose_matrices_kernel<float><<<grid, block, 0, s>>>(static_cast<const float*>(d_in), static_cast<float*>(d_out), rows, cols);
+  } else {
+    return gfail(B200_ERR_UNSUPPORTED, "b200_transpose_matrices: element size %d", elem_bytes);
+  }
+  return gcuda(cudaGetLastError(), "b200_transpose_matrices");
 }
 
 int b200_embedding_lookup(const int32_t* d_ids, int rows, const int8_t* d_table, const float* d_row_scales, int vocab,

@@ -52,6 +52,7 @@ struct FcParams {
   const float* bias_f32;     // [n] or null
   const int32_t* row_sums;   // [n]
   int activation;
+  int float_offset;          // hybrid: zero-point correction through float, as BATCH_MATMUL's reference kernel does
   // int8 epilogue
   const int32_t* bias_i32;
   const int32_t* multipliers;  // [n] or [1]
@@ -138,6 +139,9 @@ struct SdpaParams {
   int m_alloc;
   size_t ws_bytes;
   int* status;
+  // > 1: rows b * rows_per_kv .. + rows_per_kv - 1 are the query tokens of sequence b and attend over
+  // that sequence's cache (the composite with several query tokens; q / out / mask are then indexed by row)
+  int rows_per_kv;
   // 1: every row of the batch attends over the SAME cache (k / v / scales of one sequence, [s_max, nkv, h]),
   // row b up to lengths[b] tokens: a prompt pass, whose rows are consecutive tokens of one sequence
   int shared_kv;

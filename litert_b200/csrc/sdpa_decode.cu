@@ -159,7 +159,8 @@ struct WarpAttention {
   static __device__ __forceinline__ Rows cache_rows(const SdpaParams& p, int b, int kvh) {
     Rows r;
     r.stride = (size_t)p.nkv * H * kv_elem_bytes<KV>();
-    const size_t first = (p.shared_kv ? (size_t)0 : (size_t)b * p.s_max) * p.nkv + kvh;
+    const size_t seq = p.shared_kv ? (size_t)0 : (size_t)(p.rows_per_kv > 1 ? b / p.rows_per_kv : b);
+    const size_t first = seq * p.s_max * p.nkv + kvh;
     r.k = static_cast<const uint8_t*>(p.k) + first * H * kv_elem_bytes<KV>();
     r.v = static_cast<const uint8_t*>(p.v) + first * H * kv_elem_bytes<KV>();
     r.k_scale = p.k_scale ? p.k_scale + first : nullptr;
@@ -1249,7 +1250,7 @@ __global__ void sdpa_decode_generic_kernel(const SdpaParams p) {
   }
   __syncwarp();
   auto kv_at = [&](const void* basep, const float* sc, int s, int d) -> float {
-    const size_t tok = ((size_t)(p.shared_kv ? 0 : b) * p.s_max + s) * p.nkv + kvh;
+    const size_t tok = ((size_t)(p.shared_kv ? 0 : (p.rows_per_kv > 1 ? b / p.rows_per_kv : b)) * p.s_max + s) * p.nkv + kvh;
     const size_t idx = tok * h + d;
     if (KV == kKvF16) return __half2float(static_cast<const __half*>(basep)[idx]);
     if (KV == kKvF32) return static_cast<const float*>(basep)[idx];

@@ -88,12 +88,23 @@ int b200_sdpa_decode_static(const void* d_q, const void* d_k, const void* d_v, c
     return static_fail(B200_ERR_UNSUPPORTED, "b200_sdpa_decode_static: kv dtype %d", kv_dtype);
   if (kv_dtype == B200_DTYPE_I8 && (!d_k_scale || !d_v_scale))
     return static_fail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa_decode_static: int8 cache needs scales");
-  const size_t need = b200::sdpa_workspace_bytes(b, n, nkv, h, s_max);
+  // only the split-K kernels use the workspace; other head layouts run on a kernel that needs none
+  const bool uses_workspace = n / nkv <= 8 && (h == 64 || h == 128 || h == 256);
+  const size_t need = uses_workspace ? b200::sdpa_workspace_bytes(b, n, nkv, h, s_max) : 0;
   if (need > kStaticWorkspaceBytes)
     return static_fail(B200_ERR_UNSUPPORTED,
                        "b200_sdpa_decode_static: this shape needs %zu bytes of workspace, the built-in one holds %zu "
                        "(use b200_sdpa_decode with a caller-owned workspace)",
                        need, kStaticWorkspaceBytes);
+  // the array's address is that of the CURRENT device: a stream of another device would be handed
+  // the wrong GPU's memory
+  if (stream) {
+    int cur = -1, sdev = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cudaStreamGetDevice(static_cast<cudaStream_t>(stream), &sdev) == cudaSuccess &&
+        sdev != cur)
+      return static_fail(B200_ERR_INVALID_ARGUMENT,
+                         "b200_sdpa_decode_static: the stream belongs to device %d but device %d is current", sdev, cur);
+  }
   void* ws = nullptr;
   const int rc = workspace_for_current_device(&ws);
   if (rc != B200_OK) return rc;

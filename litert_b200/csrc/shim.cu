@@ -220,14 +220,15 @@ int b200_fc_int8(const int8_t* d_x, int m, int k, const void* d_w_packed, int n,
   return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_fc_int8");
 }
 
-int b200_fc_hybrid(const float* d_x, int m, int k, const void* d_w_packed, int n, const int32_t* d_row_sums,
-                   const float* d_w_scales, int per_channel, const float* d_bias, int asymmetric_inputs,
-                   int activation, float* d_y, void* d_zero_ws, void* d_scratch, size_t scratch_bytes, void* stream) {
-  int rc = check_fc_common("b200_fc_hybrid", d_x, m, k, d_w_packed, n, d_y, d_zero_ws, d_scratch, scratch_bytes);
+static int fc_hybrid_impl(const char* name, const float* d_x, int m, int k, const void* d_w_packed, int n,
+                          const int32_t* d_row_sums, const float* d_w_scales, int per_channel, const float* d_bias,
+                          int asymmetric_inputs, int activation, int float_offset, float* d_y, void* d_zero_ws,
+                          void* d_scratch, size_t scratch_bytes, void* stream) {
+  int rc = check_fc_common(name, d_x, m, k, d_w_packed, n, d_y, d_zero_ws, d_scratch, scratch_bytes);
   if (rc) return rc;
-  if (!d_w_scales) return fail(B200_ERR_INVALID_ARGUMENT, "b200_fc_hybrid: weight scales are null");
-  if (asymmetric_inputs && !d_row_sums) return fail(B200_ERR_INVALID_ARGUMENT, "b200_fc_hybrid: row sums needed for asymmetric inputs");
-  if (activation < B200_ACT_NONE || activation > B200_ACT_SIGMOID) return fail(B200_ERR_INVALID_ARGUMENT, "b200_fc_hybrid: bad activation %d", activation);
+  if (!d_w_scales) return fail(B200_ERR_INVALID_ARGUMENT, "%s: weight scales are null", name);
+  if ((asymmetric_inputs || float_offset) && !d_row_sums) return fail(B200_ERR_INVALID_ARGUMENT, "%s: row sums needed", name);
+  if (activation < B200_ACT_NONE || activation > B200_ACT_SIGMOID) return fail(B200_ERR_INVALID_ARGUMENT, "%s: bad activation %d", name, activation);
   if (m == 0) return B200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int k_tiles = b200::tiles_k8(k);
@@ -235,7 +236,7 @@ int b200_fc_hybrid(const float* d_x, int m, int k, const void* d_w_packed, int n
   const int m_alloc = b200::m_alloc_for(m);
   cudaError_t e = b200::launch_quantize_rows(d_x, m, k, k_tiles * 128, m_alloc, asymmetric_inputs, sc.q_tiled, nullptr,
                                              sc.scales, sc.zps, s);
-  if (e != cudaSuccess) return cuda_fail(e, "b200_fc_hybrid (quantize)");
+  if (e != cudaSuccess) return cuda_fail(e, name);
   b200::FcParams p;
   memset(&p, 0, sizeof(p));
   p.w_packed = static_cast<const uint8_t*>(d_w_packed);
@@ -248,10 +249,25 @@ int b200_fc_hybrid(const float* d_x, int m, int k, const void* d_w_packed, int n
   p.bias_f32 = d_bias;
   p.row_sums = d_row_sums;
   p.activation = activation;
+  p.float_offset = float_offset;
   p.y = d_y;
   fill_ws(p, d_zero_ws);
   e = run_fc_i8(p, b200::kEpiHybridF32, s);
-  return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_fc_hybrid");
+  return e == cudaSuccess ? B200_OK : cuda_fail(e, name);
+}
+
+int b200_fc_hybrid(const float* d_x, int m, int k, const void* d_w_packed, int n, const int32_t* d_row_sums,
+                   const float* d_w_scales, int per_channel, const float* d_bias, int asymmetric_inputs,
+                   int activation, float* d_y, void* d_zero_ws, void* d_scratch, size_t scratch_bytes, void* stream) {
+  return fc_hybrid_impl("b200_fc_hybrid", d_x, m, k, d_w_packed, n, d_row_sums, d_w_scales, per_channel, d_bias,
+                        asymmetric_inputs, activation, 0, d_y, d_zero_ws, d_scratch, scratch_bytes, stream);
+}
+
+int b200_bmm_hybrid(const float* d_x, int m, int k, const void* d_w_packed, int n, const int32_t* d_row_sums,
+                    const float* d_w_scales, int per_channel, int asymmetric_inputs, float* d_y, void* d_zero_ws,
+                    void* d_scratch, size_t scratch_bytes, void* stream) {
+  return fc_hybrid_impl("b200_bmm_hybrid", d_x, m, k, d_w_packed, n, d_row_sums, d_w_scales, per_channel, nullptr,
+                        asymmetric_inputs, B200_ACT_NONE, 1, d_y, d_zero_ws, d_scratch, scratch_bytes, stream);
 }
 
 int b200_fc_w4(const float* d_x, int m, int k, const void* d_w4_packed, int n, int blocksize, const float* d_kfsum,
@@ -282,6 +298,10 @@ int b200_fc_w4(const float* d_x, int m, int k, const void* d_w4_packed, int n, i
   return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_fc_w4");
 }
 
+// Shapes the split-K attention kernels take (the others run on the one-warp-per-head fallback,
+// which needs no workspace but holds all logits of a head in shared memory).
+static bool sdpa_fast_shape(int n, int nkv, int h) { return n % nkv == 0 && n / nkv <= 8 && (h == 64 || h == 128 || h == 256); }
+
 size_t b200_sdpa_workspace_bytes(int b, int n, int nkv, int h, int s_max) {
   if (b <= 0 || n <= 0 || nkv <= 0 || h <= 0 || s_max <= 0) return 0;
   return b200::sdpa_workspace_bytes(b, n, nkv, h, s_max);
@@ -297,6 +317,11 @@ int b200_sdpa_decode(const void* d_q, const void* d_k, const void* d_v, const fl
   if (q_dtype != B200_DTYPE_F16 && q_dtype != B200_DTYPE_F32) return fail(B200_ERR_UNSUPPORTED, "b200_sdpa_decode: q dtype %d", q_dtype);
   if (kv_dtype < B200_DTYPE_F16 || kv_dtype > B200_DTYPE_F32) return fail(B200_ERR_UNSUPPORTED, "b200_sdpa_decode: kv dtype %d", kv_dtype);
   if (kv_dtype == B200_DTYPE_I8 && (!d_k_scale || !d_v_scale)) return fail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa_decode: int8 cache needs scales");
+  if (sdpa_fast_shape(n, nkv, h) && (!d_workspace || workspace_bytes < b200::sdpa_workspace_bytes(b, n, nkv, h, s_max)))
+    return fail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa_decode: workspace too small (%zu < %zu, see b200_sdpa_workspace_bytes)",
+                workspace_bytes, b200::sdpa_workspace_bytes(b, n, nkv, h, s_max));
+  if (!sdpa_fast_shape(n, nkv, h) && sizeof(float) * ((size_t)h + s_max) > 200 * 1024)
+    return fail(B200_ERR_UNSUPPORTED, "b200_sdpa_decode: this head layout runs on the fallback kernel, which holds s_max logits in shared memory (s_max + h <= 51200)");
   b200::SdpaParams p;
   memset(&p, 0, sizeof(p));
   p.q = d_q; p.k = d_k; p.v = d_v; p.k_scale = d_k_scale; p.v_scale = d_v_scale;
@@ -310,6 +335,34 @@ int b200_sdpa_decode(const void* d_q, const void* d_k, const void* d_v, const fl
   p.ws_bytes = workspace_bytes;
   cudaError_t e = b200::launch_sdpa_decode(p, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_sdpa_decode");
+}
+
+int b200_sdpa(const void* d_q, const void* d_k, const void* d_v, const float* d_mask, void* d_out, int b, int t, int n,
+              int nkv, int h, int s_max, int q_dtype, int kv_dtype, float scale, float logit_cap, void* d_workspace,
+              size_t workspace_bytes, void* stream) {
+  if (!d_q || !d_k || !d_v || !d_out) return fail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa: null pointer");
+  if (b <= 0 || t <= 0 || n <= 0 || nkv <= 0 || h <= 0 || s_max <= 0 || n % nkv != 0 || (long long)b * t > (1 << 24))
+    return fail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa: bad shape b=%d t=%d n=%d nkv=%d h=%d s=%d", b, t, n, nkv, h, s_max);
+  if (q_dtype != B200_DTYPE_F16 && q_dtype != B200_DTYPE_F32) return fail(B200_ERR_UNSUPPORTED, "b200_sdpa: q dtype %d", q_dtype);
+  if (kv_dtype != B200_DTYPE_F16 && kv_dtype != B200_DTYPE_F32) return fail(B200_ERR_UNSUPPORTED, "b200_sdpa: kv dtype %d", kv_dtype);
+  if (sdpa_fast_shape(n, nkv, h) && (!d_workspace || workspace_bytes < b200::sdpa_workspace_bytes(b * t, n, nkv, h, s_max)))
+    return fail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa: workspace too small (b200_sdpa_workspace_bytes(b * t, ...))");
+  if (!sdpa_fast_shape(n, nkv, h) && sizeof(float) * ((size_t)h + s_max) > 200 * 1024)
+    return fail(B200_ERR_UNSUPPORTED, "b200_sdpa: this head layout runs on the fallback kernel (s_max + h <= 51200)");
+  b200::SdpaParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = d_q; p.k = d_k; p.v = d_v;
+  p.mask = d_mask; p.out = d_out;
+  p.b = b * t; p.n = n; p.nkv = nkv; p.h = h; p.s_max = s_max;
+  p.rows_per_kv = t;
+  p.q_dtype = q_dtype == B200_DTYPE_F32 ? 1 : 0;
+  p.kv_dtype = kv_dtype;
+  p.scale = scale > 0.0f ? scale : 1.0f / sqrtf((float)h);
+  p.logit_cap = logit_cap;
+  p.ws = static_cast<float*>(d_workspace);
+  p.ws_bytes = workspace_bytes;
+  cudaError_t e = b200::launch_sdpa_decode(p, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_sdpa");
 }
 
 size_t b200_sdpa_rows_workspace_bytes(int rows, int n, int nkv, int h, int s_max) {

@@ -244,12 +244,14 @@ def batch_matmul_float(x, y, adj_x=False, adj_y=False):
     return out
 
 
-def batch_matmul_hybrid(x, y, y_scale, adj_x=False, adj_y=False, asymmetric_inputs=True):
+def batch_matmul_hybrid(x, y, y_scale, adj_x=False, adj_y=False, asymmetric_inputs=True, per_channel_scales=None):
+    """per_channel_scales: one scale per output column (replaces y_scale)."""
     x = _c(x, np.float32)
     y = _c(y, np.int8)
+    pc = _c(per_channel_scales, np.float32)
     out = np.empty(_bmm_out_shape(x, y, adj_x, adj_y), np.float32)
-    lib().orc_batch_matmul_hybrid(_i(x.ndim), _dims(x), _p(x), _i(y.ndim), _dims(y), _p(y), _f(y_scale),
-                                  _i(adj_x), _i(adj_y), _i(1 if asymmetric_inputs else 0), _p(out))
+    lib().orc_batch_matmul_hybrid_pc(_i(x.ndim), _dims(x), _p(x), _i(y.ndim), _dims(y), _p(y), _f(y_scale or 0.0),
+                                     _p(pc), _i(adj_x), _i(adj_y), _i(1 if asymmetric_inputs else 0), _p(out))
     return out
 
 

@@ -725,9 +725,12 @@ void orc_batch_matmul_float(int x_rank, const int* x_dims, const float* x, int y
   if (orr) free((void*)rb);
 }
 
-void orc_batch_matmul_hybrid(int x_rank, const int* x_dims, const float* x, int y_rank, const int* y_dims,
-                             const int8_t* y, float y_scale, int adj_x, int adj_y, int asymmetric_inputs,
-                             float* out) {
+/* per_channel_scales (optional): one scale per output column of the op (the RHS's quantized dimension
+ * after the transposition of tflite/kernels/batch_matmul.cc:701-708); then y_scale is not used
+ * (:487-503). */
+void orc_batch_matmul_hybrid_pc(int x_rank, const int* x_dims, const float* x, int y_rank, const int* y_dims,
+                                const int8_t* y, float y_scale, const float* per_channel_scales, int adj_x, int adj_y,
+                                int asymmetric_inputs, float* out) {
   shape_t xs, ys;
   xs.rank = x_rank;
   ys.rank = y_rank;
@@ -747,7 +750,8 @@ void orc_batch_matmul_hybrid(int x_rank, const int* x_dims, const float* x, int 
   int32_t* zp = (int32_t*)malloc(sizeof(int32_t) * num_vec);
   orc_batch_quantize_floats((const float*)lb, (int)num_vec, (int)depth, q, sf, zp, asymmetric_inputs);
   if (!asymmetric_inputs) memset(zp, 0, sizeof(int32_t) * num_vec);
-  for (size_t i = 0; i < num_vec; ++i) sf[i] *= y_scale;
+  if (!per_channel_scales)
+    for (size_t i = 0; i < num_vec; ++i) sf[i] *= y_scale;
   /* output size */
   const size_t bd = (size_t)bmm_broadcast_dim(kl[0], kr[0]) * bmm_broadcast_dim(kl[1], kr[1]) *
                     bmm_broadcast_dim(kl[2], kr[2]);
@@ -755,13 +759,19 @@ void orc_batch_matmul_hybrid(int x_rank, const int* x_dims, const float* x, int 
   for (size_t i = 0; i < out_size; ++i) out[i] = 0.0f;
   const size_t n_rows = (size_t)kl[1] * kl[2] * kl[3] * (size_t)kl[0];
   int32_t* row_sums = (int32_t*)calloc(n_rows + 1, sizeof(int32_t));
-  orc_ref_bmm_hybrid(kl, (const int8_t*)rb, kr, q, sf, zp, row_sums, 1, NULL, out);
+  orc_ref_bmm_hybrid(kl, (const int8_t*)rb, kr, q, sf, zp, row_sums, 1, per_channel_scales, out);
   free(q);
   free(sf);
   free(zp);
   free(row_sums);
   if (ol) free((void*)lb);
   if (orr) free((void*)rb);
+}
+
+void orc_batch_matmul_hybrid(int x_rank, const int* x_dims, const float* x, int y_rank, const int* y_dims,
+                             const int8_t* y, float y_scale, int adj_x, int adj_y, int asymmetric_inputs,
+                             float* out) {
+  orc_batch_matmul_hybrid_pc(x_rank, x_dims, x, y_rank, y_dims, y, y_scale, NULL, adj_x, adj_y, asymmetric_inputs, out);
 }
 
 void orc_batch_matmul_int8(int x_rank, const int* x_dims, const int8_t* x, int32_t x_zero_point,

@@ -159,6 +159,10 @@ void orc_batch_matmul_float(int x_rank, const int* x_dims, const float* x, int y
 void orc_batch_matmul_hybrid(int x_rank, const int* x_dims, const float* x, int y_rank, const int* y_dims,
                              const int8_t* y, float y_scale, int adj_x, int adj_y, int asymmetric_inputs,
                              float* out);
+/* Same with one scale per output column instead of y_scale when per_channel_scales is given. */
+void orc_batch_matmul_hybrid_pc(int x_rank, const int* x_dims, const float* x, int y_rank, const int* y_dims,
+                                const int8_t* y, float y_scale, const float* per_channel_scales, int adj_x, int adj_y,
+                                int asymmetric_inputs, float* out);
 /* int8 x int8 -> int8 (tflite/kernels/batch_matmul.cc:528-556). */
 void orc_batch_matmul_int8(int x_rank, const int* x_dims, const int8_t* x, int32_t x_zero_point,
                            int y_rank, const int* y_dims, const int8_t* y, int32_t y_zero_point,

@@ -107,13 +107,15 @@ class Accelerator:
 
 class MiniRuntime:
     def __init__(self):
-        self.lib = ctypes.CDLL(build())
+        # global symbols: the delegate looks the runtime's MarkSubgraphAsDelegationSkippable up with dlsym
+        self.lib = ctypes.CDLL(build(), mode=ctypes.RTLD_GLOBAL)
         L = self.lib
         L.mrt_create.restype = ctypes.c_void_p
         L.mrt_last_error.restype = ctypes.c_char_p
         L.mrt_tensor_data.restype = ctypes.c_void_p
         L.mrt_tensor_bytes.restype = ctypes.c_size_t
         for name in ("mrt_destroy", "mrt_last_error", "mrt_clear_error", "mrt_num_partitions", "mrt_plan_size",
+                     "mrt_num_skippable_subgraphs",
                      "mrt_num_cpu_nodes_in_plan", "mrt_invoke"):
             getattr(L, name).argtypes = [ctypes.c_void_p]
         L.mrt_apply_delegate.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
@@ -212,6 +214,10 @@ class MiniRuntime:
     @property
     def cpu_nodes(self):
         return self.lib.mrt_num_cpu_nodes_in_plan(self.h)
+
+    @property
+    def skippable_subgraphs(self):
+        return self.lib.mrt_num_skippable_subgraphs(self.h)
 
     @property
     def plan_size(self):

@@ -51,6 +51,7 @@ struct Graph {
   CpuCallback cpu = nullptr;
   int partitions = 0;
   bool replace_called = false;
+  std::vector<int> skippable_subgraphs;  // marked by the delegate (MarkSubgraphAsDelegationSkippable)
 };
 
 Graph* G(TfLiteContext* ctx) { return static_cast<Graph*>(ctx->impl_); }
@@ -456,6 +457,7 @@ MRT_API int mrt_invoke(void* h) {
   return kTfLiteOk;
 }
 
+MRT_API int mrt_num_skippable_subgraphs(void* h) { return static_cast<int>(static_cast<Graph*>(h)->skippable_subgraphs.size()); }
 MRT_API void* mrt_tensor_data(void* h, int tensor) { return static_cast<Graph*>(h)->tensors[tensor].data.raw; }
 MRT_API size_t mrt_tensor_bytes(void* h, int tensor) { return static_cast<Graph*>(h)->tensors[tensor].bytes; }
 MRT_API int mrt_tensor_is_stale(void* h, int tensor) { return static_cast<Graph*>(h)->tensors[tensor].data_is_stale; }
@@ -533,3 +535,17 @@ MRT_API void mrt_accelerator_release(void* wrapped) {
 }
 
 }  // extern "C"
+
+// What the runtime exports for delegates that absorb other subgraphs
+// (tflite/delegates/utils.h:62-93, Subgraph::MarkSubgraphAsDelegationSkippable,
+// tflite/core/subgraph.cc:751-757): same name, same signature, same checks (index 0, the primary
+// subgraph, is refused), so that a plugin resolving the symbol at run time finds it here.
+namespace tflite {
+namespace delegates {
+MRT_API TfLiteStatus MarkSubgraphAsDelegationSkippable(const TfLiteContext* context, int subgraph_index) {
+  if (!context || subgraph_index <= 0) return kTfLiteError;
+  static_cast<Graph*>(context->impl_)->skippable_subgraphs.push_back(subgraph_index);
+  return kTfLiteOk;
+}
+}  // namespace delegates
+}  // namespace tflite

@@ -96,9 +96,9 @@ def test_support_predicate_bmm_and_sdpa(plugin_path):
     w = m.tensor(I8, (10, 3), np.ones((10, 3), np.int8), scale=0.1)
     y0 = m.tensor(F32, (2, 3))
     m.batch_matmul(x, w, y0)                       # claimed: hybrid, constant rhs
-    w2 = m.tensor(I8, (3, 10))                     # not constant
+    w2 = m.tensor(I8, (3, 10), scale=0.1)          # not constant: repacked at every invocation
     y1 = m.tensor(F32, (2, 10))
-    m.batch_matmul(y0, w2, y1)                     # not claimed
+    m.batch_matmul(y0, w2, y1)                     # claimed
     q = m.tensor(F32, (1, 1, 8, 64))
     k = m.tensor(F32, (1, 32, 2, 64))
     v = m.tensor(F32, (1, 32, 2, 64))
@@ -112,10 +112,21 @@ def test_support_predicate_bmm_and_sdpa(plugin_path):
     q4 = m.tensor(F32, (1, 4, 8, 64))
     mask4 = m.tensor(F32, (1, 1, 4, 32))
     o4 = m.tensor(F32, (1, 4, 8, 64))
-    m.custom("odml.scaled_dot_product_attention", b"", [q4, k, v, mask4], o4)  # 4 query tokens: not claimed
-    m.set_io([x, q, k, v, mask, q4, mask4], [y1, o, o2, o3, o4])
+    m.custom("odml.scaled_dot_product_attention", b"", [q4, k, v, mask4], o4)  # 4 query tokens: claimed
+    q5 = m.tensor(F16, (1, 1, 8, 64))
+    o5 = m.tensor(F16, (1, 1, 8, 64))
+    m.custom("odml.scaled_dot_product_attention", b"", [q5, k, v, mask], o5)   # mixed float16 / float32: not claimed
+    x6 = m.tensor(F32, (2, 5, 10))
+    w6 = m.tensor(I8, (3, 10, 3), np.ones((3, 10, 3), np.int8), scale=0.1)
+    y6 = m.tensor(F32, (3, 5, 3))
+    m.batch_matmul(x6, w6, y6)                     # batch dimensions 2 and 3 do not broadcast: not claimed
+    w7 = m.tensor(I8, (10, 3), np.ones((10, 3), np.int8), channel_scales=np.full(10, 0.1, np.float32), quantized_dimension=0)
+    y7 = m.tensor(F32, (2, 3))
+    m.batch_matmul(x, w7, y7)                      # per-channel scales along k: not claimed
+    m.set_io([x, w2, q, k, v, mask, q4, mask4, q5, x6], [y1, o, o2, o3, o4, o5, y6, y7])
     m.apply(d)
-    assert d.claimed == 3
+    assert d.claimed == 5
+    assert m.skippable_subgraphs == 1              # the one claimed STABLEHLO_COMPOSITE carries a decomposition
     m.close()
     d.close()
 

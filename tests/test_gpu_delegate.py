@@ -359,3 +359,161 @@ def test_hybrid_fc_through_the_litert_accelerator(rt, oracle):
     rt.close()
     acc.close()
 
+
+
+# ---- BATCH_MATMUL beyond a constant 2-D right-hand side ------------------------------------------------------
+def _w8(rng, shape):
+    return np.clip(np.rint(rng.standard_normal(shape) * 40), -127, 127).astype(np.int8)
+
+
+BMM_CASES = [
+    # (lhs shape, rhs shape, adj_x, adj_y, constant rhs, per-channel)
+    ((3, 5, 17, 40), (40, 24), False, False, True, False),      # leading dimensions fold into the rows
+    ((3, 5, 17, 40), (24, 40), False, True, True, True),        # adj_y, per-channel scales along n
+    ((2, 40, 17), (40, 24), True, False, True, False),          # adj_x: the LHS is transposed on the device
+    ((2, 3, 17, 40), (2, 1, 40, 24), False, False, True, False),  # batched constant RHS, broadcast over one dimension
+    ((1, 3, 17, 40), (2, 3, 40, 24), False, False, True, True),   # the LHS broadcasts
+    ((4, 9, 130), (4, 130, 33), False, False, False, False),    # run-time RHS: repacked every invocation
+    ((4, 130, 9), (4, 33, 130), True, True, False, False),      # both adjoint, run-time RHS
+    ((1, 1, 300), (300, 1), False, False, True, False),         # a single output
+]
+
+
+@pytest.mark.parametrize("asymmetric", [True, False])
+@pytest.mark.parametrize("xs,ws,adj_x,adj_y,const,per_channel", BMM_CASES)
+def test_hybrid_bmm_random_shapes_against_the_oracle(rt, delegate, oracle, xs, ws, adj_x, adj_y, const, per_channel, asymmetric):
+    """Bit-equal to the reference arithmetic, including the zero-point correction through float
+    (tflite/kernels/internal/reference/batch_matmul.h:189,197)."""
+    rng = np.random.default_rng(abs(hash((xs, ws, adj_x, adj_y))) % 2**31)
+    x_data = (rng.standard_normal(xs) * 2.0 + 0.7).astype(np.float32)
+    w_data = _w8(rng, ws)
+    n = ws[-2] if adj_y else ws[-1]
+    kw = dict(scale=0.013)
+    pc = None
+    if per_channel:
+        pc = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+        kw = dict(channel_scales=pc, quantized_dimension=len(ws) - 2 if adj_y else len(ws) - 1)
+    w = rt.tensor(I8, ws, w_data if const else None, **kw)
+    x = rt.tensor(F32, xs)
+    want = oracle.batch_matmul_hybrid(x_data, w_data, 0.013, adj_x, adj_y, asymmetric, per_channel_scales=pc)
+    out = rt.tensor(F32, want.shape)
+    rt.batch_matmul(x, w, out, adj_x=adj_x, adj_y=adj_y, asymmetric=asymmetric)
+    rt.set_io([x] if const else [x, w], [out])
+    rt.write(x, x_data)
+    if not const:
+        rt.write(w, w_data)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.partitions == 1 and rt.cpu_nodes == 0
+    for _ in range(2):   # twice: a run-time RHS is repacked per invocation, temporaries are reused
+        assert rt.invoke() == 0, rt.error
+        assert np.array_equal(rt.view(out), want), np.max(np.abs(rt.view(out) - want))
+
+
+def test_hybrid_bmm_zero_point_correction_goes_through_float(rt, delegate, oracle):
+    """abs(row_sum x zero_point) above 2^24: the reference's `total -= row_sum * batch_offset` (float
+    batch_offset) rounds where int32 arithmetic would not. The delegate reproduces it; FULLY_CONNECTED on the
+    same data (int32 correction) must differ from it somewhere, or the case would prove nothing."""
+    rng = np.random.default_rng(5)
+    k, n, m = 4096, 64, 6
+    w_data = np.full((k, n), 127, np.int8)
+    w_data[rng.integers(0, k, 300), rng.integers(0, n, 300)] = 126
+    x_data = rng.uniform(0.05, 5.0, (m, k)).astype(np.float32)   # all positive: zero point -128
+    q, s, zp = oracle.batch_quantize_floats(x_data)
+    assert np.all(np.abs(zp.astype(np.int64) * 127 * k) > 2**24)
+    w = rt.tensor(I8, (k, n), w_data, scale=0.01)
+    x = rt.tensor(F32, (m, k))
+    out = rt.tensor(F32, (m, n))
+    rt.batch_matmul(x, w, out)
+    rt.set_io([x], [out])
+    rt.write(x, x_data)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.invoke() == 0, rt.error
+    want = oracle.batch_matmul_hybrid(x_data, w_data, 0.01)
+    assert np.array_equal(rt.view(out), want)
+    as_fc = oracle.fc_hybrid(x_data, np.ascontiguousarray(w_data.T), np.float32(0.01))
+    assert not np.array_equal(as_fc, want), "the float detour is not exercised by this data"
+
+
+@pytest.mark.parametrize("xs,ws,adj_x,adj_y,const", [c[:5] for c in BMM_CASES])
+def test_int8_bmm_random_shapes_bit_exact(rt, delegate, oracle, xs, ws, adj_x, adj_y, const):
+    rng = np.random.default_rng(abs(hash((xs, ws, adj_x, adj_y, 8))) % 2**31)
+    x_data = rng.integers(-128, 128, xs).astype(np.int8)
+    w_data = _w8(rng, ws)
+    x_scale, x_zp, w_scale, w_zp, o_scale, o_zp = 0.05, -7, 0.02, 3, 4.0, -11
+    want = oracle.batch_matmul_int8(x_data, x_zp, x_scale, w_data, w_zp, w_scale, o_scale, o_zp, adj_x, adj_y)
+    w = rt.tensor(I8, ws, w_data if const else None, scale=w_scale, zero_point=w_zp)
+    x = rt.tensor(I8, xs, scale=x_scale, zero_point=x_zp)
+    out = rt.tensor(I8, want.shape, scale=o_scale, zero_point=o_zp)
+    rt.batch_matmul(x, w, out, adj_x=adj_x, adj_y=adj_y)
+    rt.set_io([x] if const else [x, w], [out])
+    rt.write(x, x_data)
+    if not const:
+        rt.write(w, w_data)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.partitions == 1 and rt.cpu_nodes == 0
+    assert rt.invoke() == 0, rt.error
+    assert np.array_equal(rt.view(out), want)
+    assert len(np.unique(want)) > 20
+
+
+# ---- the composite with several query tokens, float16 tensors, and the reference's own models ---------------
+@pytest.mark.parametrize("dtype", ["f32", "f16"])
+@pytest.mark.parametrize("b,t,n,nkv,h,s", [(2, 5, 8, 1, 256, 300), (1, 33, 8, 2, 64, 70), (2, 3, 6, 6, 24, 40)])
+def test_sdpa_with_several_query_tokens_through_the_delegate(rt, delegate, oracle, dtype, b, t, n, nkv, h, s):
+    """A prompt-shaped composite: [b, t, n, h] queries, an arbitrary additive mask [b, 1, t, s] (here causal
+    behind a cached prefix, with noise where it is open), float32 or float16 tensors."""
+    rng = np.random.default_rng(b * 100 + t)
+    np_t = np.float32 if dtype == "f32" else np.float16
+    tt = F32 if dtype == "f32" else F16
+    q = rng.standard_normal((b, t, n, h)).astype(np_t)
+    k = rng.standard_normal((b, s, nkv, h)).astype(np_t)
+    v = rng.standard_normal((b, s, nkv, h)).astype(np_t)
+    prefix = s - t
+    open_ = np.arange(s)[None, None, None, :] <= (prefix + np.arange(t))[None, None, :, None]
+    mask = np.where(open_, rng.uniform(-1, 0, (b, 1, t, s)), -1e30).astype(np.float32)
+    ins = [rt.tensor(tt, q.shape), rt.tensor(tt, k.shape), rt.tensor(tt, v.shape), rt.tensor(F32, mask.shape)]
+    out = rt.tensor(tt, q.shape)
+    rt.composite("odml.scaled_dot_product_attention", minirt.flex_map({"scale": 0.11}), ins, out)
+    rt.set_io(ins, [out])
+    for tensor, d in zip(ins, (q, k, v, mask)):
+        rt.write(tensor, d)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.partitions == 1 and rt.cpu_nodes == 0
+    assert rt.skippable_subgraphs == 1   # the composite's decomposition subgraph was marked for the runtime
+    assert rt.invoke() == 0, rt.error
+    want = oracle.sdpa_f32(q.astype(np.float32), k.astype(np.float32), v.astype(np.float32), mask, 0.11)
+    got = rt.view(out).astype(np.float32)
+    assert np.max(np.abs(got - want)) / np.max(np.abs(want)) <= (2e-2 if h in (64, 128, 256) or dtype == "f16" else 1e-4)
+
+
+@pytest.mark.parametrize("name", ["mha", "mqa", "gqa"])
+def test_reference_sdpa_composite_models_run_on_the_device(delegate, oracle, name):
+    """The models the reference keeps for its differential test of the composite
+    (tflite/delegates/xnnpack/odml_sdpa_composite_{mha,mqa,gqa}.tflite.bin, regenerated into tests/golden by
+    make_sdpa_models.py), loaded from their .tflite bytes, claimed whole and executed, inputs drawn as
+    tflite/delegates/xnnpack/odml_sdpa_tester.cc:81-99 draws them (uniform in [0, 1))."""
+    import os
+
+    from litert_b200 import tflite_model as tm
+
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", f"odml_sdpa_composite_{name}.tflite")
+    model = tm.read_model(open(path, "rb").read())
+    rt = minirt.load_model(model)
+    sg = model.subgraphs[0]
+    op = sg.operators[0]
+    rng = np.random.default_rng(31)
+    data = [rng.uniform(0, 1, sg.tensors[i].shape).astype(np.float32) for i in op.inputs]
+    for i, d in zip(op.inputs, data):
+        rt.write(i, d)
+    assert rt.apply(delegate) == 0, rt.error
+    assert rt.partitions == 1 and rt.cpu_nodes == 0 and delegate.claimed == 1
+    assert rt.invoke() == 0, rt.error
+    import struct
+    # The node's attribute blob is a FlexBuffers map {"scale": float}: the delegate decodes it; here every
+    # aligned float in the blob is a candidate, and exactly the right one reproduces the device's output.
+    attrs = op.options["composite_attributes"]
+    candidates = {float(struct.unpack_from("<f", attrs, o)[0]) for o in range(0, max(len(attrs) - 3, 0))}
+    best = min((float(np.max(np.abs(rt.view(op.outputs[0]) - oracle.sdpa_f32(*data, scale=c))))
+                for c in candidates if 1e-3 < c < 10), default=1.0)
+    assert best <= 1e-4, best
+    rt.close()
