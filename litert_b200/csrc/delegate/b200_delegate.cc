@@ -258,6 +258,17 @@ OpKind Classify(TfLiteContext* ctx, const TfLiteNode* node, const TfLiteRegistra
     const auto* q = Affine(*w);
     const bool per_channel = q && q->scale && q->scale->size > 1;
     if (x->type == kTfLiteFloat32 && w->type == kTfLiteInt8 && y->type == kTfLiteFloat32) {
+      // The reference's hybrid kernel steps through the per-row scales and zero points (and the RHS row
+      // sums) by (b0 + b1 + b2) x rows, not by the flattened batch index
+      // (tflite/kernels/internal/reference/batch_matmul.h:138-143, 160-186): with one varying batch
+      // dimension per operand that is the same thing, with two it reads another batch's parameters.
+      // Such graphs are left to it rather than answered differently.
+      int lhs_varying = 0, rhs_varying = 0;
+      for (int d = 0; d < 3; ++d) {
+        lhs_varying += g.lhs_batch[d] > 1;
+        rhs_varying += g.rhs_batch[d] > 1;
+      }
+      if (lhs_varying > 1 || rhs_varying > 1) return *why = "hybrid batch_matmul over several batch dimensions", OpKind::kNone;
       if (per_channel) {
         // the scales follow the output columns: the RHS's N axis (tflite/kernels/batch_matmul.cc:701-708, 487-497)
         const int n_axis = p->adj_y ? w->dims->size - 2 : w->dims->size - 1;

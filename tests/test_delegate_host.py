@@ -123,7 +123,11 @@ def test_support_predicate_bmm_and_sdpa(plugin_path):
     w7 = m.tensor(I8, (10, 3), np.ones((10, 3), np.int8), channel_scales=np.full(10, 0.1, np.float32), quantized_dimension=0)
     y7 = m.tensor(F32, (2, 3))
     m.batch_matmul(x, w7, y7)                      # per-channel scales along k: not claimed
-    m.set_io([x, w2, q, k, v, mask, q4, mask4, q5, x6], [y1, o, o2, o3, o4, o5, y6, y7])
+    x8 = m.tensor(F32, (3, 5, 2, 10))
+    y8 = m.tensor(F32, (3, 5, 2, 3))
+    m.batch_matmul(x8, w, y8)                      # hybrid over two batch dimensions (the reference kernel mixes up
+                                                   # the rows' parameters there): not claimed
+    m.set_io([x, w2, q, k, v, mask, q4, mask4, q5, x6, x8], [y1, o, o2, o3, o4, o5, y6, y7, y8])
     m.apply(d)
     assert d.claimed == 5
     assert m.skippable_subgraphs == 1              # the one claimed STABLEHLO_COMPOSITE carries a decomposition
