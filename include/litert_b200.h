@@ -275,6 +275,17 @@ B200_API size_t b200_argmax_workspace_bytes(int rows);
 B200_API int b200_argmax_rows(const float* d_logits, int rows, int n, float soft_cap, int32_t* d_out,
                               void* d_workspace, size_t workspace_bytes, void* stream);
 
+/* The LM head with the greedy pick in its epilogue, for up to 16 rows: the vocabulary projection
+ * (b200_fc_hybrid_quantized arithmetic, one scale per vocabulary row), the logits soft-cap of
+ * litert/vendors/nvidia/trtllm/head_kernels.cu:35-43 and the first-index arg-max with the NaN rule
+ * of litert/vendors/nvidia/dispatch/greedy_sampler_kernel.cu:31-94, so that one int32 per row
+ * leaves the kernels. d_logits (optional, [m, n]) also receives the (capped) logits. */
+B200_API size_t b200_lm_head_workspace_bytes(int m);
+B200_API int b200_lm_head_greedy(const int8_t* d_q_tiled, const float* d_scales, const int32_t* d_zero_points, int m,
+                                 int k, const void* d_w_packed, int n, const int32_t* d_row_sums,
+                                 const float* d_w_scales, float soft_cap, float* d_logits, int32_t* d_tokens,
+                                 void* d_workspace, size_t workspace_bytes, void* d_zero_ws, void* stream);
+
 /* One decode step of a layer's attention in ONE launch, for multi-query
  * attention (one KV head, at most 8 query heads, head size 64/128/256, at most
  * 9 sequences): b200_rope_kv_append + b200_sdpa_decode over the first
@@ -387,6 +398,12 @@ B200_API int b200_decoder_reset(b200_decoder* dec);
  * time-out the ranks' step counters may differ: reset every rank before going on. */
 B200_API int b200_decoder_set_wait_budget(b200_decoder* dec, unsigned long long nanoseconds);
 B200_API int b200_decoder_clear_fault(b200_decoder* dec);
+/* Logits soft-cap applied before the greedy pick: cap * tanh(logit / cap)
+ * (litert/vendors/nvidia/trtllm/head_kernels.cu:35-43); 0 = none (the default). The pick itself is the
+ * first index of the maximum with the NaN rule of
+ * litert/vendors/nvidia/dispatch/greedy_sampler_kernel.cu:31-50, computed inside the LM-head GEMV's
+ * epilogue for up to 16 sequences on one GPU (no logits leave the kernel unless d_logits is given). */
+B200_API int b200_decoder_set_logit_soft_cap(b200_decoder* dec, float cap);
 /* Declares h_positions[i] tokens already cached for sequence i (cache rows never written hold
  * zeros): lets a caller resume from a cache filled elsewhere, or time a step at a given depth. */
 B200_API int b200_decoder_set_positions(b200_decoder* dec, const int32_t* h_positions, int batch);

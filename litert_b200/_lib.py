@@ -52,6 +52,8 @@ SIGNATURES = {
     "b200_rope_kv_append": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "b200_argmax_workspace_bytes": (_sz, [_i]),
     "b200_argmax_rows": (_i, [_vp, _i, _i, _f, _vp, _vp, _sz, _vp]),
+    "b200_lm_head_workspace_bytes": (_sz, [_i]),
+    "b200_lm_head_greedy": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _sz, _vp, _vp]),
     "b200_attention_step_supported": (_i, [_i, _i, _i, _i]),
     "b200_attention_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp]),
     "b200_sdpa_decode_quantized": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp,
@@ -72,6 +74,7 @@ SIGNATURES = {
     "b200_decoder_set_wait_budget": (_i, [_vp, ctypes.c_ulonglong]),
     "b200_decoder_clear_fault": (_i, [_vp]),
     "b200_decoder_reset": (_i, [_vp]),
+    "b200_decoder_set_logit_soft_cap": (_i, [_vp, _f]),
     "b200_decoder_set_positions": (_i, [_vp, _vp, _i]),
     "b200_decoder_step": (_i, [_vp, _vp, _i, _vp, _vp]),
     "b200_decoder_run": (_i, [_vp, _vp, _i, _i, _vp]),

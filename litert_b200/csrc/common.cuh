@@ -148,6 +148,14 @@ __device__ __forceinline__ void bulk_g2s_hint(void* smem_dst, const void* gmem_s
       : "memory");
 }
 
+// Asks L2 for a range of global memory without any destination (16-byte aligned address, size a
+// multiple of 16): used by the GEMV producers for their own weight tiles beyond the shared-memory
+// ring while they wait for the kernel that produces their activations, so that HBM keeps streaming
+// during the short row kernels between two projections.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* gmem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem_src), "r"(bytes) : "memory");
+}
+
 // ---- legacy tensor-core MMA -------------------------------------------------
 // D(16x8,s32) += A(16x32,s8,row) * B(32x8,s8,col)
 __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,

@@ -97,6 +97,7 @@ struct b200_decoder {
   cudaGraphExec_t graph[257] = {nullptr};  // indexed by batch
   std::unique_ptr<PrefillBufs> pf;         // allocated by the first prompt pass
   int launches = 0;
+  float soft_cap = 0.0f;  // logits soft-cap of the greedy pick (0 = none)
   // per-kernel-class timing of one eager step (b200_decoder_profile_step)
   bool profiling = false;
   std::vector<cudaEvent_t> prof_events;  // start/stop pairs
@@ -226,8 +227,10 @@ struct FusedInput {
   float* h_out;
 };
 
+// pick: the greedy pick fused into the projection's epilogue (the LM head at up to 16 rows): the CTAs'
+// candidates go to arg_val / arg_idx, y may be null.
 cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_t* q_tiled, const float* scales,
-                   const int32_t* zps, float* y, const FusedInput* fused = nullptr) {
+                   const int32_t* zps, float* y, const FusedInput* fused = nullptr, bool pick = false) {
   FcParams p;
   memset(&p, 0, sizeof(p));
   if (fused) {
@@ -253,6 +256,24 @@ cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_
   p.row_sums = pr.row_sums.as<int32_t>();
   p.activation = 0;
   p.y = y;
+  if (pick) {
+    p.argmax_val = d->arg_val.as<float>();
+    p.argmax_idx = d->arg_idx.as<int32_t>();
+    p.argmax_parts = fc_argmax_ctas(pr.n);
+    p.soft_cap = d->soft_cap;
+  }
+  // Between two projections of a decode step run short row kernels that leave HBM idle, with this
+  // projection's CTAs already resident and waiting: they pull their weights towards L2 meanwhile. The
+  // layers' projections fit L2 whole; of the LM head only a first slice is asked for.
+  {
+    static const int pf_env = [] {
+      const char* e = getenv("B200_L2_PREFETCH");  // measurement knob: tiles per CTA, 0 = off
+      return e ? atoi(e) : -1;
+    }();
+    const size_t bytes = (size_t)p.n_tiles * p.k_tiles * kTileBytes;
+    p.l2_prefetch_tiles = batch <= 16 ? (bytes <= (80u << 20) ? 1 << 20 : 12) : 0;
+    if (pf_env >= 0) p.l2_prefetch_tiles = pf_env;
+  }
   uint8_t* z = d->zero_ws.as<uint8_t>();
   p.status = reinterpret_cast<int*>(z);
   p.ws_count = reinterpret_cast<int32_t*>(z + zero_ws_counter_off());
@@ -261,7 +282,7 @@ cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_
   ++d->launches;
   if (d->trace.p && d->trace_next < kTraceSlots) p.trace = d->trace.as<unsigned long long>() + 4 * d->trace_next++;
   ProfScope scope(d, 0);
-  return launch_fc_i8_umma(p, kEpiHybridF32, d->stream);
+  return launch_fc_i8_umma(p, pick ? kEpiHybridPick : kEpiHybridF32, d->stream);
 }
 
 // The exchange whose sum the next consuming kernel needs: partials at byte offset `off` of every
@@ -436,20 +457,34 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
     if (!(skip & 128)) DEC_CUDA(run_fc(d, L.down, batch, d->q_f.as<int8_t>(), d->sc_f.as<float>(), d->zp_f.as<int32_t>(), d->down_out));
     if (int rc = reduce(d->down_out, (size_t)batch * c.d_model)) return rc;
   }
-  float* logits = d_logits_out ? d_logits_out : d->logits.as<float>();
+  // One sequence batch on one GPU, at most 16 rows: the LM-head GEMV picks the greedy token in its own
+  // epilogue (soft-cap, first index of the maximum, NaN rule), so that no logits are written unless the
+  // caller asked for them, and one small kernel compares the CTAs' candidates.
+  static const bool pick_env = [] {
+    const char* e = getenv("B200_FUSED_PICK");  // measurement knob: 0 keeps the separate arg-max kernels
+    return !(e && e[0] == '0');
+  }();
+  const bool fused_pick = pick_env && !tp && batch <= 16 && fc_argmax_ctas(d->lm_head.n) <= kArgmaxSlots;
+  float* logits = d_logits_out ? d_logits_out : (fused_pick ? nullptr : d->logits.as<float>());
   if (fuse_norm) {
     const FusedInput fi{hbuf[cur], d->down_out, d->final_norm.as<float>(), hbuf[cur ^ 1]};
-    if (!(skip & 256)) DEC_CUDA(run_fc(d, d->lm_head, batch, nullptr, nullptr, nullptr, logits, &fi));
+    if (!(skip & 256)) DEC_CUDA(run_fc(d, d->lm_head, batch, nullptr, nullptr, nullptr, logits, &fi, fused_pick));
   } else {
     const TpExchange x = fused ? make_exchange(d, 2 * c.n_layers - 1, d->off_part_b) : TpExchange();
     if (!(skip & 1)) GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->down_out, d->final_norm.as<float>(), batch, c.d_model, c.rms_eps,
                                    m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(),
                                    fused ? &x : nullptr, s));
     count();
-    if (!(skip & 256)) DEC_CUDA(run_fc(d, d->lm_head, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), logits));
+    if (!(skip & 256)) DEC_CUDA(run_fc(d, d->lm_head, batch, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(), logits, nullptr, fused_pick));
+  }
+  if (fused_pick) {
+    GLUE_CUDA(launch_argmax_final(d->arg_val.as<float>(), d->arg_idx.as<int32_t>(), batch, fc_argmax_ctas(d->lm_head.n), 0,
+                                 d->next_tokens.as<int32_t>(), d->positions.as<int32_t>(), c.max_seq, nullptr, s));
+    count();
+    return B200_OK;
   }
   if (!tp) {
-    GLUE_CUDA(launch_argmax(logits, batch, c.vocab, 0, 0.0f, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
+    GLUE_CUDA(launch_argmax(logits, batch, c.vocab, 0, d->soft_cap, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
                            d->next_tokens.as<int32_t>(), d->positions.as<int32_t>(), c.max_seq, nullptr, s));
     count(2);
     return B200_OK;
@@ -591,7 +626,7 @@ int enqueue_prefill_chunk(b200_decoder* d, int seq, int rows, bool pick) {
   DEC_CUDA(run_fc(d, d->lm_head, 1, f.q_d.as<int8_t>(), f.sc_d.as<float>(), f.zp_d.as<int32_t>(), logits));
   int32_t* scratch_pos = f.attn_len.as<int32_t>();  // the arg-max advances a position: not the sequence's, set by the caller
   if (!tp) {
-    DEC_CUDA(launch_argmax(logits, 1, c.vocab, 0, 0.0f, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
+    DEC_CUDA(launch_argmax(logits, 1, c.vocab, 0, d->soft_cap, d->arg_val.as<float>(), d->arg_idx.as<int32_t>(),
                            d->next_tokens.as<int32_t>() + seq, scratch_pos, c.max_seq, nullptr, s));
     return B200_OK;
   }
@@ -721,8 +756,8 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
   size_t sdpa_bytes = 0;  // the chunking depends on the batch: size for the worst batch <= max_batch
   for (int b = 1; b <= B; ++b) sdpa_bytes = std::max(sdpa_bytes, sdpa_workspace_bytes(b, d->hl, d->kvl, c.head_dim, c.max_seq));
   DEC_CUDA(d->sdpa_ws.alloc(sdpa_bytes));
-  DEC_CUDA(d->arg_val.alloc(sizeof(float) * B * kArgmaxParts));
-  DEC_CUDA(d->arg_idx.alloc(sizeof(int32_t) * B * kArgmaxParts));
+  DEC_CUDA(d->arg_val.alloc(sizeof(float) * B * kArgmaxSlots));
+  DEC_CUDA(d->arg_idx.alloc(sizeof(int32_t) * B * kArgmaxSlots));
   DEC_CUDA(cudaMemsetAsync(d->positions.p, 0, sizeof(int32_t) * B, d->stream));
   DEC_CUDA(cudaMallocHost(&d->h_tokens_pinned, sizeof(int32_t) * B));
   DEC_CUDA(cudaMallocHost(&d->h_next_pinned, sizeof(int32_t) * (B + 1)));  // + the status word read back with the tokens
@@ -923,6 +958,18 @@ int b200_decoder_connect_peer_pointers(b200_decoder* d, void* const* d_exchange_
 }
 
 void* b200_decoder_exchange_buffer(b200_decoder* d) { return d ? d->comm.p : nullptr; }
+
+int b200_decoder_set_logit_soft_cap(b200_decoder* d, float cap) {
+  if (!d || !(cap >= 0.0f)) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_set_logit_soft_cap: bad argument");
+  if (d->cfg.tp_size > 1 && cap > 0.0f) return dec_fail(B200_ERR_UNSUPPORTED, "b200_decoder_set_logit_soft_cap: one GPU only");
+  d->soft_cap = cap;
+  for (auto& g : d->graph)  // captured steps hold the old value
+    if (g) {
+      cudaGraphExecDestroy(g);
+      g = nullptr;
+    }
+  return B200_OK;
+}
 
 int b200_decoder_set_positions(b200_decoder* d, const int32_t* h_positions, int batch) {
   if (!d || !h_positions || batch <= 0 || batch > d->cfg.max_batch) return dec_fail(B200_ERR_INVALID_ARGUMENT, "b200_decoder_set_positions: bad argument");

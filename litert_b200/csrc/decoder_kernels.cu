@@ -11,6 +11,7 @@
 #include <cooperative_groups.h>
 #include <math_constants.h>
 
+#include "argmax.cuh"
 #include "common.cuh"
 #include "decoder_kernels.h"
 #include "quant.cuh"
@@ -306,28 +307,7 @@ __global__ void rope_cache_kernel(const float* __restrict__ qkv, int heads, int 
   }
 }
 
-struct BestPair {
-  float v;
-  int i;
-};
-__device__ __forceinline__ BestPair better(BestPair a, BestPair b) {
-  // The serial scan `if (x[i] > x[best]) best = i` from best = 0, whatever the order pairs are
-  // combined in (litert/vendors/nvidia/dispatch/greedy_sampler_kernel.cu:31-50): a NaN at index 0
-  // wins outright, a NaN anywhere else never does; otherwise the larger value, ties to the lower index.
-  if (a.i == 0 && isnan(a.v)) return a;
-  if (b.i == 0 && isnan(b.v)) return b;
-  if (isnan(a.v)) return b;
-  if (isnan(b.v)) return a;
-  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
-  return a;
-}
-
 // grid (parts, b): each CTA scans a slice of the row.
-__device__ __forceinline__ float soft_capped(float v, float inv_cap, float cap) {
-  // litert/vendors/nvidia/trtllm/head_kernels.cu:35-43: tanh(logit / cap) * cap
-  return cap > 0.0f ? __fmul_rn(tanhf(__fmul_rn(v, inv_cap)), cap) : v;
-}
-
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ logits, int n, int parts,
                                                              float soft_cap, float* __restrict__ part_val,
                                                              int32_t* __restrict__ part_idx) {
@@ -338,14 +318,12 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
   const int per = (n + parts - 1) / parts;
   const int lo = part * per, hi = min(n, lo + per);
   const float* row = logits + (size_t)b * n;
-  const float inv_cap = soft_cap > 0.0f ? __fdiv_rn(1.0f, soft_cap) : 0.0f;
-  BestPair best{lo < n ? soft_capped(row[lo], inv_cap, soft_cap) : -CUDART_INF_F, lo < n ? lo : 0x7fffffff};
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x)
-    best = better(best, BestPair{soft_capped(row[i], inv_cap, soft_cap), i});
+  BestPick best{lo < n ? soft_capped(row[lo], soft_cap) : -CUDART_INF_F, lo < n ? lo : 0x7fffffff};
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) best = better_pick(best, BestPick{soft_capped(row[i], soft_cap), i});
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    BestPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
-    best = better(best, other);
+    BestPick other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better_pick(best, other);
   }
   if ((threadIdx.x & 31) == 0) {
     sv[threadIdx.x >> 5] = best.v;
@@ -353,7 +331,7 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int w = 1; w < 8; ++w) best = better(best, BestPair{sv[w], si[w]});
+    for (int w = 1; w < 8; ++w) best = better_pick(best, BestPick{sv[w], si[w]});
     part_val[(size_t)b * parts + part] = best.v;
     part_idx[(size_t)b * parts + part] = best.i;
   }
@@ -365,13 +343,13 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val, const in
                                     int32_t* __restrict__ positions, int max_seq, float2* __restrict__ pair_out) {
   pdl_enter();
   const int b = blockIdx.x;
-  BestPair best{part_val[(size_t)b * parts], part_idx[(size_t)b * parts]};
+  BestPick best{part_val[(size_t)b * parts], part_idx[(size_t)b * parts]};
   for (int i = threadIdx.x; i < parts; i += 32)
-    best = better(best, BestPair{part_val[(size_t)b * parts + i], part_idx[(size_t)b * parts + i]});
+    best = better_pick(best, BestPick{part_val[(size_t)b * parts + i], part_idx[(size_t)b * parts + i]});
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    BestPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
-    best = better(best, other);
+    BestPick other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better_pick(best, other);
   }
   if (threadIdx.x == 0) {
     if (pair_out) {
@@ -394,12 +372,12 @@ __global__ void argmax_pick_kernel(PairTable pairs, int tp_size, int32_t* __rest
   if (xch.tp_size > 1) tp_handshake(xch, blockIdx.x == 0);
   const int b = blockIdx.x;
   if (threadIdx.x == 0) {
-    BestPair best{-CUDART_INF_F, 0x7fffffff};
+    BestPick best{-CUDART_INF_F, 0x7fffffff};
     for (int j = 0; j < tp_size; ++j) {
       const float* pj = reinterpret_cast<const float*>(pairs.p[j] + b);
       const float v = ld_peer(pj), fi = ld_peer(pj + 1);
-      const BestPair cand{v, (int)fi};
-      best = j == 0 ? cand : better(best, cand);
+      const BestPick cand{v, (int)fi};
+      best = j == 0 ? cand : better_pick(best, cand);
     }
     next_tokens[b] = best.i;
     if (positions[b] < max_seq) positions[b] += 1;
@@ -489,6 +467,12 @@ cudaError_t launch_argmax(const float* logits, int batch, int n, int idx_offset,
   if (e != cudaSuccess) return e;
   return launch_chained(argmax_final_kernel, dim3(batch), dim3(32), 0, s, (const float*)part_val, (const int32_t*)part_idx,
                         (int)kArgmaxParts, idx_offset, next_tokens, positions, max_seq, pair_out);
+}
+
+cudaError_t launch_argmax_final(const float* part_val, const int32_t* part_idx, int batch, int parts, int idx_offset,
+                                int32_t* next_tokens, int32_t* positions, int max_seq, float2* pair_out, cudaStream_t s) {
+  return launch_chained(argmax_final_kernel, dim3(batch), dim3(32), 0, s, part_val, part_idx, parts, idx_offset, next_tokens,
+                        positions, max_seq, pair_out);
 }
 
 cudaError_t launch_argmax_pick(const float2* const* pairs, int tp_size, int batch, int32_t* next_tokens,

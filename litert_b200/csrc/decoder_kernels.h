@@ -7,6 +7,7 @@
 namespace b200 {
 
 constexpr int kArgmaxParts = 128;
+constexpr int kArgmaxSlots = 512;  // candidate slots per row: kArgmaxParts, or one per CTA of the fused LM-head pick
 constexpr int kMaxTpRanks = 8;
 
 // One cross-rank exchange of a tensor-parallel step, done inside the kernel that consumes the sum.
@@ -54,6 +55,10 @@ cudaError_t launch_rope_cache(const float* qkv, int batch, int heads, int kv_hea
 cudaError_t launch_argmax(const float* logits, int batch, int n, int idx_offset, float soft_cap, float* part_val,
                           int32_t* part_idx, int32_t* next_tokens, int32_t* positions, int max_seq, float2* pair_out,
                           cudaStream_t s);
+// The last stage alone, over `parts` candidates per row that an earlier kernel left in part_val / part_idx
+// (row-major [batch, parts]): the LM-head GEMV's fused pick writes one per CTA.
+cudaError_t launch_argmax_final(const float* part_val, const int32_t* part_idx, int batch, int parts, int idx_offset,
+                                int32_t* next_tokens, int32_t* positions, int max_seq, float2* pair_out, cudaStream_t s);
 // Picks the best of tp_size candidate pairs per row. pairs[j] = rank j's float2[batch]; when xch is given
 // they are peers' memory and the exchange handshake runs first, otherwise they are local.
 cudaError_t launch_argmax_pick(const float2* const* pairs, int tp_size, int batch, int32_t* next_tokens,

@@ -23,10 +23,14 @@
 // count sums the contributors' slots and runs the epilogue. Integer addition
 // makes the result bit-equal to a serial sum.
 // Every wait is bounded (see mbar_wait_bounded); TMEM is always freed.
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
+#include <math_constants.h>
+
+#include "argmax.cuh"
 #include "common.cuh"
 #include "kernels.h"
 #include "prologue.cuh"
@@ -104,7 +108,7 @@ template <int EPI>
 __device__ __forceinline__ int32_t compute_output(const FcParams& p, int32_t total, int32_t rs, float ws, float bias_f,
                                                   int32_t base_i, int32_t mult, int32_t shift, float in_scale,
                                                   int32_t in_aux) {
-  if constexpr (EPI == kEpiHybridF32) {
+  if constexpr (EPI == kEpiHybridF32 || EPI == kEpiHybridPick) {
     const int32_t dot = hybrid_dot(p, total, rs, in_aux);  // in_aux: the row's zero point
     // reference order: scale = in_scale * w_scale; out = bias + dot * scale (no fused multiply-add)
     const float scale = __fmul_rn(in_scale, ws);
@@ -127,7 +131,7 @@ template <int EPI>
 __device__ __forceinline__ void store_output(const FcParams& p, int m, int n, int32_t total, int32_t rs, float ws,
                                              float bias_f, int32_t base_i, int32_t mult, int32_t shift,
                                              float in_scale, int32_t in_aux) {
-  if constexpr (EPI == kEpiHybridF32) {
+  if constexpr (EPI == kEpiHybridF32 || EPI == kEpiHybridPick) {
     const int32_t dot = hybrid_dot(p, total, rs, in_aux);  // in_aux: the row's zero point
     // reference order: scale = in_scale * w_scale; out = bias + dot * scale (no fused multiply-add)
     const float scale = __fmul_rn(in_scale, ws);
@@ -215,6 +219,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         mbar_arrive_expect_tx(&full_bar[pre], stage_tx);
         bulk_g2s_hint(dst, p.w_packed + (size_t)t * kTileBytes, kTileBytes, &full_bar[pre], stream_policy);
       }
+      // ... and the tiles behind the ring go to L2 meanwhile (the row kernels between two projections
+      // leave HBM idle otherwise)
+      {
+        const long long pf_end = t_begin + pre + p.l2_prefetch_tiles < t_end ? t_begin + pre + p.l2_prefetch_tiles : t_end;
+        for (long long t = t_begin + pre; t < pf_end; ++t) prefetch_l2_bulk(p.w_packed + (size_t)t * kTileBytes, kTileBytes);
+      }
       pdl_wait();               // activations (and the split-K scratch) are now safe to touch
       if (p.trace && blockIdx.x == 0) p.trace[1] = global_timer_ns();
       if (!p.prologue) {
@@ -277,7 +287,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
             // 32 reduction bytes per MMA: 32 B further along the swizzled rows; 8-row groups 1 KiB apart
             const uint64_t a_desc = umma_smem_desc(a_addr + ks * 32);
             const uint64_t b_desc = umma_smem_desc(b_addr + ks * 32);
-            if (!(p.debug_flags & 1)) umma_s8(d_tmem, a_desc, b_desc, idesc, (first && ks == 0) ? 0u : 1u);
+            umma_s8(d_tmem, a_desc, b_desc, idesc, (first && ks == 0) ? 0u : 1u);
           }
           first = false;
           umma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
@@ -304,7 +314,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
       rs = 0, base_i = 0, mult = 0, shift = 0, wsc = 0.0f, bias_f = 0.0f;
       if (n >= p.n) return;
       rs = p.row_sums ? p.row_sums[n] : 0;
-      if constexpr (EPI == kEpiHybridF32) {
+      if constexpr (EPI == kEpiHybridF32 || EPI == kEpiHybridPick) {
         wsc = p.per_channel ? p.w_scales[n] : p.w_scales[0];
         bias_f = p.bias_f32 ? p.bias_f32[n] : 0.0f;
       } else {
@@ -327,7 +337,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         const int m = m_base + i;
         const bool ok = m < p.m;
         sh->in_scale[i] = (ok && p.in_scales) ? p.in_scales[m] : 0.0f;
-        if constexpr (EPI == kEpiHybridF32) {
+        if constexpr (EPI == kEpiHybridF32 || EPI == kEpiHybridPick) {
           sh->in_aux[i] = (ok && p.in_zps) ? p.in_zps[m] : 0;
         } else {
           sh->in_aux[i] = (ok && p.x_sums) ? p.x_sums[m] : 0;
@@ -335,6 +345,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
       }
       named_barrier(1, kEpiThreads);
     }
+    // fused greedy pick (one pass of up to 16 rows): this thread's best value and column per row
+    BestPick best[EPI == kEpiHybridPick ? 16 : 1];
+#pragma unroll
+    for (int j = 0; j < (EPI == kEpiHybridPick ? 16 : 1); ++j) best[j] = BestPick{-CUDART_INF_F, 0x7fffffff};
     uint32_t seg = 0;
     long long t = t_begin;
     while (t < t_end) {
@@ -354,28 +368,19 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
       tc_fence_after();
 
       const bool partial = seg_tiles != p.k_tiles;
-      if (p.debug_flags & 2) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[ab]);
-      } else if (!partial) {
+      if (!partial) {
 #pragma unroll 1
         for (int c = 0; c < NB / 16; ++c) {
           if (c * 16 >= m_valid) break;
           int r[16];
-          if (!(p.debug_flags & 8)) {
-            tmem_ld16(taddr + c * 16, r);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] = c + j;
-          }
+          tmem_ld16(taddr + c * 16, r);
+          tmem_ld_wait();
           if constexpr (NB >= 64) {
             // Many activation rows: a thread storing its own output channel writes 4 bytes (1 for int8)
             // per row and a warp 128 (32) bytes per store instruction, 57 KB apart from the next; at
             // 256 rows that costs more than the MMAs. The 16 x 128 block goes through shared memory
             // instead and leaves as whole 512-byte (128-byte) row segments, 16 bytes per thread.
-            if (!(p.debug_flags & 4)) {
+            {
               constexpr int kElem = EPI == kEpiRequantI8 ? 1 : 4;
               uint8_t* st = out_stage + (c & 1) * (16 * kTileN * 4);
               float sc[16];  // the rows' parameters first: behind the staging stores they would be reloaded one by one
@@ -395,7 +400,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
                 }
               }
               named_barrier(2, kEpiThreads);  // the block is complete (and the other buffer's readers are done)
-              if (p.debug_flags & 32) continue;  // measurement: values computed and staged, never written out
               const int n0 = (int)nt * kTileN;
               constexpr int kChunksPerRow = kTileN * kElem / 16;        // 16-byte pieces per output row segment
               constexpr int kPieces = 16 * kChunksPerRow;
@@ -405,8 +409,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
                 const int rr = idx / kChunksPerRow, cc = idx % kChunksPerRow;
                 const int m = c * 16 + rr;
                 if (m >= m_valid) continue;
-                size_t off = ((size_t)(m_base + m) * p.n + n0) * kElem + cc * 16;
-                if (p.debug_flags & 16) off &= (1u << 20) - 16;  // measurement: every store lands in one MiB
+                const size_t off = ((size_t)(m_base + m) * p.n + n0) * kElem + cc * 16;
                 uint8_t* dst = static_cast<uint8_t*>(p.y) + off;
                 const uint8_t* src = st + (size_t)rr * kTileN * kElem + cc * 16;
                 if (vec_ok) {
@@ -417,7 +420,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
                 }
               }
             }
-          } else if (row_ok && !(p.debug_flags & 4)) {
+          } else if (row_ok) {
             float sc[16];  // parameters of the 16 rows, read before the first output store
             int32_t ax[16];
 #pragma unroll
@@ -428,10 +431,20 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int m = c * 16 + j;
-              if (m < m_valid) store_output<EPI>(p, m_base + m, n, r[j], rs, wsc, bias_f, base_i, mult, shift, sc[j], ax[j]);
+              if (m >= m_valid) continue;
+              if constexpr (NB == 16 && EPI == kEpiHybridPick) {
+                {
+                  // fused greedy pick: the value takes part in this thread's running best of row m; the
+                  // logit itself is stored only when the caller wants the logits
+                  float v = __int_as_float(compute_output<EPI>(p, r[j], rs, wsc, bias_f, base_i, mult, shift, sc[j], ax[j]));
+                  v = soft_capped(v, p.soft_cap);
+                  if (p.y) static_cast<float*>(p.y)[(size_t)(m_base + m) * p.n + n] = v;
+                  best[j] = better_pick(best[j], BestPick{v, n});
+                  continue;
+                }
+              }
+              store_output<EPI>(p, m_base + m, n, r[j], rs, wsc, bias_f, base_i, mult, shift, sc[j], ax[j]);
             }
-          } else if (row_ok && r[3] == 0x7fffffff) {
-            store_output<EPI>(p, m_base, n, r[0], rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[0], sh->in_aux[0]);
           }
         }
         tc_fence_before();
@@ -498,6 +511,32 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
         named_barrier(1, kEpiThreads);  // sh->last is rewritten by the next split tile
       }
       ++seg;
+    }
+    if constexpr (NB == 16 && EPI == kEpiHybridPick) {
+      {
+        // this CTA's candidate per row: over the lanes, then over the four epilogue warps; the rows'
+        // candidates of all CTAs are compared by a small kernel afterwards
+        BestPick* cand = reinterpret_cast<BestPick*>(sh->in_aux);  // the rows' zero points are no longer needed
+        named_barrier(1, kEpiThreads);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (j < m_valid) {  // uniform over the CTA: rows that do not exist cost nothing at the kernel's tail
+            BestPick b = best[j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+              b = better_pick(b, BestPick{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)});
+            if (lane == 0) cand[quarter * 16 + j] = b;
+          }
+        }
+        named_barrier(1, kEpiThreads);
+        if (etid < m_valid) {
+          BestPick b = cand[etid];
+          for (int w = 1; w < 4; ++w) b = better_pick(b, cand[w * 16 + etid]);
+          const size_t slot = (size_t)(m_base + etid) * p.argmax_parts + blockIdx.x;
+          p.argmax_val[slot] = b.v;
+          p.argmax_idx[slot] = b.i;
+        }
+      }
     }
   }
 
@@ -590,6 +629,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
         bulk_g2s_hint(smem + (size_t)pre * L::kStageBytes, w_tiles + (size_t)kt * kTileBytes, kTileBytes, &full_bar[pre],
                       stream_policy);
       }
+      {  // the tiles behind the ring go to L2 while this CTA waits for its activations
+        const int pf_end = kt_begin + (int)pre + p.l2_prefetch_tiles < kt_end ? kt_begin + (int)pre + p.l2_prefetch_tiles : kt_end;
+        for (int kt = kt_begin + (int)pre; kt < pf_end; ++kt) prefetch_l2_bulk(w_tiles + (size_t)kt * kTileBytes, kTileBytes);
+      }
       pdl_wait();
       if (p.trace && blockIdx.x == 0) p.trace[1] = global_timer_ns();
       if (!p.prologue) {
@@ -666,7 +709,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
     // weights-side constants of the owned row: fetched while the predecessor kernel still runs
     if (n_own < p.n) {
       rs = p.row_sums ? p.row_sums[n_own] : 0;
-      if constexpr (EPI == kEpiHybridF32) {
+      if constexpr (EPI == kEpiHybridF32 || EPI == kEpiHybridPick) {
         wsc = p.per_channel ? p.w_scales[n_own] : p.w_scales[0];
         bias_f = p.bias_f32 ? p.bias_f32[n_own] : 0.0f;
       } else {
@@ -686,7 +729,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
         const int m = m_base + i;
         const bool ok = m < p.m;
         sh->in_scale[i] = (ok && p.in_scales) ? p.in_scales[m] : 0.0f;
-        if constexpr (EPI == kEpiHybridF32) {
+        if constexpr (EPI == kEpiHybridF32 || EPI == kEpiHybridPick) {
           sh->in_aux[i] = (ok && p.in_zps) ? p.in_zps[m] : 0;
         } else {
           sh->in_aux[i] = (ok && p.x_sums) ? p.x_sums[m] : 0;
@@ -901,7 +944,7 @@ __global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_
           const int m = m_base + i;
           const bool ok = m < p.m;
           sh->in_scale[i] = (ok && p.in_scales) ? p.in_scales[m] : 0.0f;
-          if constexpr (EPI == kEpiHybridF32) {
+          if constexpr (EPI == kEpiHybridF32 || EPI == kEpiHybridPick) {
             sh->in_aux[i] = (ok && p.in_zps) ? p.in_zps[m] : 0;
           } else {
             sh->in_aux[i] = (ok && p.x_sums) ? p.x_sums[m] : 0;
@@ -919,7 +962,7 @@ __global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_
         const int n = (idx * TILES + j) * kTileN + row_in_tile;
         if (j >= tiles || n >= p.n) continue;
         rs[j] = p.row_sums ? p.row_sums[n] : 0;
-        if constexpr (EPI == kEpiHybridF32) {
+        if constexpr (EPI == kEpiHybridF32 || EPI == kEpiHybridPick) {
           wsc[j] = p.per_channel ? p.w_scales[n] : p.w_scales[0];
           bias_f[j] = p.bias_f32 ? p.bias_f32[n] : 0.0f;
         } else {
@@ -1079,9 +1122,7 @@ cudaError_t launch_umma_one(const FcParams& p, int m_base, int passes, cudaStrea
 }
 
 template <int EPI>
-cudaError_t launch_umma_nb(const FcParams& p_in, int m_base, int nb, int passes, cudaStream_t s) {
-  FcParams p = p_in;
-  if (const char* e = getenv("B200_FC_DEBUG")) p.debug_flags = atoi(e);
+cudaError_t launch_umma_nb(const FcParams& p, int m_base, int nb, int passes, cudaStream_t s) {
   switch (nb) {
     case 16: return launch_umma_one<16, EPI>(p, m_base, passes, s);
     case 32: return launch_umma_one<32, EPI>(p, m_base, passes, s);
@@ -1243,6 +1284,11 @@ cudaError_t launch_all(const FcParams& p, cudaStream_t s) {
 
 }  // namespace
 
+int fc_argmax_ctas(int n) {
+  const int sms = device_sm_count();
+  return std::min(tiles_n(n), sms * UmmaBudget<16>::kCtasPerSm);
+}
+
 bool fc_prologue_supported(int m, int k) { return m >= 1 && m <= kPrologueMaxM && k >= 1 && k <= kPrologueMaxK; }
 
 int umma_rows_per_pass(int m) {
@@ -1251,7 +1297,18 @@ int umma_rows_per_pass(int m) {
   return nb;
 }
 
+// The hybrid projection with the greedy pick in its epilogue: one pass of up to 16 rows, whole n tiles per
+// CTA, one candidate slot per CTA and row.
+static cudaError_t launch_pick(const FcParams& p, cudaStream_t s) {
+  if (umma_rows_per_pass(p.m) != 16 || !p.argmax_val || !p.argmax_idx) return cudaErrorInvalidValue;
+  FcParams q = p;
+  q.force_whole_tiles = 1;
+  if (fc_argmax_ctas(q.n) > q.argmax_parts) return cudaErrorInvalidValue;
+  return launch_umma_one<16, kEpiHybridPick>(q, 0, 1, s);
+}
+
 cudaError_t launch_fc_i8_umma(const FcParams& p, FcEpilogue epi, cudaStream_t s) {
+  if (epi == kEpiHybridPick) return launch_pick(p, s);
   if (epi == kEpiHybridF32) return launch_all<kEpiHybridF32>(p, s);
   if (epi == kEpiRequantI8) return launch_all<kEpiRequantI8>(p, s);
   return launch_all<kEpiRawI32>(p, s);

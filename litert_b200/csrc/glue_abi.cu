@@ -246,4 +246,42 @@ int b200_fc_hybrid_quantized(const int8_t* d_q_tiled, const float* d_scales, con
   return gcuda(launch_fc_i8_umma(p, kEpiHybridF32, static_cast<cudaStream_t>(stream)), "b200_fc_hybrid_quantized");
 }
 
+size_t b200_lm_head_workspace_bytes(int m) { return m > 0 ? (size_t)m * kArgmaxSlots * 8 : 0; }
+
+int b200_lm_head_greedy(const int8_t* d_q_tiled, const float* d_scales, const int32_t* d_zero_points, int m, int k,
+                        const void* d_w_packed, int n, const int32_t* d_row_sums, const float* d_w_scales, float soft_cap,
+                        float* d_logits, int32_t* d_tokens, void* d_workspace, size_t workspace_bytes, void* d_zero_ws,
+                        void* stream) {
+  if (!d_q_tiled || !d_scales || !d_w_packed || !d_row_sums || !d_w_scales || !d_tokens || !d_workspace || !d_zero_ws ||
+      m <= 0 || n <= 0 || k <= 0)
+    return gfail(B200_ERR_INVALID_ARGUMENT, "b200_lm_head_greedy: bad argument");
+  if (m > 16) return gfail(B200_ERR_UNSUPPORTED, "b200_lm_head_greedy: at most 16 rows (use b200_fc_hybrid_quantized + b200_argmax_rows)");
+  if (workspace_bytes < b200_lm_head_workspace_bytes(m)) return gfail(B200_ERR_INVALID_ARGUMENT, "b200_lm_head_greedy: workspace too small");
+  if (!(soft_cap >= 0.0f)) return gfail(B200_ERR_INVALID_ARGUMENT, "b200_lm_head_greedy: soft cap must be >= 0");
+  const int parts = fc_argmax_ctas(n);
+  if (parts > kArgmaxSlots) return gfail(B200_ERR_UNSUPPORTED, "b200_lm_head_greedy: device with more CTAs than candidate slots");
+  float* part_val = static_cast<float*>(d_workspace);
+  int32_t* part_idx = reinterpret_cast<int32_t*>(part_val + (size_t)m * kArgmaxSlots);
+  FcParams p;
+  memset(&p, 0, sizeof(p));
+  p.w_packed = static_cast<const uint8_t*>(d_w_packed);
+  p.q_tiled = d_q_tiled;
+  p.m = m; p.n = n; p.k = k;
+  p.n_tiles = tiles_n(n); p.k_tiles = tiles_k8(k); p.m_alloc = m_alloc_for(m);
+  p.in_scales = d_scales;
+  p.in_zps = d_zero_points;
+  p.w_scales = d_w_scales; p.per_channel = 1;
+  p.row_sums = d_row_sums;
+  p.y = d_logits;
+  p.argmax_val = part_val;
+  p.argmax_idx = part_idx;
+  p.argmax_parts = parts;
+  p.soft_cap = soft_cap;
+  fill_fc_ws(p, d_zero_ws);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = launch_fc_i8_umma(p, kEpiHybridPick, s);
+  if (e != cudaSuccess) return gcuda(e, "b200_lm_head_greedy (projection)");
+  return gcuda(launch_argmax_final(part_val, part_idx, m, parts, 0, d_tokens, nullptr, 0, nullptr, s), "b200_lm_head_greedy (pick)");
+}
+
 }  // extern "C"

@@ -36,6 +36,7 @@ enum FcEpilogue : int {
   kEpiHybridF32 = 0,  // float out: bias + (acc - row_sum*zp) * (in_scale*w_scale), activation
   kEpiRequantI8 = 1,  // int8 out: fixed-point requantization
   kEpiRawI32 = 2,     // int32 accumulators out (row-major [m,n])
+  kEpiHybridPick = 3, // the hybrid epilogue plus the fused greedy pick (FcParams::argmax_val), at most 16 rows
 };
 
 struct FcParams {
@@ -85,12 +86,25 @@ struct FcParams {
   // measurement only: four %globaltimer stamps per launch (first CTA: entry, dependency wait passed,
   // exit; any CTA: latest exit), or null
   unsigned long long* trace;
+  // Weight tiles beyond its shared-memory ring that a CTA asks L2 for before it waits for its
+  // activations (0 = none). Only worth it inside a chain of dependent kernels, where the wait is long.
+  int l2_prefetch_tiles;
   int max_ctas;              // 0 = chosen per shape
   int whole_tiles;           // set by the launcher: CTAs own whole n tiles (no split-K)
   int force_whole_tiles;     // set by the launcher for prefill-sized passes
   int split_passes;       // several passes in one launch, each split over its share of the SMs (stream-K)
-  int debug_flags;           // measurement only: 1 = skip the MMAs, 2 = the epilogue, 4 = the output stores, 8 = the TMEM loads
+  // Fused greedy pick (hybrid epilogue, at most 16 rows, tcgen05 path): every CTA writes the best value
+  // and column of each row among the channels it owns to argmax_val / argmax_idx[row * argmax_parts +
+  // CTA] (first index of the maximum, NaN rule of the reference's sampler); soft_cap > 0 replaces a logit
+  // by cap * tanh(logit / cap) first. y may then be null (no logits written). The caller pre-fills
+  // unused slots of a row with {-inf, INT_MAX} or reduces over exactly argmax_ctas() slots.
+  float* argmax_val;
+  int32_t* argmax_idx;
+  int argmax_parts;
+  float soft_cap;
 };
+// Number of CTAs (= candidate slots per row) the fused pick uses for n output channels.
+int fc_argmax_ctas(int n);
 
 // Streamed-weights GEMM on the packed int8 tiles (any m; m > 64 runs in
 // chunks of 64 rows).

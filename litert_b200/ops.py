@@ -353,3 +353,20 @@ def fully_connected_hybrid_quantized(rows, weights, filter_scales, bias=None, ac
                                                  _ptr(fs), 1 if fs.numel() > 1 else 0, _ptr(bias), int(activation),
                                                  _ptr(y), _ptr(ws.zero), _stream()))
     return y
+
+
+def lm_head_greedy(rows, weights, filter_scales, soft_cap=0.0, want_logits=False, ws=None):
+    """The vocabulary projection with the greedy pick in its epilogue (at most 16 rows): returns
+    (tokens int32 [m], logits [m, n] or None)."""
+    lib = _lib.load()
+    fs = _need(filter_scales, torch.float32, "filter_scales").reshape(-1)
+    ws = ws or Workspace(rows.tiled.device)
+    dev = rows.tiled.device
+    tokens = torch.empty(rows.m, dtype=torch.int32, device=dev)
+    logits = torch.empty((rows.m, weights.n), dtype=torch.float32, device=dev) if want_logits else None
+    need = int(lib.b200_lm_head_workspace_bytes(rows.m))
+    wsb = torch.empty(need, dtype=torch.uint8, device=dev)
+    _gcheck(lib.b200_lm_head_greedy(_ptr(rows.tiled), _ptr(rows.scales), _ptr(rows.zero_points), rows.m, rows.k,
+                                    _ptr(weights.packed), weights.n, _ptr(weights.row_sums), _ptr(fs), float(soft_cap),
+                                    _ptr(logits), _ptr(tokens), _ptr(wsb), need, _ptr(ws.zero), _stream()))
+    return tokens, logits

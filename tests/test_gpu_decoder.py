@@ -93,6 +93,30 @@ def test_decoder_wide_batch_uses_chunked_attention(oracle):
     ref.close()
 
 
+def test_decoder_greedy_pick_is_the_first_index_argmax_of_its_logits(oracle):
+    """The token the step returns (picked inside the LM-head GEMV's epilogue) is the serial first-index
+    arg-max of the logits the same call hands out, with and without the logits soft-cap, and the graph path
+    (no logits written at all) returns the same tokens."""
+    from litert_b200 import _lib
+    from litert_b200 import decoder as dec
+
+    cfg = dict(dec.TINY)
+    d = dec.Decoder(cfg, max_seq=16, max_batch=3, weights=dec.make_weights(cfg, seed=31))
+    tok = np.asarray([1, 500, 999], np.int32)
+    for cap in (0.0, 2.0):
+        assert _lib.load().b200_decoder_set_logit_soft_cap(d.handle, cap) == 0
+        d.reset()
+        nxt, logits = d.step(tok, want_logits=True)
+        lg = logits.cpu().numpy()
+        assert np.array_equal(nxt, oracle.stage_argmax(lg))
+        if cap:
+            assert np.max(np.abs(lg)) <= cap + 1e-6
+        d.reset()
+        nxt_graph, _ = d.step(tok)
+        assert np.array_equal(nxt_graph, nxt)
+    d.close()
+
+
 def test_decoder_graph_path_equals_eager_path_and_is_repeatable():
     from litert_b200 import decoder as dec
 

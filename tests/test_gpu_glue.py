@@ -304,3 +304,42 @@ def test_projection_at_decoder_widths_bit_exact(oracle, m, n, k, name):
     want = _hybrid_from_quantized(rows.rows().cpu().numpy(), rows.scales[:m].cpu().numpy(),
                                   rows.zero_points[:m].cpu().numpy(), w, ws)
     assert np.array_equal(y, want), (name, np.max(np.abs(y - want)))
+
+
+@pytest.mark.parametrize("m", [1, 5, 16])
+def test_lm_head_greedy_fused_pick(oracle, m):
+    """The vocabulary GEMV with the pick in its epilogue (256000 rows: the 296-CTA launch): the tokens are those
+    of the serial scan over the bit-exact logits, with ties, a NaN logit at index 0 (wins) and elsewhere (never
+    wins), and under a soft-cap."""
+    from litert_b200 import ops
+
+    rng = np.random.default_rng(130 + m)
+    n, k = VOCAB, D_MODEL
+    w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    w[70000] = w[3]                       # two equal columns: the lower index wins a tie
+    ws = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    ws[70000] = ws[3]
+    h = (rng.standard_normal((m, k)) * 2.0).astype(np.float32)
+    rows = ops.add_rmsnorm_quantize(_dev(h), None, _dev(np.ones(k, np.float32)))
+    packed = ops.PackedInt8Weights(_dev(w))
+    want_logits = _hybrid_from_quantized(rows.rows().cpu().numpy(), rows.scales[:m].cpu().numpy(),
+                                         rows.zero_points[:m].cpu().numpy(), w, ws)
+    tok, logits = ops.lm_head_greedy(rows, packed, _dev(ws), want_logits=True)
+    assert np.array_equal(logits.cpu().numpy(), want_logits)
+    assert np.array_equal(tok.cpu().numpy(), oracle.stage_argmax(want_logits))
+    tok2, none = ops.lm_head_greedy(rows, packed, _dev(ws))        # without the logits: nothing else changes
+    assert none is None and np.array_equal(tok2.cpu().numpy(), tok.cpu().numpy())
+    # soft-cap: compare on the capped logits (the cap saturates the largest ones into ties)
+    tok3, capped = ops.lm_head_greedy(rows, packed, _dev(ws), soft_cap=30.0, want_logits=True)
+    cap_ref = oracle.stage_softcap(want_logits, 30.0)
+    got_capped = capped.cpu().numpy()
+    assert np.max(np.abs(got_capped - cap_ref)) <= 1e-4
+    assert np.array_equal(tok3.cpu().numpy(), oracle.stage_argmax(got_capped))
+    # NaN rule: a NaN scale makes that vocabulary row's logit NaN
+    for bad, expect_zero in ((0, True), (12345, False)):
+        ws_nan = ws.copy()
+        ws_nan[bad] = np.nan
+        tok4, lg4 = ops.lm_head_greedy(rows, packed, _dev(ws_nan), want_logits=True)
+        ref = oracle.stage_argmax(lg4.cpu().numpy())
+        assert np.array_equal(tok4.cpu().numpy(), ref)
+        assert np.all(ref == 0) if expect_zero else np.all(ref != bad)
