@@ -314,6 +314,36 @@ B200_API int b200_fc_hybrid_quantized(const int8_t* d_q_tiled, const float* d_sc
                                       const float* d_w_scales, int per_channel, const float* d_bias, int activation,
                                       float* d_y, void* d_zero_ws, void* stream);
 
+/* ---- float32 builtins around the projections ------------------------------------
+ * What a decoder-only graph has between its quantized projections when it comes out
+ * of the reference's converters (tensor/examples/gemma3/gemma3_graph.cc): so that a
+ * delegate can keep the whole graph in one partition. Shapes are given as four
+ * dimensions (pad with leading ones). */
+B200_API const char* b200_elementwise_last_error(void);
+/* op 0 = ADD, 1 = MUL, NumPy broadcasting (tflite/kernels/internal/reference/add.h,
+ * mul.h: BroadcastAdd4DSlow / BroadcastMul4DSlow), no fused activation. */
+B200_API int b200_binary_f32(int op, const float* d_a, const int* a_dims4, const float* d_b, const int* b_dims4,
+                             float* d_out, const int* out_dims4, void* stream);
+/* GELU (tflite/kernels/internal/reference/gelu.h:31-45), tanh approximation or erf. */
+B200_API int b200_gelu_f32(const float* d_x, float* d_y, size_t n, int approximate, void* stream);
+/* Copies the box box4 from src (at src_begin4) to dst (at dst_begin4): SLICE
+ * (tflite/kernels/slice.cc) and the pieces of CONCATENATION; elements of 1 or 4 bytes. */
+B200_API int b200_box_copy(const void* d_src, const int* src_dims4, const int* src_begin4, void* d_dst,
+                           const int* dst_dims4, const int* dst_begin4, const int* box4, int elem_bytes, void* stream);
+/* odml.rms_norm composite (ml_drift_delegate/tflite/convert/convert_rms_norm.cc:40-61):
+ * y = x * rsqrt(mean(x^2) + eps) * gain per row of d elements (gain may be NULL). */
+B200_API int b200_rms_norm_f32(const float* d_x, const float* d_gain, float* d_y, int rows, int d, float eps,
+                               void* stream);
+/* odml.update_kv_cache custom op (tflite/experimental/genai/kvcache.cc:230-340) on
+ * device-resident float32 caches [max_entries, row_elems]: the t rows of d_k / d_v go
+ * to slots *d_position .. + t - 1. The reference shifts the cache down when the
+ * write runs past the last slot; here that raises status 201 in the zero workspace
+ * (b200_read_status) and writes nothing. */
+B200_API int b200_kv_cache_update_f32(const int64_t* d_position, const float* d_k, const float* d_v, int t,
+                                      int row_elems, int max_entries, float* d_k_cache, float* d_v_cache,
+                                      void* d_zero_ws, void* stream);
+B200_API int b200_widen_i32_to_i64(const int32_t* d_in, int64_t* d_out, int n, void* stream);
+
 /* ---- Gemma-shaped decoder, one decode step per call ---------------------------
  * A resident decoder for the decode benchmark: every projection is a dynamic-range
  * hybrid FULLY_CONNECTED (b200_fc_hybrid semantics: per-row asymmetric input

@@ -59,6 +59,13 @@ SIGNATURES = {
     "b200_sdpa_decode_quantized": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp,
                                         _vp, _sz, _vp]),
     "b200_fc_hybrid_quantized": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp]),
+    "b200_elementwise_last_error": (ctypes.c_char_p, []),
+    "b200_binary_f32": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_gelu_f32": (_i, [_vp, _vp, _sz, _i, _vp]),
+    "b200_box_copy": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "b200_rms_norm_f32": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
+    "b200_kv_cache_update_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "b200_widen_i32_to_i64": (_i, [_vp, _vp, _i, _vp]),
     "b200_decoder_create": (_i, [_vp, _vp, ctypes.POINTER(_vp)]),
     "b200_decoder_destroy": (None, [_vp]),
     "b200_decoder_set_layer": (_i, [_vp, _i, _vp]),

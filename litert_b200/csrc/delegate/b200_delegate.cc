@@ -43,6 +43,7 @@ struct Options {
   std::string fail_on;          // "", "init", "prepare", "invoke", "alloc": host-side fault injection
   bool buffer_handles = false;  // publish outputs as buffer handles instead of copying back in invoke
   bool claim_fc = true, claim_bmm = true, claim_sdpa = true;
+  bool claim_glue = true;  // the float32 ops between a decoder's projections (ADD, MUL, GELU, RESHAPE, SLICE, ...)
   int min_nodes_per_partition = 1;
 };
 
@@ -69,6 +70,15 @@ struct Options {
     int _rc = (expr);                                                                  \
     if (_rc != B200_OK) {                                                              \
       TF_LITE_KERNEL_LOG((ctx), "B200 delegate: %s", b200_glue_last_error());          \
+      return kTfLiteDelegateError;                                                     \
+    }                                                                                  \
+  } while (0)
+
+#define B200_EW_OR_RETURN(ctx, expr)                                                   \
+  do {                                                                                 \
+    int _rc = (expr);                                                                  \
+    if (_rc != B200_OK) {                                                              \
+      TF_LITE_KERNEL_LOG((ctx), "B200 delegate: %s", b200_elementwise_last_error());   \
       return kTfLiteDelegateError;                                                     \
     }                                                                                  \
   } while (0)
@@ -127,7 +137,23 @@ static void* ArenaAlloc(void* user, size_t bytes) {
 static void ArenaFree(void*, void* p) { cudaFree(p); }
 
 // ---------------------------------------------------------------- node classification
-enum class OpKind { kNone, kFcInt8, kFcHybrid, kFcW4, kBmmHybrid, kBmmInt8, kSdpa };
+enum class OpKind {
+  kNone, kFcInt8, kFcHybrid, kFcW4, kBmmHybrid, kBmmInt8, kSdpa,
+  // the ops between a decoder's projections
+  kEmbedding, kAdd, kMul, kGelu, kReshape, kSlice, kConcat, kRmsNorm, kKvCache, kArgMax
+};
+
+constexpr char kRmsNormName[] = "odml.rms_norm";
+constexpr char kKvCacheName[] = "odml.update_kv_cache";
+
+// A tensor's shape as four dimensions, padded with leading ones; false beyond rank 4.
+inline bool Pad4(const TfLiteTensor& t, int out[4]) {
+  const int r = t.dims->size;
+  if (r > 4) return false;
+  for (int i = 0; i < 4; ++i) out[i] = 1;
+  for (int i = 0; i < r; ++i) out[4 - r + i] = t.dims->data[i];
+  return true;
+}
 
 inline bool IsConst(const TfLiteTensor& t) { return t.allocation_type == kTfLiteMmapRo && t.data.raw != nullptr; }
 
@@ -188,6 +214,148 @@ bool IsSdpaNode(const TfLiteNode* node, const TfLiteRegistration* reg) {
     return reg->custom_name && strcmp(reg->custom_name, kSdpaName) == 0;  // xnnpack_delegate.cc:3443-3444
   }
   return false;
+}
+
+
+bool IsCompositeNamed(const TfLiteNode* node, const TfLiteRegistration* reg, const char* name) {
+  if (reg->builtin_code != kTfLiteBuiltinStablehloComposite) return false;
+  const auto* p = static_cast<const TfLiteStablehloCompositeParams*>(node->builtin_data);
+  return p && p->name && strcmp(p->name, name) == 0;
+}
+
+// The float32 ops a decoder-only graph has between its projections (as
+// tensor/examples/gemma3/gemma3_graph.cc authors them), claimed so that the whole graph is one partition.
+// Leaves *why empty when the op is simply none of them.
+OpKind ClassifyGlue(TfLiteContext* ctx, const TfLiteNode* node, const TfLiteRegistration* reg, std::string* why) {
+  const TfLiteTensor* T = ctx->tensors;
+  auto in = [&](int i) -> const TfLiteTensor* {
+    if (i >= node->inputs->size) return nullptr;
+    const int idx = node->inputs->data[i];
+    return idx == kTfLiteOptionalTensor ? nullptr : &T[idx];
+  };
+  if (node->outputs->size < 1) return OpKind::kNone;
+  const TfLiteTensor* y = &T[node->outputs->data[0]];
+  int d4[4];
+  switch (reg->builtin_code) {
+    case kTfLiteBuiltinAdd:
+    case kTfLiteBuiltinMul: {
+      const TfLiteTensor *a = in(0), *b = in(1);
+      if (!a || !b || node->inputs->size != 2) return *why = "binary op operands", OpKind::kNone;
+      const auto act = reg->builtin_code == kTfLiteBuiltinAdd
+                           ? static_cast<const TfLiteAddParams*>(node->builtin_data)->activation
+                           : static_cast<const TfLiteMulParams*>(node->builtin_data)->activation;
+      if (act != kTfLiteActNone) return *why = "fused activation on a binary op", OpKind::kNone;
+      if (a->type != kTfLiteFloat32 || b->type != kTfLiteFloat32 || y->type != kTfLiteFloat32)
+        return *why = "binary op is not float32", OpKind::kNone;
+      if (IsConst(*a) && IsConst(*b)) return *why = "constant binary op", OpKind::kNone;
+      int da[4], db[4];
+      if (!Pad4(*a, da) || !Pad4(*b, db) || !Pad4(*y, d4)) return *why = "binary op rank", OpKind::kNone;
+      for (int i = 0; i < 4; ++i) {
+        const int o = da[i] == 1 ? db[i] : da[i];
+        if ((db[i] != 1 && db[i] != o) || d4[i] != o || o <= 0) return *why = "binary op shapes do not broadcast", OpKind::kNone;
+      }
+      return reg->builtin_code == kTfLiteBuiltinAdd ? OpKind::kAdd : OpKind::kMul;
+    }
+    case kTfLiteBuiltinGelu: {
+      const TfLiteTensor* x = in(0);
+      if (!x || x->type != kTfLiteFloat32 || y->type != kTfLiteFloat32 || IsConst(*x) || NumElements(*x) != NumElements(*y))
+        return *why = "gelu operands", OpKind::kNone;
+      return OpKind::kGelu;
+    }
+    case kTfLiteBuiltinReshape: {
+      const TfLiteTensor* x = in(0);
+      if (!x || IsConst(*x) || x->type != y->type || x->bytes != y->bytes || x->bytes == 0) return *why = "reshape operands", OpKind::kNone;
+      if (x->type != kTfLiteFloat32 && x->type != kTfLiteInt32 && x->type != kTfLiteInt8) return *why = "reshape type", OpKind::kNone;
+      if (node->inputs->size > 1 && in(1) && !IsConst(*in(1))) return *why = "reshape to a run-time shape", OpKind::kNone;
+      return OpKind::kReshape;
+    }
+    case kTfLiteBuiltinSlice: {
+      const TfLiteTensor *x = in(0), *b = in(1), *sz = in(2);
+      if (!x || !b || !sz || IsConst(*x) || !IsConst(*b) || !IsConst(*sz)) return *why = "slice operands", OpKind::kNone;
+      if (x->type != kTfLiteFloat32 || y->type != kTfLiteFloat32 || b->type != kTfLiteInt32 || sz->type != kTfLiteInt32)
+        return *why = "slice types", OpKind::kNone;
+      const int r = x->dims->size;
+      if (r > 4 || r < 1 || NumElements(*b) != r || NumElements(*sz) != r || y->dims->size != r) return *why = "slice rank", OpKind::kNone;
+      for (int i = 0; i < r; ++i) {
+        const int begin = b->data.i32[i];
+        const int size = sz->data.i32[i] < 0 ? x->dims->data[i] - begin : sz->data.i32[i];
+        if (begin < 0 || size <= 0 || begin + size > x->dims->data[i] || y->dims->data[i] != size) return *why = "slice box", OpKind::kNone;
+      }
+      return OpKind::kSlice;
+    }
+    case kTfLiteBuiltinConcatenation: {
+      const auto* p = static_cast<const TfLiteConcatenationParams*>(node->builtin_data);
+      if (!p || p->activation != kTfLiteActNone || node->inputs->size < 1) return *why = "concatenation parameters", OpKind::kNone;
+      const int r = y->dims->size;
+      if (r < 1 || r > 4 || y->type != kTfLiteFloat32) return *why = "concatenation output", OpKind::kNone;
+      const int axis = p->axis < 0 ? p->axis + r : p->axis;
+      if (axis < 0 || axis >= r) return *why = "concatenation axis", OpKind::kNone;
+      int along = 0;
+      for (int i = 0; i < node->inputs->size; ++i) {
+        const TfLiteTensor* x = in(i);
+        if (!x || x->type != kTfLiteFloat32 || x->dims->size != r || IsConst(*x)) return *why = "concatenation operands", OpKind::kNone;
+        for (int d = 0; d < r; ++d)
+          if (d != axis && x->dims->data[d] != y->dims->data[d]) return *why = "concatenation shapes", OpKind::kNone;
+        along += x->dims->data[axis];
+      }
+      if (along != y->dims->data[axis]) return *why = "concatenation shapes", OpKind::kNone;
+      return OpKind::kConcat;
+    }
+    case kTfLiteBuiltinEmbeddingLookup: {
+      // hybrid lookup: int8 table with per-tensor or per-row scales (tflite/kernels/embedding_lookup.cc:307-395)
+      const TfLiteTensor *ids = in(0), *table = in(1);
+      if (!ids || !table || ids->type != kTfLiteInt32 || IsConst(*ids)) return *why = "embedding ids", OpKind::kNone;
+      if (!IsConst(*table) || table->type != kTfLiteInt8 || table->dims->size != 2 || y->type != kTfLiteFloat32)
+        return *why = "embedding table is not a constant int8 matrix", OpKind::kNone;
+      const auto* q = Affine(*table);
+      if (q && q->scale && q->scale->size > 1 && (q->quantized_dimension != 0 || q->scale->size != table->dims->data[0]))
+        return *why = "embedding scales must follow the rows", OpKind::kNone;
+      if (NumElements(*y) != NumElements(*ids) * table->dims->data[1]) return *why = "embedding output shape", OpKind::kNone;
+      return OpKind::kEmbedding;
+    }
+    case kTfLiteBuiltinArgMax: {
+      const TfLiteTensor *x = in(0), *axis = in(1);
+      if (!x || !axis || x->type != kTfLiteFloat32 || IsConst(*x) || !IsConst(*axis) || axis->type != kTfLiteInt32)
+        return *why = "arg_max operands", OpKind::kNone;
+      const int r = x->dims->size;
+      const int a = axis->data.i32[0] < 0 ? axis->data.i32[0] + r : axis->data.i32[0];
+      if (r < 1 || a != r - 1) return *why = "arg_max over another axis than the last", OpKind::kNone;
+      if (y->type != kTfLiteInt32 && y->type != kTfLiteInt64) return *why = "arg_max output type", OpKind::kNone;
+      if (NumElements(*y) * x->dims->data[r - 1] != NumElements(*x)) return *why = "arg_max output shape", OpKind::kNone;
+      return OpKind::kArgMax;
+    }
+    default:
+      break;
+  }
+  if (IsCompositeNamed(node, reg, kRmsNormName)) {
+    const TfLiteTensor *x = in(0), *g = in(1);
+    if (!x || x->type != kTfLiteFloat32 || y->type != kTfLiteFloat32 || IsConst(*x) || x->dims->size < 1 || x->bytes != y->bytes)
+      return *why = "rms_norm operands", OpKind::kNone;
+    const int d = x->dims->data[x->dims->size - 1];
+    if (g && (!IsConst(*g) || g->type != kTfLiteFloat32 || NumElements(*g) != d)) return *why = "rms_norm scale", OpKind::kNone;
+    return OpKind::kRmsNorm;
+  }
+  if (reg->builtin_code == kTfLiteBuiltinCustom && reg->custom_name && strcmp(reg->custom_name, kKvCacheName) == 0) {
+    // tflite/experimental/genai/kvcache.cc:78-228: (position, key, value) -> (full keys, full values), float32, batch 1
+    const TfLiteTensor *pos = in(0), *k = in(1), *v = in(2);
+    if (node->inputs->size != 3 || node->outputs->size != 2 || !pos || !k || !v) return *why = "kv cache operands", OpKind::kNone;
+    const TfLiteTensor* y2 = &T[node->outputs->data[1]];
+    if (pos->type != kTfLiteInt64 || IsConst(*pos) || IsConst(*k) || IsConst(*v)) return *why = "kv cache operands", OpKind::kNone;
+    for (const TfLiteTensor* t : {k, v, y, y2})
+      if (t->type != kTfLiteFloat32 || t->dims->size != 4 || t->dims->data[0] != 1) return *why = "kv cache wants float32 [1, t, heads, dim]", OpKind::kNone;
+    float cap = 0.0f;
+    b200::FlexMapFloat(static_cast<const uint8_t*>(node->custom_initial_data), static_cast<size_t>(node->custom_initial_data_size),
+                       "kv_cache_max", &cap);
+    const int max_entries = cap > 0.0f ? static_cast<int>(cap) : 2048;  // kDefaultMaxNumCacheEntries
+    for (const TfLiteTensor* t : {y, y2})
+      if (t->dims->data[1] != max_entries || t->dims->data[2] != k->dims->data[2] || t->dims->data[3] != k->dims->data[3])
+        return *why = "kv cache output shape", OpKind::kNone;
+    if (v->dims->data[1] != k->dims->data[1] || v->dims->data[2] != k->dims->data[2] || v->dims->data[3] != k->dims->data[3] ||
+        k->dims->data[1] > max_entries)
+      return *why = "kv cache key / value shapes", OpKind::kNone;
+    return OpKind::kKvCache;
+  }
+  return OpKind::kNone;
 }
 
 // Why a node is not claimed is reported through `why` (one line).
@@ -310,6 +478,10 @@ OpKind Classify(TfLiteContext* ctx, const TfLiteNode* node, const TfLiteRegistra
       return *why = "sdpa cache too long for this head layout", OpKind::kNone;
     return OpKind::kSdpa;
   }
+  if (opt.claim_glue) {
+    const OpKind k = ClassifyGlue(ctx, node, reg, why);
+    if (k != OpKind::kNone || !why->empty()) return k;
+  }
   return *why = "op not on the hot path", OpKind::kNone;
 }
 
@@ -330,6 +502,15 @@ struct OpRecord {
   bool adj_x = false, adj_y = false, rhs_const = true, fold_lhs = false;
   BmmGeometry g;
   size_t packed_stride = 0;         // bytes between the packed matrices of a batched RHS
+  // glue ops
+  std::vector<int> ins;             // operand tensors (graph numbering; -1 = a constant held in const_a / const_b)
+  int y2 = -1;                      // second output (kv cache)
+  DeviceMem const_a, const_b, ws_small;
+  int dims_a[4] = {1, 1, 1, 1}, dims_b[4] = {1, 1, 1, 1}, dims_o[4] = {1, 1, 1, 1}, begin[4] = {0, 0, 0, 0};
+  int axis = 0, rows = 0, width = 0, max_entries = 0, approximate = 1, vocab = 0;
+  float eps = 0.0f;
+  bool out_i64 = false;
+  DeviceMem k_cache, v_cache;       // odml.update_kv_cache: the persistent float32 caches
   // sdpa
   int B = 0, T = 1, N = 0, Nkv = 0, H = 0, S = 0;
   int sdpa_dtype = B200_DTYPE_F32;
@@ -428,12 +609,18 @@ class DelegateKernel {
     CUDA_OK(ctx, cudaSetDevice(st_->options.device));
     // tensors living on the device for this partition: every op operand that is not a constant
     slot_of_.clear();
+    persistent_.clear();
+    for (auto& opp : ops_)  // (before any touch: a later op's operand may be an earlier op's persistent output)
+      if (opp->kind == OpKind::kKvCache) {
+        persistent_[opp->y] = opp->k_cache.ptr;
+        persistent_[opp->y2] = opp->v_cache.ptr;
+      }
     std::vector<b200::ArenaRequest> req;
     const int num_ops = static_cast<int>(ops_.size());
     auto touch = [&](int tensor, int op_index) {
       if (tensor < 0) return;
       const TfLiteTensor& t = ctx->tensors[tensor];
-      if (IsConst(t)) return;
+      if (IsConst(t) || persistent_.count(tensor)) return;
       auto it = slot_of_.find(tensor);
       if (it == slot_of_.end()) {
         slot_of_[tensor] = static_cast<int>(req.size());
@@ -463,6 +650,15 @@ class DelegateKernel {
           if (!op.adj_y) bmm_rhs = std::max(bmm_rhs, ctx->tensors[op.w].bytes);
           bmm_packed = std::max(bmm_packed, mats * b200_packed_w8_bytes(op.n, op.kdim));
           bmm_rs = std::max(bmm_rs, mats * sizeof(int32_t) * op.n);
+        }
+      } else if (op.kind >= OpKind::kEmbedding) {
+        for (int t : op.ins) touch(t, i);
+        if (op.kind == OpKind::kKvCache) {
+          // the op's outputs ARE its persistent caches: never arena tensors
+          persistent_[op.y] = op.k_cache.ptr;
+          persistent_[op.y2] = op.v_cache.ptr;
+        } else {
+          touch(op.y, i);
         }
       } else {
         const TfLiteTensor& x = ctx->tensors[op.x];
@@ -511,16 +707,16 @@ class DelegateKernel {
     }
     for (auto& opp : ops_) TF_LITE_ENSURE_STATUS(Launch(ctx, *opp));
     for (int t : outputs_) {
-      auto it = slot_of_.find(t);
-      if (it == slot_of_.end()) continue;
+      void* dev = Dev(t);
+      if (!dev) continue;
       TfLiteTensor& tensor = ctx->tensors[t];
       if (st_->options.buffer_handles) {
         if (tensor.buffer_handle == kTfLiteNullBufferHandle) tensor.buffer_handle = st_->next_handle++;
-        st_->handles[tensor.buffer_handle] = {arena_.Resolve(it->second), tensor.bytes};
+        st_->handles[tensor.buffer_handle] = {dev, tensor.bytes};
         tensor.delegate = &st_->delegate;
         tensor.data_is_stale = true;
       } else if (tensor.data.raw) {
-        CUDA_OK(ctx, cudaMemcpyAsync(tensor.data.raw, arena_.Resolve(it->second), tensor.bytes, cudaMemcpyDeviceToHost, s));
+        CUDA_OK(ctx, cudaMemcpyAsync(tensor.data.raw, dev, tensor.bytes, cudaMemcpyDeviceToHost, s));
       }
     }
     int status = 0;
@@ -536,6 +732,8 @@ class DelegateKernel {
 
  private:
   void* Dev(int tensor) {
+    auto pit = persistent_.find(tensor);
+    if (pit != persistent_.end()) return pit->second;
     auto it = slot_of_.find(tensor);
     return it == slot_of_.end() ? nullptr : arena_.Resolve(it->second);
   }
@@ -754,6 +952,96 @@ class DelegateKernel {
         CUDA_OK(ctx, cudaStreamSynchronize(st_->stream));
         return kTfLiteOk;
       }
+      case OpKind::kAdd:
+      case OpKind::kMul: {
+        const TfLiteTensor &a = T[idx(0)], &b = T[idx(1)];
+        Pad4(a, op->dims_a);
+        Pad4(b, op->dims_b);
+        Pad4(T[op->y], op->dims_o);
+        op->ins = {IsConst(a) ? -1 : idx(0), IsConst(b) ? -1 : idx(1)};
+        if (IsConst(a)) TF_LITE_ENSURE_STATUS(UploadRaw(ctx, a.data.raw, a.bytes, &op->const_a));
+        if (IsConst(b)) TF_LITE_ENSURE_STATUS(UploadRaw(ctx, b.data.raw, b.bytes, &op->const_b));
+        return kTfLiteOk;
+      }
+      case OpKind::kGelu:
+        op->ins = {idx(0)};
+        op->approximate = static_cast<const TfLiteGeluParams*>(node->builtin_data)->approximate ? 1 : 0;
+        return kTfLiteOk;
+      case OpKind::kReshape:
+        op->ins = {idx(0)};
+        return kTfLiteOk;
+      case OpKind::kSlice: {
+        const TfLiteTensor &x = T[idx(0)], &b = T[idx(1)];
+        op->ins = {idx(0)};
+        Pad4(x, op->dims_a);
+        Pad4(T[op->y], op->dims_o);
+        const int r = x.dims->size;
+        for (int i = 0; i < r; ++i) op->begin[4 - r + i] = b.data.i32[i];
+        return kTfLiteOk;
+      }
+      case OpKind::kConcat: {
+        const auto* p = static_cast<const TfLiteConcatenationParams*>(node->builtin_data);
+        const int r = T[op->y].dims->size;
+        op->axis = (p->axis < 0 ? p->axis + r : p->axis) + (4 - r);
+        Pad4(T[op->y], op->dims_o);
+        for (int i = 0; i < node->inputs->size; ++i) op->ins.push_back(idx(i));
+        return kTfLiteOk;
+      }
+      case OpKind::kEmbedding: {
+        const TfLiteTensor& table = T[idx(1)];
+        op->ins = {idx(0)};
+        op->vocab = table.dims->data[0];
+        op->width = table.dims->data[1];
+        op->rows = static_cast<int>(NumElements(T[idx(0)]));
+        TF_LITE_ENSURE_STATUS(UploadRaw(ctx, table.data.raw, table.bytes, &op->const_a));
+        const auto* q = Affine(table);
+        std::vector<float> scales(op->vocab, table.params.scale);
+        if (q && q->scale && q->scale->size > 1) scales.assign(q->scale->data, q->scale->data + q->scale->size);
+        TF_LITE_ENSURE_STATUS(Upload(ctx, scales, &op->w_scales));
+        CUDA_OK(ctx, cudaStreamSynchronize(st_->stream));
+        return kTfLiteOk;
+      }
+      case OpKind::kArgMax: {
+        const TfLiteTensor& x = T[idx(0)];
+        op->ins = {idx(0)};
+        op->width = x.dims->data[x.dims->size - 1];
+        op->rows = static_cast<int>(NumElements(x) / op->width);
+        op->out_i64 = T[op->y].type == kTfLiteInt64;
+        if (!op->ws_small.ensure(b200_argmax_workspace_bytes(op->rows) + sizeof(int32_t) * op->rows)) {
+          TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed");
+          return kTfLiteDelegateError;
+        }
+        return kTfLiteOk;
+      }
+      case OpKind::kRmsNorm: {
+        const TfLiteTensor& x = T[idx(0)];
+        op->ins = {idx(0)};
+        op->width = x.dims->data[x.dims->size - 1];
+        op->rows = static_cast<int>(NumElements(x) / op->width);
+        if (idx(1) >= 0) TF_LITE_ENSURE_STATUS(UploadRaw(ctx, T[idx(1)].data.raw, T[idx(1)].bytes, &op->const_a));
+        const auto* p = static_cast<const TfLiteStablehloCompositeParams*>(node->builtin_data);
+        float eps = 1e-6f;
+        b200::FlexMapFloat(p->attributes, p->attributes_size, "epsilon", &eps);
+        op->eps = eps;
+        return kTfLiteOk;
+      }
+      case OpKind::kKvCache: {
+        const TfLiteTensor& k = T[idx(1)];
+        op->ins = {idx(0), idx(1), idx(2)};
+        op->y2 = node->outputs->data[1];
+        op->rows = k.dims->data[1];                       // new tokens per invocation
+        op->width = k.dims->data[2] * k.dims->data[3];    // elements per cached token
+        op->max_entries = T[op->y].dims->data[1];
+        const size_t bytes = sizeof(float) * static_cast<size_t>(op->max_entries) * op->width;
+        if (!op->k_cache.ensure(bytes) || !op->v_cache.ensure(bytes)) {
+          TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed (kv cache)");
+          return kTfLiteDelegateError;
+        }
+        // a fresh cache holds zeros, like resource::CacheBuffer::Initialize
+        CUDA_OK(ctx, cudaMemsetAsync(op->k_cache.ptr, 0, bytes, st_->stream));
+        CUDA_OK(ctx, cudaMemsetAsync(op->v_cache.ptr, 0, bytes, st_->stream));
+        return kTfLiteOk;
+      }
       case OpKind::kSdpa: {
         op->q = idx(0);
         op->k = idx(1);
@@ -817,6 +1105,63 @@ class DelegateKernel {
                                          static_cast<const float*>(op.kfsum.ptr),
                                          static_cast<const float*>(op.bias.ptr), static_cast<float*>(Dev(op.y)),
                                          st_->zero_ws.ptr, st_->scratch.ptr, st_->scratch.bytes, s));
+        return kTfLiteOk;
+      case OpKind::kAdd:
+      case OpKind::kMul: {
+        const float* a = op.ins[0] < 0 ? static_cast<const float*>(op.const_a.ptr) : static_cast<const float*>(Dev(op.ins[0]));
+        const float* b = op.ins[1] < 0 ? static_cast<const float*>(op.const_b.ptr) : static_cast<const float*>(Dev(op.ins[1]));
+        B200_EW_OR_RETURN(ctx, b200_binary_f32(op.kind == OpKind::kAdd ? 0 : 1, a, op.dims_a, b, op.dims_b,
+                                              static_cast<float*>(Dev(op.y)), op.dims_o, s));
+        return kTfLiteOk;
+      }
+      case OpKind::kGelu:
+        B200_EW_OR_RETURN(ctx, b200_gelu_f32(static_cast<const float*>(Dev(op.ins[0])), static_cast<float*>(Dev(op.y)),
+                                            static_cast<size_t>(NumElements(ctx->tensors[op.y])), op.approximate, s));
+        return kTfLiteOk;
+      case OpKind::kReshape:
+        CUDA_OK(ctx, cudaMemcpyAsync(Dev(op.y), Dev(op.ins[0]), ctx->tensors[op.y].bytes, cudaMemcpyDeviceToDevice, s));
+        return kTfLiteOk;
+      case OpKind::kSlice: {
+        const int zero[4] = {0, 0, 0, 0};
+        B200_EW_OR_RETURN(ctx, b200_box_copy(Dev(op.ins[0]), op.dims_a, op.begin, Dev(op.y), op.dims_o, zero, op.dims_o, 4, s));
+        return kTfLiteOk;
+      }
+      case OpKind::kConcat: {
+        int at[4] = {0, 0, 0, 0};
+        const int zero[4] = {0, 0, 0, 0};
+        for (int t : op.ins) {
+          int d[4];
+          Pad4(ctx->tensors[t], d);
+          B200_EW_OR_RETURN(ctx, b200_box_copy(Dev(t), d, zero, Dev(op.y), op.dims_o, at, d, 4, s));
+          at[op.axis] += d[op.axis];
+        }
+        return kTfLiteOk;
+      }
+      case OpKind::kEmbedding:
+        B200_GLUE_OR_RETURN(ctx, b200_embedding_lookup(static_cast<const int32_t*>(Dev(op.ins[0])), op.rows,
+                                                      static_cast<const int8_t*>(op.const_a.ptr),
+                                                      static_cast<const float*>(op.w_scales.ptr), op.vocab, op.width, 1.0f,
+                                                      static_cast<float*>(Dev(op.y)), s));
+        return kTfLiteOk;
+      case OpKind::kArgMax: {
+        uint8_t* ws = static_cast<uint8_t*>(op.ws_small.ptr);
+        const size_t ws_bytes = b200_argmax_workspace_bytes(op.rows);
+        int32_t* out32 = op.out_i64 ? reinterpret_cast<int32_t*>(ws + ws_bytes) : static_cast<int32_t*>(Dev(op.y));
+        B200_GLUE_OR_RETURN(ctx, b200_argmax_rows(static_cast<const float*>(Dev(op.ins[0])), op.rows, op.width, 0.0f, out32, ws,
+                                                 ws_bytes, s));
+        if (op.out_i64) B200_EW_OR_RETURN(ctx, b200_widen_i32_to_i64(out32, static_cast<int64_t*>(Dev(op.y)), op.rows, s));
+        return kTfLiteOk;
+      }
+      case OpKind::kRmsNorm:
+        B200_EW_OR_RETURN(ctx, b200_rms_norm_f32(static_cast<const float*>(Dev(op.ins[0])), static_cast<const float*>(op.const_a.ptr),
+                                                static_cast<float*>(Dev(op.y)), op.rows, op.width, op.eps, s));
+        return kTfLiteOk;
+      case OpKind::kKvCache:
+        B200_EW_OR_RETURN(ctx, b200_kv_cache_update_f32(static_cast<const int64_t*>(Dev(op.ins[0])),
+                                                       static_cast<const float*>(Dev(op.ins[1])),
+                                                       static_cast<const float*>(Dev(op.ins[2])), op.rows, op.width,
+                                                       op.max_entries, static_cast<float*>(op.k_cache.ptr),
+                                                       static_cast<float*>(op.v_cache.ptr), st_->zero_ws.ptr, s));
         return kTfLiteOk;
       case OpKind::kSdpa:
         if (op.T == 1) {
@@ -903,6 +1248,7 @@ class DelegateKernel {
   std::vector<int> inputs_, outputs_;
   std::vector<std::unique_ptr<OpRecord>> ops_;
   std::unordered_map<int, int> slot_of_;
+  std::unordered_map<int, void*> persistent_;  // tensors that live outside the arena (the kv-cache op's outputs)
 };
 
 // ---------------------------------------------------------------- registration glue
@@ -1038,6 +1384,8 @@ TfLiteDelegate* tflite_plugin_create_delegate(const char* const* keys, const cha
       st->options.claim_bmm = ParseBool(v);
     } else if (!strcmp(k, "claim_sdpa")) {
       st->options.claim_sdpa = ParseBool(v);
+    } else if (!strcmp(k, "claim_glue")) {
+      st->options.claim_glue = ParseBool(v);
     } else {
       snprintf(msg, sizeof(msg), "B200 delegate: unknown option '%s'", k);
       if (report_error) report_error(msg);

@@ -128,6 +128,8 @@ int b200_read_status(void* d_zero_ws, void* stream, int* status_out) {
   cudaError_t e = cudaMemcpyAsync(status_out, d_zero_ws, sizeof(int), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e != cudaSuccess) return cuda_fail(e, "b200_read_status");
+  if (*status_out == 201)
+    return fail(B200_ERR_INVALID_ARGUMENT, "a key/value cache update ran past the cache's last slot (status 201)");
   if (*status_out != 0) return fail(B200_ERR_KERNEL_TIMEOUT, "device-side wait ran out (status %d)", *status_out);
   return B200_OK;
 }

@@ -134,6 +134,9 @@ class MiniRuntime:
         L.mrt_add_custom.argtypes = L.mrt_add_composite.argtypes
         L.mrt_add_other.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
                                     ctypes.c_int]
+        L.mrt_add_node.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                   ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_void_p, ctypes.c_int, ctypes.c_char_p,
+                                   ctypes.c_int]
         L.mrt_set_io.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int,
                                  ctypes.POINTER(ctypes.c_int)]
         self.h = L.mrt_create()
@@ -175,6 +178,51 @@ class MiniRuntime:
 
     def custom(self, name, init_data, ins, out):
         return self.lib.mrt_add_custom(self.h, name.encode(), init_data, len(init_data), len(ins), self._ints(ins), out)
+
+    def node(self, builtin_code, ins, outs, params=b"", custom_name="", init_data=b""):
+        """Any builtin or custom node; `params` is the op's builtin-data struct as bytes (see the helpers below)."""
+        buf = ctypes.create_string_buffer(params, len(params)) if params else None
+        return self.lib.mrt_add_node(self.h, builtin_code, custom_name.encode(), len(ins), self._ints(ins), len(outs),
+                                     self._ints(outs), ctypes.cast(buf, ctypes.c_void_p) if buf else None, len(params),
+                                     init_data if init_data else None, len(init_data))
+
+    # ---- the builtins a decoder-only graph is made of (builtin codes: tflite/builtin_ops.h; parameter structs:
+    # tflite/core/c/builtin_op_data.h, all plain ints / bools / floats)
+    def add(self, a, b, out):
+        import struct
+        return self.node(0, [a, b], [out], struct.pack("<i?xxx", 0, False))          # TfLiteAddParams
+
+    def mul(self, a, b, out):
+        import struct
+        return self.node(18, [a, b], [out], struct.pack("<i", 0))                    # TfLiteMulParams
+
+    def gelu(self, x, out, approximate=True):
+        import struct
+        return self.node(150, [x], [out], struct.pack("<?", approximate))            # TfLiteGeluParams
+
+    def reshape(self, x, out):
+        import struct
+        shape = self.meta[out][1]
+        return self.node(22, [x], [out], struct.pack("<8ii", *(list(shape) + [0] * (8 - len(shape))), len(shape)))  # TfLiteReshapeParams
+
+    def slice(self, x, begin, size, out):
+        """begin / size: constant int32 tensors are created here."""
+        b = self.tensor(I32, (len(begin),), np.asarray(begin, np.int32))
+        s = self.tensor(I32, (len(size),), np.asarray(size, np.int32))
+        return self.node(65, [x, b, s], [out])
+
+    def concatenation(self, ins, out, axis):
+        import struct
+        return self.node(2, list(ins), [out], struct.pack("<ii", axis, 0))           # TfLiteConcatenationParams
+
+    def embedding_lookup(self, ids, table, out):
+        return self.node(7, [ids, table], [out])
+
+    def arg_max(self, x, out, axis=-1):
+        import struct
+        a = self.tensor(I32, (1,), np.asarray([axis], np.int32))
+        out_type = self.meta[out][0]
+        return self.node(56, [x, a], [out], struct.pack("<i", out_type))             # TfLiteArgMaxParams
 
     def other(self, builtin_code, ins, out):
         return self.lib.mrt_add_other(self.h, builtin_code, len(ins), self._ints(ins), out)
@@ -230,8 +278,9 @@ class MiniRuntime:
 
 
 def flex_map(values):
-    """Encodes {key: float} as a FlexBuffers map with 4-byte inline floats -- the form the SDPA
-    composite's attribute blob takes. Layout, back to front: root (offset to the map, type, width);
+    """Encodes {key: float or int} as a FlexBuffers map with 4-byte inline scalars -- the form the SDPA
+    composite's attribute blob ({"scale": float}) and the kv-cache op's initial data ({"kv_cache_max": int,
+    ...}) take. Layout, back to front: root (offset to the map, type, width);
     map = [keys vector offset][keys width][size][values...][value types]; keys vector of offsets to
     NUL-terminated strings, sorted by key."""
     import struct
@@ -257,9 +306,9 @@ def flex_map(values):
     buf += struct.pack("<I", len(keys))
     map_pos = len(buf)
     for k in keys:
-        buf += struct.pack("<f", values[k])
-    for _ in keys:
-        buf += bytes([(3 << 2) | 2])  # FLOAT, 4 bytes
+        buf += struct.pack("<i", values[k]) if isinstance(values[k], (int, np.integer)) else struct.pack("<f", values[k])
+    for k in keys:
+        buf += bytes([((1 if isinstance(values[k], (int, np.integer)) else 3) << 2) | 2])  # INT or FLOAT, 4 bytes
     while len(buf) % 4:
         buf += b"\0"
     root = len(buf)

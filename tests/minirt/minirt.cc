@@ -385,6 +385,27 @@ MRT_API int mrt_add_custom(void* h, const char* custom_name, const uint8_t* init
   return idx;
 }
 
+// Any builtin or custom node with several outputs: `params` (may be null) is the op's plain builtin-data
+// struct as bytes (TfLiteAddParams, TfLiteGeluParams, ... of tflite/core/c/builtin_op_data.h; copied),
+// `init_data` the custom initial data of a custom op (kept alive with the node).
+MRT_API int mrt_add_node(void* h, int builtin_code, const char* custom_name, int n_in, const int* ins, int n_out,
+                         const int* outs, const void* params, int params_size, const uint8_t* init_data, int init_size) {
+  Graph* g = static_cast<Graph*>(h);
+  void* data = nullptr;
+  if (params && params_size > 0) {
+    data = calloc(1, static_cast<size_t>(params_size));
+    memcpy(data, params, static_cast<size_t>(params_size));
+  }
+  const int idx = AddNode(g, builtin_code, custom_name && custom_name[0] ? custom_name : nullptr, n_in, ins, n_out, outs, data);
+  NodeRec* r = g->nodes[idx].get();
+  if (init_data && init_size > 0) {
+    r->blob.assign(init_data, init_data + init_size);
+    r->node.custom_initial_data = r->blob.data();
+    r->node.custom_initial_data_size = init_size;
+  }
+  return idx;
+}
+
 // Any other builtin (no parameters): stands for ops that stay on the CPU.
 MRT_API int mrt_add_other(void* h, int builtin_code, int n_in, const int* ins, int out) {
   return AddNode(static_cast<Graph*>(h), builtin_code, nullptr, n_in, ins, 1, &out, nullptr);

@@ -106,7 +106,9 @@ def test_support_predicate_bmm_and_sdpa(plugin_path):
     o = m.tensor(F32, (1, 1, 8, 64))
     m.composite("odml.scaled_dot_product_attention", minirt.flex_map({"scale": 0.125}), [q, k, v, mask], o)  # claimed
     o2 = m.tensor(F32, (1, 1, 8, 64))
-    m.composite("odml.rms_norm", b"", [q], o2)     # some other composite: not claimed
+    m.composite("odml.rms_norm", b"", [q], o2)     # the norm composite of a decoder graph: claimed
+    o2b = m.tensor(F32, (1, 1, 8, 64))
+    m.composite("odml.group_norm", b"", [q], o2b)  # some other composite: not claimed
     o3 = m.tensor(F32, (1, 1, 8, 64))
     m.custom("odml.scaled_dot_product_attention", b"", [q, k, v, mask], o3)  # custom-op form: claimed
     q4 = m.tensor(F32, (1, 4, 8, 64))
@@ -127,10 +129,10 @@ def test_support_predicate_bmm_and_sdpa(plugin_path):
     y8 = m.tensor(F32, (3, 5, 2, 3))
     m.batch_matmul(x8, w, y8)                      # hybrid over two batch dimensions (the reference kernel mixes up
                                                    # the rows' parameters there): not claimed
-    m.set_io([x, w2, q, k, v, mask, q4, mask4, q5, x6, x8], [y1, o, o2, o3, o4, o5, y6, y7, y8])
+    m.set_io([x, w2, q, k, v, mask, q4, mask4, q5, x6, x8], [y1, o, o2, o2b, o3, o4, o5, y6, y7, y8])
     m.apply(d)
-    assert d.claimed == 5
-    assert m.skippable_subgraphs == 1              # the one claimed STABLEHLO_COMPOSITE carries a decomposition
+    assert d.claimed == 6
+    assert m.skippable_subgraphs == 2              # the two claimed STABLEHLO_COMPOSITE nodes carry a decomposition each
     m.close()
     d.close()
 
@@ -180,6 +182,66 @@ def test_support_predicate_leaves_constant_activations_and_bad_shapes_alone(plug
 
     assert claimed(lambda m: sdpa(m, False)) == 1
     assert claimed(lambda m: sdpa(m, True)) == 0
+
+
+def test_support_predicate_decoder_glue_ops(plugin_path):
+    """The float32 ops between a decoder's projections: claimed in the forms a converter emits, left alone
+    otherwise (fused activations, run-time shapes, other axes, constant-only operands)."""
+    import struct
+
+    def claimed(build, options=None):
+        m, d = minirt.MiniRuntime(), minirt.Delegate(options)
+        build(m)
+        m.apply(d)
+        n = d.claimed
+        m.close()
+        d.close()
+        return n
+
+    def binary(m, act=0, b_shape=(1, 4, 1, 8), const_both=False):
+        a = m.tensor(F32, (1, 4, 3, 8), np.ones((1, 4, 3, 8), np.float32) if const_both else None)
+        b = m.tensor(F32, b_shape, np.ones(b_shape, np.float32) if const_both else None)
+        y = m.tensor(F32, (1, 4, 3, 8))
+        m.node(18, [a, b], [y], struct.pack("<i", act))
+        m.set_io([] if const_both else [a, b], [y])
+
+    assert claimed(binary) == 1
+    assert claimed(binary, {"claim_glue": 0}) == 0
+    assert claimed(lambda m: binary(m, act=1)) == 0                       # fused RELU
+    assert claimed(lambda m: binary(m, b_shape=(1, 4, 2, 8))) == 0        # does not broadcast
+    assert claimed(lambda m: binary(m, const_both=True)) == 0
+
+    def argmax(m, axis):
+        x = m.tensor(F32, (3, 50))
+        y = m.tensor(I32, (3,) if axis in (-1, 1) else (50,))
+        m.arg_max(x, y, axis=axis)
+        m.set_io([x], [y])
+
+    assert claimed(lambda m: argmax(m, -1)) == 1
+    assert claimed(lambda m: argmax(m, 0)) == 0
+
+    def kv(m, batch=1, dtype_pos=4):
+        pos = m.tensor(dtype_pos, (1,))
+        k = m.tensor(F32, (batch, 2, 1, 16))
+        v = m.tensor(F32, (batch, 2, 1, 16))
+        kf, vf = m.tensor(F32, (batch, 24, 1, 16)), m.tensor(F32, (batch, 24, 1, 16))
+        m.node(32, [pos, k, v], [kf, vf], custom_name="odml.update_kv_cache", init_data=minirt.flex_map({"kv_cache_max": 24}))
+        m.set_io([pos, k, v], [kf, vf])
+
+    assert claimed(kv) == 1
+    assert claimed(lambda m: kv(m, batch=2)) == 0                         # the reference op is batch 1 only
+    assert claimed(lambda m: kv(m, dtype_pos=I32)) == 0                   # positions are int64
+
+    def embedding(m, table_const=True):
+        ids = m.tensor(I32, (5,))
+        table = m.tensor(I8, (40, 16), np.ones((40, 16), np.int8) if table_const else None,
+                         channel_scales=np.full(40, 0.1, np.float32))
+        y = m.tensor(F32, (5, 16))
+        m.embedding_lookup(ids, table, y)
+        m.set_io([ids] if table_const else [ids, table], [y])
+
+    assert claimed(embedding) == 1
+    assert claimed(lambda m: embedding(m, table_const=False)) == 0
 
 
 def test_no_cuda_device_fails_loudly_and_rolls_back(plugin_path):

@@ -523,3 +523,60 @@ def test_reference_sdpa_composite_models_run_on_the_device(delegate, oracle, nam
                 for c in candidates if 1e-3 < c < 10), default=1.0)
     assert best <= 1e-4, best
     rt.close()
+
+
+# ---- a whole decoder behind the delegate ------------------------------------------------------------------------
+def _host_weights(cfg, seed):
+    from litert_b200 import decoder as dec
+
+    w = dec.make_weights(cfg, seed=seed, device="cpu")
+    out = dict(layers=[{k: v.numpy() for k, v in lw.items()} for lw in w["layers"]])
+    for k in ("embed", "embed_scales", "final_norm"):
+        out[k] = w[k].numpy()
+    return out
+
+
+@pytest.mark.parametrize("tokens_per_call", [1, 6])
+def test_gemma_shaped_graph_is_one_partition_and_matches_the_cpu_graph(oracle, tokens_per_call):
+    """The graph a converter would emit for a Gemma-shaped decoder (EMBEDDING_LOOKUP, odml.rms_norm, hybrid
+    FULLY_CONNECTED, RESHAPE, the rotary embedding out of SLICE / MUL / CONCATENATION / ADD, odml.update_kv_cache,
+    the attention composite, GELU, residual ADDs, the LM head, ARG_MAX): every node is claimed, the plan is ONE
+    delegate kernel with no CPU node, the kv caches stay on the device between invocations, and the logits follow
+    the CPU restatement of the same graph (float32 cache, as the reference's kv-cache op keeps it) step by step."""
+    from tests.minirt.decoder_graph import DecoderGraph
+
+    cfg = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=1, head_dim=64, d_ff=512, vocab=1000)
+    host = _host_weights(cfg, 77)
+    S, T = 32, tokens_per_call
+    rt, d = minirt.MiniRuntime(), minirt.Delegate()
+    g = DecoderGraph(rt, cfg, host, T, S)
+    n_nodes = rt.plan_size
+    assert rt.apply(d) == 0, rt.error
+    assert rt.partitions == 1 and rt.cpu_nodes == 0 and d.claimed == n_nodes
+    assert rt.skippable_subgraphs >= cfg["n_layers"]          # the composites' decomposition subgraphs
+    ref = oracle.DecoderRef(cfg, host, 1, S, fast=False, kv_mode=0)
+    rng = np.random.default_rng(3)
+    tokens = rng.integers(0, cfg["vocab"], 18).astype(np.int32)
+    pos, worst = 0, 0.0
+    while pos + T <= tokens.size:
+        g.feed(tokens[pos:pos + T], pos)
+        assert rt.invoke() == 0, rt.error
+        logits = rt.view(g.logits).copy()
+        picked = rt.view(g.tokens).copy()
+        for i in range(T):
+            nxt_r, lr = ref.step(tokens[pos + i:pos + i + 1], want_logits=True)
+            err = np.linalg.norm(logits[i] - lr[0]) / np.linalg.norm(lr[0])
+            worst = max(worst, err)
+            assert err <= 6e-2, (pos, i, err)
+            assert picked[i] == int(np.argmax(logits[i])), "ARG_MAX is the first index of the row's maximum"
+            top2 = np.sort(lr[0])[-2:]
+            if top2[1] - top2[0] > 4 * np.max(np.abs(logits[i] - lr[0])):
+                assert picked[i] == nxt_r[0]
+        pos += T
+    print(f"decoder graph through the delegate, {T} token(s) per call: worst relative L2 {worst:.3e}")
+    # a write past the cache's last slot is refused with an error, not executed
+    g.feed(tokens[:T], S - T + 1)
+    assert rt.invoke() != 0 and "cache" in rt.error
+    rt.close()
+    d.close()
+    ref.close()
