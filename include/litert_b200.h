@@ -342,6 +342,10 @@ B200_API int b200_rms_norm_f32(const float* d_x, const float* d_gain, float* d_y
 B200_API int b200_kv_cache_update_f32(const int64_t* d_position, const float* d_k, const float* d_v, int t,
                                       int row_elems, int max_entries, float* d_k_cache, float* d_v_cache,
                                       void* d_zero_ws, void* stream);
+/* The rotary embedding of gemma3_graph.cc:150-176 as one kernel: out = x * cos + concat(-x2, x1) * sin,
+ * x / out [tokens, heads, h], cos / sin [tokens, h] (host-prepared graph inputs, shared by the heads). */
+B200_API int b200_rope_f32(const float* d_x, const float* d_cos, const float* d_sin, float* d_out, int tokens,
+                           int heads, int h, void* stream);
 B200_API int b200_widen_i32_to_i64(const int32_t* d_in, int64_t* d_out, int n, void* stream);
 
 /* ---- Gemma-shaped decoder, one decode step per call ---------------------------

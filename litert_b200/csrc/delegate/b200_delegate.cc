@@ -43,6 +43,8 @@ struct Options {
   std::string fail_on;          // "", "init", "prepare", "invoke", "alloc": host-side fault injection
   bool buffer_handles = false;  // publish outputs as buffer handles instead of copying back in invoke
   bool claim_fc = true, claim_bmm = true, claim_sdpa = true;
+  bool fuse = true;        // merge op sequences of a decoder graph into the fused kernels (results stay within tolerance)
+  bool cuda_graph = true;  // replay a partition's launches as one CUDA graph from its third invocation on
   bool claim_glue = true;  // the float32 ops between a decoder's projections (ADD, MUL, GELU, RESHAPE, SLICE, ...)
   int min_nodes_per_partition = 1;
 };
@@ -140,7 +142,14 @@ static void ArenaFree(void*, void* p) { cudaFree(p); }
 enum class OpKind {
   kNone, kFcInt8, kFcHybrid, kFcW4, kBmmHybrid, kBmmInt8, kSdpa,
   // the ops between a decoder's projections
-  kEmbedding, kAdd, kMul, kGelu, kReshape, kSlice, kConcat, kRmsNorm, kKvCache, kArgMax
+  kEmbedding, kAdd, kMul, kGelu, kReshape, kSlice, kConcat, kRmsNorm, kKvCache, kArgMax,
+  // produced by the fusion pass over a partition's ops (never by Classify)
+  kNormQuant,      // odml.rms_norm whose result only feeds hybrid projections: normalised AND quantized once
+  kFcQuantized,    // a hybrid projection reading rows another op already quantized
+  kGateUpGeglu,    // gate and up projections as one GEMV + GELU x up + quantization for the down projection
+  kLmHeadPick,     // the vocabulary projection with ARG_MAX in its epilogue: no logits are written
+  kRope,           // SLICE / SLICE / MUL(-1) / CONCATENATION / MUL / MUL / ADD of the rotary embedding as one kernel
+  kSkipped         // a node whose work a fused op does
 };
 
 constexpr char kRmsNormName[] = "odml.rms_norm";
@@ -502,6 +511,12 @@ struct OpRecord {
   bool adj_x = false, adj_y = false, rhs_const = true, fold_lhs = false;
   BmmGeometry g;
   size_t packed_stride = 0;         // bytes between the packed matrices of a batched RHS
+  // every tensor the node reads and writes (graph numbering, constants included): the fusion pass's view
+  std::vector<int> all_in, all_out;
+  // fused ops
+  int rows_from = -1;               // kFcQuantized: index (in the partition) of the op that holds its quantized rows
+  DeviceMem q_tiled, q_scales, q_zps, tmp_f32;  // kNormQuant / kGateUpGeglu: the quantized rows they produce
+  int heads = 0;
   // glue ops
   std::vector<int> ins;             // operand tensors (graph numbering; -1 = a constant held in const_a / const_b)
   int y2 = -1;                      // second output (kv cache)
@@ -595,9 +610,219 @@ class DelegateKernel {
       OpRecord& op = *ops_.back();
       op.kind = kind;
       op.node_index = node_index;
+      for (int j = 0; j < node->inputs->size; ++j) op.all_in.push_back(node->inputs->data[j]);
+      for (int j = 0; j < node->outputs->size; ++j) op.all_out.push_back(node->outputs->data[j]);
       TF_LITE_ENSURE_STATUS(BuildOp(ctx, node, reg, &op));
     }
+    if (st_->options.fuse) TF_LITE_ENSURE_STATUS(FuseOps(ctx));
     CUDA_OK(ctx, cudaStreamSynchronize(st_->stream));  // staging buffers below go out of scope
+    return kTfLiteOk;
+  }
+
+  // ---- fusion pass -------------------------------------------------------------------------------------
+  // Rewrites op sequences a converter emits for a decoder layer into the fused kernels, wherever every
+  // intermediate tensor is consumed inside the pattern and nowhere else (not by another node, not as a
+  // partition output). Unfused, the graph is still executed op by op: fusion only removes launches and
+  // float32 round trips.
+  int Producer(int tensor) const {
+    for (size_t i = 0; i < ops_.size(); ++i)
+      for (int t : ops_[i]->all_out)
+        if (t == tensor && ops_[i]->kind != OpKind::kSkipped) return static_cast<int>(i);
+    return -1;
+  }
+  std::vector<int> Consumers(int tensor) const {
+    std::vector<int> c;
+    for (size_t i = 0; i < ops_.size(); ++i)
+      for (int t : ops_[i]->all_in)
+        if (t == tensor) {
+          c.push_back(static_cast<int>(i));
+          break;
+        }
+    return c;
+  }
+  bool IsPartitionOutput(int tensor) const {
+    for (int t : outputs_)
+      if (t == tensor) return true;
+    return false;
+  }
+  // the only consumer of `tensor`, or -1 (also when it leaves the partition)
+  int OnlyConsumer(int tensor) const {
+    if (IsPartitionOutput(tensor)) return -1;
+    const std::vector<int> c = Consumers(tensor);
+    return c.size() == 1 ? c[0] : -1;
+  }
+  bool AllocRows(TfLiteContext* ctx, OpRecord* op, int m, int k) {
+    const size_t per = static_cast<size_t>(std::max(m, 256)) * sizeof(float);
+    if (op->q_tiled.ensure(b200_tiled_rows_bytes(m, k)) && op->q_scales.ensure(per) && op->q_zps.ensure(per)) return true;
+    TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed (quantized rows)");
+    return false;
+  }
+
+  TfLiteStatus FuseOps(TfLiteContext* ctx) {
+    const TfLiteTensor* T = ctx->tensors;
+    const int n_ops = static_cast<int>(ops_.size());
+    // (1) rotary embedding: ADD(MUL(x, cos), MUL(CONCAT(MUL(SLICE_hi(x), -1), SLICE_lo(x)), sin))
+    for (int i = 0; i < n_ops; ++i) {
+      OpRecord& add = *ops_[i];
+      if (add.kind != OpKind::kAdd || add.ins[0] < 0 || add.ins[1] < 0) continue;
+      const int ma = Producer(add.ins[0]), mb = Producer(add.ins[1]);
+      if (ma < 0 || mb < 0 || ops_[ma]->kind != OpKind::kMul || ops_[mb]->kind != OpKind::kMul) continue;
+      OpRecord *xc = ops_[ma].get(), *rs = ops_[mb].get();
+      if (OnlyConsumer(xc->y) != i || OnlyConsumer(rs->y) != i || xc->ins[0] < 0 || xc->ins[1] < 0 || rs->ins[0] < 0 || rs->ins[1] < 0)
+        continue;
+      // which MUL is x * cos and which rot * sin: the latter's first operand comes from a CONCATENATION
+      auto is_concat = [&](int t) { const int p = Producer(t); return p >= 0 && ops_[p]->kind == OpKind::kConcat; };
+      if (is_concat(xc->ins[0])) std::swap(xc, rs);
+      if (!is_concat(rs->ins[0])) continue;
+      const int x = xc->ins[0], cos_t = xc->ins[1], sin_t = rs->ins[1];
+      OpRecord& cat = *ops_[Producer(rs->ins[0])];
+      if (cat.ins.size() != 2 || cat.axis != 3 || OnlyConsumer(cat.y) != Producer(rs->y)) continue;
+      const int neg_i = Producer(cat.ins[0]), lo_i = Producer(cat.ins[1]);
+      if (neg_i < 0 || lo_i < 0 || ops_[neg_i]->kind != OpKind::kMul || ops_[lo_i]->kind != OpKind::kSlice) continue;
+      OpRecord &neg = *ops_[neg_i], &lo = *ops_[lo_i];
+      if (neg.ins[0] < 0 || neg.ins[1] >= 0 || neg.const_b.bytes != sizeof(float)) continue;  // MUL by a constant scalar
+      const TfLiteTensor& scalar = T[neg.all_in[1]];
+      if (!IsConst(scalar) || scalar.data.f[0] != -1.0f) continue;
+      const int hi_i = Producer(neg.ins[0]);
+      if (hi_i < 0 || ops_[hi_i]->kind != OpKind::kSlice) continue;
+      OpRecord& hi = *ops_[hi_i];
+      const TfLiteTensor& xt = T[x];
+      if (xt.dims->size != 4 || hi.ins[0] != x || lo.ins[0] != x) continue;
+      const int tokens = xt.dims->data[0] * xt.dims->data[1], heads = xt.dims->data[2], h = xt.dims->data[3];
+      if (h % 2 || lo.begin[3] != 0 || hi.begin[3] != h / 2 || lo.dims_o[3] != h / 2 || hi.dims_o[3] != h / 2) continue;
+      if (lo.begin[0] || lo.begin[1] || lo.begin[2] || hi.begin[0] || hi.begin[1] || hi.begin[2]) continue;
+      if (lo.dims_o[2] != heads || hi.dims_o[2] != heads || lo.dims_o[1] != xt.dims->data[1]) continue;
+      if (OnlyConsumer(hi.y) != neg_i || OnlyConsumer(neg.y) != Producer(rs->ins[0]) || OnlyConsumer(lo.y) != Producer(rs->ins[0])) continue;
+      const TfLiteTensor &ct = T[cos_t], &st = T[sin_t];
+      if (NumElements(ct) != static_cast<int64_t>(tokens) * h || NumElements(st) != NumElements(ct) || IsConst(ct) || IsConst(st)) continue;
+      for (OpRecord* dead : {xc, rs, &cat, &neg, &lo, &hi}) dead->kind = OpKind::kSkipped;
+      add.kind = OpKind::kRope;
+      add.ins = {x, cos_t, sin_t};
+      add.rows = tokens;
+      add.heads = heads;
+      add.width = h;
+    }
+    // (2) odml.rms_norm feeding only hybrid projections: normalise and quantize once for all of them
+    for (int i = 0; i < n_ops; ++i) {
+      OpRecord& norm = *ops_[i];
+      if (norm.kind != OpKind::kRmsNorm || !norm.const_a.ptr || norm.width > 12288 || IsPartitionOutput(norm.y)) continue;
+      const std::vector<int> users = Consumers(norm.y);
+      bool ok = !users.empty();
+      for (int u : users) ok = ok && ops_[u]->kind == OpKind::kFcHybrid && ops_[u]->asymmetric && ops_[u]->x == norm.y && ops_[u]->kdim == norm.width;
+      if (!ok) continue;
+      if (!AllocRows(ctx, &norm, norm.rows, norm.width)) return kTfLiteDelegateError;
+      norm.kind = OpKind::kNormQuant;
+      for (int u : users) {
+        ops_[u]->kind = OpKind::kFcQuantized;
+        ops_[u]->rows_from = i;
+        ops_[u]->m = norm.rows;
+      }
+    }
+    // (3) gate / up projections + GELU x up + the down projection's quantization
+    for (int i = 0; i < n_ops; ++i) {
+      OpRecord& mul = *ops_[i];
+      if (mul.kind != OpKind::kMul || mul.ins[0] < 0 || mul.ins[1] < 0) continue;
+      int gelu_i = Producer(mul.ins[0]), up_i = Producer(mul.ins[1]);
+      if (gelu_i >= 0 && ops_[gelu_i]->kind != OpKind::kGelu) std::swap(gelu_i, up_i);
+      if (gelu_i < 0 || up_i < 0 || ops_[gelu_i]->kind != OpKind::kGelu || !ops_[gelu_i]->approximate) continue;
+      const int gate_i = Producer(ops_[gelu_i]->ins[0]);
+      if (gate_i < 0) continue;
+      OpRecord &gate = *ops_[gate_i], &up = *ops_[up_i], &gelu = *ops_[gelu_i];
+      if (gate.kind != OpKind::kFcQuantized || up.kind != OpKind::kFcQuantized || gate.rows_from != up.rows_from) continue;
+      if (gate.n != up.n || gate.kdim != up.kdim || !gate.per_channel || !up.per_channel || gate.bias.ptr || up.bias.ptr ||
+          gate.activation || up.activation)
+        continue;
+      const int down_i = OnlyConsumer(mul.y);
+      if (down_i < 0 || ops_[down_i]->kind != OpKind::kFcHybrid || !ops_[down_i]->asymmetric || ops_[down_i]->kdim != gate.n) continue;
+      if (OnlyConsumer(gate.y) != gelu_i || OnlyConsumer(gelu.y) != i || OnlyConsumer(up.y) != i) continue;
+      for (int d = 0; d < 4; ++d)
+        if (mul.dims_a[d] != mul.dims_b[d]) gelu_i = -1;  // a broadcasting MUL is something else
+      if (gelu_i < 0) continue;
+      // one packed matrix [2 f, k]: the gate's rows, then the up projection's
+      const TfLiteTensor &wg = T[gate.all_in[1]], &wu = T[up.all_in[1]];
+      const int f = gate.n, k = gate.kdim, m = gate.m;
+      {
+        std::vector<int8_t> both(static_cast<size_t>(2) * f * k);
+        memcpy(both.data(), wg.data.int8, static_cast<size_t>(f) * k);
+        memcpy(both.data() + static_cast<size_t>(f) * k, wu.data.int8, static_cast<size_t>(f) * k);
+        TF_LITE_ENSURE_STATUS(PackInt8(ctx, both.data(), 2 * f, k, false, &mul));
+      }
+      std::vector<float> scales(static_cast<size_t>(2) * f);
+      const auto *qg = Affine(wg), *qu = Affine(wu);
+      for (int c = 0; c < f; ++c) {
+        scales[c] = qg->scale->data[c];
+        scales[f + c] = qu->scale->data[c];
+      }
+      TF_LITE_ENSURE_STATUS(Upload(ctx, scales, &mul.w_scales));
+      if (!mul.tmp_f32.ensure(sizeof(float) * static_cast<size_t>(m) * 2 * f) || !AllocRows(ctx, &mul, m, f)) {
+        TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed (gate / up buffer)");
+        return kTfLiteDelegateError;
+      }
+      CUDA_OK(ctx, cudaStreamSynchronize(st_->stream));
+      mul.kind = OpKind::kGateUpGeglu;
+      mul.rows_from = gate.rows_from;
+      mul.m = m;
+      mul.n = 2 * f;
+      mul.kdim = k;
+      mul.per_channel = true;
+      gate.packed.reset();
+      up.packed.reset();
+      gate.kind = up.kind = gelu.kind = OpKind::kSkipped;
+      ops_[down_i]->kind = OpKind::kFcQuantized;
+      ops_[down_i]->rows_from = i;
+      ops_[down_i]->m = m;
+    }
+    // (2b) the residual ADD in front of such a norm moves into it: h += delta in place, then normalise and
+    // quantize. The sum tensor becomes another name for h's buffer, which no one else may still need.
+    for (int i = 0; i < n_ops; ++i) {
+      OpRecord& norm = *ops_[i];
+      if (norm.kind != OpKind::kNormQuant) continue;
+      const int add_i = Producer(norm.ins[0]);
+      if (add_i < 0 || ops_[add_i]->kind != OpKind::kAdd) continue;
+      OpRecord& add = *ops_[add_i];
+      if (add.ins[0] < 0 || add.ins[1] < 0 || IsPartitionOutput(add.y)) continue;
+      bool same = true;
+      for (int d = 0; d < 4; ++d) same = same && add.dims_a[d] == add.dims_o[d] && add.dims_b[d] == add.dims_o[d];
+      if (!same) continue;
+      // the residual stream is the operand that dies here; prefer the first, as the graph writes ADD(h, delta)
+      int h = add.ins[0], delta = add.ins[1];
+      if (OnlyConsumer(h) != add_i) std::swap(h, delta);
+      if (OnlyConsumer(h) != add_i || persistent_.count(h) || IsConst(T[h])) continue;
+      bool is_input = false;
+      for (int t : inputs_) is_input = is_input || t == h;
+      if (is_input) continue;  // a partition input keeps its host meaning: do not overwrite its device copy's role
+      inplace_alias_[add.y] = h;
+      norm.ins = {h, delta};
+      add.kind = OpKind::kSkipped;
+    }
+    // (4) a projection read only by ARG_MAX (the LM head under greedy sampling): the pick moves into its epilogue
+    for (int i = 0; i < n_ops; ++i) {
+      OpRecord& am = *ops_[i];
+      if (am.kind != OpKind::kArgMax || am.rows > 16) continue;
+      const int fc_i = Producer(am.ins[0]);
+      if (fc_i < 0 || ops_[fc_i]->kind != OpKind::kFcQuantized || OnlyConsumer(ops_[fc_i]->y) != i) continue;
+      OpRecord& fc = *ops_[fc_i];
+      if (fc.bias.ptr || fc.activation || !fc.per_channel || fc.n != am.width || fc.m != am.rows) continue;
+      const size_t ws = b200_lm_head_workspace_bytes(am.rows) + sizeof(int32_t) * am.rows;
+      if (!am.ws_small.ensure(ws)) {
+        TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed");
+        return kTfLiteDelegateError;
+      }
+      am.kind = OpKind::kLmHeadPick;
+      am.rows_from = fc.rows_from;
+      am.m = fc.m;
+      am.n = fc.n;
+      am.kdim = fc.kdim;
+      am.packed.ptr = fc.packed.ptr;  // the projection's constants move over
+      am.packed.bytes = fc.packed.bytes;
+      fc.packed.ptr = nullptr;
+      fc.packed.bytes = 0;
+      std::swap(am.row_sums.ptr, fc.row_sums.ptr);
+      std::swap(am.row_sums.bytes, fc.row_sums.bytes);
+      std::swap(am.w_scales.ptr, fc.w_scales.ptr);
+      std::swap(am.w_scales.bytes, fc.w_scales.bytes);
+      fc.kind = OpKind::kSkipped;
+    }
     return kTfLiteOk;
   }
 
@@ -607,9 +832,17 @@ class DelegateKernel {
       return kTfLiteDelegateError;
     }
     CUDA_OK(ctx, cudaSetDevice(st_->options.device));
+    if (graph_exec_) {  // a new plan moves tensors: the recorded launches hold the old addresses
+      cudaGraphExecDestroy(graph_exec_);
+      graph_exec_ = nullptr;
+    }
+    invocations_ = 0;
     // tensors living on the device for this partition: every op operand that is not a constant
     slot_of_.clear();
     persistent_.clear();
+    alias_ = inplace_alias_;  // sums computed in place by a fused norm share the residual stream's buffer
+    for (auto& opp : ops_)  // a RESHAPE's result is its operand's bytes: same device buffer, nothing to run
+      if (opp->kind == OpKind::kReshape) alias_[opp->y] = opp->ins[0];
     for (auto& opp : ops_)  // (before any touch: a later op's operand may be an earlier op's persistent output)
       if (opp->kind == OpKind::kKvCache) {
         persistent_[opp->y] = opp->k_cache.ptr;
@@ -619,6 +852,7 @@ class DelegateKernel {
     const int num_ops = static_cast<int>(ops_.size());
     auto touch = [&](int tensor, int op_index) {
       if (tensor < 0) return;
+      tensor = Canonical(tensor);
       const TfLiteTensor& t = ctx->tensors[tensor];
       if (IsConst(t) || persistent_.count(tensor)) return;
       auto it = slot_of_.find(tensor);
@@ -651,8 +885,17 @@ class DelegateKernel {
           bmm_packed = std::max(bmm_packed, mats * b200_packed_w8_bytes(op.n, op.kdim));
           bmm_rs = std::max(bmm_rs, mats * sizeof(int32_t) * op.n);
         }
+      } else if (op.kind == OpKind::kSkipped) {
+        continue;
+      } else if (op.kind == OpKind::kFcQuantized) {
+        touch(op.y, i);
+      } else if (op.kind == OpKind::kLmHeadPick) {
+        touch(op.y, i);
+      } else if (op.kind == OpKind::kGateUpGeglu) {
+        continue;  // reads another op's quantized rows, writes its own: no arena tensor
       } else if (op.kind >= OpKind::kEmbedding) {
         for (int t : op.ins) touch(t, i);
+        if (op.kind == OpKind::kNormQuant) continue;  // its float32 result is never materialised
         if (op.kind == OpKind::kKvCache) {
           // the op's outputs ARE its persistent caches: never arena tensors
           persistent_[op.y] = op.k_cache.ptr;
@@ -670,11 +913,11 @@ class DelegateKernel {
     }
     // partition inputs arrive before the first op and outputs are read after the last one
     for (int t : inputs_) {
-      auto it = slot_of_.find(t);
+      auto it = slot_of_.find(Canonical(t));
       if (it != slot_of_.end()) req[it->second].first_use = 0;
     }
     for (int t : outputs_) {
-      auto it = slot_of_.find(t);
+      auto it = slot_of_.find(Canonical(t));
       if (it != slot_of_.end()) req[it->second].last_use = num_ops - 1;
     }
     if (!arena_.Commit(req, num_ops)) {
@@ -705,7 +948,36 @@ class DelegateKernel {
       if (!tensor.data.raw) continue;
       CUDA_OK(ctx, cudaMemcpyAsync(arena_.Resolve(it->second), tensor.data.raw, tensor.bytes, cudaMemcpyHostToDevice, s));
     }
-    for (auto& opp : ops_) TF_LITE_ENSURE_STATUS(Launch(ctx, *opp));
+    // The partition's launches: eagerly the first time (one-time kernel set-up happens here), recorded into
+    // a CUDA graph the second time, replayed from then on: shapes are static and every device address is
+    // fixed once the arena is planned, so a partition of hundreds of small kernels costs one launch call.
+    ++invocations_;
+    if (graph_exec_) {
+      CUDA_OK(ctx, cudaGraphLaunch(graph_exec_, s));
+    } else if (st_->options.cuda_graph && !graph_failed_ && invocations_ == 2 && ops_.size() > 1) {
+      cudaGraph_t g = nullptr;
+      TfLiteStatus launched = kTfLiteOk;
+      if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+        for (auto& opp : ops_)
+          if ((launched = Launch(ctx, *opp)) != kTfLiteOk) break;
+        const cudaError_t e = cudaStreamEndCapture(s, &g);
+        if (launched == kTfLiteOk && e == cudaSuccess && g && cudaGraphInstantiate(&graph_exec_, g, 0) == cudaSuccess) {
+          CUDA_OK(ctx, cudaGraphLaunch(graph_exec_, s));
+        } else {
+          graph_exec_ = nullptr;
+          graph_failed_ = true;  // an op that cannot be recorded: plain launches from now on
+          cudaGetLastError();
+          for (auto& opp : ops_) TF_LITE_ENSURE_STATUS(Launch(ctx, *opp));
+        }
+        if (g) cudaGraphDestroy(g);
+      } else {
+        graph_failed_ = true;
+        cudaGetLastError();
+        for (auto& opp : ops_) TF_LITE_ENSURE_STATUS(Launch(ctx, *opp));
+      }
+    } else {
+      for (auto& opp : ops_) TF_LITE_ENSURE_STATUS(Launch(ctx, *opp));
+    }
     for (int t : outputs_) {
       void* dev = Dev(t);
       if (!dev) continue;
@@ -731,7 +1003,18 @@ class DelegateKernel {
   }
 
  private:
+  // the tensor whose buffer `tensor` shares (chains of RESHAPEs resolved)
+  int Canonical(int tensor) const {
+    for (int hops = 0; hops < 64; ++hops) {
+      auto it = alias_.find(tensor);
+      if (it == alias_.end()) break;
+      tensor = it->second;
+    }
+    return tensor;
+  }
+
   void* Dev(int tensor) {
+    tensor = Canonical(tensor);
     auto pit = persistent_.find(tensor);
     if (pit != persistent_.end()) return pit->second;
     auto it = slot_of_.find(tensor);
@@ -1119,7 +1402,8 @@ class DelegateKernel {
                                             static_cast<size_t>(NumElements(ctx->tensors[op.y])), op.approximate, s));
         return kTfLiteOk;
       case OpKind::kReshape:
-        CUDA_OK(ctx, cudaMemcpyAsync(Dev(op.y), Dev(op.ins[0]), ctx->tensors[op.y].bytes, cudaMemcpyDeviceToDevice, s));
+        if (Dev(op.y) != Dev(op.ins[0]))
+          CUDA_OK(ctx, cudaMemcpyAsync(Dev(op.y), Dev(op.ins[0]), ctx->tensors[op.y].bytes, cudaMemcpyDeviceToDevice, s));
         return kTfLiteOk;
       case OpKind::kSlice: {
         const int zero[4] = {0, 0, 0, 0};
@@ -1163,6 +1447,59 @@ class DelegateKernel {
                                                        op.max_entries, static_cast<float*>(op.k_cache.ptr),
                                                        static_cast<float*>(op.v_cache.ptr), st_->zero_ws.ptr, s));
         return kTfLiteOk;
+      case OpKind::kSkipped:
+        return kTfLiteOk;
+      case OpKind::kRope:
+        B200_EW_OR_RETURN(ctx, b200_rope_f32(static_cast<const float*>(Dev(op.ins[0])), static_cast<const float*>(Dev(op.ins[1])),
+                                            static_cast<const float*>(Dev(op.ins[2])), static_cast<float*>(Dev(op.y)), op.rows,
+                                            op.heads, op.width, s));
+        return kTfLiteOk;
+      case OpKind::kNormQuant:
+        // (with a second operand: the residual ADD in front of the norm, h += delta in place)
+        B200_GLUE_OR_RETURN(ctx, b200_add_rmsnorm_quantize(static_cast<float*>(Dev(op.ins[0])),
+                                                          op.ins.size() > 1 ? static_cast<const float*>(Dev(op.ins[1])) : nullptr,
+                                                          static_cast<const float*>(op.const_a.ptr), op.rows, op.width, op.eps,
+                                                          static_cast<int8_t*>(op.q_tiled.ptr), static_cast<float*>(op.q_scales.ptr),
+                                                          static_cast<int32_t*>(op.q_zps.ptr), s));
+        return kTfLiteOk;
+      case OpKind::kFcQuantized: {
+        const OpRecord& src = *ops_[op.rows_from];
+        B200_GLUE_OR_RETURN(ctx, b200_fc_hybrid_quantized(static_cast<const int8_t*>(src.q_tiled.ptr),
+                                                         static_cast<const float*>(src.q_scales.ptr),
+                                                         static_cast<const int32_t*>(src.q_zps.ptr), op.m, op.kdim, op.packed.ptr,
+                                                         op.n, static_cast<const int32_t*>(op.row_sums.ptr),
+                                                         static_cast<const float*>(op.w_scales.ptr), op.per_channel ? 1 : 0,
+                                                         static_cast<const float*>(op.bias.ptr), op.activation,
+                                                         static_cast<float*>(Dev(op.y)), st_->zero_ws.ptr, s));
+        return kTfLiteOk;
+      }
+      case OpKind::kLmHeadPick: {
+        const OpRecord& src = *ops_[op.rows_from];
+        uint8_t* ws = static_cast<uint8_t*>(op.ws_small.ptr);
+        const size_t ws_bytes = b200_lm_head_workspace_bytes(op.m);
+        int32_t* out32 = op.out_i64 ? reinterpret_cast<int32_t*>(ws + ws_bytes) : static_cast<int32_t*>(Dev(op.y));
+        B200_GLUE_OR_RETURN(ctx, b200_lm_head_greedy(static_cast<const int8_t*>(src.q_tiled.ptr),
+                                                    static_cast<const float*>(src.q_scales.ptr),
+                                                    static_cast<const int32_t*>(src.q_zps.ptr), op.m, op.kdim, op.packed.ptr, op.n,
+                                                    static_cast<const int32_t*>(op.row_sums.ptr),
+                                                    static_cast<const float*>(op.w_scales.ptr), 0.0f, nullptr, out32, ws, ws_bytes,
+                                                    st_->zero_ws.ptr, s));
+        if (op.out_i64) B200_EW_OR_RETURN(ctx, b200_widen_i32_to_i64(out32, static_cast<int64_t*>(Dev(op.y)), op.m, s));
+        return kTfLiteOk;
+      }
+      case OpKind::kGateUpGeglu: {
+        const OpRecord& src = *ops_[op.rows_from];
+        B200_GLUE_OR_RETURN(ctx, b200_fc_hybrid_quantized(static_cast<const int8_t*>(src.q_tiled.ptr),
+                                                         static_cast<const float*>(src.q_scales.ptr),
+                                                         static_cast<const int32_t*>(src.q_zps.ptr), op.m, op.kdim, op.packed.ptr,
+                                                         op.n, static_cast<const int32_t*>(op.row_sums.ptr),
+                                                         static_cast<const float*>(op.w_scales.ptr), 1, nullptr, 0,
+                                                         static_cast<float*>(op.tmp_f32.ptr), st_->zero_ws.ptr, s));
+        B200_GLUE_OR_RETURN(ctx, b200_geglu_quantize(static_cast<const float*>(op.tmp_f32.ptr), op.m, op.n / 2,
+                                                    static_cast<int8_t*>(op.q_tiled.ptr), static_cast<float*>(op.q_scales.ptr),
+                                                    static_cast<int32_t*>(op.q_zps.ptr), s));
+        return kTfLiteOk;
+      }
       case OpKind::kSdpa:
         if (op.T == 1) {
           B200_OK_OR_RETURN(ctx, b200_sdpa_decode(Dev(op.q), Dev(op.k), Dev(op.v), nullptr, nullptr, nullptr,
@@ -1248,7 +1585,17 @@ class DelegateKernel {
   std::vector<int> inputs_, outputs_;
   std::vector<std::unique_ptr<OpRecord>> ops_;
   std::unordered_map<int, int> slot_of_;
+  std::unordered_map<int, int> inplace_alias_; // residual sums a fused norm computes in place -> the stream's tensor
+  std::unordered_map<int, int> alias_;         // RESHAPE results -> the tensor whose buffer they share
   std::unordered_map<int, void*> persistent_;  // tensors that live outside the arena (the kv-cache op's outputs)
+  cudaGraphExec_t graph_exec_ = nullptr;
+  bool graph_failed_ = false;
+  long long invocations_ = 0;
+
+ public:
+  ~DelegateKernel() {
+    if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+  }
 };
 
 // ---------------------------------------------------------------- registration glue
@@ -1384,6 +1731,10 @@ TfLiteDelegate* tflite_plugin_create_delegate(const char* const* keys, const cha
       st->options.claim_bmm = ParseBool(v);
     } else if (!strcmp(k, "claim_sdpa")) {
       st->options.claim_sdpa = ParseBool(v);
+    } else if (!strcmp(k, "fuse")) {
+      st->options.fuse = ParseBool(v);
+    } else if (!strcmp(k, "cuda_graph")) {
+      st->options.cuda_graph = ParseBool(v);
     } else if (!strcmp(k, "claim_glue")) {
       st->options.claim_glue = ParseBool(v);
     } else {

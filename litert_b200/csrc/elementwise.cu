@@ -116,6 +116,22 @@ __global__ void kv_cache_update_f32_kernel(const long long* __restrict__ positio
   }
 }
 
+// The rotary embedding as the graph spells it (tensor/examples/gemma3/gemma3_graph.cc:150-176):
+// out = x * cos + concat(-x2, x1) * sin over the last dimension, cos / sin [tokens, h] shared by the heads.
+// One kernel for the seven nodes, same roundings (every product and the sum on their own).
+__global__ void rope_f32_kernel(const float* __restrict__ x, const float* __restrict__ cs, const float* __restrict__ sn,
+                                float* __restrict__ out, int heads, int h, size_t total) {
+  const int half = h / 2;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int d = (int)(i % h);
+    const size_t token = i / ((size_t)heads * h);
+    const float xv = x[i];
+    const float rot = d < half ? __fmul_rn(x[i + half], -1.0f) : x[i - half];
+    const float c = cs[token * h + d], s = sn[token * h + d];
+    out[i] = __fadd_rn(__fmul_rn(xv, c), __fmul_rn(rot, s));
+  }
+}
+
 __global__ void widen_i32_to_i64_kernel(const int32_t* __restrict__ in, long long* __restrict__ out, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = in[i];
@@ -213,6 +229,15 @@ int b200_kv_cache_update_f32(const int64_t* d_position, const float* d_k, const 
       reinterpret_cast<const long long*>(d_position), d_k, d_v, t, row_elems, max_entries, d_k_cache, d_v_cache,
       static_cast<int*>(d_zero_ws));
   return ecuda("b200_kv_cache_update_f32");
+}
+
+int b200_rope_f32(const float* d_x, const float* d_cos, const float* d_sin, float* d_out, int tokens, int heads, int h,
+                  void* stream) {
+  if (!d_x || !d_cos || !d_sin || !d_out || tokens <= 0 || heads <= 0 || h <= 0 || h % 2)
+    return efail(B200_ERR_INVALID_ARGUMENT, "b200_rope_f32: bad argument");
+  const size_t total = (size_t)tokens * heads * h;
+  rope_f32_kernel<<<grid_for(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(d_x, d_cos, d_sin, d_out, heads, h, total);
+  return ecuda("b200_rope_f32");
 }
 
 int b200_widen_i32_to_i64(const int32_t* d_in, int64_t* d_out, int n, void* stream) {

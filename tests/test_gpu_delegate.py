@@ -574,6 +574,25 @@ def test_gemma_shaped_graph_is_one_partition_and_matches_the_cpu_graph(oracle, t
                 assert picked[i] == nxt_r[0]
         pos += T
     print(f"decoder graph through the delegate, {T} token(s) per call: worst relative L2 {worst:.3e}")
+    # the same graph with the fusion pass off (every node its own kernels) and without the logits as an output
+    # (the LM head then picks the token in its epilogue): same tokens where the margin is clear
+    for options, logits_out in (({"fuse": 0}, True), ({}, False)):
+        rt2, d2 = minirt.MiniRuntime(), minirt.Delegate(options)
+        g2 = DecoderGraph(rt2, cfg, host, T, S, want_logits=logits_out)
+        assert rt2.apply(d2) == 0 and rt2.partitions == 1 and rt2.cpu_nodes == 0
+        ref2 = oracle.DecoderRef(cfg, host, 1, S, fast=False, kv_mode=0)
+        for p0 in range(0, (tokens.size // T) * T, T):
+            g2.feed(tokens[p0:p0 + T], p0)
+            assert rt2.invoke() == 0, rt2.error
+            picked = rt2.view(g2.tokens).copy()
+            for i in range(T):
+                nxt_r, lr = ref2.step(tokens[p0 + i:p0 + i + 1], want_logits=True)
+                top2 = np.sort(lr[0])[-2:]
+                if top2[1] - top2[0] > 0.1 * (lr[0].max() - lr[0].min()):
+                    assert picked[i] == nxt_r[0], (options, p0, i)
+        rt2.close()
+        d2.close()
+        ref2.close()
     # a write past the cache's last slot is refused with an error, not executed
     g.feed(tokens[:T], S - T + 1)
     assert rt.invoke() != 0 and "cache" in rt.error
