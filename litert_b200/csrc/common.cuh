@@ -24,12 +24,13 @@ constexpr int kTileBytes = kTileN * kTileK8;  // 16 KiB
 constexpr int kRowGroups = kTileN / 8;        // 16
 constexpr int kChunks8 = kTileK8 / 16;        // 8 chunks of 16 bytes along K
 
-// 4-bit tiles: kTileN rows x 256 reduction elements (8 sub-blocks of 32), the
-// same 16 KiB of nibbles, followed by kTileN x 8 fp16 scales (2 KiB).
+// 4-bit tiles: kTileN rows x 256 reduction elements as four sub-tiles of 64 (the K extent of one
+// fp16 operand tile), each 4 KiB of nibbles followed by its 2 x kTileN fp16 block scales: 18 KiB.
 constexpr int kTileK4 = 256;
 constexpr int kSubBlocks4 = kTileK4 / 32;                     // 8
-constexpr int kTile4ScaleBytes = kTileN * kSubBlocks4 * 2;    // 2 KiB
-constexpr int kTile4Bytes = kTileBytes + kTile4ScaleBytes;    // 18 KiB
+constexpr int kTile4SubWordBytes = kTileN * 64 / 2;           // 4 KiB of nibbles per sub-tile
+constexpr int kTile4SubBytes = kTile4SubWordBytes + kTileN * 2 * 2;  // + 512 B of scales
+constexpr int kTile4Bytes = 4 * kTile4SubBytes;               // 18 KiB
 
 // Status word values written by kernels (0 = ok).
 enum : int {

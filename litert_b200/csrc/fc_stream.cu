@@ -20,7 +20,6 @@
 //    exact and order-independent, so results are deterministic and bit-equal
 //    to a serial sum.
 #include <cstdlib>
-#include <type_traits>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -33,10 +32,10 @@ constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 
-template <int MT, bool W4>
+template <int MT>
 struct StageLayout {
-  static constexpr int kWBytes = W4 ? kTile4Bytes : kTileBytes;
-  static constexpr int kQBytes = (W4 ? 2 : 1) * MT * 1024;  // MT groups x 128 (or 256) k bytes
+  static constexpr int kWBytes = kTileBytes;
+  static constexpr int kQBytes = MT * 1024;  // MT groups x 128 k bytes
   static constexpr int kStageBytes = kWBytes + kQBytes;
   static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
   static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kStages * 8 + 64;
@@ -117,38 +116,10 @@ __device__ __forceinline__ void epilogue_requant(const FcParams& p, int nt, int 
   }
 }
 
-template <int MT>
-__device__ __forceinline__ void epilogue_w4(const FcParams& p, int nt, int m_base, const float (&acc)[MT][4],
-                                            int warp, int lane) {
-  const int g = lane >> 2, t4 = lane & 3;
-  float* y = static_cast<float*>(p.y);
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int n = nt * kTileN + warp * 16 + g + half * 8;
-    if (n >= p.n) continue;
-    const float kf = p.kfsum[n];
-    const float bias = p.bias_f32 ? p.bias_f32[n] : 0.0f;
-#pragma unroll
-    for (int j = 0; j < MT; ++j) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int m = m_base + j * 8 + t4 * 2 + e;
-        if (m >= p.m) continue;
-        // tflite/kernels/fully_connected.cc:1077-1082: subtract zp*kfsum, scale, add bias
-        float out = acc[j][half * 2 + e];
-        out = __fsub_rn(out, __fmul_rn((float)p.in_zps[m], kf));
-        out = __fmul_rn(out, p.in_scales[m]);
-        if (p.bias_f32) out = __fadd_rn(out, bias);
-        y[(size_t)m * p.n + n] = out;
-      }
-    }
-  }
-}
-
-template <int MT, int EPI, bool W4>
+template <int MT, int EPI>
 __global__ void __launch_bounds__(kThreads, 1) fc_stream_kernel(const FcParams p, const int m_base) {
-  using L = StageLayout<MT, W4>;
-  using AccT = typename std::conditional<W4, float, int>::type;
+  using L = StageLayout<MT>;
+  using AccT = int;
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
   uint64_t* empty_bar = full_bar + L::kStages;
@@ -190,17 +161,8 @@ __global__ void __launch_bounds__(kThreads, 1) fc_stream_kernel(const FcParams p
         mbar_arrive_expect_tx(&full_bar[s], L::kStageBytes);
         bulk_g2s(dst, p.w_packed + (size_t)t * L::kWBytes, L::kWBytes, &full_bar[s]);
         const int kt = (int)(t % p.k_tiles);
-        if (W4) {
-          // 256 reduction elements = two 128-wide activation tiles
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const size_t off = (((size_t)(2 * kt + h) * m_groups_alloc) + mg_base) * 1024;
-            bulk_g2s(dst + L::kWBytes + h * MT * 1024, p.q_tiled + off, MT * 1024, &full_bar[s]);
-          }
-        } else {
-          const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
-          bulk_g2s(dst + L::kWBytes, p.q_tiled + off, MT * 1024, &full_bar[s]);
-        }
+        const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
+        bulk_g2s(dst + L::kWBytes, p.q_tiled + off, MT * 1024, &full_bar[s]);
       }
     }
     return;
@@ -221,7 +183,7 @@ __global__ void __launch_bounds__(kThreads, 1) fc_stream_kernel(const FcParams p
     mbar_wait_bounded(&full_bar[s], ph, abort_flag, p.status, kStatusWaitTimeoutFull);
     const uint8_t* sw = smem + (size_t)s * L::kStageBytes;
     const uint8_t* sq = sw + L::kWBytes;
-    if constexpr (!W4) {
+    {
       // weight rows 16*warp .. +15 = row groups 2*warp, 2*warp+1; thread (g, t) reads word t of the
       // 16-byte chunk `c` of row g, which the swizzled layout keeps at chunk position c ^ g
       const int g = lane >> 2, t4 = lane & 3;
@@ -240,35 +202,6 @@ __global__ void __launch_bounds__(kThreads, 1) fc_stream_kernel(const FcParams p
           const uint32_t b0 = qg[j * 256 + c0];
           const uint32_t b1 = qg[j * 256 + c1];
           mma_s8(reinterpret_cast<int(&)[4]>(acc[j]), a0, a1, a2, a3, b0, b1);
-        }
-      }
-    } else {
-      const uint32_t* wa = reinterpret_cast<const uint32_t*>(sw + (size_t)(2 * warp) * kSubBlocks4 * 128) + lane;
-      const __half* sc = reinterpret_cast<const __half*>(sw + kTileBytes);
-      const int g = lane >> 2;
-#pragma unroll
-      for (int blk = 0; blk < kSubBlocks4; ++blk) {
-        const uint32_t w0 = wa[blk * 32];
-        const uint32_t w1 = wa[(kSubBlocks4 + blk) * 32];
-        const uint32_t a0 = (w0 << 4) & 0xF0F0F0F0u, a2 = w0 & 0xF0F0F0F0u;
-        const uint32_t a1 = (w1 << 4) & 0xF0F0F0F0u, a3 = w1 & 0xF0F0F0F0u;
-        const float s0 = __half2float(sc[blk * kTileN + warp * 16 + g]);
-        const float s1 = __half2float(sc[blk * kTileN + warp * 16 + g + 8]);
-        // activation tile h = blk / 4 (128 k each), chunks 2*(blk%4), +1
-        const uint32_t* qa = reinterpret_cast<const uint32_t*>(sq + (blk >> 2) * MT * 1024) + g * 32 + (lane & 3);
-        const int kc = 2 * (blk & 3);
-        const int c0 = (kc ^ g) * 4, c1 = ((kc + 1) ^ g) * 4;  // swizzled chunk positions of row g
-#pragma unroll
-        for (int j = 0; j < MT; ++j) {
-          int d[4] = {0, 0, 0, 0};
-          const uint32_t b0 = qa[j * 256 + c0];
-          const uint32_t b1 = qa[j * 256 + c1];
-          mma_s8(d, a0, a1, a2, a3, b0, b1);
-          // operands carry 16x the 4-bit value; the shift is exact
-          acc[j][0] = __fadd_rn(acc[j][0], __fmul_rn((float)(d[0] >> 4), s0));
-          acc[j][1] = __fadd_rn(acc[j][1], __fmul_rn((float)(d[1] >> 4), s0));
-          acc[j][2] = __fadd_rn(acc[j][2], __fmul_rn((float)(d[2] >> 4), s1));
-          acc[j][3] = __fadd_rn(acc[j][3], __fmul_rn((float)(d[3] >> 4), s1));
         }
       }
     }
@@ -314,9 +247,7 @@ __global__ void __launch_bounds__(kThreads, 1) fc_stream_kernel(const FcParams p
         named_barrier(1, kConsumerThreads);  // flags->last may be rewritten next time
       }
       if (run_epilogue) {
-        if constexpr (W4) {
-          epilogue_w4<MT>(p, nt, m_base, acc, warp, lane);
-        } else if constexpr (EPI == kEpiHybridF32) {
+        if constexpr (EPI == kEpiHybridF32) {
           epilogue_hybrid<MT>(p, nt, m_base, acc, warp, lane);
         } else {
           epilogue_requant<MT>(p, nt, m_base, acc, warp, lane, EPI == kEpiRawI32);
@@ -330,11 +261,11 @@ __global__ void __launch_bounds__(kThreads, 1) fc_stream_kernel(const FcParams p
   }
 }
 
-template <int MT, int EPI, bool W4>
+template <int MT, int EPI>
 cudaError_t launch_one(const FcParams& p, int m_base, cudaStream_t s) {
-  using L = StageLayout<MT, W4>;
+  using L = StageLayout<MT>;
   static bool configured[64] = {false};
-  auto kernel = fc_stream_kernel<MT, EPI, W4>;
+  auto kernel = fc_stream_kernel<MT, EPI>;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
@@ -362,31 +293,28 @@ cudaError_t launch_one(const FcParams& p, int m_base, cudaStream_t s) {
   return cudaGetLastError();
 }
 
-template <int EPI, bool W4>
+template <int EPI>
 cudaError_t launch_by_mt(const FcParams& p, int m_base, int mt, cudaStream_t s) {
   switch (mt) {
-    case 1: return launch_one<1, EPI, W4>(p, m_base, s);
-    case 2: return launch_one<2, EPI, W4>(p, m_base, s);
-    case 4: return launch_one<4, EPI, W4>(p, m_base, s);
-    default: return launch_one<8, EPI, W4>(p, m_base, s);
+    case 1: return launch_one<1, EPI>(p, m_base, s);
+    case 2: return launch_one<2, EPI>(p, m_base, s);
+    case 4: return launch_one<4, EPI>(p, m_base, s);
+    default: return launch_one<8, EPI>(p, m_base, s);
   }
 }
 
-template <bool W4>
 cudaError_t launch_chunks(const FcParams& p, int epi, cudaStream_t s) {
   // up to 64 activation rows per pass over the weights
   for (int m_base = 0; m_base < p.m; m_base += 64) {
     const int rows = p.m - m_base < 64 ? p.m - m_base : 64;
     const int mt = p.m > 64 ? 8 : m_tiles_for(rows);
     cudaError_t e;
-    if (W4) {
-      e = launch_by_mt<kEpiHybridF32, true>(p, m_base, mt, s);
-    } else if (epi == kEpiHybridF32) {
-      e = launch_by_mt<kEpiHybridF32, false>(p, m_base, mt, s);
+    if (epi == kEpiHybridF32) {
+      e = launch_by_mt<kEpiHybridF32>(p, m_base, mt, s);
     } else if (epi == kEpiRequantI8) {
-      e = launch_by_mt<kEpiRequantI8, false>(p, m_base, mt, s);
+      e = launch_by_mt<kEpiRequantI8>(p, m_base, mt, s);
     } else {
-      e = launch_by_mt<kEpiRawI32, false>(p, m_base, mt, s);
+      e = launch_by_mt<kEpiRawI32>(p, m_base, mt, s);
     }
     if (e != cudaSuccess) return e;
   }
@@ -409,7 +337,6 @@ int device_sm_count() {
 }
 
 
-cudaError_t launch_fc_i8(const FcParams& p, FcEpilogue epi, cudaStream_t s) { return launch_chunks<false>(p, epi, s); }
-cudaError_t launch_fc_w4(const FcParams& p, cudaStream_t s) { return launch_chunks<true>(p, kEpiHybridF32, s); }
+cudaError_t launch_fc_i8(const FcParams& p, FcEpilogue epi, cudaStream_t s) { return launch_chunks(p, epi, s); }
 
 }  // namespace b200

@@ -27,7 +27,8 @@ cudaError_t launch_pack_w8(const int8_t* w, int n, int k, uint8_t* packed, int32
 cudaError_t launch_pack_w4(const uint8_t* w4, const void* scales_f16, int n, int k, int blocksize, uint8_t* packed,
                            float* kfsum, cudaStream_t s);
 cudaError_t launch_quantize_rows(const float* x, int m, int k, int k_pad, int m_alloc, int asymmetric,
-                                 int8_t* q_tiled, int8_t* q_rowmajor, float* scales, int32_t* zps, cudaStream_t s);
+                                 int8_t* q_tiled, int8_t* q_rowmajor, float* scales, int32_t* zps, cudaStream_t s,
+                                 void* h_tiled = nullptr);
 cudaError_t launch_retile_x8(const int8_t* x, int m, int k, int k_pad, int m_alloc, int8_t* q_tiled,
                              int32_t* x_sums, cudaStream_t s);
 
@@ -115,8 +116,13 @@ cudaError_t launch_fc_i8_umma(const FcParams& p, FcEpilogue epi, cudaStream_t s)
 int umma_rows_per_pass(int m);
 // Whether FcParams::prologue can be used for these sizes (the tcgen05 kernels only).
 bool fc_prologue_supported(int m, int k);
-// Blockwise 4-bit weights, float out.
+// Blockwise 4-bit weights, float out: the tcgen05 path (any m; q_tiled holds the quantized rows as
+// fp16 in the tiled layout, w4_rows_per_pass(m) rows per pass) ...
 cudaError_t launch_fc_w4(const FcParams& p, cudaStream_t s);
+int w4_rows_per_pass(int m);
+// ... and the one-launch path for up to 16 rows, which quantizes the float rows `x` itself.
+bool w4_gemv_supported(int m, int k);
+cudaError_t launch_fc_w4_gemv(const FcParams& p, const float* x, cudaStream_t s);
 
 constexpr int kZeroWsSlots = 320;            // counters; >= 2 x CTAs per launch
 constexpr int kAccSlots = 160;               // mma.sync path: one accumulator slot per CTA

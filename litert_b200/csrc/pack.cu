@@ -61,11 +61,17 @@ __global__ void row_sums_kernel(const int8_t* __restrict__ w, int n, int k, int3
 // ---- int4 blockwise weights -------------------------------------------------
 // Source: n rows of k2/2 bytes (k2 = k rounded up to even), element 2i in the
 // low nibble of byte i (tflite/kernels/fully_connected.cc:1053-1067); fp16
-// scales [n, k/blocksize]. Destination tile: [row group][sub-block of 32][row]
-// [4 words]; word t of a row holds, in byte j, element 4t+j of the sub-block in
-// the low nibble and element 16+4t+j in the high nibble, so that one shift and
-// two masks turn a word into the two int8 MMA registers (values x16). The
-// tile's fp16 scales follow as [sub-block][row].
+// scales [n, k/blocksize]. Destination: tiles of kTileN rows x 256 reduction
+// elements, 18 KiB each, in (n tile, k tile) order. A tile is four sub-tiles of
+// 64 reduction elements (the K extent of one 128-byte-swizzled fp16 operand
+// tile), each [2 blocks of 32][128 rows][4 words] of nibbles (one 16-byte load
+// per row and block, conflict-free across a warp of consecutive rows) followed
+// by [2 blocks][128 rows] fp16 scales. Word j (0..7) of a row holds its elements 8j .. 8j+7 as
+// offset-binary nibbles (value + 8): element 2p in bits 4p .. 4p+3 and element
+// 2p+1 in bits 16+4p .. 16+4p+3, so that `(word >> 4p) & 0x000F000F` is a pair
+// of neighbouring elements, one per 16-bit half. A scale is stored once per
+// block of 32 whatever the tensor's block size (a multiple of 32): blocks of 64
+// or more repeat theirs.
 __device__ __forceinline__ uint32_t nibble_at(const uint8_t* __restrict__ w4, size_t row_bytes, int row, int kk,
                                               int n, int k) {
   if (row >= n || kk >= k) return 0u;
@@ -77,43 +83,44 @@ __global__ void pack_w4_kernel(const uint8_t* __restrict__ w4, const __half* __r
                                int blocksize, int n_tiles, int k_tiles, uint8_t* __restrict__ packed) {
   const size_t row_bytes = ((size_t)k + 1) / 2;
   const int num_blocks = k / blocksize;
-  // words of nibbles
-  const long long words_per_tile = kTileBytes / 4;
-  const long long total_words = (long long)n_tiles * k_tiles * words_per_tile;
   const long long stride = (long long)gridDim.x * blockDim.x;
+  // words of nibbles: 4 sub-tiles x 8 words x 128 rows per tile
+  const long long total_words = (long long)n_tiles * k_tiles * (kTileBytes / 4);
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_words; idx += stride) {
-    const int t = (int)(idx & 3);
-    const int r = (int)((idx >> 2) & 7);
-    const int blk = (int)((idx >> 5) & 7);
-    const int rg = (int)((idx >> 8) & 15);
+    const int r = (int)(idx & 127);
+    const int j = (int)((idx >> 7) & 7);
+    const int sub = (int)((idx >> 10) & 3);
     const long long tile = idx >> 12;
     const int kt = (int)(tile % k_tiles);
     const int nt = (int)(tile / k_tiles);
-    const int row = nt * kTileN + rg * 8 + r;
-    const int k0 = kt * kTileK4 + blk * 32;
+    const int row = nt * kTileN + r;
+    const int k0 = kt * kTileK4 + sub * 64 + j * 8;
     uint32_t word = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t lo = nibble_at(w4, row_bytes, row, k0 + 4 * t + j, n, k);
-      const uint32_t hi = nibble_at(w4, row_bytes, row, k0 + 16 + 4 * t + j, n, k);
-      word |= (lo | (hi << 4)) << (8 * j);
+    for (int e = 0; e < 8; ++e) {
+      // two's complement nibble -> offset binary; padding (rows >= n, k >= the tensor's) holds the value 0
+      const uint32_t u = (row < n && k0 + e < k) ? (nibble_at(w4, row_bytes, row, k0 + e, n, k) ^ 8u) : 8u;
+      word |= u << ((e & 1) * 16 + (e >> 1) * 4);
     }
-    *reinterpret_cast<uint32_t*>(packed + (size_t)tile * kTile4Bytes + (size_t)(idx & 4095) * 4) = word;
+    *reinterpret_cast<uint32_t*>(packed + (size_t)tile * kTile4Bytes + (size_t)sub * kTile4SubBytes +
+                                 (size_t)(((j >> 2) * 128 + r) * 4 + (j & 3)) * 4) = word;
   }
-  // scales
+  // scales: 4 sub-tiles x 2 blocks x 128 rows per tile
   const long long scales_per_tile = kTileN * kSubBlocks4;
   const long long total_scales = (long long)n_tiles * k_tiles * scales_per_tile;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total_scales; idx += stride) {
-    const int row_in = (int)(idx % kTileN);
-    const int blk = (int)((idx / kTileN) % kSubBlocks4);
-    const long long tile = idx / scales_per_tile;
+    const int r = (int)(idx & 127);
+    const int blk = (int)((idx >> 7) & 1);
+    const int sub = (int)((idx >> 8) & 3);
+    const long long tile = idx >> 10;
     const int kt = (int)(tile % k_tiles);
     const int nt = (int)(tile / k_tiles);
-    const int row = nt * kTileN + row_in;
-    const int k0 = kt * kTileK4 + blk * 32;
+    const int row = nt * kTileN + r;
+    const int k0 = kt * kTileK4 + sub * 64 + blk * 32;
     __half s = __float2half(0.0f);
     if (row < n && k0 < k && k0 / blocksize < num_blocks) s = scales[(size_t)row * num_blocks + k0 / blocksize];
-    reinterpret_cast<__half*>(packed + (size_t)tile * kTile4Bytes + kTileBytes)[blk * kTileN + row_in] = s;
+    reinterpret_cast<__half*>(packed + (size_t)tile * kTile4Bytes + (size_t)sub * kTile4SubBytes + kTile4SubWordBytes)
+        [blk * 128 + r] = s;
   }
 }
 
@@ -152,7 +159,8 @@ __global__ void __launch_bounds__(1024) quantize_rows_kernel(const float* __rest
                                                             int8_t* __restrict__ q_tiled,
                                                             int8_t* __restrict__ q_rowmajor,
                                                             float* __restrict__ scales,
-                                                            int32_t* __restrict__ zero_points) {
+                                                            int32_t* __restrict__ zero_points,
+                                                            __half* __restrict__ h_tiled) {
   __shared__ float2 s_mm[32];
   __shared__ float s_inv;
   __shared__ int s_zp;
@@ -212,6 +220,15 @@ __global__ void __launch_bounds__(1024) quantize_rows_kernel(const float* __rest
     for (int b = 0; b < 4; ++b)
       if (k4 + b < k) word |= quant(v[b]) << (8 * b);
     if (q_tiled) *reinterpret_cast<uint32_t*>(q_tiled + q_tiled_offset(row, k4, m_alloc)) = word;
+    if (h_tiled) {
+      // the same integers as fp16 (exact), for the kind::f16 MMA of the 4-bit path
+      const __half2 lo = __floats2half2_rn((float)(int8_t)(word & 0xFF), (float)(int8_t)((word >> 8) & 0xFF));
+      const __half2 hi = __floats2half2_rn((float)(int8_t)((word >> 16) & 0xFF), (float)(int8_t)(word >> 24));
+      uint2 v;
+      v.x = *reinterpret_cast<const uint32_t*>(&lo);
+      v.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(h_tiled) + h_tiled_offset(row, k4, m_alloc)) = v;
+    }
     if (q_rowmajor) {
 #pragma unroll
       for (int b = 0; b < 4; ++b)
@@ -275,12 +292,12 @@ cudaError_t launch_pack_w4(const uint8_t* w4, const void* scales_f16, int n, int
 
 cudaError_t launch_quantize_rows(const float* x, int m, int k, int k_pad, int m_alloc, int asymmetric,
                                  int8_t* q_tiled, int8_t* q_rowmajor, float* scales, int32_t* zps,
-                                 cudaStream_t s) {
+                                 cudaStream_t s, void* h_tiled) {
   if (m <= 0) return cudaSuccess;
   // few long rows (decode): one large CTA per row hides more latency; many rows: more CTAs per SM
   const int threads = (m <= 32 && k >= 2048) ? 1024 : 256;
   return launch_chained(quantize_rows_kernel, dim3(m), dim3(threads), 0, s, x, m, k, k_pad, m_alloc, asymmetric, q_tiled,
-                        q_rowmajor, scales, zps);
+                        q_rowmajor, scales, zps, static_cast<__half*>(h_tiled));
 }
 
 cudaError_t launch_retile_x8(const int8_t* x, int m, int k, int k_pad, int m_alloc, int8_t* q_tiled,

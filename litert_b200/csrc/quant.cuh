@@ -13,6 +13,12 @@ __device__ __forceinline__ size_t q_tiled_offset(int m, int kk, int m_alloc) {
   return ((size_t)kt * (m_alloc / 8) + (m / 8)) * 1024 + swz_chunk_offset(m % 8, c) + b;
 }
 
+// The same rows as fp16 (operands of the kind::f16 MMA): k tiles of 64 elements, 128-byte rows.
+__device__ __forceinline__ size_t h_tiled_offset(int m, int kk, int m_alloc) {
+  const int kt = kk / 64, c = (kk % 64) / 8, b = kk % 8;
+  return ((size_t)kt * (m_alloc / 8) + (m / 8)) * 1024 + swz_chunk_offset(m % 8, c) + b * 2;
+}
+
 template <typename T, typename Op>
 __device__ __forceinline__ T block_reduce(T v, Op op, T identity, T* scratch) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -118,8 +118,8 @@ int b200_clear_status(void* d_zero_ws, void* stream) {
 
 size_t b200_fc_scratch_bytes(int m, int k) {
   if (m <= 0 || k <= 0) return 0;
-  // sized for either weight format: 4-bit tiles are 256 wide
-  return carve_scratch(nullptr, m, 2 * b200::tiles_k4(k)).bytes;
+  // sized for either weight format: the 4-bit path keeps the quantized rows as fp16, in tiles 256 wide
+  return carve_scratch(nullptr, m, 4 * b200::tiles_k4(k)).bytes;
 }
 
 int b200_read_status(void* d_zero_ws, void* stream, int* status_out) {
@@ -277,25 +277,32 @@ int b200_fc_w4(const float* d_x, int m, int k, const void* d_w4_packed, int n, i
   int rc = check_fc_common("b200_fc_w4", d_x, m, k, d_w4_packed, n, d_y, d_zero_ws, d_scratch, scratch_bytes);
   if (rc) return rc;
   if (!d_kfsum) return fail(B200_ERR_INVALID_ARGUMENT, "b200_fc_w4: kfsum is null");
-  if (blocksize != 32) return fail(B200_ERR_UNSUPPORTED, "b200_fc_w4: blocksize %d (only 32 is built)", blocksize);
+  if (blocksize <= 0 || blocksize % 32 != 0 || k % blocksize != 0)
+    return fail(B200_ERR_UNSUPPORTED, "b200_fc_w4: blocksize %d must be a multiple of 32 dividing k=%d", blocksize, k);
   if (m == 0) return B200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int k_tiles4 = b200::tiles_k4(k);
-  Scratch sc = carve_scratch(d_scratch, m, 2 * k_tiles4);
-  const int m_alloc = b200::m_alloc_for(m);
-  cudaError_t e = b200::launch_quantize_rows(d_x, m, k, k_tiles4 * 256, m_alloc, 1, sc.q_tiled, nullptr, sc.scales,
-                                             sc.zps, s);
-  if (e != cudaSuccess) return cuda_fail(e, "b200_fc_w4 (quantize)");
   b200::FcParams p;
   memset(&p, 0, sizeof(p));
   p.w_packed = static_cast<const uint8_t*>(d_w4_packed);
-  p.q_tiled = sc.q_tiled;
   p.m = m; p.n = n; p.k = k;
-  p.n_tiles = b200::tiles_n(n); p.k_tiles = k_tiles4; p.m_alloc = m_alloc;
-  p.in_scales = sc.scales; p.in_zps = sc.zps;
+  p.n_tiles = b200::tiles_n(n); p.k_tiles = k_tiles4;
   p.kfsum = d_kfsum; p.bias_f32 = d_bias;
   p.y = d_y;
   fill_ws(p, d_zero_ws);
+  if (b200::w4_gemv_supported(m, k)) {
+    // decode-sized: one launch, rows quantized inside the kernel
+    cudaError_t e = b200::launch_fc_w4_gemv(p, d_x, s);
+    return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_fc_w4");
+  }
+  Scratch sc = carve_scratch(d_scratch, m, 4 * k_tiles4);  // fp16 rows: twice the bytes of the int8 ones
+  const int m_alloc = b200::m_alloc_for(m);
+  cudaError_t e = b200::launch_quantize_rows(d_x, m, k, k_tiles4 * 256, m_alloc, 1, nullptr, nullptr, sc.scales, sc.zps,
+                                             s, sc.q_tiled);
+  if (e != cudaSuccess) return cuda_fail(e, "b200_fc_w4 (quantize)");
+  p.q_tiled = sc.q_tiled;
+  p.m_alloc = m_alloc;
+  p.in_scales = sc.scales; p.in_zps = sc.zps;
   e = b200::launch_fc_w4(p, s);
   return e == cudaSuccess ? B200_OK : cuda_fail(e, "b200_fc_w4");
 }

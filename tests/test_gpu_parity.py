@@ -280,6 +280,18 @@ def test_fc_w4_config3(ops, oracle, ws, m):
     n_check = 16384 if m == 1 else 2048
     want = oracle.fc_blockwise4(c["x"], c["w4"][:n_check], c["scales"][:n_check], c["blocksize"])
     assert rel_err(y[:, :n_check], want) <= 1e-3
+    # up to 8 rows the block sums are exact integers, as in the reference; only the order of the float additions differs
+    assert rel_err(y[:, :n_check], want) <= 2e-6
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 130, 96), (2, 257, 320), (2, 1024, 4096), (5, 300, 2048), (8, 512, 1024), (3, 16384, 256)])
+def test_fc_w4_decode_sized_batches_have_exact_block_sums(ops, oracle, ws, m, n, k):
+    c = workloads.config3(m, n, k, seed=7 * m + n + k)
+    x = (c["x"] + 1.5).astype(np.float32)
+    bias = np.random.default_rng(3).standard_normal(n).astype(np.float32)
+    wp = ops.PackedInt4Weights(dev(c["w4"]), dev(c["scales"]), 32)
+    y = ops.fully_connected_blockwise4(dev(x), wp, dev(bias), ws=ws).cpu().numpy()
+    assert rel_err(y, oracle.fc_blockwise4(x, c["w4"], c["scales"], 32, bias)) <= 2e-6
 
 
 def test_fc_w4_config3_m512(ops, oracle, ws):
@@ -305,6 +317,23 @@ def test_fc_w4_ragged_shapes(ops, oracle, ws, m, n, k):
     y = ops.fully_connected_blockwise4(dev(c["x"]), wp, dev(bias), ws=ws).cpu().numpy()
     want = oracle.fc_blockwise4(c["x"], c["w4"], c["scales"], 32, bias)
     np.testing.assert_allclose(y, want, rtol=1e-3, atol=1e-3 * np.abs(want).max())
+
+
+@pytest.mark.parametrize("m,n,k,blocksize", [(4, 256, 4096, 32), (40, 384, 1024, 64), (100, 200, 512, 128),
+                                             (300, 256, 768, 256), (16, 1024, 2048, 2048), (513, 130, 320, 32)])
+def test_fc_w4_row_passes_block_sizes_and_split_reductions(ops, oracle, ws, m, n, k, blocksize):
+    """Every rows-per-pass variant (16 .. 256 and several passes), block sizes beyond 32 (one scale per
+    block, whatever its length), and shapes with so few output tiles that the reduction is cut across
+    SMs and merged through the scratch slots; inputs far from zero, so that the zero-point term counts."""
+    c = workloads.config3(m, n, k, blocksize=blocksize, seed=m + n + k)
+    x = (c["x"] * 0.25 + 3.0).astype(np.float32)
+    bias = np.random.default_rng(2).standard_normal(n).astype(np.float32)
+    wp = ops.PackedInt4Weights(dev(c["w4"]), dev(c["scales"]), blocksize)
+    y = ops.fully_connected_blockwise4(dev(x), wp, dev(bias), ws=ws).cpu().numpy()
+    y2 = ops.fully_connected_blockwise4(dev(x), wp, dev(bias), ws=ws).cpu().numpy()
+    assert np.array_equal(y, y2)  # the merge order is fixed: no run-to-run differences
+    want = oracle.fc_blockwise4(x, c["w4"], c["scales"], blocksize, bias)
+    assert rel_err(y, want) <= 1e-3
 
 
 def _kfsum(w, scales_f16):
