@@ -104,16 +104,20 @@ __device__ __forceinline__ int32_t hybrid_dot(const FcParams& p, int32_t total, 
 
 // Value of one output element from its exact int32 dot product: the float's bits (hybrid), the
 // int32 (raw) or the requantized int8 (sign-extended).
-template <int EPI>
+// PLAIN (see plain_epilogue): no fused activation and the integer zero-point term, as straight-line code.
+// An epilogue warp is alone, or nearly, on its scheduler and pays every branch's latency in full: with
+// the activation switch and the zero-point form tested per output, 128 x 256 outputs took 20 us; hoisted
+// out of the loops, 3.6 us (measured on B200).
+template <int EPI, bool PLAIN = false>
 __device__ __forceinline__ int32_t compute_output(const FcParams& p, int32_t total, int32_t rs, float ws, float bias_f,
                                                   int32_t base_i, int32_t mult, int32_t shift, float in_scale,
                                                   int32_t in_aux) {
   if constexpr (EPI == kEpiHybridF32 || EPI == kEpiHybridPick) {
-    const int32_t dot = hybrid_dot(p, total, rs, in_aux);  // in_aux: the row's zero point
+    const int32_t dot = PLAIN ? total - rs * in_aux : hybrid_dot(p, total, rs, in_aux);  // in_aux: the row's zero point
     // reference order: scale = in_scale * w_scale; out = bias + dot * scale (no fused multiply-add)
     const float scale = __fmul_rn(in_scale, ws);
     float out = __fadd_rn(bias_f, __fmul_rn((float)dot, scale));
-    out = apply_activation(out, p.activation);
+    if constexpr (!PLAIN) out = apply_activation(out, p.activation);
     return __float_as_int(out);
   } else {
     const int32_t t = total + base_i + p.filter_offset * in_aux;  // in_aux: the row's sum
@@ -124,6 +128,13 @@ __device__ __forceinline__ int32_t compute_output(const FcParams& p, int32_t tot
       return max(p.act_min, min(p.act_max, v));
     }
   }
+}
+
+// Whether the PLAIN form of compute_output applies to this launch (uniform over the grid).
+template <int EPI>
+__device__ __forceinline__ bool plain_epilogue(const FcParams& p) {
+  if constexpr (EPI == kEpiHybridF32 || EPI == kEpiHybridPick) return p.activation == 0 && !p.float_offset;
+  return EPI == kEpiRawI32;
 }
 
 // Epilogue for one output element; `total` is the exact int32 dot product.
@@ -368,6 +379,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
       tc_fence_after();
 
       const bool partial = seg_tiles != p.k_tiles;
+      const bool plain = plain_epilogue<EPI>(p);
       if (!partial) {
 #pragma unroll 1
         for (int c = 0; c < NB / 16; ++c) {
@@ -390,13 +402,20 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_umma_kernel(const FcParams
                 sc[j] = sh->in_scale[c * 16 + j];
                 ax[j] = sh->in_aux[c * 16 + j];
               }
+              if (plain) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int32_t v = compute_output<EPI>(p, r[j], rs, wsc, bias_f, base_i, mult, shift, sc[j], ax[j]);
-                if constexpr (kElem == 4) {
-                  reinterpret_cast<int32_t*>(st)[j * kTileN + row_in_tile] = v;
-                } else {
-                  reinterpret_cast<int8_t*>(st)[j * kTileN + row_in_tile] = (int8_t)v;
+                for (int j = 0; j < 16; ++j)
+                  reinterpret_cast<int32_t*>(st)[j * kTileN + row_in_tile] =
+                      compute_output<EPI, true>(p, r[j], rs, wsc, bias_f, base_i, mult, shift, sc[j], ax[j]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const int32_t v = compute_output<EPI>(p, r[j], rs, wsc, bias_f, base_i, mult, shift, sc[j], ax[j]);
+                  if constexpr (kElem == 4) {
+                    reinterpret_cast<int32_t*>(st)[j * kTileN + row_in_tile] = v;
+                  } else {
+                    reinterpret_cast<int8_t*>(st)[j * kTileN + row_in_tile] = (int8_t)v;
+                  }
                 }
               }
               named_barrier(2, kEpiThreads);  // the block is complete (and the other buffer's readers are done)
@@ -789,22 +808,24 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
 
 // ---- prefill-sized variant ------------------------------------------------------------------------
 // 256 activation rows per pass, whole work units per CTA, persistent CTAs: a unit is (n tile, pass of
-// 256 rows) and a CTA takes units blockIdx.x, blockIdx.x + gridDim.x, ... One 16 KiB weight tile +
-// the 32 KiB activation tile per stage; the two 256-column accumulators alternate, so the epilogue of
-// a unit runs under the MMAs of the CTA's next unit. The epilogue is the expensive part (128 x 256
-// outputs per unit, ~10 instructions each): eight warps share it, two per TMEM lane quarter, and the
-// outputs leave through shared-memory staging blocks as whole row segments (see fc_umma_kernel).
-// Measured, config 2 at M = 512: 86 us one unit per CTA -> 68 persistent -> 63 row parameters
-// preloaded -> 43 with eight epilogue warps (34 with the epilogue left out).
-// (TILES = 2, two weight tiles of consecutive n tiles per activation tile, is written into the
-// kernel but not instantiated: with four epilogue warps it measured slower, 73 us, since a unit
-// then owns both accumulators and nothing overlaps; it has not been run with eight.)
-template <int TILES>
+// 256 rows, k range) and a CTA takes units blockIdx.x, blockIdx.x + gridDim.x, ... One 16 KiB weight
+// tile + the 32 KiB activation tile per stage; the two 256-column accumulators alternate, so the
+// epilogue of a unit runs under the MMAs of the CTA's next unit. Eight epilogue warps, two per TMEM
+// lane quarter, each pair splitting the unit's activation rows. 4-byte outputs leave straight from
+// the registers (for one activation row a warp holds 32 consecutive output channels: one full
+// 128-byte line per store instruction); int8 outputs go through shared-memory staging blocks and
+// leave as whole 128-byte row segments.
+// With few units and a long reduction (the down projection of a prompt pass: 16 n tiles x 4 passes,
+// 128 k tiles) the reduction is cut into `ksplit` ranges: every unit parks its raw int32 accumulator
+// in a scratch slot, adds one to the (n tile, pass) counter, and whoever completes the count sums the
+// slots and runs the epilogue. Integer sums: the result does not depend on the order.
+// Measured on B200, config 2 at M = 512: 86 us one unit per CTA -> 68 persistent -> 63 row parameters
+// preloaded -> 43 with eight epilogue warps -> 35 with the per-output branches hoisted (plain_epilogue).
 struct PrefillLayout {
   static constexpr int kNB = 256;
   static constexpr int kQBytes = kNB * kTileK8;                      // 32 KiB
-  static constexpr int kStageBytes = TILES * kTileBytes + kQBytes;
-  static constexpr int kStages = 206 * 1024 / kStageBytes - (TILES == 2 ? 0 : 0);
+  static constexpr int kStageBytes = kTileBytes + kQBytes;
+  static constexpr int kStages = 206 * 1024 / kStageBytes;
   static constexpr int kEpiWarps = 8;                                 // two per TMEM lane quarter
   static constexpr int kThreads = 64 + 32 * kEpiWarps;
   static constexpr int kOutStageBytes = 2 * 2 * 16 * kTileN * 4;      // two blocks per half of the epilogue warps
@@ -814,9 +835,23 @@ struct PrefillLayout {
   static_assert(kSmemBytes <= kMaxDynamicSmem, "prefill kernel: shared memory over the per-CTA limit");
 };
 
-template <int EPI, int TILES>
-__global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_kernel(const FcParams p, const int n_units, const int passes) {
-  using L = PrefillLayout<TILES>;
+struct PrefillUnit {
+  int nt, pass, kt_begin, kt_end, tile_id;
+};
+__device__ __forceinline__ PrefillUnit prefill_unit(const FcParams& p, int u, int ksplit) {
+  PrefillUnit w;
+  const int ks = u % ksplit;
+  w.tile_id = u / ksplit;
+  w.pass = w.tile_id / p.n_tiles;
+  w.nt = w.tile_id % p.n_tiles;
+  w.kt_begin = (int)((long long)p.k_tiles * ks / ksplit);
+  w.kt_end = (int)((long long)p.k_tiles * (ks + 1) / ksplit);
+  return w;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(PrefillLayout::kThreads, 1) fc_prefill_kernel(const FcParams p, const int units, const int ksplit) {
+  using L = PrefillLayout;
   constexpr int NB = L::kNB;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
@@ -838,6 +873,7 @@ __global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_
       mbar_init(&acc_empty[a], L::kEpiWarps);  // one arrival per epilogue warp
     }
     sh->abort_flag = 0;
+    sh->last = 0;
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&sh->tmem_base, L::kTmemCols);
@@ -845,11 +881,7 @@ __global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
-  const int units = n_units * passes;
   const int m_groups_alloc = p.m_alloc / 8;
-  // accumulator set of the CTA's i-th unit, and how often that set has been used before
-  auto acc_of = [](uint32_t i) { return TILES == 2 ? 0u : (i & 1u); };
-  auto use_of = [](uint32_t i) { return TILES == 2 ? i : (i >> 1); };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -858,21 +890,17 @@ __global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_
       pdl_wait();
       uint32_t it = 0;
       for (int u = blockIdx.x; u < units; u += gridDim.x) {
-        const int pass = u / n_units, idx = u % n_units;
-        const int nt0 = idx * TILES;
-        const int tiles = (TILES == 2 && nt0 + 1 < p.n_tiles) ? 2 : 1;
-        const int mg_base = pass * (NB / 8);
-        for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
+        const PrefillUnit w = prefill_unit(p, u, ksplit);
+        const int mg_base = w.pass * (NB / 8);
+        for (int kt = w.kt_begin; kt < w.kt_end; ++kt, ++it) {
           const int s = it % L::kStages;
           const uint32_t ph = (it / L::kStages) & 1u;
           mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, p.status, kStatusWaitTimeoutEmpty);
           uint8_t* dst = smem + (size_t)s * L::kStageBytes;
-          mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(tiles * kTileBytes + L::kQBytes));
-          for (int j = 0; j < tiles; ++j)
-            bulk_g2s_hint(dst + j * kTileBytes, p.w_packed + ((size_t)(nt0 + j) * p.k_tiles + kt) * kTileBytes, kTileBytes,
-                          &full_bar[s], stream_policy);
+          mbar_arrive_expect_tx(&full_bar[s], (uint32_t)L::kStageBytes);
+          bulk_g2s_hint(dst, p.w_packed + ((size_t)w.nt * p.k_tiles + kt) * kTileBytes, kTileBytes, &full_bar[s], stream_policy);
           const size_t off = (((size_t)kt * m_groups_alloc) + mg_base) * 1024;
-          bulk_g2s(dst + TILES * kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[s]);
+          bulk_g2s(dst + kTileBytes, p.q_tiled + off, L::kQBytes, &full_bar[s]);
         }
       }
       const uint32_t issued = it;  // never leave with copies in flight (only possible after an abort)
@@ -886,27 +914,23 @@ __global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_
       constexpr uint32_t idesc = umma_idesc_s8(NB);
       uint32_t it = 0, done = 0;
       for (int u = blockIdx.x; u < units; u += gridDim.x, ++done) {
-        const int idx = u % n_units;
-        const int tiles = (TILES == 2 && idx * TILES + 1 < p.n_tiles) ? 2 : 1;
-        const uint32_t ab = acc_of(done), use = use_of(done);
-        // the accumulator set is free once the epilogue has drained its previous unit
+        const PrefillUnit w = prefill_unit(p, u, ksplit);
+        const uint32_t ab = done & 1u, use = done >> 1;
+        // the accumulator is free once the epilogue has drained the unit before the previous one
         mbar_wait_bounded(&acc_empty[ab], (use & 1u) ^ 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
         tc_fence_after();
-        for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
+        const uint32_t d_tmem = tmem_base + ab * NB;
+        for (int kt = w.kt_begin; kt < w.kt_end; ++kt, ++it) {
           const int s = it % L::kStages;
           const uint32_t ph = (it / L::kStages) & 1u;
           mbar_wait_bounded(&full_bar[s], ph, abort_flag, p.status, kStatusWaitTimeoutFull);
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + (size_t)s * L::kStageBytes);
-          const uint32_t b_addr = a_addr + TILES * kTileBytes;
-          for (int j = 0; j < tiles; ++j) {
-            const uint32_t d_tmem = tmem_base + (TILES == 2 ? j : ab) * NB;
+          const uint32_t b_addr = a_addr + kTileBytes;
 #pragma unroll
-            for (int ks = 0; ks < kTileK8 / 32; ++ks) {
-              const uint64_t a_desc = umma_smem_desc(a_addr + j * kTileBytes + ks * 32);
-              const uint64_t b_desc = umma_smem_desc(b_addr + ks * 32);
-              umma_s8(d_tmem, a_desc, b_desc, idesc, (kt == 0 && ks == 0) ? 0u : 1u);
-            }
+          for (int ks = 0; ks < kTileK8 / 32; ++ks) {
+            umma_s8(d_tmem, umma_smem_desc(a_addr + ks * 32), umma_smem_desc(b_addr + ks * 32), idesc,
+                    (kt == w.kt_begin && ks == 0) ? 0u : 1u);
           }
           umma_commit(&empty_bar[s]);
         }
@@ -915,12 +939,11 @@ __global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_
       // wait for the last accumulators to be complete before the CTA tears TMEM down
       for (uint32_t back = 0; back < 2 && back < done; ++back) {
         const uint32_t i = done - 1 - back;
-        mbar_wait_bounded(&acc_full[acc_of(i)], use_of(i) & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
+        mbar_wait_bounded(&acc_full[i & 1u], (i >> 1) & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
       }
     }
   } else {
-    // eight epilogue warps: the TMEM lane quarter is warp % 4, and the two warps of a quarter take
-    // the even and the odd 16-row blocks; each half works through its own pair of staging blocks
+    // eight epilogue warps: the TMEM lane quarter is warp % 4; the two warps of a quarter split the rows
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const int half = (warp - 2) >> 2;
@@ -929,16 +952,16 @@ __global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_
     constexpr int kHalfThreads = 128;
     constexpr int kAllEpi = L::kEpiWarps * 32;
     constexpr int kElem = EPI == kEpiRequantI8 ? 1 : 4;
+    const bool plain = plain_epilogue<EPI>(p);
     pdl_wait();
     uint32_t done = 0;
     int staged_pass = -1;
     for (int u = blockIdx.x; u < units; u += gridDim.x, ++done) {
-      const int pass = u / n_units, idx = u % n_units;
-      const int tiles = (TILES == 2 && idx * TILES + 1 < p.n_tiles) ? 2 : 1;
-      const int m_base = pass * NB;
+      const PrefillUnit w = prefill_unit(p, u, ksplit);
+      const int m_base = w.pass * NB;
       const int m_valid = p.m - m_base < NB ? p.m - m_base : NB;
-      const uint32_t ab = acc_of(done), use = use_of(done);
-      if (pass != staged_pass) {  // per-row scale and zero point (or row sum) of this pass
+      const uint32_t ab = done & 1u, use = done >> 1;
+      if (w.pass != staged_pass) {  // per-row scale and zero point (or row sum) of this pass
         named_barrier(1, kAllEpi);
         for (int i = etid_all; i < NB; i += kAllEpi) {
           const int m = m_base + i;
@@ -951,84 +974,156 @@ __global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_
           }
         }
         named_barrier(1, kAllEpi);
-        staged_pass = pass;
+        staged_pass = w.pass;
       }
-      int32_t rs[TILES], base_i[TILES], mult[TILES], shift[TILES];
-      float wsc[TILES], bias_f[TILES];
-#pragma unroll
-      for (int j = 0; j < TILES; ++j) {
-        rs[j] = base_i[j] = mult[j] = shift[j] = 0;
-        wsc[j] = bias_f[j] = 0.0f;
-        const int n = (idx * TILES + j) * kTileN + row_in_tile;
-        if (j >= tiles || n >= p.n) continue;
-        rs[j] = p.row_sums ? p.row_sums[n] : 0;
+      int32_t rs = 0, base_i = 0, mult = 0, shift = 0;
+      float wsc = 0.0f, bias_f = 0.0f;
+      const int n0 = w.nt * kTileN;
+      const int n = n0 + row_in_tile;
+      const bool n_ok = n < p.n;
+      if (n_ok) {
+        rs = p.row_sums ? p.row_sums[n] : 0;
         if constexpr (EPI == kEpiHybridF32 || EPI == kEpiHybridPick) {
-          wsc[j] = p.per_channel ? p.w_scales[n] : p.w_scales[0];
-          bias_f[j] = p.bias_f32 ? p.bias_f32[n] : 0.0f;
+          wsc = p.per_channel ? p.w_scales[n] : p.w_scales[0];
+          bias_f = p.bias_f32 ? p.bias_f32[n] : 0.0f;
         } else {
-          base_i[j] = p.input_offset * rs[j] + p.k * p.filter_offset * p.input_offset + (p.bias_i32 ? p.bias_i32[n] : 0);
+          base_i = p.input_offset * rs + p.k * p.filter_offset * p.input_offset + (p.bias_i32 ? p.bias_i32[n] : 0);
           if (p.multipliers) {
-            mult[j] = p.multipliers[p.per_channel ? n : 0];
-            shift[j] = p.shifts[p.per_channel ? n : 0];
+            mult = p.multipliers[p.per_channel ? n : 0];
+            shift = p.shifts[p.per_channel ? n : 0];
           }
         }
       }
-      mbar_wait_bounded(&acc_full[ab], use & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
-      tc_fence_after();
+      // sixteen outputs of this thread's channel, activation rows m0 .. m0 + 15, from their exact dot products
+      auto finish16 = [&](const int (&r)[16], int m0, uint8_t* st) {
+        float sc[16];
+        int32_t ax[16];
 #pragma unroll
-      for (int j = 0; j < TILES; ++j) {
-        if (j >= tiles) break;
-        const int n0 = (idx * TILES + j) * kTileN;
-        const uint32_t taddr = tmem_base + (TILES == 2 ? j : ab) * NB + ((uint32_t)(quarter * 32) << 16);
+        for (int e = 0; e < 16; ++e) {
+          sc[e] = sh->in_scale[m0 + e];
+          ax[e] = sh->in_aux[m0 + e];
+        }
+        if constexpr (kElem == 4) {
+          int32_t* ycol = static_cast<int32_t*>(p.y) + (size_t)m_base * p.n + n;
+          if (plain) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const int32_t v = compute_output<EPI, true>(p, r[e], rs, wsc, bias_f, base_i, mult, shift, sc[e], ax[e]);
+              if (n_ok && m0 + e < m_valid) ycol[(size_t)(m0 + e) * p.n] = v;
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const int32_t v = compute_output<EPI>(p, r[e], rs, wsc, bias_f, base_i, mult, shift, sc[e], ax[e]);
+              if (n_ok && m0 + e < m_valid) ycol[(size_t)(m0 + e) * p.n] = v;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            reinterpret_cast<int8_t*>(st)[e * kTileN + row_in_tile] =
+                (int8_t)compute_output<EPI>(p, r[e], rs, wsc, bias_f, base_i, mult, shift, sc[e], ax[e]);
+        }
+      };
+      // int8 outputs: the staged 16 x 128 block leaves as whole 128-byte row segments, 16 bytes per thread
+      auto flush_block = [&](const uint8_t* st, int m0) {
+        constexpr int kChunksPerRow = kTileN * kElem / 16;
+        constexpr int kPieces = 16 * kChunksPerRow;
         const bool vec_ok = (((size_t)p.n * kElem) % 16 == 0) && (n0 + kTileN <= p.n) &&
                             ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
+        for (int i = etid; i < kPieces; i += kHalfThreads) {
+          const int rr = i / kChunksPerRow, cc = i % kChunksPerRow;
+          const int m = m0 + rr;
+          if (m >= m_valid) continue;
+          uint8_t* dst = static_cast<uint8_t*>(p.y) + ((size_t)(m_base + m) * p.n + n0) * kElem + cc * 16;
+          const uint8_t* src = st + (size_t)rr * kTileN * kElem + cc * 16;
+          if (vec_ok) {
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+          } else {
+            for (int bb = 0; bb < 16; ++bb)
+              if (n0 + (cc * 16 + bb) / kElem < p.n) dst[bb] = src[bb];
+          }
+        }
+      };
+      mbar_wait_bounded(&acc_full[ab], use & 1u, abort_flag, p.status, kStatusWaitTimeoutTmem);
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ab * NB + ((uint32_t)(quarter * 32) << 16);
+      const int c_begin = half * (NB / 2), c_end = min((half + 1) * (NB / 2), m_valid);
+      if (ksplit == 1) {
 #pragma unroll 1
-        for (int c = half; c < NB / 16; c += 2) {
-          if (c * 16 >= m_valid) break;
-          int r[16];
-          tmem_ld16(taddr + c * 16, r);
+        for (int m0 = c_begin; m0 < c_end; m0 += 32) {
+          int ra[16], rb[16];
+          tmem_ld16(taddr + m0, ra);  // both loads in flight before the first wait
+          tmem_ld16(taddr + m0 + 16, rb);
           tmem_ld_wait();
-          uint8_t* st = out_stage + (half * 2 + ((c >> 1) & 1)) * (16 * kTileN * 4);
-          // the rows' parameters first, all at once: behind the staging stores the compiler would have
-          // to reload them one by one (it cannot rule out that the stores change them)
-          float sc[16];
-          int32_t ax[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            sc[e] = sh->in_scale[c * 16 + e];
-            ax[e] = sh->in_aux[c * 16 + e];
+          uint8_t* st = out_stage + (half * 2 + ((m0 >> 5) & 1)) * (16 * kTileN * 4);
+          finish16(ra, m0, st);
+          if constexpr (kElem != 4) {
+            named_barrier(2 + half, kHalfThreads);  // the block is complete
+            flush_block(st, m0);
+            named_barrier(2 + half, kHalfThreads);  // ... and read, before it is rewritten
           }
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int32_t v = compute_output<EPI>(p, r[e], rs[j], wsc[j], bias_f[j], base_i[j], mult[j], shift[j],
-                                                  sc[e], ax[e]);
-            if constexpr (kElem == 4) {
-              reinterpret_cast<int32_t*>(st)[e * kTileN + row_in_tile] = v;
-            } else {
-              reinterpret_cast<int8_t*>(st)[e * kTileN + row_in_tile] = (int8_t)v;
-            }
-          }
-          named_barrier(2 + half, kHalfThreads);  // the block is complete (and the other block's readers are done)
-          constexpr int kChunksPerRow = kTileN * kElem / 16;
-          constexpr int kPieces = 16 * kChunksPerRow;
-          for (int i = etid; i < kPieces; i += kHalfThreads) {
-            const int rr = i / kChunksPerRow, cc = i % kChunksPerRow;
-            const int m = c * 16 + rr;
-            if (m >= m_valid) continue;
-            uint8_t* dst = static_cast<uint8_t*>(p.y) + ((size_t)(m_base + m) * p.n + n0) * kElem + cc * 16;
-            const uint8_t* src = st + (size_t)rr * kTileN * kElem + cc * 16;
-            if (vec_ok) {
-              *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
-            } else {
-              for (int bb = 0; bb < 16; ++bb)
-                if (n0 + (cc * 16 + bb) / kElem < p.n) dst[bb] = src[bb];
+          if (m0 + 16 < c_end) {
+            finish16(rb, m0 + 16, st);
+            if constexpr (kElem != 4) {
+              named_barrier(2 + half, kHalfThreads);
+              flush_block(st, m0 + 16);
+              named_barrier(2 + half, kHalfThreads);
             }
           }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[ab]);
+      } else {
+        // this unit's raw sums to its scratch slot (coalesced: a warp writes 32 consecutive channels of a row)
+        int32_t* mine = p.ws_part + (size_t)u * kZeroWsSlotInts;
+#pragma unroll 1
+        for (int m0 = c_begin; m0 < c_end; m0 += 32) {
+          int ra[16], rb[16];
+          tmem_ld16(taddr + m0, ra);
+          tmem_ld16(taddr + m0 + 16, rb);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            __stcg(&mine[(m0 + e) * kTileN + row_in_tile], ra[e]);
+            __stcg(&mine[(m0 + 16 + e) * kTileN + row_in_tile], rb[e]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[ab]);
+        named_barrier(1, kAllEpi);
+        if (etid_all == 0) {
+          __threadfence();
+          const int old = atomicAdd(&p.ws_count[w.tile_id], 1);
+          sh->last = (old + 1 == ksplit) ? 1 : 0;
+        }
+        named_barrier(1, kAllEpi);
+        if (sh->last) {
+          __threadfence();
+          const int32_t* first = p.ws_part + (size_t)w.tile_id * ksplit * kZeroWsSlotInts + row_in_tile;
+#pragma unroll 1
+          for (int m0 = c_begin; m0 < c_end; m0 += 16) {
+            int r[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) r[e] = 0;
+            for (int ks = 0; ks < ksplit; ++ks) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) r[e] += __ldcg(first + (size_t)ks * kZeroWsSlotInts + (m0 + e) * kTileN);
+            }
+            uint8_t* st = out_stage + (half * 2) * (16 * kTileN * 4);
+            finish16(r, m0, st);
+            if constexpr (kElem != 4) {
+              named_barrier(2 + half, kHalfThreads);
+              flush_block(st, m0);
+              named_barrier(2 + half, kHalfThreads);
+            }
+          }
+          if (etid_all == 0) p.ws_count[w.tile_id] = 0;
+        }
+        named_barrier(1, kAllEpi);  // sh->last is rewritten by the next unit
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[ab]);
     }
   }
   tc_fence_before();
@@ -1036,11 +1131,11 @@ __global__ void __launch_bounds__(PrefillLayout<TILES>::kThreads, 1) fc_prefill_
   if (warp == 1) tmem_dealloc(tmem_base, L::kTmemCols);
 }
 
-template <int EPI, int TILES>
+template <int EPI>
 cudaError_t launch_prefill(const FcParams& p, cudaStream_t s) {
-  using L = PrefillLayout<TILES>;
+  using L = PrefillLayout;
   static bool configured[64] = {false};
-  auto kernel = fc_prefill_kernel<EPI, TILES>;
+  auto kernel = fc_prefill_kernel<EPI>;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
@@ -1049,16 +1144,21 @@ cudaError_t launch_prefill(const FcParams& p, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const int n_units = (p.n_tiles + TILES - 1) / TILES;
   const int passes = (p.m + L::kNB - 1) / L::kNB;
   const int sms = device_sm_count();
-  const int units = n_units * passes;
-  int ctas = units < sms ? units : sms;
-  if (const char* e = getenv("B200_FC_MAX_CTAS")) {  // measurement knob
-    const int v = atoi(e);
-    if (v > 0 && v < ctas) ctas = v;
+  const int tiles = p.n_tiles * passes;
+  // few tiles, a long reduction: cut it so that most SMs get a unit (at least 16 k tiles per range)
+  int ksplit = 1;
+  if (tiles * 2 <= sms && p.k_tiles >= 32) {
+    ksplit = sms / tiles;
+    if (ksplit > p.k_tiles / 16) ksplit = p.k_tiles / 16;
+    while (ksplit > 1 && tiles * ksplit > kZeroWsSlots) --ksplit;
+    if (ksplit < 1) ksplit = 1;
   }
-  return launch_chained(kernel, dim3(ctas), dim3(L::kThreads), (size_t)L::kSmemBytes, s, p, n_units, passes);
+  if (const char* e = getenv("B200_FC_KSPLIT")) ksplit = atoi(e) > 0 ? atoi(e) : ksplit;  // measurement knob
+  const int units = tiles * ksplit;
+  const int ctas = units < sms ? units : sms;
+  return launch_chained(kernel, dim3(ctas), dim3(L::kThreads), (size_t)L::kSmemBytes, s, p, units, ksplit);
 }
 
 // Chooses the number of CTAs and the split for one launch (measured on B200, batch 1, graph
@@ -1254,21 +1354,16 @@ cudaError_t launch_all(const FcParams& p, cudaStream_t s) {
       if (m_base + 64 >= p.m) return cudaSuccess;
     }
   }
-  // Prefill-sized: every (n tile range, pass of nb activation rows) is a CTA of one launch, whole n
-  // tiles per CTA (merging split-K partials of 128+ columns through memory costs more than it
-  // saves). 128 rows per pass when 256 would leave SMs idle (few n tiles).
-  if (nb == 256 && p.n_tiles * ((p.m + 255) / 256) < sms) nb = 128;
+  // Prefill-sized: persistent CTAs over (n tile, pass of 256 activation rows) units. (Passes of 128 rows
+  // through the decode kernel, which give twice the CTAs when there are few n tiles, measured no faster
+  // for any shape once the epilogue stopped being the limit: 10.4 against 22.5 us at m = 1024, n = 2560,
+  // k = 2048.) B200_FC_NB=128 keeps that launch for measurements.
   if (const char* e = getenv("B200_FC_NB")) {  // measurement knob
     const int v = atoi(e);
     if (v == 128 || v == 256) nb = v;
   }
   if (p.m_alloc % nb != 0) return cudaErrorInvalidValue;
-  if (nb == 256) {
-    // persistent CTAs over (n tile, pass) units; B200_FC_PREFILL=0 keeps the one-unit-per-CTA launch
-    // below (measurement knob)
-    const char* e = getenv("B200_FC_PREFILL");
-    if (!(e && e[0] == '0')) return launch_prefill<EPI, 1>(p, s);
-  }
+  if (nb == 256) return launch_prefill<EPI>(p, s);
   const int passes = (p.m + nb - 1) / nb;
   FcParams q = p;
   // Whole n tiles per CTA. B200_FC_SPLIT_PASSES=1 (measurement knob) instead shares the SMs out among
