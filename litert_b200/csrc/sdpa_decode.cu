@@ -122,10 +122,6 @@ __host__ __device__ inline size_t partial_stride(int h) { return (size_t)h + 2; 
 // softmax state for heads 2t and 2t+1 (log2 domain) and the un-normalised outputs, in registers.
 // GPI = groups of 16 tokens a warp takes per pass (1, 2 or 4): small for short caches, where the
 // kernel is latency-bound and wants as many warps as possible, 4 for long ones.
-#ifdef B200_ATTN_DBG
-__device__ long long g_attn_dbg[64];
-__device__ int g_attn_dbg_on;
-#endif
 
 template <int KV, int H, int GPI>
 struct WarpAttention {
@@ -172,7 +168,10 @@ struct WarpAttention {
   // Tokens first, first + step, ... (blocks of kTokensPerWarpIter) below `c1`.
     // `fresh` false continues the running softmax state of an earlier call; `finish` false leaves the
   // denominators per thread for a later call to complete (calls over consecutive pieces of a chunk).
-  template <int SRC>
+  // EXTRAS false: the caller knows that there is neither a logit cap nor a mask, and the tests for them
+  // leave the loop (a warp alone on its scheduler pays each branch's latency in full). Rows beyond c1 are
+  // not skipped by a branch either: they read the last valid row, and their logits are set to -inf.
+  template <int SRC, bool EXTRAS = true>
   __device__ __forceinline__ void run(const SdpaParams& p, const uint32_t (&qf)[KSTEPS][4], const Rows& rows_src, int b,
                                       int first, int step, int c1, int lane, bool fresh = true, bool finish = true) {
     const int g = lane >> 2, t = lane & 3;
@@ -183,26 +182,20 @@ struct WarpAttention {
   const float* ksc = rows_src.k_scale;
   const float* vsc = rows_src.v_scale;
   const int sc_stride = rows_src.scale_stride;
-  const float* maskp = p.mask ? p.mask + (size_t)b * p.s_max : nullptr;
+  const float* maskp = (EXTRAS && p.mask) ? p.mask + (size_t)b * p.s_max : nullptr;
+  const int last_tok = c1 - 1;
 
   const float scale_log2 = p.scale * kLog2e;
 
-#ifdef B200_ATTN_DBG
-  int dbg_i = 0;
-#define DBG_STAMP(k) if (g_attn_dbg_on && threadIdx.x == 0 && blockIdx.x == 0 && dbg_i < 4) g_attn_dbg[dbg_i * 8 + (k)] = clock64()
-#else
-#define DBG_STAMP(k)
-#endif
   for (int base = first; base < c1; base += step) {
-    DBG_STAMP(0);
     // ---- S^T = K Q^T for GPI groups of 16 tokens ----
     float s[GPI][4];
 #pragma unroll
     for (int gi = 0; gi < GPI; ++gi) {
       const int ta = base + gi * 16 + g, tb = ta + 8;
       const bool va = ta < c1, vb = tb < c1;
-      const void* ra = kbase + (size_t)ta * row_stride;
-      const void* rb = kbase + (size_t)tb * row_stride;
+      const void* ra = kbase + (size_t)min(ta, last_tok) * row_stride;
+      const void* rb = kbase + (size_t)min(tb, last_tok) * row_stride;
       // four independent accumulation chains: a chain of 2 * KSTEPS dependent MMAs would leave the
       // tensor pipe idle for its whole latency between steps
       float part[4][4];
@@ -212,14 +205,13 @@ struct WarpAttention {
       for (int i = 0; i < KSTEPS; ++i) {
         uint32_t ka[4], kb[4];
         const int d0 = 8 * (t + 4 * i);
-        load8<KV, SRC>(ra, d0, va, ka);
-        load8<KV, SRC>(rb, d0, vb, kb);
+        load8<KV, SRC>(ra, d0, true, ka);
+        load8<KV, SRC>(rb, d0, true, kb);
         mma_f16(part[(2 * i) & 3], ka[0], kb[0], ka[1], kb[1], qf[i][0], qf[i][1]);
         mma_f16(part[(2 * i + 1) & 3], ka[2], kb[2], ka[3], kb[3], qf[i][2], qf[i][3]);
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[gi][e] = (part[0][e] + part[1][e]) + (part[2][e] + part[3][e]);
-      if (gi == 0) { DBG_STAMP(1); }
       // scale (and dequantise), cap, mask; work in the log2 domain
       float fa = scale_log2, fb = scale_log2;
       if constexpr (KV == kKvI8) {
@@ -230,22 +222,23 @@ struct WarpAttention {
       s[gi][1] *= fa;
       s[gi][2] *= fb;
       s[gi][3] *= fb;
-      if (p.logit_cap > 0.0f) {
+      if (EXTRAS && p.logit_cap > 0.0f) {
         const float c = p.logit_cap * kLog2e, ic = 1.0f / c;
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[gi][e] = c * tanhf(s[gi][e] * ic);
       }
-      if (maskp) {
+      if (EXTRAS && maskp) {
         const float ma = va ? maskp[ta] * kLog2e : 0.0f, mb = vb ? maskp[tb] * kLog2e : 0.0f;
         s[gi][0] += ma;
         s[gi][1] += ma;
         s[gi][2] += mb;
         s[gi][3] += mb;
       }
-      if (!va) s[gi][0] = s[gi][1] = -CUDART_INF_F;
-      if (!vb) s[gi][2] = s[gi][3] = -CUDART_INF_F;
+      s[gi][0] = va ? s[gi][0] : -CUDART_INF_F;
+      s[gi][1] = va ? s[gi][1] : -CUDART_INF_F;
+      s[gi][2] = vb ? s[gi][2] : -CUDART_INF_F;
+      s[gi][3] = vb ? s[gi][3] : -CUDART_INF_F;
     }
-    DBG_STAMP(2);
     // ---- online softmax over these tokens ----
     float mx[2];
 #pragma unroll
@@ -274,7 +267,6 @@ struct WarpAttention {
       o[i][2] *= alpha[0];
       o[i][3] *= alpha[1];
     }
-    DBG_STAMP(3);
     // ---- O^T += V^T P^T ----
 #pragma unroll
     for (int gi = 0; gi < GPI; ++gi) {
@@ -301,8 +293,8 @@ struct WarpAttention {
         uint32_t vr[4][DPT / 2];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-          const void* row = vbase + (size_t)rows[r] * row_stride;
-          const bool ok = rows[r] < c1;
+          const void* row = vbase + (size_t)min(rows[r], last_tok) * row_stride;  // (its weight is 0 beyond c1)
+          const bool ok = true;
 #pragma unroll
           for (int hlf = 0; hlf < DPT / 8; ++hlf) {
             uint32_t tmp[4];
@@ -987,7 +979,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
       if (first >= last) {
         wa.clear();
       } else {
-        wa.template run<kSrcShared>(sp, qf, rows1, b, first, 16, last, lane);
+        wa.template run<kSrcShared, false>(sp, qf, rows1, b, first, 16, last, lane);
       }
       if (tracer && live) p.trace[4] = global_timer_ns();
       wa.park(sm.sm_m, sm.sm_l, sm_o, warp, lane);
@@ -996,7 +988,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
       if (first >= last) {
         wa.clear();
       } else {
-        wa.template run<kSrcGlobalCoherent>(sp, qf, rows, b, first, WA::kTokensPerWarpIter, last, lane);
+        wa.template run<kSrcGlobalCoherent, false>(sp, qf, rows, b, first, WA::kTokensPerWarpIter, last, lane);
       }
       if (tracer && live) p.trace[4] = global_timer_ns();
       wa.park(sm.sm_m, sm.sm_l, sm_o, warp, lane);
