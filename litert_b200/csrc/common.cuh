@@ -3,6 +3,8 @@
 // and the tile geometry of the packed weight layouts.
 #pragma once
 
+#include <cstdlib>
+
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -335,7 +337,20 @@ __device__ __forceinline__ void pdl_enter() {
   pdl_wait();
 }
 
-// B200_PDL=0 turns the attribute off (plain stream order) for A/B measurement.
+// Measurement knobs (B200_PDL, B200_FC_*, B200_SDPA_*, B200_DEC_* ...: environment variables that pick a
+// kernel variant or leave work out, for A/B timing) exist only in builds made with -DB200_TUNING_KNOBS
+// (B200_NVCC_FLAGS=-DB200_TUNING_KNOBS python -m litert_b200.build --force). A regular build reads no
+// environment variable on any kernel path: tuning_env() is a constant null pointer there.
+inline const char* tuning_env(const char* name) {
+#ifdef B200_TUNING_KNOBS
+  return getenv(name);
+#else
+  (void)name;
+  return nullptr;
+#endif
+}
+
+// B200_PDL=0 (tuning builds) turns the attribute off (plain stream order) for A/B measurement.
 bool pdl_enabled();
 
 template <typename... KArgs, typename... Args>

@@ -267,7 +267,7 @@ cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_
   // layers' projections fit L2 whole; of the LM head only a first slice is asked for.
   {
     static const int pf_env = [] {
-      const char* e = getenv("B200_L2_PREFETCH");  // measurement knob: tiles per CTA, 0 = off
+      const char* e = tuning_env("B200_L2_PREFETCH");  // measurement knob: tiles per CTA, 0 = off
       return e ? atoi(e) : -1;
     }();
     const size_t bytes = (size_t)p.n_tiles * p.k_tiles * kTileBytes;
@@ -336,7 +336,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
   // the shared memory, so the prologue's latency is exposed, whereas the small separate kernel runs
   // beside the previous GEMV and the next one fills its ring meanwhile. Kept for wider rows per SM.
   static const bool fuse_env = [] {
-    const char* e = getenv("B200_FUSED_PROLOGUE");
+    const char* e = tuning_env("B200_FUSED_PROLOGUE");
     return e && e[0] == '1';
   }();
   const bool fuse_norm = fuse_env && !tp && fc_prologue_supported(batch, c.d_model);
@@ -344,14 +344,14 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
   // (the results are then meaningless). Bits: 1 norm, 2 rope, 4 attention, 8 GeGLU, 16 qkv, 32 o,
   // 64 gate/up, 128 down, 256 LM head.
   static const int skip = [] {
-    const char* e = getenv("B200_DEC_SKIP");
+    const char* e = tuning_env("B200_DEC_SKIP");
     return e ? atoi(e) : 0;
   }();
   // Rotary embedding, cache append, attention and output quantization as one cluster kernel where
   // the shape allows (one KV head on this rank, at most eight query heads); B200_ATTN_STEP=0 keeps
   // the three separate kernels.
   static const bool attn_env = [] {
-    const char* e = getenv("B200_ATTN_STEP");
+    const char* e = tuning_env("B200_ATTN_STEP");
     return !(e && e[0] == '0');
   }();
   // (one cluster of 8 CTAs per sequence, each with most of an SM's shared memory: beyond about a
@@ -461,7 +461,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
   // epilogue (soft-cap, first index of the maximum, NaN rule), so that no logits are written unless the
   // caller asked for them, and one small kernel compares the CTAs' candidates.
   static const bool pick_env = [] {
-    const char* e = getenv("B200_FUSED_PICK");  // measurement knob: 0 keeps the separate arg-max kernels
+    const char* e = tuning_env("B200_FUSED_PICK");  // measurement knob: 0 keeps the separate arg-max kernels
     return !(e && e[0] == '0');
   }();
   const bool fused_pick = pick_env && !tp && batch <= 16 && fc_argmax_ctas(d->lm_head.n) <= kArgmaxSlots;
@@ -525,7 +525,7 @@ int ensure_prefill_bufs(b200_decoder* d) {
   const b200_decoder_config& c = d->cfg;
   auto pf = std::make_unique<PrefillBufs>();
   int R = kPrefillRows;
-  if (const char* e = getenv("B200_PREFILL_ROWS")) {
+  if (const char* e = tuning_env("B200_PREFILL_ROWS")) {
     const int v = atoi(e);
     if (v >= 1 && v <= 8192) R = v;
   }
@@ -748,7 +748,7 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
   DEC_CUDA(d->q_f.alloc(q_tiled_bytes(m_alloc, d->fl)));
   for (DevBuf* b : {&d->sc_d, &d->sc_a, &d->sc_f, &d->zp_d, &d->zp_a, &d->zp_f}) DEC_CUDA(b->alloc(sizeof(float) * m_alloc));
   DEC_CUDA(d->zero_ws.alloc(zero_ws_total_bytes()));
-  if (getenv("B200_DEC_TRACE")) {
+  if (tuning_env("B200_DEC_TRACE")) {
     DEC_CUDA(d->trace.alloc(sizeof(unsigned long long) * (4 * kTraceSlots + 16 * 64)));
     DEC_CUDA(cudaMemsetAsync(d->trace.p, 0, d->trace.bytes, d->stream));
   }
@@ -796,7 +796,7 @@ void b200_decoder_destroy(b200_decoder* d) {
   if (d->trace.p) {  // measurement: the last step's stamps, one line per GEMV launch
     std::vector<unsigned long long> t(4 * kTraceSlots + 16 * 64);
     if (cudaMemcpy(t.data(), d->trace.p, d->trace.bytes, cudaMemcpyDeviceToHost) == cudaSuccess) {
-      if (FILE* f = fopen(getenv("B200_DEC_TRACE"), "w")) {
+      if (FILE* f = fopen(tuning_env("B200_DEC_TRACE"), "w")) {
         for (int i = 0; i < kTraceSlots && t[4 * i]; ++i)
           fprintf(f, "%d %llu %llu %llu %llu\n", i, t[4 * i], t[4 * i + 1], t[4 * i + 2], t[4 * i + 3]);
         for (int l = 0; l < 64 && l < d->cfg.n_layers; ++l) {  // attention step kernel, nine stamps per layer

@@ -277,14 +277,14 @@ cudaError_t launch_one(const FcParams& p, int m_base, cudaStream_t s) {
   const long long total = (long long)p.n_tiles * p.k_tiles;
   const int sms = device_sm_count();
   int ctas = p.max_ctas > 0 ? p.max_ctas : sms;
-  if (const char* e = getenv("B200_FC_MAX_CTAS")) {  // tuning knob
+  if (const char* e = tuning_env("B200_FC_MAX_CTAS")) {  // tuning knob
     const int v = atoi(e);
     if (v > 0) ctas = v;
   }
   FcParams q = p;
   // with at least half as many n tiles as SMs, whole tiles per CTA: nothing to merge across CTAs
-  q.whole_tiles = (p.n_tiles * 2 >= sms && p.max_ctas <= 0 && !getenv("B200_FC_MAX_CTAS")) ? 1 : 0;
-  if (const char* e = getenv("B200_FC_SPLIT")) q.whole_tiles = atoi(e) ? 0 : 1;  // measurement knob
+  q.whole_tiles = (p.n_tiles * 2 >= sms && p.max_ctas <= 0 && !tuning_env("B200_FC_MAX_CTAS")) ? 1 : 0;
+  if (const char* e = tuning_env("B200_FC_SPLIT")) q.whole_tiles = atoi(e) ? 0 : 1;  // measurement knob
   if (q.whole_tiles && ctas > p.n_tiles) ctas = p.n_tiles;
   if (ctas > kAccSlots) ctas = kAccSlots;
   if (ctas > total) ctas = (int)total;

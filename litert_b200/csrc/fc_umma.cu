@@ -1155,7 +1155,7 @@ cudaError_t launch_prefill(const FcParams& p, cudaStream_t s) {
     while (ksplit > 1 && tiles * ksplit > kZeroWsSlots) --ksplit;
     if (ksplit < 1) ksplit = 1;
   }
-  if (const char* e = getenv("B200_FC_KSPLIT")) ksplit = atoi(e) > 0 ? atoi(e) : ksplit;  // measurement knob
+  if (const char* e = tuning_env("B200_FC_KSPLIT")) ksplit = atoi(e) > 0 ? atoi(e) : ksplit;  // measurement knob
   const int units = tiles * ksplit;
   const int ctas = units < sms ? units : sms;
   return launch_chained(kernel, dim3(ctas), dim3(L::kThreads), (size_t)L::kSmemBytes, s, p, units, ksplit);
@@ -1170,7 +1170,7 @@ int plan_ctas(FcParams* p, int passes, int ctas_per_sm) {
   const int sms = device_sm_count();
   const long long total = (long long)p->n_tiles * p->k_tiles;
   int mode = -1;  // -1 auto, 0 stream-K, 1 whole tiles
-  if (const char* e = getenv("B200_FC_SPLIT")) mode = atoi(e) ? 0 : 1;  // measurement knob
+  if (const char* e = tuning_env("B200_FC_SPLIT")) mode = atoi(e) ? 0 : 1;  // measurement knob
   int ctas;
   if (p->split_passes && passes > 1 && mode != 1) {
     // few n tiles, a long reduction, several passes of activation rows: the SMs are shared out
@@ -1187,7 +1187,7 @@ int plan_ctas(FcParams* p, int passes, int ctas_per_sm) {
     ctas = sms * ctas_per_sm;
   }
   if (p->max_ctas > 0) ctas = p->max_ctas;
-  if (const char* e = getenv("B200_FC_MAX_CTAS")) {  // measurement knob
+  if (const char* e = tuning_env("B200_FC_MAX_CTAS")) {  // measurement knob
     const int v = atoi(e);
     if (v > 0) ctas = v;
   }
@@ -1236,7 +1236,7 @@ cudaError_t launch_umma_nb(const FcParams& p, int m_base, int nb, int passes, cu
 // better served by the kernels above (many n tiles, or a single k tile).
 template <int NB, int EPI>
 int plan_cluster_split(const FcParams& p) {
-  if (const char* e = getenv("B200_FC_CLUSTER"))  // measurement knob: 0 turns the cluster kernel off
+  if (const char* e = tuning_env("B200_FC_CLUSTER"))  // measurement knob: 0 turns the cluster kernel off
     if (e[0] == '0') return 0;
   const int sms = device_sm_count();
   if (p.n_tiles * 2 >= sms || p.k_tiles < 2) return 0;
@@ -1254,7 +1254,7 @@ int plan_cluster_split(const FcParams& p) {
     }
     configured[dev] = true;
   }
-  if (const char* e = getenv("B200_FC_CLUSTER")) {  // measurement knob: force a split
+  if (const char* e = tuning_env("B200_FC_CLUSTER")) {  // measurement knob: force a split
     const int v = atoi(e);
     if (v >= 2 && v <= 16 && v <= p.k_tiles) {
       // beyond 8 the cluster size is "non-portable": the kernel has to opt in
@@ -1292,7 +1292,7 @@ int plan_cluster_split(const FcParams& p) {
         n = -1;
       }
       capacity[dev][split] = n;
-      if (getenv("B200_FC_VERBOSE")) fprintf(stderr, "[b200] cluster size %d: %d clusters resident (NB=%d)\n", split, n, NB);
+      if (tuning_env("B200_FC_VERBOSE")) fprintf(stderr, "[b200] cluster size %d: %d clusters resident (NB=%d)\n", split, n, NB);
     }
     // (the query counts one CTA per SM; CTAs this small share an SM, and clusters beyond the
     // resident ones simply start as earlier ones finish: nothing waits across clusters)
@@ -1358,7 +1358,7 @@ cudaError_t launch_all(const FcParams& p, cudaStream_t s) {
   // through the decode kernel, which give twice the CTAs when there are few n tiles, measured no faster
   // for any shape once the epilogue stopped being the limit: 10.4 against 22.5 us at m = 1024, n = 2560,
   // k = 2048.) B200_FC_NB=128 keeps that launch for measurements.
-  if (const char* e = getenv("B200_FC_NB")) {  // measurement knob
+  if (const char* e = tuning_env("B200_FC_NB")) {  // measurement knob
     const int v = atoi(e);
     if (v == 128 || v == 256) nb = v;
   }
@@ -1372,7 +1372,7 @@ cudaError_t launch_all(const FcParams& p, cudaStream_t s) {
   // whole tiles, 57 us on average when split): the merge of 128-row partials through memory costs
   // more than the idle SMs.
   q.split_passes = 0;
-  if (const char* e = getenv("B200_FC_SPLIT_PASSES")) q.split_passes = atoi(e) ? 1 : 0;
+  if (const char* e = tuning_env("B200_FC_SPLIT_PASSES")) q.split_passes = atoi(e) ? 1 : 0;
   q.force_whole_tiles = q.split_passes ? 0 : 1;
   return launch_umma_nb<EPI>(q, 0, nb, passes, s);
 }

@@ -11,7 +11,7 @@ namespace b200 {
 bool pdl_enabled() {
   static int cached = -1;
   if (cached < 0) {
-    const char* e = getenv("B200_PDL");
+    const char* e = tuning_env("B200_PDL");
     cached = (e && e[0] == '0') ? 0 : 1;
   }
   return cached == 1;

@@ -753,7 +753,6 @@ constexpr int kAttnCluster = 8;
 // take 4.6 us in the token loop, 8 warps x 2 passes 5.4 us: the loop's cost is mostly fixed (cold
 // instruction and data fetches after the weight stream has swept L2), not per token.
 constexpr int kAttnWarps = 4;
-constexpr bool kAttnDryRun = false;
 
 template <int H>
 struct AttnStepSmem {
@@ -798,8 +797,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
   AttnStepSmem<H>& sm = *reinterpret_cast<AttnStepSmem<H>*>(attn_smem_raw);
   uint8_t* stage_k = attn_smem_raw + ((sizeof(AttnStepSmem<H>) + 127) / 128) * 128;
   uint8_t* stage_v = stage_k + (size_t)stage_rows * PITCH;
-  // the warps' parked outputs follow the staged rows (the dry-run pass parks too: no sharing)
-  float (*sm_o)[8][H + 4] = reinterpret_cast<float (*)[8][H + 4]>(stage_v + (size_t)stage_rows * PITCH);
+  // the warps' parked outputs reuse the staging area once every warp has left the token loop
+  float (*sm_o)[8][H + 4] = reinterpret_cast<float (*)[8][H + 4]>(stage_k);
 
   const bool tracer = p.trace && blockIdx.x == 0 && threadIdx.x == 0;
   if (tracer) p.trace[0] = global_timer_ns();
@@ -819,14 +818,18 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
   const int per = (((len + C - 1) / C) + 15) / 16 * 16;
   const int c0 = rank * per;
   const int c1 = min(len, c0 + per);
-  const bool staged = c1 - c0 <= stage_rows;   // else the rows are read straight from the cache
+  // The first `stage_rows` rows of the share are staged in shared memory; a share a little longer than
+  // the staging area reads its last rows straight from the cache (a context that outgrows the staging
+  // area by a few tokens must not fall off a cliff), a much longer one reads all of them from there.
+  const bool staged = c1 - c0 <= stage_rows + 64;
+  const int s_end = min(c1, c0 + stage_rows);      // staged rows: [c0, s_end)
   const int old_end = append ? min(c1, pos) : c1;  // rows [c0, old_end) are already in the cache
   const uint8_t* kglob = static_cast<const uint8_t*>(p.k_cache) + (size_t)b * p.s_max * ROW_BYTES;
   const uint8_t* vglob = static_cast<const uint8_t*>(p.v_cache) + (size_t)b * p.s_max * ROW_BYTES;
   if (staged) {
     // 16-byte asynchronous copies, all in flight at once (no registers held): the rows land padded
     constexpr int PIECES = ROW_BYTES / 16;
-    const int n_pieces = (old_end - c0) * PIECES;
+    const int n_pieces = (min(old_end, s_end) - c0) * PIECES;
     for (int i = tid; i < n_pieces; i += kAttnWarps * 32) {
       const int r = i / PIECES, c = i % PIECES;
       cp_async16(stage_k + (size_t)r * PITCH + c * 16, kglob + (size_t)(c0 + r) * ROW_BYTES + c * 16);
@@ -838,14 +841,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
   // cos / sin of this position's rotation angles, from the table the host side prepared
   for (int i = tid; i < HALF; i += kAttnWarps * 32) sm.cs[i] = p.rope_cs[(size_t)min(pos, p.s_max) * HALF + i];
   if (tracer) p.trace[11] = global_timer_ns();
-  // With kAttnDryRun the code below runs twice: first at once, on stale q / k / v, storing nothing
-  // outside the CTAs' shared memory, to pull instructions into the caches while the projection
-  // kernel is still running; then for real after the dependency wait. Measured on B200 it does not
-  // pay here (the dry run outlasts the projection kernel by 8 us, and the real pass is no faster:
-  // its time is not instruction fetches), so it is off; the row kernels of the decoder keep theirs.
-#pragma unroll 1
-  for (int pass = kAttnDryRun ? 0 : 1; pass < 2; ++pass) {
-    const bool live = pass == 1;
+  // (Running the code below once ahead of the dependency wait, on stale q / k / v, to warm the caches was
+  // measured on B200 and does not pay here: the early run outlasts the projection kernel by 8 us and the
+  // real one is no faster. The row kernels of the decoder keep theirs.)
+  {
+    constexpr bool live = true;
     if (live) {
       pdl_wait();  // this step's q / k / v
       if (tracer) p.trace[1] = global_timer_ns();
@@ -900,7 +900,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
           const int8_t v1 = (int8_t)max(-127, min(127, __float2int_rn(__fdiv_rn(__ldcg(vsrc + i), vs))));
           const int8_t v2 = (int8_t)max(-127, min(127, __float2int_rn(__fdiv_rn(__ldcg(vsrc + i + HALF), vs))));
           if (live) kd[i] = k1, kd[i + HALF] = k2, vd[i] = v1, vd[i + HALF] = v2;
-          if (staged) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
+          if (staged && pos < s_end) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
         }
         if (tid == 0 && live) {
           p.k_scale[tok] = ks;
@@ -917,7 +917,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
           const __half k1 = __float2half_rn(rope_lo(x1, x2, r)), k2 = __float2half_rn(rope_hi(x1, x2, r));
           const __half v1 = __float2half_rn(__ldcg(vsrc + i)), v2 = __float2half_rn(__ldcg(vsrc + i + HALF));
           if (live) kd[i] = k1, kd[i + HALF] = k2, vd[i] = v1, vd[i + HALF] = v2;
-          if (staged) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
+          if (staged && pos < s_end) ks_row[i] = k1, ks_row[i + HALF] = k2, vs_row[i] = v1, vs_row[i + HALF] = v2;
         }
       }
     }
@@ -960,9 +960,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
     }
     if (tracer && live) p.trace[3] = global_timer_ns();
     // the warps take equal contiguous shares of the CTA's tokens (multiples of 16)
-    const int wper = ((((c1 - c0) + kAttnWarps - 1) / kAttnWarps) + 15) / 16 * 16;
-    const int first = c0 + warp * wper;
-    const int last = min(c1, first + wper);
     // Staged rows are read from shared memory, where passes are cheap: the smallest loop body (16
     // tokens per pass) whatever the cache's capacity. Rows read from the cache itself (a share
     // longer than the staging area) want the long passes the kernel was instantiated with.
@@ -976,14 +973,31 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
       rows1.k_scale = rows.k_scale;
       rows1.v_scale = rows.v_scale;
       rows1.scale_stride = rows.scale_stride;
-      if (first >= last) {
-        wa.clear();
-      } else {
-        wa.template run<kSrcShared, false>(sp, qf, rows1, b, first, 16, last, lane);
+      wa.clear();
+      {
+        const int wper = ((((s_end - c0) + kAttnWarps - 1) / kAttnWarps) + 15) / 16 * 16;
+        const int first = c0 + warp * wper;
+        const int last = min(s_end, first + wper);
+        if (first < last) wa.template run<kSrcShared, false>(sp, qf, rows1, b, first, 16, last, lane, /*fresh=*/false, /*finish=*/false);
       }
+      if (s_end < c1) {  // the share's rows beyond the staging area, from the cache (this CTA's own append included)
+        rows1.k = kglob;
+        rows1.v = vglob;
+        rows1.stride = ROW_BYTES;
+        const int wper = ((((c1 - s_end) + kAttnWarps - 1) / kAttnWarps) + 15) / 16 * 16;
+        const int first = s_end + warp * wper;
+        const int last = min(c1, first + wper);
+        if (first < last)
+          wa.template run<kSrcGlobalCoherent, false>(sp, qf, rows1, b, first, 16, last, lane, /*fresh=*/false, /*finish=*/false);
+      }
+      wa.finish_sums();
       if (tracer && live) p.trace[4] = global_timer_ns();
+      __syncthreads();  // the staged rows are dead: the parked outputs take their place
       wa.park(sm.sm_m, sm.sm_l, sm_o, warp, lane);
     } else {
+      const int wper = ((((c1 - c0) + kAttnWarps - 1) / kAttnWarps) + 15) / 16 * 16;
+      const int first = c0 + warp * wper;
+      const int last = min(c1, first + wper);
       WA wa;
       if (first >= last) {
         wa.clear();
@@ -1021,7 +1035,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
     }
     __syncthreads();
     if (tracer && live) p.trace[5] = global_timer_ns();
-    if (pass == (kAttnDryRun ? 0 : 1)) cluster_wait();  // phase 0, once
+    cluster_wait();  // phase 0
     // head h goes to CTA h (n <= 8 = cluster size)
     for (int head = 0; head < p.n; ++head) {
       const uint32_t dst = map_to_rank(smem_u32(&sm.inbox[rank][0]), (uint32_t)head);
@@ -1103,8 +1117,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
       }
     }
     if (tracer && live) p.trace[8] = global_timer_ns();
-
-    __syncthreads();  // the next pass reuses the shared buffers
   }
 }
 
@@ -1288,14 +1300,14 @@ int pick_chunk_tokens(int b, int s_max, int shared_kv) {
   // heads x 256): 64-token chunks 128 us, 128 tokens 101 us, 256 tokens 95 us per layer
   if (shared_kv) {
     static const int chunk = [] {  // B200_ROWS_CHUNK: measurement knob
-      const char* e = getenv("B200_ROWS_CHUNK");
+      const char* e = tuning_env("B200_ROWS_CHUNK");
       const int v = e ? atoi(e) : 0;
       return (v == 64 || v == 128 || v == 256 || v == 512) ? v : 256;
     }();
     return chunk;
   }
   static const int forced = [] {  // B200_SDPA_CHUNK: measurement knob
-    const char* e = getenv("B200_SDPA_CHUNK");
+    const char* e = tuning_env("B200_SDPA_CHUNK");
     const int v = e ? atoi(e) : 0;
     return (v == 64 || v == 128 || v == 256 || v == 512) ? v : 0;
   }();
@@ -1315,7 +1327,7 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
   cudaError_t e;
   bool staged = false;
   static const bool ring_env = [] {  // B200_SDPA_RING=0: measurement knob, keeps the register-fed kernel
-    const char* e = getenv("B200_SDPA_RING");
+    const char* e = tuning_env("B200_SDPA_RING");
     return !(e && e[0] == '0');
   }();
   if constexpr (KV != kKvF32) {
@@ -1329,7 +1341,7 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
       int stages = std::min(kRingStagesMax, chunk_tokens / kRingTokens);
       stages = std::min(stages, std::max(1, (104 * 1024) / L::kStageBytes));
       static const int stages_env = [] {  // B200_SDPA_STAGES: measurement knob
-        const char* e = getenv("B200_SDPA_STAGES");
+        const char* e = tuning_env("B200_SDPA_STAGES");
         return e ? atoi(e) : 0;
       }();
       if (stages_env >= 1 && stages_env <= kRingStagesMax) stages = std::min(stages, stages_env);
@@ -1376,7 +1388,7 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
     // prompt pass: a warp per row, the CTA's rows share the chunk's traffic; long passes
     const dim3 rgrid(chunks_max, p.nkv, (p.b + kWarps - 1) / kWarps);
     static const int gpi = [] {  // B200_ROWS_GPI: measurement knob
-      const char* e = getenv("B200_ROWS_GPI");
+      const char* e = tuning_env("B200_ROWS_GPI");
       return e ? atoi(e) : 4;
     }();
     if (gpi == 1) {
@@ -1430,14 +1442,16 @@ cudaError_t launch_kv(const SdpaParams& p, cudaStream_t s) {
 template <int KV, int H>
 cudaError_t launch_attn_step_h(const AttnStepParams& p, cudaStream_t s) {
   constexpr size_t kBudget = 224 * 1024;
-  const size_t fixed = ((sizeof(AttnStepSmem<H>) + 127) / 128) * 128 + attn_park_bytes<H>();
+  const size_t fixed = ((sizeof(AttnStepSmem<H>) + 127) / 128) * 128;
   const int pitch = attn_row_pitch<KV, H>();
-  // as many staged rows as a CTA's share of the longest cache needs, within the budget
+  // as many staged rows as a CTA's share of the longest cache needs, within the budget (the warps'
+  // parked outputs take the staging area's place after the token loop)
   const int per_max = ((p.s_max + kAttnCluster - 1) / kAttnCluster + 15) / 16 * 16;
   int rows = (int)((kBudget - fixed) / (2 * (size_t)pitch));
-  rows = rows / 8 * 8;  // keeps the parked outputs 128-byte aligned
+  rows = rows / 8 * 8;
   if (rows > per_max) rows = per_max;
-  const size_t smem = fixed + 2 * (size_t)rows * pitch;
+  const size_t staging = 2 * (size_t)rows * pitch;
+  const size_t smem = fixed + (staging > attn_park_bytes<H>() ? staging : attn_park_bytes<H>());
   auto go = [&](auto kernel) -> cudaError_t {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

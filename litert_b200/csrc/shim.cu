@@ -63,7 +63,7 @@ Scratch carve_scratch(void* base, int m, int k_tiles8) {
 bool use_umma() {
   static int cached = -1;
   if (cached < 0) {
-    const char* e = getenv("B200_FC_PATH");
+    const char* e = b200::tuning_env("B200_FC_PATH");
     cached = (e && !strcmp(e, "mma")) ? 0 : 1;
   }
   return cached == 1;

@@ -179,10 +179,11 @@ def _attention_reference(oracle, q_rot, k_rows, v_rows, scale):
 
 
 @pytest.mark.parametrize("kv", ["f16", "i8"])
-@pytest.mark.parametrize("positions", [[0], [69], [1039], [7999], [3, 70, 1040, 5000]])
+@pytest.mark.parametrize("positions", [[0], [69], [1039], [1250], [1299], [2440], [7999], [3, 70, 1040, 5000]])
 def test_attention_step_against_the_float_restatement(oracle, kv, positions):
     """attn_step_cluster_kernel: rotation + append + attention + quantization in one launch, at 1, 70,
-    1040 and 8000 cached tokens (the new one included)."""
+    1040 and 8000 cached tokens (the new one included); 1251, 1300 and 2441 tokens give a CTA a share a
+    little longer than its staging area (fp16 and int8 rows), whose tail is read from the cache."""
     from litert_b200 import ops
 
     max_seq = 8192
