@@ -299,12 +299,20 @@ B200_API int b200_attention_step(const float* d_qkv, const int32_t* d_positions,
 
 /* b200_sdpa_decode whose [b, n * h] result leaves as quantized tiled rows (the
  * attention-output projection's input) instead of floats. fp16 / int8 caches,
- * at most 8 query heads per KV head, head size 64/128/256. */
+ * at most 8 query heads per KV head, head size 64/128/256. The _masked form
+ * also takes float32 caches, the composite's additive mask [b, 1, 1, s_max]
+ * (tflite/experimental/genai/sdpa.cc:376-386) and its logit cap. */
 B200_API int b200_sdpa_decode_quantized(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale,
                                         const float* d_v_scale, const int32_t* d_lengths, int b, int n, int nkv, int h,
                                         int s_max, int q_dtype, int kv_dtype, float scale, int8_t* d_q_tiled,
                                         float* d_scales, int32_t* d_zero_points, void* d_workspace,
                                         size_t workspace_bytes, void* stream);
+B200_API int b200_sdpa_decode_quantized_masked(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale,
+                                               const float* d_v_scale, const int32_t* d_lengths, const float* d_mask,
+                                               int b, int n, int nkv, int h, int s_max, int q_dtype, int kv_dtype,
+                                               float scale, float logit_cap, int8_t* d_q_tiled, float* d_scales,
+                                               int32_t* d_zero_points, void* d_workspace, size_t workspace_bytes,
+                                               void* stream);
 
 /* b200_fc_hybrid on rows that are already quantized (tiled rows + per-row scale
  * and zero point from one of the ops above): the second half of EvalHybridDense

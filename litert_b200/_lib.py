@@ -58,6 +58,8 @@ SIGNATURES = {
     "b200_attention_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp]),
     "b200_sdpa_decode_quantized": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp,
                                         _vp, _sz, _vp]),
+    "b200_sdpa_decode_quantized_masked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp,
+                                               _vp, _vp, _vp, _sz, _vp]),
     "b200_fc_hybrid_quantized": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp]),
     "b200_elementwise_last_error": (ctypes.c_char_p, []),
     "b200_binary_f32": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

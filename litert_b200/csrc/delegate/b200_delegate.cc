@@ -146,6 +146,8 @@ enum class OpKind {
   // produced by the fusion pass over a partition's ops (never by Classify)
   kNormQuant,      // odml.rms_norm whose result only feeds hybrid projections: normalised AND quantized once
   kFcQuantized,    // a hybrid projection reading rows another op already quantized
+  kSdpaQuant,      // the attention composite (one query token) whose result only feeds a hybrid projection: leaves quantized
+  kFcGroup,        // several such projections of the same single row (q, k, v) as one GEMV over the stacked weights
   kGateUpGeglu,    // gate and up projections as one GEMV + GELU x up + quantization for the down projection
   kLmHeadPick,     // the vocabulary projection with ARG_MAX in its epilogue: no logits are written
   kRope,           // SLICE / SLICE / MUL(-1) / CONCATENATION / MUL / MUL / ADD of the rotary embedding as one kernel
@@ -515,6 +517,7 @@ struct OpRecord {
   std::vector<int> all_in, all_out;
   // fused ops
   int rows_from = -1;               // kFcQuantized: index (in the partition) of the op that holds its quantized rows
+  std::vector<std::pair<int, int>> group_out;  // kFcGroup: (result tensor, first channel in the stacked output)
   DeviceMem q_tiled, q_scales, q_zps, tmp_f32;  // kNormQuant / kGateUpGeglu: the quantized rows they produce
   int heads = 0;
   // glue ops
@@ -772,6 +775,53 @@ class DelegateKernel {
       ops_[down_i]->rows_from = i;
       ops_[down_i]->m = m;
     }
+    // (3b) what is left of the projections that read the same quantized rows (q, k and v after a norm): with
+    // one row per call their results are consecutive slices of one stacked GEMV's output row
+    for (int i = 0; i < n_ops; ++i) {
+      if (ops_[i]->kind != OpKind::kNormQuant || ops_[i]->rows != 1) continue;
+      std::vector<int> sib;
+      for (int u = 0; u < n_ops; ++u) {
+        const OpRecord& f = *ops_[u];
+        if (f.kind == OpKind::kFcQuantized && f.rows_from == i && f.m == 1 && f.per_channel && !f.bias.ptr && !f.activation &&
+            f.kdim == ops_[i]->width)
+          sib.push_back(u);
+      }
+      if (sib.size() < 2) continue;
+      OpRecord& lead = *ops_[sib[0]];
+      const int k = lead.kdim;
+      int total = 0;
+      for (int u : sib) total += ops_[u]->n;
+      std::vector<int8_t> stacked(static_cast<size_t>(total) * k);
+      std::vector<float> scales(static_cast<size_t>(total));
+      std::vector<std::pair<int, int>> outs;
+      int at = 0;
+      for (int u : sib) {
+        const OpRecord& f = *ops_[u];
+        const TfLiteTensor& w = T[f.all_in[1]];
+        memcpy(stacked.data() + static_cast<size_t>(at) * k, w.data.int8, static_cast<size_t>(f.n) * k);
+        const auto* q = Affine(w);
+        for (int c = 0; c < f.n; ++c) scales[at + c] = q->scale->data[c];
+        outs.emplace_back(f.y, at);
+        at += f.n;
+      }
+      if (!lead.tmp_f32.ensure(sizeof(float) * static_cast<size_t>(total))) {
+        TF_LITE_KERNEL_LOG(ctx, "B200 delegate: device allocation failed (stacked projections)");
+        return kTfLiteDelegateError;
+      }
+      TF_LITE_ENSURE_STATUS(PackInt8(ctx, stacked.data(), total, k, false, &lead));
+      TF_LITE_ENSURE_STATUS(Upload(ctx, scales, &lead.w_scales));
+      CUDA_OK(ctx, cudaStreamSynchronize(st_->stream));
+      for (size_t j = 1; j < sib.size(); ++j) {
+        OpRecord& f = *ops_[sib[j]];
+        f.packed.reset();
+        f.row_sums.reset();
+        f.w_scales.reset();
+        f.kind = OpKind::kSkipped;
+      }
+      lead.kind = OpKind::kFcGroup;
+      lead.n = total;
+      lead.group_out = outs;
+    }
     // (2b) the residual ADD in front of such a norm moves into it: h += delta in place, then normalise and
     // quantize. The sum tensor becomes another name for h's buffer, which no one else may still need.
     for (int i = 0; i < n_ops; ++i) {
@@ -794,6 +844,28 @@ class DelegateKernel {
       inplace_alias_[add.y] = h;
       norm.ins = {h, delta};
       add.kind = OpKind::kSkipped;
+    }
+    // (5) one-token attention read only by a hybrid projection (through RESHAPEs): the merge of the
+    // attention partials quantizes the row for that projection, no float result, no separate row kernel
+    for (int i = 0; i < n_ops; ++i) {
+      OpRecord& at = *ops_[i];
+      if (at.kind != OpKind::kSdpa || at.T != 1 || at.sdpa_dtype != B200_DTYPE_F32 || IsPartitionOutput(at.y)) continue;
+      if (at.N % at.Nkv || at.N / at.Nkv > 8 || at.N > 64 || (at.H != 64 && at.H != 128 && at.H != 256)) continue;
+      int y = at.y, user = OnlyConsumer(y);
+      bool through_ok = true;
+      for (int hops = 0; hops < 4 && user >= 0 && ops_[user]->kind == OpKind::kReshape; ++hops) {
+        if (IsPartitionOutput(ops_[user]->y)) through_ok = false;
+        y = ops_[user]->y;
+        user = OnlyConsumer(y);
+      }
+      if (!through_ok || user < 0) continue;
+      OpRecord& fc = *ops_[user];
+      if (fc.kind != OpKind::kFcHybrid || !fc.asymmetric || fc.x != y || fc.kdim != at.N * at.H) continue;
+      if (!AllocRows(ctx, &at, at.B, at.N * at.H)) return kTfLiteDelegateError;
+      at.kind = OpKind::kSdpaQuant;
+      fc.kind = OpKind::kFcQuantized;
+      fc.rows_from = i;
+      fc.m = at.B;
     }
     // (4) a projection read only by ARG_MAX (the LM head under greedy sampling): the pick moves into its epilogue
     for (int i = 0; i < n_ops; ++i) {
@@ -847,6 +919,9 @@ class DelegateKernel {
       if (opp->kind == OpKind::kKvCache) {
         persistent_[opp->y] = opp->k_cache.ptr;
         persistent_[opp->y2] = opp->v_cache.ptr;
+      } else if (opp->kind == OpKind::kFcGroup) {
+        // the members' results are slices of the group's own output row
+        for (const auto& o : opp->group_out) persistent_[o.first] = static_cast<float*>(opp->tmp_f32.ptr) + o.second;
       }
     std::vector<b200::ArenaRequest> req;
     const int num_ops = static_cast<int>(ops_.size());
@@ -869,7 +944,10 @@ class DelegateKernel {
     size_t scratch = 0, sdpa = 0, bmm_lhs = 0, bmm_rhs = 0, bmm_packed = 0, bmm_rs = 0;
     for (int i = 0; i < num_ops; ++i) {
       OpRecord& op = *ops_[i];
-      if (op.kind == OpKind::kSdpa) {
+      if (op.kind == OpKind::kSdpaQuant) {
+        for (int t : {op.q, op.k, op.v, op.mask}) touch(t, i);
+        sdpa = std::max(sdpa, b200_sdpa_workspace_bytes(op.B, op.N, op.Nkv, op.H, op.S));
+      } else if (op.kind == OpKind::kSdpa) {
         for (int t : {op.q, op.k, op.v, op.mask, op.y}) touch(t, i);
         sdpa = std::max(sdpa, b200_sdpa_workspace_bytes(op.B * op.T, op.N, op.Nkv, op.H, op.S));
       } else if (op.kind == OpKind::kBmmHybrid || op.kind == OpKind::kBmmInt8) {
@@ -891,8 +969,8 @@ class DelegateKernel {
         touch(op.y, i);
       } else if (op.kind == OpKind::kLmHeadPick) {
         touch(op.y, i);
-      } else if (op.kind == OpKind::kGateUpGeglu) {
-        continue;  // reads another op's quantized rows, writes its own: no arena tensor
+      } else if (op.kind == OpKind::kGateUpGeglu || op.kind == OpKind::kFcGroup) {
+        continue;  // reads another op's quantized rows, writes its own buffer: no arena tensor
       } else if (op.kind >= OpKind::kEmbedding) {
         for (int t : op.ins) touch(t, i);
         if (op.kind == OpKind::kNormQuant) continue;  // its float32 result is never materialised
@@ -1473,6 +1551,16 @@ class DelegateKernel {
                                                          static_cast<float*>(Dev(op.y)), st_->zero_ws.ptr, s));
         return kTfLiteOk;
       }
+      case OpKind::kFcGroup: {
+        const OpRecord& src = *ops_[op.rows_from];
+        B200_GLUE_OR_RETURN(ctx, b200_fc_hybrid_quantized(static_cast<const int8_t*>(src.q_tiled.ptr),
+                                                         static_cast<const float*>(src.q_scales.ptr),
+                                                         static_cast<const int32_t*>(src.q_zps.ptr), 1, op.kdim, op.packed.ptr, op.n,
+                                                         static_cast<const int32_t*>(op.row_sums.ptr),
+                                                         static_cast<const float*>(op.w_scales.ptr), 1, nullptr, 0,
+                                                         static_cast<float*>(op.tmp_f32.ptr), st_->zero_ws.ptr, s));
+        return kTfLiteOk;
+      }
       case OpKind::kLmHeadPick: {
         const OpRecord& src = *ops_[op.rows_from];
         uint8_t* ws = static_cast<uint8_t*>(op.ws_small.ptr);
@@ -1500,6 +1588,14 @@ class DelegateKernel {
                                                     static_cast<int32_t*>(op.q_zps.ptr), s));
         return kTfLiteOk;
       }
+      case OpKind::kSdpaQuant:
+        B200_GLUE_OR_RETURN(ctx, b200_sdpa_decode_quantized_masked(
+                                     Dev(op.q), Dev(op.k), Dev(op.v), nullptr, nullptr, nullptr,
+                                     op.mask >= 0 ? static_cast<const float*>(Dev(op.mask)) : nullptr, op.B, op.N, op.Nkv, op.H,
+                                     op.S, op.sdpa_dtype, op.sdpa_dtype, op.scale, op.logit_cap,
+                                     static_cast<int8_t*>(op.q_tiled.ptr), static_cast<float*>(op.q_scales.ptr),
+                                     static_cast<int32_t*>(op.q_zps.ptr), st_->sdpa_ws.ptr, st_->sdpa_ws.bytes, s));
+        return kTfLiteOk;
       case OpKind::kSdpa:
         if (op.T == 1) {
           B200_OK_OR_RETURN(ctx, b200_sdpa_decode(Dev(op.q), Dev(op.k), Dev(op.v), nullptr, nullptr, nullptr,

@@ -189,34 +189,49 @@ int b200_attention_step(const float* d_qkv, const int32_t* d_positions, const fl
   return gcuda(launch_attn_step(ap, static_cast<cudaStream_t>(stream)), "b200_attention_step");
 }
 
-int b200_sdpa_decode_quantized(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale,
-                               const float* d_v_scale, const int32_t* d_lengths, int b, int n, int nkv, int h, int s_max,
-                               int q_dtype, int kv_dtype, float scale, int8_t* d_q_tiled, float* d_scales,
-                               int32_t* d_zero_points, void* d_workspace, size_t workspace_bytes, void* stream) {
+int b200_sdpa_decode_quantized_masked(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale,
+                                      const float* d_v_scale, const int32_t* d_lengths, const float* d_mask, int b, int n,
+                                      int nkv, int h, int s_max, int q_dtype, int kv_dtype, float scale, float logit_cap,
+                                      int8_t* d_q_tiled, float* d_scales, int32_t* d_zero_points, void* d_workspace,
+                                      size_t workspace_bytes, void* stream) {
+  const char* name = "b200_sdpa_decode_quantized";
   if (!d_q || !d_k || !d_v || !d_q_tiled || !d_scales || !d_zero_points || b <= 0 || n <= 0 || nkv <= 0 || n % nkv || h <= 0 || s_max <= 0)
-    return gfail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa_decode_quantized: bad argument");
-  if (q_dtype != B200_DTYPE_F16 && q_dtype != B200_DTYPE_F32) return gfail(B200_ERR_UNSUPPORTED, "b200_sdpa_decode_quantized: q dtype %d", q_dtype);
-  if (kv_dtype != B200_DTYPE_F16 && kv_dtype != B200_DTYPE_I8) return gfail(B200_ERR_UNSUPPORTED, "b200_sdpa_decode_quantized: kv dtype %d", kv_dtype);
-  if (kv_dtype == B200_DTYPE_I8 && (!d_k_scale || !d_v_scale)) return gfail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa_decode_quantized: int8 cache needs scales");
+    return gfail(B200_ERR_INVALID_ARGUMENT, "%s: bad argument", name);
+  if (q_dtype != B200_DTYPE_F16 && q_dtype != B200_DTYPE_F32) return gfail(B200_ERR_UNSUPPORTED, "%s: q dtype %d", name, q_dtype);
+  if (kv_dtype != B200_DTYPE_F16 && kv_dtype != B200_DTYPE_I8 && kv_dtype != B200_DTYPE_F32)
+    return gfail(B200_ERR_UNSUPPORTED, "%s: kv dtype %d", name, kv_dtype);
+  if (kv_dtype == B200_DTYPE_I8 && (!d_k_scale || !d_v_scale)) return gfail(B200_ERR_INVALID_ARGUMENT, "%s: int8 cache needs scales", name);
   if (n / nkv > 8 || (h != 64 && h != 128 && h != 256))
-    return gfail(B200_ERR_UNSUPPORTED, "b200_sdpa_decode_quantized: at most 8 query heads per KV head, head size 64, 128 or 256");
+    return gfail(B200_ERR_UNSUPPORTED, "%s: at most 8 query heads per KV head, head size 64, 128 or 256", name);
+  if (n > 64) return gfail(B200_ERR_UNSUPPORTED, "%s: at most 64 query heads", name);
   if (!d_workspace || workspace_bytes < sdpa_workspace_bytes(b, n, nkv, h, s_max))
-    return gfail(B200_ERR_INVALID_ARGUMENT, "b200_sdpa_decode_quantized: workspace too small (b200_sdpa_workspace_bytes)");
+    return gfail(B200_ERR_INVALID_ARGUMENT, "%s: workspace too small (b200_sdpa_workspace_bytes)", name);
   SdpaParams p;
   memset(&p, 0, sizeof(p));
   p.q = d_q; p.k = d_k; p.v = d_v; p.k_scale = d_k_scale; p.v_scale = d_v_scale;
   p.lengths = d_lengths;
+  p.mask = d_mask;
   p.b = b; p.n = n; p.nkv = nkv; p.h = h; p.s_max = s_max;
   p.q_dtype = q_dtype == B200_DTYPE_F32 ? 1 : 0;
   p.kv_dtype = kv_dtype;
   p.scale = scale > 0.0f ? scale : 1.0f / sqrtf((float)h);
+  p.logit_cap = logit_cap;
   p.q_tiled_out = d_q_tiled;
   p.out_scales = d_scales;
   p.out_zps = d_zero_points;
   p.m_alloc = m_alloc_for(b);
   p.ws = static_cast<float*>(d_workspace);
   p.ws_bytes = workspace_bytes;
-  return gcuda(launch_sdpa_decode(p, static_cast<cudaStream_t>(stream)), "b200_sdpa_decode_quantized");
+  return gcuda(launch_sdpa_decode(p, static_cast<cudaStream_t>(stream)), name);
+}
+
+int b200_sdpa_decode_quantized(const void* d_q, const void* d_k, const void* d_v, const float* d_k_scale,
+                               const float* d_v_scale, const int32_t* d_lengths, int b, int n, int nkv, int h, int s_max,
+                               int q_dtype, int kv_dtype, float scale, int8_t* d_q_tiled, float* d_scales,
+                               int32_t* d_zero_points, void* d_workspace, size_t workspace_bytes, void* stream) {
+  return b200_sdpa_decode_quantized_masked(d_q, d_k, d_v, d_k_scale, d_v_scale, d_lengths, nullptr, b, n, nkv, h, s_max,
+                                           q_dtype, kv_dtype, scale, 0.0f, d_q_tiled, d_scales, d_zero_points, d_workspace,
+                                           workspace_bytes, stream);
 }
 
 int b200_fc_hybrid_quantized(const int8_t* d_q_tiled, const float* d_scales, const int32_t* d_zero_points, int m, int k,
