@@ -445,12 +445,16 @@ struct RingLayout {
 
 template <int KV, int H, bool QF32>
 __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_ring_kernel(const SdpaParams p, const int chunk_tokens,
-                                                                       const int chunks_max, const int stages) {
+                                                                       const int chunks_max, const int stages,
+                                                                       const int stage_tokens) {
   using WA = WarpAttention<KV, H, 1>;
   using L = RingLayout<KV, H>;
   constexpr int KSTEPS = WA::KSTEPS;
   static_assert(kWarps * 32 == 2 * kRingTokens, "one row copy per thread and stage");
   static_assert(kWarps * 16 == kRingTokens, "one 16-token group per warp and stage");
+  // `stage_tokens` (a multiple of 16, at most kRingTokens) tokens per stage: two stages must fit beside a
+  // second CTA on the SM, so that the copy of the next stage runs under the arithmetic of this one
+  const int stage_bytes = 2 * stage_tokens * L::kPitch;
   extern __shared__ __align__(128) uint8_t ring_smem[];
   __shared__ float sm_m[kWarps][8], sm_l[kWarps][8];
   __shared__ int s_abort;
@@ -472,23 +476,37 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_ring_kernel(const Sdp
   const int c0 = chunk * chunk_tokens;
   if (c0 >= len) return;  // uniform over the CTA, nothing in flight
   const int c1 = min(len, c0 + chunk_tokens);
-  const int n_sub = (c1 - c0 + kRingTokens - 1) / kRingTokens;
+  const int n_sub = (c1 - c0 + stage_tokens - 1) / stage_tokens;
   const int g = lane >> 2, t = lane & 3;
   const int group = p.n / p.nkv;
   const typename WA::Rows cache = WA::cache_rows(p, b, kvh);
+  // With one kv head the cached rows of consecutive tokens follow one another in memory: a stage is then
+  // ONE bulk copy per operand (32 KB of fp16 rows) instead of one per row, unpadded in shared memory. (128
+  // copies of 512 bytes per stage keep the copy engine busier issuing than moving; the 2- to 4-way bank
+  // conflicts of the unpadded rows cost the fragment loads less than that.)
+  const bool contiguous = cache.stride == (size_t)L::kRowBytes;
+  const int pitch = contiguous ? L::kRowBytes : L::kPitch;
 
   // stage `s` <- tokens [c0 + j * 64, ...): thread r (< 64) fetches key row r, thread 64 + r value row r
   auto issue = [&](int j) {
     const int s = j % stages;
-    const int t0 = c0 + j * kRingTokens;
-    const int rows = min(kRingTokens, c1 - t0);
-    uint8_t* stage = ring + (size_t)s * L::kStageBytes;
+    const int t0 = c0 + j * stage_tokens;
+    const int rows = min(stage_tokens, c1 - t0);
+    uint8_t* stage = ring + (size_t)s * stage_bytes;
     if (tid == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(2 * rows * L::kRowBytes));
+    if (contiguous) {
+      if (tid == 0) {
+        bulk_g2s(stage, cache.k + (size_t)t0 * cache.stride, (uint32_t)(rows * L::kRowBytes), &full_bar[s]);
+        bulk_g2s(stage + (size_t)stage_tokens * L::kPitch, cache.v + (size_t)t0 * cache.stride, (uint32_t)(rows * L::kRowBytes),
+                 &full_bar[s]);
+      }
+      return;
+    }
     const int r = tid & (kRingTokens - 1);
     if (r < rows) {
       const bool is_v = tid >= kRingTokens;
       const uint8_t* src = (is_v ? cache.v : cache.k) + (size_t)(t0 + r) * cache.stride;
-      bulk_g2s(stage + (size_t)(is_v ? kRingTokens : 0) * L::kPitch + (size_t)r * L::kPitch, src, L::kRowBytes, &full_bar[s]);
+      bulk_g2s(stage + (size_t)(is_v ? stage_tokens : 0) * L::kPitch + (size_t)r * L::kPitch, src, L::kRowBytes, &full_bar[s]);
     }
   };
   int issued = min(stages, n_sub);
@@ -518,15 +536,15 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_ring_kernel(const Sdp
   for (int j = 0; j < n_sub; ++j) {
     const int s = j % stages;
     mbar_wait_bounded(&full_bar[s], (uint32_t)(j / stages) & 1u, abort_flag, p.status, kStatusWaitTimeoutFull);
-    const int t0 = c0 + j * kRingTokens;
-    const int t1 = min(c1, t0 + kRingTokens);
+    const int t0 = c0 + j * stage_tokens;
+    const int t1 = min(c1, t0 + stage_tokens);
     const int first = t0 + warp * 16;
     if (first < t1 && !*abort_flag) {
       typename WA::Rows rows = cache;  // scales stay in global memory
-      const uint8_t* stage = ring + (size_t)s * L::kStageBytes;
-      rows.k = stage - (ptrdiff_t)t0 * L::kPitch;  // indexed by absolute token
-      rows.v = stage + (size_t)kRingTokens * L::kPitch - (ptrdiff_t)t0 * L::kPitch;
-      rows.stride = L::kPitch;
+      const uint8_t* stage = ring + (size_t)s * stage_bytes;
+      rows.k = stage - (ptrdiff_t)t0 * pitch;  // indexed by absolute token
+      rows.v = stage + (size_t)stage_tokens * L::kPitch - (ptrdiff_t)t0 * pitch;
+      rows.stride = pitch;
       wa.template run<kSrcShared>(p, qf, rows, b, first, kRingTokens, t1, lane, /*fresh=*/false, /*finish=*/false);
     }
     __syncthreads();  // every warp is done with stage s
@@ -538,7 +556,8 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_decode_ring_kernel(const Sdp
   wa.finish_sums();
   // after an abort: the latest copies towards each stage may still be in flight
   if (*abort_flag)
-    for (int j = max(0, issued - stages); j < issued; ++j) mbar_drain_bounded(&full_bar[j % stages], (uint32_t)(j / stages) & 1u);
+    for (int j = max(0, issued - stages); j < issued; ++j)
+      mbar_drain_bounded(&full_bar[j % stages], (uint32_t)(j / stages) & 1u);
   __syncthreads();
 
   // ---- merge the warps of this CTA (the parked outputs reuse the ring) ----
@@ -629,11 +648,13 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_rows_kernel(const SdpaParams
 // record) over each stage, masked at the row's own length.
 template <int KV, int H, bool QF32>
 __global__ void __launch_bounds__(kWarps * 32) sdpa_rows_ring_kernel(const SdpaParams p, const int chunk_tokens,
-                                                                     const int chunks_max, const int stages) {
+                                                                     const int chunks_max, const int stages,
+                                                                     const int stage_tokens) {
   using WA = WarpAttention<KV, H, 4>;  // one pass of 64 tokens per stage
   using L = RingLayout<KV, H>;
   constexpr int KSTEPS = WA::KSTEPS;
   static_assert(WA::kTokensPerWarpIter == kRingTokens, "a warp takes a whole stage per pass");
+  const int stage_bytes = 2 * stage_tokens * L::kPitch;  // (stage_tokens <= kRingTokens: see the decode kernel's launcher)
   extern __shared__ __align__(128) uint8_t ring_smem[];
   __shared__ float sm_m[kWarps][8], sm_l[kWarps][8];
   __shared__ int s_abort;
@@ -661,22 +682,22 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_rows_ring_kernel(const SdpaP
   if (c0 >= len_cta) return;  // uniform over the CTA, nothing in flight
   const int c1 = min(len_cta, c0 + chunk_tokens);
   const int len_w = row_ok ? length_of(b) : 0;
-  const int n_sub = (c1 - c0 + kRingTokens - 1) / kRingTokens;
+  const int n_sub = (c1 - c0 + stage_tokens - 1) / stage_tokens;
   const int g = lane >> 2, t = lane & 3;
   const int group = p.n / p.nkv;
   const typename WA::Rows cache = WA::cache_rows(p, 0, kvh);  // shared_kv: one cache for all rows
 
   auto issue = [&](int j) {
     const int s = j % stages;
-    const int t0 = c0 + j * kRingTokens;
-    const int rows = min(kRingTokens, c1 - t0);
-    uint8_t* stage = ring + (size_t)s * L::kStageBytes;
+    const int t0 = c0 + j * stage_tokens;
+    const int rows = min(stage_tokens, c1 - t0);
+    uint8_t* stage = ring + (size_t)s * stage_bytes;
     if (tid == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(2 * rows * L::kRowBytes));
     const int r = tid & (kRingTokens - 1);
     if (r < rows) {
       const bool is_v = tid >= kRingTokens;
       const uint8_t* src = (is_v ? cache.v : cache.k) + (size_t)(t0 + r) * cache.stride;
-      bulk_g2s(stage + (size_t)(is_v ? kRingTokens : 0) * L::kPitch + (size_t)r * L::kPitch, src, L::kRowBytes, &full_bar[s]);
+      bulk_g2s(stage + (size_t)(is_v ? stage_tokens : 0) * L::kPitch + (size_t)r * L::kPitch, src, L::kRowBytes, &full_bar[s]);
     }
   };
   int issued = min(stages, n_sub);
@@ -705,13 +726,13 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_rows_ring_kernel(const SdpaP
   for (int j = 0; j < n_sub; ++j) {
     const int s = j % stages;
     mbar_wait_bounded(&full_bar[s], (uint32_t)(j / stages) & 1u, abort_flag, p.status, kStatusWaitTimeoutFull);
-    const int t0 = c0 + j * kRingTokens;
-    const int t1 = min(min(c1, t0 + kRingTokens), len_w);  // this row's own causal limit
+    const int t0 = c0 + j * stage_tokens;
+    const int t1 = min(min(c1, t0 + stage_tokens), len_w);  // this row's own causal limit
     if (t0 < t1 && !*abort_flag) {
       typename WA::Rows rows = cache;
-      const uint8_t* stage = ring + (size_t)s * L::kStageBytes;
+      const uint8_t* stage = ring + (size_t)s * stage_bytes;
       rows.k = stage - (ptrdiff_t)t0 * L::kPitch;
-      rows.v = stage + (size_t)kRingTokens * L::kPitch - (ptrdiff_t)t0 * L::kPitch;
+      rows.v = stage + (size_t)stage_tokens * L::kPitch - (ptrdiff_t)t0 * L::kPitch;
       rows.stride = L::kPitch;
       wa.template run<kSrcShared>(p, qf, rows, b, t0, kRingTokens, t1, lane, /*fresh=*/false, /*finish=*/false);
     }
@@ -1120,10 +1141,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
   }
 }
 
-// Reduces the per-chunk partials of one (batch, query head): grid (n, b),
-// H threads.
+// Reduces the per-chunk partials of one (batch, query head): grid (n, b), H threads. The kernel is a chain
+// of L2 round trips, so they are made to overlap: every thread requests its element of the first chunks
+// at once, the first warp meanwhile gathers the chunks' maxima and sums (one chunk per lane and step) and
+// leaves the chunks' weights in shared memory, and the remaining chunks are summed eight loads at a time.
 template <int H, bool QF32>
 __global__ void sdpa_merge_kernel(const SdpaParams p, const int chunk_tokens, const int chunks_max) {
+  extern __shared__ float merge_w[];  // [chunks_max] weights exp2(m_chunk - m)
+  __shared__ float s_l;
   pdl_enter();
   const int b = blockIdx.y, head = blockIdx.x, d = threadIdx.x;
   const int group = p.n / p.nkv;
@@ -1132,15 +1157,42 @@ __global__ void sdpa_merge_kernel(const SdpaParams p, const int chunk_tokens, co
   const int chunks = (len + chunk_tokens - 1) / chunk_tokens;
   const float* base = p.ws + ((((size_t)b * p.nkv + kvh) * chunks_max) * 8 + hg) * partial_stride(H);
   const size_t cstride = 8 * partial_stride(H);
-  float mm = -CUDART_INF_F;
-  for (int c = 0; c < chunks; ++c) mm = fmaxf(mm, base[c * cstride + H]);
-  const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
-  float acc = 0.0f, l = 0.0f;
-  for (int c = 0; c < chunks; ++c) {
-    const float f = exp2f(base[c * cstride + H] - muse);
-    acc += f * base[c * cstride + d];
-    l += f * base[c * cstride + H + 1];
+  constexpr int kPre = 16;
+  float pre[kPre];
+#pragma unroll
+  for (int j = 0; j < kPre; ++j) pre[j] = j < chunks ? base[j * cstride + d] : 0.0f;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float mm = -CUDART_INF_F;
+    for (int c = lane; c < chunks; c += 32) mm = fmaxf(mm, base[c * cstride + H]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    const float muse = mm == -CUDART_INF_F ? 0.0f : mm;
+    float l = 0.0f;
+    for (int c = lane; c < chunks; c += 32) {
+      const float f = exp2f(base[c * cstride + H] - muse);
+      merge_w[c] = f;
+      l += f * base[c * cstride + H + 1];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) s_l = l;
   }
+  __syncthreads();
+  float acc = 0.0f;
+  const int npre = chunks < kPre ? chunks : kPre;
+#pragma unroll
+  for (int j = 0; j < kPre; ++j)
+    if (j < npre) acc += merge_w[j] * pre[j];
+  for (int c = kPre; c < chunks; c += 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = c + j < chunks ? base[(size_t)(c + j) * cstride + d] : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (c + j < chunks) acc += merge_w[c + j] * v[j];
+  }
+  const float l = s_l;
   const float out = l > 0.0f ? acc / l : 0.0f;  // no cached token (or every key masked out): zeros, not 0 / 0
   const size_t oi = ((size_t)b * p.n + head) * H + d;
   if constexpr (QF32) {
@@ -1338,14 +1390,28 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
       // warps more than it wants depth. Measured on B200, 16 ragged sequences up to 8192 tokens, head
       // size 256: fp16 rows (68 KB per stage) 23.4 us with one stage, 31.4 with three (one CTA per
       // SM); int8 rows (35 KB) 18.4 us with three, 21.9 with one. The register-fed kernel: 24.8 / 68 us.
-      int stages = std::min(kRingStagesMax, chunk_tokens / kRingTokens);
-      stages = std::min(stages, std::max(1, (104 * 1024) / L::kStageBytes));
+      // Two CTAs per SM (about 104 KB each), at least two stages per CTA so that the next stage's copy runs
+      // under this stage's arithmetic: with ONE 64-token stage per CTA (three CTAs per SM) every CTA of the
+      // grid loads, computes, loads ... in step with the others, HBM idle half of the time (device-timer
+      // stamps of one CTA, 16 ragged sequences, fp16 rows: 2.0 us copy + 1.8 us arithmetic per stage, strictly
+      // in turn). Rows that do not fit two 64-token stages get shorter stages (fp16 at head size 256: 48).
+      int stage_tokens = kRingTokens;
+      while (stage_tokens > 16 && 2 * (2 * stage_tokens * L::kPitch) > 104 * 1024) stage_tokens -= 16;
+      const int stage_bytes = 2 * stage_tokens * L::kPitch;
+      int stages = std::min(kRingStagesMax, (chunk_tokens + stage_tokens - 1) / stage_tokens);
+      stages = std::min(stages, std::max(1, (104 * 1024) / stage_bytes));
       static const int stages_env = [] {  // B200_SDPA_STAGES: measurement knob
         const char* e = tuning_env("B200_SDPA_STAGES");
         return e ? atoi(e) : 0;
       }();
       if (stages_env >= 1 && stages_env <= kRingStagesMax) stages = std::min(stages, stages_env);
-      const size_t smem = L::smem_bytes(stages);
+      static const int tokens_env = [] {  // B200_SDPA_STAGE_TOKENS: measurement knob
+        const char* e = tuning_env("B200_SDPA_STAGE_TOKENS");
+        return e ? atoi(e) : 0;
+      }();
+      if (tokens_env == 16 || tokens_env == 32 || tokens_env == 48 || tokens_env == 64) stage_tokens = tokens_env;
+      const size_t ring_bytes = (size_t)stages * (2 * stage_tokens * L::kPitch);
+      const size_t smem = (ring_bytes > (size_t)L::kParkBytes ? ring_bytes : (size_t)L::kParkBytes) + 128;
       auto kernel = sdpa_decode_ring_kernel<KV, H, QF32>;
       static size_t configured[64] = {0};
       int dev = 0;
@@ -1356,7 +1422,7 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
         if (ea != cudaSuccess) return ea;
         configured[dev] = L::smem_bytes(kRingStagesMax);
       }
-      e = launch_chained(kernel, grid, dim3(kWarps * 32), smem, s, p, chunk_tokens, chunks_max, stages);
+      e = launch_chained(kernel, grid, dim3(kWarps * 32), smem, s, p, chunk_tokens, chunks_max, stages, stage_tokens);
       staged = true;
     }
   }
@@ -1364,9 +1430,20 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
     const bool aligned = ((reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v)) & 15) == 0;
     if (ring_env && p.shared_kv && aligned && chunk_tokens % kRingTokens == 0) {
       using L = RingLayout<KV, H>;
-      int stages = std::min(kRingStagesMax, chunk_tokens / kRingTokens);
-      stages = std::min(stages, std::max(1, (104 * 1024) / L::kStageBytes));
-      const size_t smem = L::smem_bytes(stages);
+      // Whole 64-token stages here, even when only one fits: a warp's pass covers 64 tokens, and this kernel
+      // is bound by its arithmetic, not by the copies (1024-token prompt, fp16 rows, measured per layer:
+      // 65.7 us with one 64-token stage, 75.8 with two of 48, 90.2 with three of 32).
+      int stage_tokens = kRingTokens;
+      static const int rtokens_env = [] {  // B200_ROWS_STAGE_TOKENS: measurement knob
+        const char* e = tuning_env("B200_ROWS_STAGE_TOKENS");
+        return e ? atoi(e) : 0;
+      }();
+      if (rtokens_env == 16 || rtokens_env == 32 || rtokens_env == 48 || rtokens_env == 64) stage_tokens = rtokens_env;
+      const int stage_bytes = 2 * stage_tokens * L::kPitch;
+      int stages = std::min(kRingStagesMax, (chunk_tokens + stage_tokens - 1) / stage_tokens);
+      stages = std::min(stages, std::max(1, (104 * 1024) / stage_bytes));
+      const size_t ring_bytes = (size_t)stages * stage_bytes;
+      const size_t smem = (ring_bytes > (size_t)L::kParkBytes ? ring_bytes : (size_t)L::kParkBytes) + 128;
       auto kernel = sdpa_rows_ring_kernel<KV, H, QF32>;
       static bool configured[64] = {false};
       int dev = 0;
@@ -1378,7 +1455,7 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
         configured[dev] = true;
       }
       const dim3 rgrid(chunks_max, p.nkv, (p.b + kWarps - 1) / kWarps);
-      e = launch_chained(kernel, rgrid, dim3(kWarps * 32), smem, s, p, chunk_tokens, chunks_max, stages);
+      e = launch_chained(kernel, rgrid, dim3(kWarps * 32), smem, s, p, chunk_tokens, chunks_max, stages, stage_tokens);
       staged = true;
     }
   }
@@ -1416,7 +1493,8 @@ cudaError_t launch_fast(const SdpaParams& p, cudaStream_t s) {
     // a few rows (a decode step): the widest block per row; many rows (a prompt chunk): several rows per SM
     return launch_chained(sdpa_merge_quant_kernel<H>, dim3(p.b), dim3(p.b > 32 ? 256 : 1024), smem, s, p, chunk_tokens, chunks_max);
   }
-  return launch_chained(sdpa_merge_kernel<H, QF32>, dim3(p.n, p.b), dim3(H), 0, s, p, chunk_tokens, chunks_max);
+  return launch_chained(sdpa_merge_kernel<H, QF32>, dim3(p.n, p.b), dim3(H), sizeof(float) * (size_t)chunks_max, s, p,
+                        chunk_tokens, chunks_max);
 }
 
 template <int KV, bool QF32>
