@@ -470,8 +470,14 @@ def config_records(hbm_peak, i8_peak_ops):
             m.set_io([xi], [yo])
             m.write(xi, c["x"][:m_rows])
 
+        extra = None
+        if m_rows >= 256:
+            # this kernel runs on the f16 pipe (block scales folded into fp16 weights): half the int8 rate
+            bf16 = measured_peaks()[1]
+            flops = 2.0 * m_rows * 16384 * 2048 / (us * 1e-6)
+            extra = {"pipe": "tcgen05 kind::f16", "frac_of_measured_bf16_peak": flops / (bf16 * 1e12) if bf16 else None}
         record(3, "FULLY_CONNECTED blockwise int4 [M,2048]x[16384,2048]", m_rows, us, alg, 2 * m_rows * 16384 * 2048,
-               "tensor" if m_rows >= 256 else "hbm", 8, _delegate_invoke_us(g3))
+               "tensor" if m_rows >= 256 else "hbm", 8, _delegate_invoke_us(g3), extra)
     del wps
     torch.cuda.empty_cache()
     # ---- config 4: flash-decode, 16 ragged sequences, 8 heads on one KV head of 256; two copies of the cache

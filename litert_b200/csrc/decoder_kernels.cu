@@ -152,12 +152,21 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_kernel(float* __r
   }
 }
 
+// tanh(u) = 1 - 2 / (1 + e^(2u)) on the fast exponential and reciprocal units: absolute error about 1e-7
+// (the result is used as 1 + tanh, so absolute error is what counts), saturating to +-1 through e^(2u) = inf / 0.
+// tanhf's range-split polynomial costs five times the instructions, and a prompt pass evaluates 16 M of these
+// per layer: the GeGLU kernel was bound by it (50 us per layer for 1024 rows, 134 MB read).
+__device__ __forceinline__ float tanh_fast(float u) {
+  const float e = exp2f(__fmul_rn(u, 2.885390081777927f));  // e^(2u) = 2^(2u log2 e)
+  return __fsub_rn(1.0f, __fdividef(2.0f, __fadd_rn(1.0f, e)));
+}
+
 __device__ __forceinline__ float gelu_tanh(float v) {
   // every product and sum rounded on its own, in the order a C compiler without contraction gives
   // (left to right): the row is quantized to int8 next, where one ulp can flip a value
   const float k0 = 0.7978845608028654f;
   const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v);
-  const float th = tanhf(__fmul_rn(k0, __fadd_rn(v, cube)));
+  const float th = tanh_fast(__fmul_rn(k0, __fadd_rn(v, cube)));
   return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, th));
 }
 
