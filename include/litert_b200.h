@@ -354,6 +354,14 @@ B200_API int b200_kv_cache_update_f32(const int64_t* d_position, const float* d_
  * x / out [tokens, heads, h], cos / sin [tokens, h] (host-prepared graph inputs, shared by the heads). */
 B200_API int b200_rope_f32(const float* d_x, const float* d_cos, const float* d_sin, float* d_out, int tokens,
                            int heads, int h, void* stream);
+/* b200_rope_f32 on the step's query rows [t, heads_q, h] and key rows [t, heads_kv, h] and
+ * b200_kv_cache_update_f32 of the rotated keys and the value rows [t, heads_kv, h] as one launch
+ * (same arithmetic, same status 201 rule): d_q_out = rope(q); rope(k) and v go to slots
+ * *d_position .. + t - 1 of the caches [max_entries, heads_kv * h]. */
+B200_API int b200_rope_kv_cache_update_f32(const int64_t* d_position, const float* d_q, const float* d_k,
+                                           const float* d_v, const float* d_cos, const float* d_sin, float* d_q_out,
+                                           int t, int heads_q, int heads_kv, int h, int max_entries,
+                                           float* d_k_cache, float* d_v_cache, void* d_zero_ws, void* stream);
 B200_API int b200_widen_i32_to_i64(const int32_t* d_in, int64_t* d_out, int n, void* stream);
 
 /* ---- Gemma-shaped decoder, one decode step per call ---------------------------

@@ -68,6 +68,7 @@ SIGNATURES = {
     "b200_rms_norm_f32": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
     "b200_kv_cache_update_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "b200_rope_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b200_rope_kv_cache_update_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "b200_widen_i32_to_i64": (_i, [_vp, _vp, _i, _vp]),
     "b200_decoder_create": (_i, [_vp, _vp, ctypes.POINTER(_vp)]),
     "b200_decoder_destroy": (None, [_vp]),

@@ -17,6 +17,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
 #include <memory>
 #include <string>
 #include <unordered_map>
@@ -151,6 +152,7 @@ enum class OpKind {
   kGateUpGeglu,    // gate and up projections as one GEMV + GELU x up + quantization for the down projection
   kLmHeadPick,     // the vocabulary projection with ARG_MAX in its epilogue: no logits are written
   kRope,           // SLICE / SLICE / MUL(-1) / CONCATENATION / MUL / MUL / ADD of the rotary embedding as one kernel
+  kRopeKv,         // the rotary embeddings of a step's query and key rows and odml.update_kv_cache as one kernel
   kSkipped         // a node whose work a fused op does
 };
 
@@ -705,6 +707,50 @@ class DelegateKernel {
       add.heads = heads;
       add.width = h;
     }
+    // (1b) odml.update_kv_cache whose key rows come from a rotary embedding, with the rotary embedding of the
+    // query rows beside it (same cos / sin): one kernel instead of three. It runs at the cache update's place in
+    // the plan, so everything that reads the rotated queries must come after that.
+    for (int i = 0; i < n_ops; ++i) {
+      OpRecord& kv = *ops_[i];
+      if (kv.kind != OpKind::kKvCache || kv.ins.size() != 3) continue;
+      const int rk_i = Producer(kv.ins[1]);
+      if (rk_i < 0 || ops_[rk_i]->kind != OpKind::kRope || OnlyConsumer(ops_[rk_i]->y) != i) continue;
+      OpRecord& rk = *ops_[rk_i];
+      if (rk.rows != kv.rows || rk.heads * rk.width != kv.width) continue;
+      // consumers of the rotated queries (through RESHAPEs, which run nothing) must follow the fused op
+      std::function<bool(int)> later = [&](int tensor) {
+        if (IsPartitionOutput(tensor)) return false;
+        for (int c : Consumers(tensor)) {
+          if (ops_[c]->kind == OpKind::kReshape) {
+            if (!later(ops_[c]->y)) return false;
+          } else if (c <= i) {
+            return false;
+          }
+        }
+        return true;
+      };
+      // every layer's rotations share the graph's cos / sin inputs: this layer's is the nearest one in the plan whose
+      // operand exists before the cache update and whose result is only read after it
+      int rq_i = -1;
+      for (int dist = 1; dist < n_ops && rq_i < 0; ++dist)
+        for (int j : {rk_i - dist, rk_i + dist}) {
+          if (j < 0 || j >= n_ops || j >= i || rq_i >= 0) continue;
+          const OpRecord& c = *ops_[j];
+          if (c.kind == OpKind::kRope && c.ins[1] == rk.ins[1] && c.ins[2] == rk.ins[2] && c.rows == rk.rows &&
+              c.width == rk.width && later(c.y))
+            rq_i = j;
+        }
+      if (rq_i < 0) continue;
+      OpRecord& rq = *ops_[rq_i];
+      // operands: position, k, v, cos, sin, q; the rotated queries are listed too, so that the plan gives them a buffer
+      kv.ins = {kv.ins[0], rk.ins[0], kv.ins[2], rk.ins[1], rk.ins[2], rq.ins[0], rq.y};
+      kv.heads = rq.heads;    // query heads
+      kv.B = rk.heads;        // key / value heads
+      kv.H = rk.width;
+      kv.kind = OpKind::kRopeKv;
+      rk.kind = OpKind::kSkipped;
+      rq.kind = OpKind::kSkipped;
+    }
     // (2) odml.rms_norm feeding only hybrid projections: normalise and quantize once for all of them
     for (int i = 0; i < n_ops; ++i) {
       OpRecord& norm = *ops_[i];
@@ -916,7 +962,7 @@ class DelegateKernel {
     for (auto& opp : ops_)  // a RESHAPE's result is its operand's bytes: same device buffer, nothing to run
       if (opp->kind == OpKind::kReshape) alias_[opp->y] = opp->ins[0];
     for (auto& opp : ops_)  // (before any touch: a later op's operand may be an earlier op's persistent output)
-      if (opp->kind == OpKind::kKvCache) {
+      if (opp->kind == OpKind::kKvCache || opp->kind == OpKind::kRopeKv) {
         persistent_[opp->y] = opp->k_cache.ptr;
         persistent_[opp->y2] = opp->v_cache.ptr;
       } else if (opp->kind == OpKind::kFcGroup) {
@@ -974,7 +1020,7 @@ class DelegateKernel {
       } else if (op.kind >= OpKind::kEmbedding) {
         for (int t : op.ins) touch(t, i);
         if (op.kind == OpKind::kNormQuant) continue;  // its float32 result is never materialised
-        if (op.kind == OpKind::kKvCache) {
+        if (op.kind == OpKind::kKvCache || op.kind == OpKind::kRopeKv) {
           // the op's outputs ARE its persistent caches: never arena tensors
           persistent_[op.y] = op.k_cache.ptr;
           persistent_[op.y2] = op.v_cache.ptr;
@@ -1524,6 +1570,14 @@ class DelegateKernel {
                                                        static_cast<const float*>(Dev(op.ins[2])), op.rows, op.width,
                                                        op.max_entries, static_cast<float*>(op.k_cache.ptr),
                                                        static_cast<float*>(op.v_cache.ptr), st_->zero_ws.ptr, s));
+        return kTfLiteOk;
+      case OpKind::kRopeKv:
+        B200_EW_OR_RETURN(ctx, b200_rope_kv_cache_update_f32(
+                                   static_cast<const int64_t*>(Dev(op.ins[0])), static_cast<const float*>(Dev(op.ins[5])),
+                                   static_cast<const float*>(Dev(op.ins[1])), static_cast<const float*>(Dev(op.ins[2])),
+                                   static_cast<const float*>(Dev(op.ins[3])), static_cast<const float*>(Dev(op.ins[4])),
+                                   static_cast<float*>(Dev(op.ins[6])), op.rows, op.heads, op.B, op.H, op.max_entries,
+                                   static_cast<float*>(op.k_cache.ptr), static_cast<float*>(op.v_cache.ptr), st_->zero_ws.ptr, s));
         return kTfLiteOk;
       case OpKind::kSkipped:
         return kTfLiteOk;

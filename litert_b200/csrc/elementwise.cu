@@ -132,6 +132,42 @@ __global__ void rope_f32_kernel(const float* __restrict__ x, const float* __rest
   }
 }
 
+// The rotary embedding of a step's query and key rows and odml.update_kv_cache as one launch: three kernels of a
+// few kilobytes each in a row cost a decode step three kernel boundaries per layer. q_out = rope(q) (an ordinary
+// tensor), rope(k) and v go straight to slots position .. position + t - 1 of the float32 caches; same roundings as
+// rope_f32_kernel, same out-of-range rule as kv_cache_update_f32_kernel. Part of a chain of dependent launches:
+// resident early, reads and writes only after the kernel before it has finished.
+__global__ void __launch_bounds__(256) rope_kv_f32_kernel(const long long* __restrict__ position, const float* __restrict__ q,
+                                                          const float* __restrict__ k, const float* __restrict__ v,
+                                                          const float* __restrict__ cs, const float* __restrict__ sn,
+                                                          float* __restrict__ q_out, float* __restrict__ k_cache,
+                                                          float* __restrict__ v_cache, int t, int heads_q, int heads_kv, int h,
+                                                          int max_entries, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long pos = position[0];
+  const bool fits = pos >= 0 && pos + t <= max_entries;
+  if (!fits && status && blockIdx.x == 0 && threadIdx.x == 0) atomicCAS(status, 0, 201);
+  const int half = h / 2;
+  const size_t row = (size_t)heads_kv * h;  // elements per cached token
+  const size_t nq = (size_t)t * heads_q * h, nk = (size_t)t * row, total = nq + 2 * nk;
+  auto rope = [&](const float* x, size_t i, int heads) {
+    const int d = (int)(i % h);
+    const size_t token = i / ((size_t)heads * h);
+    const float rot = d < half ? __fmul_rn(x[i + half], -1.0f) : x[i - half];
+    return __fadd_rn(__fmul_rn(x[i], cs[token * h + d]), __fmul_rn(rot, sn[token * h + d]));
+  };
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    if (i < nq) {
+      q_out[i] = rope(q, i, heads_q);
+    } else if (i < nq + nk) {
+      if (fits) k_cache[(size_t)pos * row + (i - nq)] = rope(k, i - nq, heads_kv);
+    } else {
+      if (fits) v_cache[(size_t)pos * row + (i - nq - nk)] = v[i - nq - nk];
+    }
+  }
+}
+
 __global__ void widen_i32_to_i64_kernel(const int32_t* __restrict__ in, long long* __restrict__ out, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = in[i];
@@ -238,6 +274,20 @@ int b200_rope_f32(const float* d_x, const float* d_cos, const float* d_sin, floa
   const size_t total = (size_t)tokens * heads * h;
   rope_f32_kernel<<<grid_for(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(d_x, d_cos, d_sin, d_out, heads, h, total);
   return ecuda("b200_rope_f32");
+}
+
+int b200_rope_kv_cache_update_f32(const int64_t* d_position, const float* d_q, const float* d_k, const float* d_v,
+                                  const float* d_cos, const float* d_sin, float* d_q_out, int t, int heads_q, int heads_kv,
+                                  int h, int max_entries, float* d_k_cache, float* d_v_cache, void* d_zero_ws, void* stream) {
+  if (!d_position || !d_q || !d_k || !d_v || !d_cos || !d_sin || !d_q_out || !d_k_cache || !d_v_cache || t <= 0 ||
+      heads_q <= 0 || heads_kv <= 0 || h <= 0 || h % 2 || max_entries <= 0)
+    return efail(B200_ERR_INVALID_ARGUMENT, "b200_rope_kv_cache_update_f32: bad argument");
+  const size_t total = (size_t)t * ((size_t)heads_q + 2 * (size_t)heads_kv) * h;
+  const cudaError_t e = launch_chained(rope_kv_f32_kernel, dim3(grid_for(total)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                       reinterpret_cast<const long long*>(d_position), d_q, d_k, d_v, d_cos, d_sin, d_q_out,
+                                       d_k_cache, d_v_cache, t, heads_q, heads_kv, h, max_entries, static_cast<int*>(d_zero_ws));
+  if (e != cudaSuccess) return efail(B200_ERR_CUDA, "b200_rope_kv_cache_update_f32: %s", cudaGetErrorString(e));
+  return ecuda("b200_rope_kv_cache_update_f32");
 }
 
 int b200_widen_i32_to_i64(const int32_t* d_in, int64_t* d_out, int n, void* stream) {

@@ -136,6 +136,56 @@ def test_rope_kv_append_bit_exact(oracle, kv, rows, one_sequence):
     assert int((kc != 0).any(dim=-1).sum().item()) <= rows
 
 
+@pytest.mark.parametrize("t,heads_q,heads_kv,h,position", [(1, 8, 1, 256, 1030), (6, 4, 2, 64, 0), (3, 4, 1, 64, 29)])
+def test_rope_and_kv_cache_update_in_one_launch_bit_exact(t, heads_q, heads_kv, h, position):
+    """b200_rope_kv_cache_update_f32 against the graph's own arithmetic (x * cos + concat(-x2, x1) * sin, every
+    product and the sum rounded on their own) and odml.update_kv_cache's slot rule; a write past the last slot sets
+    status 201 and leaves the caches alone."""
+    import ctypes
+
+    from litert_b200 import _lib
+
+    lib = _lib.load()
+    max_entries = 1040 if position > 100 else 32
+    rng = np.random.default_rng(t * 100 + h)
+    q = (rng.standard_normal((t, heads_q, h)) * 3).astype(np.float32)
+    k = (rng.standard_normal((t, heads_kv, h)) * 3).astype(np.float32)
+    v = rng.standard_normal((t, heads_kv, h)).astype(np.float32)
+    ang = rng.uniform(-3.0, 3.0, (t, h)).astype(np.float32)
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+
+    def rope(x):
+        rot = np.concatenate([x[..., h // 2:] * np.float32(-1.0), x[..., :h // 2]], axis=-1)
+        return (x * cos[:, None, :]) + (rot * sin[:, None, :])
+
+    def run(pos):
+        d = {n: _dev(a) for n, a in (("q", q), ("k", k), ("v", v), ("cos", cos), ("sin", sin))}
+        d_pos = _dev(np.asarray([pos], np.int64))
+        q_out = torch.empty_like(d["q"])
+        kc = torch.zeros((max_entries, heads_kv * h), dtype=torch.float32, device="cuda")
+        vc = torch.zeros_like(kc)
+        ws = torch.zeros(64, dtype=torch.int32, device="cuda")
+        p = lambda x: ctypes.c_void_p(x.data_ptr())
+        rc = lib.b200_rope_kv_cache_update_f32(p(d_pos), p(d["q"]), p(d["k"]), p(d["v"]), p(d["cos"]), p(d["sin"]), p(q_out), t,
+                                               heads_q, heads_kv, h, max_entries, p(kc), p(vc), p(ws),
+                                               ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0
+        torch.cuda.synchronize()
+        return q_out.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy(), int(ws[0].item())
+
+    q_out, kc, vc, status = run(position)
+    assert status == 0
+    assert np.array_equal(q_out, rope(q)), "rotated queries"
+    want_k = np.zeros_like(kc)
+    want_v = np.zeros_like(vc)
+    want_k[position:position + t] = rope(k).reshape(t, -1)
+    want_v[position:position + t] = v.reshape(t, -1)
+    assert np.array_equal(kc, want_k) and np.array_equal(vc, want_v)
+    q_out, kc, vc, status = run(max_entries - t + 1)
+    assert status == 201 and not kc.any() and not vc.any()
+    assert np.array_equal(q_out, rope(q))
+
+
 def test_argmax_rows_first_index_and_nan_rule(oracle):
     from litert_b200 import ops
 
