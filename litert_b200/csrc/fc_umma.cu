@@ -1242,7 +1242,7 @@ int plan_cluster_split(const FcParams& p) {
   if (p.n_tiles * 2 >= sms || p.k_tiles < 2) return 0;
   using L = ClusterLayout<NB>;
   auto kernel = fc_cluster_kernel<NB, EPI>;
-  static int capacity[64][9] = {{0}};  // [device][split]: co-resident clusters, -1 = query failed
+  static int capacity[64][17] = {{0}};  // [device][split]: co-resident clusters, -1 = query failed
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1269,10 +1269,8 @@ int plan_cluster_split(const FcParams& p) {
       return v;
     }
   }
-  // the split that puts the most SMs to work with every cluster resident at once
-  int best = 0;
-  for (int split = 8; split >= 2; --split) {
-    if (split > p.k_tiles || p.n_tiles * split > sms) continue;
+  // co-resident clusters of `split` CTAs (one CTA per SM counted), -1 = the query failed
+  auto clusters_resident = [&](int split) {
     if (capacity[dev][split] == 0) {
       cudaLaunchConfig_t cfg;
       memset(&cfg, 0, sizeof(cfg));
@@ -1294,9 +1292,35 @@ int plan_cluster_split(const FcParams& p) {
       capacity[dev][split] = n;
       if (tuning_env("B200_FC_VERBOSE")) fprintf(stderr, "[b200] cluster size %d: %d clusters resident (NB=%d)\n", split, n, NB);
     }
+    return capacity[dev][split];
+  };
+  // A long reduction over few n tiles (a decoder's down projection: 16 n tiles x 128 k tiles) does better
+  // with more CTAs than SMs: clusters of 12 (beyond the portable 8: the kernel opts in), two CTAs on some
+  // SMs, more copies in flight per SM. Measured on B200, n = 2048, k = 16384, one row, inside the decode
+  // step: 8.3 us with clusters of 8 (128 CTAs), 7.9 / 7.1 / 6.7 / 6.2 / 6.9 us with 9 / 10 / 11 / 12 / 13,
+  // 12 us with 14 to 16.
+  {
+    int big = 12;
+    if (const char* e = tuning_env("B200_FC_CLUSTER_BIG")) big = atoi(e);  // measurement knob (0 = off)
+    if (big > 8 && big <= 16 && p.k_tiles >= 8 * big && p.n_tiles * big <= 2 * sms && UmmaBudget<NB>::kCtasPerSm >= 2) {
+      static bool opted[64] = {false};
+      if (!opted[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+          opted[dev] = true;
+        } else {
+          cudaGetLastError();
+        }
+      }
+      if (opted[dev] && clusters_resident(big) > 0) return big;
+    }
+  }
+  // the split that puts the most SMs to work with every cluster resident at once
+  int best = 0;
+  for (int split = 8; split >= 2; --split) {
+    if (split > p.k_tiles || p.n_tiles * split > sms) continue;
     // (the query counts one CTA per SM; CTAs this small share an SM, and clusters beyond the
     // resident ones simply start as earlier ones finish: nothing waits across clusters)
-    if (capacity[dev][split] * UmmaBudget<NB>::kCtasPerSm >= p.n_tiles) {
+    if (clusters_resident(split) * UmmaBudget<NB>::kCtasPerSm >= p.n_tiles) {
       best = split;
       break;
     }
