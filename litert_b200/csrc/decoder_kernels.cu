@@ -186,10 +186,8 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
                                                                     int32_t* __restrict__ zps) {
   namespace cg = cooperative_groups;
   extern __shared__ float xs[];
-  __shared__ float red[32];
-  __shared__ float s_minmax[2];
-  __shared__ float s_inv;
-  __shared__ int s_zp, s_zero;
+  __shared__ float2 s_mm[32];
+  __shared__ float2 s_all[CL];  // every CTA's min / max, pushed here by the CTAs themselves
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = CL > 1 ? (int)cluster.block_rank() : 0;
   const int b = blockIdx.x / CL;
@@ -198,6 +196,7 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
   const float* u = g + f;
   const int lo = rank * per_cta, hi = min(f, lo + per_cta);
   const bool vec = (f & 3) == 0;  // rows and slices then start on 16-byte boundaries
+  if (CL > 1) cluster.sync();  // every CTA of the cluster runs: remote stores are legal from here on
   // two passes over the same code: a dry run that warms the instruction caches while the producing
   // kernel is still busy (nothing stored), then the real one after the dependency wait
 #pragma unroll 1
@@ -226,34 +225,27 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
         mx = fmaxf(mx, v);
       }
     }
-    mn = block_reduce(mn, [](float a, float c) { return fminf(a, c); }, mn, red);
-    mx = block_reduce(mx, [](float a, float c) { return fmaxf(a, c); }, mx, red);
-    if (threadIdx.x == 0) {
-      s_minmax[0] = mn;
-      s_minmax[1] = mx;
-    }
-    if (CL > 1) cluster.sync();
-    if (threadIdx.x == 0) {
-      float rmn = mn, rmx = mx;
-      for (int r = 0; r < CL && CL > 1; ++r) {
-        const float* remote = cluster.map_shared_rank(s_minmax, r);
-        rmn = fminf(rmn, remote[0]);
-        rmx = fmaxf(rmx, remote[1]);
-      }
-      float sf, inv;
-      int zp, zero_row;
-      row_quant_params(rmn, rmx, true, &sf, &inv, &zp, &zero_row);
-      s_zero = zero_row;
-      s_inv = inv;
-      s_zp = zp;
-      if (rank == 0 && live) {
-        scales[b] = sf;
-        zps[b] = zp;
+    block_minmax(mn, mx, s_mm);
+    if (CL > 1) {
+      // The slices' extremes go to every CTA of the cluster by remote stores (nobody waits for a remote read),
+      // one cluster barrier makes them visible, and every thread derives the row's parameters itself.
+      if (threadIdx.x < CL) *cluster.map_shared_rank(&s_all[rank], threadIdx.x) = make_float2(mn, mx);
+      cluster.sync();
+#pragma unroll
+      for (int r = 0; r < CL; ++r) {
+        mn = fminf(mn, s_all[r].x);
+        mx = fmaxf(mx, s_all[r].y);
       }
     }
-    __syncthreads();
-    const bool zero = s_zero != 0;
-    const float inv = s_inv, zpf = (float)s_zp;
+    float sf, inv;
+    int zp, zero_row;
+    row_quant_params(mn, mx, true, &sf, &inv, &zp, &zero_row);
+    if (threadIdx.x == 0 && rank == 0 && live) {
+      scales[b] = sf;
+      zps[b] = zp;
+    }
+    const bool zero = zero_row != 0;
+    const float zpf = (float)zp;
     const int k_end = min(lo + per_cta, f_pad);  // the tiled row ends at the padded length
     for (int k4 = lo + threadIdx.x * 4; k4 < k_end; k4 += blockDim.x * 4) {
       uint32_t word = 0;
@@ -262,7 +254,10 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
         if (k4 + e < f && !zero) word |= quantize_value(xs[k4 + e - lo], inv, zpf, true) << (8 * e);
       if (live) *reinterpret_cast<uint32_t*>(q_tiled + q_tiled_offset(b, k4, m_alloc)) = word;
     }
-    if (CL > 1) cluster.sync();  // neighbours are done with this CTA's min / max (and no CTA exits before that)
+    // (no barrier at the end: a CTA's shared memory is only written remotely BEFORE the barrier above, which
+    // every CTA of the cluster passes before any of them can leave; the dry run's values are overwritten by
+    // the same CTAs in program order)
+    __syncthreads();  // xs and s_mm are rewritten by the next pass
   }
 }
 
