@@ -16,7 +16,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden"]
 COMMON += os.environ.get("B200_NVCC_FLAGS", "").split()  # e.g. -DB200_UMMA_KB=108 (shared-memory budget of a GEMV CTA)
 
-KERNEL_SOURCES = ["pack.cu", "fc_stream.cu", "fc_umma.cu", "fc_w4_umma.cu", "fc_w4_gemv.cu", "sdpa_decode.cu", "decoder_kernels.cu", "decoder.cu", "shim.cu", "sdpa_static.cu", "glue_abi.cu", "peak_probe.cu", "elementwise.cu"]
+KERNEL_SOURCES = ["pack.cu", "fc_umma.cu", "fc_w4_umma.cu", "fc_w4_gemv.cu", "sdpa_decode.cu", "decoder_kernels.cu", "decoder.cu", "shim.cu", "sdpa_static.cu", "glue_abi.cu", "peak_probe.cu", "elementwise.cu"]
 
 
 def _newer(target, deps):

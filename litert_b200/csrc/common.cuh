@@ -308,6 +308,22 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
   return r;
 }
+// Eight bytes to a peer CTA's shared memory that also count as 8 transaction bytes on the peer's
+// mbarrier: data and "it has arrived" in one message, no cluster-wide barrier. Both addresses from
+// map_to_rank; `addr` 8-byte aligned.
+__device__ __forceinline__ void st_async_cluster_f32x2(uint32_t addr, float a, float b, uint32_t remote_bar) {
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];" ::"r"(addr), "f"(a),
+               "f"(b), "r"(remote_bar)
+               : "memory");
+}
+__device__ __forceinline__ void st_async_cluster_f32(uint32_t addr, float v, uint32_t remote_bar) {  // 4 transaction bytes
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];" ::"r"(addr), "f"(v), "r"(remote_bar)
+               : "memory");
+}
+__device__ __forceinline__ void st_async_cluster_u32(uint32_t addr, int32_t v, uint32_t remote_bar) {  // 4 transaction bytes
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];" ::"r"(addr), "r"(v), "r"(remote_bar)
+               : "memory");
+}
 __device__ __forceinline__ void st_cluster_u32(uint32_t addr, int32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }

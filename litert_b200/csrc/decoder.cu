@@ -277,7 +277,6 @@ cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_
   uint8_t* z = d->zero_ws.as<uint8_t>();
   p.status = reinterpret_cast<int*>(z);
   p.ws_count = reinterpret_cast<int32_t*>(z + zero_ws_counter_off());
-  p.ws_acc = reinterpret_cast<int32_t*>(z + zero_ws_acc_off());
   p.ws_part = reinterpret_cast<int32_t*>(z + b200::zero_ws_part_off());
   ++d->launches;
   if (d->trace.p && d->trace_next < kTraceSlots) p.trace = d->trace.as<unsigned long long>() + 4 * d->trace_next++;

@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_kernel(float* __r
                                                                      int8_t* __restrict__ q_tiled,
                                                                      float* __restrict__ scales,
                                                                      int32_t* __restrict__ zps, TpExchange xch,
-                                                                     int first_pass) {
+                                                                     int first_pass, int batched) {
   extern __shared__ float xs[];
   __shared__ float red[32];
   pdl_launch_dependents();
@@ -119,6 +119,40 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_kernel(float* __r
     // inputs written by earlier kernels are read past L1 (__ldcg): the dry run must leave no stale
     // line behind for the real pass
     float ss = 0.0f;
+    if (!exchange && batched) {
+      // The row is updated in place, so the load of one element may not pass the store of the one before:
+      // a thread's elements are all requested first (one L2 round trip for the lot), then added and stored.
+      constexpr int kBatch = 2;
+      const float* dr = delta ? delta + (size_t)b * d : nullptr;
+      for (int i0 = threadIdx.x; i0 < d; i0 += kBatch * blockDim.x) {
+        float vh[kBatch], vd[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+          const int i = i0 + j * blockDim.x;
+          vh[j] = i < d ? __ldcg(hr + i) : 0.0f;
+        }
+        if (dr) {
+#pragma unroll
+          for (int j = 0; j < kBatch; ++j) {
+            const int i = i0 + j * blockDim.x;
+            vd[j] = i < d ? __ldcg(dr + i) : 0.0f;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+          const int i = i0 + j * blockDim.x;
+          if (i < d) {
+            float v = vh[j];
+            if (dr) {
+              v = __fadd_rn(v, vd[j]);
+              if (live) hr[i] = v;
+            }
+            xs[i] = v;
+            ss += v * v;
+          }
+        }
+      }
+    } else
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
       float v = __ldcg(hr + i);
       if (exchange) {
@@ -187,8 +221,14 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
   namespace cg = cooperative_groups;
   extern __shared__ float xs[];
   __shared__ float2 s_mm[32];
-  __shared__ float2 s_all[CL];  // every CTA's min / max, pushed here by the CTAs themselves
+  __shared__ __align__(8) float2 s_all[CL];  // every CTA's min / max, pushed here by the CTAs themselves
+  __shared__ __align__(8) uint64_t s_bar[2];  // one per pass: completes when all CL messages are in
   cg::cluster_group cluster = cg::this_cluster();
+  if (CL > 1 && threadIdx.x == 0) {
+    mbar_init(&s_bar[0], 1);
+    mbar_init(&s_bar[1], 1);
+    mbar_fence_init();
+  }
   const int rank = CL > 1 ? (int)cluster.block_rank() : 0;
   const int b = blockIdx.x / CL;
   pdl_launch_dependents();
@@ -227,10 +267,15 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
     }
     block_minmax(mn, mx, s_mm);
     if (CL > 1) {
-      // The slices' extremes go to every CTA of the cluster by remote stores (nobody waits for a remote read),
-      // one cluster barrier makes them visible, and every thread derives the row's parameters itself.
-      if (threadIdx.x < CL) *cluster.map_shared_rank(&s_all[rank], threadIdx.x) = make_float2(mn, mx);
-      cluster.sync();
+      // The slices' extremes go to every CTA of the cluster by remote stores that also count as transaction
+      // bytes on the receiver's barrier (st.async): nobody waits for a remote read or for a cluster-wide
+      // barrier (0.4 us dearer per launch, measured on B200), and every thread derives the row's parameters
+      // itself.
+      if (threadIdx.x == 0) mbar_arrive_expect_tx(&s_bar[pass], CL * 8u);
+      if (threadIdx.x < CL)
+        st_async_cluster_f32x2(map_to_rank(smem_u32(&s_all[rank]), threadIdx.x), mn, mx,
+                               map_to_rank(smem_u32(&s_bar[pass]), threadIdx.x));
+      mbar_drain_bounded(&s_bar[pass], 0);  // (bounded: a lost message ends in wrong numbers, never in a hang)
 #pragma unroll
       for (int r = 0; r < CL; ++r) {
         mn = fminf(mn, s_all[r].x);
@@ -254,9 +299,8 @@ __global__ void __launch_bounds__(kGegluThreads) geglu_quant_kernel(const float*
         if (k4 + e < f && !zero) word |= quantize_value(xs[k4 + e - lo], inv, zpf, true) << (8 * e);
       if (live) *reinterpret_cast<uint32_t*>(q_tiled + q_tiled_offset(b, k4, m_alloc)) = word;
     }
-    // (no barrier at the end: a CTA's shared memory is only written remotely BEFORE the barrier above, which
-    // every CTA of the cluster passes before any of them can leave; the dry run's values are overwritten by
-    // the same CTAs in program order)
+    // (no barrier at the end: a CTA cannot leave before all the messages addressed to it have arrived, and
+    // each pass has a barrier of its own, so a fast CTA's second message cannot complete a slow one's first)
     __syncthreads();  // xs and s_mm are rewritten by the next pass
   }
 }
@@ -415,8 +459,10 @@ cudaError_t launch_add_norm_quant(float* h, const float* delta, const float* gai
   const TpExchange x = xch ? *xch : TpExchange();
   // a decode step's few rows: the widest block and a dry run; a prompt chunk's many rows: several rows per SM
   const bool many = batch > kLatencyRows;
+  int batched = 1;
+  if (const char* e = tuning_env("B200_NORM_BATCHED")) batched = atoi(e);  // measurement knob
   return launch_chained(add_norm_quant_kernel, dim3(batch), dim3(many ? 256 : kNormThreads), sizeof(float) * d, s, h, delta, gain,
-                        d, d_pad, eps, m_alloc, q_tiled, scales, zps, x, many ? 1 : 0);
+                        d, d_pad, eps, m_alloc, q_tiled, scales, zps, x, many ? 1 : 0, batched);
 }
 
 cudaError_t launch_geglu_quant(const float* gate_up, int batch, int f, int m_alloc, int8_t* q_tiled, float* scales,

@@ -586,7 +586,7 @@ struct ClusterLayout {
   static constexpr int kStagesRaw = (UmmaBudget<NB>::kClusterKB * 1024 - kRedBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
   static_assert(kStages >= 2, "the ring needs two stages");
-  static constexpr int kBarriers = 2 * kStages + 2;
+  static constexpr int kBarriers = 2 * kStages + 3;
   // without the fused prologue's operand buffer, which the launcher adds
   static constexpr int kSmemBytes = kStages * kStageBytes + kRedBytes + kBarriers * 8 + (int)sizeof(UmmaShared) +
                                     2 * (int)sizeof(PrologueShared) + 1024 + 16;
@@ -602,7 +602,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
   uint64_t* empty_bar = full_bar + L::kStages;
   uint64_t* acc_full = empty_bar + L::kStages;
   uint64_t* b_ready = acc_full + 1;  // fused prologue: the operand rows are in place
-  UmmaShared* sh = reinterpret_cast<UmmaShared*>(b_ready + 1);
+  uint64_t* red_full = b_ready + 1;  // the cluster's pieces of this CTA's rows have all arrived
+  UmmaShared* sh = reinterpret_cast<UmmaShared*>(red_full + 1);
   PrologueShared* ps = reinterpret_cast<PrologueShared*>(sh + 1);
   uint8_t* bbuf = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ps + 2) + 1023) & ~uintptr_t(1023));
   volatile int* abort_flag = &sh->abort_flag;
@@ -623,6 +624,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
     }
     mbar_init(acc_full, 1);
     mbar_init(b_ready, 1);
+    mbar_init(red_full, 1);
     sh->abort_flag = 0;
     mbar_fence_init();
   }
@@ -631,7 +633,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
-  cluster_arrive();  // phase 0: "this CTA is running" (waited for before the first remote store)
+  cluster_arrive();  // phase 0: "this CTA is running, its barriers exist" (waited for before the first remote store)
 
   const int m_groups_alloc = p.m_alloc / 8;
   const int mg_base = m_base / 8;
@@ -765,7 +767,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
       tc_fence_after();
     }
     cluster_wait();  // phase 0: every CTA of the cluster is running, remote stores are legal
+    // Every int32 sent to an owner also counts as four transaction bytes on the owner's `red_full`
+    // barrier (st.async): an owner knows its pieces are in without a second cluster-wide barrier, which
+    // cost 0.4 us per launch (measured on B200 against the same exchange with barrier.cluster).
+    if (etid == 0) {
+      const int owned = min(rows_per_owner, kTileN - rank * rows_per_owner);
+      mbar_arrive_expect_tx(red_full, (uint32_t)(owned > 0 ? split * owned * m_valid * 4 : 0));
+    }
     const uint32_t owner = (uint32_t)(row / rows_per_owner);
+    const uint32_t owner_bar = map_to_rank(smem_u32(red_full), owner);
     const uint32_t slot = map_to_rank(smem_u32(red), owner) +
                           4u * (uint32_t)((rank * NB) * rows_per_owner + row % rows_per_owner);
 #pragma unroll 1
@@ -781,14 +791,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
       }
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        if (c * 16 + j < m_valid) st_cluster_u32(slot + 4u * (uint32_t)((c * 16 + j) * rows_per_owner), r[j]);
+        if (c * 16 + j < m_valid) st_async_cluster_u32(slot + 4u * (uint32_t)((c * 16 + j) * rows_per_owner), r[j], owner_bar);
     }
     tc_fence_before();
+    mbar_wait_bounded(red_full, 0, abort_flag, p.status, kStatusWaitTimeoutTmem);  // everyone's pieces of this CTA's rows
   } else {
     cluster_wait();  // phase 0
   }
-  cluster_arrive();  // phase 1: this CTA's pieces are delivered ...
-  cluster_wait();    // ... and everyone else's have arrived here
   if (warp >= 2 && n_own < p.n) {
     for (int col = col0; col < m_valid; col += col_step) {
       int32_t v = 0;
@@ -1402,6 +1411,19 @@ cudaError_t launch_all(const FcParams& p, cudaStream_t s) {
 }
 
 }  // namespace
+
+int device_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = n > 0 ? n : 148;
+  }
+  return cached[dev];
+}
 
 int fc_argmax_ctas(int n) {
   const int sms = device_sm_count();

@@ -55,7 +55,6 @@ void fill_fc_ws(FcParams& p, void* d_zero_ws) {
   uint8_t* z = static_cast<uint8_t*>(d_zero_ws);
   p.status = reinterpret_cast<int*>(z);
   p.ws_count = reinterpret_cast<int32_t*>(z + zero_ws_counter_off());
-  p.ws_acc = reinterpret_cast<int32_t*>(z + zero_ws_acc_off());
   p.ws_part = reinterpret_cast<int32_t*>(z + zero_ws_part_off());
 }
 

@@ -65,10 +65,9 @@ struct FcParams {
   const float* kfsum;        // [n]
   // outputs
   void* y;                   // [m,n] row-major float / int8 / int32
-  // split-K workspace: kZeroWsSlots slots of 128*64 int32/float accumulators and as many counters;
-  // all zero between calls
-  int32_t* ws_acc;    // mma.sync path: zero between calls
-  int32_t* ws_part;   // tcgen05 path: per-CTA partial slots, no initial contents needed
+  // split-K workspace: kZeroWsSlots counters (zero between calls) and as many per-CTA partial slots
+  // (no initial contents needed)
+  int32_t* ws_part;
   int32_t* ws_count;
   int* status;
   // Fused input prologue (decode-sized m, see prologue.cuh): when `prologue` is 1 the activation rows
@@ -107,11 +106,8 @@ struct FcParams {
 // Number of CTAs (= candidate slots per row) the fused pick uses for n output channels.
 int fc_argmax_ctas(int n);
 
-// Streamed-weights GEMM on the packed int8 tiles (any m; m > 64 runs in
-// chunks of 64 rows).
-cudaError_t launch_fc_i8(const FcParams& p, FcEpilogue epi, cudaStream_t s);
-// Same contract on the tcgen05 / TMEM path; activation rows are processed umma_rows_per_pass(m) at a
-// time and the tiled activation buffer must hold a multiple of that many rows.
+// Streamed-weights GEMM on the packed int8 tiles, tcgen05 / TMEM path (any m): activation rows are processed
+// umma_rows_per_pass(m) at a time and the tiled activation buffer must hold a multiple of that many rows.
 cudaError_t launch_fc_i8_umma(const FcParams& p, FcEpilogue epi, cudaStream_t s);
 int umma_rows_per_pass(int m);
 // Whether FcParams::prologue can be used for these sizes (the tcgen05 kernels only).
@@ -125,16 +121,13 @@ bool w4_gemv_supported(int m, int k);
 cudaError_t launch_fc_w4_gemv(const FcParams& p, const float* x, cudaStream_t s);
 
 constexpr int kZeroWsSlots = 320;            // counters; >= 2 x CTAs per launch
-constexpr int kAccSlots = 160;               // mma.sync path: one accumulator slot per CTA
-constexpr int kAccSlotInts = 128 * 64;       // 128 rows x up to 64 activation rows
 constexpr int kZeroWsSlotInts = 128 * 256;   // tcgen05 path: 128 rows x up to 256 activation rows per partial slot
 int device_sm_count();
 
-// Layout of the zero workspace: [status word + padding: 256 B][slot counters][mma.sync accumulators]
-// [tcgen05 partial slots]. Only the first three parts must be zero between calls.
+// Layout of the zero workspace: [status word + padding: 256 B][slot counters][partial slots]. Only the
+// first two parts must be zero between calls.
 inline size_t zero_ws_counter_off() { return 256; }
-inline size_t zero_ws_acc_off() { return 256 + ((sizeof(int32_t) * kZeroWsSlots + 255) / 256) * 256; }
-inline size_t zero_ws_part_off() { return zero_ws_acc_off() + sizeof(int32_t) * (size_t)kAccSlots * kAccSlotInts; }
+inline size_t zero_ws_part_off() { return 256 + ((sizeof(int32_t) * kZeroWsSlots + 255) / 256) * 256; }
 inline size_t zero_ws_total_bytes() { return zero_ws_part_off() + sizeof(int32_t) * (size_t)kZeroWsSlots * kZeroWsSlotInts; }
 
 struct SdpaParams {

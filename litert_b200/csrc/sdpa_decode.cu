@@ -784,8 +784,12 @@ struct AttnStepSmem {
   float rec[8][kRec];             // this CTA's merged state per head
   float inbox[kAttnCluster][kRec];  // the states of the head this CTA finishes, from every CTA
   float own[H];                   // finished head
-  float2 mmbox[kAttnCluster];     // min / max of every CTA's finished head
+  __align__(8) float2 mmbox[kAttnCluster];  // min / max of every CTA's finished head
   float2 red[kAttnWarps];
+  // the two exchanges of the cluster complete on these (transaction bytes carried by the remote stores
+  // themselves): [0] the head states have arrived in `inbox`, [1] the min / max pairs in `mmbox`
+  __align__(8) uint64_t xbar[2];
+  int abort_flag;
   // followed by the staging area (`stage_rows` key rows then as many value rows, each padded by
   // 16 bytes against bank conflicts) and the warps' parked outputs
 };
@@ -824,7 +828,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
   const bool tracer = p.trace && blockIdx.x == 0 && threadIdx.x == 0;
   if (tracer) p.trace[0] = global_timer_ns();
   pdl_launch_dependents();
-  cluster_arrive();  // phase 0: this CTA runs (waited for before the first remote store)
+  if (threadIdx.x == 0) {
+    mbar_init(&sm.xbar[0], 1);
+    mbar_init(&sm.xbar[1], 1);
+    sm.abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  cluster_arrive();  // phase 0: this CTA runs and its barriers exist (waited for before the first remote store)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int rank = (int)cluster_ctarank();
@@ -1057,16 +1068,23 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
     __syncthreads();
     if (tracer && live) p.trace[5] = global_timer_ns();
     cluster_wait();  // phase 0
-    // head h goes to CTA h (n <= 8 = cluster size)
+    // Head h goes to CTA h (n <= 8 = cluster size). Every float sent also counts as four transaction bytes on
+    // the receiving CTA's barrier (st.async): a CTA knows that its head's states are in without a cluster-wide
+    // barrier, which costs 0.4 us more (measured on B200 on the same exchange).
+    const bool owner = rank < p.n;
+    volatile int* abort_flag = &sm.abort_flag;
+    if (tid == 0) {
+      mbar_arrive_expect_tx(&sm.xbar[0], owner ? (uint32_t)(C * REC * 4) : 0u);
+      mbar_arrive_expect_tx(&sm.xbar[1], (uint32_t)(C * 8));
+    }
     for (int head = 0; head < p.n; ++head) {
       const uint32_t dst = map_to_rank(smem_u32(&sm.inbox[rank][0]), (uint32_t)head);
-      for (int i = tid; i < REC; i += kAttnWarps * 32) st_cluster_f32(dst + 4u * (uint32_t)i, sm.rec[head][i]);
+      const uint32_t bar = map_to_rank(smem_u32(&sm.xbar[0]), (uint32_t)head);
+      for (int i = tid; i < REC; i += kAttnWarps * 32) st_async_cluster_f32(dst + 4u * (uint32_t)i, sm.rec[head][i], bar);
     }
-    cluster_arrive();  // phase 1: delivered ...
-    cluster_wait();    // ... and received
+    mbar_wait_bounded(&sm.xbar[0], 0, abort_flag, p.status, kStatusWaitTimeoutFull);
     if (tracer && live) p.trace[6] = global_timer_ns();
     float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
-    const bool owner = rank < p.n;
     if (owner) {
       float mm = -CUDART_INF_F;
   #pragma unroll
@@ -1102,12 +1120,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
         lo = fminf(lo, sm.red[w].x);
         hi = fmaxf(hi, sm.red[w].y);
       }
-      const uint32_t dst = map_to_rank(smem_u32(&sm.mmbox[rank]), (uint32_t)tid);
-      st_cluster_f32(dst, lo);
-      st_cluster_f32(dst + 4u, hi);
+      st_async_cluster_f32x2(map_to_rank(smem_u32(&sm.mmbox[rank]), (uint32_t)tid), lo, hi,
+                             map_to_rank(smem_u32(&sm.xbar[1]), (uint32_t)tid));
     }
-    cluster_arrive();  // phase 2
-    cluster_wait();
+    mbar_wait_bounded(&sm.xbar[1], 0, abort_flag, p.status, kStatusWaitTimeoutFull);
     if (tracer && live) p.trace[7] = global_timer_ns();
     float lo = sm.mmbox[0].x, hi = sm.mmbox[0].y;
   #pragma unroll

@@ -29,7 +29,6 @@ int cuda_fail(cudaError_t e, const char* what) {
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 inline size_t zero_ws_counter_off() { return b200::zero_ws_counter_off(); }
-inline size_t zero_ws_acc_off() { return b200::zero_ws_acc_off(); }
 inline size_t zero_ws_bytes() { return b200::zero_ws_total_bytes(); }
 
 struct Scratch {
@@ -58,26 +57,14 @@ Scratch carve_scratch(void* base, int m, int k_tiles8) {
   return s;
 }
 
-// int8 GEMMs run on the tcgen05 path unless B200_FC_PATH=mma selects the mma.sync kernel
-// (kept for A/B measurement; both give identical results).
-bool use_umma() {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* e = b200::tuning_env("B200_FC_PATH");
-    cached = (e && !strcmp(e, "mma")) ? 0 : 1;
-  }
-  return cached == 1;
-}
-
 cudaError_t run_fc_i8(const b200::FcParams& p, b200::FcEpilogue epi, cudaStream_t s) {
-  return use_umma() ? b200::launch_fc_i8_umma(p, epi, s) : b200::launch_fc_i8(p, epi, s);
+  return b200::launch_fc_i8_umma(p, epi, s);
 }
 
 void fill_ws(b200::FcParams& p, void* d_zero_ws) {
   uint8_t* z = static_cast<uint8_t*>(d_zero_ws);
   p.status = reinterpret_cast<int*>(z);
   p.ws_count = reinterpret_cast<int32_t*>(z + zero_ws_counter_off());
-  p.ws_acc = reinterpret_cast<int32_t*>(z + zero_ws_acc_off());
   p.ws_part = reinterpret_cast<int32_t*>(z + b200::zero_ws_part_off());
 }
 
