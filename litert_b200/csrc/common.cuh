@@ -320,6 +320,11 @@ __device__ __forceinline__ void st_async_cluster_f32(uint32_t addr, float v, uin
   asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];" ::"r"(addr), "f"(v), "r"(remote_bar)
                : "memory");
 }
+__device__ __forceinline__ void st_async_cluster_f32x4(uint32_t addr, float4 v, uint32_t remote_bar) {  // 16 bytes, addr 16-byte aligned
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(addr),
+               "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(remote_bar)
+               : "memory");
+}
 __device__ __forceinline__ void st_async_cluster_u32(uint32_t addr, int32_t v, uint32_t remote_bar) {  // 4 transaction bytes
   asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];" ::"r"(addr), "r"(v), "r"(remote_bar)
                : "memory");

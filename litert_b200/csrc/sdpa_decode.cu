@@ -777,12 +777,12 @@ constexpr int kAttnWarps = 4;
 
 template <int H>
 struct AttnStepSmem {
-  static constexpr int kRec = H + 2;
+  static constexpr int kRec = H + 4;  // outputs, maximum, sum, two floats of padding: whole 16-byte pieces
   float2 cs[H / 2];               // cos, sin per rotation pair
   float q[8][H];                  // rotated query heads
   float sm_m[kAttnWarps][8], sm_l[kAttnWarps][8], wf[kAttnWarps][8];
-  float rec[8][kRec];             // this CTA's merged state per head
-  float inbox[kAttnCluster][kRec];  // the states of the head this CTA finishes, from every CTA
+  __align__(16) float rec[8][kRec];             // this CTA's merged state per head
+  __align__(16) float inbox[kAttnCluster][kRec];  // the states of the head this CTA finishes, from every CTA
   float own[H];                   // finished head
   __align__(8) float2 mmbox[kAttnCluster];  // min / max of every CTA's finished head
   float2 red[kAttnWarps];
@@ -815,7 +815,7 @@ template <int KV, int H, int GPI>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(const AttnStepParams p, const int stage_rows) {
   using WA = WarpAttention<KV, H, GPI>;
   constexpr int KSTEPS = WA::KSTEPS;
-  constexpr int C = kAttnCluster, HALF = H / 2, REC = H + 2;
+  constexpr int C = kAttnCluster, HALF = H / 2, REC = AttnStepSmem<H>::kRec;
   constexpr int PITCH = attn_row_pitch<KV, H>();
   constexpr int ROW_BYTES = H * (KV == kKvI8 ? 1 : 2);
   extern __shared__ __align__(128) uint8_t attn_smem_raw[];
@@ -1080,7 +1080,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_step_cluster_kernel(cons
     for (int head = 0; head < p.n; ++head) {
       const uint32_t dst = map_to_rank(smem_u32(&sm.inbox[rank][0]), (uint32_t)head);
       const uint32_t bar = map_to_rank(smem_u32(&sm.xbar[0]), (uint32_t)head);
-      for (int i = tid; i < REC; i += kAttnWarps * 32) st_async_cluster_f32(dst + 4u * (uint32_t)i, sm.rec[head][i], bar);
+      for (int i = tid; i < REC / 4; i += kAttnWarps * 32)  // 16 bytes per message
+        st_async_cluster_f32x4(dst + 16u * (uint32_t)i, *reinterpret_cast<const float4*>(&sm.rec[head][4 * i]), bar);
     }
     mbar_wait_bounded(&sm.xbar[0], 0, abort_flag, p.status, kStatusWaitTimeoutFull);
     if (tracer && live) p.trace[6] = global_timer_ns();
