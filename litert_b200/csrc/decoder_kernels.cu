@@ -186,8 +186,7 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_kernel(float* __r
   }
 }
 
-// The same stage for a decode step's rows of at most 2 * kNormThreads elements (even length, no tensor-parallel
-// exchange): a thread keeps its two neighbouring elements in registers from the load to the quantized bytes: no
+// The same stage for a decode step's rows of at most 2 * kNormThreads elements (even length): a thread keeps its two neighbouring elements in registers from the load to the quantized bytes: no
 // staging of the row in shared memory, the gains fetched before the dependency wait, one 16-bit store per thread.
 // Measured on B200 (one row of 2048, stamps of the device timer after the wait): the staged form spent 0.7 us in its
 // normalising loop (shared memory and gains per element) and 0.5 us in its quantizing loop, of 3.7 us.
@@ -197,12 +196,13 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_pair_kernel(float
                                                                           float eps, int m_alloc,
                                                                           int8_t* __restrict__ q_tiled,
                                                                           float* __restrict__ scales,
-                                                                          int32_t* __restrict__ zps) {
+                                                                          int32_t* __restrict__ zps, TpExchange xch) {
   __shared__ float red[32];
   __shared__ float2 s_mm[32];
   __shared__ float s_inv;
   __shared__ int s_zp, s_zero;
   pdl_launch_dependents();
+  const bool exchange = xch.tp_size > 1;  // the addend is the sum of the ranks' partial outputs, fetched from the peers
   const int b = blockIdx.x;
   const int i = 2 * (int)threadIdx.x;
   const bool have = i < d;  // d is even: both elements or none
@@ -213,11 +213,31 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_pair_kernel(float
 #pragma unroll 1
   for (int pass = 0; pass < 2; ++pass) {
     const bool live = pass == 1;
-    if (live) pdl_wait();
+    if (live) {
+      pdl_wait();
+      if (exchange) tp_handshake(xch, blockIdx.x == 0);
+    }
     float2 v = make_float2(0.0f, 0.0f), e = make_float2(0.0f, 0.0f);
     if (have) v = __ldcg(reinterpret_cast<const float2*>(hr + i));
-    if (have && dr) e = __ldcg(reinterpret_cast<const float2*>(dr + i));
-    if (dr) {
+    if (have && exchange) {
+      // every rank's partial is requested before the first is used; summed in rank order on every rank
+      float2 part[kMaxTpRanks];
+#pragma unroll
+      for (int j = 0; j < kMaxTpRanks; ++j) {
+        part[j] = make_float2(0.0f, 0.0f);
+        if (j < xch.tp_size) {
+          const float* pj = xch.partial[j] + (size_t)b * d + i;
+          part[j] = j == xch.tp_rank ? __ldcg(reinterpret_cast<const float2*>(pj)) : make_float2(ld_peer(pj), ld_peer(pj + 1));
+        }
+      }
+      e = part[0];
+#pragma unroll
+      for (int j = 1; j < kMaxTpRanks; ++j)
+        if (j < xch.tp_size) e = make_float2(__fadd_rn(e.x, part[j].x), __fadd_rn(e.y, part[j].y));
+    } else if (have && dr) {
+      e = __ldcg(reinterpret_cast<const float2*>(dr + i));
+    }
+    if (dr || exchange) {
       v.x = __fadd_rn(v.x, e.x);
       v.y = __fadd_rn(v.y, e.y);
       if (live && have) *reinterpret_cast<float2*>(hr + i) = v;
@@ -526,10 +546,10 @@ cudaError_t launch_add_norm_quant(float* h, const float* delta, const float* gai
   const TpExchange x = xch ? *xch : TpExchange();
   // a decode step's few rows: the widest block and a dry run; a prompt chunk's many rows: several rows per SM
   const bool many = batch > kLatencyRows;
-  if (!many && !xch && d % 2 == 0 && d_pad <= 2 * kNormThreads && (reinterpret_cast<uintptr_t>(h) & 7) == 0 &&
+  if (!many && d % 2 == 0 && d_pad <= 2 * kNormThreads && (reinterpret_cast<uintptr_t>(h) & 7) == 0 &&
       (reinterpret_cast<uintptr_t>(delta) & 7) == 0 && (reinterpret_cast<uintptr_t>(gain) & 7) == 0 && !tuning_env("B200_NORM_STAGED"))
     return launch_chained(add_norm_quant_pair_kernel, dim3(batch), dim3(kNormThreads), 0, s, h, delta, gain, d, d_pad, eps, m_alloc,
-                          q_tiled, scales, zps);
+                          q_tiled, scales, zps, x);
   int batched = 1;
   if (const char* e = tuning_env("B200_NORM_BATCHED")) batched = atoi(e);  // measurement knob
   return launch_chained(add_norm_quant_kernel, dim3(batch), dim3(many ? 256 : kNormThreads), sizeof(float) * d, s, h, delta, gain,
