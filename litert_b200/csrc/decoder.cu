@@ -88,6 +88,8 @@ struct b200_decoder {
   // partial | down-projection partial | argmax candidate pairs. proj / down_out point into it.
   DevBuf comm, gather;
   size_t off_epoch = 0, off_part_a = 0, off_part_b = 0, off_pairs = 0;
+  // message areas of the pushed exchanges (decode-sized batches): [tp_size][kTpPushRows * d_model] 8-byte messages each
+  size_t off_push_a = 0, off_push_b = 0, push_stride = 0;
   uint8_t* peer_comm[b200::kMaxTpRanks] = {nullptr};  // peers' exchange buffers mapped here (own entry: comm.p)
   bool peers_connected = false;
   bool peers_are_ipc = true;  // peer_comm entries came from cudaIpcOpenMemHandle (closed at destroy)
@@ -230,9 +232,21 @@ struct FusedInput {
 // pick: the greedy pick fused into the projection's epilogue (the LM head at up to 16 rows): the CTAs'
 // candidates go to arg_val / arg_idx, y may be null.
 cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_t* q_tiled, const float* scales,
-                   const int32_t* zps, float* y, const FusedInput* fused = nullptr, bool pick = false) {
+                   const int32_t* zps, float* y, const FusedInput* fused = nullptr, bool pick = false,
+                   int push_seq = -1) {
   FcParams p;
   memset(&p, 0, sizeof(p));
+  if (push_seq >= 0) {  // tensor-parallel, decode-sized: the outputs also go to every peer as messages
+    const b200_decoder_config& c = d->cfg;
+    const size_t off = (push_seq & 1) ? d->off_push_b : d->off_push_a;  // even: attention output, odd: down
+    for (int j = 0; j < c.tp_size; ++j)
+      p.push_out[j] = reinterpret_cast<uint2*>(d->peer_comm[j] + off) + (size_t)c.tp_rank * d->push_stride;
+    p.push_ranks = c.tp_size;
+    p.push_rank = c.tp_rank;
+    p.push_seq = push_seq;
+    p.push_per_step = 2 * c.n_layers + 1;
+    p.push_step_epoch = reinterpret_cast<const unsigned long long*>(d->comm.as<uint8_t>() + d->off_epoch);
+  }
   if (fused) {
     p.prologue = 1;
     p.pro_h_in = fused->h_in;
@@ -287,8 +301,12 @@ cudaError_t run_fc(b200_decoder* d, const Projection& pr, int batch, const int8_
 
 // The exchange whose sum the next consuming kernel needs: partials at byte offset `off` of every
 // rank's exchange buffer, `seq` = its number within the step.
-TpExchange make_exchange(const b200_decoder* d, int seq, size_t off) {
+TpExchange make_exchange(const b200_decoder* d, int seq, size_t off, bool pushed = false) {
   TpExchange x;
+  if (pushed) {
+    x.push_in = reinterpret_cast<const uint2*>(d->comm.as<uint8_t>() + (off == d->off_part_a ? d->off_push_a : d->off_push_b));
+    x.push_stride = (int)d->push_stride;
+  }
   const b200_decoder_config& c = d->cfg;
   x.tp_size = c.tp_size;
   x.tp_rank = c.tp_rank;
@@ -358,6 +376,15 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
   // sixth of the SMs in sequences the chunked kernels do better: 1.69 vs 1.86 ms per step at batch 32)
   const bool attn_one_launch = attn_env && batch * 8 <= device_sm_count() / 2 &&
                                attn_step_supported(d->hl, d->kvl, c.head_dim, c.kv_dtype == B200_DTYPE_I8 ? 1 : 0);
+  // Tensor-parallel exchange of decode-sized batches: the attention-output and down GEMVs push their partials to
+  // the peers as self-validating messages, and the norm stage that consumes the sum polls its own memory (no flag
+  // handshake, no fence, no remote read).
+  static const bool push_env = [] {
+    const char* e = tuning_env("B200_TP_PUSH");  // measurement knob: 0 keeps the flag handshake
+    return !(e && e[0] == '0');
+  }();
+  const bool push = push_env && fused && batch <= kTpPushRows && c.d_model % 2 == 0 && c.d_model <= 2048 &&
+                    fc_cluster_planned(batch, c.d_model, d->hl * c.head_dim) && fc_cluster_planned(batch, c.d_model, d->fl);
   float* hbuf[2] = {d->h.as<float>(), d->h2.as<float>()};
   int cur = 0;
   for (int l = 0; l < c.n_layers; ++l) {
@@ -367,7 +394,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
       if (!(skip & 16)) DEC_CUDA(run_fc(d, L.qkv, batch, nullptr, nullptr, nullptr, d->qkv.as<float>(), &fi));
       cur ^= 1;
     } else {
-      const TpExchange x = fused && l > 0 ? make_exchange(d, 2 * l - 1, d->off_part_b) : TpExchange();
+      const TpExchange x = fused && l > 0 ? make_exchange(d, 2 * l - 1, d->off_part_b, push) : TpExchange();
       if (!(skip & 1)) GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), l == 0 ? nullptr : d->down_out, L.norm1.as<float>(), batch,
                                      c.d_model, c.rms_eps, m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(),
                                      d->zp_d.as<int32_t>(), fused && l > 0 ? &x : nullptr, s));
@@ -436,14 +463,15 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
       }
       count(2);
     }
-    if (!(skip & 32)) DEC_CUDA(run_fc(d, L.o, batch, d->q_a.as<int8_t>(), d->sc_a.as<float>(), d->zp_a.as<int32_t>(), d->proj));
+    if (!(skip & 32)) DEC_CUDA(run_fc(d, L.o, batch, d->q_a.as<int8_t>(), d->sc_a.as<float>(), d->zp_a.as<int32_t>(), d->proj, nullptr,
+                                      false, push ? 2 * l : -1));
     if (int rc = reduce(d->proj, (size_t)batch * c.d_model)) return rc;
     if (fuse_norm) {
       const FusedInput fi{hbuf[cur], d->proj, L.norm2.as<float>(), hbuf[cur ^ 1]};
       if (!(skip & 64)) DEC_CUDA(run_fc(d, L.gate_up, batch, nullptr, nullptr, nullptr, d->gate_up.as<float>(), &fi));
       cur ^= 1;
     } else {
-      const TpExchange x = fused ? make_exchange(d, 2 * l, d->off_part_a) : TpExchange();
+      const TpExchange x = fused ? make_exchange(d, 2 * l, d->off_part_a, push) : TpExchange();
       if (!(skip & 1)) GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->proj, L.norm2.as<float>(), batch, c.d_model, c.rms_eps,
                                      m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(),
                                      fused ? &x : nullptr, s));
@@ -454,7 +482,8 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
     if (!(skip & 8)) GLUE_CUDA(launch_geglu_quant(d->gate_up.as<float>(), batch, d->fl, m_alloc, d->q_f.as<int8_t>(), d->sc_f.as<float>(),
                                 d->zp_f.as<int32_t>(), s));
     count();
-    if (!(skip & 128)) DEC_CUDA(run_fc(d, L.down, batch, d->q_f.as<int8_t>(), d->sc_f.as<float>(), d->zp_f.as<int32_t>(), d->down_out));
+    if (!(skip & 128)) DEC_CUDA(run_fc(d, L.down, batch, d->q_f.as<int8_t>(), d->sc_f.as<float>(), d->zp_f.as<int32_t>(), d->down_out,
+                                       nullptr, false, push ? 2 * l + 1 : -1));
     if (int rc = reduce(d->down_out, (size_t)batch * c.d_model)) return rc;
   }
   // One sequence batch on one GPU, at most 16 rows: the LM-head GEMV picks the greedy token in its own
@@ -470,7 +499,7 @@ int enqueue_step(b200_decoder* d, int batch, float* d_logits_out) {
     const FusedInput fi{hbuf[cur], d->down_out, d->final_norm.as<float>(), hbuf[cur ^ 1]};
     if (!(skip & 256)) DEC_CUDA(run_fc(d, d->lm_head, batch, nullptr, nullptr, nullptr, logits, &fi, fused_pick));
   } else {
-    const TpExchange x = fused ? make_exchange(d, 2 * c.n_layers - 1, d->off_part_b) : TpExchange();
+    const TpExchange x = fused ? make_exchange(d, 2 * c.n_layers - 1, d->off_part_b, push) : TpExchange();
     if (!(skip & 1)) GLUE_CUDA(launch_add_norm_quant(d->h.as<float>(), d->down_out, d->final_norm.as<float>(), batch, c.d_model, c.rms_eps,
                                    m_alloc, d->q_d.as<int8_t>(), d->sc_d.as<float>(), d->zp_d.as<int32_t>(),
                                    fused ? &x : nullptr, s));
@@ -734,7 +763,10 @@ int b200_decoder_create(const b200_decoder_config* config, void* stream, b200_de
     d->off_part_a = 512;
     d->off_part_b = d->off_part_a + part;
     d->off_pairs = d->off_part_b + part;
-    const size_t total = d->off_pairs + up(sizeof(float2) * B);
+    d->push_stride = (size_t)kTpPushRows * c.d_model;
+    d->off_push_a = d->off_pairs + up(sizeof(float2) * B);
+    d->off_push_b = d->off_push_a + up(sizeof(uint2) * d->push_stride * T);
+    const size_t total = d->off_push_b + up(sizeof(uint2) * d->push_stride * T);
     // whole 2 MiB pages, so that the exported allocation holds nothing else
     DEC_CUDA(d->comm.alloc((total + (2u << 20) - 1) / (2u << 20) * (2u << 20)));
     DEC_CUDA(cudaMemsetAsync(d->comm.p, 0, d->comm.bytes, d->stream));

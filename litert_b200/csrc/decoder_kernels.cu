@@ -213,13 +213,51 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_quant_pair_kernel(float
 #pragma unroll 1
   for (int pass = 0; pass < 2; ++pass) {
     const bool live = pass == 1;
+    const bool pushed = exchange && xch.push_in != nullptr;
     if (live) {
       pdl_wait();
-      if (exchange) tp_handshake(xch, blockIdx.x == 0);
+      if (exchange && !pushed) tp_handshake(xch, blockIdx.x == 0);
     }
     float2 v = make_float2(0.0f, 0.0f), e = make_float2(0.0f, 0.0f);
     if (have) v = __ldcg(reinterpret_cast<const float2*>(hr + i));
-    if (have && exchange) {
+    if (have && pushed) {
+      // The peers' GEMVs pushed their partials here as {value, epoch} messages: poll this rank's own memory until
+      // both of this thread's messages from every peer carry the exchange's epoch (bounded), then sum in rank order.
+      const uint32_t epoch32 =
+          (uint32_t)(*xch.step_epoch * (unsigned long long)xch.per_step + (unsigned long long)xch.seq + 1ull);
+      float2 part[kMaxTpRanks];
+#pragma unroll
+      for (int j = 0; j < kMaxTpRanks; ++j) {
+        part[j] = make_float2(0.0f, 0.0f);
+        if (j >= xch.tp_size) continue;
+        if (j == xch.tp_rank) {
+          part[j] = __ldcg(reinterpret_cast<const float2*>(xch.partial[j] + (size_t)b * d + i));
+          continue;
+        }
+        if (!live) continue;  // (the dry run has nothing to wait for)
+        const uint2* msg = xch.push_in + (size_t)j * xch.push_stride + (size_t)b * d + i;
+        uint32_t v0, e0, v1, e1;
+        const unsigned long long t0 = global_timer_ns();
+        const unsigned long long budget = wait_budget_ns(xch.status);
+        for (uint32_t spin = 0;; ++spin) {
+          asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v0), "=r"(e0) : "l"(msg) : "memory");
+          asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v1), "=r"(e1) : "l"(msg + 1) : "memory");
+          if (e0 == epoch32 && e1 == epoch32) break;
+          if ((spin & 15u) == 15u) {
+            if (*reinterpret_cast<volatile int*>(xch.status) != 0) break;  // after one wait has run out, give up at once
+            if (global_timer_ns() - t0 > budget) {
+              atomicCAS(xch.status, 0, kStatusTimeoutPeer);
+              break;
+            }
+          }
+        }
+        part[j] = make_float2(__uint_as_float(v0), __uint_as_float(v1));
+      }
+      e = part[0];
+#pragma unroll
+      for (int j = 1; j < kMaxTpRanks; ++j)
+        if (j < xch.tp_size) e = make_float2(__fadd_rn(e.x, part[j].x), __fadd_rn(e.y, part[j].y));
+    } else if (have && exchange) {
       // every rank's partial is requested before the first is used; summed in rank order on every rank
       float2 part[kMaxTpRanks];
 #pragma unroll
@@ -546,6 +584,9 @@ cudaError_t launch_add_norm_quant(float* h, const float* delta, const float* gai
   const TpExchange x = xch ? *xch : TpExchange();
   // a decode step's few rows: the widest block and a dry run; a prompt chunk's many rows: several rows per SM
   const bool many = batch > kLatencyRows;
+  const bool pair_ok = !many && d % 2 == 0 && d_pad <= 2 * kNormThreads && (reinterpret_cast<uintptr_t>(h) & 7) == 0 &&
+                       (reinterpret_cast<uintptr_t>(delta) & 7) == 0 && (reinterpret_cast<uintptr_t>(gain) & 7) == 0;
+  if (x.push_in && !pair_ok) return cudaErrorInvalidValue;  // pushed partials are only read by the register-resident kernel
   if (!many && d % 2 == 0 && d_pad <= 2 * kNormThreads && (reinterpret_cast<uintptr_t>(h) & 7) == 0 &&
       (reinterpret_cast<uintptr_t>(delta) & 7) == 0 && (reinterpret_cast<uintptr_t>(gain) & 7) == 0 && !tuning_env("B200_NORM_STAGED"))
     return launch_chained(add_norm_quant_pair_kernel, dim3(batch), dim3(kNormThreads), 0, s, h, delta, gain, d, d_pad, eps, m_alloc,

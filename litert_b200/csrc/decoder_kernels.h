@@ -25,7 +25,14 @@ struct TpExchange {
   const unsigned long long* flags_in = nullptr;          // this rank's flag array [kMaxTpRanks]
   const unsigned long long* step_epoch = nullptr;
   int* status = nullptr;
+  // Decode-sized rows (at most kTpPushRows): the producing GEMV has already PUSHED its partial into every peer's
+  // memory as 8-byte messages {value bits, low 32 bits of the epoch} (FcParams::push_out), so the consumer only
+  // polls its own memory until every message carries this exchange's epoch: no flag, no fence, no remote read.
+  // push_in: this rank's message area of the exchange, [tp_size][push_stride] messages (slot j from rank j).
+  const uint2* push_in = nullptr;
+  int push_stride = 0;
 };
+constexpr int kTpPushRows = 8;
 
 // step_epoch (optional): device counter advanced by one, the clock of the cross-rank exchanges.
 // positions / attn_len (optional): attn_len[b] = positions[b] + 1.

@@ -799,9 +799,27 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fc_cluster_kernel(const FcPar
     cluster_wait();  // phase 0
   }
   if (warp >= 2 && n_own < p.n) {
+    uint32_t epoch32 = 0;
+    if constexpr (EPI == kEpiHybridF32) {
+      if (p.push_ranks > 1)
+        epoch32 = (uint32_t)(*p.push_step_epoch * (unsigned long long)p.push_per_step + (unsigned long long)p.push_seq + 1ull);
+    }
     for (int col = col0; col < m_valid; col += col_step) {
       int32_t v = 0;
       for (int src = 0; src < split; ++src) v += red[(src * NB + col) * rows_per_owner + r_own];
+      if constexpr (EPI == kEpiHybridF32) {
+        if (p.push_ranks > 1) {
+          // the partial sum goes to every peer as a self-validating message (value and epoch in one 8-byte store)
+          const int32_t bits = compute_output<EPI>(p, v, rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[col], sh->in_aux[col]);
+          const size_t at = (size_t)(m_base + col) * p.n + n_own;
+          static_cast<float*>(p.y)[at] = __int_as_float(bits);
+          for (int j = 0; j < p.push_ranks; ++j)
+            if (j != p.push_rank)
+              asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p.push_out[j] + at), "r"((uint32_t)bits), "r"(epoch32)
+                           : "memory");
+          continue;
+        }
+      }
       store_output<EPI>(p, m_base + col, n_own, v, rs, wsc, bias_f, base_i, mult, shift, sh->in_scale[col], sh->in_aux[col]);
     }
   }
@@ -1345,6 +1363,7 @@ cudaError_t launch_cluster_one(const FcParams& p, int m_base, int split, cudaStr
     if (!fc_prologue_supported(p.m, p.k) || NB != 16 || m_base != 0) return cudaErrorInvalidValue;
     smem += (size_t)((p.k_tiles + split - 1) / split + 1) * L::kQBytes;
   }
+  if (p.push_ranks > 1 && (EPI != kEpiHybridF32 || m_base != 0 || !p.push_step_epoch)) return cudaErrorInvalidValue;
   return launch_chained_cluster(fc_cluster_kernel<NB, EPI>, dim3(p.n_tiles * split), dim3(kUmmaThreads), smem, split, s,
                                 p, m_base, split);
 }
@@ -1375,8 +1394,10 @@ cudaError_t launch_all(const FcParams& p, cudaStream_t s) {
   if (nb <= 64) {  // decode-sized: one pass, cluster split-K where the shape suits it
     const cudaError_t e = try_cluster_pass<EPI>(p, 0, nb, s);
     if (e != cudaErrorNotSupported) return e;
+    if (p.push_ranks > 1) return cudaErrorInvalidValue;  // only the cluster kernel pushes its outputs to the peers
     return launch_umma_nb<EPI>(p, 0, nb, 1, s);
   }
+  if (p.push_ranks > 1) return cudaErrorInvalidValue;
   const int sms = device_sm_count();
   if (p.m <= 128 && p.n_tiles * 2 < sms && p.m_alloc % 64 == 0) {
     // a little over one decode pass, few n tiles: 64 rows at a time through the cluster kernel
@@ -1428,6 +1449,16 @@ int device_sm_count() {
 int fc_argmax_ctas(int n) {
   const int sms = device_sm_count();
   return std::min(tiles_n(n), sms * UmmaBudget<16>::kCtasPerSm);
+}
+
+bool fc_cluster_planned(int m, int n, int k) {
+  if (m < 1 || m > 16) return false;
+  FcParams p;
+  memset(&p, 0, sizeof(p));
+  p.m = m, p.n = n, p.k = k;
+  p.n_tiles = tiles_n(n);
+  p.k_tiles = tiles_k8(k);
+  return plan_cluster_split<16, kEpiHybridF32>(p) != 0;
 }
 
 bool fc_prologue_supported(int m, int k) { return m >= 1 && m <= kPrologueMaxM && k >= 1 && k <= kPrologueMaxK; }

@@ -83,6 +83,12 @@ struct FcParams {
   float pro_eps;
   float* pro_scales_out;
   int32_t* pro_zps_out;
+  // Tensor-parallel push (hybrid float outputs of the cluster kernel, decode-sized m): besides y, every output
+  // also goes to each peer j != push_rank as one 8-byte message {float bits, low 32 bits of the exchange's
+  // epoch} at push_out[j][m * n + channel] (peer memory); epoch = *push_step_epoch * push_per_step + push_seq + 1.
+  uint2* push_out[8];
+  int push_ranks, push_rank, push_seq, push_per_step;
+  const unsigned long long* push_step_epoch;
   // measurement only: four %globaltimer stamps per launch (first CTA: entry, dependency wait passed,
   // exit; any CTA: latest exit), or null
   unsigned long long* trace;
@@ -112,6 +118,9 @@ cudaError_t launch_fc_i8_umma(const FcParams& p, FcEpilogue epi, cudaStream_t s)
 int umma_rows_per_pass(int m);
 // Whether FcParams::prologue can be used for these sizes (the tcgen05 kernels only).
 bool fc_prologue_supported(int m, int k);
+// Whether a hybrid projection of at most 16 rows runs on the cluster split-K kernel on the current device (the
+// kernel that can push its outputs to tensor-parallel peers, FcParams::push_out).
+bool fc_cluster_planned(int m, int n, int k);
 // Blockwise 4-bit weights, float out: the tcgen05 path (any m; q_tiled holds the quantized rows as
 // fp16 in the tiled layout, w4_rows_per_pass(m) rows per pass) ...
 cudaError_t launch_fc_w4(const FcParams& p, cudaStream_t s);
