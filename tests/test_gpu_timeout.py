@@ -58,6 +58,36 @@ def test_a_peer_that_never_arrives_times_out_and_the_decoder_recovers():
     d.close()
 
 
+def test_pushed_partials_that_never_arrive_time_out_too():
+    """The same absent peer at widths where the decode-sized exchange is the pushed one (the attention-output and
+    down projections run on the cluster kernel and send {value, epoch} messages; the norm stage polls its own
+    memory): the messages of rank 1 never come, the poll gives up after its budget, the step reports the time-out
+    and the context stays usable."""
+    from litert_b200 import _lib
+    from litert_b200 import decoder as dec
+    from litert_b200._lib import B200Error
+
+    lib = _lib.load()
+    cfg = dict(n_layers=2, d_model=512, n_heads=4, n_kv_heads=1, head_dim=128, d_ff=1024, vocab=1000)
+    d = dec.Decoder(cfg, max_seq=16, max_batch=2, weights=dec.make_weights(cfg, seed=5), tp_size=2, tp_rank=0)
+    nbytes = lib.b200_decoder_exchange_bytes(d.handle)
+    absent_peer = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    ptrs = (ctypes.c_void_p * 2)(None, absent_peer.data_ptr())
+    assert lib.b200_decoder_connect_peer_pointers(d.handle, ptrs) == 0
+    assert lib.b200_decoder_set_wait_budget(d.handle, 2_000_000) == 0  # 2 ms
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    with pytest.raises(B200Error, match="wait ran out"):
+        d.step(np.asarray([3, 5], np.int32))
+    assert time.perf_counter() - t0 < 5.0
+    assert float(torch.ones(8, device="cuda").sum().item()) == 8.0
+    # rank 0 pushed its own partials into the absent peer's message area: proof that this path ran
+    # (a flag handshake would have left one 8-byte flag there, the push two rows of 512 messages)
+    area = absent_peer.cpu().numpy()
+    assert np.count_nonzero(area) > 1000, "the cluster kernel's messages landed in the peer's buffer"
+    d.close()
+
+
 def test_status_word_of_the_op_level_workspace_can_be_cleared():
     """b200_clear_status after a recorded time-out: ops on the same workspace work again (the status word
     is written by hand here: the op-level kernels have no wait that a test could starve)."""
